@@ -1,0 +1,331 @@
+// Attention: split-K GQA decode attention (one query token over f32 / f16 / Q8 KV) and the causal
+// prefill attention. crates/kernels/src/lib.rs:1056-1248; decode_attention.metal, flash_attention.metal.
+//
+// KV cache rows are [position][kv head][128] in the cache's type; a Q8 row is 128 int8 codes followed
+// by four f16 scales (136 bytes, crates/quant/src/qtype.rs:81-111).
+#include "brasa_internal.h"
+
+namespace {
+
+constexpr int D = 128;
+constexpr int TS = D + 4;  // padded row of the shared f32 tile
+
+// Loads rows [key0, key0+nkeys) of one kv head into ts[key][d] as f32.
+template <int KV>
+__device__ __forceinline__ void load_tile(const uint8_t *cache, float *ts, uint32_t key0, uint32_t nkeys, uint32_t hkv, uint32_t kh) {
+    if (KV == BRASA_KV_F32) {
+        for (uint32_t i = threadIdx.x; i < nkeys * (D / 4); i += blockDim.x) {
+            uint32_t key = i / (D / 4), v4 = i % (D / 4);
+            float4 v = reinterpret_cast<const float4 *>(cache + ((size_t)(key0 + key) * hkv + kh) * D * 4)[v4];
+            float *o = ts + key * TS + v4 * 4;
+            o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+        }
+    } else if (KV == BRASA_KV_F16) {
+        for (uint32_t i = threadIdx.x; i < nkeys * (D / 8); i += blockDim.x) {
+            uint32_t key = i / (D / 8), v8 = i % (D / 8);
+            uint4 v = reinterpret_cast<const uint4 *>(cache + ((size_t)(key0 + key) * hkv + kh) * D * 2)[v8];
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+            float *o = ts + key * TS + v8 * 8;
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __half22float2(h[j]);
+                o[2 * j] = f.x; o[2 * j + 1] = f.y;
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < nkeys * (D / 8); i += blockDim.x) {
+            uint32_t key = i / (D / 8), v8 = i % (D / 8);
+            const uint8_t *row = cache + ((size_t)(key0 + key) * hkv + kh) * BRASA_KV_Q8_ROW;
+            uint2 v = reinterpret_cast<const uint2 *>(row)[v8];
+            float d = __half2float(reinterpret_cast<const __half *>(row + 128)[v8 / 4]);
+            const int8_t *c = reinterpret_cast<const int8_t *>(&v);
+            float *o = ts + key * TS + v8 * 8;
+            for (int j = 0; j < 8; ++j) o[j] = d * (float)c[j];
+        }
+    }
+}
+
+// One block per (128-key chunk, kv head): all G query heads of the group share the K and V reads.
+// partial layout per (head, chunk): m, l, acc[128]  (crates/kernels/src/lib.rs:1335).
+template <int KV>
+__global__ void __launch_bounds__(128) decode_partial_kernel(const float *q, const uint8_t *kc, const uint8_t *vc, float *partials, uint32_t hq,
+                                                             uint32_t hkv, uint32_t lk, float scale) {
+    extern __shared__ __align__(16) float sm[];
+    float *ts = sm;                    // [128][TS]
+    float *qs = ts + 128 * TS;         // [G][128]
+    float *ps = qs + 8 * D;            // [G][128] scores, then probabilities
+    float *red = ps + 8 * 128;         // [8]
+    const uint32_t chunk = blockIdx.x, kh = blockIdx.y, G = hq / hkv, chunks = gridDim.x;
+    const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    for (uint32_t i = t; i < G * D; i += 128) qs[i] = q[(size_t)kh * G * D + i];
+    load_tile<KV>(kc, ts, key0, nkeys, hkv, kh);
+    __syncthreads();
+    for (uint32_t g = 0; g < G; ++g) {
+        float s = -INFINITY;
+        if ((uint32_t)t < nkeys) {
+            const float4 *kr = reinterpret_cast<const float4 *>(ts + t * TS);
+            const float4 *qr = reinterpret_cast<const float4 *>(qs + g * D);
+            float a = 0.0f;
+#pragma unroll 8
+            for (int i = 0; i < D / 4; ++i) {
+                float4 kk = kr[i], qq = qr[i];
+                a = fmaf(qq.x, kk.x, a); a = fmaf(qq.y, kk.y, a); a = fmaf(qq.z, kk.z, a); a = fmaf(qq.w, kk.w, a);
+            }
+            s = a * scale;
+        }
+        ps[g * 128 + t] = s;
+    }
+    __syncthreads();
+    load_tile<KV>(vc, ts, key0, nkeys, hkv, kh);  // K is no longer needed
+    for (uint32_t g = 0; g < G; ++g) {
+        float s = ps[g * 128 + t];
+        float m = s;
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        float p = (uint32_t)t < nkeys ? expf(s - m) : 0.0f;
+        ps[g * 128 + t] = p;
+        float l = p;
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        __syncthreads();
+        if (lane == 0) red[4 + warp] = l;
+        __syncthreads();
+        if (t == 0) {
+            float *out = partials + ((size_t)(kh * G + g) * chunks + chunk) * 130;
+            out[0] = m;
+            out[1] = (red[4] + red[5]) + (red[6] + red[7]);
+        }
+    }
+    __syncthreads();
+    for (uint32_t g = 0; g < G; ++g) {
+        float acc = 0.0f;
+        const float *pg = ps + g * 128;
+        for (uint32_t j = 0; j < nkeys; ++j) acc = fmaf(pg[j], ts[j * TS + t], acc);
+        partials[((size_t)(kh * G + g) * chunks + chunk) * 130 + 2 + t] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(128) decode_reduce_kernel(const float *partials, float *o, uint32_t chunks) {
+    const uint32_t h = blockIdx.x, t = threadIdx.x;
+    const float *p = partials + (size_t)h * chunks * 130;
+    float M = -INFINITY;
+    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, p[c * 130]);
+    float L = 0.0f, acc = 0.0f;
+    for (uint32_t c = 0; c < chunks; ++c) {
+        float w = expf(p[c * 130] - M);
+        L = fmaf(p[c * 130 + 1], w, L);
+        acc = fmaf(p[c * 130 + 2 + t], w, acc);
+    }
+    o[(size_t)h * D + t] = acc / L;
+}
+
+// Causal prefill attention, f32 arithmetic throughout. One block = 64 queries of one query head;
+// keys in tiles of 32. HALF_IO: Q*scale is rounded to f16 and the output is written as f16, like the
+// reference's PrefillPrecision::F16 (flash_attention.metal:213,320); otherwise Q stays f32, the
+// score is (q.k)*scale and the output is f32.
+template <int KV, bool HALF_IO>
+__global__ void __launch_bounds__(256) prefill_attn_kernel(const float *q, const uint8_t *kc, const uint8_t *vc, void *o, uint32_t tokens,
+                                                           uint32_t hq, uint32_t hkv, uint32_t pos0, float scale) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int QB = 64, KB = 32;
+    float *qs = sm;                 // [64][TS]
+    float *ks = qs + QB * TS;       // [32][TS]
+    float *vs = ks + KB * TS;       // [32][TS]
+    float *ss = vs + KB * TS;       // [64][33]
+    float *mrow = ss + QB * 33;     // [64] running max
+    float *lrow = mrow + QB;        // [64] running sum
+    float *crow = lrow + QB;        // [64] correction of this tile
+    // longest query blocks first (they see the most keys)
+    const uint32_t qblocks = gridDim.x, qb = qblocks - 1 - blockIdx.x, h = blockIdx.y, kh = h / (hq / hkv);
+    const uint32_t q0 = qb * QB, nq = min((uint32_t)QB, tokens - q0);
+    const int t = threadIdx.x, ty = t >> 4, tx = t & 15;  // ty: 4 queries, tx: 2 keys / 8 dims
+    for (uint32_t i = t; i < QB * D; i += 256) {
+        uint32_t r = i / D, d = i % D;
+        float v = r < nq ? q[((size_t)(q0 + r) * hq + h) * D + d] : 0.0f;
+        if (HALF_IO) v = __half2float(__float2half_rn(v * scale));
+        qs[r * TS + d] = v;
+    }
+    if (t < QB) { mrow[t] = -INFINITY; lrow[t] = 0.0f; }
+    float oacc[4][8];
+    for (int a = 0; a < 4; ++a)
+        for (int b = 0; b < 8; ++b) oacc[a][b] = 0.0f;
+    const uint32_t last_key = pos0 + q0 + nq - 1;  // inclusive
+    __syncthreads();
+    for (uint32_t k0 = 0; k0 <= last_key; k0 += KB) {
+        uint32_t nk = min((uint32_t)KB, last_key + 1 - k0);
+        load_tile<KV>(kc, ks, k0, nk, hkv, kh);
+        load_tile<KV>(vc, vs, k0, nk, hkv, kh);
+        __syncthreads();
+        float s[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+        for (int d = 0; d < D; d += 4) {
+            float4 k0v = *reinterpret_cast<const float4 *>(ks + (2 * tx) * TS + d);
+            float4 k1v = *reinterpret_cast<const float4 *>(ks + (2 * tx + 1) * TS + d);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                float4 qv = *reinterpret_cast<const float4 *>(qs + (4 * ty + a) * TS + d);
+                s[a][0] = fmaf(qv.x, k0v.x, s[a][0]); s[a][0] = fmaf(qv.y, k0v.y, s[a][0]);
+                s[a][0] = fmaf(qv.z, k0v.z, s[a][0]); s[a][0] = fmaf(qv.w, k0v.w, s[a][0]);
+                s[a][1] = fmaf(qv.x, k1v.x, s[a][1]); s[a][1] = fmaf(qv.y, k1v.y, s[a][1]);
+                s[a][1] = fmaf(qv.z, k1v.z, s[a][1]); s[a][1] = fmaf(qv.w, k1v.w, s[a][1]);
+            }
+        }
+        for (int a = 0; a < 4; ++a)
+            for (int b = 0; b < 2; ++b) {
+                uint32_t key = k0 + 2 * tx + b, qi = 4 * ty + a;
+                bool ok = (2u * tx + b) < nk && qi < nq && key <= pos0 + q0 + qi;
+                float v = HALF_IO ? s[a][b] : s[a][b] * scale;
+                ss[qi * 33 + 2 * tx + b] = ok ? v : -INFINITY;
+            }
+        __syncthreads();
+        if (t < QB) {
+            float m_old = mrow[t], m = m_old;
+            for (int j = 0; j < KB; ++j) m = fmaxf(m, ss[t * 33 + j]);
+            float l = 0.0f;
+            for (int j = 0; j < KB; ++j) {
+                float p = m == -INFINITY ? 0.0f : expf(ss[t * 33 + j] - m);
+                ss[t * 33 + j] = p;
+                l += p;
+            }
+            float c = m_old == -INFINITY ? 0.0f : expf(m_old - m);
+            crow[t] = c;
+            lrow[t] = lrow[t] * c + l;
+            mrow[t] = m;
+        }
+        __syncthreads();
+        for (int a = 0; a < 4; ++a) {
+            float c = crow[4 * ty + a];
+            for (int b = 0; b < 8; ++b) oacc[a][b] *= c;
+        }
+        for (uint32_t j = 0; j < nk; ++j) {
+            float4 v0 = *reinterpret_cast<const float4 *>(vs + j * TS + 8 * tx);
+            float4 v1 = *reinterpret_cast<const float4 *>(vs + j * TS + 8 * tx + 4);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                float p = ss[(4 * ty + a) * 33 + j];
+                oacc[a][0] = fmaf(p, v0.x, oacc[a][0]); oacc[a][1] = fmaf(p, v0.y, oacc[a][1]);
+                oacc[a][2] = fmaf(p, v0.z, oacc[a][2]); oacc[a][3] = fmaf(p, v0.w, oacc[a][3]);
+                oacc[a][4] = fmaf(p, v1.x, oacc[a][4]); oacc[a][5] = fmaf(p, v1.y, oacc[a][5]);
+                oacc[a][6] = fmaf(p, v1.z, oacc[a][6]); oacc[a][7] = fmaf(p, v1.w, oacc[a][7]);
+            }
+        }
+        __syncthreads();
+    }
+    for (int a = 0; a < 4; ++a) {
+        uint32_t qi = 4 * ty + a;
+        if (qi >= nq) continue;
+        float inv = 1.0f / lrow[qi];
+        size_t base = ((size_t)(q0 + qi) * hq + h) * D + 8 * tx;
+        for (int b = 0; b < 8; ++b) {
+            float v = oacc[a][b] * inv;
+            if (HALF_IO) reinterpret_cast<__half *>(o)[base + b] = __float2half_rn(v);
+            else reinterpret_cast<float *>(o)[base + b] = v;
+        }
+    }
+}
+
+int32_t check_decode(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o,
+                     const brasa_attn_shape &sh) {
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, sh.tokens == 1, "decode_attention is for one token");
+    BRASA_REQUIRE(ctx, sh.dim == 128, "decode_attention needs head_dim 128");
+    BRASA_REQUIRE(ctx, sh.hkv > 0 && sh.hq % sh.hkv == 0 && sh.hq / sh.hkv <= 8, "decode_attention: GQA group must divide and be <= 8");
+    BRASA_REQUIRE(ctx, sh.kv >= BRASA_KV_F32 && sh.kv <= BRASA_KV_Q8_0, "unknown KV type %d", sh.kv);
+    uint32_t lk = sh.pos0 + 1;
+    BRASA_REQUIRE(ctx, partials_len >= brasa_decode_partials_len(sh.hq, lk) && arg_fits(partials, partials_len * 4), "decode scratch too small");
+    uint64_t kvb = brasa_kv_bytes(sh.kv, (uint64_t)lk * sh.hkv * 128);
+    BRASA_REQUIRE(ctx, arg_fits(q, (uint64_t)sh.hq * 512) && arg_fits(o, (uint64_t)sh.hq * 512) && arg_fits(k, kvb) && arg_fits(v, kvb),
+                  "decode_attention: q, o or cache too small");
+    BRASA_REQUIRE(ctx, k.offset % 16 == 0 && v.offset % 16 == 0 || sh.kv == BRASA_KV_Q8_0, "decode_attention: misaligned cache");
+    return BRASA_OK;
+}
+
+int32_t decode_common(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o,
+                      brasa_attn_shape sh) {
+    BRASA_TRY(check_decode(cmd, q, k, v, partials, partials_len, o, sh));
+    brasa_ctx *ctx = cmd->ctx;
+    uint32_t lk = sh.pos0 + 1, chunks = (lk + 127) / 128;
+    float scale = 1.0f / sqrtf((float)sh.dim);
+    size_t smem = (128 * TS + 8 * D + 8 * 128 + 16) * sizeof(float);
+    dim3 grid(chunks, sh.hkv);
+    const float *qp = (const float *)arg_ptr(q);
+    float *pp = (float *)arg_ptr(partials);
+#define LAUNCH_DEC(KVT)                                                                                                   \
+    do {                                                                                                                  \
+        static bool done = false;                                                                                         \
+        if (!done) {                                                                                                      \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            done = true;                                                                                                  \
+        }                                                                                                                 \
+        decode_partial_kernel<KVT><<<grid, 128, smem, ctx->stream>>>(qp, arg_ptr(k), arg_ptr(v), pp, sh.hq, sh.hkv, lk, scale); \
+    } while (0)
+    if (sh.kv == BRASA_KV_F32) LAUNCH_DEC(BRASA_KV_F32);
+    else if (sh.kv == BRASA_KV_F16) LAUNCH_DEC(BRASA_KV_F16);
+    else LAUNCH_DEC(BRASA_KV_Q8_0);
+#undef LAUNCH_DEC
+    BRASA_TRY(brasa_post_launch(cmd, "decode_partial"));
+    decode_reduce_kernel<<<sh.hq, 128, 0, ctx->stream>>>(pp, (float *)arg_ptr(o), chunks);
+    return brasa_post_launch(cmd, "decode_reduce");
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t brasa_k_decode_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o,
+                                 brasa_attn_shape shape) {
+    if (!cmd) return BRASA_EINVAL;
+    return decode_common(cmd, q, k, v, partials, partials_len, o, shape);
+}
+
+int32_t brasa_k_decode_attention_lanes(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len,
+                                       brasa_arg o, brasa_attn_shape shape) {
+    if (!cmd) return BRASA_EINVAL;
+    BRASA_REQUIRE(cmd->ctx, brasa_gqa_supported(shape.hq, shape.hkv), "decode_attention_lanes: GQA group not in {1, 2, 4, 8}");
+    return decode_common(cmd, q, k, v, partials, partials_len, o, shape);
+}
+
+int32_t brasa_k_flash_attention_with(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o, brasa_attn_shape sh, int32_t precision) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, sh.dim == 128, "flash_attention needs head_dim 128");
+    BRASA_REQUIRE(ctx, sh.hkv > 0 && sh.hq % sh.hkv == 0, "hq must be a multiple of hkv");
+    BRASA_REQUIRE(ctx, sh.kv >= BRASA_KV_F32 && sh.kv <= BRASA_KV_Q8_0, "unknown KV type %d", sh.kv);
+    BRASA_REQUIRE(ctx, precision == BRASA_PREFILL_F16 || precision == BRASA_PREFILL_F32, "unknown precision %d", precision);
+    if (sh.tokens == 0) return BRASA_OK;
+    uint64_t lk = (uint64_t)sh.pos0 + sh.tokens;
+    uint64_t kvb = brasa_kv_bytes(sh.kv, lk * sh.hkv * 128);
+    uint64_t qn = (uint64_t)sh.tokens * sh.hq * 128;
+    bool half_io = precision == BRASA_PREFILL_F16;
+    BRASA_REQUIRE(ctx, arg_fits(q, qn * 4) && arg_fits(o, qn * (half_io ? 2 : 4)) && arg_fits(k, kvb) && arg_fits(v, kvb), "flash_attention: buffers too small");
+    float scale = 1.0f / sqrtf((float)sh.dim);
+    size_t smem = ((64 + 32 + 32) * TS + 64 * 33 + 3 * 64) * sizeof(float);
+    dim3 grid((sh.tokens + 63) / 64, sh.hq);
+#define LAUNCH_FA(KVT, H)                                                                                                    \
+    do {                                                                                                                     \
+        static bool done = false;                                                                                            \
+        if (!done) {                                                                                                         \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<KVT, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            done = true;                                                                                                     \
+        }                                                                                                                    \
+        prefill_attn_kernel<KVT, H><<<grid, 256, smem, ctx->stream>>>((const float *)arg_ptr(q), arg_ptr(k), arg_ptr(v), arg_ptr(o), sh.tokens, \
+                                                                      sh.hq, sh.hkv, sh.pos0, scale);                      \
+    } while (0)
+    if (half_io) {
+        if (sh.kv == BRASA_KV_F32) LAUNCH_FA(BRASA_KV_F32, true);
+        else if (sh.kv == BRASA_KV_F16) LAUNCH_FA(BRASA_KV_F16, true);
+        else LAUNCH_FA(BRASA_KV_Q8_0, true);
+    } else {
+        if (sh.kv == BRASA_KV_F32) LAUNCH_FA(BRASA_KV_F32, false);
+        else if (sh.kv == BRASA_KV_F16) LAUNCH_FA(BRASA_KV_F16, false);
+        else LAUNCH_FA(BRASA_KV_Q8_0, false);
+    }
+#undef LAUNCH_FA
+    return brasa_post_launch(cmd, "prefill_attention");
+}
+
+int32_t brasa_k_flash_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o_f16, brasa_attn_shape shape) {
+    return brasa_k_flash_attention_with(cmd, q, k, v, o_f16, shape, BRASA_PREFILL_F16);
+}
+
+}  // extern "C"

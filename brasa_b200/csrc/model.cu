@@ -1,0 +1,640 @@
+// Qwen3 dense model and generation session on the device
+// (crates/models/src/qwen3.rs, crates/runtime/src/session.rs).
+//
+// Per layer (T tokens from position pos0):
+//   h = RMSNorm(x); q, k, v = W h; q, k = per-head RMSNorm then RoPE; K, V -> cache;
+//   o = attention(q, K, V); x += Wo o; h = RMSNorm(x); x += Wdown (silu(Wgate h) * Wup h)
+// Activations are f32. With more than GEMV_MAX_TOKENS tokens the projections run as GEMMs whose
+// inputs are f16 (PrefillPrecision::F16) and attention takes Q*scale in f16; with fewer they run as
+// GEMVs on f32 inputs. One token takes the fused decode path: RMSNorm folded into the GEMVs, the
+// residual adds folded into the next GEMV's input stage.
+#include <string.h>
+
+#include <chrono>
+
+#include "brasa_internal.h"
+#include "host_util.h"
+
+int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
+                          const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
+                          int epilogue);
+int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
+
+namespace {
+
+constexpr uint32_t GEMV_MAX_TOKENS = 8;  // qwen3.rs:276
+
+struct Matrix {
+    brasa_buf *buf = nullptr;
+    brasa_qmatrix q{};
+};
+
+struct Layer {
+    brasa_buf *attn_norm, *q_norm, *k_norm, *ffn_norm;
+    Matrix wq, wk, wv, wo, gate, up, down;
+};
+
+inline brasa_arg A(brasa_buf *b, uint64_t off = 0) { return brasa_arg{b, off}; }
+inline float *F(brasa_buf *b, uint64_t off_floats = 0) { return (float *)b->ptr + off_floats; }
+
+}  // namespace
+
+struct brasa_model {
+    brasa_ctx *ctx = nullptr;
+    brasa_config cfg{};
+    brasa_limits limits{};
+    int32_t prefill_precision = BRASA_PREFILL_F16;
+    Matrix embed, head;  // head aliases embed when tied
+    brasa_buf *final_norm = nullptr;
+    std::vector<Layer> layers;
+    brasa_buf *rope_cos = nullptr, *rope_sin = nullptr;
+    brasa_buf *kc = nullptr, *vc = nullptr;  // [layers, cap, kv_heads, head_dim] in the cache type
+    uint32_t cap = 0;
+    // workspace
+    brasa_buf *x = nullptr, *x2 = nullptr, *h = nullptr, *q = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr, *xh = nullptr,
+              *gate = nullptr, *up = nullptr, *ids = nullptr, *norm_out = nullptr, *ss = nullptr, *partials = nullptr, *logits = nullptr,
+              *next_id = nullptr, *out_ids = nullptr;
+    uint64_t partials_len = 0;
+    brasa_allocated alloc{};
+    std::vector<brasa_buf *> owned;
+    uint32_t *pinned_id = nullptr;  // pinned host word for the per-step token read
+};
+
+namespace {
+
+int32_t cfg_from_json(brasa_ctx *ctx, const brasa::Json &c, brasa_config *out, std::string &err) {
+    auto u = [&](const char *k, uint32_t *v) {
+        const brasa::Json *j = c.get(k);
+        if (!j || j->kind != brasa::Json::Num) {
+            err = std::string("config.json: missing ") + k;
+            return false;
+        }
+        *v = (uint32_t)j->inum;
+        return true;
+    };
+    const brasa::Json *mt = c.get("model_type");
+    if (!mt || mt->kind != brasa::Json::Str || mt->str != "qwen3") {
+        err = "model_type is not qwen3";
+        return false;
+    }
+    const brasa::Json *tie = c.get("tie_word_embeddings");
+    out->tied = (tie && tie->kind == brasa::Json::Bool && tie->b) ? 1 : 0;
+    if (!u("hidden_size", &out->hidden) || !u("num_hidden_layers", &out->layers) || !u("num_attention_heads", &out->heads) ||
+        !u("num_key_value_heads", &out->kv_heads) || !u("head_dim", &out->head_dim) || !u("intermediate_size", &out->ffn) ||
+        !u("vocab_size", &out->vocab) || !u("max_position_embeddings", &out->max_position))
+        return false;
+    const brasa::Json *e = c.get("rms_norm_eps"), *th = c.get("rope_theta");
+    out->eps = e && e->kind == brasa::Json::Num ? (float)e->num : 1e-6f;
+    out->rope_theta = th && th->kind == brasa::Json::Num ? th->num : 1e6;
+    (void)ctx;
+    return true;
+}
+
+int32_t alloc_buf(brasa_model *m, uint64_t bytes, brasa_buf **out, uint64_t *account) {
+    BRASA_TRY(brasa_buf_alloc(m->ctx, bytes, out));
+    m->owned.push_back(*out);
+    if (account) *account += brasa_plan_buffer_bytes(bytes);
+    return BRASA_OK;
+}
+
+int32_t load_f32(brasa_model *m, const brasa::BrasaFile &f, const std::string &name, uint64_t n, brasa_buf **out) {
+    brasa_ctx *ctx = m->ctx;
+    const brasa::TensorInfo *t = f.tensor(name);
+    if (!t) return brasa_fail(ctx, BRASA_EIO, "missing tensor %s", name.c_str());
+    if (t->dtype != "f32" || t->numel() != n) return brasa_fail(ctx, BRASA_EIO, "%s: expected %llu f32 values", name.c_str(), (unsigned long long)n);
+    BRASA_TRY(alloc_buf(m, t->nbytes, out, &m->alloc.weights));
+    return brasa_buf_upload(*out, 0, f.data(*t), t->nbytes);
+}
+
+// Uploads a quantised matrix and regroups it into the tiled layout when its shape allows.
+int32_t load_matrix(brasa_model *m, const brasa::BrasaFile &f, const std::string &name, uint32_t rows, uint32_t cols, brasa_buf *staging, Matrix *out) {
+    brasa_ctx *ctx = m->ctx;
+    const brasa::TensorInfo *t = f.tensor(name);
+    if (!t) return brasa_fail(ctx, BRASA_EIO, "missing tensor %s", name.c_str());
+    int qt = brasa::dtype_qtype(t->dtype);
+    if (qt < 0) return brasa_fail(ctx, BRASA_EIO, "%s: expected a quantised tensor", name.c_str());
+    if (t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != cols)
+        return brasa_fail(ctx, BRASA_EIO, "%s: unexpected shape", name.c_str());
+    BRASA_TRY(alloc_buf(m, t->nbytes, &out->buf, &m->alloc.weights));
+    out->q.data = A(out->buf);
+    out->q.qtype = qt;
+    out->q.rows = rows;
+    out->q.cols = cols;
+    if (tiled_ok(qt, rows, cols)) {
+        if (brasa_buf_bytes(staging) < t->nbytes) return brasa_fail(ctx, BRASA_EINVAL, "staging buffer too small for %s", name.c_str());
+        BRASA_TRY(brasa_buf_upload(staging, 0, f.data(*t), t->nbytes));
+        brasa_cmd *cmd;
+        BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+        int32_t rc = brasa_k_repack(cmd, qt, A(staging), A(out->buf), rows, cols);
+        int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+        BRASA_TRY(rc);
+        BRASA_TRY(rc2);
+        out->q.layout = BRASA_LAYOUT_TILED;
+    } else {
+        BRASA_TRY(brasa_buf_upload(out->buf, 0, f.data(*t), t->nbytes));
+        out->q.layout = BRASA_LAYOUT_FILE;
+    }
+    return BRASA_OK;
+}
+
+struct KvView {
+    brasa_arg k, v;
+};
+// K and V of layer li from position pos.
+KvView kv_at(brasa_model *m, uint32_t li, uint32_t pos) {
+    uint64_t kvd = (uint64_t)m->cfg.kv_heads * m->cfg.head_dim;
+    uint64_t off = brasa_kv_bytes(m->limits.kv, ((uint64_t)li * m->cap + pos) * kvd);
+    return KvView{A(m->kc, off), A(m->vc, off)};
+}
+
+int32_t matmul(brasa_model *m, brasa_cmd *cmd, const Matrix &w, brasa_arg x, brasa_arg y, uint32_t tokens, bool x_is_half) {
+    if (tokens <= GEMV_MAX_TOKENS) return brasa_k_gemv(cmd, w.q, x, y, tokens);
+    return brasa_k_gemm_with(cmd, w.q, x, y, tokens, x_is_half ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32);
+}
+
+int32_t precision_for(brasa_model *m, uint32_t tokens) { return tokens <= GEMV_MAX_TOKENS ? BRASA_PREFILL_F32 : m->prefill_precision; }
+
+// Layer li for `tokens` > 1 tokens from pos0 (also used for a single token by run_layers when asked
+// for the unfused order). Input and output in ws.x.
+int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32_t tokens, uint32_t pos0) {
+    const brasa_config &c = m->cfg;
+    Layer &l = m->layers[li];
+    const bool half_io = precision_for(m, tokens) == BRASA_PREFILL_F16;
+    const uint32_t H = c.hidden;
+    brasa_arg xin;
+    if (half_io) {
+        BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.attn_norm), A(m->xh), tokens, H, c.eps));
+        xin = A(m->xh);
+    } else {
+        BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.attn_norm), A(m->norm_out), tokens, H, c.eps));
+        xin = A(m->norm_out);
+    }
+    BRASA_TRY(matmul(m, cmd, l.wq, xin, A(m->q), tokens, half_io));
+    BRASA_TRY(matmul(m, cmd, l.wk, xin, A(m->k_new), tokens, half_io));
+    BRASA_TRY(matmul(m, cmd, l.wv, xin, A(m->v_new), tokens, half_io));
+    brasa_attn_shape sh{tokens, c.heads, c.kv_heads, c.head_dim, pos0, m->limits.kv};
+    KvView dst = kv_at(m, li, pos0), all = kv_at(m, li, 0);
+    brasa_arg qkv[3] = {A(m->q), A(m->k_new), A(m->v_new)}, norms[2] = {A(l.q_norm), A(l.k_norm)}, dsts[2] = {dst.k, dst.v};
+    BRASA_TRY(brasa_k_qk_norm_rope_store(cmd, m->limits.kv, qkv, norms, c.eps, A(m->rope_cos), A(m->rope_sin), c.head_dim, m->limits.ctx, dsts, sh));
+    brasa_arg attn = half_io ? A(m->xh) : A(m->attn);
+    if (tokens == 1) {
+        BRASA_TRY(brasa_k_decode_attention(cmd, A(m->q), all.k, all.v, A(m->partials), m->partials_len, A(m->attn), sh));
+    } else {
+        BRASA_TRY(brasa_k_flash_attention_with(cmd, A(m->q), all.k, all.v, attn, sh, half_io ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32));
+    }
+    BRASA_TRY(matmul(m, cmd, l.wo, attn, A(m->h), tokens, half_io));
+    BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)tokens * H));
+    brasa_arg act;
+    if (half_io) {
+        BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), tokens, H, c.eps));
+        BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), A(m->xh), tokens));
+        act = A(m->xh);
+    } else {
+        BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.ffn_norm), A(m->norm_out), tokens, H, c.eps));
+        BRASA_TRY(matmul(m, cmd, l.gate, A(m->norm_out), A(m->gate), tokens, false));
+        BRASA_TRY(matmul(m, cmd, l.up, A(m->norm_out), A(m->up), tokens, false));
+        BRASA_TRY(brasa_k_swiglu(cmd, A(m->gate), A(m->up), A(m->gate), (uint64_t)tokens * c.ffn));
+        act = A(m->gate);
+    }
+    BRASA_TRY(matmul(m, cmd, l.down, act, A(m->h), tokens, half_io));
+    return brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)tokens * H);
+}
+
+bool decode_fused_ok(brasa_model *m) {
+    for (Layer &l : m->layers)
+        for (const Matrix *w : {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down})
+            if (w->q.layout != BRASA_LAYOUT_TILED || w->q.qtype != BRASA_Q4_0) return false;
+    return m->head.q.layout == BRASA_LAYOUT_TILED && (m->head.q.qtype == BRASA_Q4_0 || m->head.q.qtype == BRASA_Q6_0) &&
+           m->cfg.heads / m->cfg.kv_heads <= 8;
+}
+
+// One token through all layers, fused decode order. The residual stream alternates between ws.x and
+// ws.x2: a GEMV that consumes "x + h" writes the sum to the other buffer. Leaves logits in ws.logits.
+// first_layer/last_layer allow run_layers to use the same code.
+int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t pos0, uint32_t layer_begin, uint32_t layer_end, bool with_head) {
+    const brasa_config &c = m->cfg;
+    brasa_buf *xc = m->x, *xo = m->x2;
+    bool pending = false;  // ws.h holds a residual not yet added to xc
+    for (uint32_t li = layer_begin; li < layer_end; ++li) {
+        Layer &l = m->layers[li];
+        {
+            brasa_qmatrix w[3] = {l.wq.q, l.wk.q, l.wv.q};
+            float *y[3] = {F(m->q), F(m->k_new), F(m->v_new)};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, y, F(xc), pending ? F(m->h) : nullptr, F(l.attn_norm), pending ? F(xo) : nullptr,
+                                        nullptr, 0, 1, c.eps, 0));
+            if (pending) std::swap(xc, xo);
+        }
+        brasa_attn_shape sh{1, c.heads, c.kv_heads, c.head_dim, pos0, m->limits.kv};
+        KvView dst = kv_at(m, li, pos0), all = kv_at(m, li, 0);
+        brasa_arg qkv[3] = {A(m->q), A(m->k_new), A(m->v_new)}, norms[2] = {A(l.q_norm), A(l.k_norm)}, dsts[2] = {dst.k, dst.v};
+        BRASA_TRY(brasa_k_qk_norm_rope_store(cmd, m->limits.kv, qkv, norms, c.eps, A(m->rope_cos), A(m->rope_sin), c.head_dim, m->limits.ctx, dsts, sh));
+        BRASA_TRY(brasa_k_decode_attention(cmd, A(m->q), all.k, all.v, A(m->partials), m->partials_len, A(m->attn), sh));
+        {
+            float *y[1] = {F(m->h)};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, 0));
+        }
+        {
+            brasa_qmatrix w[2] = {l.gate.q, l.up.q};
+            float *y[2] = {F(m->gate), nullptr};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, y, F(xc), F(m->h), F(l.ffn_norm), F(xo), nullptr, 0, 1, c.eps, 1));
+            std::swap(xc, xo);
+        }
+        {
+            float *y[1] = {F(m->h)};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, 0));
+        }
+        pending = true;
+    }
+    if (with_head) {
+        float *y[1] = {F(m->logits)};
+        BRASA_TRY(brasa_gemv_launch(cmd, m->head.q.qtype, 1, &m->head.q, y, F(xc), pending ? F(m->h) : nullptr, F(m->final_norm),
+                                    pending ? F(xo) : nullptr, nullptr, 0, 1, c.eps, 0));
+        if (pending) std::swap(xc, xo);
+        pending = false;
+    }
+    if (pending) {  // run_layers: materialise x + h
+        BRASA_TRY(brasa_k_add(cmd, A(xc), A(m->h), A(xc), c.hidden));
+    }
+    if (xc != m->x) BRASA_CUDA(m->ctx, cudaMemcpyAsync(m->x->ptr, xc->ptr, (size_t)c.hidden * 4, cudaMemcpyDeviceToDevice, m->ctx->stream));
+    return BRASA_OK;
+}
+
+int32_t check_tokens(brasa_model *m, uint32_t tokens, uint32_t pos0) {
+    if (tokens == 0 || tokens > m->limits.max_tokens)
+        return brasa_fail(m->ctx, BRASA_EINVAL, "%u tokens per forward; the maximum is %u", tokens, m->limits.max_tokens);
+    if ((uint64_t)pos0 + tokens > m->limits.ctx)
+        return brasa_fail(m->ctx, BRASA_EINVAL, "position %llu outside the context (%u)", (unsigned long long)pos0 + tokens, m->limits.ctx);
+    return BRASA_OK;
+}
+
+// Enqueues a whole forward for ids already in ws.ids; logits of the last logit_rows positions end
+// up in ws.logits.
+int32_t encode_forward(brasa_model *m, brasa_cmd *cmd, uint32_t tokens, uint32_t pos0, uint32_t logit_rows) {
+    const brasa_config &c = m->cfg;
+    BRASA_TRY(brasa_k_embed(cmd, m->embed.q, A(m->ids), A(m->x), tokens));
+    if (tokens == 1 && decode_fused_ok(m)) return encode_decode_token(m, cmd, pos0, 0, c.layers, true);
+    for (uint32_t li = 0; li < c.layers; ++li) BRASA_TRY(encode_layer_prefill(m, cmd, li, tokens, pos0));
+    uint32_t first = tokens - logit_rows;
+    BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x, (uint64_t)first * c.hidden * 4), A(m->final_norm), A(m->norm_out), logit_rows, c.hidden, c.eps));
+    return brasa_k_gemv(cmd, m->head.q, A(m->norm_out), A(m->logits), logit_rows);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t brasa_model_shape_from_file(const char *path, brasa_model_shape *shape, brasa_config *cfg, char *err, uint64_t err_len) {
+    std::string e;
+    auto f = brasa::BrasaFile::open(path ? path : "", e);
+    brasa_config c{};
+    if (f && f->family() != "qwen3") { e = "family " + f->family() + " is not supported"; f.reset(); }
+    if (f && !cfg_from_json(nullptr, f->config(), &c, e)) f.reset();
+    if (!f) {
+        if (err && err_len) snprintf(err, (size_t)err_len, "%s", e.c_str());
+        return BRASA_EIO;
+    }
+    if (shape) {
+        uint64_t wb = 0;
+        for (auto &t : f->tensors()) wb += brasa_plan_buffer_bytes(t.nbytes);
+        *shape = brasa_model_shape{wb, c.layers, c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab};
+    }
+    if (cfg) *cfg = c;
+    if (err && err_len) err[0] = 0;
+    return BRASA_OK;
+}
+
+void brasa_model_free(brasa_model *m) {
+    if (!m) return;
+    for (brasa_buf *b : m->owned) brasa_buf_free(b);
+    if (m->pinned_id) cudaFreeHost(m->pinned_id);
+    delete m;
+}
+
+int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, brasa_model **out) {
+    if (!ctx || !path || !out) return BRASA_EINVAL;
+    *out = nullptr;
+    std::string e;
+    auto f = brasa::BrasaFile::open(path, e);
+    if (!f) return brasa_fail(ctx, BRASA_EIO, "%s", e.c_str());
+    if (f->family() != "qwen3") return brasa_fail(ctx, BRASA_EIO, "family %s is not supported", f->family().c_str());
+    brasa_config c{};
+    if (!cfg_from_json(ctx, f->config(), &c, e)) return brasa_fail(ctx, BRASA_EIO, "%s", e.c_str());
+    BRASA_REQUIRE(ctx, limits.ctx <= c.max_position, "context %u larger than the model's maximum (%u)", limits.ctx, c.max_position);
+    BRASA_REQUIRE(ctx, limits.ctx > 0 && limits.max_tokens > 0 && limits.max_logit_rows > 0, "limits must be positive");
+    BRASA_REQUIRE(ctx, limits.kv >= BRASA_KV_F32 && limits.kv <= BRASA_KV_Q8_0, "unknown KV type %d", limits.kv);
+    BRASA_REQUIRE(ctx, c.head_dim == 128, "the kernels need head_dim 128 (got %u)", c.head_dim);
+    BRASA_REQUIRE(ctx, c.kv_heads > 0 && c.heads % c.kv_heads == 0, "heads must be a multiple of kv heads");
+    if (!c.tied && !f->tensor("lm_head.weight")) return brasa_fail(ctx, BRASA_EIO, "untied model without lm_head.weight");
+
+    brasa_model *m = new brasa_model();
+    m->ctx = ctx;
+    m->cfg = c;
+    m->limits = limits;
+    int32_t rc = [&]() -> int32_t {
+        const uint32_t H = c.hidden, qd = c.heads * c.head_dim, kvd = c.kv_heads * c.head_dim, ffn = c.ffn;
+        uint64_t biggest = 0;
+        for (auto &t : f->tensors()) biggest = std::max<uint64_t>(biggest, t.nbytes);
+        brasa_buf *staging = nullptr;
+        BRASA_TRY(brasa_buf_alloc(ctx, biggest, &staging));
+        m->layers.resize(c.layers);
+        for (uint32_t i = 0; i < c.layers; ++i) {
+            auto n = [&](const char *s) { return "model.layers." + std::to_string(i) + "." + s; };
+            Layer &l = m->layers[i];
+            BRASA_TRY(load_f32(m, *f, n("input_layernorm.weight"), H, &l.attn_norm));
+            BRASA_TRY(load_matrix(m, *f, n("self_attn.q_proj.weight"), qd, H, staging, &l.wq));
+            BRASA_TRY(load_matrix(m, *f, n("self_attn.k_proj.weight"), kvd, H, staging, &l.wk));
+            BRASA_TRY(load_matrix(m, *f, n("self_attn.v_proj.weight"), kvd, H, staging, &l.wv));
+            BRASA_TRY(load_matrix(m, *f, n("self_attn.o_proj.weight"), H, qd, staging, &l.wo));
+            BRASA_TRY(load_f32(m, *f, n("self_attn.q_norm.weight"), c.head_dim, &l.q_norm));
+            BRASA_TRY(load_f32(m, *f, n("self_attn.k_norm.weight"), c.head_dim, &l.k_norm));
+            BRASA_TRY(load_f32(m, *f, n("post_attention_layernorm.weight"), H, &l.ffn_norm));
+            BRASA_TRY(load_matrix(m, *f, n("mlp.gate_proj.weight"), ffn, H, staging, &l.gate));
+            BRASA_TRY(load_matrix(m, *f, n("mlp.up_proj.weight"), ffn, H, staging, &l.up));
+            BRASA_TRY(load_matrix(m, *f, n("mlp.down_proj.weight"), H, ffn, staging, &l.down));
+        }
+        BRASA_TRY(load_matrix(m, *f, "model.embed_tokens.weight", c.vocab, H, staging, &m->embed));
+        if (m->embed.q.qtype != BRASA_Q8_0 && m->embed.q.qtype != BRASA_Q6_0)
+            return brasa_fail(ctx, BRASA_EIO, "the embedding table must be q8_0 or q6_0");
+        if (c.tied) m->head = m->embed;
+        else BRASA_TRY(load_matrix(m, *f, "lm_head.weight", c.vocab, H, staging, &m->head));
+        BRASA_TRY(load_f32(m, *f, "model.norm.weight", H, &m->final_norm));
+        // staging is not part of the steady-state footprint
+        m->owned.erase(std::remove(m->owned.begin(), m->owned.end(), staging), m->owned.end());
+        BRASA_TRY(brasa_buf_free(staging));
+
+        uint64_t *ws = &m->alloc.workspace;
+        std::vector<float> cs((size_t)limits.ctx * c.head_dim / 2), sn(cs.size());
+        BRASA_TRY(brasa_rope_table(c.rope_theta, c.head_dim, limits.ctx, cs.data(), sn.data()));
+        BRASA_TRY(alloc_buf(m, cs.size() * 4, &m->rope_cos, ws));
+        BRASA_TRY(alloc_buf(m, sn.size() * 4, &m->rope_sin, ws));
+        BRASA_TRY(brasa_buf_upload(m->rope_cos, 0, cs.data(), cs.size() * 4));
+        BRASA_TRY(brasa_buf_upload(m->rope_sin, 0, sn.data(), sn.size() * 4));
+
+        const uint64_t t = limits.max_tokens;
+        m->cap = (limits.ctx + BRASA_KV_ALIGN - 1) / BRASA_KV_ALIGN * BRASA_KV_ALIGN;
+        uint64_t kv_elems = (uint64_t)c.layers * m->cap * kvd;
+        BRASA_TRY(alloc_buf(m, brasa_kv_bytes(limits.kv, kv_elems), &m->kc, &m->alloc.kv));
+        BRASA_TRY(alloc_buf(m, brasa_kv_bytes(limits.kv, kv_elems), &m->vc, &m->alloc.kv));
+        BRASA_TRY(alloc_buf(m, t * H * 4, &m->x, ws));
+        BRASA_TRY(alloc_buf(m, t * H * 4, &m->x2, ws));
+        BRASA_TRY(alloc_buf(m, t * H * 4, &m->h, ws));
+        BRASA_TRY(alloc_buf(m, t * H * 4, &m->norm_out, ws));
+        BRASA_TRY(alloc_buf(m, t * qd * 4, &m->q, ws));
+        BRASA_TRY(alloc_buf(m, t * qd * 4, &m->attn, ws));
+        BRASA_TRY(alloc_buf(m, t * kvd * 4, &m->k_new, ws));
+        BRASA_TRY(alloc_buf(m, t * kvd * 4, &m->v_new, ws));
+        BRASA_TRY(alloc_buf(m, t * ffn * 4, &m->gate, ws));
+        BRASA_TRY(alloc_buf(m, t * ffn * 4, &m->up, ws));
+        BRASA_TRY(alloc_buf(m, 2 * t * std::max<uint64_t>(ffn, std::max<uint64_t>(qd, H)), &m->xh, ws));
+        BRASA_TRY(alloc_buf(m, t * 4, &m->ids, ws));
+        BRASA_TRY(alloc_buf(m, (uint64_t)brasa_norm_partials(H) * 4, &m->ss, ws));
+        m->partials_len = brasa_decode_partials_len(c.heads, limits.ctx);
+        BRASA_TRY(alloc_buf(m, m->partials_len * 4, &m->partials, ws));
+        BRASA_TRY(alloc_buf(m, (uint64_t)limits.max_logit_rows * c.vocab * 4, &m->logits, ws));
+        BRASA_TRY(alloc_buf(m, 64, &m->next_id, nullptr));
+        BRASA_TRY(alloc_buf(m, (uint64_t)limits.ctx * 4, &m->out_ids, nullptr));
+        BRASA_CUDA(ctx, cudaHostAlloc((void **)&m->pinned_id, 64, cudaHostAllocDefault));
+        return brasa_ctx_sync(ctx);
+    }();
+    if (rc != BRASA_OK) {
+        std::string keep = ctx->last_error;
+        brasa_model_free(m);
+        ctx->last_error = keep;
+        return rc;
+    }
+    *out = m;
+    return BRASA_OK;
+}
+
+int32_t brasa_model_config(brasa_model *m, brasa_config *out) {
+    if (!m || !out) return BRASA_EINVAL;
+    *out = m->cfg;
+    return BRASA_OK;
+}
+int32_t brasa_model_limits(brasa_model *m, brasa_limits *out) {
+    if (!m || !out) return BRASA_EINVAL;
+    *out = m->limits;
+    return BRASA_OK;
+}
+int32_t brasa_model_allocated(brasa_model *m, brasa_allocated *out) {
+    if (!m || !out) return BRASA_EINVAL;
+    *out = m->alloc;
+    return BRASA_OK;
+}
+int32_t brasa_model_set_prefill_precision(brasa_model *m, int32_t precision) {
+    if (!m) return BRASA_EINVAL;
+    BRASA_REQUIRE(m->ctx, precision == BRASA_PREFILL_F16 || precision == BRASA_PREFILL_F32, "unknown precision %d", precision);
+    m->prefill_precision = precision;
+    return BRASA_OK;
+}
+
+int32_t brasa_model_forward(brasa_model *m, const uint32_t *ids, uint32_t tokens, uint32_t pos0, uint32_t logit_rows, float *logits,
+                            double *gpu_seconds) {
+    if (!m || !ids) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_TRY(check_tokens(m, tokens, pos0));
+    BRASA_REQUIRE(ctx, logit_rows >= 1 && logit_rows <= std::min(tokens, m->limits.max_logit_rows), "logit_rows %u is not valid", logit_rows);
+    for (uint32_t i = 0; i < tokens; ++i) BRASA_REQUIRE(ctx, ids[i] < m->cfg.vocab, "token id %u outside the vocabulary", ids[i]);
+    BRASA_CUDA(ctx, cudaMemcpyAsync(m->ids->ptr, ids, (size_t)tokens * 4, cudaMemcpyHostToDevice, ctx->stream));
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = encode_forward(m, cmd, tokens, pos0, logit_rows);
+    int32_t rc2 = brasa_cmd_wait(cmd, gpu_seconds);
+    BRASA_TRY(rc);
+    BRASA_TRY(rc2);
+    if (logits) BRASA_TRY(brasa_buf_download(m->logits, 0, logits, (uint64_t)logit_rows * m->cfg.vocab * 4));
+    return BRASA_OK;
+}
+
+int32_t brasa_model_run_layers(brasa_model *m, float *x, uint32_t tokens, uint32_t pos0, uint32_t layer_begin, uint32_t layer_end) {
+    if (!m || !x) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_TRY(check_tokens(m, tokens, pos0));
+    BRASA_REQUIRE(ctx, layer_begin <= layer_end && layer_end <= m->cfg.layers, "layer range");
+    uint64_t n = (uint64_t)tokens * m->cfg.hidden * 4;
+    BRASA_TRY(brasa_buf_upload(m->x, 0, x, n));
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = BRASA_OK;
+    if (tokens == 1 && decode_fused_ok(m)) rc = encode_decode_token(m, cmd, pos0, layer_begin, layer_end, false);
+    else
+        for (uint32_t li = layer_begin; li < layer_end && rc == BRASA_OK; ++li) rc = encode_layer_prefill(m, cmd, li, tokens, pos0);
+    int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+    BRASA_TRY(rc);
+    BRASA_TRY(rc2);
+    return brasa_buf_download(m->x, 0, x, n);
+}
+
+int32_t brasa_model_decode_greedy(brasa_model *m, uint32_t first, uint32_t pos0, uint32_t steps, uint32_t *out_ids, double *gpu_seconds) {
+    if (!m || !out_ids) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_REQUIRE(ctx, steps >= 1 && (uint64_t)pos0 + steps <= m->limits.ctx, "decode range outside the context");
+    BRASA_REQUIRE(ctx, first < m->cfg.vocab, "token id %u outside the vocabulary", first);
+    BRASA_TRY(brasa_buf_upload(m->ids, 0, &first, 4));
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = BRASA_OK;
+    for (uint32_t s = 0; s < steps && rc == BRASA_OK; ++s) {
+        rc = encode_forward(m, cmd, 1, pos0 + s, 1);
+        if (rc == BRASA_OK) rc = brasa_argmax_launch(cmd, F(m->logits), m->cfg.vocab, (uint32_t *)m->ids->ptr);
+        if (rc == BRASA_OK)
+            rc = brasa_check_cuda(ctx, cudaMemcpyAsync((uint32_t *)m->out_ids->ptr + s, m->ids->ptr, 4, cudaMemcpyDeviceToDevice, ctx->stream),
+                                  "copy of the chosen token");
+    }
+    int32_t rc2 = brasa_cmd_wait(cmd, gpu_seconds);
+    BRASA_TRY(rc);
+    BRASA_TRY(rc2);
+    return brasa_buf_download(m->out_ids, 0, out_ids, (uint64_t)steps * 4);
+}
+
+int32_t brasa_model_read_kv(brasa_model *m, uint32_t layer, int32_t which_v, uint32_t pos_begin, uint32_t pos_end, void *dst, uint64_t dst_bytes) {
+    if (!m || !dst) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_REQUIRE(ctx, layer < m->cfg.layers && pos_begin <= pos_end && pos_end <= m->limits.ctx, "read_kv: range");
+    uint64_t kvd = (uint64_t)m->cfg.kv_heads * m->cfg.head_dim;
+    uint64_t off = brasa_kv_bytes(m->limits.kv, ((uint64_t)layer * m->cap + pos_begin) * kvd);
+    uint64_t n = brasa_kv_bytes(m->limits.kv, (uint64_t)(pos_end - pos_begin) * kvd);
+    BRASA_REQUIRE(ctx, dst_bytes >= n, "read_kv: destination too small");
+    return brasa_buf_download(which_v ? m->vc : m->kc, off, dst, n);
+}
+
+}  // extern "C"
+
+// ---- session ------------------------------------------------------------------------------------
+
+struct brasa_session {
+    brasa_ctx *ctx = nullptr;
+    brasa_model *model = nullptr;
+    std::vector<uint32_t> cached;  // tokens whose K and V are in the cache
+    std::vector<uint32_t> stop_ids;
+    bool ignore_stop = false;
+    std::vector<float> logits;
+};
+
+extern "C" {
+
+int32_t brasa_session_create(brasa_ctx *ctx, const char *path, brasa_limits limits, uint64_t budget_bytes, brasa_session **out) {
+    if (!ctx || !path || !out) return BRASA_EINVAL;
+    *out = nullptr;
+    brasa_model_shape shape;
+    brasa_config cfg;
+    char err[512];
+    if (brasa_model_shape_from_file(path, &shape, &cfg, err, sizeof err) != BRASA_OK) return brasa_fail(ctx, BRASA_EIO, "%s", err);
+    brasa_session_shape ss{limits.ctx, limits.max_tokens, limits.max_logit_rows, limits.kv};
+    // the plan is checked before anything is loaded: a rejection allocates nothing
+    BRASA_TRY(brasa_plan_check(ctx, &shape, &ss, budget_bytes, nullptr, nullptr));
+    brasa_model *m = nullptr;
+    BRASA_TRY(brasa_model_load(ctx, path, limits, &m));
+    brasa_session *s = new brasa_session();
+    s->ctx = ctx;
+    s->model = m;
+    s->logits.resize(cfg.vocab);
+    *out = s;
+    return BRASA_OK;
+}
+
+void brasa_session_free(brasa_session *s) {
+    if (!s) return;
+    brasa_model_free(s->model);
+    delete s;
+}
+
+brasa_model *brasa_session_model(brasa_session *s) { return s ? s->model : nullptr; }
+
+int32_t brasa_session_reset(brasa_session *s) {
+    if (!s) return BRASA_EINVAL;
+    s->cached.clear();
+    return BRASA_OK;
+}
+
+int32_t brasa_session_set_stop_ids(brasa_session *s, const uint32_t *ids, uint32_t n, int32_t ignore_stop) {
+    if (!s || (!ids && n)) return BRASA_EINVAL;
+    s->stop_ids.assign(ids, ids + n);
+    s->ignore_stop = ignore_stop != 0;
+    return BRASA_OK;
+}
+
+int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_t prompt_len, uint32_t max_new, brasa_sampling_params params,
+                               brasa_token_cb on_token, void *user, uint32_t *out_ids, brasa_gen_stats *stats) {
+    if (!s || !prompt) return BRASA_EINVAL;
+    brasa_ctx *ctx = s->ctx;
+    brasa_model *m = s->model;
+    const brasa_limits lim = m->limits;
+    using clk = std::chrono::steady_clock;
+    auto ms_since = [](clk::time_point t0) { return std::chrono::duration<double, std::milli>(clk::now() - t0).count(); };
+    BRASA_REQUIRE(ctx, prompt_len > 0, "empty prompt");
+    BRASA_REQUIRE(ctx, prompt_len < lim.ctx, "the prompt has %u tokens and the context is %u", prompt_len, lim.ctx);
+    // longest common prefix with what the cache holds; the last prompt token is always recomputed
+    uint32_t common = 0;
+    while (common < s->cached.size() && common < prompt_len && s->cached[common] == prompt[common]) ++common;
+    common = std::min(common, prompt_len - 1);
+    s->cached.resize(common);
+
+    const bool greedy = params.temperature <= 0.0f;
+    // Greedy with nothing to mask keeps the logits on the device: the token is chosen there and only
+    // its id crosses to the host.
+    const bool device_pick = greedy && !(s->ignore_stop && !s->stop_ids.empty());
+    brasa::Sampler sampler(params.temperature, params.top_k, params.top_p, params.seed, m->cfg.vocab);
+
+    auto t0 = clk::now();
+    for (uint32_t off = common; off < prompt_len; off += lim.max_tokens) {
+        uint32_t n = std::min(lim.max_tokens, prompt_len - off);
+        bool last = off + n == prompt_len;
+        BRASA_TRY(brasa_model_forward(m, prompt + off, n, (uint32_t)s->cached.size(), 1, (last && !device_pick) ? s->logits.data() : nullptr, nullptr));
+        s->cached.insert(s->cached.end(), prompt + off, prompt + off + n);
+    }
+    double prefill_ms = ms_since(t0);
+
+    uint32_t generated = 0;
+    double ttft_ms = 0.0;
+    int32_t stop = 1;  // MaxTokens
+    auto t1 = clk::now();
+    while (generated < max_new) {
+        uint32_t next;
+        if (device_pick) {
+            brasa_cmd *cmd;
+            BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+            int32_t rc = brasa_argmax_launch(cmd, (const float *)m->logits->ptr, m->cfg.vocab, (uint32_t *)m->next_id->ptr);
+            if (rc == BRASA_OK)
+                rc = brasa_check_cuda(ctx, cudaMemcpyAsync(m->pinned_id, m->next_id->ptr, 4, cudaMemcpyDeviceToHost, ctx->stream), "token read");
+            int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+            BRASA_TRY(rc);
+            BRASA_TRY(rc2);
+            next = *m->pinned_id;
+        } else {
+            if (s->ignore_stop)
+                for (uint32_t id : s->stop_ids)
+                    if (id < s->logits.size()) s->logits[id] = -INFINITY;
+            next = sampler.sample(s->logits.data(), s->logits.size());
+        }
+        if (generated == 0) ttft_ms = ms_since(t0);
+        if (out_ids) out_ids[generated] = next;
+        ++generated;
+        if (std::find(s->stop_ids.begin(), s->stop_ids.end(), next) != s->stop_ids.end()) {
+            stop = 0;
+            break;
+        }
+        if (on_token && !on_token(user, next)) {
+            stop = 3;
+            break;
+        }
+        if (s->cached.size() >= lim.ctx) {
+            stop = 2;
+            break;
+        }
+        BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, device_pick ? nullptr : s->logits.data(), nullptr));
+        s->cached.push_back(next);
+    }
+    if (stats) {
+        stats->prompt_tokens = prompt_len;
+        stats->reused_tokens = common;
+        stats->generated = generated;
+        stats->stop = stop;
+        stats->prefill_ms = prefill_ms;
+        stats->ttft_ms = ttft_ms;
+        stats->decode_ms = ms_since(t1) - (ttft_ms - prefill_ms);
+    }
+    return BRASA_OK;
+}
+
+}  // extern "C"

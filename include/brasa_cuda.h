@@ -1,0 +1,263 @@
+/*
+ * brasa_cuda.h — C ABI of libbrasa_cuda.so: the CUDA (sm_100a) device layer and kernel set for the
+ * Qwen3 token loop. It stands where the reference's Metal device layer and kernel dispatch stand:
+ *
+ *   crates/metal/src/runtime.rs:134-425   Context, Buffer<T>, Arg, Command, Pending, GpuTiming
+ *   crates/kernels/src/lib.rs:391-1404    Kernels::* (one entry point per method, same order of
+ *                                         arguments), AttnShape, KvType, WeightType, helpers
+ *   crates/models/src/qwen3.rs:345-831    Qwen3::{load, forward, run_layers, allocated}
+ *   crates/runtime/src/session.rs:210-295 Session::generate (prefix reuse, prefill chunks, decode)
+ *   crates/runtime/src/sampler.rs:46-170  Sampler, Pcg32, argmax
+ *   crates/memory/src/planner.rs:57-95    plan / workspace_bytes / kv_bytes
+ *   crates/quant/src/brasa_file.rs:64-131 BrasaFile::{open, verify}
+ *
+ * Conventions: every function returns 0 on success or a negative BRASA_E* code; the message of the
+ * last failure on a context is read with brasa_last_error(). Nothing here aborts or traps:
+ * precondition violations (the reference's assert!) return BRASA_EINVAL. Functions on one context
+ * are not re-entrant; distinct contexts (distinct GPUs) are independent. Plain pointers and sizes
+ * only. Kernels are enqueued on the context's stream and run in submission order, like dispatches
+ * on one Metal command queue.
+ */
+#ifndef BRASA_CUDA_H
+#define BRASA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BRASA_OK 0
+#define BRASA_EINVAL (-1)   /* bad argument / shape precondition */
+#define BRASA_ENOMEM (-2)   /* device allocation failed */
+#define BRASA_ECUDA (-3)    /* CUDA runtime error (message has the detail) */
+#define BRASA_ETIMEOUT (-4) /* a bounded device-side wait ran out */
+#define BRASA_EIO (-5)      /* file errors: open, truncated, checksum */
+#define BRASA_EBUDGET (-6)  /* memory plan does not fit the budget */
+
+/* crates/kernels/src/lib.rs:85-90 (discriminants in declaration order) */
+enum brasa_weight_type { BRASA_Q4_0 = 0, BRASA_Q8_0 = 1, BRASA_Q6_0 = 2 };
+/* crates/kernels/src/lib.rs:93-101 */
+enum brasa_kv_type { BRASA_KV_F32 = 0, BRASA_KV_F16 = 1, BRASA_KV_Q8_0 = 2 };
+/* crates/kernels/src/lib.rs:1308-1314 */
+enum brasa_prefill_precision { BRASA_PREFILL_F16 = 0, BRASA_PREFILL_F32 = 1 };
+/* Byte layout of a quantised matrix in device memory.
+ * FILE  = the `.brasa` layout (crates/quant/src/qtype.rs:5-29): row-major blocks, scale then codes.
+ * TILED = the device layout produced by brasa_k_repack: same bytes, regrouped into micro-tiles of
+ *         64 rows x 128 columns in which codes, high-bit words and scales are separate, 16-byte
+ *         aligned planes (q4_0 and q6_0; rows % 64 == 0 and cols % 128 == 0). */
+enum brasa_layout { BRASA_LAYOUT_FILE = 0, BRASA_LAYOUT_TILED = 1 };
+
+typedef struct brasa_ctx brasa_ctx; /* crates/metal/src/runtime.rs:134 Context */
+typedef struct brasa_buf brasa_buf; /* crates/metal/src/runtime.rs:44  Buffer<T> (untyped bytes) */
+typedef struct brasa_cmd brasa_cmd; /* crates/metal/src/runtime.rs:306 Command / Pending */
+
+/* crates/metal/src/runtime.rs:255-295 Arg::buf / Arg::buf_at: a buffer and a byte offset. */
+typedef struct brasa_arg {
+    brasa_buf *buf;
+    uint64_t offset;
+} brasa_arg;
+
+/* crates/kernels/src/lib.rs:146-152 QMatrix, plus the device layout of `data`. */
+typedef struct brasa_qmatrix {
+    brasa_arg data;
+    int32_t qtype;  /* brasa_weight_type */
+    int32_t layout; /* brasa_layout */
+    uint32_t rows, cols;
+} brasa_qmatrix;
+
+/* crates/kernels/src/lib.rs:1354-1364 AttnShape */
+typedef struct brasa_attn_shape {
+    uint32_t tokens, hq, hkv, dim, pos0;
+    int32_t kv; /* brasa_kv_type */
+} brasa_attn_shape;
+
+/* ---- context, buffers, commands (crates/metal/src/runtime.rs) ------------------------------- */
+
+int32_t brasa_ctx_create(int32_t device, brasa_ctx **out);            /* Context::new :158 */
+void brasa_ctx_destroy(brasa_ctx *ctx);                               /* frees stragglers */
+const char *brasa_last_error(brasa_ctx *ctx);
+int32_t brasa_ctx_device(brasa_ctx *ctx);
+int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total_bytes);
+int32_t brasa_ctx_sync(brasa_ctx *ctx);
+/* cudaStream_t of the context, for callers that order their own work (NCCL, torch) against it. */
+void *brasa_ctx_stream(brasa_ctx *ctx);
+
+int32_t brasa_buf_alloc(brasa_ctx *ctx, uint64_t bytes, brasa_buf **out); /* zero-filled, :177 */
+int32_t brasa_buf_free(brasa_buf *buf);
+int32_t brasa_buf_upload(brasa_buf *buf, uint64_t offset, const void *src, uint64_t n);   /* buffer_from / as_mut_slice */
+int32_t brasa_buf_download(brasa_buf *buf, uint64_t offset, void *dst, uint64_t n);      /* as_slice */
+int32_t brasa_buf_fill(brasa_buf *buf, uint64_t offset, int32_t byte, uint64_t n);
+uint64_t brasa_buf_bytes(brasa_buf *buf);
+void *brasa_buf_ptr(brasa_buf *buf); /* device address */
+
+int32_t brasa_cmd_begin(brasa_ctx *ctx, brasa_cmd **out);     /* Context::command :237 */
+int32_t brasa_cmd_commit(brasa_cmd *cmd);                     /* Command::commit :379 */
+int32_t brasa_cmd_wait(brasa_cmd *cmd, double *gpu_seconds);  /* Pending::wait -> GpuTiming :411; frees cmd */
+
+/* ---- helpers (crates/kernels/src/lib.rs:1316-1404) ------------------------------------------ */
+
+#define BRASA_DECODE_CHUNK 128 /* DECODE_CHUNK :1332 */
+#define BRASA_KV_ALIGN 64      /* KV_ALIGN :1351 */
+#define BRASA_NORM_PREP_TG 256 /* NORM_PREP_TG :1343 */
+#define BRASA_KV_Q8_DIM 128    /* crates/quant/src/qtype.rs:81 */
+#define BRASA_KV_Q8_ROW 136    /* crates/quant/src/qtype.rs:83 */
+
+uint64_t brasa_decode_partials_len(uint32_t hq, uint32_t lk);  /* floats; :1335 */
+uint32_t brasa_norm_partials(uint32_t n);                      /* :1346 */
+int32_t brasa_gqa_supported(uint32_t hq, uint32_t hkv);        /* :1319 */
+uint64_t brasa_kv_bytes(int32_t kv, uint64_t n_elems);         /* KvType::bytes :113 */
+uint64_t brasa_qtype_nbytes(int32_t qtype, uint64_t n_elems);  /* QType::nbytes qtype.rs:22 */
+/* cos/sin(p * theta^(-2i/dim)), double precision, stored as float [max_pos, dim/2]; :1389 */
+int32_t brasa_rope_table(double theta, uint32_t dim, uint32_t max_pos, float *cos_out, float *sin_out);
+
+/* ---- weight layout and converter kernels (crates/quant/src/convert.rs:70-151) --------------- */
+
+/* FILE -> TILED and back; exact inverses, same byte count. rows % 64 == 0 and cols % 128 == 0;
+ * src and dst must not overlap. */
+int32_t brasa_k_repack(brasa_cmd *cmd, int32_t qtype, brasa_arg src_file, brasa_arg dst_tiled, uint32_t rows, uint32_t cols);
+int32_t brasa_k_unpack(brasa_cmd *cmd, int32_t qtype, brasa_arg src_tiled, brasa_arg dst_file, uint32_t rows, uint32_t cols);
+/* f32 -> q4_0 / q6_0 / q8_0 blocks in FILE layout, bit-identical to quant_q4_0/q6_0/q8_0. */
+int32_t brasa_k_quantize(brasa_cmd *cmd, int32_t qtype, brasa_arg src_f32, brasa_arg dst, uint64_t n);
+/* FILE-layout blocks -> f32, bit-identical to crates/quant/src/qtype.rs:141 dequantize. */
+int32_t brasa_k_dequantize(brasa_cmd *cmd, int32_t qtype, brasa_arg src, brasa_arg dst_f32, uint64_t n);
+/* Seeded N(0, std) floats (counter-based generator; same values for the same seed and offset on
+ * every GPU): the synthetic random-init weights of the benchmark configurations. */
+int32_t brasa_k_randn(brasa_cmd *cmd, brasa_arg dst_f32, uint64_t n, uint64_t seed, uint64_t stream_offset, float std);
+
+/* ---- kernels: one per Kernels method (crates/kernels/src/lib.rs) ---------------------------- */
+
+int32_t brasa_k_add(brasa_cmd *cmd, brasa_arg a, brasa_arg b, brasa_arg out, uint64_t n);                     /* :391 */
+int32_t brasa_k_swiglu(brasa_cmd *cmd, brasa_arg gate, brasa_arg up, brasa_arg out, uint64_t n);              /* :409 */
+int32_t brasa_k_swiglu_f16(brasa_cmd *cmd, brasa_arg gate, brasa_arg up, brasa_arg out_f16, uint64_t n);      /* :433 */
+int32_t brasa_k_rms_norm(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_arg out, uint32_t rows, uint32_t n, float eps);     /* :531 */
+int32_t brasa_k_rms_norm_f16(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_arg out_f16, uint32_t rows, uint32_t n, float eps); /* :511 */
+int32_t brasa_k_softmax(brasa_cmd *cmd, brasa_arg x, brasa_arg out, uint32_t rows, uint32_t n);               /* :550 */
+int32_t brasa_k_rope_neox(brasa_cmd *cmd, brasa_arg x, brasa_arg cos_t, brasa_arg sin_t, uint32_t table_dim, uint32_t table_max_pos,
+                          uint32_t tokens, uint32_t heads, uint32_t dim, uint32_t pos0);                      /* :569 */
+int32_t brasa_k_embed(brasa_cmd *cmd, brasa_qmatrix table, brasa_arg ids_u32, brasa_arg out, uint32_t tokens); /* :600 */
+/* x += h (when h.buf != NULL); xw = x*w; ss[i] = sum of x^2 over elements [256 i, 256 i + 256) :633 */
+int32_t brasa_k_add_norm_prep(brasa_cmd *cmd, brasa_arg x, brasa_arg h, brasa_arg w, brasa_arg xw, brasa_arg ss, uint32_t n);
+/* y = (W xw) / sqrt(sum(ss)/cols + eps) :663 */
+int32_t brasa_k_gemv_scaled(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg xw, brasa_arg ss, float eps, brasa_arg y);
+int32_t brasa_k_gemv_scaled3(brasa_cmd *cmd, const brasa_qmatrix w[3], brasa_arg xw, brasa_arg ss, float eps, const brasa_arg y[3]); /* :698 */
+int32_t brasa_k_gemv_scaled_swiglu(brasa_cmd *cmd, brasa_qmatrix gate, brasa_qmatrix up, brasa_arg xw, brasa_arg ss, float eps, brasa_arg y); /* :746 */
+int32_t brasa_k_gemv(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens);            /* :781 */
+int32_t brasa_k_gemv_simple(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens);     /* :813 */
+/* y[t, :] = W x[t, :]; precision F16: x is f16 and dequantised weights are rounded to f16 :856 */
+int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens, int32_t precision);
+int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg y, uint32_t tokens);        /* :842 */
+int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t count, brasa_arg x, const brasa_arg *ys, uint32_t tokens, int32_t precision); /* :872 */
+/* out_f16[t, :] = f16(silu(Wg x) * (Wu x)); gate/up scratch [tokens, rows] f32 may be used :455 */
+int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, brasa_arg x_f16, brasa_arg gate, brasa_arg up, brasa_arg out_f16, uint32_t tokens);
+/* per-head RMSNorm of q and k, RoPE of q and k, K and V written to the cache at pos0 :976 */
+int32_t brasa_k_qk_norm_rope_store(brasa_cmd *cmd, int32_t kv, const brasa_arg qkv[3], const brasa_arg norms[2], float eps,
+                                   brasa_arg cos_t, brasa_arg sin_t, uint32_t table_dim, uint32_t table_max_pos,
+                                   const brasa_arg dst[2], brasa_attn_shape shape);
+int32_t brasa_k_store_kv(brasa_cmd *cmd, int32_t kv, brasa_arg src, brasa_arg dst, uint64_t n);              /* :1029 */
+/* one query token at pos0 against keys 0..pos0; partials >= brasa_decode_partials_len floats :1056,:1110 */
+int32_t brasa_k_decode_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o, brasa_attn_shape shape);
+int32_t brasa_k_decode_attention_lanes(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o, brasa_attn_shape shape);
+/* causal GQA attention for a chunk; precision F16: Q*scale rounded to f16, o in f16 :1185 */
+int32_t brasa_k_flash_attention_with(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o, brasa_attn_shape shape, int32_t precision);
+int32_t brasa_k_flash_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o_f16, brasa_attn_shape shape); /* :1169 */
+
+/* ---- sampling on the device (crates/runtime/src/sampler.rs) --------------------------------- */
+
+/* first index of the maximum, NaN ignored, 0 when nothing exceeds -inf (:148-170); out: one u32 */
+int32_t brasa_k_argmax(brasa_cmd *cmd, brasa_arg logits, uint32_t n, brasa_arg out_u32);
+
+/* ---- memory planner (crates/memory/src/planner.rs) ------------------------------------------ */
+
+typedef struct brasa_model_shape { /* planner.rs:23-35 ModelShape (tensor bytes summed by the caller) */
+    uint64_t weight_bytes;
+    uint32_t layers, hidden, heads, kv_heads, head_dim, ffn, vocab;
+} brasa_model_shape;
+typedef struct brasa_session_shape { /* planner.rs:37-47 SessionShape */
+    uint32_t ctx, max_tokens, max_logit_rows;
+    int32_t kv; /* brasa_kv_type */
+} brasa_session_shape;
+typedef struct brasa_memory_plan { /* planner.rs:49-55 MemoryPlan */
+    uint64_t weights, kv, workspace, overhead, total;
+} brasa_memory_plan;
+uint64_t brasa_plan_buffer_bytes(uint64_t n); /* device allocation granularity; planner.rs:57 */
+int32_t brasa_plan(const brasa_model_shape *m, const brasa_session_shape *s, brasa_memory_plan *out); /* :83 */
+/* 0 when the plan fits budget_bytes (0 = device free memory minus a reserve); else BRASA_EBUDGET
+ * and *max_ctx_out = the largest context that fits (0 if none) :237-313 */
+int32_t brasa_plan_check(brasa_ctx *ctx, const brasa_model_shape *m, const brasa_session_shape *s, uint64_t budget_bytes,
+                         brasa_memory_plan *out, uint32_t *max_ctx_out);
+
+/* ---- model and session (crates/models/src/qwen3.rs, crates/runtime/src/session.rs) ---------- */
+
+typedef struct brasa_model brasa_model;     /* Qwen3 */
+typedef struct brasa_session brasa_session; /* Session */
+
+typedef struct brasa_limits { /* qwen3.rs:175-185 Limits */
+    uint32_t ctx, max_tokens, max_logit_rows;
+    int32_t kv; /* brasa_kv_type */
+} brasa_limits;
+
+typedef struct brasa_config { /* qwen3.rs:28-41 Config */
+    uint32_t hidden, layers, heads, kv_heads, head_dim, ffn, vocab, max_position;
+    float eps;
+    double rope_theta;
+    int32_t tied; /* 1: lm_head is the embedding table (the reference supports only this) */
+} brasa_config;
+
+typedef struct brasa_allocated { /* qwen3.rs:430 Allocated */
+    uint64_t weights, kv, workspace;
+} brasa_allocated;
+
+/* BrasaFile::open + verify over a path: structure checks always, sha256 when verify != 0. */
+int32_t brasa_file_check(const char *path, int32_t verify, char *err, uint64_t err_len);
+int32_t brasa_model_shape_from_file(const char *path, brasa_model_shape *shape, brasa_config *cfg, char *err, uint64_t err_len); /* qwen3.rs:79 */
+
+int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, brasa_model **out); /* Qwen3::load :345 */
+void brasa_model_free(brasa_model *m);
+int32_t brasa_model_config(brasa_model *m, brasa_config *out);
+int32_t brasa_model_limits(brasa_model *m, brasa_limits *out);
+int32_t brasa_model_allocated(brasa_model *m, brasa_allocated *out);
+int32_t brasa_model_set_prefill_precision(brasa_model *m, int32_t precision); /* qwen3.rs:310 */
+/* Qwen3::forward :763. ids: host u32[tokens]; logits: host f32[logit_rows * vocab] (may be NULL to
+ * leave them on the device); gpu_seconds: device time of the call (may be NULL). */
+int32_t brasa_model_forward(brasa_model *m, const uint32_t *ids, uint32_t tokens, uint32_t pos0, uint32_t logit_rows, float *logits, double *gpu_seconds);
+/* Qwen3::run_layers :743. x: host f32[tokens*hidden], replaced by the output. */
+int32_t brasa_model_run_layers(brasa_model *m, float *x, uint32_t tokens, uint32_t pos0, uint32_t layer_begin, uint32_t layer_end);
+/* Device-resident decode: feeds the token chosen on the device back as the next input for `steps`
+ * greedy steps starting from `first` at position pos0, without host round trips; out_ids: host
+ * u32[steps] read once at the end. Used for the HBM-resident throughput figure. */
+int32_t brasa_model_decode_greedy(brasa_model *m, uint32_t first, uint32_t pos0, uint32_t steps, uint32_t *out_ids, double *gpu_seconds);
+/* Copies K or V cache rows [pos_begin, pos_end) of a layer to the host in the cache's own bytes. */
+int32_t brasa_model_read_kv(brasa_model *m, uint32_t layer, int32_t which_v, uint32_t pos_begin, uint32_t pos_end, void *dst, uint64_t dst_bytes);
+
+typedef struct brasa_sampling_params { /* sampler.rs:5-13 SamplingParams */
+    float temperature; /* 0 = greedy */
+    uint32_t top_k;    /* 0 = no limit */
+    float top_p;       /* 1.0 = no limit */
+    uint64_t seed;
+} brasa_sampling_params;
+
+typedef struct brasa_gen_stats { /* session.rs:29-53 GenStats */
+    uint32_t prompt_tokens, reused_tokens, generated;
+    int32_t stop; /* 0 Stop, 1 MaxTokens, 2 ContextFull, 3 Cancelled */
+    double prefill_ms, ttft_ms, decode_ms;
+} brasa_gen_stats;
+
+/* return 0 to cancel (the reference's on_text returning false) */
+typedef int32_t (*brasa_token_cb)(void *user, uint32_t token);
+
+int32_t brasa_session_create(brasa_ctx *ctx, const char *path, brasa_limits limits, uint64_t budget_bytes, brasa_session **out); /* load_with_budget :150 */
+void brasa_session_free(brasa_session *s);
+brasa_model *brasa_session_model(brasa_session *s);
+int32_t brasa_session_reset(brasa_session *s); /* :182 */
+int32_t brasa_session_set_stop_ids(brasa_session *s, const uint32_t *ids, uint32_t n, int32_t ignore_stop);
+/* Session::generate :210. prompt: host ids; out_ids: host u32[max_new]. */
+int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_t prompt_len, uint32_t max_new,
+                               brasa_sampling_params params, brasa_token_cb on_token, void *user,
+                               uint32_t *out_ids, brasa_gen_stats *stats);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRASA_CUDA_H */

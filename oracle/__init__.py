@@ -94,9 +94,7 @@ def f32_to_f16_array(x) -> np.ndarray:
     """Bits (uint16) of RNE f32 -> f16, element-wise, through the C restatement."""
     x = _f32(x).ravel()
     out = np.empty(x.size, np.uint16)
-    fn = lib().bo_f32_to_f16
-    for i in range(x.size):
-        out[i] = fn(C.c_float(x[i]))
+    lib().bo_f32_to_f16_array(_p(x), C.c_size_t(x.size), _p(out))
     return out
 
 

@@ -73,6 +73,9 @@ uint16_t bo_f32_to_f16(float f) {
 }
 
 float bo_round_f16(float v) { return bo_f16_to_f32(bo_f32_to_f16(v)); }
+void bo_f32_to_f16_array(const float *x, size_t n, uint16_t *out) {
+    for (size_t i = 0; i < n; ++i) out[i] = bo_f32_to_f16(x[i]);
+}
 
 static inline uint16_t rd16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 static inline void wr16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }

@@ -1,0 +1,500 @@
+"""CUDA kernels against the CPU oracle, through the C ABI, on the reference's own test shapes, seeds
+and tolerances (crates/kernels/tests/{ops,attention,fused,elementwise}.rs; tolerances from
+crates/kernels/src/lib.rs:7-15). Integer and byte outputs must match bit for bit."""
+
+import numpy as np
+import pytest
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    import brasa_b200
+    return brasa_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(B):
+    c = B.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def K(B, ctx):
+    return B.Kernels(ctx)
+
+
+def run(ctx, fn):
+    cmd = ctx.command()
+    fn(cmd)
+    return cmd.wait()
+
+
+QT = {"q4_0": (O.Q4_0, 0), "q8_0": (O.Q8_0, 1), "q6_0": (O.Q6_0, 2)}  # oracle id, ABI id
+
+
+def tiled(B, ctx, K, name, raw, rows, cols):
+    src = ctx.buffer_from(raw)
+    dst = ctx.buffer(raw.nbytes)
+    run(ctx, lambda c: K.repack(c, QT[name][1], src, dst, rows, cols))
+    return B.QMatrix(dst, B.WeightType(QT[name][1]), rows, cols, B.Layout.TILED), dst
+
+
+# ---- layout and converter ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["q4_0", "q6_0"])
+def test_repack_is_a_bijection(B, ctx, K, name):
+    rows, cols = 192, 384
+    raw = O.Rng(5).qmatrix(QT[name][0], rows, cols)
+    _, t = tiled(B, ctx, K, name, raw, rows, cols)
+    packed = t.download(np.uint8)
+    assert packed.size == raw.size and not np.array_equal(packed, raw)
+    back = ctx.buffer(raw.nbytes)
+    run(ctx, lambda c: K.unpack(c, QT[name][1], t, back, rows, cols))
+    assert np.array_equal(back.download(np.uint8), raw)
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.repack(c, QT[name][1], t, back, 100, cols))
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q6_0", "q8_0"])
+def test_quantize_and_dequantize_bit_exact(B, ctx, K, name, golden_dir):
+    g = np.load(golden_dir / "quant_cases.npz")
+    rng = np.random.default_rng(7)
+    w = np.concatenate([g["w"].ravel(), (rng.standard_normal(32 * 4000) * 0.02).astype(np.float32),
+                        rng.standard_normal(32 * 500).astype(np.float32) * 50])
+    # exact half-way cases for every quantiser
+    d = np.float32(0.125)
+    w[:32] = (np.arange(32, dtype=np.float32) - 15.5) * d
+    src = ctx.buffer_from(w)
+    dst = ctx.buffer(O.nbytes(QT[name][0], w.size))
+    run(ctx, lambda c: K.quantize(c, QT[name][1], src, dst, w.size))
+    got = dst.download(np.uint8)
+    want = O.quantize(QT[name][0], w)
+    assert np.array_equal(got, want)
+    out = ctx.buffer(w.size * 4)
+    run(ctx, lambda c: K.dequantize(c, QT[name][1], dst, out, w.size))
+    assert np.array_equal(out.download(np.float32).view(np.uint32), O.dequantize(QT[name][0], want, w.size).view(np.uint32))
+
+
+def test_randn_is_seeded_and_normal(ctx, K):
+    n = 1 << 20
+    a, b = ctx.buffer(n * 4), ctx.buffer(n * 4)
+    run(ctx, lambda c: (K.randn(c, a, n, 42, 0, 0.02), K.randn(c, b, n, 42, 0, 0.02)))
+    x, y = a.download(np.float32), b.download(np.float32)
+    assert np.array_equal(x, y)
+    assert abs(x.mean()) < 1e-4 and abs(x.std() - 0.02) < 2e-4
+    run(ctx, lambda c: K.randn(c, b, n, 43, 0, 0.02))
+    assert not np.array_equal(x, b.download(np.float32))
+    # a later offset continues the same stream
+    run(ctx, lambda c: K.randn(c, b, n // 2, 42, n // 4, 0.02))
+    assert np.array_equal(b.download(np.float32)[: n // 2], x[n // 2:])
+
+
+# ---- element-wise --------------------------------------------------------------------------------
+
+def test_add_and_swiglu(B, ctx, K):
+    rng = O.Rng(1)
+    n = 9728 * 3 + 5
+    a, b = rng.vec(n, 4.0), rng.vec(n, 4.0)
+    ga, gb, go = ctx.buffer_from(a), ctx.buffer_from(b), ctx.buffer(n * 4)
+    run(ctx, lambda c: K.add(c, ga, gb, go, n))
+    assert np.array_equal(go.download(np.float32), O.add(a, b))
+    run(ctx, lambda c: K.swiglu(c, ga, gb, go, n))
+    got, want = go.download(np.float32), O.swiglu(a, b)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-30)) <= 1e-6
+    gh = ctx.buffer(n * 2)
+    run(ctx, lambda c: K.swiglu_f16(c, ga, gb, gh, n))
+    assert np.array_equal(gh.download(np.uint16), O.f32_to_f16_array(got))  # == f16(f32 result), bit for bit
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.add(c, ga, gb, go, n + 1))
+
+
+@pytest.mark.parametrize("rows,n", [(1, 2560), (37, 2560), (2048, 128), (3, 100)])
+def test_rms_norm(ctx, K, rows, n):
+    rng = O.Rng(11)
+    x, w = rng.vec(rows * n, 3.0), rng.vec(n, 2.0)
+    gx, gw, go, gh = ctx.buffer_from(x), ctx.buffer_from(w), ctx.buffer(rows * n * 4), ctx.buffer(rows * n * 2)
+    run(ctx, lambda c: (K.rms_norm(c, gx, gw, go, rows, n, 1e-6), K.rms_norm_f16(c, gx, gw, gh, rows, n, 1e-6)))
+    got, want = go.download(np.float32), O.rms_norm(x, w, n, 1e-6)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-6)) <= 1e-5
+    assert np.array_equal(gh.download(np.uint16), O.f32_to_f16_array(got))
+
+
+def test_softmax(ctx, K):
+    rng = O.Rng(12)
+    for rows, n in [(4, 1000), (32, 129), (1, 16384)]:
+        x = rng.vec(rows * n, 8.0)
+        gx, go = ctx.buffer_from(x), ctx.buffer(rows * n * 4)
+        run(ctx, lambda c: K.softmax(c, gx, go, rows, n))
+        got, want = go.download(np.float32), O.softmax(x, n)
+        assert np.max(np.abs(got - want) / np.maximum(want, 1e-12)) <= 1e-5
+
+
+@pytest.mark.parametrize("pos0", [0, 3, 40944])
+def test_rope(B, ctx, K, pos0):
+    rng = O.Rng(13)
+    tokens, heads, dim = 4, 5, 128
+    table = B.RopeTable(ctx, 1e6, dim, pos0 + tokens)
+    cos, sin = O.rope_table(1e6, dim, pos0 + tokens)
+    x = rng.vec(tokens * heads * dim, 2.0)
+    gx = ctx.buffer_from(x)
+    run(ctx, lambda c: K.rope_neox(c, gx, table, tokens, heads, dim, pos0))
+    got, want = gx.download(np.float32), O.rope_neox(x, heads, dim, pos0, cos, sin)
+    xv = x.reshape(-1, dim)
+    bound = 1e-6 * (np.abs(xv) + np.abs(np.roll(xv, 64, axis=1))).ravel()
+    assert np.all(np.abs(got - want) <= bound + 1e-12)
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.rope_neox(c, gx, table, tokens, heads, dim, pos0 + 1))
+
+
+def test_embed_exact(B, ctx, K):
+    rng = O.Rng(14)
+    vocab, h = 256, 384
+    ids = np.array([0, 255, 17, 17, 128, 64, 63], dtype=np.uint32)
+    gi = ctx.buffer_from(ids)
+    for name in ("q6_0", "q8_0"):
+        raw = rng.qmatrix(QT[name][0], vocab, h)
+        want = O.embed(QT[name][0], raw, h, ids)
+        out = ctx.buffer(ids.size * h * 4)
+        m = B.QMatrix(ctx.buffer_from(raw), B.WeightType(QT[name][1]), vocab, h)
+        run(ctx, lambda c: K.embed(c, m, gi, out, ids.size))
+        assert np.array_equal(out.download(np.float32).reshape(-1, h), want)
+        if name == "q6_0":
+            mt, _ = tiled(B, ctx, K, name, raw, vocab, h)
+            run(ctx, lambda c: K.embed(c, mt, gi, out, ids.size))
+            assert np.array_equal(out.download(np.float32).reshape(-1, h), want)
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.embed(c, B.QMatrix(ctx.buffer(64), B.WeightType.Q4_0, 2, 32), gi, out, 1))
+
+
+def test_add_norm_prep(B, ctx, K):
+    rng = O.Rng(15)
+    n = 2560
+    x, h, w = rng.vec(n, 3.0), rng.vec(n, 1.0), rng.vec(n, 2.0)
+    for add in (False, True):
+        gx, gh, gw = ctx.buffer_from(x), ctx.buffer_from(h), ctx.buffer_from(w)
+        gxw, gss = ctx.buffer(n * 4), ctx.buffer(B.norm_partials(n) * 4)
+        run(ctx, lambda c: K.add_norm_prep(c, gx, gh if add else None, gw, gxw, gss, n))
+        xs = (x + h) if add else x
+        assert np.array_equal(gx.download(np.float32), xs)
+        assert np.array_equal(gxw.download(np.float32), xs * w)
+        ss = gss.download(np.float32)
+        want = (xs.astype(np.float64) ** 2).reshape(-1, 256).sum(axis=1)
+        assert np.max(np.abs(ss - want) / want) <= 1e-6
+
+
+# ---- GEMV ----------------------------------------------------------------------------------------
+
+GEMV_SHAPES = [(4096, 2560), (9728, 2560), (2560, 9728), (5, 64)]
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q6_0", "q8_0"])
+@pytest.mark.parametrize("rows,cols", GEMV_SHAPES)
+def test_gemv_layouts_and_types(B, ctx, K, name, rows, cols):
+    rng = O.Rng(16)
+    raw = rng.qmatrix(QT[name][0], rows, cols)
+    for tokens in (1, 3):
+        x = rng.vec(tokens * cols, 1.0)
+        want, scale = O.matmul(QT[name][0], raw, rows, cols, x)
+        gx, gy = ctx.buffer_from(x), ctx.buffer(tokens * rows * 4)
+        m = B.QMatrix(ctx.buffer_from(raw), B.WeightType(QT[name][1]), rows, cols)
+        for fn in (K.gemv, K.gemv_simple):
+            gy.fill(0xFF)
+            run(ctx, lambda c: fn(c, m, gx, gy, tokens))
+            got = gy.download(np.float32).reshape(tokens, rows)
+            assert np.max(np.abs(got - want) / scale) <= 1e-5, (name, fn.__name__)
+        if name != "q8_0" and rows % 64 == 0 and cols % 128 == 0:
+            mt, _ = tiled(B, ctx, K, name, raw, rows, cols)
+            gy.fill(0xFF)
+            run(ctx, lambda c: K.gemv(c, mt, gx, gy, tokens))
+            got = gy.download(np.float32).reshape(tokens, rows)
+            assert np.max(np.abs(got - want) / scale) <= 1e-5, (name, "tiled")
+            # the split-K reduction has a fixed order: same bits on every run
+            run(ctx, lambda c: K.gemv(c, mt, gx, gy, tokens))
+            assert np.array_equal(gy.download(np.float32).reshape(tokens, rows), got)
+
+
+def test_gemv_config1_shape_with_quantised_gaussian_weights(B, ctx, K):
+    """[9728 x 2560] weights ~ N(0, 0.02) through the q4_0 quantiser, x ~ N(0, 1) rounded to f16."""
+    rng = np.random.default_rng(2024)
+    rows, cols = 9728, 2560
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    raw = O.quantize(O.Q4_0, w)
+    x = rng.standard_normal(cols).astype(np.float16).astype(np.float32)
+    want, scale = O.matmul(O.Q4_0, raw, rows, cols, x)
+    mt, _ = tiled(B, ctx, K, "q4_0", raw, rows, cols)
+    gx, gy = ctx.buffer_from(x), ctx.buffer(rows * 4)
+    run(ctx, lambda c: K.gemv(c, mt, gx, gy, 1))
+    got = gy.download(np.float32)
+    err = np.abs(got - want[0])
+    assert np.max(err / scale[0]) <= 1e-5
+    assert np.max(err) <= 1e-2 and np.max(err / np.maximum(np.abs(want[0]), 1e-2)) <= 1e-3
+    # against dequantise-then-matvec in numpy f64, as the configuration describes
+    ref = O.dequantize(O.Q4_0, raw, rows * cols).reshape(rows, cols).astype(np.float64) @ x.astype(np.float64)
+    assert np.max(np.abs(got - ref)) <= 1e-2
+
+
+def _norm_inputs(B, ctx, K, rng, cols):
+    x, w = rng.vec(cols, 3.0), rng.vec(cols, 1.5)
+    gx, gw, gxw, gss = ctx.buffer_from(x), ctx.buffer_from(w), ctx.buffer(cols * 4), ctx.buffer(B.norm_partials(cols) * 4)
+    run(ctx, lambda c: K.add_norm_prep(c, gx, None, gw, gxw, gss, cols))
+    normed = O.rms_norm(x, w, cols, 1e-6)
+    return gxw, gss, normed
+
+
+@pytest.mark.parametrize("layout", ["file", "tiled"])
+def test_gemv_scaled_family(B, ctx, K, layout):
+    rng = O.Rng(17)
+    cols = 2560
+
+    def mat(name, rows):
+        raw = rng.qmatrix(QT[name][0], rows, cols)
+        if layout == "tiled":
+            return tiled(B, ctx, K, name, raw, rows, cols)[0], raw
+        return B.QMatrix(ctx.buffer_from(raw), B.WeightType(QT[name][1]), rows, cols), raw
+
+    gxw, gss, normed = _norm_inputs(B, ctx, K, rng, cols)
+    # gemv_scaled: q4_0 and q6_0
+    for name, rows in (("q4_0", 4096), ("q6_0", 1024)):
+        m, raw = mat(name, rows)
+        want, scale = O.matmul(QT[name][0], raw, rows, cols, normed)
+        gy = ctx.buffer(rows * 4)
+        run(ctx, lambda c: K.gemv_scaled(c, m, gxw, gss, 1e-6, gy))
+        assert np.max(np.abs(gy.download(np.float32) - want[0]) / scale[0]) <= 2e-5
+    # gemv_scaled3 == three gemv_scaled
+    ms = [mat("q4_0", r) for r in (4096, 1024, 1024)]
+    ys = [ctx.buffer(r * 4) for r in (4096, 1024, 1024)]
+    run(ctx, lambda c: K.gemv_scaled3(c, [m for m, _ in ms], gxw, gss, 1e-6, ys))
+    for (m, raw), gy in zip(ms, ys):
+        want, scale = O.matmul(O.Q4_0, raw, m.rows, cols, normed)
+        got = gy.download(np.float32)
+        assert np.max(np.abs(got - want[0]) / scale[0]) <= 2e-5
+        single = ctx.buffer(m.rows * 4)
+        run(ctx, lambda c: K.gemv_scaled(c, m, gxw, gss, 1e-6, single))
+        assert np.array_equal(single.download(np.float32), got)  # same bits fused or not
+    # gemv_scaled_swiglu
+    (g, graw), (u, uraw) = mat("q4_0", 9728), mat("q4_0", 9728)
+    gy = ctx.buffer(9728 * 4)
+    run(ctx, lambda c: K.gemv_scaled_swiglu(c, g, u, gxw, gss, 1e-6, gy))
+    wg, sg = O.matmul(O.Q4_0, graw, 9728, cols, normed)
+    wu, su = O.matmul(O.Q4_0, uraw, 9728, cols, normed)
+    want = O.swiglu(wg[0], wu[0])
+    got = gy.download(np.float32)
+    # error of silu(g)*u from errors in g and u: |u| * (|dsilu| <= 1.1) * eg + |silu(g)| * eu
+    bound = 2e-5 * (np.abs(wu[0]) * 1.1 * sg[0] + np.abs(wg[0]) * su[0]) + 1e-6 * np.abs(want)
+    assert np.all(np.abs(got - want) <= bound + 1e-9)
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.gemv_scaled_swiglu(c, g, ms[0][0], gxw, gss, 1e-6, gy))
+
+
+# ---- KV store ------------------------------------------------------------------------------------
+
+def test_store_kv_f32_and_f16(B, ctx, K):
+    rng = O.Rng(24)
+    x = rng.vec(4099, 50.0)
+    mid = np.float32((O.f16_to_f32(0x3C01) + O.f16_to_f32(0x3C02)) / 2.0)
+    x[:8] = [mid, -mid, 65520.0, 1e-7, 3e-8, 0.0, -0.0, 70000.0]
+    src, d32, d16 = ctx.buffer_from(x), ctx.buffer(x.size * 4), ctx.buffer(x.size * 2)
+    run(ctx, lambda c: (K.store_kv(c, B.KvType.F32, src, d32, x.size), K.store_kv(c, B.KvType.F16, src, d16, x.size)))
+    assert np.array_equal(d32.download(np.float32).view(np.uint32), x.view(np.uint32))
+    assert np.array_equal(d16.download(np.uint16), O.f32_to_f16_array(x))
+
+
+def test_store_kv_q8_bit_exact(B, ctx, K):
+    rng = O.Rng(26)
+    x = rng.vec(128 * 64, 20.0)
+    x[32:64] = 0.0
+    d = np.float32(O.f16_to_f32(O.f32_to_f16(1.0 / 127.0)))
+    x[128:160] = (np.arange(32, dtype=np.float32) - np.float32(15.5)) * d  # exact ties
+    x[128 + 31] = 1.0
+    x[256:288] = 3000.0
+    src, dst = ctx.buffer_from(x), ctx.buffer(B.KvType.Q8_0.bytes(x.size))
+    run(ctx, lambda c: K.store_kv(c, B.KvType.Q8_0, src, dst, x.size))
+    assert np.array_equal(dst.download(np.uint8), O.quantize_kv_q8(x))
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.store_kv(c, B.KvType.Q8_0, src, dst, 100))
+
+
+@pytest.mark.parametrize("kv", ["F32", "F16", "Q8_0"])
+@pytest.mark.parametrize("tokens,pos0", [(1, 0), (1, 777), (7, 3), (64, 448)])
+def test_qk_norm_rope_store(B, ctx, K, kv, tokens, pos0):
+    kvt = B.KvType[kv]
+    rng = O.Rng(27)
+    hq, hkv, dim = 32, 8, 128
+    q, k, v = rng.vec(tokens * hq * dim, 2.0), rng.vec(tokens * hkv * dim, 2.0), rng.vec(tokens * hkv * dim, 3.0)
+    qn, kn = rng.vec(dim, 1.5), rng.vec(dim, 1.5)
+    table = B.RopeTable(ctx, 1e6, dim, pos0 + tokens)
+    cos, sin = O.rope_table(1e6, dim, pos0 + tokens)
+    gq, gk, gv, gqn, gkn = (ctx.buffer_from(a) for a in (q, k, v, qn, kn))
+    cap = pos0 + tokens
+    kc, vc = ctx.buffer(kvt.bytes(cap * hkv * dim)), ctx.buffer(kvt.bytes(cap * hkv * dim))
+    off = kvt.bytes(pos0 * hkv * dim)
+    shape = B.AttnShape(tokens, hq, hkv, dim, pos0, kvt)
+    run(ctx, lambda c: K.qk_norm_rope_store(c, kvt, [gq, gk, gv], [gqn, gkn], 1e-6, table, [kc.at(off), vc.at(off)], shape))
+    want_q = O.rope_neox(O.rms_norm(q, qn, dim, 1e-6), hq, dim, pos0, cos, sin)
+    want_k = O.rope_neox(O.rms_norm(k, kn, dim, 1e-6), hkv, dim, pos0, cos, sin)
+    got_q, got_k = gq.download(np.float32), gk.download(np.float32)
+    assert np.max(np.abs(got_q - want_q)) <= 2e-5 * np.max(np.abs(want_q))
+    assert np.max(np.abs(got_k - want_k)) <= 2e-5 * np.max(np.abs(want_k))
+    n = tokens * hkv * dim
+    kb, vb = kc.download(np.uint8, kvt.bytes(n), off), vc.download(np.uint8, kvt.bytes(n), off)
+    # the cache holds exactly the rounding of the values the kernel produced
+    if kvt == B.KvType.F32:
+        assert np.array_equal(kb.view(np.float32), got_k) and np.array_equal(vb.view(np.float32), v)
+    elif kvt == B.KvType.F16:
+        assert np.array_equal(kb.view(np.uint16), O.f32_to_f16_array(got_k))
+        assert np.array_equal(vb.view(np.uint16), O.f32_to_f16_array(v))
+    else:
+        assert np.array_equal(kb, O.quantize_kv_q8(got_k)) and np.array_equal(vb, O.quantize_kv_q8(v))
+    # nothing before pos0 was touched
+    assert not kc.download(np.uint8, off).any()
+
+
+# ---- attention -----------------------------------------------------------------------------------
+
+def make_cache(B, ctx, kvt, k, v):
+    """Device cache in type kvt and the values the kernel will see (crates/kernels/src/testutil.rs:93-154)."""
+    if kvt == B.KvType.F32:
+        return ctx.buffer_from(k), ctx.buffer_from(v), k, v
+    if kvt == B.KvType.F16:
+        kh, vh = k.astype(np.float16), v.astype(np.float16)
+        return ctx.buffer_from(kh), ctx.buffer_from(vh), kh.astype(np.float32), vh.astype(np.float32)
+    kq, vq = O.quantize_kv_q8(k), O.quantize_kv_q8(v)
+    return ctx.buffer_from(kq), ctx.buffer_from(vq), O.dequantize_kv_q8(kq), O.dequantize_kv_q8(vq)
+
+
+@pytest.mark.parametrize("kv", ["F32", "F16", "Q8_0"])
+@pytest.mark.parametrize("hq", [32, 8, 16, 64])
+def test_decode_attention(B, ctx, K, kv, hq):
+    kvt = B.KvType[kv]
+    rng = O.Rng(23)
+    hkv, dim = 8, 128
+    positions = [0, 1, 255, 256, 700, 4095, 16383] if hq == 32 else [0, 300, 4095]
+    worst = 0.0
+    for pos0 in positions:
+        lk = pos0 + 1
+        q = rng.vec(hq * dim, 2.0)
+        gk, gv, k, v = make_cache(B, ctx, kvt, rng.vec(lk * hkv * dim, 2.0), rng.vec(lk * hkv * dim, 3.0))
+        want, vmax = O.attention(q, k, v, 1, hq, hkv, dim, pos0)
+        gq, go = ctx.buffer_from(q), ctx.buffer(hq * dim * 4)
+        part = ctx.buffer(B.decode_partials_len(hq, lk) * 4)
+        shape = B.AttnShape(1, hq, hkv, dim, pos0, kvt)
+        for fn in (K.decode_attention, K.decode_attention_lanes):
+            go.fill(0xFF)
+            run(ctx, lambda c: fn(c, gq, gk, gv, part, go, shape))
+            got = go.download(np.float32)
+            worst = max(worst, float(np.max(np.abs(got - want) / np.maximum(vmax, 1e-30))))
+        for b in (gk, gv, gq, go, part):
+            b.free()
+    assert worst <= 1e-5, worst
+
+
+def test_decode_attention_rejects_bad_arguments(B, ctx, K):
+    q, o = ctx.buffer(32 * 128 * 4), ctx.buffer(32 * 128 * 4)
+    k = ctx.buffer(8 * 128 * 4 * 10)
+    small = ctx.buffer(16)
+    big = ctx.buffer(B.decode_partials_len(32, 10) * 4)
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.decode_attention(c, q, k, k, small, o, B.AttnShape(1, 32, 8, 128, 9, B.KvType.F32)))
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.decode_attention(c, q, k, k, big, o, B.AttnShape(2, 32, 8, 128, 8, B.KvType.F32)))
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.decode_attention(c, q, k, k, big, o, B.AttnShape(1, 32, 8, 64, 9, B.KvType.F32)))
+    with pytest.raises(B.BrasaError):
+        run(ctx, lambda c: K.decode_attention_lanes(c, q, k, k, big, o, B.AttnShape(1, 24, 8, 128, 9, B.KvType.F32)))
+
+
+@pytest.mark.parametrize("kv", ["F32", "F16", "Q8_0"])
+def test_flash_attention_gqa_causal(B, ctx, K, kv):
+    kvt = B.KvType[kv]
+    rng = O.Rng(22)
+    hq, hkv, dim = 32, 8, 128
+    w16 = wraw = w32 = 0.0
+    for tokens, pos0 in [(9, 0), (5, 11), (1, 0), (1, 1500), (33, 40), (64, 448), (32, 0), (100, 7)]:
+        lk = pos0 + tokens
+        cap = (lk + 63) // 64 * 64  # capacity rounded to KV_ALIGN with finite garbage past the range
+        q = rng.vec(tokens * hq * dim, 2.0)
+        gk, gv, k, v = make_cache(B, ctx, kvt, rng.vec(cap * hkv * dim, 2.0), rng.vec(cap * hkv * dim, 3.0))
+        want16, vmax = O.attention(q, k, v, tokens, hq, hkv, dim, pos0, q16=True)
+        raw, _ = O.attention(q, k, v, tokens, hq, hkv, dim, pos0)
+        gq, go, goh = ctx.buffer_from(q), ctx.buffer(q.size * 4), ctx.buffer(q.size * 2)
+        shape = B.AttnShape(tokens, hq, hkv, dim, pos0, kvt)
+        run(ctx, lambda c: K.flash_attention(c, gq, gk, gv, goh, shape))
+        oh = goh.download(np.float16).astype(np.float32)
+        # the final rounding of the output to f16 (at most 2^-11 |value|) is discounted
+        d = np.maximum(np.abs(oh - want16) - np.abs(want16) * 2.0 ** -11, 0.0)
+        w16 = max(w16, float(np.max(d / np.maximum(vmax, 1e-30))))
+        wraw = max(wraw, float(np.max(np.abs(oh - raw) / np.maximum(vmax, 1e-30))))
+        run(ctx, lambda c: K.flash_attention_with(c, gq, gk, gv, go, shape, B.PrefillPrecision.F32))
+        w32 = max(w32, float(np.max(np.abs(go.download(np.float32) - raw) / np.maximum(vmax, 1e-30))))
+    assert w16 <= 1e-5 and w32 <= 1e-5 and wraw <= 2e-3, (w16, w32, wraw)
+
+
+# ---- prefill GEMM --------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (192, 256)])
+def test_gemm_f16_and_f32(B, ctx, K, rows, cols):
+    rng = O.Rng(18)
+    raw = rng.qmatrix(O.Q4_0, rows, cols)
+    mt, _ = tiled(B, ctx, K, "q4_0", raw, rows, cols) if rows % 64 == 0 and cols % 128 == 0 else (None, None)
+    mf = B.QMatrix(ctx.buffer_from(raw), B.WeightType.Q4_0, rows, cols)
+    for tokens in (9, 33, 64, 100, 150):
+        x = rng.vec(tokens * cols, 1.0)
+        xh = x.astype(np.float16)
+        want16, s16 = O.matmul(O.Q4_0, raw, rows, cols, x, f16_inputs=True)
+        want32, s32 = O.matmul(O.Q4_0, raw, rows, cols, x)
+        gx, gxh, gy = ctx.buffer_from(x), ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4)
+        for m in filter(None, (mf, mt)):
+            run(ctx, lambda c: K.gemm(c, m, gxh, gy, tokens))
+            got = gy.download(np.float32).reshape(tokens, rows)
+            assert np.max(np.abs(got - want16) / s16) <= 1e-5
+            assert np.max(np.abs(got - want32) / s32) <= 2.0 ** -10  # f16 inputs against the unrounded product
+            run(ctx, lambda c: K.gemm_with(c, m, gx, gy, tokens, B.PrefillPrecision.F32))
+            got = gy.download(np.float32).reshape(tokens, rows)
+            assert np.max(np.abs(got - want32) / s32) <= 1e-5
+        if rows == 4096:
+            break  # one token count is enough for the large shapes
+
+
+def test_gemm_swiglu_equals_unfused(B, ctx, K):
+    rng = O.Rng(19)
+    rows, cols, tokens = 1024, 512, 70
+    graw, uraw = rng.qmatrix(O.Q4_0, rows, cols), rng.qmatrix(O.Q4_0, rows, cols)
+    g, _ = tiled(B, ctx, K, "q4_0", graw, rows, cols)
+    u, _ = tiled(B, ctx, K, "q4_0", uraw, rows, cols)
+    xh = rng.vec(tokens * cols, 1.0).astype(np.float16)
+    gx = ctx.buffer_from(xh)
+    gg, gu, go, go2 = (ctx.buffer(tokens * rows * 4) for _ in range(4))
+    run(ctx, lambda c: K.gemm_swiglu(c, g, u, gx, gg, gu, go, tokens))
+    fused = go.download(np.uint16, tokens * rows)
+    run(ctx, lambda c: (K.gemm_multi(c, [g, u], gx, [gg, gu], tokens, B.PrefillPrecision.F16), K.swiglu_f16(c, gg, gu, go2, tokens * rows)))
+    assert np.array_equal(fused, go2.download(np.uint16, tokens * rows))
+    wg, _ = O.matmul(O.Q4_0, graw, rows, cols, xh.astype(np.float32), f16_inputs=True)
+    wu, _ = O.matmul(O.Q4_0, uraw, rows, cols, xh.astype(np.float32), f16_inputs=True)
+    want = O.swiglu(wg, wu).ravel()
+    got = fused.view(np.float16).astype(np.float32)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) <= 2e-3
+
+
+# ---- argmax --------------------------------------------------------------------------------------
+
+def test_argmax_edge_cases(ctx, K):
+    inf, nan = float("-inf"), float("nan")
+    cases = [[inf, inf], [nan, inf, nan], [nan, 1.0, nan, 1.0], [-3.0, -1.0, -1.0, -2.0],
+             [float((i * 7919) % 1000) for i in range(151_936)], [float((i * 13) % 5 - 2) for i in range(37)], [5.0]]
+    out = ctx.buffer(4)
+    for v in cases:
+        a = np.array(v, dtype=np.float32)
+        g = ctx.buffer_from(a)
+        run(ctx, lambda c: K.argmax(c, g, a.size, out))
+        assert int(out.download(np.uint32)[0]) == O.argmax(a), v[:8]
+    rng = O.Rng(31)
+    a = rng.vec(151_936, 5.0)
+    a[[77, 90_000, 151_935]] = 9.0  # ties: the first one wins
+    g = ctx.buffer_from(a)
+    run(ctx, lambda c: K.argmax(c, g, a.size, out))
+    assert int(out.download(np.uint32)[0]) == 77
