@@ -1,0 +1,380 @@
+"""Benchmark of the Qwen3 token loop on B200: batch-1 greedy decode of the Qwen3-4B architecture in Q4.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the metric is quoted on): 36 layers, hidden 2560, FFN 9728, 32 query / 8 KV
+heads, head_dim 128, vocab 151936, tied embeddings; weights N(0, 0.02) from a seed, norms 1, quantised to
+the `.brasa` layout (q4_0 linears, q6_0 embedding/lm_head); a seeded 512-token prompt, then 256 greedy
+tokens with an f16 KV cache, ctx 2048. One step = the 255 decode forwards that follow the first token
+(decode tok/s = (generated - 1) / decode time, the reference's GenStats::decode_tok_s).
+
+`value`   device-resident: the chosen token is fed back on the device, timed with CUDA events.
+`e2e`     through Session.generate with host buffers: prompt upload, prefill, and one token id read
+          back per step, timed by the session itself (host clock around the decode loop).
+`roofline` the dominant kernel (the q4_0 GEMV at the gate/up shape) timed alone over the model's own 36
+          layers of weights (1 GB, larger than L2), against the measured HBM copy peak.
+`cpu_baseline` the oracle's C port of the reference CPU path, a few decode tokens on the host cores.
+
+With --gpus N > 1 (launched by torch.distributed.run) every rank serves its own replica: the path has
+no exchange step at batch 1, so the ranks share nothing and the aggregate is the sum ("replicas only").
+--impl reference times the CPU path alone (rank 0 only).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT, GENERATE, CTX = 512, 256, 2048
+SEED = 20251
+METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
+WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load: drop the idle tail below half of the top clock seen
+        busy = [v for v in sm if v >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def prompt_ids(vocab: int) -> np.ndarray:
+    return np.random.default_rng(SEED).integers(0, vocab, size=PROMPT).astype(np.uint32)
+
+
+def model_path(tag: str) -> pathlib.Path:
+    d = pathlib.Path(os.environ.get("BRASA_BENCH_DIR", "/tmp/brasa_bench"))
+    d.mkdir(parents=True, exist_ok=True)
+    return d / f"{tag}-seed{SEED}.brasa"
+
+
+# ---- the CPU arm ------------------------------------------------------------------------------------
+
+def cpu_decode_sample(brasa_path, kv_rows, first_ids, pos0: int, tokens: int):
+    """Decodes `tokens` tokens with the oracle's C port starting at pos0 over a given KV cache
+    (kv_rows: per layer (k, v) float arrays [pos0, kv_dim]) or a zero cache. Returns (seconds per token, logits)."""
+    import oracle
+    from oracle import brasa_format
+    f = brasa_format.BrasaFile(brasa_path)
+    orc = oracle.Qwen3Oracle(f, kv="f16", ctx=pos0 + tokens + 1)
+    if kv_rows is not None:
+        for li, (k, v) in enumerate(kv_rows):
+            orc.k[li, :pos0] = k
+            orc.v[li, :pos0] = v
+    orc.pos = pos0
+    times, logits = [], []
+    for t in range(tokens):
+        t0 = time.perf_counter()
+        lg = orc.forward([int(first_ids[t])])
+        times.append(time.perf_counter() - t0)
+        logits.append(lg[0])
+    return times, logits
+
+
+def write_random_block_model(path, cfg: dict):
+    """A `.brasa` file of the 4B shapes whose quantised tensors are random valid blocks (the reference's
+    test generator, crates/kernels/src/testutil.rs:45-83): CPU throughput does not depend on the values."""
+    import oracle
+    from brasa_b200 import synth
+    shapes = synth.tensor_shapes(cfg)
+    rng = oracle.Rng(SEED)
+    tensors, blobs = [], {}
+    import hashlib
+    for name in sorted(shapes):
+        dt = synth.dtype_for(name, len(shapes[name]))
+        n = int(np.prod(shapes[name]))
+        if dt == "f32":
+            data = np.ones(n, "<f4").tobytes()
+        else:
+            rows, cols = shapes[name]
+            data = rng.qmatrix(oracle.QTYPE[dt], rows, cols).tobytes()
+        blobs[name] = data
+        tensors.append({"name": name, "dtype": dt, "shape": shapes[name], "nbytes": len(data), "offset": 0, "sha256": "0" * 64})
+    meta = {"format": "brasa", "version": 1, "converter": "bench.py random blocks",
+            "model": {"family": "qwen3", "source_repo": "synthetic", "source_commit": "random-blocks", "config": cfg},
+            "quant": {"block": 32, "scheme": "random blocks"}, "page": 16384, "tensors": tensors, "data_sha256": "0" * 64}
+    off = 16384 * 12
+    for t in tensors:
+        t["offset"] = off
+        off = (off + t["nbytes"] + 16383) // 16384 * 16384
+    hdr = synth._header(meta)
+    assert len(hdr) <= 16384 * 12
+    with open(path, "wb") as f:
+        f.truncate(off)
+        f.write(hdr)
+        for t in tensors:
+            f.seek(t["offset"])
+            f.write(blobs[t["name"]])
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    import oracle
+    from brasa_b200 import synth
+    oracle.build()
+    cfg = synth.QWEN3_4B
+    path = model_path("qwen3-4b-random-blocks")
+    if not path.exists():
+        write_random_block_model(path, cfg)
+    cores = os.cpu_count() or 1
+    ids = prompt_ids(cfg["vocab_size"])
+    total = args.warmup + args.steps
+    times, _ = cpu_decode_sample(path, None, ids[:total], PROMPT, total)
+    timed = times[args.warmup:]
+    sec = sum(timed) / len(timed)
+    value = 1.0 / sec
+    sample = (f"{args.steps} decode tokens at positions {PROMPT}.. of the same architecture, oracle C port (dequantise a row, f64 dot; "
+              f"OpenMP over rows), KV cache of {PROMPT} zero rows, weights = random valid q4_0/q6_0 blocks")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, q4_0 weights",
+            "data": "synthetic", "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---- the GPU arm ------------------------------------------------------------------------------------
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import brasa_b200 as B
+    from brasa_b200 import synth
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = B.Context(local_rank)
+    cfg = synth.QWEN3_4B
+    path = model_path("qwen3-4b")
+    if rank == 0 and not path.exists():
+        tmp = path.with_suffix(".tmp")
+        synth.write_synthetic_model(ctx, tmp, cfg, seed=SEED)
+        os.replace(tmp, path)
+    if dist:
+        dist.barrier()
+    ids = prompt_ids(cfg["vocab_size"])
+    sess = B.Session(ctx, path, B.Limits(ctx=CTX, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
+    model = sess.model
+    K = B.Kernels(ctx)
+
+    # ---- device-resident decode (value) ----
+    logits, _ = model.forward(ids, 0)
+    first = int(np.argmax(logits[0]))
+    steps_tokens = GENERATE - 1
+    for _ in range(args.warmup):
+        model.decode_greedy(first, PROMPT, steps_tokens)
+    if dist:
+        dist.barrier()
+    ctx.sync()
+    launches0 = ctx.launch_count()
+    dev_s, out_ids = [], None
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.steps):
+            out_ids, s = model.decode_greedy(first, PROMPT, steps_tokens)
+            dev_s.append(s)
+        ctx.sync()
+    launches = ctx.launch_count() - launches0
+    if dist:
+        dist.barrier()
+    total_s = float(sum(dev_s))
+    if dist:
+        import torch
+        t = torch.tensor([total_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_s = float(t.item())
+    value = world * args.steps * steps_tokens / total_s
+
+    # ---- end to end through Session.generate (host buffers) ----
+    e2e_vals, prefill_vals = [], []
+    for i in range(args.warmup + args.steps):
+        sess.reset()
+        gen, st = sess.generate(ids, GENERATE)
+        if i >= args.warmup:
+            e2e_vals.append(st.decode_tok_s())
+            prefill_vals.append(st.prefill_tok_s())
+    e2e = statistics.median(e2e_vals)
+    same_tokens = bool(out_ids is not None and list(gen[1:]) == list(out_ids))
+    if dist:
+        import torch
+        t = torch.tensor([e2e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        e2e = float(t.item())
+    if rank != 0:
+        return
+
+    peak, peak_kind = measured_peaks()
+    wbytes = synth.weight_bytes_per_token(cfg)
+    kvb = synth.kv_bytes_per_position(cfg, "f16")
+    mean_pos = PROMPT + 1 + (steps_tokens - 1) / 2.0  # keys seen by step s: PROMPT + 1 + s
+    bytes_per_token = wbytes + kvb * mean_pos
+    per_gpu_tok_s = value / world
+    token_frac = per_gpu_tok_s * bytes_per_token / 1e9 / peak
+
+    # ---- dominant kernel alone: gate/up GEMV + SwiGLU over 36 distinct weight pairs ----
+    roof = None
+    try:
+        rows, cols = cfg["intermediate_size"], cfg["hidden_size"]
+        nlayers = cfg["num_hidden_layers"]
+        per = B.qtype_nbytes(B.WeightType.Q4_0, rows * cols)
+        # distinct random matrices: generate once, quantise, tile; 72 buffers of 14 MB
+        f32buf, filebuf = ctx.buffer(rows * cols * 4), ctx.buffer(per)
+        mats = []
+        for i in range(2 * nlayers):
+            dst = ctx.buffer(per)
+            cmd = ctx.command()
+            K.randn(cmd, f32buf, rows * cols, SEED + 7, i * rows * cols, 0.02)
+            K.quantize(cmd, B.WeightType.Q4_0, f32buf, filebuf, rows * cols)
+            K.repack(cmd, B.WeightType.Q4_0, filebuf, dst, rows, cols)
+            cmd.wait()
+            mats.append(B.QMatrix(dst, B.WeightType.Q4_0, rows, cols, B.Layout.TILED))
+        x = np.random.default_rng(1).standard_normal(cols).astype(np.float16).astype(np.float32)
+        gx, gw = ctx.buffer_from(x), ctx.buffer_from(np.ones(cols, np.float32))
+        gxw, gss, gy = ctx.buffer(cols * 4), ctx.buffer(B.norm_partials(cols) * 4), ctx.buffer(rows * 4)
+        cmd = ctx.command()
+        K.add_norm_prep(cmd, gx, None, gw, gxw, gss, cols)
+        cmd.wait()
+        graph = ctx.capture(lambda c: [K.gemv_scaled_swiglu(c, mats[2 * i], mats[2 * i + 1], gxw, gss, 1e-6, gy) for i in range(nlayers)])
+        best = []
+        for _ in range(8):
+            cmd = ctx.command()
+            graph.launch(cmd)
+            best.append(cmd.wait())
+        t_launch = statistics.median(best[3:]) / nlayers
+        algo = 2 * per + cols * 4 + rows * 4
+        ach = algo / t_launch / 1e9
+        roof = {"bound": "hbm", "kernel": "gemv_rows_kernel<q4_0> gate+up+SwiGLU [2x9728x2560]", "achieved": ach, "peak": peak, "unit": "GB/s",
+                "frac": ach / peak, "peak_source": peak_kind, "us_per_launch": t_launch * 1e6, "algorithmic_bytes_per_launch": algo,
+                "traffic": None}
+    except B.BrasaError as e:  # out of memory on a shared device: report the token-level figure only
+        roof = {"bound": "hbm", "error": str(e), "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None}
+
+    # ---- CPU baseline: the oracle's port on the host cores, over the GPU's own prefill state ----
+    cpu = None
+    try:
+        import oracle
+        oracle.build()
+        model.forward(ids, 0, want_logits=False)
+        kvd = cfg["num_key_value_heads"] * cfg["head_dim"]
+        kv_rows = []
+        for li in range(cfg["num_hidden_layers"]):
+            k = model.read_kv(li, "k", 0, PROMPT).view(np.float16).astype(np.float32).reshape(PROMPT, kvd)
+            v = model.read_kv(li, "v", 0, PROMPT).view(np.float16).astype(np.float32).reshape(PROMPT, kvd)
+            kv_rows.append((k, v))
+        ntok = 3
+        feed = [first] + [int(t) for t in out_ids[:ntok - 1]]
+        times, cpu_logits = cpu_decode_sample(path, kv_rows, feed, PROMPT, ntok)
+        worst, same = 0.0, True
+        model.forward(ids, 0, want_logits=False)
+        for i, tok in enumerate(feed):
+            lg, _ = model.forward([tok], PROMPT + i)
+            worst = max(worst, float(np.abs(lg[0] - cpu_logits[i]).max() / np.abs(cpu_logits[i]).max()))
+            same = same and int(np.argmax(lg[0])) == int(np.argmax(cpu_logits[i]))
+        sec = statistics.median(times)
+        cpu = {"value": 1.0 / sec, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"{ntok} decode tokens at positions {PROMPT}..{PROMPT + ntok - 1} of this workload over the GPU's prefill KV cache, "
+                         f"oracle C port with OpenMP on all host cores",
+               "parity_max_rel_logit_err": worst, "parity_same_greedy_tokens": same}
+    except Exception as e:  # the baseline is reported, never required for the GPU figure
+        cpu = {"value": None, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": f"failed: {e}"}
+
+    line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 activations and accumulation, q4_0/q6_0 weights, f16 KV", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: 2.36 GB of weights are read per token",
+                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU", "tokens_per_step": steps_tokens},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * PROMPT + 4 * steps_tokens, "d2h_bytes_per_step": 4 * GENERATE,
+                    "prefill_tok_s": statistics.median(prefill_vals), "same_tokens_as_device_resident": same_tokens},
+            "gpu_launches": int(launches),
+            "roofline": roof,
+            "token_roofline": {"bytes_per_token": bytes_per_token, "achieved_gbs": per_gpu_tok_s * bytes_per_token / 1e9, "peak": peak,
+                               "frac_of_measured": token_frac, "frac_of_8tbs": per_gpu_tok_s * bytes_per_token / 8e12,
+                               "roofline_tok_s_at_8tbs": 8e12 / bytes_per_token},
+            "cpu_baseline": cpu}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

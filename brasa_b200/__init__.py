@@ -148,11 +148,13 @@ def lib() -> C.CDLL:
         L.brasa_qtype_nbytes.restype = C.c_uint64
         L.brasa_plan_buffer_bytes.restype = C.c_uint64
         L.brasa_session_model.restype = C.c_void_p
+        L.brasa_ctx_launch_count.restype = C.c_uint64
         L.brasa_ctx_destroy.restype = None
         L.brasa_model_free.restype = None
         L.brasa_session_free.restype = None
+        L.brasa_graph_free.restype = None
         for name in ("brasa_ctx_destroy", "brasa_model_free", "brasa_session_free", "brasa_buf_free", "brasa_buf_ptr", "brasa_buf_bytes",
-                     "brasa_ctx_stream", "brasa_session_model"):
+                     "brasa_ctx_stream", "brasa_session_model", "brasa_graph_free"):
             getattr(L, name).argtypes = [C.c_void_p]
         _lib = L
     return _lib
@@ -224,6 +226,23 @@ class Context:
 
     def sync(self):
         self._check(lib().brasa_ctx_sync(self._h))
+
+    def capture(self, record) -> "Graph":
+        """Records the kernels `record(cmd)` enqueues into a CUDA graph instead of running them."""
+        cmd = self.command()
+        self._check(lib().brasa_graph_capture_begin(self._h))
+        try:
+            record(cmd)
+        finally:
+            g = C.c_void_p()
+            rc = lib().brasa_graph_capture_end(self._h, C.byref(g))
+        self._check(rc)
+        cmd.wait()
+        return Graph(self, g)
+
+    def launch_count(self) -> int:
+        """Kernels enqueued on this context so far (graph replays count their kernels)."""
+        return int(lib().brasa_ctx_launch_count(self._h))
 
     def mem_info(self) -> tuple[int, int]:
         f, t = C.c_uint64(), C.c_uint64()
@@ -334,6 +353,21 @@ class Command:
         return s.value
 
     commit_and_wait = wait
+
+
+class Graph:
+    """A recorded sequence of kernels, replayed with one submission."""
+
+    def __init__(self, ctx: Context, handle):
+        self.ctx, self._h = ctx, handle
+
+    def launch(self, cmd: Command):
+        self.ctx._check(lib().brasa_graph_launch(cmd._h, self._h))
+
+    def free(self):
+        if self._h:
+            lib().brasa_graph_free(self._h)
+        self._h = C.c_void_p()
 
 
 class RopeTable:

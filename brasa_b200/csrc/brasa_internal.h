@@ -25,14 +25,23 @@ struct brasa_ctx {
     size_t gemv_counters_n = 0;
     uint32_t *status = nullptr;  // device status word: non-zero after a bounded wait gave up
     bool pdl = true;             // programmatic dependent launch between decode kernels
+    bool capturing = false;      // a stream capture is open (brasa_graph_capture_begin)
+    uint64_t launches = 0;       // kernels enqueued on this context (graph replays count their nodes)
+    uint64_t capture_launches = 0;
     void *argmax_scratch = nullptr;  // arrival counter + per-block partial maxima
-    bool gemv_attr_done[2] = {false, false};  // opt-in shared memory size set on this device
+    bool gemv_attr_done[10] = {};  // opt-in shared memory size set on this device, per kernel instance
 };
 
 struct brasa_buf {
     brasa_ctx *ctx;
     void *ptr;
     uint64_t bytes;
+};
+
+struct brasa_graph {
+    brasa_ctx *ctx;
+    cudaGraphExec_t exec;
+    uint64_t kernels;  // kernel nodes recorded
 };
 
 struct brasa_cmd {
@@ -71,18 +80,32 @@ int32_t brasa_post_launch(brasa_cmd *cmd, const char *name);
 // Makes sure the context's split-K scratch holds at least this many floats / counters.
 int32_t brasa_gemv_scratch(brasa_ctx *ctx, size_t partial_floats, size_t counters);
 
-// ---- tiled weight layout --------------------------------------------------------------------
-// A matrix [rows, cols] is cut into micro-tiles of 64 rows x 4 blocks (128 columns), stored one
-// after another with the column index fastest. Inside a micro-tile, for q4_0:
-//     codes  [4 blocks][64 rows][16 bytes]   the block's 16 code bytes, unchanged
-//     scales [4 blocks][64 rows] f16
-// q6_0 adds the high-bit plane:  ql [4][64][16], qh [4][64][8], scales [4][64] f16.
-// Total bytes equal the file layout's (18 or 26 bytes per 32 weights).
-constexpr int MT_ROWS = 64;
-constexpr int MT_BLOCKS = 4;
-constexpr int MT_BYTES_Q4 = MT_BLOCKS * MT_ROWS * 18;  // 4608
-constexpr int MT_BYTES_Q6 = MT_BLOCKS * MT_ROWS * 26;  // 6656
-static inline int mt_bytes(int qtype) { return qtype == BRASA_Q4_0 ? MT_BYTES_Q4 : MT_BYTES_Q6; }
+// ---- tiled (row-planar) weight layout ----------------------------------------------------------
+// Each row keeps its own bytes, regrouped into planes so that every access is an aligned vector:
+//     q4_0: codes [nb][16 bytes] | scales [nb] f16
+//     q6_0: codes [nb][16 bytes] | high-bit words [nb][2] u32 | scales [nb] f16
+// nb = cols / 32 blocks per row; total bytes equal the file layout's (18 or 26 per block). The code
+// bytes of a block are unchanged (byte j = element j in the low nibble, element j + 16 in the high
+// nibble). A q6_0 high-bit word serves the two code words of one half block (16 codes). After
+// `word & 0x0F0F0F0F` or `(word >> 4) & 0x0F0F0F0F` a register holds four codes, one per byte; the
+// 2-bit field of the code in byte b of quad {word 0 low nibbles, word 0 high nibbles, word 1 low, word 1
+// high} sits in byte b of the high-bit word at bit 4, 6, 2 or 0, so a shift by 0, >>2, <<2 or <<4 puts
+// all four fields of a quad at bits 4-5 of their bytes.
+// Row strides stay 16-byte multiples because cols % 256 == 0 is required.
+#if defined(__CUDACC__)
+#define BRASA_HD __host__ __device__
+#else
+#define BRASA_HD
+#endif
+BRASA_HD static inline uint32_t tiled_row_bytes(int qtype, uint32_t cols) { return cols / 32 * (qtype == BRASA_Q4_0 ? 18u : 26u); }
+BRASA_HD static inline uint32_t tiled_hi_off(uint32_t cols) { return cols / 32 * 16u; }
+BRASA_HD static inline uint32_t tiled_scale_off(int qtype, uint32_t cols) { return cols / 32 * (qtype == BRASA_Q4_0 ? 16u : 24u); }
+// word_in_pair: code word 0 or 1 of the half block; k: nibble 0..7 inside that word
+BRASA_HD static inline int q6_hi_bitpos(int word_in_pair, int k) {
+    int quad = 2 * word_in_pair + (k & 1), byte = k >> 1;
+    int field = quad == 0 ? 4 : (quad == 1 ? 6 : (quad == 2 ? 2 : 0));
+    return 8 * byte + field;
+}
 static inline bool tiled_ok(int qtype, uint32_t rows, uint32_t cols) {
-    return (qtype == BRASA_Q4_0 || qtype == BRASA_Q6_0) && rows % MT_ROWS == 0 && cols % (32 * MT_BLOCKS) == 0;
+    return (qtype == BRASA_Q4_0 || qtype == BRASA_Q6_0) && rows > 0 && cols > 0 && cols % 256 == 0;
 }

@@ -84,6 +84,8 @@ int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total
     return BRASA_OK;
 }
 
+uint64_t brasa_ctx_launch_count(brasa_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
 int32_t brasa_ctx_sync(brasa_ctx *ctx) {
     if (!ctx) return BRASA_EINVAL;
     BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -209,6 +211,45 @@ int32_t brasa_cmd_wait(brasa_cmd *cmd, double *gpu_seconds) {
     return rc;
 }
 
+// ---- CUDA graphs: record the kernels enqueued between begin and end, replay them with one launch ----
+
+int32_t brasa_graph_capture_begin(brasa_ctx *ctx) {
+    if (!ctx) return BRASA_EINVAL;
+    BRASA_REQUIRE(ctx, !ctx->capturing, "a capture is already open on this context");
+    BRASA_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    ctx->capture_launches = 0;
+    return BRASA_OK;
+}
+
+int32_t brasa_graph_capture_end(brasa_ctx *ctx, brasa_graph **out) {
+    if (!ctx || !out) return BRASA_EINVAL;
+    *out = nullptr;
+    BRASA_REQUIRE(ctx, ctx->capturing, "no capture is open on this context");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    BRASA_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    BRASA_CUDA(ctx, e);
+    *out = new brasa_graph{ctx, exec, ctx->capture_launches};
+    return BRASA_OK;
+}
+
+int32_t brasa_graph_launch(brasa_cmd *cmd, brasa_graph *graph) {
+    if (!cmd || !graph || graph->ctx != cmd->ctx) return BRASA_EINVAL;
+    BRASA_CUDA(cmd->ctx, cudaGraphLaunch(graph->exec, cmd->ctx->stream));
+    cmd->ctx->launches += graph->kernels;
+    return BRASA_OK;
+}
+
+void brasa_graph_free(brasa_graph *graph) {
+    if (!graph) return;
+    cudaGraphExecDestroy(graph->exec);
+    delete graph;
+}
+
 // ---- helpers ------------------------------------------------------------------------------------
 
 uint64_t brasa_decode_partials_len(uint32_t hq, uint32_t lk) {
@@ -255,6 +296,8 @@ int32_t brasa_rope_table(double theta, uint32_t dim, uint32_t max_pos, float *co
 int32_t brasa_post_launch(brasa_cmd *cmd, const char *name) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return brasa_fail(cmd->ctx, BRASA_ECUDA, "launch of %s: %s", name, cudaGetErrorString(e));
+    if (cmd->ctx->capturing) cmd->ctx->capture_launches += 1;
+    else cmd->ctx->launches += 1;
     return BRASA_OK;
 }
 

@@ -39,21 +39,16 @@ __device__ __forceinline__ void dequant_block(const WView &w, uint32_t r, uint32
             return;
         }
     } else {
-        int mtb = w.qtype == BRASA_Q4_0 ? MT_BYTES_Q4 : MT_BYTES_Q6;
-        const uint8_t *tb = w.p + ((size_t)(r / MT_ROWS) * (nb / MT_BLOCKS) + b / MT_BLOCKS) * mtb;
-        uint32_t slot = (b % MT_BLOCKS) * MT_ROWS + r % MT_ROWS;
-        codes = tb + slot * 16;
-        constexpr int NS = MT_BLOCKS * MT_ROWS;
-        d = __half2float(*reinterpret_cast<const __half *>(tb + NS * (w.qtype == BRASA_Q4_0 ? 16 : 24) + slot * 2));
+        const uint8_t *row = w.p + (size_t)r * tiled_row_bytes(w.qtype, w.cols);
+        codes = row + b * 16;
+        d = __half2float(*reinterpret_cast<const __half *>(row + tiled_scale_off(w.qtype, w.cols) + b * 2));
         if (w.qtype == BRASA_Q6_0) {
-            const uint32_t *hw = reinterpret_cast<const uint32_t *>(tb + NS * 16 + slot * 8);
+            const uint32_t *hw = reinterpret_cast<const uint32_t *>(row + tiled_hi_off(w.cols) + b * 8);
             for (int j = 0; j < 32; ++j) {
                 int byte = codes[j & 15];
                 int lo = j < 16 ? (byte & 15) : (byte >> 4);
                 int ww = (j & 15) >> 2, k = 2 * (j & 3) + (j >> 4);
-                int pos = 4 * (k & 3) + 4 + 2 * (k >> 2);
-                if (ww & 1) pos = (pos + 16) & 31;
-                out[j] = d * (float)((lo | (((hw[ww >> 1] >> pos) & 3) << 4)) - 32);
+                out[j] = d * (float)((lo | (((hw[ww >> 1] >> q6_hi_bitpos(ww & 1, k)) & 3) << 4)) - 32);
             }
             return;
         }

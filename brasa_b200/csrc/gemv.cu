@@ -1,49 +1,58 @@
-// Decode GEMVs: y = W x for quantised W (q4_0 / q6_0 in the tiled layout), one token.
+// Decode GEMVs: y = W x for quantised W (q4_0 / q6_0 in the row-planar tiled layout), one token.
 //
 // The reference's GEMV family (crates/kernels/src/lib.rs:633-838 and the MSL bodies it dispatches)
-// is HBM-bound: every weight byte is read once per token. On B200 the matrices are small next to
-// the machine (o_proj is 40 KB per SM), so the kernel is built around three things:
-//   * weights move HBM -> shared memory with bulk async copies (cp.async.bulk + mbarrier), issued
-//     by one thread before the kernel waits for its input vector (programmatic dependent launch),
-//     so the stream of weight bytes does not stop at kernel boundaries;
-//   * work is cut into 4.6 KB micro-tiles (64 rows x 128 columns) spread evenly over all SMs
-//     (split-K); the warp that completes a 64-row group sums its partials in a fixed order, so the
-//     result is deterministic, and applies the epilogue (RMSNorm scale, SwiGLU);
-//   * one lane owns one row (two per warp pass): x is read from shared memory as a warp-wide
-//     broadcast, codes as conflict-free 128-bit loads, no cross-lane reduction is needed.
-// Dequantisation is fused and exact: a 4-bit (6-bit) code is OR-ed into the mantissa of 2^23, the
-// constant is subtracted (packed f32x2 add), and the product with the pre-scaled x is accumulated
-// in f32 (packed f32x2 fma): (q - 8) * 16^k * (x * 16^-k).
+// is HBM-bound: every weight byte is read once per token. On B200 the matrices are small next to the
+// machine (o_proj is 40 KB per SM) and each GEMV depends on the previous one, so the kernel is built
+// to keep the weight stream flowing and the per-kernel latency short:
+//   * every block owns whole output rows, rows / grid of them (balanced to one row), so no partial
+//     result ever crosses blocks: no atomics, no second pass, the epilogue (RMSNorm scale, SwiGLU,
+//     residual add) runs where the row was computed;
+//   * the block's rows are one contiguous byte range; it moves HBM -> shared memory with bulk async
+//     copies (cp.async.bulk + mbarrier) issued before the kernel waits for its input vector
+//     (programmatic dependent launch): the weight stream does not stop at kernel boundaries;
+//   * a warp computes (row, column slice) dot products, two rows at a time. Each lane owns the same
+//     16-column half blocks of every row, so its share of x stays in registers for the whole kernel;
+//     the 32 partial sums are combined with warp shuffles.
+// Dequantisation is fused and the integer part of the arithmetic is exact. The packed f32x2
+// instructions of sm_100 issue at a fraction of the scalar rate and a scalar float path needs three
+// instructions per weight, so the dot product runs on the integer pipe instead: the lane's x values are
+// converted once per kernel to 22-bit fixed point relative to the largest of each 16-value group and
+// split into three byte planes; a code word becomes two registers of four byte-wide codes with two
+// logic instructions, and dp4a accumulates codes x bytes exactly in int32:
+//     sum_j (q_j - bias) X_j = S0 + 256 S1 + 65536 S2 - bias * sum_j X_j
+// One int-to-float conversion and one multiply by (block scale x group scale) per 16 weights follow.
 #include <type_traits>
 
 #include "brasa_internal.h"
 
 namespace {
 
-constexpr int CONSUMER_WARPS = 8;
-constexpr int GEMV_THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait rounds before a wait gives up
+constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait rounds before a wait gives up
+constexpr int MAX_WARPS = 10;              // consumer warps per block (a multiple of the slice count)
+constexpr int PRODUCER_LANES = 1;
 
-enum { EPI_SCALE = 0, EPI_SWIGLU = 1 };
+enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2 };
 
 struct GemvParams {
     const uint8_t *w[3];
     float *y[3];
-    uint32_t mt_count[3];  // micro-tiles per matrix
+    uint32_t rows[3];
     uint32_t nmat;
-    uint32_t cols, nkc;    // nkc = cols / 128 micro-tile columns
-    uint32_t total_mt;
+    uint32_t cols;
+    uint32_t slices;       // column slices per row (S); consumer warps are a multiple of it
+    uint32_t warps;        // consumer warps
+    uint32_t rows_per_slot;  // 2 * warps / slices
     uint32_t nslot;        // ring slots in shared memory
+    uint32_t max_items;    // partial sums kept in shared memory per block
     int epilogue;
-    // input vector: either `x` alone (already multiplied by the norm weight, reference form, with
-    // optional partial sums ss[nss] of x^2), or x (+ h) with norm weight for the fused form
+    // input vector: x (optionally + h) times normw when given; ss: partial sums of x^2 computed by
+    // add_norm_prep (reference form), else the block computes the sum itself
     const float *x, *h, *normw, *ss;
-    float *x_out;          // fused form: block 0 writes x + h here
+    float *x_out;          // when h is given: block 0 writes x + h here
+    const float *resid;    // EPI_RESID: y = resid + W x
     uint32_t nss;
     int scaled;            // multiply outputs by 1/sqrt(mean(x^2) + eps)
     float eps;
-    float *partials;
-    uint32_t *counters;
     uint32_t *status;
 };
 
@@ -80,31 +89,15 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  : "memory");
 }
 
-typedef unsigned long long f2;  // two packed floats
-__device__ __forceinline__ f2 pack2(float a, float b) {
-    f2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    int r;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
 }
-__device__ __forceinline__ f2 pack2u(uint32_t a, uint32_t b) {
-    f2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // unsigned codes x signed bytes
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
-}
-__device__ __forceinline__ f2 add2(f2 a, f2 b) {
-    f2 r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
-    f2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ float sum2(f2 a) {
-    float lo, hi;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a));
-    return lo + hi;
 }
 __device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t c) {  // (a & b) | c
     uint32_t r;
@@ -112,234 +105,310 @@ __device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t 
     return r;
 }
 
-constexpr uint32_t MAGIC = 0x4B000000u;  // 2^23 as float bits: the code becomes the low mantissa
+// The lane's x values of one half block in fixed point: quad j (4 values) x byte plane d, the sum of
+// the 16 integers, and the power-of-two step.
+struct XFixed {
+    uint32_t d[4][3];
+    int total;
+    float step;
+};
 
-// Adds the dot products of one 8-code word `a` (and, for q6_0, the aligned high-bit words) with
-// the 8 pre-scaled x values {x01, x23, x45, x67} to acc.
+// sum over the 16 weights of a half block of (code - bias) * X, as an integer.
+// Quads: 0 = low nibbles of word x, 1 = high nibbles of word x, 2 and 3 likewise for word y.
 template <int QT>
-__device__ __forceinline__ f2 word_dot(uint32_t a, uint32_t hb, f2 x01, f2 x23, f2 x45, f2 x67, f2 c01, f2 c23, f2 acc) {
-    uint32_t ah = a >> 16;
-    uint32_t f0, f1, f2_, f3, f4, f5, f6, f7;
-    f0 = lop_and_or(a, 0x000Fu, MAGIC);
-    f1 = lop_and_or(a, 0x00F0u, MAGIC);
-    f2_ = lop_and_or(a, 0x0F00u, MAGIC);
-    f3 = lop_and_or(a, 0xF000u, MAGIC);
-    f4 = lop_and_or(ah, 0x000Fu, MAGIC);
-    f5 = lop_and_or(ah, 0x00F0u, MAGIC);
-    f6 = lop_and_or(ah, 0x0F00u, MAGIC);
-    f7 = lop_and_or(ah, 0xF000u, MAGIC);
-    if (QT == BRASA_Q6_0) {
-        uint32_t hh = hb >> 2;
-        f0 = lop_and_or(hb, 0x00030u, f0);
-        f1 = lop_and_or(hb, 0x00300u, f1);
-        f2_ = lop_and_or(hb, 0x03000u, f2_);
-        f3 = lop_and_or(hb, 0x30000u, f3);
-        f4 = lop_and_or(hh, 0x00030u, f4);
-        f5 = lop_and_or(hh, 0x00300u, f5);
-        f6 = lop_and_or(hh, 0x03000u, f6);
-        f7 = lop_and_or(hh, 0x30000u, f7);
+__device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const XFixed &x) {
+    uint32_t a[4];
+    a[0] = codes.x & 0x0F0F0F0Fu;
+    a[1] = (codes.x >> 4) & 0x0F0F0F0Fu;
+    a[2] = codes.y & 0x0F0F0F0Fu;
+    a[3] = (codes.y >> 4) & 0x0F0F0F0Fu;
+    if (QT == BRASA_Q6_0) {  // the two high bits of each code, stored so a shift puts them at bits 4-5 of its byte
+        a[0] = lop_and_or(hb, 0x30303030u, a[0]);
+        a[1] = lop_and_or(hb >> 2, 0x30303030u, a[1]);
+        a[2] = lop_and_or(hb << 2, 0x30303030u, a[2]);
+        a[3] = lop_and_or(hb << 4, 0x30303030u, a[3]);
     }
-    acc = fma2(add2(pack2u(f0, f1), c01), x01, acc);
-    acc = fma2(add2(pack2u(f2_, f3), c23), x23, acc);
-    acc = fma2(add2(pack2u(f4, f5), c01), x45, acc);
-    acc = fma2(add2(pack2u(f6, f7), c23), x67, acc);
-    return acc;
+    int s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        s0 = dp4a_uu(a[j], x.d[j][0], s0);
+        s1 = dp4a_uu(a[j], x.d[j][1], s1);
+        s2 = dp4a_us(a[j], x.d[j][2], s2);
+    }
+    constexpr int BIAS = QT == BRASA_Q4_0 ? 8 : 32;
+    return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
 }
 
-// One micro-tile (64 rows x 4 blocks) against xs (this column chunk's 128 pre-scaled values).
-// Lane owns rows `lane` and `lane + 32`.
-template <int QT>
-__device__ __forceinline__ void microtile_dot(const uint8_t *tile, const float *xs, int lane, float &out0, float &out1) {
-    constexpr int NSLOT = MT_BLOCKS * MT_ROWS;
-    constexpr float BIAS = QT == BRASA_Q4_0 ? 8.0f : 32.0f;
-    const f2 c01 = pack2(-(8388608.0f + BIAS), -(8388608.0f + BIAS * 16.0f));
-    const f2 c23 = pack2(-(8388608.0f + BIAS * 256.0f), -(8388608.0f + BIAS * 4096.0f));
-    const uint4 *codes = reinterpret_cast<const uint4 *>(tile);
-    const uint2 *hi = reinterpret_cast<const uint2 *>(tile + NSLOT * 16);
-    const __half *sc = reinterpret_cast<const __half *>(tile + NSLOT * (QT == BRASA_Q4_0 ? 16 : 24));
-    float a0 = 0.0f, a1 = 0.0f;
-#pragma unroll
-    for (int blk = 0; blk < MT_BLOCKS; ++blk) {
-        int s0 = blk * MT_ROWS + lane, s1 = s0 + 32;
-        uint4 p0 = codes[s0], p1 = codes[s1];
-        float d0 = __half2float(sc[s0]), d1 = __half2float(sc[s1]);
-        uint2 h0 = make_uint2(0, 0), h1 = make_uint2(0, 0);
-        if (QT == BRASA_Q6_0) { h0 = hi[s0]; h1 = hi[s1]; }
-        const ulonglong2 *xv = reinterpret_cast<const ulonglong2 *>(xs + blk * 32);
-        f2 acc0 = 0ull, acc1 = 0ull;
-        uint32_t w0[4] = {p0.x, p0.y, p0.z, p0.w}, w1[4] = {p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            ulonglong2 xa = xv[2 * w], xb = xv[2 * w + 1];  // warp-wide broadcast
-            uint32_t hb0 = (w & 2) ? h0.y : h0.x, hb1 = (w & 2) ? h1.y : h1.x;
-            if (QT == BRASA_Q6_0 && (w & 1)) {
-                hb0 = __funnelshift_r(hb0, hb0, 16);
-                hb1 = __funnelshift_r(hb1, hb1, 16);
-            }
-            acc0 = word_dot<QT>(w0[w], hb0, xa.x, xa.y, xb.x, xb.y, c01, c23, acc0);
-            acc1 = word_dot<QT>(w1[w], hb1, xa.x, xa.y, xb.x, xb.y, c01, c23, acc1);
-        }
-        a0 = fmaf(d0, sum2(acc0), a0);
-        a1 = fmaf(d1, sum2(acc1), a1);
-    }
-    out0 = a0;
-    out1 = a1;
-}
-
-template <int QT>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_tiled_kernel(GemvParams p) {
-    constexpr int MTB = QT == BRASA_Q4_0 ? MT_BYTES_Q4 : MT_BYTES_Q6;
+// N = half blocks per lane and slice (the lane's x registers hold 16 N values).
+template <int QT, int N>
+__global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: ring [nslot][MTB] | xs [cols] floats | barriers | red
+    const uint32_t row_bytes = tiled_row_bytes(QT, p.cols);
+    const uint32_t slot_bytes = p.rows_per_slot * row_bytes;
+    // layout: ring [nslot][slot_bytes] | xs [cols] | nws [cols] (norm weight, when given) | xf [14][cols/16] | part [max_items]
+    //         | full, empty [nslot] | xbar, wbar | red
     uint8_t *ring = smem;
-    float *xs = reinterpret_cast<float *>(smem + (size_t)p.nslot * MTB);
-    uint64_t *full = reinterpret_cast<uint64_t *>(xs + p.cols);
+    float *xs = reinterpret_cast<float *>(smem + (size_t)p.nslot * slot_bytes);
+    float *nws = xs + p.cols;
+    uint32_t *xf = reinterpret_cast<uint32_t *>(nws + (p.normw ? p.cols : 0));  // fixed-point x: [14][cols / 16] words
+    float *part = reinterpret_cast<float *>(xf + 14 * (p.cols / 16));
+    uint64_t *full = reinterpret_cast<uint64_t *>(part + ((p.max_items + 1) & ~1u));
     uint64_t *empty = full + p.nslot;
-    float *red = reinterpret_cast<float *>(empty + p.nslot);
+    uint64_t *xbar = empty + p.nslot, *wbar = xbar + 1;
+    float *red = reinterpret_cast<float *>(wbar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t W = p.warps, S = p.slices, RPS = p.rows_per_slot;
     const uint32_t G = gridDim.x, b = blockIdx.x;
-    const uint32_t m0 = (uint32_t)((uint64_t)p.total_mt * b / G), m1 = (uint32_t)((uint64_t)p.total_mt * (b + 1) / G);
-    const uint32_t items = m1 - m0;
+    // logical rows: matrices one after another (SwiGLU: the rows of gate; up follows the same range)
+    const uint32_t nseg = p.epilogue == EPI_SWIGLU ? 2 : p.nmat;
+    uint32_t total_rows = 0;
+    for (uint32_t i = 0; i < (p.epilogue == EPI_SWIGLU ? 1u : p.nmat); ++i) total_rows += p.rows[i];
+    const uint32_t r0 = (uint32_t)((uint64_t)total_rows * b / G), r1 = (uint32_t)((uint64_t)total_rows * (b + 1) / G);
+    // per segment: first row inside its matrix and row count
+    // per segment: first row inside its matrix, row count, first slot, rows of the segments before it.
+    // Only constant indices below, so the arrays stay in registers.
+    uint32_t seg_first[3] = {0, 0, 0}, seg_rows[3] = {0, 0, 0}, seg_slot0[3] = {0, 0, 0}, seg_before[3] = {0, 0, 0};
+    {
+        uint32_t base = 0, slot = 0, before = 0;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            if ((uint32_t)i < nseg) {
+                if (p.epilogue == EPI_SWIGLU) { seg_first[i] = r0; seg_rows[i] = r1 - r0; }
+                else {
+                    uint32_t lo = max(r0, base), hi = min(r1, base + p.rows[i]);
+                    seg_first[i] = lo > base ? lo - base : 0;
+                    seg_rows[i] = hi > lo ? hi - lo : 0;
+                    base += p.rows[i];
+                }
+            }
+            seg_slot0[i] = slot;
+            seg_before[i] = before;
+            slot += (seg_rows[i] + RPS - 1) / RPS;
+            before += seg_rows[i];
+        }
+    }
+    const uint32_t total_slots = seg_slot0[2] + (seg_rows[2] + RPS - 1) / RPS;
+    auto seg_of = [&](uint32_t k) -> uint32_t { return (uint32_t)(nseg > 1 && k >= seg_slot0[1]) + (uint32_t)(nseg > 2 && k >= seg_slot0[2]); };
+#define SEG_PICK(arr, i) ((i) == 0 ? arr[0] : ((i) == 1 ? arr[1] : arr[2]))
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nslot; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
+            mbar_init(&empty[s], W);
         }
+        mbar_init(xbar, 1);
+        mbar_init(wbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     // Let the next kernel of the stream start its own weight prefetch.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    auto tile_src = [&](uint32_t m) -> const uint8_t * {
-        uint32_t mi = 0;
-        while (mi + 1 < p.nmat && m >= p.mt_count[mi]) { m -= p.mt_count[mi]; ++mi; }
-        return p.w[mi] + (size_t)m * MTB;
+    auto issue = [&](uint32_t k) {  // slot k of this block -> ring[k % nslot]
+        const uint32_t i = seg_of(k);
+        uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
+        const uint8_t *src = p.w[i] + (size_t)(SEG_PICK(seg_first, i) + first) * row_bytes;
+        uint32_t s = k % p.nslot;
+        mbar_expect_tx(&full[s], n * row_bytes);
+        bulk_g2s(ring + (size_t)s * slot_bytes, src, n * row_bytes, &full[s]);
     };
 
-    uint32_t issued = 0;
-    if (warp == CONSUMER_WARPS && lane == 0) {
-        // weights are immutable: the first ring-full of copies starts before the input is ready
-        uint32_t first = items < p.nslot ? items : p.nslot;
-        for (; issued < first; ++issued) {
-            mbar_expect_tx(&full[issued], MTB);
-            bulk_g2s(ring + (size_t)issued * MTB, tile_src(m0 + issued), MTB, &full[issued]);
+    if (warp == (int)W) {  // producer warp: lanes 0..3 issue alternating slots
+        if (lane < PRODUCER_LANES) {
+            // weights are immutable: the first ring-full of copies starts before the input is ready
+            uint32_t k = lane;
+            if (lane == 0 && p.normw) {  // the norm weight is a weight too
+                mbar_expect_tx(wbar, p.cols * 4);
+                bulk_g2s(nws, p.normw, p.cols * 4, wbar);
+            }
+            for (; k < total_slots && k < p.nslot; k += PRODUCER_LANES) issue(k);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (lane == 0 && !p.h) {  // the input vector: one bulk copy once the previous kernel is done
+                mbar_expect_tx(xbar, p.cols * 4);
+                bulk_g2s(xs, p.x, p.cols * 4, xbar);
+            }
+            for (; k < total_slots; k += PRODUCER_LANES) {
+                if (!mbar_wait(&empty[k % p.nslot], (k / p.nslot - 1) & 1)) {
+                    atomicExch(p.status, 1u);
+                    break;
+                }
+                issue(k);
+            }
         }
+        return;
     }
     // Everything below depends on the previous kernel's output.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp == CONSUMER_WARPS) {
-        if (lane == 0) {
-            bool ok = true;
-            for (; issued < items && ok; ++issued) {
-                uint32_t s = issued % p.nslot, round = issued / p.nslot;
-                ok = mbar_wait(&empty[s], (round - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&full[s], MTB);
-                bulk_g2s(ring + (size_t)s * MTB, tile_src(m0 + issued), MTB, &full[s]);
-            }
-            if (!ok) atomicExch(p.status, 1u);
+    // ---- x in shared memory (bulk copy; with h: x + h through registers), sum of squares ----
+    const uint32_t CT = W * 32;
+    bool ok_in = true;
+    if (p.h) {
+        for (uint32_t j = threadIdx.x; j < p.cols; j += CT) {
+            float v = p.x[j] + p.h[j];
+            if (p.x_out && b == 0) p.x_out[j] = v;
+            xs[j] = v;
         }
-        // the producer warp takes no part in the block-wide sums below: consumers use named barrier 1
-        return;
+        asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+    } else {
+        ok_in = mbar_wait(xbar, 0);
     }
-
-    // ---- stage x: permuted and pre-scaled so that each code meets its x in mantissa position ----
-    const int ct = threadIdx.x, CT = CONSUMER_WARPS * 32;
-    float ssq = 0.0f;
-    for (uint32_t j = ct; j < p.cols; j += CT) {
-        float v = p.x[j];
-        if (p.h) v += p.h[j];
-        if (p.x_out && b == 0) p.x_out[j] = v;
-        ssq += v * v;
-        if (p.normw) v *= p.normw[j];
-        uint32_t blk = j >> 5, e = j & 31;
-        uint32_t k = 2 * (e & 3) + (e >> 4), w = (e & 15) >> 2;
-        float sc = (k & 3) == 0 ? 1.0f : ((k & 3) == 1 ? 0.0625f : ((k & 3) == 2 ? 0.00390625f : 0.000244140625f));
-        xs[blk * 32 + w * 8 + k] = v * sc;
-    }
+    if (p.normw) ok_in = mbar_wait(wbar, 0) && ok_in;
+    if (!ok_in && lane == 0) atomicExch(p.status, 3u);
     float scale = 1.0f;
     if (p.scaled) {
-        float tot;
+        float tot = 0.0f;
         if (p.ss) {  // reference form: fixed-order sum of add_norm_prep's partials
-            tot = 0.0f;
             for (uint32_t i = 0; i < p.nss; ++i) tot += p.ss[i];
         } else {
+            float ssq = 0.0f;
+            for (uint32_t j = threadIdx.x; j < p.cols; j += CT) ssq = fmaf(xs[j], xs[j], ssq);
             for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
             if (lane == 0) red[warp] = ssq;
-            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-            tot = 0.0f;
-            for (int i = 0; i < CONSUMER_WARPS; ++i) tot += red[i];
+            asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+            for (uint32_t i = 0; i < W; ++i) tot += red[i];
         }
         scale = 1.0f / sqrtf(tot / (float)p.cols + p.eps);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
 
-    // ---- consume micro-tiles ----
-    const uint32_t contributors = p.nkc * (p.epilogue == EPI_SWIGLU ? 2u : 1u);
-    for (uint32_t i = warp; i < items; i += CONSUMER_WARPS) {
-        uint32_t s = i % p.nslot, round = i / p.nslot;
-        if (!mbar_wait(&full[s], round & 1)) {
-            if (lane == 0) atomicExch(p.status, 2u);
-            return;
+    // ---- x to fixed point, once per block: thread t converts half block t (t + CT, ...) into shared memory ----
+    const uint32_t slice = warp % S, row_in_slot = warp / S;
+    const uint32_t nhb = p.cols / 16;
+    for (uint32_t hbi = threadIdx.x; hbi < nhb; hbi += CT) {
+        const uint32_t blk = hbi >> 1, half = hbi & 1;
+        float v[4][4];  // quad j: values that meet low/high nibbles of word x (j = 0, 1) and word y (j = 2, 3)
+#pragma unroll
+        for (int ww = 0; ww < 2; ++ww) {
+            const uint32_t e0 = blk * 32 + 8 * half + 4 * ww;
+            float4 lo = *reinterpret_cast<const float4 *>(xs + e0), hi = *reinterpret_cast<const float4 *>(xs + e0 + 16);
+            if (p.normw) {
+                float4 wl = *reinterpret_cast<const float4 *>(nws + e0), wh = *reinterpret_cast<const float4 *>(nws + e0 + 16);
+                lo.x *= wl.x; lo.y *= wl.y; lo.z *= wl.z; lo.w *= wl.w;
+                hi.x *= wh.x; hi.y *= wh.y; hi.z *= wh.z; hi.w *= wh.w;
+            }
+            v[2 * ww][0] = lo.x; v[2 * ww][1] = lo.y; v[2 * ww][2] = lo.z; v[2 * ww][3] = lo.w;
+            v[2 * ww + 1][0] = hi.x; v[2 * ww + 1][1] = hi.y; v[2 * ww + 1][2] = hi.z; v[2 * ww + 1][3] = hi.w;
         }
-        uint32_t m = m0 + i;          // logical micro-tile
-        uint32_t rt = m / p.nkc, c = m % p.nkc;  // 64-row group (over all matrices) and column chunk
-        float v0, v1;
-        microtile_dot<QT>(ring + (size_t)s * MTB, xs + c * 128, lane, v0, v1);
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[j][e]));
+        // step = 2^(exponent(amax) - 20): every |x| / step is below 2^21; zero (or denormal) groups get step 0
+        uint32_t ebits = __float_as_uint(amax) & 0x7F800000u;
+        bool live = ebits > (21u << 23) && ebits < 0x7F800000u;
+        // infinities and NaNs are not representable: their group's step carries them into the result
+        float step = live ? __uint_as_float(ebits - (20u << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
+        float inv = live ? __uint_as_float((254u << 23) - (ebits - (20u << 23))) : 0.0f;  // 1 / step, exact
+        int total = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int X[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                X[e] = __float2int_rn(v[j][e] * inv);
+                total += X[e];
+            }
+            // byte planes of the four integers: byte k of every X gathered into one word
+            uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);  // b0 b0' b1 b1'
+            uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);  // b2 b2' b3 b3'
+            xf[(3 * j + 0) * nhb + hbi] = __byte_perm(lo01, lo23, 0x5410);
+            xf[(3 * j + 1) * nhb + hbi] = __byte_perm(lo01, lo23, 0x7632);
+            xf[(3 * j + 2) * nhb + hbi] = __byte_perm(hi01, hi23, 0x5410);
+        }
+        xf[12 * nhb + hbi] = (uint32_t)total;
+        xf[13 * nhb + hbi] = __float_as_uint(step);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+    // ---- the lane's share: the same half blocks of every row ----
+    XFixed xr[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        uint32_t hbi = (slice * N + i) * 32 + lane;
+        bool ok = hbi < nhb;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int d = 0; d < 3; ++d) xr[i].d[j][d] = ok ? xf[(3 * j + d) * nhb + hbi] : 0u;
+        xr[i].total = ok ? (int)xf[12 * nhb + hbi] : 0;
+        xr[i].step = ok ? __uint_as_float(xf[13 * nhb + hbi]) : 0.0f;
+    }
+    const uint32_t hi_off = tiled_hi_off(p.cols), sc_off = tiled_scale_off(QT, p.cols);
+
+    // ---- consume slots: warp = (row pair in slot, slice); two rows at a time for instruction-level parallelism ----
+    for (uint32_t k = 0; k < total_slots; ++k) {
+        uint32_t s = k % p.nslot;
+        if (!mbar_wait(&full[s], (k / p.nslot) & 1)) {
+            // give up on the remaining slots but still meet the other warps at the barrier below
+            if (lane == 0) atomicExch(p.status, 2u);
+            break;
+        }
+        const uint32_t i = seg_of(k);
+        uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
+        const uint32_t ra = row_in_slot * 2;
+        if (ra < n) {
+            const bool two = ra + 1 < n;
+            const uint8_t *row_a = ring + (size_t)s * slot_bytes + (size_t)ra * row_bytes;
+            const uint8_t *row_b = two ? row_a + row_bytes : row_a;
+            float acc_a = 0.0f, acc_b = 0.0f;
+            // straight-line code: lanes past the end of the row read the last half block and multiply by step 0
+#pragma unroll
+            for (int it = 0; it < N; ++it) {
+                const uint32_t hbi = min((slice * N + it) * 32 + lane, nhb - 1);
+                uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
+                uint2 cb = *reinterpret_cast<const uint2 *>(row_b + hbi * 8);
+                uint32_t ha = 0, hb = 0;
+                if (QT == BRASA_Q6_0) {
+                    ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
+                    hb = *reinterpret_cast<const uint32_t *>(row_b + hi_off + hbi * 4);
+                }
+                float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
+                float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
+                int sa = half_block_idot<QT>(ca, ha, xr[it]);
+                int sb = half_block_idot<QT>(cb, hb, xr[it]);
+                acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+                acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+                acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
+            }
+            // partial index: rows of all segments in order, slices innermost
+            const uint32_t rows_before = SEG_PICK(seg_before, i);
+            if (lane == 0) {
+                part[(rows_before + first + ra) * S + slice] = acc_a;
+                if (two) part[(rows_before + first + ra + 1) * S + slice] = acc_b;
+            }
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        float *part = p.partials + (size_t)m * MT_ROWS;
-        __stcg(part + lane, v0);
-        __stcg(part + lane + 32, v1);
-        __threadfence();
-        __syncwarp();
-        // which counter: SwiGLU pairs the gate and up groups of the same rows
-        uint32_t rt_gate = 0, ci = rt;
-        if (p.epilogue == EPI_SWIGLU) {
-            uint32_t per = p.mt_count[0] / p.nkc;
-            rt_gate = rt % per;
-            ci = rt_gate;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+
+    // ---- epilogue: one thread per output row of this block ----
+    if (p.epilogue == EPI_SWIGLU) {
+        uint32_t nr = r1 - r0;
+        for (uint32_t j = threadIdx.x; j < nr; j += CT) {
+            float g = 0.0f, u = 0.0f;
+            for (uint32_t sl = 0; sl < S; ++sl) { g += part[j * S + sl]; u += part[(nr + j) * S + sl]; }
+            g *= scale; u *= scale;
+            p.y[0][r0 + j] = (g / (1.0f + expf(-g))) * u;
         }
-        uint32_t old = 0;
-        if (lane == 0) old = atomicAdd(&p.counters[ci], 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old != contributors - 1) continue;
-        // last to arrive for this row group: fixed-order sum of all column chunks, epilogue, store
-        __threadfence();
-        if (lane == 0) p.counters[ci] = 0;
-        if (p.epilogue == EPI_SWIGLU) {
-            uint32_t per = p.mt_count[0] / p.nkc;
-            const float *pg = p.partials + (size_t)rt_gate * p.nkc * MT_ROWS;
-            const float *pu = p.partials + (size_t)(per + rt_gate) * p.nkc * MT_ROWS;
-            float g0 = 0, g1 = 0, u0 = 0, u1 = 0;
-            for (uint32_t cc = 0; cc < p.nkc; ++cc) {
-                g0 += __ldcg(pg + cc * MT_ROWS + lane);
-                g1 += __ldcg(pg + cc * MT_ROWS + lane + 32);
-                u0 += __ldcg(pu + cc * MT_ROWS + lane);
-                u1 += __ldcg(pu + cc * MT_ROWS + lane + 32);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            for (uint32_t j = threadIdx.x; j < seg_rows[i]; j += CT) {
+                float v = 0.0f;
+                for (uint32_t sl = 0; sl < S; ++sl) v += part[(seg_before[i] + j) * S + sl];
+                uint32_t r = seg_first[i] + j;
+                v *= scale;
+                if (p.epilogue == EPI_RESID) v += p.resid[r];
+                p.y[i][r] = v;
             }
-            g0 *= scale; g1 *= scale; u0 *= scale; u1 *= scale;
-            float *y = p.y[0] + (size_t)rt_gate * MT_ROWS;
-            y[lane] = (g0 / (1.0f + expf(-g0))) * u0;
-            y[lane + 32] = (g1 / (1.0f + expf(-g1))) * u1;
-        } else {
-            const float *pp = p.partials + (size_t)rt * p.nkc * MT_ROWS;
-            float t0 = 0, t1 = 0;
-            for (uint32_t cc = 0; cc < p.nkc; ++cc) {
-                t0 += __ldcg(pp + cc * MT_ROWS + lane);
-                t1 += __ldcg(pp + cc * MT_ROWS + lane + 32);
-            }
-            uint32_t mi = 0, r = rt;
-            while (mi + 1 < p.nmat && r >= p.mt_count[mi] / p.nkc) { r -= p.mt_count[mi] / p.nkc; ++mi; }
-            float *y = p.y[mi] + (size_t)r * MT_ROWS;
-            y[lane] = t0 * scale;
-            y[lane + 32] = t1 * scale;
         }
     }
+#undef SEG_PICK
 }
 
 // ---- file-layout fallback: one warp per row, any shape (cols % 32 == 0) ----------------------
@@ -395,54 +464,81 @@ __global__ void swiglu_inplace_kernel(float *g, const float *u, uint32_t n) {
 }  // namespace
 
 // Shared by the model's fused decode path (model.cu) and the reference-shaped entry points below.
+// epilogue: 0 scale, 1 SwiGLU (w[0] = gate, w[1] = up, y[0]), 2 residual (y = resid + W x).
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
-                          int epilogue) {
+                          int epilogue, const float *resid) {
     brasa_ctx *ctx = cmd->ctx;
     GemvParams p{};
     p.nmat = nmat;
     p.cols = w[0].cols;
-    p.nkc = p.cols / (32 * MT_BLOCKS);
-    uint32_t total = 0, groups = 0;
+    uint32_t total_rows = 0;
     for (uint32_t i = 0; i < nmat; ++i) {
         BRASA_REQUIRE(ctx, w[i].layout == BRASA_LAYOUT_TILED && w[i].qtype == qtype && w[i].cols == p.cols && tiled_ok(qtype, w[i].rows, w[i].cols),
                       "gemv: matrix %u is not a tiled %s matrix of %u columns", i, qtype == BRASA_Q4_0 ? "q4_0" : "q6_0", p.cols);
         BRASA_REQUIRE(ctx, qm_fits(w[i]) && w[i].data.offset % 16 == 0, "gemv: matrix %u exceeds its buffer or is misaligned", i);
         p.w[i] = arg_ptr(w[i].data);
         p.y[i] = y[i];
-        p.mt_count[i] = (w[i].rows / MT_ROWS) * p.nkc;
-        total += p.mt_count[i];
-        groups += w[i].rows / MT_ROWS;
+        p.rows[i] = w[i].rows;
+        total_rows += w[i].rows;
     }
-    if (epilogue == EPI_SWIGLU) BRASA_REQUIRE(ctx, nmat == 2 && w[0].rows == w[1].rows, "gemv swiglu: gate and up must have the same rows");
-    p.total_mt = total;
+    if (epilogue == EPI_SWIGLU) {
+        BRASA_REQUIRE(ctx, nmat == 2 && w[0].rows == w[1].rows, "gemv swiglu: gate and up must have the same rows");
+        total_rows = w[0].rows;
+    }
+    if (epilogue == EPI_RESID) BRASA_REQUIRE(ctx, nmat == 1 && resid, "gemv residual: one matrix and a residual vector");
     p.epilogue = epilogue;
-    p.x = x; p.h = h; p.normw = normw; p.x_out = x_out; p.ss = ss; p.nss = nss;
+    p.x = x; p.h = h; p.normw = normw; p.x_out = x_out; p.ss = ss; p.nss = nss; p.resid = resid;
     p.scaled = scaled; p.eps = eps;
-    BRASA_TRY(brasa_gemv_scratch(ctx, (size_t)total * MT_ROWS, groups));
-    p.partials = ctx->gemv_partials;
-    p.counters = ctx->gemv_counters;
     p.status = ctx->status;
 
-    const int mtb = mt_bytes(qtype);
-    uint32_t grid = std::min<uint32_t>((uint32_t)ctx->sm_count, total);
-    uint32_t per_block = (total + grid - 1) / grid;
-    size_t fixed = (size_t)p.cols * 4 + 256;
-    size_t budget = ctx->smem_optin - fixed - 2048;
-    uint32_t nslot = (uint32_t)std::min<size_t>(per_block, budget / (mtb + 16));
-    BRASA_REQUIRE(ctx, nslot >= 1, "gemv: %u columns do not fit shared memory", p.cols);
-    p.nslot = nslot;
-    size_t smem = (size_t)nslot * mtb + fixed + (size_t)nslot * 16;
+    // slices and half blocks per lane: the smallest slice count that keeps a lane's x within 5 half blocks
+    const uint32_t nhb = p.cols / 16;
+    uint32_t S = 1, N = 0;
+    for (;; ++S) {
+        N = (nhb + 32 * S - 1) / (32 * S);
+        if (N <= 5) break;
+    }
+    BRASA_REQUIRE(ctx, S <= MAX_WARPS, "gemv: %u columns need more column slices than the kernel has warps", p.cols);
+    uint32_t warps = 8 % S == 0 ? 8 : (MAX_WARPS / S) * S;
+    p.slices = S;
+    p.warps = warps;
+    p.rows_per_slot = 2 * warps / S;  // every warp takes two rows of a slot
 
-    auto kern = qtype == BRASA_Q4_0 ? gemv_tiled_kernel<BRASA_Q4_0> : gemv_tiled_kernel<BRASA_Q6_0>;
-    bool &attr_done = ctx->gemv_attr_done[qtype == BRASA_Q4_0 ? 0 : 1];
+    const uint32_t row_bytes = tiled_row_bytes(qtype, p.cols);
+    const uint32_t slot_bytes = p.rows_per_slot * row_bytes;
+    uint32_t grid = std::min<uint32_t>((uint32_t)ctx->sm_count, total_rows);
+    uint32_t rows_per_block = (total_rows + grid - 1) / grid;
+    p.max_items = (rows_per_block + 1) * S * (epilogue == EPI_SWIGLU ? 2 : 1) + S * nmat;
+    size_t fixed = (size_t)p.cols * 4 * (normw ? 2 : 1) + (size_t)(p.cols / 16) * 56 + (size_t)((p.max_items + 1) & ~1u) * 4 + 160;
+    BRASA_REQUIRE(ctx, fixed + slot_bytes + 64 <= ctx->smem_optin, "gemv: %u columns do not fit shared memory", p.cols);
+    uint32_t segs = epilogue == EPI_SWIGLU ? 2 : nmat;
+    uint32_t need_slots = (rows_per_block + 1 + p.rows_per_slot - 1) / p.rows_per_slot * (epilogue == EPI_SWIGLU ? 2 : 1) + segs;
+    size_t budget = ctx->smem_optin - fixed - 1024;
+    uint32_t nslot = (uint32_t)std::min<size_t>(need_slots, budget / (slot_bytes + 16));
+    BRASA_REQUIRE(ctx, nslot >= 1, "gemv: no room for a ring slot");
+    p.nslot = nslot;
+    size_t smem = (size_t)nslot * slot_bytes + fixed + (size_t)nslot * 16;
+
+    void (*kern)(GemvParams) = nullptr;
+#define PICK(QT)                                                 \
+    switch (N) {                                                 \
+    case 1: kern = gemv_rows_kernel<QT, 1>; break;               \
+    case 2: kern = gemv_rows_kernel<QT, 2>; break;               \
+    case 3: kern = gemv_rows_kernel<QT, 3>; break;               \
+    case 4: kern = gemv_rows_kernel<QT, 4>; break;               \
+    default: kern = gemv_rows_kernel<QT, 5>; break;              \
+    }
+    if (qtype == BRASA_Q4_0) { PICK(BRASA_Q4_0) } else { PICK(BRASA_Q6_0) }
+#undef PICK
+    bool &attr_done = ctx->gemv_attr_done[(qtype == BRASA_Q4_0 ? 0 : 5) + (N - 1)];
     if (!attr_done) {
         BRASA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.blockDim = dim3((warps + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -451,7 +547,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
-    return BRASA_OK;
+    return brasa_post_launch(cmd, "gemv_rows");
 }
 
 namespace {
@@ -483,7 +579,7 @@ int32_t gemv_any(brasa_cmd *cmd, const brasa_qmatrix &w, brasa_arg x, brasa_arg 
         for (uint32_t t = 0; t < tokens; ++t) {
             float *yt = (float *)arg_ptr(y) + (size_t)t * w.rows;
             BRASA_TRY(brasa_gemv_launch(cmd, w.qtype, 1, &w, &yt, (const float *)arg_ptr(x) + (size_t)t * w.cols, nullptr, nullptr, nullptr, ssp,
-                                        nss, scaled, eps, EPI_SCALE));
+                                        nss, scaled, eps, EPI_SCALE, nullptr));
         }
         return BRASA_OK;
     }
@@ -533,7 +629,7 @@ int32_t brasa_k_gemv_scaled3(brasa_cmd *cmd, const brasa_qmatrix w[3], brasa_arg
     BRASA_REQUIRE(ctx, arg_fits(xw, (uint64_t)w[0].cols * 4) && arg_fits(ss, (uint64_t)nss * 4), "gemv_scaled3: xw or ss too small");
     float *ys[3] = {(float *)arg_ptr(y[0]), (float *)arg_ptr(y[1]), (float *)arg_ptr(y[2])};
     return brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, ys, (const float *)arg_ptr(xw), nullptr, nullptr, nullptr, (const float *)arg_ptr(ss), nss, 1,
-                             eps, EPI_SCALE);
+                             eps, EPI_SCALE, nullptr);
 }
 
 int32_t brasa_k_gemv_scaled_swiglu(brasa_cmd *cmd, brasa_qmatrix gate, brasa_qmatrix up, brasa_arg xw, brasa_arg ss, float eps, brasa_arg y) {
@@ -548,9 +644,9 @@ int32_t brasa_k_gemv_scaled_swiglu(brasa_cmd *cmd, brasa_qmatrix gate, brasa_qma
         brasa_qmatrix w[2] = {gate, up};
         float *ys[2] = {(float *)arg_ptr(y), nullptr};
         return brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, ys, (const float *)arg_ptr(xw), nullptr, nullptr, nullptr, (const float *)arg_ptr(ss), nss,
-                                 1, eps, EPI_SWIGLU);
+                                 1, eps, EPI_SWIGLU, nullptr);
     }
-    // file layout: gate into y, up into the split-K scratch, then SwiGLU in place
+    // file layout: gate into y, up into scratch, then SwiGLU in place
     BRASA_TRY(brasa_gemv_scratch(ctx, gate.rows, 1));
     BRASA_TRY(gemv_file(cmd, gate, (const float *)arg_ptr(xw), (float *)arg_ptr(y), 1, (const float *)arg_ptr(ss), nss, eps, 1));
     BRASA_TRY(gemv_file(cmd, up, (const float *)arg_ptr(xw), ctx->gemv_partials, 1, (const float *)arg_ptr(ss), nss, eps, 1));

@@ -405,7 +405,7 @@ static uint64_t workspace_bytes(const brasa_model_shape *m, const brasa_session_
     auto f = [](uint64_t n) { return brasa_plan_buffer_bytes(4 * n); };
     uint64_t t = s->max_tokens, h = m->hidden, qd = (uint64_t)m->heads * m->head_dim, kvd = (uint64_t)m->kv_heads * m->head_dim, ffn = m->ffn;
     uint64_t widest = std::max(ffn, std::max(qd, h));
-    return 4 * f(t * h)                                 // x (two copies for the decode ping-pong), h, norm_out
+    return 3 * f(t * h)                                 // x, h, norm_out
            + 2 * f(t * qd)                              // q, attn
            + 2 * f(t * kvd)                             // k_new, v_new
            + 2 * f(t * ffn)                             // gate, up

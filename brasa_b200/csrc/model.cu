@@ -17,7 +17,7 @@
 
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
-                          int epilogue);
+                          int epilogue, const float *resid);
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
 
 namespace {
@@ -51,7 +51,7 @@ struct brasa_model {
     brasa_buf *kc = nullptr, *vc = nullptr;  // [layers, cap, kv_heads, head_dim] in the cache type
     uint32_t cap = 0;
     // workspace
-    brasa_buf *x = nullptr, *x2 = nullptr, *h = nullptr, *q = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr, *xh = nullptr,
+    brasa_buf *x = nullptr, *h = nullptr, *q = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr, *xh = nullptr,
               *gate = nullptr, *up = nullptr, *ids = nullptr, *norm_out = nullptr, *ss = nullptr, *partials = nullptr, *logits = nullptr,
               *next_id = nullptr, *out_ids = nullptr;
     uint64_t partials_len = 0;
@@ -208,21 +208,20 @@ bool decode_fused_ok(brasa_model *m) {
            m->cfg.heads / m->cfg.kv_heads <= 8;
 }
 
-// One token through all layers, fused decode order. The residual stream alternates between ws.x and
-// ws.x2: a GEMV that consumes "x + h" writes the sum to the other buffer. Leaves logits in ws.logits.
-// first_layer/last_layer allow run_layers to use the same code.
+// One token through layers [layer_begin, layer_end), fused decode order, in place on ws.x:
+//   q, k, v = W (RMSNorm(x));  attention;  x += Wo attn;  act = silu(Wg n) * (Wu n), n = RMSNorm(x);  x += Wd act
+// RMSNorm is folded into the GEMV that consumes it and the residual adds into the GEMV that produces
+// the addend. with_head adds the final norm and the lm_head GEMV into ws.logits.
 int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t pos0, uint32_t layer_begin, uint32_t layer_end, bool with_head) {
     const brasa_config &c = m->cfg;
-    brasa_buf *xc = m->x, *xo = m->x2;
-    bool pending = false;  // ws.h holds a residual not yet added to xc
+    enum { SCALE = 0, SWIGLU = 1, RESID = 2 };  // epilogues of brasa_gemv_launch
+    float *x = F(m->x);
     for (uint32_t li = layer_begin; li < layer_end; ++li) {
         Layer &l = m->layers[li];
         {
             brasa_qmatrix w[3] = {l.wq.q, l.wk.q, l.wv.q};
             float *y[3] = {F(m->q), F(m->k_new), F(m->v_new)};
-            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, y, F(xc), pending ? F(m->h) : nullptr, F(l.attn_norm), pending ? F(xo) : nullptr,
-                                        nullptr, 0, 1, c.eps, 0));
-            if (pending) std::swap(xc, xo);
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, y, x, nullptr, F(l.attn_norm), nullptr, nullptr, 0, 1, c.eps, SCALE, nullptr));
         }
         brasa_attn_shape sh{1, c.heads, c.kv_heads, c.head_dim, pos0, m->limits.kv};
         KvView dst = kv_at(m, li, pos0), all = kv_at(m, li, 0);
@@ -230,32 +229,23 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t pos0, uint3
         BRASA_TRY(brasa_k_qk_norm_rope_store(cmd, m->limits.kv, qkv, norms, c.eps, A(m->rope_cos), A(m->rope_sin), c.head_dim, m->limits.ctx, dsts, sh));
         BRASA_TRY(brasa_k_decode_attention(cmd, A(m->q), all.k, all.v, A(m->partials), m->partials_len, A(m->attn), sh));
         {
-            float *y[1] = {F(m->h)};
-            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, 0));
+            float *y[1] = {x};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
         {
             brasa_qmatrix w[2] = {l.gate.q, l.up.q};
             float *y[2] = {F(m->gate), nullptr};
-            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, y, F(xc), F(m->h), F(l.ffn_norm), F(xo), nullptr, 0, 1, c.eps, 1));
-            std::swap(xc, xo);
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, y, x, nullptr, F(l.ffn_norm), nullptr, nullptr, 0, 1, c.eps, SWIGLU, nullptr));
         }
         {
-            float *y[1] = {F(m->h)};
-            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, 0));
+            float *y[1] = {x};
+            BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
-        pending = true;
     }
     if (with_head) {
         float *y[1] = {F(m->logits)};
-        BRASA_TRY(brasa_gemv_launch(cmd, m->head.q.qtype, 1, &m->head.q, y, F(xc), pending ? F(m->h) : nullptr, F(m->final_norm),
-                                    pending ? F(xo) : nullptr, nullptr, 0, 1, c.eps, 0));
-        if (pending) std::swap(xc, xo);
-        pending = false;
+        BRASA_TRY(brasa_gemv_launch(cmd, m->head.q.qtype, 1, &m->head.q, y, x, nullptr, F(m->final_norm), nullptr, nullptr, 0, 1, c.eps, SCALE, nullptr));
     }
-    if (pending) {  // run_layers: materialise x + h
-        BRASA_TRY(brasa_k_add(cmd, A(xc), A(m->h), A(xc), c.hidden));
-    }
-    if (xc != m->x) BRASA_CUDA(m->ctx, cudaMemcpyAsync(m->x->ptr, xc->ptr, (size_t)c.hidden * 4, cudaMemcpyDeviceToDevice, m->ctx->stream));
     return BRASA_OK;
 }
 
@@ -376,7 +366,6 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         BRASA_TRY(alloc_buf(m, brasa_kv_bytes(limits.kv, kv_elems), &m->kc, &m->alloc.kv));
         BRASA_TRY(alloc_buf(m, brasa_kv_bytes(limits.kv, kv_elems), &m->vc, &m->alloc.kv));
         BRASA_TRY(alloc_buf(m, t * H * 4, &m->x, ws));
-        BRASA_TRY(alloc_buf(m, t * H * 4, &m->x2, ws));
         BRASA_TRY(alloc_buf(m, t * H * 4, &m->h, ws));
         BRASA_TRY(alloc_buf(m, t * H * 4, &m->norm_out, ws));
         BRASA_TRY(alloc_buf(m, t * qd * 4, &m->q, ws));

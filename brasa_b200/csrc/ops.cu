@@ -107,18 +107,15 @@ __global__ void embed_kernel(const uint8_t *table, const uint32_t *ids, float *o
             q = (lo | (hi << 4)) - 32;
         }
     } else {
-        const uint8_t *tb = table + ((size_t)(r / MT_ROWS) * (nb / MT_BLOCKS) + b / MT_BLOCKS) * MT_BYTES_Q6;
-        uint32_t slot = (b % MT_BLOCKS) * MT_ROWS + r % MT_ROWS;
-        const uint8_t *codes = tb + slot * 16;
-        const uint32_t *hw = reinterpret_cast<const uint32_t *>(tb + MT_BLOCKS * MT_ROWS * 16 + slot * 8);
-        d = __half2float(*reinterpret_cast<const __half *>(tb + MT_BLOCKS * MT_ROWS * 24 + slot * 2));
+        const uint8_t *row = table + (size_t)r * tiled_row_bytes(BRASA_Q6_0, h);
+        const uint8_t *codes = row + b * 16;
+        const uint32_t *hw = reinterpret_cast<const uint32_t *>(row + tiled_hi_off(h) + b * 8);
+        d = __half2float(*reinterpret_cast<const __half *>(row + tiled_scale_off(BRASA_Q6_0, h) + b * 2));
         int byte = codes[j & 15];
         int lo = j < 16 ? (byte & 15) : (byte >> 4);
         // element j lives in code word w = (j & 15) / 4 as nibble k = 2 * (j & 3) + (j >= 16)
         int w = (j & 15) >> 2, k = 2 * (j & 3) + (j >> 4);
-        int pos = 4 * (k & 3) + 4 + 2 * (k >> 2);
-        if (w & 1) pos = (pos + 16) & 31;
-        int hi = (hw[w >> 1] >> pos) & 3;
+        int hi = (hw[w >> 1] >> q6_hi_bitpos(w & 1, k)) & 3;
         q = (lo | (hi << 4)) - 32;
     }
     out[idx] = d * (float)q;

@@ -3,23 +3,14 @@
 // The `.brasa` block formats follow crates/quant/src/qtype.rs:5-29 and the quantisers
 // crates/quant/src/convert.rs:70-151 (IEEE division, round-half-even, f16 scale with
 // round-to-nearest-even); every kernel here is bit-exact against that specification.
+#include <type_traits>
+
 #include "brasa_internal.h"
 
 namespace {
 
 __device__ __forceinline__ uint16_t ld16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
 __device__ __forceinline__ void st16(uint8_t *p, uint16_t v) { *reinterpret_cast<uint16_t *>(p) = v; }
-
-// Position of the 2-bit high field of code `e` (0..15 within a pair of code words) in the q6 tiled
-// high-bit word: chosen so that (word >> {0,2}) or (rotr(word,16) >> {0,2}) puts the field directly
-// above its low nibble (see gemv.cu).
-__host__ __device__ __forceinline__ int q6_hi_bitpos(int word_in_pair, int k) {
-    // k: nibble index 0..7 inside the code word; low half k<4 sits at bits 4k, high half at 4(k-4)+16
-    int kk = k & 3, high_half = k >> 2;
-    int pos = 4 * kk + 4 + 2 * high_half;  // position wanted after the shift by 2*high_half
-    if (word_in_pair) pos = (pos + 16) & 31;
-    return pos;
-}
 
 // One thread per 32-weight block.
 template <int QT, bool TO_TILED>
@@ -28,14 +19,11 @@ __global__ void repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restri
     if (i >= (uint64_t)rows * nb) return;
     uint32_t r = (uint32_t)(i / nb), b = (uint32_t)(i % nb);
     constexpr int BB = QT == BRASA_Q4_0 ? 18 : 26;
-    constexpr int MTB = MT_BLOCKS * MT_ROWS * BB;
-    uint64_t mt = (uint64_t)(r / MT_ROWS) * (nb / MT_BLOCKS) + b / MT_BLOCKS;
-    uint32_t slot = (b % MT_BLOCKS) * MT_ROWS + r % MT_ROWS;
-    uint8_t *fp = (uint8_t *)(TO_TILED ? src : dst) + i * BB;            // file-layout block
-    uint8_t *tb = (uint8_t *)(TO_TILED ? dst : src) + mt * MTB;          // micro-tile base
-    uint8_t *codes = tb + slot * 16;
-    constexpr int NSLOT = MT_BLOCKS * MT_ROWS;
-    uint8_t *scale = tb + NSLOT * (BB - 2) + slot * 2;
+    const uint32_t cols = nb * 32;
+    uint8_t *fp = (uint8_t *)(TO_TILED ? src : dst) + i * BB;                                   // file-layout block
+    uint8_t *row = (uint8_t *)(TO_TILED ? dst : src) + (size_t)r * tiled_row_bytes(QT, cols);   // tiled row
+    uint8_t *codes = row + b * 16;
+    uint8_t *scale = row + tiled_scale_off(QT, cols) + b * 2;
     if (TO_TILED) {
         st16(scale, ld16(fp));
         for (int j = 0; j < 8; ++j) st16(codes + 2 * j, ld16(fp + 2 + 2 * j));
@@ -44,7 +32,7 @@ __global__ void repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restri
         for (int j = 0; j < 8; ++j) st16(fp + 2 + 2 * j, ld16(codes + 2 * j));
     }
     if (QT == BRASA_Q6_0) {
-        uint8_t *hi = tb + NSLOT * 16 + slot * 8;  // two 32-bit words
+        uint32_t *hi = reinterpret_cast<uint32_t *>(row + tiled_hi_off(cols) + b * 8);  // two words
         if (TO_TILED) {
             uint32_t h[2] = {0, 0};
             for (int w = 0; w < 4; ++w)
@@ -53,10 +41,10 @@ __global__ void repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restri
                     uint32_t two = (fp[18 + (e & 7)] >> (2 * (e >> 3))) & 3u;
                     h[w >> 1] |= two << q6_hi_bitpos(w & 1, k);
                 }
-            reinterpret_cast<uint32_t *>(hi)[0] = h[0];
-            reinterpret_cast<uint32_t *>(hi)[1] = h[1];
+            hi[0] = h[0];
+            hi[1] = h[1];
         } else {
-            uint32_t h[2] = {reinterpret_cast<uint32_t *>(hi)[0], reinterpret_cast<uint32_t *>(hi)[1]};
+            uint32_t h[2] = {hi[0], hi[1]};
             uint8_t qh[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int w = 0; w < 4; ++w)
                 for (int k = 0; k < 8; ++k) {
@@ -176,7 +164,7 @@ int32_t launch_by_qtype(brasa_cmd *cmd, int32_t qtype, F &&f) {
 int32_t repack_common(brasa_cmd *cmd, int32_t qtype, brasa_arg src, brasa_arg dst, uint32_t rows, uint32_t cols, bool to_tiled) {
     if (!cmd) return BRASA_EINVAL;
     brasa_ctx *ctx = cmd->ctx;
-    BRASA_REQUIRE(ctx, tiled_ok(qtype, rows, cols), "tiled layout needs q4_0/q6_0, rows %% 64 == 0 and cols %% 128 == 0 (got %u x %u)", rows, cols);
+    BRASA_REQUIRE(ctx, tiled_ok(qtype, rows, cols), "the tiled layout needs q4_0 or q6_0 and cols %% 256 == 0 (got %u x %u)", rows, cols);
     uint64_t bytes = brasa_qtype_nbytes(qtype, (uint64_t)rows * cols);
     BRASA_REQUIRE(ctx, arg_fits(src, bytes) && arg_fits(dst, bytes), "repack: buffers smaller than the matrix");
     BRASA_REQUIRE(ctx, arg_ptr(src) != arg_ptr(dst), "repack cannot run in place");
@@ -202,7 +190,7 @@ int32_t brasa_k_repack(brasa_cmd *cmd, int32_t qtype, brasa_arg src, brasa_arg d
     return repack_common(cmd, qtype, src, dst, rows, cols, true);
 }
 int32_t brasa_k_unpack(brasa_cmd *cmd, int32_t qtype, brasa_arg src, brasa_arg dst, uint32_t rows, uint32_t cols) {
-    return repack_common(cmd, qtype, dst, src, rows, cols, false);
+    return repack_common(cmd, qtype, src, dst, rows, cols, false);
 }
 
 int32_t brasa_k_quantize(brasa_cmd *cmd, int32_t qtype, brasa_arg src, brasa_arg dst, uint64_t n) {

@@ -81,6 +81,8 @@ const char *brasa_last_error(brasa_ctx *ctx);
 int32_t brasa_ctx_device(brasa_ctx *ctx);
 int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total_bytes);
 int32_t brasa_ctx_sync(brasa_ctx *ctx);
+/* Kernels enqueued on this context so far; a graph replay counts every kernel it holds. */
+uint64_t brasa_ctx_launch_count(brasa_ctx *ctx);
 /* cudaStream_t of the context, for callers that order their own work (NCCL, torch) against it. */
 void *brasa_ctx_stream(brasa_ctx *ctx);
 
@@ -95,6 +97,16 @@ void *brasa_buf_ptr(brasa_buf *buf); /* device address */
 int32_t brasa_cmd_begin(brasa_ctx *ctx, brasa_cmd **out);     /* Context::command :237 */
 int32_t brasa_cmd_commit(brasa_cmd *cmd);                     /* Command::commit :379 */
 int32_t brasa_cmd_wait(brasa_cmd *cmd, double *gpu_seconds);  /* Pending::wait -> GpuTiming :411; frees cmd */
+
+/* CUDA graphs. No counterpart call in the reference, whose two command buffers per forward play this
+ * role (crates/models/src/qwen3.rs:781-797): kernels enqueued on the context between begin and end are
+ * recorded instead of run, and brasa_graph_launch replays them in one submission. Nothing that
+ * allocates or synchronises may be called while a capture is open. */
+typedef struct brasa_graph brasa_graph;
+int32_t brasa_graph_capture_begin(brasa_ctx *ctx);
+int32_t brasa_graph_capture_end(brasa_ctx *ctx, brasa_graph **out);
+int32_t brasa_graph_launch(brasa_cmd *cmd, brasa_graph *graph);
+void brasa_graph_free(brasa_graph *graph);
 
 /* ---- helpers (crates/kernels/src/lib.rs:1316-1404) ------------------------------------------ */
 

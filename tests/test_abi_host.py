@@ -107,7 +107,7 @@ def test_planner_arithmetic(B, golden_dir):
     assert p["kv"] == 2 * bb(2 * (2 * cap * 2 * 128))
     f = lambda n: bb(4 * n)
     t, h, qd, kvd, ffn = 64, 256, 512, 256, 512
-    want_ws = (4 * f(t * h) + 2 * f(t * qd) + 2 * f(t * kvd) + 2 * f(t * ffn) + bb(2 * t * 512) + f(t) + f(1)
+    want_ws = (3 * f(t * h) + 2 * f(t * qd) + 2 * f(t * kvd) + 2 * f(t * ffn) + bb(2 * t * 512) + f(t) + f(1)
                + f(4 * 3 * 130) + f(2 * 512) + 2 * f(300 * 64))
     assert p["workspace"] == want_ws
     assert p["weights"] == shape.weight_bytes and p["overhead"] == 256 << 20

@@ -48,7 +48,7 @@ def tiled(B, ctx, K, name, raw, rows, cols):
 
 @pytest.mark.parametrize("name", ["q4_0", "q6_0"])
 def test_repack_is_a_bijection(B, ctx, K, name):
-    rows, cols = 192, 384
+    rows, cols = 100, 512
     raw = O.Rng(5).qmatrix(QT[name][0], rows, cols)
     _, t = tiled(B, ctx, K, name, raw, rows, cols)
     packed = t.download(np.uint8)
@@ -57,7 +57,7 @@ def test_repack_is_a_bijection(B, ctx, K, name):
     run(ctx, lambda c: K.unpack(c, QT[name][1], t, back, rows, cols))
     assert np.array_equal(back.download(np.uint8), raw)
     with pytest.raises(B.BrasaError):
-        run(ctx, lambda c: K.repack(c, QT[name][1], t, back, 100, cols))
+        run(ctx, lambda c: K.repack(c, QT[name][1], t, back, rows, 100))
 
 
 @pytest.mark.parametrize("name", ["q4_0", "q6_0", "q8_0"])
@@ -153,7 +153,7 @@ def test_rope(B, ctx, K, pos0):
 
 def test_embed_exact(B, ctx, K):
     rng = O.Rng(14)
-    vocab, h = 256, 384
+    vocab, h = 256, 512
     ids = np.array([0, 255, 17, 17, 128, 64, 63], dtype=np.uint32)
     gi = ctx.buffer_from(ids)
     for name in ("q6_0", "q8_0"):
@@ -207,7 +207,7 @@ def test_gemv_layouts_and_types(B, ctx, K, name, rows, cols):
             run(ctx, lambda c: fn(c, m, gx, gy, tokens))
             got = gy.download(np.float32).reshape(tokens, rows)
             assert np.max(np.abs(got - want) / scale) <= 1e-5, (name, fn.__name__)
-        if name != "q8_0" and rows % 64 == 0 and cols % 128 == 0:
+        if name != "q8_0" and cols % 256 == 0:
             mt, _ = tiled(B, ctx, K, name, raw, rows, cols)
             gy.fill(0xFF)
             run(ctx, lambda c: K.gemv(c, mt, gx, gy, tokens))
@@ -436,11 +436,11 @@ def test_flash_attention_gqa_causal(B, ctx, K, kv):
 
 # ---- prefill GEMM --------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (192, 256)])
+@pytest.mark.parametrize("rows,cols", [(4096, 2560), (2560, 9728), (192, 256), (100, 96)])
 def test_gemm_f16_and_f32(B, ctx, K, rows, cols):
     rng = O.Rng(18)
     raw = rng.qmatrix(O.Q4_0, rows, cols)
-    mt, _ = tiled(B, ctx, K, "q4_0", raw, rows, cols) if rows % 64 == 0 and cols % 128 == 0 else (None, None)
+    mt, _ = tiled(B, ctx, K, "q4_0", raw, rows, cols) if cols % 256 == 0 else (None, None)
     mf = B.QMatrix(ctx.buffer_from(raw), B.WeightType.Q4_0, rows, cols)
     for tokens in (9, 33, 64, 100, 150):
         x = rng.vec(tokens * cols, 1.0)
@@ -473,11 +473,13 @@ def test_gemm_swiglu_equals_unfused(B, ctx, K):
     fused = go.download(np.uint16, tokens * rows)
     run(ctx, lambda c: (K.gemm_multi(c, [g, u], gx, [gg, gu], tokens, B.PrefillPrecision.F16), K.swiglu_f16(c, gg, gu, go2, tokens * rows)))
     assert np.array_equal(fused, go2.download(np.uint16, tokens * rows))
-    wg, _ = O.matmul(O.Q4_0, graw, rows, cols, xh.astype(np.float32), f16_inputs=True)
-    wu, _ = O.matmul(O.Q4_0, uraw, rows, cols, xh.astype(np.float32), f16_inputs=True)
+    wg, sg = O.matmul(O.Q4_0, graw, rows, cols, xh.astype(np.float32), f16_inputs=True)
+    wu, su = O.matmul(O.Q4_0, uraw, rows, cols, xh.astype(np.float32), f16_inputs=True)
     want = O.swiglu(wg, wu).ravel()
     got = fused.view(np.float16).astype(np.float32)
-    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) <= 2e-3
+    # f32 accumulation error of gate and up carried through silu(g) * u, plus the final f16 rounding
+    bound = 1e-5 * (np.abs(wu) * 1.1 * sg + np.abs(wg) * su).ravel() + np.abs(want) * 2.0 ** -10 + 1e-7
+    assert np.all(np.abs(got - want) <= bound)
 
 
 # ---- argmax --------------------------------------------------------------------------------------

