@@ -224,6 +224,242 @@ __global__ void __launch_bounds__(256) prefill_attn_kernel(const float *q, const
     }
 }
 
+// ---- fused decode attention: QK-norm + RoPE + KV store + split-K attention + merge, one kernel ----
+// The position comes from device memory, so the same launch (recorded in a CUDA graph) serves every
+// step. Grid: (ceil(ctx / 128), kv heads); blocks whose chunk lies past the position return at once.
+// K and V tiles stay in the cache's own type in shared memory and are fetched with cp.async before the
+// kernel waits for q, k and v of this token (older rows never change). The block that owns the newest
+// position normalises, rotates, rounds and stores the new K and V rows and uses the rounded values.
+// The last block of a kv head to finish merges the chunk partials (arrival counter, no spinning).
+template <int KV> struct KvRow;
+template <> struct KvRow<BRASA_KV_F32> { static constexpr int BYTES = 512, STRIDE = 528; };
+template <> struct KvRow<BRASA_KV_F16> { static constexpr int BYTES = 256, STRIDE = 272; };
+template <> struct KvRow<BRASA_KV_Q8_0> { static constexpr int BYTES = 136, STRIDE = 144; };
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// element d of a tile row in the cache's type
+template <int KV>
+__device__ __forceinline__ float tile_at(const uint8_t *row, int d) {
+    if (KV == BRASA_KV_F32) return reinterpret_cast<const float *>(row)[d];
+    if (KV == BRASA_KV_F16) return __half2float(reinterpret_cast<const __half *>(row)[d]);
+    return __half2float(reinterpret_cast<const __half *>(row + 128)[d >> 5]) * (float)reinterpret_cast<const int8_t *>(row)[d];
+}
+
+// 8 consecutive elements starting at d (d % 8 == 0)
+template <int KV>
+__device__ __forceinline__ void tile_load8(const uint8_t *row, int d, float out[8]) {
+    if (KV == BRASA_KV_F32) {
+        float4 a = reinterpret_cast<const float4 *>(row)[d / 4], b = reinterpret_cast<const float4 *>(row)[d / 4 + 1];
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    } else if (KV == BRASA_KV_F16) {
+        uint4 v = reinterpret_cast<const uint4 *>(row)[d / 8];
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+        for (int j = 0; j < 4; ++j) {
+            float2 f = __half22float2(h[j]);
+            out[2 * j] = f.x; out[2 * j + 1] = f.y;
+        }
+    } else {
+        uint2 v = reinterpret_cast<const uint2 *>(row)[d / 8];
+        float sc = __half2float(reinterpret_cast<const __half *>(row + 128)[d >> 5]);
+        const int8_t *c = reinterpret_cast<const int8_t *>(&v);
+        for (int j = 0; j < 8; ++j) out[j] = sc * (float)c[j];
+    }
+}
+
+// The warp holds one row of 128 values (lane + 32 j). Writes it, rounded to the cache type, to both the
+// cache row in global memory and the tile row in shared memory.
+template <int KV>
+__device__ __forceinline__ void put_row(uint8_t *grow, uint8_t *srow, const float y[4], int lane) {
+    for (int j = 0; j < 4; ++j) {
+        if (KV == BRASA_KV_Q8_0) {
+            float amax = fabsf(y[j]);
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            __half dh = __float2half_rn(__fdiv_rn(amax, 127.0f));
+            float d = __half2float(dh);
+            int8_t q = (int8_t)(d == 0.0f ? 0.0f : fminf(fmaxf(rintf(__fdiv_rn(y[j], d)), -127.0f), 127.0f));
+            reinterpret_cast<int8_t *>(grow)[lane + 32 * j] = q;
+            reinterpret_cast<int8_t *>(srow)[lane + 32 * j] = q;
+            if (lane == 0) {
+                reinterpret_cast<__half *>(grow + 128)[j] = dh;
+                reinterpret_cast<__half *>(srow + 128)[j] = dh;
+            }
+        } else if (KV == BRASA_KV_F16) {
+            __half h = __float2half_rn(y[j]);
+            reinterpret_cast<__half *>(grow)[lane + 32 * j] = h;
+            reinterpret_cast<__half *>(srow)[lane + 32 * j] = h;
+        } else {
+            reinterpret_cast<float *>(grow)[lane + 32 * j] = y[j];
+            reinterpret_cast<float *>(srow)[lane + 32 * j] = y[j];
+        }
+    }
+}
+
+// per-head RMSNorm then NeoX RoPE of one row held by a warp (qkv.metal semantics)
+__device__ __forceinline__ void norm_rope_row(const float *x, const float *w, const float *cos_t, const float *sin_t, uint32_t pos, float eps,
+                                              int lane, float y[4]) {
+    float xv[4], ss = 0.0f;
+    for (int j = 0; j < 4; ++j) {
+        xv[j] = x[lane + 32 * j];
+        ss += xv[j] * xv[j];
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+    for (int j = 0; j < 4; ++j) y[j] = xv[j] * scale * w[lane + 32 * j];
+    for (int j = 0; j < 2; ++j) {
+        int i = lane + 32 * j;
+        float c = cos_t[(size_t)pos * 64 + i], s = sin_t[(size_t)pos * 64 + i];
+        float a = y[j], b = y[j + 2];
+        y[j] = a * c - b * s;
+        y[j + 2] = b * c + a * s;
+    }
+}
+
+struct FusedAttnParams {
+    const float *q, *k_new, *v_new, *q_norm, *k_norm, *cos_t, *sin_t;
+    uint8_t *kc, *vc;      // this layer's cache, position 0
+    float *partials;       // [hq][gridDim.x][130]
+    uint32_t *counters;    // [hkv], zero between launches
+    float *o;              // [hq][128]
+    const uint32_t *pos;   // device scalar: position of this token
+    uint32_t hq, hkv;
+    float eps, scale;
+};
+
+template <int KV>
+__global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedAttnParams p) {
+    constexpr int RB = KvRow<KV>::BYTES, RS = KvRow<KV>::STRIDE;
+    extern __shared__ __align__(16) uint8_t smraw[];
+    uint8_t *kt = smraw, *vt = smraw + 128 * RS;
+    float *qs = reinterpret_cast<float *>(vt + 128 * RS);  // [G][128]
+    float *ps = qs + 8 * 128;                               // [G][128]
+    float *red = ps + 8 * 128;                              // [16]
+    __shared__ bool last_block;
+    const uint32_t pos = *p.pos, lk = pos + 1, nchunks = (lk + 127) / 128;
+    const uint32_t chunk = blockIdx.x, kh = blockIdx.y, G = p.hq / p.hkv, max_chunks = gridDim.x;
+    if (chunk >= nchunks) return;
+    const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
+    const bool has_new = chunk == nchunks - 1;
+    const uint32_t nold = has_new ? nkeys - 1 : nkeys;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    // older rows never change: fetch them before this token's q, k, v exist
+    {
+        constexpr int VEC = KV == BRASA_KV_Q8_0 ? 8 : 16, PER_ROW = RB / VEC;
+        for (uint32_t i = t; i < nold * PER_ROW; i += 128) {
+            uint32_t r = i / PER_ROW, v = i % PER_ROW;
+            size_t goff = ((size_t)(key0 + r) * p.hkv + kh) * RB + (size_t)v * VEC;
+            if (KV == BRASA_KV_Q8_0) { cp_async8(kt + r * RS + v * VEC, p.kc + goff); cp_async8(vt + r * RS + v * VEC, p.vc + goff); }
+            else { cp_async16(kt + r * RS + v * VEC, p.kc + goff); cp_async16(vt + r * RS + v * VEC, p.vc + goff); }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // q heads of this group: norm + rope into shared memory (warps take heads round robin)
+    for (uint32_t g = warp; g < G; g += 4) {
+        float y[4];
+        norm_rope_row(p.q + (size_t)(kh * G + g) * 128, p.q_norm, p.cos_t, p.sin_t, pos, p.eps, lane, y);
+        for (int j = 0; j < 4; ++j) qs[g * 128 + lane + 32 * j] = y[j];
+    }
+    if (has_new) {
+        size_t grow = ((size_t)pos * p.hkv + kh) * RB;
+        if (warp == 3) {
+            float y[4];
+            norm_rope_row(p.k_new + (size_t)kh * 128, p.k_norm, p.cos_t, p.sin_t, pos, p.eps, lane, y);
+            put_row<KV>(p.kc + grow, kt + (nkeys - 1) * RS, y, lane);
+        } else if (warp == 2) {
+            float y[4];
+            for (int j = 0; j < 4; ++j) y[j] = p.v_new[(size_t)kh * 128 + lane + 32 * j];
+            put_row<KV>(p.vc + grow, vt + (nkeys - 1) * RS, y, lane);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // scores: one key per thread, all heads of the group
+    {
+        float s[8];
+        for (int g = 0; g < 8; ++g) s[g] = 0.0f;
+        if ((uint32_t)t < nkeys) {
+            const uint8_t *row = kt + t * RS;
+            for (int d = 0; d < 128; d += 8) {
+                float kv8[8];
+                tile_load8<KV>(row, d, kv8);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if ((uint32_t)g >= G) break;
+                    const float4 qa = *reinterpret_cast<const float4 *>(qs + g * 128 + d), qb = *reinterpret_cast<const float4 *>(qs + g * 128 + d + 4);
+                    float a = s[g];
+                    a = fmaf(qa.x, kv8[0], a); a = fmaf(qa.y, kv8[1], a); a = fmaf(qa.z, kv8[2], a); a = fmaf(qa.w, kv8[3], a);
+                    a = fmaf(qb.x, kv8[4], a); a = fmaf(qb.y, kv8[5], a); a = fmaf(qb.z, kv8[6], a); a = fmaf(qb.w, kv8[7], a);
+                    s[g] = a;
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            if ((uint32_t)g < G) ps[g * 128 + t] = (uint32_t)t < nkeys ? s[g] * p.scale : -INFINITY;
+    }
+    __syncthreads();
+    // partial softmax per head: warp w reduces heads w, w + 4
+    for (uint32_t g = warp; g < G; g += 4) {
+        float v0 = ps[g * 128 + lane], v1 = ps[g * 128 + lane + 32], v2 = ps[g * 128 + lane + 64], v3 = ps[g * 128 + lane + 96];
+        float m = fmaxf(fmaxf(v0, v1), fmaxf(v2, v3));
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        v0 = expf(v0 - m); v1 = expf(v1 - m); v2 = expf(v2 - m); v3 = expf(v3 - m);
+        ps[g * 128 + lane] = v0; ps[g * 128 + lane + 32] = v1; ps[g * 128 + lane + 64] = v2; ps[g * 128 + lane + 96] = v3;
+        float l = (v0 + v1) + (v2 + v3);
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) { red[g] = m; red[8 + g] = l; }
+    }
+    __syncthreads();
+    // P V: one output dimension per thread
+    float acc[8];
+    for (int g = 0; g < 8; ++g) acc[g] = 0.0f;
+    for (uint32_t j = 0; j < nkeys; ++j) {
+        float vv = tile_at<KV>(vt + j * RS, t);
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            if ((uint32_t)g < G) acc[g] = fmaf(ps[g * 128 + j], vv, acc[g]);
+    }
+    if (nchunks == 1) {  // nothing to merge
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+            if ((uint32_t)g < G) p.o[(size_t)(kh * G + g) * 128 + t] = acc[g] / red[8 + g];
+        return;
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        if ((uint32_t)g >= G) break;
+        float *out = p.partials + ((size_t)(kh * G + g) * max_chunks + chunk) * 130;
+        __stcg(out + 2 + t, acc[g]);
+        if (t == 0) { __stcg(out, red[g]); __stcg(out + 1, red[8 + g]); }
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) last_block = atomicAdd(&p.counters[kh], 1u) == nchunks - 1;
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    if (t == 0) p.counters[kh] = 0;
+    for (uint32_t g = 0; g < G; ++g) {
+        const float *pp = p.partials + (size_t)(kh * G + g) * max_chunks * 130;
+        float M = -INFINITY;
+        for (uint32_t c = 0; c < nchunks; ++c) M = fmaxf(M, __ldcg(pp + c * 130));
+        float L = 0.0f, a = 0.0f;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            float w = expf(__ldcg(pp + c * 130) - M);
+            L = fmaf(__ldcg(pp + c * 130 + 1), w, L);
+            a = fmaf(__ldcg(pp + c * 130 + 2 + t), w, a);
+        }
+        p.o[(size_t)(kh * G + g) * 128 + t] = a / L;
+    }
+}
+
 int32_t check_decode(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o,
                      const brasa_attn_shape &sh) {
     brasa_ctx *ctx = cmd->ctx;
@@ -269,6 +505,41 @@ int32_t decode_common(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, bra
 }
 
 }  // namespace
+
+// Used by the model's decode graph. Launched with programmatic dependent launch so that the KV tile
+// fetch overlaps the GEMV that produces q, k and v.
+int32_t brasa_attn_decode_fused_launch(brasa_cmd *cmd, int32_t kv, const float *q, const float *k_new, const float *v_new, const float *q_norm,
+                                       const float *k_norm, const float *cos_t, const float *sin_t, uint8_t *kc, uint8_t *vc, float *partials,
+                                       uint32_t *counters, float *o, const uint32_t *pos, uint32_t hq, uint32_t hkv, uint32_t ctx_len, float eps) {
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, hkv > 0 && hq % hkv == 0 && hq / hkv <= 8, "fused decode attention: GQA group must divide and be <= 8");
+    FusedAttnParams p{q, k_new, v_new, q_norm, k_norm, cos_t, sin_t, kc, vc, partials, counters, o, pos, hq, hkv, eps, 1.0f / sqrtf(128.0f)};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((ctx_len + 127) / 128, hkv);
+    cfg.blockDim = dim3(128);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define LAUNCH_FUSED(KVT)                                                                                                          \
+    do {                                                                                                                           \
+        size_t smem = 2 * 128 * KvRow<KVT>::STRIDE + (8 * 128 * 2 + 16) * sizeof(float);                                           \
+        static bool done = false;                                                                                                  \
+        if (!done) {                                                                                                               \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(attn_decode_fused_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            done = true;                                                                                                           \
+        }                                                                                                                          \
+        cfg.dynamicSmemBytes = smem;                                                                                               \
+        BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<KVT>, p));                                               \
+    } while (0)
+    if (kv == BRASA_KV_F32) LAUNCH_FUSED(BRASA_KV_F32);
+    else if (kv == BRASA_KV_F16) LAUNCH_FUSED(BRASA_KV_F16);
+    else LAUNCH_FUSED(BRASA_KV_Q8_0);
+#undef LAUNCH_FUSED
+    return brasa_post_launch(cmd, "attn_decode_fused");
+}
 
 extern "C" {
 

@@ -50,6 +50,8 @@ int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
     cudaMemset(ctx->status, 0, 256);
     const char *env = getenv("BRASA_PDL");
     if (env && env[0] == '0') ctx->pdl = false;
+    env = getenv("BRASA_GRAPH");
+    if (env && env[0] == '0') ctx->graphs = false;
     *out = ctx;
     return BRASA_OK;
 }

@@ -202,8 +202,6 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // Let the next kernel of the stream start its own weight prefetch.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     auto issue = [&](uint32_t k) {  // slot k of this block -> ring[k % nslot]
         const uint32_t i = seg_of(k);
@@ -238,8 +236,11 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
         }
         return;
     }
-    // Everything below depends on the previous kernel's output.
+    // Everything below depends on the previous kernel's output. Once that kernel is complete the next one
+    // of the stream may start its own weight prefetch: at most two kernels of the chain overlap, so a
+    // kernel's early reads (weights, older KV rows) never race with a producer further back.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- x in shared memory (bulk copy; with h: x + h through registers), sum of squares ----
     const uint32_t CT = W * 32;

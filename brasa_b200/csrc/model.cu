@@ -19,6 +19,11 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
                           int epilogue, const float *resid);
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
+int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
+                             uint32_t *pos);
+int32_t brasa_attn_decode_fused_launch(brasa_cmd *cmd, int32_t kv, const float *q, const float *k_new, const float *v_new, const float *q_norm,
+                                       const float *k_norm, const float *cos_t, const float *sin_t, uint8_t *kc, uint8_t *vc, float *partials,
+                                       uint32_t *counters, float *o, const uint32_t *pos, uint32_t hq, uint32_t hkv, uint32_t ctx_len, float eps);
 
 namespace {
 
@@ -53,7 +58,8 @@ struct brasa_model {
     // workspace
     brasa_buf *x = nullptr, *h = nullptr, *q = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr, *xh = nullptr,
               *gate = nullptr, *up = nullptr, *ids = nullptr, *norm_out = nullptr, *ss = nullptr, *partials = nullptr, *logits = nullptr,
-              *next_id = nullptr, *out_ids = nullptr;
+              *next_id = nullptr, *out_ids = nullptr, *dev_state = nullptr;  // dev_state: u32 pos, out_count, attention counters
+    brasa_graph *decode_graph = nullptr;  // one decode step: embed .. lm_head, argmax, advance
     uint64_t partials_len = 0;
     brasa_allocated alloc{};
     std::vector<brasa_buf *> owned;
@@ -211,8 +217,9 @@ bool decode_fused_ok(brasa_model *m) {
 // One token through layers [layer_begin, layer_end), fused decode order, in place on ws.x:
 //   q, k, v = W (RMSNorm(x));  attention;  x += Wo attn;  act = silu(Wg n) * (Wu n), n = RMSNorm(x);  x += Wd act
 // RMSNorm is folded into the GEMV that consumes it and the residual adds into the GEMV that produces
-// the addend. with_head adds the final norm and the lm_head GEMV into ws.logits.
-int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t pos0, uint32_t layer_begin, uint32_t layer_end, bool with_head) {
+// the addend. with_head adds the final norm and the lm_head GEMV into ws.logits. The position is read by
+// the attention kernel from dev_state[0], so the same sequence of launches serves every step.
+int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin, uint32_t layer_end, bool with_head) {
     const brasa_config &c = m->cfg;
     enum { SCALE = 0, SWIGLU = 1, RESID = 2 };  // epilogues of brasa_gemv_launch
     float *x = F(m->x);
@@ -223,11 +230,11 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t pos0, uint3
             float *y[3] = {F(m->q), F(m->k_new), F(m->v_new)};
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, y, x, nullptr, F(l.attn_norm), nullptr, nullptr, 0, 1, c.eps, SCALE, nullptr));
         }
-        brasa_attn_shape sh{1, c.heads, c.kv_heads, c.head_dim, pos0, m->limits.kv};
-        KvView dst = kv_at(m, li, pos0), all = kv_at(m, li, 0);
-        brasa_arg qkv[3] = {A(m->q), A(m->k_new), A(m->v_new)}, norms[2] = {A(l.q_norm), A(l.k_norm)}, dsts[2] = {dst.k, dst.v};
-        BRASA_TRY(brasa_k_qk_norm_rope_store(cmd, m->limits.kv, qkv, norms, c.eps, A(m->rope_cos), A(m->rope_sin), c.head_dim, m->limits.ctx, dsts, sh));
-        BRASA_TRY(brasa_k_decode_attention(cmd, A(m->q), all.k, all.v, A(m->partials), m->partials_len, A(m->attn), sh));
+        KvView all = kv_at(m, li, 0);
+        uint32_t *st = (uint32_t *)m->dev_state->ptr;
+        BRASA_TRY(brasa_attn_decode_fused_launch(cmd, m->limits.kv, F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos),
+                                                 F(m->rope_sin), arg_ptr(all.k), arg_ptr(all.v), F(m->partials), st + 4, F(m->attn), st,
+                                                 c.heads, c.kv_heads, m->limits.ctx, c.eps));
         {
             float *y[1] = {x};
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
@@ -257,12 +264,46 @@ int32_t check_tokens(brasa_model *m, uint32_t tokens, uint32_t pos0) {
     return BRASA_OK;
 }
 
+// One full decode step for the token in ws.ids[0] at position pos0: embed, layers, lm_head, argmax into
+// next_id, then "advance" (next_id -> ids[0] and the output list, position + 1). The first call runs the
+// kernels directly and records them; later calls replay the CUDA graph.
+int32_t decode_step_kernels(brasa_model *m, brasa_cmd *cmd) {
+    uint32_t *st = (uint32_t *)m->dev_state->ptr;
+    BRASA_TRY(brasa_k_embed(cmd, m->embed.q, A(m->ids), A(m->x), 1));
+    BRASA_TRY(encode_decode_token(m, cmd, 0, m->cfg.layers, true));
+    BRASA_TRY(brasa_argmax_launch(cmd, F(m->logits), m->cfg.vocab, (uint32_t *)m->next_id->ptr));
+    return brasa_advance_launch(cmd, (uint32_t *)m->ids->ptr, (const uint32_t *)m->next_id->ptr, (uint32_t *)m->out_ids->ptr, st + 1,
+                                m->limits.ctx, st);
+}
+
+int32_t set_position(brasa_model *m, uint32_t pos0) {
+    return brasa_check_cuda(m->ctx, cudaMemcpyAsync(m->dev_state->ptr, &pos0, 4, cudaMemcpyHostToDevice, m->ctx->stream), "position upload");
+}
+
+// pos0 == UINT32_MAX keeps the position the device already holds (device-resident loop).
+int32_t decode_step(brasa_model *m, brasa_cmd *cmd, uint32_t pos0) {
+    if (pos0 != UINT32_MAX) BRASA_TRY(set_position(m, pos0));
+    if (m->decode_graph) return brasa_graph_launch(cmd, m->decode_graph);
+    BRASA_TRY(decode_step_kernels(m, cmd));
+    if (m->ctx->graphs && !m->ctx->capturing) {
+        // everything lazily created (scratch, function attributes) exists now: record the same sequence
+        BRASA_TRY(brasa_graph_capture_begin(m->ctx));
+        int32_t rc = decode_step_kernels(m, cmd);
+        brasa_graph *g = nullptr;
+        int32_t rc2 = brasa_graph_capture_end(m->ctx, &g);
+        BRASA_TRY(rc);
+        BRASA_TRY(rc2);
+        m->decode_graph = g;
+    }
+    return BRASA_OK;
+}
+
 // Enqueues a whole forward for ids already in ws.ids; logits of the last logit_rows positions end
 // up in ws.logits.
 int32_t encode_forward(brasa_model *m, brasa_cmd *cmd, uint32_t tokens, uint32_t pos0, uint32_t logit_rows) {
     const brasa_config &c = m->cfg;
+    if (tokens == 1 && decode_fused_ok(m)) return decode_step(m, cmd, pos0);
     BRASA_TRY(brasa_k_embed(cmd, m->embed.q, A(m->ids), A(m->x), tokens));
-    if (tokens == 1 && decode_fused_ok(m)) return encode_decode_token(m, cmd, pos0, 0, c.layers, true);
     for (uint32_t li = 0; li < c.layers; ++li) BRASA_TRY(encode_layer_prefill(m, cmd, li, tokens, pos0));
     uint32_t first = tokens - logit_rows;
     BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x, (uint64_t)first * c.hidden * 4), A(m->final_norm), A(m->norm_out), logit_rows, c.hidden, c.eps));
@@ -295,6 +336,7 @@ int32_t brasa_model_shape_from_file(const char *path, brasa_model_shape *shape, 
 
 void brasa_model_free(brasa_model *m) {
     if (!m) return;
+    if (m->decode_graph) brasa_graph_free(m->decode_graph);
     for (brasa_buf *b : m->owned) brasa_buf_free(b);
     if (m->pinned_id) cudaFreeHost(m->pinned_id);
     delete m;
@@ -382,6 +424,7 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         BRASA_TRY(alloc_buf(m, (uint64_t)limits.max_logit_rows * c.vocab * 4, &m->logits, ws));
         BRASA_TRY(alloc_buf(m, 64, &m->next_id, nullptr));
         BRASA_TRY(alloc_buf(m, (uint64_t)limits.ctx * 4, &m->out_ids, nullptr));
+        BRASA_TRY(alloc_buf(m, 256, &m->dev_state, nullptr));
         BRASA_CUDA(ctx, cudaHostAlloc((void **)&m->pinned_id, 64, cudaHostAllocDefault));
         return brasa_ctx_sync(ctx);
     }();
@@ -445,7 +488,10 @@ int32_t brasa_model_run_layers(brasa_model *m, float *x, uint32_t tokens, uint32
     brasa_cmd *cmd;
     BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
     int32_t rc = BRASA_OK;
-    if (tokens == 1 && decode_fused_ok(m)) rc = encode_decode_token(m, cmd, pos0, layer_begin, layer_end, false);
+    if (tokens == 1 && decode_fused_ok(m)) {
+        rc = set_position(m, pos0);
+        if (rc == BRASA_OK) rc = encode_decode_token(m, cmd, layer_begin, layer_end, false);
+    }
     else
         for (uint32_t li = layer_begin; li < layer_end && rc == BRASA_OK; ++li) rc = encode_layer_prefill(m, cmd, li, tokens, pos0);
     int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
@@ -459,17 +505,14 @@ int32_t brasa_model_decode_greedy(brasa_model *m, uint32_t first, uint32_t pos0,
     brasa_ctx *ctx = m->ctx;
     BRASA_REQUIRE(ctx, steps >= 1 && (uint64_t)pos0 + steps <= m->limits.ctx, "decode range outside the context");
     BRASA_REQUIRE(ctx, first < m->cfg.vocab, "token id %u outside the vocabulary", first);
+    BRASA_REQUIRE(ctx, decode_fused_ok(m), "the device-resident loop needs tiled q4_0 layers");
     BRASA_TRY(brasa_buf_upload(m->ids, 0, &first, 4));
+    uint32_t st[2] = {pos0, 0};  // position, output count
+    BRASA_TRY(brasa_buf_upload(m->dev_state, 0, st, 8));
     brasa_cmd *cmd;
     BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
     int32_t rc = BRASA_OK;
-    for (uint32_t s = 0; s < steps && rc == BRASA_OK; ++s) {
-        rc = encode_forward(m, cmd, 1, pos0 + s, 1);
-        if (rc == BRASA_OK) rc = brasa_argmax_launch(cmd, F(m->logits), m->cfg.vocab, (uint32_t *)m->ids->ptr);
-        if (rc == BRASA_OK)
-            rc = brasa_check_cuda(ctx, cudaMemcpyAsync((uint32_t *)m->out_ids->ptr + s, m->ids->ptr, 4, cudaMemcpyDeviceToDevice, ctx->stream),
-                                  "copy of the chosen token");
-    }
+    for (uint32_t s = 0; s < steps && rc == BRASA_OK; ++s) rc = decode_step(m, cmd, UINT32_MAX);
     int32_t rc2 = brasa_cmd_wait(cmd, gpu_seconds);
     BRASA_TRY(rc);
     BRASA_TRY(rc2);
@@ -578,9 +621,13 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
     double ttft_ms = 0.0;
     int32_t stop = 1;  // MaxTokens
     auto t1 = clk::now();
+    // Greedy with the fused decode path: the device keeps the position and feeds the chosen token back
+    // itself; per token the host launches one graph and reads one id (pinned memory), nothing else.
+    const bool resident = device_pick && decode_fused_ok(m);
+    bool primed = false;  // device position and input token are set up
     while (generated < max_new) {
         uint32_t next;
-        if (device_pick) {
+        if (device_pick && !(resident && primed)) {
             brasa_cmd *cmd;
             BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
             int32_t rc = brasa_argmax_launch(cmd, (const float *)m->logits->ptr, m->cfg.vocab, (uint32_t *)m->next_id->ptr);
@@ -590,6 +637,8 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
             BRASA_TRY(rc);
             BRASA_TRY(rc2);
             next = *m->pinned_id;
+        } else if (device_pick) {
+            next = *m->pinned_id;  // read back by the previous step
         } else {
             if (s->ignore_stop)
                 for (uint32_t id : s->stop_ids)
@@ -611,9 +660,23 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
             stop = 2;
             break;
         }
-        BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, device_pick ? nullptr : s->logits.data(), nullptr));
+        if (resident) {
+            if (!primed) {
+                uint32_t st[2] = {(uint32_t)s->cached.size(), 0};
+                BRASA_CUDA(ctx, cudaMemcpyAsync(m->ids->ptr, &next, 4, cudaMemcpyHostToDevice, ctx->stream));
+                BRASA_CUDA(ctx, cudaMemcpyAsync(m->dev_state->ptr, st, 8, cudaMemcpyHostToDevice, ctx->stream));
+                primed = true;
+            }
+            brasa_cmd step{ctx, nullptr, nullptr, false};
+            BRASA_TRY(decode_step(m, &step, UINT32_MAX));
+            BRASA_CUDA(ctx, cudaMemcpyAsync(m->pinned_id, m->next_id->ptr, 4, cudaMemcpyDeviceToHost, ctx->stream));
+            BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        } else {
+            BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, device_pick ? nullptr : s->logits.data(), nullptr));
+        }
         s->cached.push_back(next);
     }
+    BRASA_TRY(brasa_ctx_sync(ctx));  // surfaces a device-side wait that gave up during the loop
     if (stats) {
         stats->prompt_tokens = prompt_len;
         stats->reused_tokens = common;

@@ -60,7 +60,24 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *v, uint32_t n,
     }
 }
 
+// End of a decode step: the chosen token becomes the next input, is appended to the output list, and
+// the position advances. One thread.
+__global__ void advance_kernel(uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap, uint32_t *pos) {
+    uint32_t tok = *next;
+    ids[0] = tok;
+    uint32_t n = *out_count;
+    if (n < out_cap) out_ids[n] = tok;
+    *out_count = n + 1;
+    *pos += 1;
+}
+
 }  // namespace
+
+int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
+                             uint32_t *pos) {
+    advance_kernel<<<1, 1, 0, cmd->ctx->stream>>>(ids, next, out_ids, out_count, out_cap, pos);
+    return brasa_post_launch(cmd, "advance");
+}
 
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out) {
     brasa_ctx *ctx = cmd->ctx;
