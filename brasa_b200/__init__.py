@@ -486,6 +486,11 @@ class Kernels:
         self._k(self.L.brasa_k_decode_attention_lanes(cmd._h, _arg(q), _arg(k), _arg(v), _arg(partials), C.c_uint64(partials.nbytes // 4),
                                                       _arg(o), shape._c()))
 
+    def decode_attention_static(self, cmd, q, k, v, o, shape: AttnShape):
+        """decode_attention without a scratch argument, for callers that cannot allocate device memory: the
+        chunk partials go to a fixed array inside the library (at most 64 query heads and 8192 keys)."""
+        self._k(self.L.brasa_k_decode_attention_static(cmd._h, _arg(q), _arg(k), _arg(v), _arg(o), shape._c()))
+
     def flash_attention(self, cmd, q, k, v, o, shape: AttnShape):
         self._k(self.L.brasa_k_flash_attention(cmd._h, _arg(q), _arg(k), _arg(v), _arg(o), shape._c()))
 

@@ -120,6 +120,12 @@ __global__ void __launch_bounds__(128) decode_reduce_kernel(const float *partial
     o[(size_t)h * D + t] = acc / L;
 }
 
+// Scratch for brasa_k_decode_attention_static: the chunk partials live in this array instead of a
+// caller-provided buffer. Sized for 64 query heads and 8192 keys (64 chunks of 128): 64 * 64 * 130 floats.
+constexpr uint32_t STATIC_MAX_HQ = 64, STATIC_MAX_KEYS = 8192;
+constexpr size_t STATIC_PARTIAL_FLOATS = (size_t)STATIC_MAX_HQ * (STATIC_MAX_KEYS / 128) * 130;
+static __device__ __align__(256) float g_decode_partials[STATIC_PARTIAL_FLOATS];
+
 // Causal prefill attention, f32 arithmetic throughout. One block = 64 queries of one query head;
 // keys in tiles of 32. HALF_IO: Q*scale is rounded to f16 and the output is written as f16, like the
 // reference's PrefillPrecision::F16 (flash_attention.metal:213,320); otherwise Q stays f32, the
@@ -599,4 +605,55 @@ int32_t brasa_k_flash_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_
     return brasa_k_flash_attention_with(cmd, q, k, v, o_f16, shape, BRASA_PREFILL_F16);
 }
 
+int32_t brasa_k_decode_attention_static(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o, brasa_attn_shape shape) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, shape.hq <= STATIC_MAX_HQ && (uint64_t)shape.pos0 + 1 <= STATIC_MAX_KEYS,
+                  "decode_attention_static holds scratch for at most %u query heads and %u keys (got %u heads, %llu keys); use "
+                  "brasa_k_decode_attention with a caller-allocated scratch buffer for larger shapes",
+                  STATIC_MAX_HQ, STATIC_MAX_KEYS, shape.hq, (unsigned long long)shape.pos0 + 1);
+    // In host code the array's name stands for the symbol, not for device memory: each device has its own
+    // copy, whose address is looked up once per device with that device current.
+    static float *scratch_of_device[64] = {};
+    BRASA_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "device index %d out of range", ctx->device);
+    if (!scratch_of_device[ctx->device]) {
+        BRASA_CUDA(ctx, cudaSetDevice(ctx->device));
+        float *ptr = nullptr;
+        BRASA_CUDA(ctx, cudaGetSymbolAddress((void **)&ptr, g_decode_partials));
+        scratch_of_device[ctx->device] = ptr;
+    }
+    float *partials = scratch_of_device[ctx->device];
+    // same checks and launches as brasa_k_decode_attention, minus the scratch argument
+    BRASA_REQUIRE(ctx, shape.tokens == 1, "decode_attention is for one token");
+    BRASA_REQUIRE(ctx, shape.dim == 128, "decode_attention needs head_dim 128");
+    BRASA_REQUIRE(ctx, shape.hkv > 0 && shape.hq % shape.hkv == 0 && shape.hq / shape.hkv <= 8, "decode_attention: GQA group must divide and be <= 8");
+    BRASA_REQUIRE(ctx, shape.kv >= BRASA_KV_F32 && shape.kv <= BRASA_KV_Q8_0, "unknown KV type %d", shape.kv);
+    const uint32_t lk = shape.pos0 + 1, chunks = (lk + 127) / 128;
+    const uint64_t kvb = brasa_kv_bytes(shape.kv, (uint64_t)lk * shape.hkv * 128);
+    BRASA_REQUIRE(ctx, arg_fits(q, (uint64_t)shape.hq * 512) && arg_fits(o, (uint64_t)shape.hq * 512) && arg_fits(k, kvb) && arg_fits(v, kvb),
+                  "decode_attention_static: q, o or cache too small");
+    BRASA_REQUIRE(ctx, shape.kv == BRASA_KV_Q8_0 || (k.offset % 16 == 0 && v.offset % 16 == 0), "decode_attention_static: misaligned cache");
+    const float scale = 1.0f / sqrtf((float)shape.dim);
+    const size_t smem = (128 * TS + 8 * D + 8 * 128 + 16) * sizeof(float);
+    dim3 grid(chunks, shape.hkv);
+    const float *qp = (const float *)arg_ptr(q);
+#define LAUNCH_STATIC(KVT)                                                                                                 \
+    do {                                                                                                                   \
+        static bool done = false;                                                                                          \
+        if (!done) {                                                                                                       \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            done = true;                                                                                                   \
+        }                                                                                                                  \
+        decode_partial_kernel<KVT><<<grid, 128, smem, ctx->stream>>>(qp, arg_ptr(k), arg_ptr(v), partials, shape.hq, shape.hkv, lk, scale); \
+    } while (0)
+    if (shape.kv == BRASA_KV_F32) LAUNCH_STATIC(BRASA_KV_F32);
+    else if (shape.kv == BRASA_KV_F16) LAUNCH_STATIC(BRASA_KV_F16);
+    else LAUNCH_STATIC(BRASA_KV_Q8_0);
+#undef LAUNCH_STATIC
+    BRASA_TRY(brasa_post_launch(cmd, "decode_partial"));
+    decode_reduce_kernel<<<shape.hq, 128, 0, ctx->stream>>>(partials, (float *)arg_ptr(o), chunks);
+    return brasa_post_launch(cmd, "decode_reduce");
+}
+
 }  // extern "C"
+

@@ -171,6 +171,20 @@ int32_t brasa_k_store_kv(brasa_cmd *cmd, int32_t kv, brasa_arg src, brasa_arg ds
 /* one query token at pos0 against keys 0..pos0; partials >= brasa_decode_partials_len floats :1056,:1110 */
 int32_t brasa_k_decode_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o, brasa_attn_shape shape);
 int32_t brasa_k_decode_attention_lanes(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg partials, uint64_t partials_len, brasa_arg o, brasa_attn_shape shape);
+/* Decode attention for callers that cannot allocate device memory. It has no counterpart in the reference,
+ * whose caller always hands the kernel a preallocated `partials` buffer (crates/models/src/qwen3.rs:400).
+ * Who needs it: code running where cudaMalloc is forbidden or unaffordable, such as a host thread that is
+ * inside a stream capture, a plugin that was given a fixed memory budget by its host process, or a
+ * latency-critical loop that must never enter the allocator. Same arithmetic and same result as
+ * brasa_k_decode_attention; the per-chunk partial results go to an array that is part of the library image
+ * instead (2.1 MB, present on every GPU that loads the library until the process exits).
+ * Limits: at most 64 query heads and 8192 keys (pos0 + 1 <= 8192); larger shapes are refused with
+ * BRASA_EINVAL and a message that names the limit. The first call on each device looks up the array's
+ * device address (a CUDA runtime query, no allocation); make that first call before any stream capture
+ * begins. Every call uses the same array and nothing in it has to be cleared, since each call overwrites
+ * what it later reads; for the same reason two calls must not overlap on the GPU (two streams or two
+ * contexts of one process): they would read each other's partials. */
+int32_t brasa_k_decode_attention_static(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o, brasa_attn_shape shape);
 /* causal GQA attention for a chunk; precision F16: Q*scale rounded to f16, o in f16 :1185 */
 int32_t brasa_k_flash_attention_with(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o, brasa_attn_shape shape, int32_t precision);
 int32_t brasa_k_flash_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg o_f16, brasa_attn_shape shape); /* :1169 */
