@@ -452,15 +452,32 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedAttnParams 
     if (!last_block) return;
     __threadfence();
     if (t == 0) p.counters[kh] = 0;
+    // merge: weights of all (head, chunk) pairs first (one round trip), then the accumulators with all
+    // loads of a head in flight at once
+    for (uint32_t i = t; i < G * nchunks; i += 128) {
+        uint32_t g = i / nchunks, c = i % nchunks;
+        const float *pp = p.partials + ((size_t)(kh * G + g) * max_chunks + c) * 130;
+        ps[g * 128 + c] = __ldcg(pp);            // m
+        ps[g * 128 + 64 + c] = __ldcg(pp + 1);   // l
+    }
+    __syncthreads();
     for (uint32_t g = 0; g < G; ++g) {
-        const float *pp = p.partials + (size_t)(kh * G + g) * max_chunks * 130;
+        const float *pp = p.partials + (size_t)(kh * G + g) * max_chunks * 130 + 2 + t;
         float M = -INFINITY;
-        for (uint32_t c = 0; c < nchunks; ++c) M = fmaxf(M, __ldcg(pp + c * 130));
+        for (uint32_t c = 0; c < nchunks; ++c) M = fmaxf(M, ps[g * 128 + c]);
         float L = 0.0f, a = 0.0f;
-        for (uint32_t c = 0; c < nchunks; ++c) {
-            float w = expf(__ldcg(pp + c * 130) - M);
-            L = fmaf(__ldcg(pp + c * 130 + 1), w, L);
-            a = fmaf(__ldcg(pp + c * 130 + 2 + t), w, a);
+        for (uint32_t c0 = 0; c0 < nchunks; c0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = c0 + j < nchunks ? __ldcg(pp + (size_t)(c0 + j) * 130) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (c0 + j < nchunks) {
+                    float w = expf(ps[g * 128 + c0 + j] - M);
+                    L = fmaf(ps[g * 128 + 64 + c0 + j], w, L);
+                    a = fmaf(v[j], w, a);
+                }
+            }
         }
         p.o[(size_t)(kh * G + g) * 128 + t] = a / L;
     }

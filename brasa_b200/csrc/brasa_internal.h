@@ -26,6 +26,7 @@ struct brasa_ctx {
     uint32_t *status = nullptr;  // device status word: non-zero after a bounded wait gave up
     bool pdl = true;             // programmatic dependent launch between decode kernels
     bool capturing = false;      // a stream capture is open (brasa_graph_capture_begin)
+    unsigned long long *gemv_trace = nullptr;  // device buffer of phase timestamps when BRASA_TRACE=1
     bool graphs = true;          // replay the decode step as a CUDA graph (BRASA_GRAPH=0 turns it off)
     uint64_t launches = 0;       // kernels enqueued on this context (graph replays count their nodes)
     uint64_t capture_launches = 0;

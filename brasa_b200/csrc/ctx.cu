@@ -50,6 +50,8 @@ int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
     cudaMemset(ctx->status, 0, 256);
     const char *env = getenv("BRASA_PDL");
     if (env && env[0] == '0') ctx->pdl = false;
+    env = getenv("BRASA_TRACE");
+    if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 256) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 256);
     env = getenv("BRASA_GRAPH");
     if (env && env[0] == '0') ctx->graphs = false;
     *out = ctx;
@@ -67,6 +69,7 @@ void brasa_ctx_destroy(brasa_ctx *ctx) {
     cudaFree(ctx->gemv_partials);
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->gemv_trace);
     cudaFree(ctx->status);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -87,6 +90,14 @@ int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total
 }
 
 uint64_t brasa_ctx_launch_count(brasa_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]) {
+    if (!ctx || !out) return BRASA_EINVAL;
+    BRASA_REQUIRE(ctx, ctx->gemv_trace, "tracing is off: create the context with BRASA_TRACE=1");
+    BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    BRASA_CUDA(ctx, cudaMemcpy(out, ctx->gemv_trace, 128, cudaMemcpyDeviceToHost));
+    return BRASA_OK;
+}
 
 int32_t brasa_ctx_sync(brasa_ctx *ctx) {
     if (!ctx) return BRASA_EINVAL;
@@ -316,6 +327,7 @@ int32_t brasa_gemv_scratch(brasa_ctx *ctx, size_t partial_floats, size_t counter
         BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->gemv_trace);
         ctx->gemv_counters = nullptr;
         ctx->gemv_counters_n = 0;
         BRASA_CUDA(ctx, cudaMalloc(&ctx->gemv_counters, counters * sizeof(uint32_t)));

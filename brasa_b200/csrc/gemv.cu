@@ -28,8 +28,7 @@
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait rounds before a wait gives up
-constexpr int MAX_WARPS = 10;              // consumer warps per block (a multiple of the slice count)
-constexpr int PRODUCER_LANES = 1;
+constexpr int GEMV_WARPS = 8;               // consumer warps per block; column slices per row divide it
 
 enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2 };
 
@@ -38,10 +37,11 @@ struct GemvParams {
     float *y[3];
     uint32_t rows[3];
     uint32_t nmat;
+    uint32_t total_rows;   // logical rows the grid shares out (SwiGLU: the rows of gate)
     uint32_t cols;
     uint32_t slices;       // column slices per row (S); consumer warps are a multiple of it
     uint32_t warps;        // consumer warps
-    uint32_t rows_per_slot;  // 2 * warps / slices
+    uint32_t rows_per_slot;  // rows of one ring slot: the rows half of the warps take per iteration
     uint32_t nslot;        // ring slots in shared memory
     uint32_t max_items;    // partial sums kept in shared memory per block
     int epilogue;
@@ -54,8 +54,15 @@ struct GemvParams {
     int scaled;            // multiply outputs by 1/sqrt(mean(x^2) + eps)
     float eps;
     uint32_t *status;
+    unsigned long long *trace;  // optional: block 0 records the time of each phase (debugging aid)
 };
 
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(i) do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[i] = gtime(); } while (0)
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -139,33 +146,78 @@ __device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const X
     return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
 }
 
-// N = half blocks per lane and slice (the lane's x registers hold 16 N values).
+// Dot products of NV (1..4) rows of a slot with the lane's share of x; the NV row sums end up in lanes
+// 0, 8, 16, 24 after folding across lanes.
+template <int QT, int N, int NV>
+__device__ __forceinline__ float rows_dot(const uint8_t *row0, uint32_t row_bytes, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
+                                          uint32_t hi_off, uint32_t sc_off, int lane) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // straight-line code: lanes past the end of the row read the last half block and have step 0
+#pragma unroll
+    for (int it = 0; it < N; ++it) {
+        const uint32_t hbi = min((slice * N + it) * 32 + lane, nhb - 1);
+#pragma unroll
+        for (int r = 0; r < NV; ++r) {
+            const uint8_t *row = row0 + (size_t)r * row_bytes;
+            uint2 codes = *reinterpret_cast<const uint2 *>(row + hbi * 8);
+            uint32_t hb = 0;
+            if (QT == BRASA_Q6_0) hb = *reinterpret_cast<const uint32_t *>(row + hi_off + hbi * 4);
+            float d = __half2float(*reinterpret_cast<const __half *>(row + sc_off + (hbi >> 1) * 2));
+            int sum = half_block_idot<QT>(codes, hb, xr[it]);
+            acc[r] = fmaf(d * xr[it].step, (float)sum, acc[r]);
+        }
+    }
+    // fold the row sums across lane bits 4 and 3, then reduce over bits 2..0: lanes 0, 8, 16, 24 get rows 0, 1, 2, 3
+    const bool hi4 = lane & 16, hi3 = lane & 8;
+    float z;
+    if (NV > 2) {
+        float a = hi4 ? acc[2] : acc[0], a_send = hi4 ? acc[0] : acc[2];
+        float c = hi4 ? acc[3] : acc[1], c_send = hi4 ? acc[1] : acc[3];
+        a += __shfl_xor_sync(0xffffffffu, a_send, 16);
+        c += __shfl_xor_sync(0xffffffffu, c_send, 16);
+        z = hi3 ? c : a;
+        float z_send = hi3 ? a : c;
+        z += __shfl_xor_sync(0xffffffffu, z_send, 8);
+    } else {
+        float a = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 16);
+        float c = NV > 1 ? acc[1] + __shfl_xor_sync(0xffffffffu, acc[1], 16) : 0.0f;
+        z = hi3 ? c : a;
+        float z_send = hi3 ? a : c;
+        z += __shfl_xor_sync(0xffffffffu, z_send, 8);
+    }
+    z += __shfl_xor_sync(0xffffffffu, z, 4);
+    z += __shfl_xor_sync(0xffffffffu, z, 2);
+    z += __shfl_xor_sync(0xffffffffu, z, 1);
+    return z;
+}
+
+// N = half blocks per lane and slice (the lane's x registers hold 14 N words).
+constexpr int R = 4;         // rows a warp works on at a time
+constexpr int MAX_CONV = 3;  // half blocks of x a thread converts with all its loads in flight
+
 template <int QT, int N>
-__global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(GemvParams p) {
+__global__ void __maxnreg__(112) gemv_rows_kernel(GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t row_bytes = tiled_row_bytes(QT, p.cols);
     const uint32_t slot_bytes = p.rows_per_slot * row_bytes;
-    // layout: ring [nslot][slot_bytes] | xs [cols] | nws [cols] (norm weight, when given) | xf [14][cols/16] | part [max_items]
-    //         | full, empty [nslot] | xbar, wbar | red
+    const uint32_t nhb = p.cols / 16;
+    // layout: ring [nslot][slot_bytes] | xf [nhb] records of 16 words | part [max_items] | full, empty [nslot] | red
     uint8_t *ring = smem;
-    float *xs = reinterpret_cast<float *>(smem + (size_t)p.nslot * slot_bytes);
-    float *nws = xs + p.cols;
-    uint32_t *xf = reinterpret_cast<uint32_t *>(nws + (p.normw ? p.cols : 0));  // fixed-point x: [14][cols / 16] words
-    float *part = reinterpret_cast<float *>(xf + 14 * (p.cols / 16));
+    uint4 *xf = reinterpret_cast<uint4 *>(smem + (size_t)p.nslot * slot_bytes);
+    float *part = reinterpret_cast<float *>(xf + 4 * nhb);
     uint64_t *full = reinterpret_cast<uint64_t *>(part + ((p.max_items + 1) & ~1u));
     uint64_t *empty = full + p.nslot;
-    uint64_t *xbar = empty + p.nslot, *wbar = xbar + 1;
-    float *red = reinterpret_cast<float *>(wbar + 1);
+    float *red = reinterpret_cast<float *>(empty + p.nslot);
 
+    TRACE(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t W = p.warps, S = p.slices, RPS = p.rows_per_slot;
+    const uint32_t Wp = W / S;                                     // warps side by side on different rows
+    const uint32_t split = (Wp & 1) ? 1u : 2u;                     // slots consumed per iteration of the block
     const uint32_t G = gridDim.x, b = blockIdx.x;
     // logical rows: matrices one after another (SwiGLU: the rows of gate; up follows the same range)
     const uint32_t nseg = p.epilogue == EPI_SWIGLU ? 2 : p.nmat;
-    uint32_t total_rows = 0;
-    for (uint32_t i = 0; i < (p.epilogue == EPI_SWIGLU ? 1u : p.nmat); ++i) total_rows += p.rows[i];
-    const uint32_t r0 = (uint32_t)((uint64_t)total_rows * b / G), r1 = (uint32_t)((uint64_t)total_rows * (b + 1) / G);
-    // per segment: first row inside its matrix and row count
+    const uint32_t r0 = p.total_rows * b / G, r1 = p.total_rows * (b + 1) / G;
     // per segment: first row inside its matrix, row count, first slot, rows of the segments before it.
     // Only constant indices below, so the arrays stay in registers.
     uint32_t seg_first[3] = {0, 0, 0}, seg_rows[3] = {0, 0, 0}, seg_slot0[3] = {0, 0, 0}, seg_before[3] = {0, 0, 0};
@@ -195,38 +247,27 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nslot; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], W);
+            mbar_init(&empty[s], W / split);
         }
-        mbar_init(xbar, 1);
-        mbar_init(wbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    auto issue = [&](uint32_t k) {  // slot k of this block -> ring[k % nslot]
-        const uint32_t i = seg_of(k);
-        uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
-        const uint8_t *src = p.w[i] + (size_t)(SEG_PICK(seg_first, i) + first) * row_bytes;
-        uint32_t s = k % p.nslot;
-        mbar_expect_tx(&full[s], n * row_bytes);
-        bulk_g2s(ring + (size_t)s * slot_bytes, src, n * row_bytes, &full[s]);
-    };
-
-    if (warp == (int)W) {  // producer warp: lanes 0..3 issue alternating slots
-        if (lane < PRODUCER_LANES) {
+    if (warp == (int)W) {  // producer warp: one lane streams this block's rows, slot after slot
+        if (lane == 0) {
+            auto issue = [&](uint32_t k) {  // slot k of this block -> ring[k % nslot]
+                const uint32_t i = seg_of(k);
+                uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
+                const uint8_t *src = p.w[i] + (size_t)(SEG_PICK(seg_first, i) + first) * row_bytes;
+                uint32_t s = k % p.nslot;
+                mbar_expect_tx(&full[s], n * row_bytes);
+                bulk_g2s(ring + (size_t)s * slot_bytes, src, n * row_bytes, &full[s]);
+            };
             // weights are immutable: the first ring-full of copies starts before the input is ready
-            uint32_t k = lane;
-            if (lane == 0 && p.normw) {  // the norm weight is a weight too
-                mbar_expect_tx(wbar, p.cols * 4);
-                bulk_g2s(nws, p.normw, p.cols * 4, wbar);
-            }
-            for (; k < total_slots && k < p.nslot; k += PRODUCER_LANES) issue(k);
+            uint32_t k = 0;
+            for (; k < total_slots && k < p.nslot; ++k) issue(k);
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (lane == 0 && !p.h) {  // the input vector: one bulk copy once the previous kernel is done
-                mbar_expect_tx(xbar, p.cols * 4);
-                bulk_g2s(xs, p.x, p.cols * 4, xbar);
-            }
-            for (; k < total_slots; k += PRODUCER_LANES) {
+            for (; k < total_slots; ++k) {
                 if (!mbar_wait(&empty[k % p.nslot], (k / p.nslot - 1) & 1)) {
                     atomicExch(p.status, 1u);
                     break;
@@ -236,61 +277,27 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
         }
         return;
     }
+
+    // ---- before the input exists: the norm weights of the half blocks this thread will convert ----
+    const uint32_t CT = W * 32;
+    float4 nw0[4];  // of this thread's first half block; wider inputs fetch the rest later
+    if (p.normw && threadIdx.x < nhb) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(p.normw + (threadIdx.x >> 1) * 32 + 8 * (threadIdx.x & 1));
+        nw0[0] = w4[0]; nw0[1] = w4[4]; nw0[2] = w4[1]; nw0[3] = w4[5];
+    }
     // Everything below depends on the previous kernel's output. Once that kernel is complete the next one
     // of the stream may start its own weight prefetch: at most two kernels of the chain overlap, so a
     // kernel's early reads (weights, older KV rows) never race with a producer further back.
+    TRACE(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    TRACE(2);
 
-    // ---- x in shared memory (bulk copy; with h: x + h through registers), sum of squares ----
-    const uint32_t CT = W * 32;
-    bool ok_in = true;
-    if (p.h) {
-        for (uint32_t j = threadIdx.x; j < p.cols; j += CT) {
-            float v = p.x[j] + p.h[j];
-            if (p.x_out && b == 0) p.x_out[j] = v;
-            xs[j] = v;
-        }
-        asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
-    } else {
-        ok_in = mbar_wait(xbar, 0);
-    }
-    if (p.normw) ok_in = mbar_wait(wbar, 0) && ok_in;
-    if (!ok_in && lane == 0) atomicExch(p.status, 3u);
-    float scale = 1.0f;
-    if (p.scaled) {
-        float tot = 0.0f;
-        if (p.ss) {  // reference form: fixed-order sum of add_norm_prep's partials
-            for (uint32_t i = 0; i < p.nss; ++i) tot += p.ss[i];
-        } else {
-            float ssq = 0.0f;
-            for (uint32_t j = threadIdx.x; j < p.cols; j += CT) ssq = fmaf(xs[j], xs[j], ssq);
-            for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-            if (lane == 0) red[warp] = ssq;
-            asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
-            for (uint32_t i = 0; i < W; ++i) tot += red[i];
-        }
-        scale = 1.0f / sqrtf(tot / (float)p.cols + p.eps);
-    }
-
-    // ---- x to fixed point, once per block: thread t converts half block t (t + CT, ...) into shared memory ----
-    const uint32_t slice = warp % S, row_in_slot = warp / S;
-    const uint32_t nhb = p.cols / 16;
-    for (uint32_t hbi = threadIdx.x; hbi < nhb; hbi += CT) {
-        const uint32_t blk = hbi >> 1, half = hbi & 1;
-        float v[4][4];  // quad j: values that meet low/high nibbles of word x (j = 0, 1) and word y (j = 2, 3)
-#pragma unroll
-        for (int ww = 0; ww < 2; ++ww) {
-            const uint32_t e0 = blk * 32 + 8 * half + 4 * ww;
-            float4 lo = *reinterpret_cast<const float4 *>(xs + e0), hi = *reinterpret_cast<const float4 *>(xs + e0 + 16);
-            if (p.normw) {
-                float4 wl = *reinterpret_cast<const float4 *>(nws + e0), wh = *reinterpret_cast<const float4 *>(nws + e0 + 16);
-                lo.x *= wl.x; lo.y *= wl.y; lo.z *= wl.z; lo.w *= wl.w;
-                hi.x *= wh.x; hi.y *= wh.y; hi.z *= wh.z; hi.w *= wh.w;
-            }
-            v[2 * ww][0] = lo.x; v[2 * ww][1] = lo.y; v[2 * ww][2] = lo.z; v[2 * ww][3] = lo.w;
-            v[2 * ww + 1][0] = hi.x; v[2 * ww + 1][1] = hi.y; v[2 * ww + 1][2] = hi.z; v[2 * ww + 1][3] = hi.w;
-        }
+    // ---- x to 22-bit fixed point, once per block: thread t converts half blocks t, t + CT, ... into records ----
+    // quad j of a half block: the values that meet the low / high nibbles of code word 0 (j = 0, 1) and 1 (j = 2, 3)
+    float ssq = 0.0f;
+    auto convert = [&](uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) {
+        float v[4][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}, {q2.x, q2.y, q2.z, q2.w}, {q3.x, q3.y, q3.z, q3.w}};
         float amax = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -303,6 +310,7 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
         float step = live ? __uint_as_float(ebits - (20u << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
         float inv = live ? __uint_as_float((254u << 23) - (ebits - (20u << 23))) : 0.0f;  // 1 / step, exact
         int total = 0;
+        uint32_t rec[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int X[4];
@@ -312,80 +320,154 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
                 total += X[e];
             }
             // byte planes of the four integers: byte k of every X gathered into one word
-            uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);  // b0 b0' b1 b1'
-            uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);  // b2 b2' b3 b3'
-            xf[(3 * j + 0) * nhb + hbi] = __byte_perm(lo01, lo23, 0x5410);
-            xf[(3 * j + 1) * nhb + hbi] = __byte_perm(lo01, lo23, 0x7632);
-            xf[(3 * j + 2) * nhb + hbi] = __byte_perm(hi01, hi23, 0x5410);
+            uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);
+            uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
+            rec[3 * j + 0] = __byte_perm(lo01, lo23, 0x5410);
+            rec[3 * j + 1] = __byte_perm(lo01, lo23, 0x7632);
+            rec[3 * j + 2] = __byte_perm(hi01, hi23, 0x5410);
         }
-        xf[12 * nhb + hbi] = (uint32_t)total;
-        xf[13 * nhb + hbi] = __float_as_uint(step);
+        rec[12] = (uint32_t)total;
+        rec[13] = __float_as_uint(step);
+        rec[14] = rec[15] = 0;
+        // 16-byte chunk c of record h is stored at chunk c ^ ((h >> 1) & 3): conflict-free for consecutive h
+        const uint32_t sw = (hbi >> 1) & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) xf[hbi * 4 + (c ^ sw)] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
+    };
+    {
+        float4 xq[MAX_CONV][4];
+#pragma unroll
+        for (int c = 0; c < MAX_CONV; ++c) {
+            const uint32_t hbi = threadIdx.x + c * CT;
+            if (hbi < nhb) {
+                const uint32_t e0 = (hbi >> 1) * 32 + 8 * (hbi & 1);
+                const float4 *x4 = reinterpret_cast<const float4 *>(p.x + e0);
+                xq[c][0] = x4[0]; xq[c][1] = x4[4]; xq[c][2] = x4[1]; xq[c][3] = x4[5];
+                if (p.h) {
+                    const float4 *h4 = reinterpret_cast<const float4 *>(p.h + e0);
+                    const float4 hv[4] = {h4[0], h4[4], h4[1], h4[5]};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { xq[c][j].x += hv[j].x; xq[c][j].y += hv[j].y; xq[c][j].z += hv[j].z; xq[c][j].w += hv[j].w; }
+                    if (p.x_out && b == 0) {
+                        float4 *o4 = reinterpret_cast<float4 *>(p.x_out + e0);
+                        o4[0] = xq[c][0]; o4[4] = xq[c][1]; o4[1] = xq[c][2]; o4[5] = xq[c][3];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < MAX_CONV; ++c) {
+            const uint32_t hbi = threadIdx.x + c * CT;
+            if (hbi < nhb) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float4 &q = xq[c][j];
+                    ssq = fmaf(q.x, q.x, ssq); ssq = fmaf(q.y, q.y, ssq); ssq = fmaf(q.z, q.z, ssq); ssq = fmaf(q.w, q.w, ssq);
+                    if (p.normw) {
+                        const int off[4] = {0, 16, 4, 20};
+                        float4 wv = c == 0 ? nw0[j] : *reinterpret_cast<const float4 *>(p.normw + (hbi >> 1) * 32 + 8 * (hbi & 1) + off[j]);
+                        q.x *= wv.x; q.y *= wv.y; q.z *= wv.z; q.w *= wv.w;
+                    }
+                }
+                convert(hbi, xq[c][0], xq[c][1], xq[c][2], xq[c][3]);
+            }
+        }
+        // very wide inputs: the rest one at a time
+        for (uint32_t hbi = threadIdx.x + MAX_CONV * CT; hbi < nhb; hbi += CT) {
+            const uint32_t e0 = (hbi >> 1) * 32 + 8 * (hbi & 1);
+            float4 q[4];
+            const int off[4] = {0, 16, 4, 20};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                q[j] = *reinterpret_cast<const float4 *>(p.x + e0 + off[j]);
+                if (p.h) {
+                    float4 hv = *reinterpret_cast<const float4 *>(p.h + e0 + off[j]);
+                    q[j].x += hv.x; q[j].y += hv.y; q[j].z += hv.z; q[j].w += hv.w;
+                    if (p.x_out && b == 0) *reinterpret_cast<float4 *>(p.x_out + e0 + off[j]) = q[j];
+                }
+                ssq = fmaf(q[j].x, q[j].x, ssq); ssq = fmaf(q[j].y, q[j].y, ssq); ssq = fmaf(q[j].z, q[j].z, ssq); ssq = fmaf(q[j].w, q[j].w, ssq);
+                if (p.normw) {
+                    float4 wv = *reinterpret_cast<const float4 *>(p.normw + e0 + off[j]);
+                    q[j].x *= wv.x; q[j].y *= wv.y; q[j].z *= wv.z; q[j].w *= wv.w;
+                }
+            }
+            convert(hbi, q[0], q[1], q[2], q[3]);
+        }
     }
+    // the residual this thread will add in the epilogue (one output row per thread)
+    float resid = 0.0f;
+    if (p.epilogue == EPI_RESID && threadIdx.x < seg_rows[0]) resid = p.resid[seg_first[0] + threadIdx.x];
+    TRACE(3);
+    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    if (lane == 0) red[warp] = ssq;
     asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+    float scale = 1.0f;
+    if (p.scaled) {
+        float tot = 0.0f;
+        if (p.ss) {  // reference form: fixed-order sum of add_norm_prep's partials
+            for (uint32_t i = 0; i < p.nss; ++i) tot += p.ss[i];
+        } else {
+            for (uint32_t i = 0; i < W; ++i) tot += red[i];
+        }
+        scale = 1.0f / sqrtf(tot / (float)p.cols + p.eps);
+    }
+    TRACE(4);
     // ---- the lane's share: the same half blocks of every row ----
+    const uint32_t slice = warp % S, rw = warp / S;
     XFixed xr[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-        uint32_t hbi = (slice * N + i) * 32 + lane;
-        bool ok = hbi < nhb;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int d = 0; d < 3; ++d) xr[i].d[j][d] = ok ? xf[(3 * j + d) * nhb + hbi] : 0u;
-        xr[i].total = ok ? (int)xf[12 * nhb + hbi] : 0;
-        xr[i].step = ok ? __uint_as_float(xf[13 * nhb + hbi]) : 0.0f;
+        const uint32_t want = (slice * N + i) * 32 + lane;
+        const uint32_t hbi = min(want, nhb - 1), sw = (hbi >> 1) & 3;
+        uint4 c0 = xf[hbi * 4 + (0 ^ sw)], c1 = xf[hbi * 4 + (1 ^ sw)], c2 = xf[hbi * 4 + (2 ^ sw)], c3 = xf[hbi * 4 + (3 ^ sw)];
+        xr[i].d[0][0] = c0.x; xr[i].d[0][1] = c0.y; xr[i].d[0][2] = c0.z; xr[i].d[1][0] = c0.w;
+        xr[i].d[1][1] = c1.x; xr[i].d[1][2] = c1.y; xr[i].d[2][0] = c1.z; xr[i].d[2][1] = c1.w;
+        xr[i].d[2][2] = c2.x; xr[i].d[3][0] = c2.y; xr[i].d[3][1] = c2.z; xr[i].d[3][2] = c2.w;
+        xr[i].total = (int)c3.x;
+        xr[i].step = want < nhb ? __uint_as_float(c3.y) : 0.0f;  // lanes past the end of the row contribute nothing
     }
     const uint32_t hi_off = tiled_hi_off(p.cols), sc_off = tiled_scale_off(QT, p.cols);
+    TRACE(5);
 
-    // ---- consume slots: warp = (row pair in slot, slice); two rows at a time for instruction-level parallelism ----
-    for (uint32_t k = 0; k < total_slots; ++k) {
-        uint32_t s = k % p.nslot;
-        if (!mbar_wait(&full[s], (k / p.nslot) & 1)) {
-            // give up on the remaining slots but still meet the other warps at the barrier below
-            if (lane == 0) atomicExch(p.status, 2u);
-            break;
-        }
-        const uint32_t i = seg_of(k);
-        uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
-        const uint32_t ra = row_in_slot * 2;
-        if (ra < n) {
-            const bool two = ra + 1 < n;
-            const uint8_t *row_a = ring + (size_t)s * slot_bytes + (size_t)ra * row_bytes;
-            const uint8_t *row_b = two ? row_a + row_bytes : row_a;
-            float acc_a = 0.0f, acc_b = 0.0f;
-            // straight-line code: lanes past the end of the row read the last half block and multiply by step 0
+    // ---- consume: per iteration the block covers Wp * R rows of a segment; a warp takes R rows of one slot ----
+    const uint32_t half_w = Wp / split;                     // row-warps per slot
+    const uint32_t my_sub = split == 2 ? rw / half_w : 0;   // which of the iteration's slots
 #pragma unroll
-            for (int it = 0; it < N; ++it) {
-                const uint32_t hbi = min((slice * N + it) * 32 + lane, nhb - 1);
-                uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
-                uint2 cb = *reinterpret_cast<const uint2 *>(row_b + hbi * 8);
-                uint32_t ha = 0, hb = 0;
-                if (QT == BRASA_Q6_0) {
-                    ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
-                    hb = *reinterpret_cast<const uint32_t *>(row_b + hi_off + hbi * 4);
+    for (int sgi = 0; sgi < 3; ++sgi) {
+        const uint32_t nslots_seg = (seg_rows[sgi] + RPS - 1) / RPS;
+        for (uint32_t ks = my_sub; ks < nslots_seg; ks += split) {
+            const uint32_t k = seg_slot0[sgi] + ks, s = k % p.nslot;
+            if (!mbar_wait(&full[s], (k / p.nslot) & 1)) {
+                // give up on the remaining slots but still meet the other warps at the barrier below
+                if (lane == 0) atomicExch(p.status, 2u);
+                break;
+            }
+            if (k == 0) TRACE(6);
+            // the slot's rows are shared out evenly among the warps that consume it (a last, partial slot
+            // gives each warp fewer than R rows instead of leaving most warps idle)
+            const uint32_t n_slot = min(RPS, seg_rows[sgi] - ks * RPS);
+            const uint32_t q = (n_slot + half_w - 1) / half_w, in_slot = (rw % half_w) * q;
+            const uint32_t nv = in_slot < n_slot ? min(q, n_slot - in_slot) : 0u;
+            if (nv > 0) {
+                const uint8_t *row0 = ring + (size_t)s * slot_bytes + (size_t)in_slot * row_bytes;
+                float z;
+                switch (nv) {
+                case 1: z = rows_dot<QT, N, 1>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
+                case 2: z = rows_dot<QT, N, 2>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
+                case 3: z = rows_dot<QT, N, 3>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
+                default: z = rows_dot<QT, N, 4>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
                 }
-                float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
-                float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
-                int sa = half_block_idot<QT>(ca, ha, xr[it]);
-                int sb = half_block_idot<QT>(cb, hb, xr[it]);
-                acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
-                acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
+                // lane 8 r holds row r (for one or two rows: lane 0 holds row 0, lane 8 row 1)
+                const uint32_t r = nv > 2 ? ((lane & 16) ? 2u : 0u) + ((lane & 8) ? 1u : 0u) : ((lane & 8) ? 1u : 0u);
+                const bool holder = nv > 2 ? (lane & 7) == 0 : (lane & 23) == 0;
+                if (holder && r < nv) part[(seg_before[sgi] + ks * RPS + in_slot + r) * S + slice] = z;
             }
-            for (int o = 16; o > 0; o >>= 1) {
-                acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
-                acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
-            }
-            // partial index: rows of all segments in order, slices innermost
-            const uint32_t rows_before = SEG_PICK(seg_before, i);
-            if (lane == 0) {
-                part[(rows_before + first + ra) * S + slice] = acc_a;
-                if (two) part[(rows_before + first + ra + 1) * S + slice] = acc_b;
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+    TRACE(7);
 
     // ---- epilogue: one thread per output row of this block ----
     if (p.epilogue == EPI_SWIGLU) {
@@ -404,11 +486,12 @@ __global__ void __launch_bounds__((MAX_WARPS + 1) * 32, 1) gemv_rows_kernel(Gemv
                 for (uint32_t sl = 0; sl < S; ++sl) v += part[(seg_before[i] + j) * S + sl];
                 uint32_t r = seg_first[i] + j;
                 v *= scale;
-                if (p.epilogue == EPI_RESID) v += p.resid[r];
+                if (p.epilogue == EPI_RESID) v += (i == 0 && j == threadIdx.x) ? resid : p.resid[r];
                 p.y[i][r] = v;
             }
         }
     }
+    TRACE(8);
 #undef SEG_PICK
 }
 
@@ -492,30 +575,36 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     p.x = x; p.h = h; p.normw = normw; p.x_out = x_out; p.ss = ss; p.nss = nss; p.resid = resid;
     p.scaled = scaled; p.eps = eps;
     p.status = ctx->status;
+    p.trace = ctx->gemv_trace;
 
-    // slices and half blocks per lane: the smallest slice count that keeps a lane's x within 5 half blocks
+    // column slices per row: the smallest power of two that keeps a lane's share of x within 5 half blocks
     const uint32_t nhb = p.cols / 16;
-    uint32_t S = 1, N = 0;
-    for (;; ++S) {
+    uint32_t S = 1, N = (nhb + 31) / 32;
+    while (N > 5 && S < GEMV_WARPS) {
+        S *= 2;
         N = (nhb + 32 * S - 1) / (32 * S);
-        if (N <= 5) break;
     }
-    BRASA_REQUIRE(ctx, S <= MAX_WARPS, "gemv: %u columns need more column slices than the kernel has warps", p.cols);
-    uint32_t warps = 8 % S == 0 ? 8 : (MAX_WARPS / S) * S;
+    BRASA_REQUIRE(ctx, N <= 5, "gemv: %u columns are more than this kernel takes (%u)", p.cols, 5 * 32 * 16 * GEMV_WARPS);
+    const uint32_t warps = GEMV_WARPS, Wp = warps / S;
     p.slices = S;
     p.warps = warps;
-    p.rows_per_slot = 2 * warps / S;  // every warp takes two rows of a slot
+    p.total_rows = total_rows;
+    p.rows_per_slot = (Wp & 1) ? Wp * R : Wp * R / 2;
 
     const uint32_t row_bytes = tiled_row_bytes(qtype, p.cols);
     const uint32_t slot_bytes = p.rows_per_slot * row_bytes;
     uint32_t grid = std::min<uint32_t>((uint32_t)ctx->sm_count, total_rows);
     uint32_t rows_per_block = (total_rows + grid - 1) / grid;
-    p.max_items = (rows_per_block + 1) * S * (epilogue == EPI_SWIGLU ? 2 : 1) + S * nmat;
-    size_t fixed = (size_t)p.cols * 4 * (normw ? 2 : 1) + (size_t)(p.cols / 16) * 56 + (size_t)((p.max_items + 1) & ~1u) * 4 + 160;
-    BRASA_REQUIRE(ctx, fixed + slot_bytes + 64 <= ctx->smem_optin, "gemv: %u columns do not fit shared memory", p.cols);
     uint32_t segs = epilogue == EPI_SWIGLU ? 2 : nmat;
+    p.max_items = (rows_per_block + 1) * S * (epilogue == EPI_SWIGLU ? 2 : 1) + S * nmat;
+    size_t fixed = (size_t)nhb * 64 + (size_t)((p.max_items + 1) & ~1u) * 4 + 160;
     uint32_t need_slots = (rows_per_block + 1 + p.rows_per_slot - 1) / p.rows_per_slot * (epilogue == EPI_SWIGLU ? 2 : 1) + segs;
-    size_t budget = ctx->smem_optin - fixed - 1024;
+    // When the block's whole share of rows fits next to a second block (100 KB each), stay under that: the
+    // next kernel's block can then start on the same SM and prefetch its weights meanwhile. A larger share
+    // takes the whole shared memory instead: a deep ring matters more than the overlap there.
+    const size_t cap = 100 * 1024;
+    size_t budget = fixed + (size_t)need_slots * (slot_bytes + 16) <= cap ? cap - fixed : ctx->smem_optin - fixed - 1024;
+    BRASA_REQUIRE(ctx, fixed + slot_bytes + 1024 <= ctx->smem_optin, "gemv: %u columns do not fit shared memory", p.cols);
     uint32_t nslot = (uint32_t)std::min<size_t>(need_slots, budget / (slot_bytes + 16));
     BRASA_REQUIRE(ctx, nslot >= 1, "gemv: no room for a ring slot");
     p.nslot = nslot;

@@ -83,6 +83,11 @@ int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total
 int32_t brasa_ctx_sync(brasa_ctx *ctx);
 /* Kernels enqueued on this context so far; a graph replay counts every kernel it holds. */
 uint64_t brasa_ctx_launch_count(brasa_ctx *ctx);
+/* Debugging aid: with BRASA_TRACE=1 in the environment when the context is created, block 0 of the latest
+ * GEMV launch records the global timer (ns) at nine points: entry, before and after the dependency wait, input
+ * vector in shared memory, fixed-point conversion done, registers loaded, first weight slot ready, all rows
+ * done, exit. */
+int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]);
 /* cudaStream_t of the context, for callers that order their own work (NCCL, torch) against it. */
 void *brasa_ctx_stream(brasa_ctx *ctx);
 
