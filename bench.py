@@ -39,6 +39,9 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT, GENERATE, CTX = 512, 256, 2048
 SEED = 20251
+# dram__bytes_read + dram__bytes_write of one gate/up + SwiGLU launch, from the ncu capture summarised in
+# profiles/gemv_rows_kernel_gate_up_alone.md (algorithmic bytes: 28 065 792)
+GATE_UP_TRAFFIC_BYTES = 28_130_000
 METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
 WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
 
@@ -200,6 +203,63 @@ def run_reference(args, rank: int):
 
 # ---- the GPU arm ------------------------------------------------------------------------------------
 
+def profiler_range(on: bool):
+    """Marks the timed decode region for a profiler started with --profile-from-start off (no effect otherwise)."""
+    try:
+        from cuda.bindings import runtime as rt
+    except ImportError:
+        try:
+            from cuda import cudart as rt
+        except ImportError:
+            return
+    (rt.cudaProfilerStart if on else rt.cudaProfilerStop)()
+
+
+def kernel_roofline(B, ctx, K, cfg, peak, peak_kind, profile=False):
+    """The dominant kernel alone: gate/up GEMV + SwiGLU over 36 distinct weight pairs (1 GB) in one CUDA graph."""
+    roof = None
+    try:
+        rows, cols = cfg["intermediate_size"], cfg["hidden_size"]
+        nlayers = cfg["num_hidden_layers"]
+        per = B.qtype_nbytes(B.WeightType.Q4_0, rows * cols)
+        # distinct random matrices: generate once, quantise, tile; 72 buffers of 14 MB
+        f32buf, filebuf = ctx.buffer(rows * cols * 4), ctx.buffer(per)
+        mats = []
+        for i in range(2 * nlayers):
+            dst = ctx.buffer(per)
+            cmd = ctx.command()
+            K.randn(cmd, f32buf, rows * cols, SEED + 7, i * rows * cols, 0.02)
+            K.quantize(cmd, B.WeightType.Q4_0, f32buf, filebuf, rows * cols)
+            K.repack(cmd, B.WeightType.Q4_0, filebuf, dst, rows, cols)
+            cmd.wait()
+            mats.append(B.QMatrix(dst, B.WeightType.Q4_0, rows, cols, B.Layout.TILED))
+        x = np.random.default_rng(1).standard_normal(cols).astype(np.float16).astype(np.float32)
+        gx, gw = ctx.buffer_from(x), ctx.buffer_from(np.ones(cols, np.float32))
+        gxw, gss, gy = ctx.buffer(cols * 4), ctx.buffer(B.norm_partials(cols) * 4), ctx.buffer(rows * 4)
+        cmd = ctx.command()
+        K.add_norm_prep(cmd, gx, None, gw, gxw, gss, cols)
+        cmd.wait()
+        graph = ctx.capture(lambda c: [K.gemv_scaled_swiglu(c, mats[2 * i], mats[2 * i + 1], gxw, gss, 1e-6, gy) for i in range(nlayers)])
+        best = []
+        for i in range(8):
+            if profile and i == 7:
+                profiler_range(True)
+            cmd = ctx.command()
+            graph.launch(cmd)
+            best.append(cmd.wait())
+        if profile:
+            profiler_range(False)
+        t_launch = statistics.median(best[3:]) / nlayers
+        algo = 2 * per + cols * 4 + rows * 4
+        ach = algo / t_launch / 1e9
+        roof = {"bound": "hbm", "kernel": "gemv_rows_kernel<q4_0> gate+up+SwiGLU [2x9728x2560]", "achieved": ach, "peak": peak, "unit": "GB/s",
+                "frac": ach / peak, "peak_source": peak_kind, "us_per_launch": t_launch * 1e6, "algorithmic_bytes_per_launch": algo,
+                "traffic": GATE_UP_TRAFFIC_BYTES}
+    except B.BrasaError as e:  # out of memory on a shared device: report the token-level figure only
+        roof = {"bound": "hbm", "error": str(e), "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None}
+    return roof
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import brasa_b200 as B
     from brasa_b200 import synth
@@ -211,6 +271,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = B.Context(local_rank)
     cfg = synth.QWEN3_4B
+    if args.only_kernel:
+        if rank == 0:
+            peak, peak_kind = measured_peaks()
+            print(json.dumps({"roofline": kernel_roofline(B, ctx, B.Kernels(ctx), cfg, peak, peak_kind, profile=True),
+                              "note": "dominant kernel alone (profiling run)"}))
+        return
     path = model_path("qwen3-4b")
     if rank == 0 and not path.exists():
         tmp = path.with_suffix(".tmp")
@@ -226,7 +292,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- device-resident decode (value) ----
     logits, _ = model.forward(ids, 0)
     first = int(np.argmax(logits[0]))
-    steps_tokens = GENERATE - 1
+    steps_tokens = args.decode_tokens
     for _ in range(args.warmup):
         model.decode_greedy(first, PROMPT, steps_tokens)
     if dist:
@@ -234,11 +300,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ctx.sync()
     launches0 = ctx.launch_count()
     dev_s, out_ids = [], None
+    profiler_range(True)
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.steps):
             out_ids, s = model.decode_greedy(first, PROMPT, steps_tokens)
             dev_s.append(s)
         ctx.sync()
+    profiler_range(False)
     launches = ctx.launch_count() - launches0
     if dist:
         dist.barrier()
@@ -249,6 +317,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_s = float(t.item())
     value = world * args.steps * steps_tokens / total_s
+    if args.only_decode:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                              "ms_per_step": total_s / args.steps * 1e3, "config": {"workload": WORKLOAD, "tokens_per_step": steps_tokens},
+                              "gpu_launches": int(launches), "note": "decode loop only (profiling run)"}))
+        return
 
     # ---- end to end through Session.generate (host buffers) ----
     e2e_vals, prefill_vals = [], []
@@ -276,43 +350,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     per_gpu_tok_s = value / world
     token_frac = per_gpu_tok_s * bytes_per_token / 1e9 / peak
 
-    # ---- dominant kernel alone: gate/up GEMV + SwiGLU over 36 distinct weight pairs ----
-    roof = None
-    try:
-        rows, cols = cfg["intermediate_size"], cfg["hidden_size"]
-        nlayers = cfg["num_hidden_layers"]
-        per = B.qtype_nbytes(B.WeightType.Q4_0, rows * cols)
-        # distinct random matrices: generate once, quantise, tile; 72 buffers of 14 MB
-        f32buf, filebuf = ctx.buffer(rows * cols * 4), ctx.buffer(per)
-        mats = []
-        for i in range(2 * nlayers):
-            dst = ctx.buffer(per)
-            cmd = ctx.command()
-            K.randn(cmd, f32buf, rows * cols, SEED + 7, i * rows * cols, 0.02)
-            K.quantize(cmd, B.WeightType.Q4_0, f32buf, filebuf, rows * cols)
-            K.repack(cmd, B.WeightType.Q4_0, filebuf, dst, rows, cols)
-            cmd.wait()
-            mats.append(B.QMatrix(dst, B.WeightType.Q4_0, rows, cols, B.Layout.TILED))
-        x = np.random.default_rng(1).standard_normal(cols).astype(np.float16).astype(np.float32)
-        gx, gw = ctx.buffer_from(x), ctx.buffer_from(np.ones(cols, np.float32))
-        gxw, gss, gy = ctx.buffer(cols * 4), ctx.buffer(B.norm_partials(cols) * 4), ctx.buffer(rows * 4)
-        cmd = ctx.command()
-        K.add_norm_prep(cmd, gx, None, gw, gxw, gss, cols)
-        cmd.wait()
-        graph = ctx.capture(lambda c: [K.gemv_scaled_swiglu(c, mats[2 * i], mats[2 * i + 1], gxw, gss, 1e-6, gy) for i in range(nlayers)])
-        best = []
-        for _ in range(8):
-            cmd = ctx.command()
-            graph.launch(cmd)
-            best.append(cmd.wait())
-        t_launch = statistics.median(best[3:]) / nlayers
-        algo = 2 * per + cols * 4 + rows * 4
-        ach = algo / t_launch / 1e9
-        roof = {"bound": "hbm", "kernel": "gemv_rows_kernel<q4_0> gate+up+SwiGLU [2x9728x2560]", "achieved": ach, "peak": peak, "unit": "GB/s",
-                "frac": ach / peak, "peak_source": peak_kind, "us_per_launch": t_launch * 1e6, "algorithmic_bytes_per_launch": algo,
-                "traffic": None}
-    except B.BrasaError as e:  # out of memory on a shared device: report the token-level figure only
-        roof = {"bound": "hbm", "error": str(e), "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None}
+    roof = kernel_roofline(B, ctx, K, cfg, peak, peak_kind)
 
     # ---- CPU baseline: the oracle's port on the host cores, over the GPU's own prefill state ----
     cpu = None
@@ -366,6 +404,12 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--decode-tokens", type=int, default=GENERATE - 1,
+                    help="decode forwards per step (default: the workload's 255); smaller values are for profiler captures")
+    ap.add_argument("--only-kernel", action="store_true",
+                    help="run only the dominant kernel's own timing leg (profiler captures)")
+    ap.add_argument("--only-decode", action="store_true",
+                    help="run only the device-resident decode loop (profiler captures): no end-to-end, kernel or CPU legs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -27,6 +27,11 @@ struct brasa_ctx {
     bool pdl = true;             // programmatic dependent launch between decode kernels
     bool capturing = false;      // a stream capture is open (brasa_graph_capture_begin)
     unsigned long long *gemv_trace = nullptr;  // device buffer of phase timestamps when BRASA_TRACE=1
+    struct {
+        const uint8_t *w[3];
+        uint32_t rows[3];
+        uint32_t nmat, total_rows, row_bytes, swiglu;
+    } gemv_next = {};  // see brasa_gemv_hint_next
     bool graphs = true;          // replay the decode step as a CUDA graph (BRASA_GRAPH=0 turns it off)
     uint64_t launches = 0;       // kernels enqueued on this context (graph replays count their nodes)
     uint64_t capture_launches = 0;

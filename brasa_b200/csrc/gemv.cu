@@ -28,7 +28,7 @@
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait rounds before a wait gives up
-constexpr int GEMV_WARPS = 8;               // consumer warps per block; column slices per row divide it
+constexpr int GEMV_WARPS = 16;              // consumer warps per block; column slices per row divide it
 
 enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2 };
 
@@ -55,6 +55,11 @@ struct GemvParams {
     float eps;
     uint32_t *status;
     unsigned long long *trace;  // optional: block 0 records the time of each phase (debugging aid)
+    // weights of the GEMV that follows in the token loop: this block asks L2 for the rows the same block
+    // index will own there, so that kernel's bulk copies find them on chip
+    const uint8_t *pf_w[3];
+    uint32_t pf_rows[3];
+    uint32_t pf_nmat, pf_total_rows, pf_row_bytes, pf_swiglu;
 };
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -70,9 +75,6 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait for the phase with the given parity. False when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
@@ -146,45 +148,36 @@ __device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const X
     return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
 }
 
-// Dot products of NV (1..4) rows of a slot with the lane's share of x; the NV row sums end up in lanes
-// 0, 8, 16, 24 after folding across lanes.
-template <int QT, int N, int NV>
-__device__ __forceinline__ float rows_dot(const uint8_t *row0, uint32_t row_bytes, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
-                                          uint32_t hi_off, uint32_t sc_off, int lane) {
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+// Dot products of two rows of a slot with the lane's share of x (row_b == row_a when there is only one).
+// After folding across lanes, lane 0 holds the sum of row a and lane 8 the sum of row b. The body is kept
+// small on purpose: a fully unrolled four-row version ran out of instruction cache.
+template <int QT, int N>
+__device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_t *row_b, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
+                                              uint32_t hi_off, uint32_t sc_off, int lane) {
+    float acc_a = 0.0f, acc_b = 0.0f;
     // straight-line code: lanes past the end of the row read the last half block and have step 0
 #pragma unroll
     for (int it = 0; it < N; ++it) {
         const uint32_t hbi = min((slice * N + it) * 32 + lane, nhb - 1);
-#pragma unroll
-        for (int r = 0; r < NV; ++r) {
-            const uint8_t *row = row0 + (size_t)r * row_bytes;
-            uint2 codes = *reinterpret_cast<const uint2 *>(row + hbi * 8);
-            uint32_t hb = 0;
-            if (QT == BRASA_Q6_0) hb = *reinterpret_cast<const uint32_t *>(row + hi_off + hbi * 4);
-            float d = __half2float(*reinterpret_cast<const __half *>(row + sc_off + (hbi >> 1) * 2));
-            int sum = half_block_idot<QT>(codes, hb, xr[it]);
-            acc[r] = fmaf(d * xr[it].step, (float)sum, acc[r]);
+        uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
+        uint2 cb = *reinterpret_cast<const uint2 *>(row_b + hbi * 8);
+        uint32_t ha = 0, hb = 0;
+        if (QT == BRASA_Q6_0) {
+            ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
+            hb = *reinterpret_cast<const uint32_t *>(row_b + hi_off + hbi * 4);
         }
+        float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
+        float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
+        int sa = half_block_idot<QT>(ca, ha, xr[it]);
+        int sb = half_block_idot<QT>(cb, hb, xr[it]);
+        acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+        acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
     }
-    // fold the row sums across lane bits 4 and 3, then reduce over bits 2..0: lanes 0, 8, 16, 24 get rows 0, 1, 2, 3
-    const bool hi4 = lane & 16, hi3 = lane & 8;
-    float z;
-    if (NV > 2) {
-        float a = hi4 ? acc[2] : acc[0], a_send = hi4 ? acc[0] : acc[2];
-        float c = hi4 ? acc[3] : acc[1], c_send = hi4 ? acc[1] : acc[3];
-        a += __shfl_xor_sync(0xffffffffu, a_send, 16);
-        c += __shfl_xor_sync(0xffffffffu, c_send, 16);
-        z = hi3 ? c : a;
-        float z_send = hi3 ? a : c;
-        z += __shfl_xor_sync(0xffffffffu, z_send, 8);
-    } else {
-        float a = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 16);
-        float c = NV > 1 ? acc[1] + __shfl_xor_sync(0xffffffffu, acc[1], 16) : 0.0f;
-        z = hi3 ? c : a;
-        float z_send = hi3 ? a : c;
-        z += __shfl_xor_sync(0xffffffffu, z_send, 8);
-    }
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 16);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 16);
+    const bool hi3 = lane & 8;
+    float z = hi3 ? acc_b : acc_a, z_send = hi3 ? acc_a : acc_b;
+    z += __shfl_xor_sync(0xffffffffu, z_send, 8);
     z += __shfl_xor_sync(0xffffffffu, z, 4);
     z += __shfl_xor_sync(0xffffffffu, z, 2);
     z += __shfl_xor_sync(0xffffffffu, z, 1);
@@ -192,11 +185,11 @@ __device__ __forceinline__ float rows_dot(const uint8_t *row0, uint32_t row_byte
 }
 
 // N = half blocks per lane and slice (the lane's x registers hold 14 N words).
-constexpr int R = 4;         // rows a warp works on at a time
+constexpr int R = 2;         // rows a warp works on at a time
 constexpr int MAX_CONV = 3;  // half blocks of x a thread converts with all its loads in flight
 
 template <int QT, int N>
-__global__ void __maxnreg__(112) gemv_rows_kernel(GemvParams p) {
+__global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t row_bytes = tiled_row_bytes(QT, p.cols);
     const uint32_t slot_bytes = p.rows_per_slot * row_bytes;
@@ -244,38 +237,45 @@ __global__ void __maxnreg__(112) gemv_rows_kernel(GemvParams p) {
     auto seg_of = [&](uint32_t k) -> uint32_t { return (uint32_t)(nseg > 1 && k >= seg_slot0[1]) + (uint32_t)(nseg > 2 && k >= seg_slot0[2]); };
 #define SEG_PICK(arr, i) ((i) == 0 ? arr[0] : ((i) == 1 ? arr[1] : arr[2]))
 
+    uint32_t *done = reinterpret_cast<uint32_t *>(empty);  // per slot: warps that have finished with it
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nslot; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], W / split);
+            done[s] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == (int)W) {  // producer warp: one lane streams this block's rows, slot after slot
-        if (lane == 0) {
-            auto issue = [&](uint32_t k) {  // slot k of this block -> ring[k % nslot]
-                const uint32_t i = seg_of(k);
-                uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
-                const uint8_t *src = p.w[i] + (size_t)(SEG_PICK(seg_first, i) + first) * row_bytes;
-                uint32_t s = k % p.nslot;
-                mbar_expect_tx(&full[s], n * row_bytes);
-                bulk_g2s(ring + (size_t)s * slot_bytes, src, n * row_bytes, &full[s]);
-            };
-            // weights are immutable: the first ring-full of copies starts before the input is ready
-            uint32_t k = 0;
-            for (; k < total_slots && k < p.nslot; ++k) issue(k);
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (; k < total_slots; ++k) {
-                if (!mbar_wait(&empty[k % p.nslot], (k / p.nslot - 1) & 1)) {
-                    atomicExch(p.status, 1u);
-                    break;
+    // Slot k of this block -> ring[k % nslot]. There is no producer warp: thread 0 starts the first ring-full of
+    // copies, and the warp that is last to finish with a slot starts the copy that reuses it.
+    auto issue = [&](uint32_t k) {
+        const uint32_t i = seg_of(k);
+        uint32_t first = (k - SEG_PICK(seg_slot0, i)) * RPS, n = min(RPS, SEG_PICK(seg_rows, i) - first);
+        const uint8_t *src = p.w[i] + (size_t)(SEG_PICK(seg_first, i) + first) * row_bytes;
+        uint32_t s = k % p.nslot;
+        mbar_expect_tx(&full[s], n * row_bytes);
+        bulk_g2s(ring + (size_t)s * slot_bytes, src, n * row_bytes, &full[s]);
+    };
+    if (threadIdx.x == 0) {
+        // weights are immutable: these copies start before the input is ready
+        for (uint32_t k = 0; k < total_slots && k < p.nslot; ++k) issue(k);
+        if (p.pf_total_rows) {  // ask L2 for the rows this block index owns in the next GEMV of the chain
+            const uint32_t q0 = p.pf_total_rows * b / G, q1 = p.pf_total_rows * (b + 1) / G;
+            uint32_t base = 0;
+            for (uint32_t i = 0; i < p.pf_nmat; ++i) {
+                uint32_t lo = p.pf_swiglu ? q0 : max(q0, base), hi = p.pf_swiglu ? q1 : min(q1, base + p.pf_rows[i]);
+                if (hi > lo) {
+                    const uint8_t *ptr = p.pf_w[i] + (size_t)(lo - (p.pf_swiglu ? 0 : base)) * p.pf_row_bytes;
+                    size_t bytes = (size_t)(hi - lo) * p.pf_row_bytes;
+                    for (size_t off = 0; off < bytes; off += 32768) {
+                        uint32_t n = (uint32_t)min((size_t)32768, bytes - off);
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr + off), "r"(n) : "memory");
+                    }
                 }
-                issue(k);
+                base += p.pf_rows[i];
             }
         }
-        return;
     }
 
     // ---- before the input exists: the norm weights of the half blocks this thread will convert ----
@@ -450,20 +450,25 @@ __global__ void __maxnreg__(112) gemv_rows_kernel(GemvParams p) {
             const uint32_t nv = in_slot < n_slot ? min(q, n_slot - in_slot) : 0u;
             if (nv > 0) {
                 const uint8_t *row0 = ring + (size_t)s * slot_bytes + (size_t)in_slot * row_bytes;
-                float z;
-                switch (nv) {
-                case 1: z = rows_dot<QT, N, 1>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
-                case 2: z = rows_dot<QT, N, 2>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
-                case 3: z = rows_dot<QT, N, 3>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
-                default: z = rows_dot<QT, N, 4>(row0, row_bytes, xr, slice, nhb, hi_off, sc_off, lane); break;
+#pragma unroll 1
+                for (uint32_t r = 0; r < nv; r += 2) {
+                    const bool two = r + 1 < nv;
+                    const uint8_t *row_a = row0 + (size_t)r * row_bytes, *row_b = two ? row_a + row_bytes : row_a;
+                    float z = row_pair_dot<QT, N>(row_a, row_b, xr, slice, nhb, hi_off, sc_off, lane);
+                    // lane 0 holds row r, lane 8 row r + 1
+                    if ((lane & 23) == 0 && (lane == 0 || two))
+                        part[(seg_before[sgi] + ks * RPS + in_slot + r + (lane >> 3)) * S + slice] = z;
                 }
-                // lane 8 r holds row r (for one or two rows: lane 0 holds row 0, lane 8 row 1)
-                const uint32_t r = nv > 2 ? ((lane & 16) ? 2u : 0u) + ((lane & 8) ? 1u : 0u) : ((lane & 8) ? 1u : 0u);
-                const bool holder = nv > 2 ? (lane & 7) == 0 : (lane & 23) == 0;
-                if (holder && r < nv) part[(seg_before[sgi] + ks * RPS + in_slot + r) * S + slice] = z;
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
+            if (lane == 0 && k + p.nslot < total_slots) {
+                __threadfence_block();
+                if (atomicAdd(&done[s], 1u) == W / split - 1) {
+                    done[s] = 0;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    issue(k + p.nslot);
+                }
+            }
         }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
@@ -547,6 +552,25 @@ __global__ void swiglu_inplace_kernel(float *g, const float *u, uint32_t n) {
 
 }  // namespace
 
+// Tells the next brasa_gemv_launch on this context which matrices the GEMV after it will read, so that it can
+// ask L2 for them while it runs (tiled matrices sharing one column count; swiglu: gate and up row for row).
+void brasa_gemv_hint_next(brasa_ctx *ctx, uint32_t nmat, const brasa_qmatrix *w, bool swiglu) {
+    auto &n = ctx->gemv_next;
+    n = {};
+    if (nmat == 0 || nmat > 3) return;
+    uint32_t total = 0;
+    for (uint32_t i = 0; i < nmat; ++i) {
+        if (w[i].layout != BRASA_LAYOUT_TILED) return;
+        n.w[i] = arg_ptr(w[i].data);
+        n.rows[i] = w[i].rows;
+        total += w[i].rows;
+    }
+    n.nmat = nmat;
+    n.swiglu = swiglu ? 1 : 0;
+    n.row_bytes = tiled_row_bytes(w[0].qtype, w[0].cols);
+    n.total_rows = swiglu ? w[0].rows : total;
+}
+
 // Shared by the model's fused decode path (model.cu) and the reference-shaped entry points below.
 // epilogue: 0 scale, 1 SwiGLU (w[0] = gate, w[1] = up, y[0]), 2 residual (y = resid + W x).
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
@@ -576,6 +600,12 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     p.scaled = scaled; p.eps = eps;
     p.status = ctx->status;
     p.trace = ctx->gemv_trace;
+    if (ctx->gemv_next.total_rows) {
+        for (int i = 0; i < 3; ++i) { p.pf_w[i] = ctx->gemv_next.w[i]; p.pf_rows[i] = ctx->gemv_next.rows[i]; }
+        p.pf_nmat = ctx->gemv_next.nmat; p.pf_total_rows = ctx->gemv_next.total_rows;
+        p.pf_row_bytes = ctx->gemv_next.row_bytes; p.pf_swiglu = ctx->gemv_next.swiglu;
+        ctx->gemv_next.total_rows = 0;
+    }
 
     // column slices per row: the smallest power of two that keeps a lane's share of x within 5 half blocks
     const uint32_t nhb = p.cols / 16;
@@ -628,7 +658,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3((warps + 1) * 32);
+    cfg.blockDim = dim3(warps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];

@@ -19,6 +19,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
                           int epilogue, const float *resid);
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
+void brasa_gemv_hint_next(brasa_ctx *ctx, uint32_t nmat, const brasa_qmatrix *w, bool swiglu);
 int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
                              uint32_t *pos);
 int32_t brasa_attn_decode_fused_launch(brasa_cmd *cmd, int32_t kv, const float *q, const float *k_new, const float *v_new, const float *q_norm,
@@ -228,6 +229,7 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
         {
             brasa_qmatrix w[3] = {l.wq.q, l.wk.q, l.wv.q};
             float *y[3] = {F(m->q), F(m->k_new), F(m->v_new)};
+            brasa_gemv_hint_next(m->ctx, 1, &l.wo.q, false);
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, y, x, nullptr, F(l.attn_norm), nullptr, nullptr, 0, 1, c.eps, SCALE, nullptr));
         }
         KvView all = kv_at(m, li, 0);
@@ -237,15 +239,25 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
                                                  c.heads, c.kv_heads, m->limits.ctx, c.eps));
         {
             float *y[1] = {x};
+            brasa_qmatrix nxt[2] = {l.gate.q, l.up.q};
+            brasa_gemv_hint_next(m->ctx, 2, nxt, true);
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
         {
             brasa_qmatrix w[2] = {l.gate.q, l.up.q};
             float *y[2] = {F(m->gate), nullptr};
+            brasa_gemv_hint_next(m->ctx, 1, &l.down.q, false);
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, y, x, nullptr, F(l.ffn_norm), nullptr, nullptr, 0, 1, c.eps, SWIGLU, nullptr));
         }
         {
             float *y[1] = {x};
+            if (li + 1 < layer_end) {
+                Layer &nl = m->layers[li + 1];
+                brasa_qmatrix nxt[3] = {nl.wq.q, nl.wk.q, nl.wv.q};
+                brasa_gemv_hint_next(m->ctx, 3, nxt, false);
+            } else if (with_head) {
+                brasa_gemv_hint_next(m->ctx, 1, &m->head.q, false);
+            }
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
     }
