@@ -42,6 +42,9 @@ SEED = 20251
 # dram__bytes_read + dram__bytes_write of one gate/up + SwiGLU launch, from the ncu capture summarised in
 # profiles/gemv_rows_kernel_gate_up_alone.md (algorithmic bytes: 28 065 792)
 GATE_UP_TRAFFIC_BYTES = 28_130_000
+# dram__bytes_read + dram__bytes_write of one decode_token_kernel launch at position 512, from the ncu capture summarised
+# in profiles/decode_token_kernel_qwen3_4b.md (algorithmic bytes at that position: 2 436 050 976)
+TOKEN_KERNEL_TRAFFIC_BYTES = 2_451_680_000
 METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
 WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
 
@@ -350,7 +353,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     per_gpu_tok_s = value / world
     token_frac = per_gpu_tok_s * bytes_per_token / 1e9 / peak
 
-    roof = kernel_roofline(B, ctx, K, cfg, peak, peak_kind)
+    # ---- dominant kernel: the whole-token decode kernel, one launch per token (timed above with CUDA events) ----
+    t_token = total_s / (args.steps * steps_tokens)
+    ach = bytes_per_token / t_token / 1e9
+    roof = {"bound": "hbm", "kernel": "decode_token_kernel<kv f16>: one launch = one token (36 layers, lm_head, argmax)",
+            "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": peak_kind, "us_per_launch": t_token * 1e6,
+            "algorithmic_bytes_per_launch": bytes_per_token, "traffic": TOKEN_KERNEL_TRAFFIC_BYTES,
+            "note": "weights 2 360 553 504 B + 147 456 B per cached position, mean position of the timed steps"}
+    if launches != args.steps * steps_tokens:  # the kernel-per-operation path ran (BRASA_TOKEN_KERNEL=0 or unsupported shapes)
+        roof = None
+    gemv_roof = kernel_roofline(B, ctx, K, cfg, peak, peak_kind)
+    if roof is None:
+        roof = gemv_roof
 
     # ---- CPU baseline: the oracle's port on the host cores, over the GPU's own prefill state ----
     cpu = None
@@ -391,6 +405,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "prefill_tok_s": statistics.median(prefill_vals), "same_tokens_as_device_resident": same_tokens},
             "gpu_launches": int(launches),
             "roofline": roof,
+            "gemv_roofline": gemv_roof,
             "token_roofline": {"bytes_per_token": bytes_per_token, "achieved_gbs": per_gpu_tok_s * bytes_per_token / 1e9, "peak": peak,
                                "frac_of_measured": token_frac, "frac_of_8tbs": per_gpu_tok_s * bytes_per_token / 8e12,
                                "roofline_tok_s_at_8tbs": 8e12 / bytes_per_token},

@@ -33,6 +33,7 @@ struct brasa_ctx {
         uint32_t nmat, total_rows, row_bytes, swiglu;
     } gemv_next = {};  // see brasa_gemv_hint_next
     bool graphs = true;          // replay the decode step as a CUDA graph (BRASA_GRAPH=0 turns it off)
+    bool token_kernel = true;    // run a decode token as one persistent kernel (BRASA_TOKEN_KERNEL=0 turns it off)
     uint64_t launches = 0;       // kernels enqueued on this context (graph replays count their nodes)
     uint64_t capture_launches = 0;
     void *argmax_scratch = nullptr;  // arrival counter + per-block partial maxima

@@ -51,9 +51,11 @@ int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
     const char *env = getenv("BRASA_PDL");
     if (env && env[0] == '0') ctx->pdl = false;
     env = getenv("BRASA_TRACE");
-    if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 256) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 256);
+    if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 4096) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 4096);
     env = getenv("BRASA_GRAPH");
     if (env && env[0] == '0') ctx->graphs = false;
+    env = getenv("BRASA_TOKEN_KERNEL");
+    if (env && env[0] == '0') ctx->token_kernel = false;
     *out = ctx;
     return BRASA_OK;
 }
@@ -96,6 +98,14 @@ int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]) {
     BRASA_REQUIRE(ctx, ctx->gemv_trace, "tracing is off: create the context with BRASA_TRACE=1");
     BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     BRASA_CUDA(ctx, cudaMemcpy(out, ctx->gemv_trace, 128, cudaMemcpyDeviceToHost));
+    return BRASA_OK;
+}
+
+int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n) {
+    if (!ctx || !out) return BRASA_EINVAL;
+    BRASA_REQUIRE(ctx, ctx->gemv_trace && n <= 512, "tracing is off (create the context with BRASA_TRACE=1) or more than 512 words asked");
+    BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    BRASA_CUDA(ctx, cudaMemcpy(out, ctx->gemv_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
     return BRASA_OK;
 }
 

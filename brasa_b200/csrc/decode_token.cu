@@ -1,0 +1,926 @@
+// One decode token as ONE persistent kernel (the token loop of crates/models/src/qwen3.rs:551-831 for a single
+// token, plus the greedy choice of crates/runtime/src/sampler.rs:148-170).
+//
+// A token is a chain of about 180 small dependent operations (per layer: QKV GEMV, attention, o_proj GEMV, gate/up
+// GEMV, down GEMV). Launched as separate kernels each link costs about 10 us on B200 although its bytes need 1-4 us,
+// so the chain runs here inside one cooperative launch, one block per SM:
+//   * Weights never wait. Every block owns the same share of rows of every matrix, known when the model is loaded,
+//     so its weight traffic is a fixed list of byte ranges (slots). They stream through a shared-memory ring with
+//     bulk async copies; the warp that is last to finish with a slot starts the copy that reuses it, across
+//     operation boundaries, and asks L2 for the slots a little further down the list. HBM keeps working while the
+//     blocks exchange activations.
+//   * Activations cross blocks without barriers. Every activation vector lives in L2 as 8-byte words
+//     {float, epoch}; a consumer polls the words it needs until they carry the epoch of the producing operation of
+//     this launch. A single 8-byte store is indivisible, so no fence, flag or grid barrier is needed, and one round
+//     trip to L2 both synchronises and delivers the data. Reuse of a buffer is safe by construction: a block can
+//     only write operation k + 2 after every block has finished reading the output of operation k (it needs all of
+//     k + 1, which needs every block to have produced its part, which needs all of k).
+//   * Every poll and every mbarrier wait is bounded. A wait that runs out sets the context's status word and a
+//     block-wide flag after which the block stops waiting and runs to its end; the host reports BRASA_ETIMEOUT.
+// GEMV arithmetic, x conversion and epilogues are those of gemv.cu (same rounding); attention works on 64-key
+// chunks (32 for an f32 cache) shared out over the blocks and is merged per head by the blocks at the far end of
+// the grid.
+#include <stdlib.h>
+
+#include <memory>
+
+#include "attn_device.cuh"
+#include "decode_token.h"
+#include "gemv_device.cuh"
+
+using namespace brasa_dev;
+
+namespace {
+
+constexpr int TK_WARPS = 16, TK_THREADS = TK_WARPS * 32;
+constexpr uint32_t SLOT_CAP = 24 * 1024;   // bytes of one ring slot
+constexpr uint32_t POLL_LIMIT = 1u << 20;  // polls of an activation word before the wait gives up
+constexpr int R = 2;                       // rows a warp works on at a time
+constexpr int NMAX = 5;                    // half blocks of x a lane keeps per column slice
+constexpr uint32_t L2_AHEAD = 8;           // slots asked from L2 beyond the ring
+constexpr uint32_t EPOCH_SPAN = 1024;      // epochs of one launch; operations + 2 must stay below it
+
+enum { OP_GEMV = 0, OP_ATTN = 1 };
+enum { IN_LL = 0, IN_EMBED = 1 };
+enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_LOGITS = 3 };
+
+struct SlotDesc {
+    const uint8_t *src;
+    uint32_t bytes;
+    uint32_t pad;
+};
+
+struct TokOp {
+    uint32_t type, qtype, cols, nmat;
+    uint32_t rows[3], total_rows;
+    uint32_t epilogue, scaled, log2S, nact;
+    uint32_t in_kind, in_op, save_resid, pad0;
+    float eps;
+    uint32_t pad1[3];
+    const uint8_t *w[3];
+    const float *normw;
+    const unsigned long long *in;
+    unsigned long long *out;
+    const float *q_norm, *k_norm;
+    uint8_t *kc, *vc;
+};
+constexpr uint32_t OP_WORDS = sizeof(TokOp) / 4;
+constexpr uint32_t OPS_WORDS = OP_WORDS + 4;  // in shared memory the block's row counts follow the operation
+static_assert(sizeof(TokOp) % 16 == 0, "TokOp is copied as words");
+
+struct TokParams {
+    const TokOp *ops;
+    uint32_t nops;
+    const SlotDesc *slots;
+    const uint32_t *slot_begin;  // [grid + 1]
+    const uint4 *block_ops;      // [nops][grid]: first output row, rows of segments 0 | 1 << 16, rows of segment 2, -
+    uint32_t nslot, xf_bytes, part_floats, resid_floats, sdesc_n;
+    uint32_t *state, *ids, *next_id, *out_ids;
+    uint32_t out_cap;
+    const uint8_t *embed;
+    uint32_t vocab, hidden, heads, kv_heads, max_chunks;
+    const float *cos_t, *sin_t;
+    float *logits;
+    unsigned long long *cand;      // [grid][2]: best logit, its index
+    unsigned long long *partials;  // [heads][max_chunks][130]
+    float attn_scale;
+    uint32_t *status;
+    unsigned long long *trace;  // optional: block 0 stamps the phases of 16 operations from trace_op on (debugging aid)
+    uint32_t trace_op;
+};
+
+struct Best {
+    float v;
+    uint32_t i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
+
+__device__ __forceinline__ void ll_store(unsigned long long *p, uint32_t bits, uint32_t epoch) {
+    unsigned long long w = ((unsigned long long)epoch << 32) | bits;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ll_load(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ void ll_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+// Rows of block b: logical rows [r0, r1) of `total` (matrices one after another; SwiGLU: the rows of gate, up follows
+// the same range), cut into per-matrix segments.
+BRASA_HD inline void block_rows(uint32_t total, uint32_t nmat, const uint32_t rows[3], bool swiglu, uint32_t b, uint32_t G, uint32_t &r0,
+                                uint32_t &r1, uint32_t first[3], uint32_t nrows[3]) {
+    r0 = (uint32_t)((uint64_t)total * b / G);
+    r1 = (uint32_t)((uint64_t)total * (b + 1) / G);
+    uint32_t base = 0;
+    const uint32_t nseg = swiglu ? 2 : nmat;
+    for (int i = 0; i < 3; ++i) {
+        first[i] = 0;
+        nrows[i] = 0;
+        if ((uint32_t)i < nseg) {
+            if (swiglu) {
+                first[i] = r0;
+                nrows[i] = r1 - r0;
+            } else {
+                uint32_t lo = r0 > base ? r0 : base, hi = r1 < base + rows[i] ? r1 : base + rows[i];
+                first[i] = lo > base ? lo - base : 0;
+                nrows[i] = hi > lo ? hi - lo : 0;
+                base += rows[i];
+            }
+        }
+    }
+}
+
+// 16 values of row `row` of a tiled q6_0 table as the four quads of half block hbi (embed_kernel's arithmetic).
+__device__ __forceinline__ void embed_half_block(const uint8_t *table, uint32_t row, uint32_t cols, uint32_t hbi, float4 q[4]) {
+    const uint8_t *r = table + (size_t)row * tiled_row_bytes(BRASA_Q6_0, cols);
+    const uint2 codes = *reinterpret_cast<const uint2 *>(r + hbi * 8);
+    const uint32_t hb = *reinterpret_cast<const uint32_t *>(r + tiled_hi_off(cols) + hbi * 4);
+    const float d = __half2float(*reinterpret_cast<const __half *>(r + tiled_scale_off(BRASA_Q6_0, cols) + (hbi >> 1) * 2));
+    uint32_t a[4];
+    a[0] = lop_and_or(hb, 0x30303030u, codes.x & 0x0F0F0F0Fu);
+    a[1] = lop_and_or(hb >> 2, 0x30303030u, (codes.x >> 4) & 0x0F0F0F0Fu);
+    a[2] = lop_and_or(hb << 2, 0x30303030u, codes.y & 0x0F0F0F0Fu);
+    a[3] = lop_and_or(hb << 4, 0x30303030u, (codes.y >> 4) & 0x0F0F0F0Fu);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        q[j].x = d * (float)((int)(a[j] & 255u) - 32);
+        q[j].y = d * (float)((int)((a[j] >> 8) & 255u) - 32);
+        q[j].z = d * (float)((int)((a[j] >> 16) & 255u) - 32);
+        q[j].w = d * (float)((int)(a[j] >> 24) - 32);
+    }
+}
+
+#define TRACE(i) do { if (c.trace && c.b == 0 && threadIdx.x == 0 && oi >= c.trace_op && oi < c.trace_op + 16) c.trace[16 + (oi - c.trace_op) * 8 + (i)] = (unsigned long long)clock64(); } while (0)
+
+// What the phases of an operation share. The phase functions are inlined: with 227 KB of shared memory in use the
+// L1 cache is a few KB, so a stack frame (calls, spills) costs a trip to L2 per access.
+struct TokCtx {
+    uint8_t *ring, *xfb;
+    float *part, *resid, *red;
+    uint4 *sdesc;
+    uint64_t *full;
+    uint32_t *done;
+    volatile uint32_t *s_abort;
+    const uint4 *myslots;
+    uint32_t *status;
+    unsigned long long *trace;
+    uint32_t trace_op, my_slots, nslot, G, b, pos, seq, token, h0, hn;
+};
+
+// This warp's place in the block's slot list: next list index, its ring slot, that use's phase parity.
+struct WarpRing {
+    uint32_t kk, rs, rph;
+};
+
+// A wait ran out: remember it, stop waiting in this block.
+__device__ __forceinline__ void give_up(const TokCtx &c, uint32_t code) {
+    atomicExch(c.status, code);
+    *c.s_abort = 1;
+}
+
+// Four activation words at once: all loads in flight together, so a wait costs one round trip to L2 when the data is there.
+__device__ __forceinline__ void ll_wait4(const TokCtx &c, const unsigned long long *p0, const unsigned long long *p1, const unsigned long long *p2,
+                                         const unsigned long long *p3, uint32_t epoch, uint32_t out[4]) {
+    for (uint32_t it = 0;; ++it) {
+        const unsigned long long w0 = ll_load(p0), w1 = ll_load(p1), w2 = ll_load(p2), w3 = ll_load(p3);
+        out[0] = (uint32_t)w0; out[1] = (uint32_t)w1; out[2] = (uint32_t)w2; out[3] = (uint32_t)w3;
+        const bool ok = (uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch && (uint32_t)(w3 >> 32) == epoch;
+        if (ok || *c.s_abort) break;
+        if (it >= POLL_LIMIT) {
+            give_up(c, 3);
+            break;
+        }
+    }
+}
+
+// a slot descriptor {address lo, address hi, bytes, -} -> ring[s]
+__device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s) {
+    const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
+    mbar_expect_tx(&c.full[s], d.z);
+    bulk_g2s(c.ring + (size_t)s * SLOT_CAP, src, d.z, &c.full[s]);
+}
+__device__ __forceinline__ void l2_ask(uint4 d) {
+    const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
+    if (d.z) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(d.z) : "memory");
+}
+
+// ---- GEMV, phase 1: wait for the input, fold the norm weight, convert to fixed point (thread t: half blocks t, t + 512, ..).
+// Returns the thread's share of sum x^2.
+__device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, const uint8_t *embed, uint32_t vocab, uint32_t epoch_in) {
+    const int tid = threadIdx.x;
+    const uint32_t cols = op.cols, nhb = cols / 16;
+    uint4 *xf = reinterpret_cast<uint4 *>(c.xfb);
+    float ssq = 0.0f;
+    const uint32_t off[4] = {0, 16, 4, 20};
+#pragma unroll 1
+    for (uint32_t hbi = tid; hbi < nhb; hbi += TK_THREADS) {
+        const uint32_t e0 = (hbi >> 1) * 32 + 8 * (hbi & 1);
+        float4 q[4];
+        if (op.in_kind == IN_EMBED) {
+            if (c.token < vocab) embed_half_block(embed, c.token, cols, hbi, q);
+            else q[0] = q[1] = q[2] = q[3] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        } else {
+            const unsigned long long *src = op.in + e0;
+            unsigned long long w[16];
+            for (uint32_t it = 0;; ++it) {
+                ll_load2(src + 0, w[0], w[1]);   ll_load2(src + 2, w[2], w[3]);      // quad 0: e0 .. e0 + 3
+                ll_load2(src + 16, w[4], w[5]);  ll_load2(src + 18, w[6], w[7]);     // quad 1: e0 + 16 ..
+                ll_load2(src + 4, w[8], w[9]);   ll_load2(src + 6, w[10], w[11]);    // quad 2: e0 + 4 ..
+                ll_load2(src + 20, w[12], w[13]); ll_load2(src + 22, w[14], w[15]);  // quad 3: e0 + 20 ..
+                uint32_t bad = 0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) bad |= (uint32_t)(w[i] >> 32) ^ epoch_in;
+                if (bad == 0 || *c.s_abort) break;
+                if (it >= POLL_LIMIT) {
+                    give_up(c, 3);
+                    break;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                q[j] = make_float4(__uint_as_float((uint32_t)w[4 * j]), __uint_as_float((uint32_t)w[4 * j + 1]),
+                                   __uint_as_float((uint32_t)w[4 * j + 2]), __uint_as_float((uint32_t)w[4 * j + 3]));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 &v = q[j];
+            ssq = fmaf(v.x, v.x, ssq); ssq = fmaf(v.y, v.y, ssq); ssq = fmaf(v.z, v.z, ssq); ssq = fmaf(v.w, v.w, ssq);
+            if (op.save_resid) {  // this vector is the residual a later epilogue adds: keep this block's rows
+                const uint32_t e = e0 + off[j] - c.h0;  // wraps for rows before h0
+                if (e + 0 < c.hn) c.resid[e + 0] = v.x;
+                if (e + 1 < c.hn) c.resid[e + 1] = v.y;
+                if (e + 2 < c.hn) c.resid[e + 2] = v.z;
+                if (e + 3 < c.hn) c.resid[e + 3] = v.w;
+            }
+            if (op.normw) {
+                const float4 nw = *reinterpret_cast<const float4 *>(op.normw + e0 + off[j]);
+                v.x *= nw.x; v.y *= nw.y; v.z *= nw.z; v.w *= nw.w;
+            }
+        }
+        x_half_block_to_fixed(xf, hbi, q[0], q[1], q[2], q[3]);
+    }
+    return ssq;
+}
+
+// ---- GEMV, phase 2: the rows. A slot holds up to RPS rows of one segment; its eight warps (half_w rows x S slices)
+// share them; a lane keeps the same half blocks of x for every row.
+template <int QT>
+__device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, const uint32_t *bo, uint32_t gslot, const WarpRing wr) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cols = op.cols, nhb = cols / 16, lS = op.log2S, S = 1u << lS, nact = op.nact;
+    const uint32_t lRPS = 4 - lS, RPS = 1u << lRPS, lhw = lRPS - 1, half_w = 1u << lhw;  // rows per slot = warps side by side
+    const uint32_t row_bytes = tiled_row_bytes(QT, cols);
+    const uint32_t rows0 = bo[1] & 0xffffu, rows1 = bo[1] >> 16, rows2 = bo[2];
+    const uint32_t sl0 = (rows0 + RPS - 1) >> lRPS, sl1 = sl0 + ((rows1 + RPS - 1) >> lRPS), total_slots = sl1 + ((rows2 + RPS - 1) >> lRPS);
+    const uint4 *xf = reinterpret_cast<const uint4 *>(c.xfb);
+    const uint32_t slice = warp & (S - 1), rwl = (warp >> lS) & (half_w - 1);
+    XFixed xr[NMAX];
+#pragma unroll
+    for (int i = 0; i < NMAX; ++i) {
+        const uint32_t want = (slice * nact + i) * 32 + lane;
+        const uint32_t hbi = min(want, nhb - 1), sw = (hbi >> 1) & 3;
+        uint4 c0 = xf[hbi * 4 + (0 ^ sw)], c1 = xf[hbi * 4 + (1 ^ sw)], c2 = xf[hbi * 4 + (2 ^ sw)], c3 = xf[hbi * 4 + (3 ^ sw)];
+        xr[i].d[0][0] = c0.x; xr[i].d[0][1] = c0.y; xr[i].d[0][2] = c0.z; xr[i].d[1][0] = c0.w;
+        xr[i].d[1][1] = c1.x; xr[i].d[1][2] = c1.y; xr[i].d[2][0] = c1.z; xr[i].d[2][1] = c1.w;
+        xr[i].d[2][2] = c2.x; xr[i].d[3][0] = c2.y; xr[i].d[3][1] = c2.z; xr[i].d[3][2] = c2.w;
+        xr[i].total = (int)c3.x;
+        xr[i].step = (want < nhb && (uint32_t)i < nact) ? __uint_as_float(c3.y) : 0.0f;
+    }
+    const uint32_t hi_off = tiled_hi_off(cols), sc_off = tiled_scale_off(QT, cols);
+    uint32_t kk = wr.kk, rs = wr.rs, rph = wr.rph;
+#pragma unroll 1
+    for (uint32_t j = kk - gslot; j < total_slots; j += 2) {
+        const uint32_t sgi = (j >= sl0) + (j >= sl1);
+        const uint32_t ks = j - (sgi == 0 ? 0u : (sgi == 1 ? sl0 : sl1));
+        const uint32_t sg_rows = sgi == 0 ? rows0 : (sgi == 1 ? rows1 : rows2), sg_before = sgi == 0 ? 0u : (sgi == 1 ? rows0 : rows0 + rows1);
+        if (!*c.s_abort && !mbar_wait(&c.full[rs], rph)) {
+            if (lane == 0) give_up(c, 2);
+        }
+        const uint32_t n_slot = min(RPS, sg_rows - (ks << lRPS));
+        const uint32_t qn = (n_slot + half_w - 1) >> lhw, in_slot = rwl * qn;
+        const uint32_t nv = in_slot < n_slot ? min(qn, n_slot - in_slot) : 0u;
+        const uint8_t *row0 = c.ring + (size_t)rs * SLOT_CAP + (size_t)in_slot * row_bytes;
+#pragma unroll 1
+        for (uint32_t r = 0; r < nv; r += 2) {
+            const bool two = r + 1 < nv;
+            const uint8_t *row_a = row0 + (size_t)r * row_bytes, *row_b = two ? row_a + row_bytes : row_a;
+            float z = row_pair_dot<QT, NMAX>(row_a, row_b, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            if ((lane & 23) == 0 && (lane == 0 || two)) c.part[((sg_before + (ks << lRPS) + in_slot + r + (lane >> 3)) << lS) + slice] = z;
+        }
+        __syncwarp();
+        if (lane == 0 && kk + c.nslot < c.my_slots) {
+            __threadfence_block();
+            if (atomicAdd(&c.done[rs], 1u) == TK_WARPS / 2 - 1) {  // last of the eight: the slot is free, refill it
+                c.done[rs] = 0;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_slot(c, c.sdesc[j], rs);
+                l2_ask(c.sdesc[j + L2_AHEAD]);
+            }
+        }
+        kk += 2;
+        rs += 2;
+        if (rs >= c.nslot) {
+            rs -= c.nslot;
+            rph ^= 1;
+        }
+    }
+    return WarpRing{kk, rs, rph};
+}
+
+// ---- GEMV, phase 3: one thread per output row of this block; the result goes out as {value, epoch} words.
+__device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, const uint32_t *bo, float scale, uint32_t epoch, float *logits,
+                                           unsigned long long *cand) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t lS = op.log2S, S = 1u << lS;
+    const bool swiglu = op.epilogue == EPI_SWIGLU;
+    const uint32_t r0 = bo[0], rows0 = bo[1] & 0xffffu, rows1 = bo[1] >> 16, rows2 = bo[2];
+    const uint32_t nr = swiglu ? rows0 : rows0 + rows1 + rows2;  // segments follow one another in part[] and in the output
+    const float *part = c.part;
+    Best bst{-INFINITY, 0xffffffffu};
+#pragma unroll 1
+    for (uint32_t j = tid; j < nr; j += TK_THREADS) {
+        float v = 0.0f;
+#pragma unroll 1
+        for (uint32_t sl = 0; sl < S; ++sl) v += part[(j << lS) + sl];
+        v *= scale;
+        if (swiglu) {
+            float u = 0.0f;
+#pragma unroll 1
+            for (uint32_t sl = 0; sl < S; ++sl) u += part[((nr + j) << lS) + sl];
+            u *= scale;
+            v = (v / (1.0f + expf(-v))) * u;
+        }
+        if (op.epilogue == EPI_RESID) v += c.resid[j];
+        if (op.epilogue == EPI_LOGITS) {
+            logits[r0 + j] = v;
+            if (v > bst.v) bst = Best{v, r0 + j};
+        } else {
+            ll_store(op.out + r0 + j, __float_as_uint(v), epoch);
+        }
+    }
+    if (op.epilogue == EPI_LOGITS) {  // this block's best logit for the greedy choice
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, bst.v, o), __shfl_xor_sync(0xffffffffu, bst.i, o)};
+            bst = better(bst, other);
+        }
+        if (lane == 0) { c.red[16 + warp] = bst.v; c.red[32 + warp] = __uint_as_float(bst.i); }
+        __syncthreads();
+        if (tid == 0) {
+#pragma unroll 1
+            for (int w = 1; w < TK_WARPS; ++w) bst = better(bst, Best{c.red[16 + w], __float_as_uint(c.red[32 + w])});
+            ll_store(cand + 2 * c.b, __float_as_uint(bst.v), epoch);
+            ll_store(cand + 2 * c.b + 1, bst.i, epoch);
+        }
+    }
+}
+
+// ---- attention of this token over the cache, new row included ----
+template <int KV>
+__device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, uint32_t oi, uint32_t epoch, uint32_t epoch_in, uint32_t heads,
+                                          uint32_t kv_heads, uint32_t max_chunks, const float *cos_t, const float *sin_t,
+                                          unsigned long long *partials, float attn_scale) {
+    constexpr int RB = KvRow<KV>::BYTES, RS = KvRow<KV>::STRIDE;
+    constexpr uint32_t C = KV == BRASA_KV_F32 ? 32 : 64;  // keys per work item
+    constexpr int KPW = C / TK_WARPS, LPK = 32 / KPW, DPL = 128 / LPK;  // keys per warp, lanes per key, dims per lane
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t Gq = heads / kv_heads, pos = c.pos;
+    const uint32_t lk = pos + 1, nchunks = (lk + C - 1) / C;
+    uint8_t *kt = c.xfb, *vt = c.xfb + C * RS;
+    float *qs = reinterpret_cast<float *>(vt + C * RS);  // [8][128]
+    float *ps = qs + 8 * 128;                            // [8][C]
+    float *ml = ps + 8 * C;                              // merge: m[max_chunks], l[max_chunks]
+    float *red = c.red;
+    const uint32_t nitems = kv_heads * nchunks;
+#pragma unroll 1
+    for (uint32_t item = c.b; item < nitems; item += c.G) {
+        const uint32_t kh = item / nchunks, ch = item - kh * nchunks;
+        const uint32_t key0 = ch * C, nkeys = min(C, lk - key0);
+        const bool has_new = ch == nchunks - 1;
+        const uint32_t nold = has_new ? nkeys - 1 : nkeys;
+        {
+            constexpr int VEC = KV == BRASA_KV_Q8_0 ? 8 : 16, PER_ROW = RB / VEC;
+#pragma unroll 1
+            for (uint32_t i = tid; i < nold * PER_ROW; i += TK_THREADS) {
+                uint32_t r = i / PER_ROW, v = i % PER_ROW;
+                size_t goff = ((size_t)(key0 + r) * kv_heads + kh) * RB + (size_t)v * VEC;
+                if (KV == BRASA_KV_Q8_0) { cp_async8(kt + r * RS + v * VEC, op.kc + goff); cp_async8(vt + r * RS + v * VEC, op.vc + goff); }
+                else { cp_async16(kt + r * RS + v * VEC, op.kc + goff); cp_async16(vt + r * RS + v * VEC, op.vc + goff); }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        if ((uint32_t)warp < Gq + 2 && ((uint32_t)warp < Gq || has_new)) {
+            // warps 0 .. Gq-1: a query head; warp Gq: the new key row; warp Gq + 1: the new value row
+            const uint32_t g = warp;
+            const unsigned long long *src = g < Gq ? op.in + (size_t)(kh * Gq + g) * 128 : op.in + (size_t)(heads + (g - Gq) * kv_heads + kh) * 128;
+            float xv[4], y[4];
+            {
+                uint32_t raw[4];
+                ll_wait4(c, src + lane, src + lane + 32, src + lane + 64, src + lane + 96, epoch_in, raw);
+                for (int j = 0; j < 4; ++j) xv[j] = __uint_as_float(raw[j]);
+            }
+            if (g <= Gq) norm_rope_vals(xv, g < Gq ? op.q_norm : op.k_norm, cos_t, sin_t, pos, op.eps, lane, y);
+            if (g < Gq) {
+                for (int j = 0; j < 4; ++j) qs[g * 128 + lane + 32 * j] = y[j];
+            } else {
+                const size_t grow = ((size_t)pos * kv_heads + kh) * RB;
+                if (g == Gq) put_row<KV>(op.kc + grow, kt + (nkeys - 1) * RS, y, lane);
+                else put_row<KV>(op.vc + grow, vt + (nkeys - 1) * RS, xv, lane);
+            }
+        }
+        TRACE(1);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        TRACE(2);
+        {   // scores: KPW keys per warp, LPK lanes share a key
+            const uint32_t key = warp * KPW + lane / LPK;
+            const int d0 = (lane % LPK) * DPL;
+            float kv[DPL];
+            const uint8_t *row = kt + min(key, nkeys - 1) * RS;
+#pragma unroll
+            for (int d = 0; d < DPL; d += 8) tile_load8<KV>(row, d0 + d, kv + d);
+#pragma unroll 1
+            for (uint32_t g = 0; g < Gq; ++g) {
+                float a = 0.0f;
+#pragma unroll
+                for (int d = 0; d < DPL; d += 4) {
+                    const float4 qa = *reinterpret_cast<const float4 *>(qs + g * 128 + d0 + d);
+                    a = fmaf(qa.x, kv[d], a); a = fmaf(qa.y, kv[d + 1], a); a = fmaf(qa.z, kv[d + 2], a); a = fmaf(qa.w, kv[d + 3], a);
+                }
+                for (int o = LPK / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                if (lane % LPK == 0) ps[g * C + key] = key < nkeys ? a * attn_scale : -INFINITY;
+            }
+        }
+        __syncthreads();
+        TRACE(3);
+        if ((uint32_t)warp < Gq) {  // softmax numerators of this chunk, head = warp
+            const uint32_t g = warp;
+            float v0 = ps[g * C + lane], v1 = C == 64 ? ps[g * C + lane + 32] : -INFINITY;
+            float m = fmaxf(v0, v1);
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            v0 = expf(v0 - m);
+            v1 = C == 64 ? expf(v1 - m) : 0.0f;
+            ps[g * C + lane] = v0;
+            if (C == 64) ps[g * C + lane + 32] = v1;
+            float l = v0 + v1;
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            if (lane == 0) { red[g] = m; red[8 + g] = l; }
+        }
+        __syncthreads();
+        TRACE(4);
+#pragma unroll 1
+        for (uint32_t o = tid; o < Gq * 128; o += TK_THREADS) {  // P V: one output element per thread
+            const uint32_t g = o >> 7, d = o & 127;
+            float acc = 0.0f;
+#pragma unroll 4
+            for (uint32_t j = 0; j < nkeys; ++j) acc = fmaf(ps[g * C + j], tile_at<KV>(vt + j * RS, d), acc);
+            const uint32_t head = kh * Gq + g;
+            if (nchunks == 1) {
+                ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(acc / red[8 + g]), epoch);
+            } else {
+                unsigned long long *pp = partials + ((size_t)head * max_chunks + ch) * 130;
+                ll_store(pp + 2 + d, __float_as_uint(acc), epoch);
+                if (d == 0) { ll_store(pp, __float_as_uint(red[g]), epoch); ll_store(pp + 1, __float_as_uint(red[8 + g]), epoch); }
+            }
+        }
+        __syncthreads();
+    }
+    TRACE(5);
+    if (nchunks > 1) {
+        // merge the chunks of a head; heads go to the blocks at the far end of the grid (the work items start at block 0)
+#pragma unroll 1
+        for (uint32_t head = c.G - 1 - c.b; head < heads; head += c.G) {
+            const unsigned long long *pp = partials + (size_t)head * max_chunks * 130;
+#pragma unroll 1
+            for (uint32_t ch = tid; ch < nchunks; ch += TK_THREADS) {
+                uint32_t raw[4];
+                ll_wait4(c, pp + (size_t)ch * 130, pp + (size_t)ch * 130 + 1, pp + (size_t)ch * 130, pp + (size_t)ch * 130 + 1, epoch, raw);
+                ml[ch] = __uint_as_float(raw[0]);
+                ml[max_chunks + ch] = __uint_as_float(raw[1]);
+            }
+            __syncthreads();
+            float M = -INFINITY;
+#pragma unroll 1
+            for (uint32_t ch = 0; ch < nchunks; ++ch) M = fmaxf(M, ml[ch]);
+            const uint32_t d = tid & 127, cg = tid >> 7;
+            float L = 0.0f, a = 0.0f;
+#pragma unroll 1
+            for (uint32_t ch = cg; ch < nchunks; ch += 16) {  // four of this thread's chunks per round trip
+                const uint32_t cc[4] = {ch, min(ch + 4, nchunks - 1), min(ch + 8, nchunks - 1), min(ch + 12, nchunks - 1)};
+                uint32_t raw[4];
+                ll_wait4(c, pp + (size_t)cc[0] * 130 + 2 + d, pp + (size_t)cc[1] * 130 + 2 + d, pp + (size_t)cc[2] * 130 + 2 + d,
+                         pp + (size_t)cc[3] * 130 + 2 + d, epoch, raw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (ch + 4 * j < nchunks) {
+                        float w = expf(ml[cc[j]] - M);
+                        L = fmaf(ml[max_chunks + cc[j]], w, L);
+                        a = fmaf(__uint_as_float(raw[j]), w, a);
+                    }
+                }
+            }
+            qs[cg * 128 + d] = a;
+            if (d == 0) qs[512 + cg] = L;
+            __syncthreads();
+            if (tid < 128) {
+                float A = (qs[d] + qs[128 + d]) + (qs[256 + d] + qs[384 + d]);
+                float Lt = (qs[512] + qs[513]) + (qs[514] + qs[515]);
+                ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(A / Lt), epoch);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+template <int KV>
+__global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    TokCtx c;
+    c.ring = smem;
+    c.xfb = c.ring + (size_t)p.nslot * SLOT_CAP;
+    c.part = reinterpret_cast<float *>(c.xfb + p.xf_bytes);
+    c.resid = c.part + p.part_floats;
+    c.sdesc = reinterpret_cast<uint4 *>(c.resid + p.resid_floats);  // descriptors of the slots this operation refills
+    c.full = reinterpret_cast<uint64_t *>(c.sdesc + p.sdesc_n);
+    c.done = reinterpret_cast<uint32_t *>(c.full + p.nslot);
+    c.red = reinterpret_cast<float *>(c.done + p.nslot);             // [48]
+    uint32_t *ops_s = reinterpret_cast<uint32_t *>(c.red + 48);      // [2][OPS_WORDS]: operation, then this block's rows
+    c.s_abort = ops_s + 2 * OPS_WORDS;
+    c.status = p.status;
+    c.trace = p.trace;
+    c.trace_op = p.trace_op;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t G = gridDim.x, b = blockIdx.x;
+    c.G = G;
+    c.b = b;
+    c.pos = p.state[0];
+    c.seq = p.state[2];
+    c.token = p.ids[0];
+    c.nslot = p.nslot;
+    const uint32_t slot_lo = p.slot_begin[b];
+    c.my_slots = p.slot_begin[b + 1] - slot_lo;
+    c.myslots = reinterpret_cast<const uint4 *>(p.slots + slot_lo);
+    c.h0 = p.hidden * b / G;  // this block's rows of a hidden-size vector
+    c.hn = p.hidden * (b + 1) / G - c.h0;
+
+    // operation oi and this block's row counts for it -> ops_s[oi & 1]
+    // (by the last threads of the block: the first ones are the busiest in the input phase)
+    auto fetch_op = [&](uint32_t oi) {
+        const int t = TK_THREADS - 1 - tid;
+        if (t < (int)OP_WORDS) ops_s[(oi & 1) * OPS_WORDS + t] = reinterpret_cast<const uint32_t *>(p.ops + oi)[t];
+        else if (t < (int)OPS_WORDS) ops_s[(oi & 1) * OPS_WORDS + t] = reinterpret_cast<const uint32_t *>(p.block_ops + (size_t)oi * G + b)[t - OP_WORDS];
+    };
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.nslot; ++s) {
+            mbar_init(&c.full[s], 1);
+            c.done[s] = 0;
+        }
+        *c.s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fetch_op(0);
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t k = 0;
+        for (; k < c.my_slots && k < p.nslot; ++k) issue_slot(c, c.myslots[k], k);
+        for (; k < c.my_slots && k < p.nslot + L2_AHEAD; ++k) l2_ask(c.myslots[k]);
+    }
+
+    // This warp's slots are the list entries kk = sub, sub + 2, ..: warps 0-7 take the even ones, warps 8-15 the odd
+    // ones, and with an even ring a ring slot always serves the same eight warps, which all wait for every use of it.
+    WarpRing wr{(uint32_t)warp >> 3, (uint32_t)warp >> 3, 0u};
+    uint32_t gslot = 0;  // list index of the current operation's first slot
+
+#pragma unroll 1
+    for (uint32_t oi = 0; oi < p.nops; ++oi) {
+        const TokOp &op = *reinterpret_cast<const TokOp *>(ops_s + (oi & 1) * OPS_WORDS);
+        const uint32_t *bo = ops_s + (oi & 1) * OPS_WORDS + OP_WORDS;  // r0, rows of segments 0 and 1 (16 bits each), rows of segment 2
+        if (oi + 1 < p.nops) fetch_op(oi + 1);
+        const uint32_t epoch = c.seq * EPOCH_SPAN + oi + 1;
+        const uint32_t epoch_in = c.seq * EPOCH_SPAN + op.in_op + 1;
+
+        TRACE(0);
+        if (op.type == OP_GEMV) {
+            const uint32_t lRPS = 4 - op.log2S, RPS = 1u << lRPS;
+            const uint32_t total_slots = (((bo[1] & 0xffffu) + RPS - 1) >> lRPS) + (((bo[1] >> 16) + RPS - 1) >> lRPS) + ((bo[2] + RPS - 1) >> lRPS);
+            // the descriptors this operation's refills and L2 requests will need, fetched by the threads that poll least
+            for (uint32_t i = TK_THREADS - 1 - tid; i < total_slots + L2_AHEAD; i += TK_THREADS) {
+                const uint32_t k = gslot + p.nslot + i;
+                c.sdesc[i] = k < c.my_slots ? c.myslots[k] : make_uint4(0, 0, 0, 0);
+            }
+            float ssq = gemv_input(c, op, p.embed, p.vocab, epoch_in);
+            TRACE(1);
+            for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            if (lane == 0) c.red[warp] = ssq;
+            __syncthreads();
+            TRACE(2);
+            if (warp == TK_WARPS - 1) {  // 1 / rms of the whole input from the warps' sums, parked for the epilogue
+                float tot = c.red[lane & (TK_WARPS - 1)];
+                for (int o = TK_WARPS / 2; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+                if (lane == 0) c.red[47] = op.scaled ? 1.0f / sqrtf(tot / (float)op.cols + op.eps) : 1.0f;
+            }
+            if (op.qtype == BRASA_Q4_0) wr = gemv_rows<BRASA_Q4_0>(c, op, bo, gslot, wr);
+            else wr = gemv_rows<BRASA_Q6_0>(c, op, bo, gslot, wr);
+            TRACE(4);
+            gslot += total_slots;
+            __syncthreads();
+            TRACE(5);
+            gemv_epilogue(c, op, bo, c.red[47], epoch, p.logits, p.cand);
+        } else {
+            attention_op<KV>(c, op, oi, epoch, epoch_in, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
+        }
+        TRACE(6);
+        __syncthreads();
+        TRACE(7);
+    }
+
+    // ---- greedy choice and the step's bookkeeping: block 0 gathers every block's best logit ----
+    if (b == 0) {
+        const uint32_t epoch = c.seq * EPOCH_SPAN + p.nops;  // of the lm_head, the last operation
+        Best bst{-INFINITY, 0xffffffffu};
+#pragma unroll 1
+        for (uint32_t i = tid; i < G; i += TK_THREADS) {
+            uint32_t raw[4];
+            ll_wait4(c, p.cand + 2 * i, p.cand + 2 * i + 1, p.cand + 2 * i, p.cand + 2 * i + 1, epoch, raw);
+            bst = better(bst, Best{__uint_as_float(raw[0]), raw[1]});
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, bst.v, o), __shfl_xor_sync(0xffffffffu, bst.i, o)};
+            bst = better(bst, other);
+        }
+        if (lane == 0) { c.red[16 + warp] = bst.v; c.red[32 + warp] = __uint_as_float(bst.i); }
+        __syncthreads();
+        if (tid == 0) {
+#pragma unroll 1
+            for (int w = 1; w < TK_WARPS; ++w) bst = better(bst, Best{c.red[16 + w], __float_as_uint(c.red[32 + w])});
+            const uint32_t tok = (bst.v == -INFINITY || bst.i == 0xffffffffu) ? 0u : bst.i;
+            *p.next_id = tok;
+            p.ids[0] = tok;
+            const uint32_t n = p.state[1];
+            if (n < p.out_cap) p.out_ids[n] = tok;
+            p.state[1] = n + 1;
+            p.state[0] = c.pos + 1;
+            p.state[2] = c.seq + 1;
+        }
+    }
+}
+
+uint32_t attn_chunk(int32_t kv) { return kv == BRASA_KV_F32 ? 32u : 64u; }
+uint32_t attn_row_stride(int32_t kv) { return kv == BRASA_KV_F32 ? 528u : (kv == BRASA_KV_F16 ? 272u : 144u); }
+
+// Column slices and active half blocks per lane for a GEMV of this width; false when the kernel does not take it.
+bool gemv_shape(int qtype, uint32_t cols, uint32_t *S_out, uint32_t *nact_out) {
+    if (cols == 0 || cols % 256 != 0) return false;
+    const uint32_t nhb = cols / 16, row_bytes = tiled_row_bytes(qtype, cols);
+    for (uint32_t S = 1; S <= 8; S *= 2) {
+        uint32_t N = (nhb + 32 * S - 1) / (32 * S);
+        uint32_t RPS = TK_WARPS / S * R / 2;
+        if (N <= NMAX && (uint64_t)RPS * row_bytes <= SLOT_CAP) {
+            *S_out = S;
+            *nact_out = N;
+            return true;
+        }
+    }
+    return false;
+}
+
+}  // namespace
+
+struct brasa_token_program {
+    brasa_ctx *ctx = nullptr;
+    TokParams params{};
+    size_t smem = 0;
+    int32_t kv = 0;
+    uint32_t grid = 0;
+    std::vector<void *> device;  // allocations owned by the program
+};
+
+bool brasa_token_program_supported(brasa_ctx *ctx, const brasa_token_model &m) {
+    if (m.head_dim != 128 || m.kv_heads == 0 || m.heads % m.kv_heads != 0 || m.heads / m.kv_heads > 8) return false;
+    if (m.layers.empty() || m.layers.size() * 5 + 3 >= EPOCH_SPAN) return false;
+    if (m.embed.layout != BRASA_LAYOUT_TILED || m.embed.qtype != BRASA_Q6_0 || m.embed.cols != m.hidden) return false;
+    if (m.head.layout != BRASA_LAYOUT_TILED || (m.head.qtype != BRASA_Q4_0 && m.head.qtype != BRASA_Q6_0)) return false;
+    uint32_t S, n;
+    if (!gemv_shape(m.head.qtype, m.hidden, &S, &n) || !gemv_shape(BRASA_Q4_0, m.hidden, &S, &n) ||
+        !gemv_shape(BRASA_Q4_0, m.heads * 128, &S, &n) || !gemv_shape(BRASA_Q4_0, m.ffn, &S, &n))
+        return false;
+    for (const brasa_token_layer &l : m.layers)
+        for (const brasa_qmatrix *w : {&l.wq, &l.wk, &l.wv, &l.wo, &l.gate, &l.up, &l.down})
+            if (w->layout != BRASA_LAYOUT_TILED || w->qtype != BRASA_Q4_0) return false;
+    int coop = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device) != cudaSuccess || !coop) return false;
+    return true;
+}
+
+void brasa_token_program_free(brasa_token_program *p) {
+    if (!p) return;
+    for (void *d : p->device) cudaFree(d);
+    delete p;
+}
+
+int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, brasa_token_program **out) {
+    BRASA_REQUIRE(ctx, out && brasa_token_program_supported(ctx, m), "token program: model shape not supported");
+    std::unique_ptr<brasa_token_program, void (*)(brasa_token_program *)> prog(new brasa_token_program, brasa_token_program_free);
+    prog->ctx = ctx;
+    prog->kv = m.kv;
+    const uint32_t G = (uint32_t)ctx->sm_count;
+    prog->grid = G;
+    const uint32_t H = m.hidden, QD = m.heads * 128, KD = m.kv_heads * 128, F = m.ffn;
+    const uint32_t C = attn_chunk(m.kv), max_chunks = (m.cache_positions + C - 1) / C;
+
+    auto dev_alloc = [&](size_t bytes, void **ptr) -> int32_t {
+        BRASA_CUDA(ctx, cudaMalloc(ptr, bytes));
+        prog->device.push_back(*ptr);
+        return brasa_check_cuda(ctx, cudaMemset(*ptr, 0, bytes), "cudaMemset");
+    };
+    // activation vectors as {value, epoch} words
+    unsigned long long *xa, *xb, *qkv, *attn, *act, *partials, *cand;
+    const size_t ll_words = (size_t)2 * H + (QD + 2 * KD) + QD + F + (size_t)m.heads * max_chunks * 130 + 2 * G;
+    void *ll_base;
+    BRASA_TRY(dev_alloc(ll_words * 8, &ll_base));
+    xa = (unsigned long long *)ll_base;
+    xb = xa + H;
+    qkv = xb + H;
+    attn = qkv + (QD + 2 * KD);
+    act = attn + QD;
+    partials = act + F;
+    cand = partials + (size_t)m.heads * max_chunks * 130;
+
+    // ---- the operations ----
+    std::vector<TokOp> ops;
+    auto gemv_op = [&](uint32_t nmat, const brasa_qmatrix *w, uint32_t epilogue, bool scaled, const float *normw, const unsigned long long *in,
+                       int in_op, unsigned long long *outp, bool save_resid) {
+        TokOp o{};
+        o.type = OP_GEMV;
+        o.qtype = (uint32_t)w[0].qtype;
+        o.cols = w[0].cols;
+        o.nmat = nmat;
+        o.total_rows = 0;
+        for (uint32_t i = 0; i < nmat; ++i) {
+            o.rows[i] = w[i].rows;
+            o.w[i] = arg_ptr(w[i].data);
+            o.total_rows += w[i].rows;
+        }
+        if (epilogue == EPI_SWIGLU) o.total_rows = w[0].rows;
+        o.epilogue = epilogue;
+        o.scaled = scaled ? 1 : 0;
+        uint32_t S = 1;
+        gemv_shape(w[0].qtype, o.cols, &S, &o.nact);
+        for (o.log2S = 0; (1u << o.log2S) < S; ++o.log2S) {}
+        o.in_kind = in_op < 0 ? IN_EMBED : IN_LL;
+        o.in_op = in_op < 0 ? 0 : (uint32_t)in_op;
+        o.save_resid = save_resid ? 1 : 0;
+        o.eps = m.eps;
+        o.normw = normw;
+        o.in = in;
+        o.out = outp;
+        ops.push_back(o);
+        return (int)ops.size() - 1;
+    };
+    int x_op = -1;  // operation that produced the current residual stream (-1: the embedding row)
+    for (const brasa_token_layer &l : m.layers) {
+        brasa_qmatrix wqkv[3] = {l.wq, l.wk, l.wv};
+        BRASA_REQUIRE(ctx, l.wq.rows == QD && l.wk.rows == KD && l.wv.rows == KD && l.wq.cols == H && l.wo.rows == H && l.wo.cols == QD &&
+                               l.gate.rows == F && l.up.rows == F && l.gate.cols == H && l.down.rows == H && l.down.cols == F,
+                      "token program: unexpected matrix shape");
+        int qkv_op = gemv_op(3, wqkv, EPI_SCALE, true, l.attn_norm, xa, x_op, qkv, true);
+        TokOp a{};
+        a.type = OP_ATTN;
+        a.in_op = (uint32_t)qkv_op;
+        a.eps = m.eps;
+        a.in = qkv;
+        a.out = attn;
+        a.q_norm = l.q_norm;
+        a.k_norm = l.k_norm;
+        a.kc = l.kc;
+        a.vc = l.vc;
+        ops.push_back(a);
+        int attn_op = (int)ops.size() - 1;
+        int o_op = gemv_op(1, &l.wo, EPI_RESID, false, nullptr, attn, attn_op, xb, false);
+        brasa_qmatrix wgu[2] = {l.gate, l.up};
+        int gu_op = gemv_op(2, wgu, EPI_SWIGLU, true, l.ffn_norm, xb, o_op, act, true);
+        x_op = gemv_op(1, &l.down, EPI_RESID, false, nullptr, act, gu_op, xa, false);
+    }
+    BRASA_REQUIRE(ctx, m.head.rows == m.vocab && m.head.cols == H, "token program: unexpected lm_head shape");
+    gemv_op(1, &m.head, EPI_LOGITS, true, m.final_norm, xa, x_op, nullptr, false);
+    BRASA_REQUIRE(ctx, ops.size() + 2 < EPOCH_SPAN, "token program: too many operations");
+
+    // ---- every block's slot list, in the order the kernel consumes it, and its rows of every operation ----
+    std::vector<SlotDesc> slots;
+    std::vector<uint32_t> slot_begin(G + 1, 0);
+    std::vector<uint4> block_ops(ops.size() * G, make_uint4(0, 0, 0, 0));
+    uint32_t part_floats = 0, max_cols = 0, max_op_slots = 0;
+    for (uint32_t b = 0; b < G; ++b) {
+        slot_begin[b] = (uint32_t)slots.size();
+        for (size_t oi = 0; oi < ops.size(); ++oi) {
+            const TokOp &o = ops[oi];
+            if (o.type != OP_GEMV) continue;
+            const bool swiglu = o.epilogue == EPI_SWIGLU;
+            uint32_t r0, r1, first[3], nrows[3];
+            block_rows(o.total_rows, o.nmat, o.rows, swiglu, b, G, r0, r1, first, nrows);
+            BRASA_REQUIRE(ctx, nrows[0] < 65536 && nrows[1] < 65536, "token program: too many rows per block");
+            block_ops[oi * G + b] = make_uint4(r0, nrows[0] | (nrows[1] << 16), nrows[2], 0);
+            const uint32_t S = 1u << o.log2S, RPS = TK_WARPS / S * R / 2, row_bytes = tiled_row_bytes((int)o.qtype, o.cols);
+            uint32_t items = 0, op_slots = 0;
+            for (int i = 0; i < 3; ++i) {
+                for (uint32_t f = 0; f < nrows[i]; f += RPS) {
+                    uint32_t n = std::min(RPS, nrows[i] - f);
+                    slots.push_back(SlotDesc{o.w[i] + (size_t)(first[i] + f) * row_bytes, n * row_bytes, 0});
+                    ++op_slots;
+                }
+                items += nrows[i];
+            }
+            part_floats = std::max(part_floats, items * S);
+            max_cols = std::max(max_cols, o.cols);
+            max_op_slots = std::max(max_op_slots, op_slots);
+        }
+    }
+    slot_begin[G] = (uint32_t)slots.size();
+
+    TokParams &p = prog->params;
+    void *d_ops, *d_slots, *d_begin, *d_bops;
+    BRASA_TRY(dev_alloc(block_ops.size() * sizeof(uint4), &d_bops));
+    BRASA_CUDA(ctx, cudaMemcpy(d_bops, block_ops.data(), block_ops.size() * sizeof(uint4), cudaMemcpyHostToDevice));
+    BRASA_TRY(dev_alloc(ops.size() * sizeof(TokOp), &d_ops));
+    BRASA_TRY(dev_alloc(std::max<size_t>(slots.size(), 1) * sizeof(SlotDesc), &d_slots));
+    BRASA_TRY(dev_alloc(slot_begin.size() * 4, &d_begin));
+    BRASA_CUDA(ctx, cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(TokOp), cudaMemcpyHostToDevice));
+    BRASA_CUDA(ctx, cudaMemcpy(d_slots, slots.data(), slots.size() * sizeof(SlotDesc), cudaMemcpyHostToDevice));
+    BRASA_CUDA(ctx, cudaMemcpy(d_begin, slot_begin.data(), slot_begin.size() * 4, cudaMemcpyHostToDevice));
+    p.ops = (const TokOp *)d_ops;
+    p.nops = (uint32_t)ops.size();
+    p.slots = (const SlotDesc *)d_slots;
+    p.slot_begin = (const uint32_t *)d_begin;
+    p.block_ops = (const uint4 *)d_bops;
+
+    // ---- shared memory ----
+    const size_t attn_bytes = (size_t)2 * C * attn_row_stride(m.kv) + (8 * 128 + 8 * C + 2 * max_chunks) * 4;
+    p.xf_bytes = (uint32_t)((std::max<size_t>((size_t)max_cols * 4, attn_bytes) + 127) / 128 * 128);
+    p.part_floats = (part_floats + 3) & ~3u;
+    p.resid_floats = ((H + G - 1) / G + 4) & ~3u;
+    p.sdesc_n = max_op_slots + L2_AHEAD;
+    const size_t fixed = p.xf_bytes + (size_t)(p.part_floats + p.resid_floats) * 4 + (size_t)p.sdesc_n * 16 + 48 * 4 + 2 * OPS_WORDS * 4 + 16;
+    BRASA_REQUIRE(ctx, fixed + 2 * (SLOT_CAP + 12) + 1024 <= ctx->smem_optin, "token program: the model's vectors do not fit shared memory");
+    uint32_t nslot = (uint32_t)((ctx->smem_optin - 1024 - fixed) / (SLOT_CAP + 12));
+    nslot &= ~1u;  // even: a ring slot always serves the same half of the warps
+    p.nslot = nslot;
+    prog->smem = (size_t)nslot * (SLOT_CAP + 12) + fixed;
+
+    p.state = m.state;
+    p.ids = m.ids;
+    p.next_id = m.next_id;
+    p.out_ids = m.out_ids;
+    p.out_cap = m.out_cap;
+    p.embed = arg_ptr(m.embed.data);
+    p.vocab = m.vocab;
+    p.hidden = H;
+    p.heads = m.heads;
+    p.kv_heads = m.kv_heads;
+    p.max_chunks = max_chunks;
+    p.cos_t = m.cos_t;
+    p.sin_t = m.sin_t;
+    p.logits = m.logits;
+    p.cand = cand;
+    p.partials = partials;
+    p.attn_scale = 1.0f / sqrtf(128.0f);
+    p.status = ctx->status;
+    p.trace = ctx->gemv_trace;
+    {
+        const char *env = getenv("BRASA_TRACE_OP");
+        p.trace_op = env ? (uint32_t)atoi(env) : 5;
+    }
+
+#define SET_ATTR(KVT) BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_token_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prog->smem))
+    if (m.kv == BRASA_KV_F32) SET_ATTR(BRASA_KV_F32);
+    else if (m.kv == BRASA_KV_F16) SET_ATTR(BRASA_KV_F16);
+    else SET_ATTR(BRASA_KV_Q8_0);
+#undef SET_ATTR
+    int per_sm = 0;
+    const void *fn = m.kv == BRASA_KV_F32 ? (const void *)decode_token_kernel<BRASA_KV_F32>
+                     : m.kv == BRASA_KV_F16 ? (const void *)decode_token_kernel<BRASA_KV_F16> : (const void *)decode_token_kernel<BRASA_KV_Q8_0>;
+    BRASA_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, TK_THREADS, prog->smem));
+    BRASA_REQUIRE(ctx, per_sm >= 1, "token program: the kernel does not fit an SM");
+    *out = prog.release();
+    return BRASA_OK;
+}
+
+int32_t brasa_token_program_launch(brasa_cmd *cmd, brasa_token_program *prog) {
+    brasa_ctx *ctx = cmd->ctx;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(prog->grid);
+    cfg.blockDim = dim3(TK_THREADS);
+    cfg.dynamicSmemBytes = prog->smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // every block resident at once: blocks wait for one another's outputs
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (prog->kv == BRASA_KV_F32) BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_token_kernel<BRASA_KV_F32>, prog->params));
+    else if (prog->kv == BRASA_KV_F16) BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_token_kernel<BRASA_KV_F16>, prog->params));
+    else BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, decode_token_kernel<BRASA_KV_Q8_0>, prog->params));
+    return brasa_post_launch(cmd, "decode_token");
+}

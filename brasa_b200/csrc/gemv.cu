@@ -24,10 +24,12 @@
 #include <type_traits>
 
 #include "brasa_internal.h"
+#include "gemv_device.cuh"
+
+using namespace brasa_dev;
 
 namespace {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait rounds before a wait gives up
 constexpr int GEMV_WARPS = 16;              // consumer warps per block; column slices per row divide it
 
 enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2 };
@@ -62,128 +64,7 @@ struct GemvParams {
     uint32_t pf_nmat, pf_total_rows, pf_row_bytes, pf_swiglu;
 };
 
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 #define TRACE(i) do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[i] = gtime(); } while (0)
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity. False when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
-    int r;
-    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // unsigned codes x signed bytes
-    int r;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t c) {  // (a & b) | c
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-
-// The lane's x values of one half block in fixed point: quad j (4 values) x byte plane d, the sum of
-// the 16 integers, and the power-of-two step.
-struct XFixed {
-    uint32_t d[4][3];
-    int total;
-    float step;
-};
-
-// sum over the 16 weights of a half block of (code - bias) * X, as an integer.
-// Quads: 0 = low nibbles of word x, 1 = high nibbles of word x, 2 and 3 likewise for word y.
-template <int QT>
-__device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const XFixed &x) {
-    uint32_t a[4];
-    a[0] = codes.x & 0x0F0F0F0Fu;
-    a[1] = (codes.x >> 4) & 0x0F0F0F0Fu;
-    a[2] = codes.y & 0x0F0F0F0Fu;
-    a[3] = (codes.y >> 4) & 0x0F0F0F0Fu;
-    if (QT == BRASA_Q6_0) {  // the two high bits of each code, stored so a shift puts them at bits 4-5 of its byte
-        a[0] = lop_and_or(hb, 0x30303030u, a[0]);
-        a[1] = lop_and_or(hb >> 2, 0x30303030u, a[1]);
-        a[2] = lop_and_or(hb << 2, 0x30303030u, a[2]);
-        a[3] = lop_and_or(hb << 4, 0x30303030u, a[3]);
-    }
-    int s0 = 0, s1 = 0, s2 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        s0 = dp4a_uu(a[j], x.d[j][0], s0);
-        s1 = dp4a_uu(a[j], x.d[j][1], s1);
-        s2 = dp4a_us(a[j], x.d[j][2], s2);
-    }
-    constexpr int BIAS = QT == BRASA_Q4_0 ? 8 : 32;
-    return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
-}
-
-// Dot products of two rows of a slot with the lane's share of x (row_b == row_a when there is only one).
-// After folding across lanes, lane 0 holds the sum of row a and lane 8 the sum of row b. The body is kept
-// small on purpose: a fully unrolled four-row version ran out of instruction cache.
-template <int QT, int N>
-__device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_t *row_b, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
-                                              uint32_t hi_off, uint32_t sc_off, int lane) {
-    float acc_a = 0.0f, acc_b = 0.0f;
-    // straight-line code: lanes past the end of the row read the last half block and have step 0
-#pragma unroll
-    for (int it = 0; it < N; ++it) {
-        const uint32_t hbi = min((slice * N + it) * 32 + lane, nhb - 1);
-        uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
-        uint2 cb = *reinterpret_cast<const uint2 *>(row_b + hbi * 8);
-        uint32_t ha = 0, hb = 0;
-        if (QT == BRASA_Q6_0) {
-            ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
-            hb = *reinterpret_cast<const uint32_t *>(row_b + hi_off + hbi * 4);
-        }
-        float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
-        float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
-        int sa = half_block_idot<QT>(ca, ha, xr[it]);
-        int sb = half_block_idot<QT>(cb, hb, xr[it]);
-        acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
-        acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
-    }
-    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 16);
-    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 16);
-    const bool hi3 = lane & 8;
-    float z = hi3 ? acc_b : acc_a, z_send = hi3 ? acc_a : acc_b;
-    z += __shfl_xor_sync(0xffffffffu, z_send, 8);
-    z += __shfl_xor_sync(0xffffffffu, z, 4);
-    z += __shfl_xor_sync(0xffffffffu, z, 2);
-    z += __shfl_xor_sync(0xffffffffu, z, 1);
-    return z;
-}
-
 // N = half blocks per lane and slice (the lane's x registers hold 14 N words).
 constexpr int R = 2;         // rows a warp works on at a time
 constexpr int MAX_CONV = 3;  // half blocks of x a thread converts with all its loads in flight
@@ -296,44 +177,7 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
     // ---- x to 22-bit fixed point, once per block: thread t converts half blocks t, t + CT, ... into records ----
     // quad j of a half block: the values that meet the low / high nibbles of code word 0 (j = 0, 1) and 1 (j = 2, 3)
     float ssq = 0.0f;
-    auto convert = [&](uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) {
-        float v[4][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}, {q2.x, q2.y, q2.z, q2.w}, {q3.x, q3.y, q3.z, q3.w}};
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[j][e]));
-        // step = 2^(exponent(amax) - 20): every |x| / step is below 2^21; zero (or denormal) groups get step 0
-        uint32_t ebits = __float_as_uint(amax) & 0x7F800000u;
-        bool live = ebits > (21u << 23) && ebits < 0x7F800000u;
-        // infinities and NaNs are not representable: their group's step carries them into the result
-        float step = live ? __uint_as_float(ebits - (20u << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
-        float inv = live ? __uint_as_float((254u << 23) - (ebits - (20u << 23))) : 0.0f;  // 1 / step, exact
-        int total = 0;
-        uint32_t rec[16];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int X[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                X[e] = __float2int_rn(v[j][e] * inv);
-                total += X[e];
-            }
-            // byte planes of the four integers: byte k of every X gathered into one word
-            uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);
-            uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
-            rec[3 * j + 0] = __byte_perm(lo01, lo23, 0x5410);
-            rec[3 * j + 1] = __byte_perm(lo01, lo23, 0x7632);
-            rec[3 * j + 2] = __byte_perm(hi01, hi23, 0x5410);
-        }
-        rec[12] = (uint32_t)total;
-        rec[13] = __float_as_uint(step);
-        rec[14] = rec[15] = 0;
-        // 16-byte chunk c of record h is stored at chunk c ^ ((h >> 1) & 3): conflict-free for consecutive h
-        const uint32_t sw = (hbi >> 1) & 3;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) xf[hbi * 4 + (c ^ sw)] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
-    };
+    auto convert = [&](uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) { x_half_block_to_fixed(xf, hbi, q0, q1, q2, q3); };
     {
         float4 xq[MAX_CONV][4];
 #pragma unroll
@@ -435,7 +279,10 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
 #pragma unroll
     for (int sgi = 0; sgi < 3; ++sgi) {
         const uint32_t nslots_seg = (seg_rows[sgi] + RPS - 1) / RPS;
-        for (uint32_t ks = my_sub; ks < nslots_seg; ks += split) {
+        // Slots go to the two halves of the warps by the parity of their index in the block's whole list, and a reused
+        // ring has an even number of slots: a ring slot is then always consumed by the same warps, which wait for every
+        // one of its uses (a warp that skipped a use could mistake the previous phase for the one it waits for).
+        for (uint32_t ks = split == 2 ? ((my_sub + seg_slot0[sgi]) & 1u) : 0u; ks < nslots_seg; ks += split) {
             const uint32_t k = seg_slot0[sgi] + ks, s = k % p.nslot;
             if (!mbar_wait(&full[s], (k / p.nslot) & 1)) {
                 // give up on the remaining slots but still meet the other warps at the barrier below
@@ -636,6 +483,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     size_t budget = fixed + (size_t)need_slots * (slot_bytes + 16) <= cap ? cap - fixed : ctx->smem_optin - fixed - 1024;
     BRASA_REQUIRE(ctx, fixed + slot_bytes + 1024 <= ctx->smem_optin, "gemv: %u columns do not fit shared memory", p.cols);
     uint32_t nslot = (uint32_t)std::min<size_t>(need_slots, budget / (slot_bytes + 16));
+    if (nslot < need_slots && nslot > 1) nslot &= ~1u;  // reused ring: even, see the slot loop of the kernel
     BRASA_REQUIRE(ctx, nslot >= 1, "gemv: no room for a ring slot");
     p.nslot = nslot;
     size_t smem = (size_t)nslot * slot_bytes + fixed + (size_t)nslot * 16;

@@ -1,0 +1,174 @@
+// Device-side pieces shared by the GEMV kernel and the whole-token decode kernel: mbarrier and bulk-copy wrappers,
+// the fixed-point form of the input vector and the exact integer dot product of a half block (see gemv.cu).
+#pragma once
+#include "brasa_internal.h"
+
+namespace brasa_dev {
+
+constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait rounds before a wait gives up
+
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity. False when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    int r;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // unsigned codes x signed bytes
+    int r;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t c) {  // (a & b) | c
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+// The lane's x values of one half block in fixed point: quad j (4 values) x byte plane d, the sum of
+// the 16 integers, and the power-of-two step.
+struct XFixed {
+    uint32_t d[4][3];
+    int total;
+    float step;
+};
+
+// sum over the 16 weights of a half block of (code - bias) * X, as an integer.
+// Quads: 0 = low nibbles of word x, 1 = high nibbles of word x, 2 and 3 likewise for word y.
+template <int QT>
+__device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const XFixed &x) {
+    uint32_t a[4];
+    a[0] = codes.x & 0x0F0F0F0Fu;
+    a[1] = (codes.x >> 4) & 0x0F0F0F0Fu;
+    a[2] = codes.y & 0x0F0F0F0Fu;
+    a[3] = (codes.y >> 4) & 0x0F0F0F0Fu;
+    if (QT == BRASA_Q6_0) {  // the two high bits of each code, stored so a shift puts them at bits 4-5 of its byte
+        a[0] = lop_and_or(hb, 0x30303030u, a[0]);
+        a[1] = lop_and_or(hb >> 2, 0x30303030u, a[1]);
+        a[2] = lop_and_or(hb << 2, 0x30303030u, a[2]);
+        a[3] = lop_and_or(hb << 4, 0x30303030u, a[3]);
+    }
+    int s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        s0 = dp4a_uu(a[j], x.d[j][0], s0);
+        s1 = dp4a_uu(a[j], x.d[j][1], s1);
+        s2 = dp4a_us(a[j], x.d[j][2], s2);
+    }
+    constexpr int BIAS = QT == BRASA_Q4_0 ? 8 : 32;
+    return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
+}
+
+// Dot products of two rows of a slot with the lane's share of x (row_b == row_a when there is only one).
+// After folding across lanes, lane 0 holds the sum of row a and lane 8 the sum of row b. The body is kept
+// small on purpose: a fully unrolled four-row version ran out of instruction cache.
+template <int QT, int N>
+__device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_t *row_b, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
+                                              uint32_t hi_off, uint32_t sc_off, int lane, int nact = N) {
+    float acc_a = 0.0f, acc_b = 0.0f;
+    // straight-line code: lanes past the end of the row read the last half block and have step 0
+#pragma unroll
+    for (int it = 0; it < N; ++it) {
+        if (it < nact) {  // nact < N: a narrower input in a kernel built for N (uniform across the block)
+            const uint32_t hbi = min((slice * nact + it) * 32 + lane, nhb - 1);
+            uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
+            uint2 cb = *reinterpret_cast<const uint2 *>(row_b + hbi * 8);
+            uint32_t ha = 0, hb = 0;
+            if (QT == BRASA_Q6_0) {
+                ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
+                hb = *reinterpret_cast<const uint32_t *>(row_b + hi_off + hbi * 4);
+            }
+            float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
+            float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
+            int sa = half_block_idot<QT>(ca, ha, xr[it]);
+            int sb = half_block_idot<QT>(cb, hb, xr[it]);
+            acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+            acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
+        }
+    }
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 16);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 16);
+    const bool hi3 = lane & 8;
+    float z = hi3 ? acc_b : acc_a, z_send = hi3 ? acc_a : acc_b;
+    z += __shfl_xor_sync(0xffffffffu, z_send, 8);
+    z += __shfl_xor_sync(0xffffffffu, z, 4);
+    z += __shfl_xor_sync(0xffffffffu, z, 2);
+    z += __shfl_xor_sync(0xffffffffu, z, 1);
+    return z;
+}
+
+// x to 22-bit fixed point: one half block (16 values, as the four quads that meet the low / high nibbles of code
+// word 0 and of code word 1) becomes a 64-byte record in xf: 12 byte-plane words, the sum of the integers, the step.
+__device__ __forceinline__ void x_half_block_to_fixed(uint4 *xf, uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) {
+    float v[4][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}, {q2.x, q2.y, q2.z, q2.w}, {q3.x, q3.y, q3.z, q3.w}};
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[j][e]));
+    // step = 2^(exponent(amax) - 20): every |x| / step is below 2^21; zero (or denormal) groups get step 0
+    uint32_t ebits = __float_as_uint(amax) & 0x7F800000u;
+    bool live = ebits > (21u << 23) && ebits < 0x7F800000u;
+    // infinities and NaNs are not representable: their group's step carries them into the result
+    float step = live ? __uint_as_float(ebits - (20u << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
+    float inv = live ? __uint_as_float((254u << 23) - (ebits - (20u << 23))) : 0.0f;  // 1 / step, exact
+    int total = 0;
+    uint32_t rec[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int X[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            X[e] = __float2int_rn(v[j][e] * inv);
+            total += X[e];
+        }
+        // byte planes of the four integers: byte k of every X gathered into one word
+        uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);
+        uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
+        rec[3 * j + 0] = __byte_perm(lo01, lo23, 0x5410);
+        rec[3 * j + 1] = __byte_perm(lo01, lo23, 0x7632);
+        rec[3 * j + 2] = __byte_perm(hi01, hi23, 0x5410);
+    }
+    rec[12] = (uint32_t)total;
+    rec[13] = __float_as_uint(step);
+    rec[14] = rec[15] = 0;
+    // 16-byte chunk c of record h is stored at chunk c ^ ((h >> 1) & 3): conflict-free for consecutive h
+    const uint32_t sw = (hbi >> 1) & 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) xf[hbi * 4 + (c ^ sw)] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
+}
+
+}  // namespace brasa_dev

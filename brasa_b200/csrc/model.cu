@@ -13,6 +13,7 @@
 #include <chrono>
 
 #include "brasa_internal.h"
+#include "decode_token.h"
 #include "host_util.h"
 
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
@@ -61,6 +62,8 @@ struct brasa_model {
               *gate = nullptr, *up = nullptr, *ids = nullptr, *norm_out = nullptr, *ss = nullptr, *partials = nullptr, *logits = nullptr,
               *next_id = nullptr, *out_ids = nullptr, *dev_state = nullptr;  // dev_state: u32 pos, out_count, attention counters
     brasa_graph *decode_graph = nullptr;  // one decode step: embed .. lm_head, argmax, advance
+    brasa_token_program *token_prog = nullptr;  // the same step as one persistent kernel, when the shapes allow
+    bool token_prog_tried = false;
     uint64_t partials_len = 0;
     brasa_allocated alloc{};
     std::vector<brasa_buf *> owned;
@@ -292,9 +295,43 @@ int32_t set_position(brasa_model *m, uint32_t pos0) {
     return brasa_check_cuda(m->ctx, cudaMemcpyAsync(m->dev_state->ptr, &pos0, 4, cudaMemcpyHostToDevice, m->ctx->stream), "position upload");
 }
 
+// Describes the model to the whole-token kernel and builds its program, once. Leaves token_prog null when the
+// shapes do not fit or BRASA_TOKEN_KERNEL=0 asks for the kernel-per-operation path.
+int32_t make_token_program(brasa_model *m) {
+    m->token_prog_tried = true;
+    if (!m->ctx->token_kernel) return BRASA_OK;
+    const brasa_config &c = m->cfg;
+    brasa_token_model d{};
+    d.hidden = c.hidden; d.heads = c.heads; d.kv_heads = c.kv_heads; d.head_dim = c.head_dim; d.ffn = c.ffn; d.vocab = c.vocab;
+    d.cache_positions = m->cap;
+    d.kv = m->limits.kv;
+    d.eps = c.eps;
+    for (uint32_t li = 0; li < c.layers; ++li) {
+        Layer &l = m->layers[li];
+        KvView all = kv_at(m, li, 0);
+        d.layers.push_back(brasa_token_layer{l.wq.q, l.wk.q, l.wv.q, l.wo.q, l.gate.q, l.up.q, l.down.q, F(l.attn_norm), F(l.q_norm), F(l.k_norm),
+                                             F(l.ffn_norm), arg_ptr(all.k), arg_ptr(all.v)});
+    }
+    d.embed = m->embed.q;
+    d.head = m->head.q;
+    d.final_norm = F(m->final_norm);
+    d.cos_t = F(m->rope_cos);
+    d.sin_t = F(m->rope_sin);
+    d.state = (uint32_t *)m->dev_state->ptr;
+    d.ids = (uint32_t *)m->ids->ptr;
+    d.next_id = (uint32_t *)m->next_id->ptr;
+    d.out_ids = (uint32_t *)m->out_ids->ptr;
+    d.out_cap = m->limits.ctx;
+    d.logits = F(m->logits);
+    if (!brasa_token_program_supported(m->ctx, d)) return BRASA_OK;
+    return brasa_token_program_create(m->ctx, d, &m->token_prog);
+}
+
 // pos0 == UINT32_MAX keeps the position the device already holds (device-resident loop).
 int32_t decode_step(brasa_model *m, brasa_cmd *cmd, uint32_t pos0) {
     if (pos0 != UINT32_MAX) BRASA_TRY(set_position(m, pos0));
+    if (!m->token_prog_tried) BRASA_TRY(make_token_program(m));
+    if (m->token_prog) return brasa_token_program_launch(cmd, m->token_prog);
     if (m->decode_graph) return brasa_graph_launch(cmd, m->decode_graph);
     BRASA_TRY(decode_step_kernels(m, cmd));
     if (m->ctx->graphs && !m->ctx->capturing) {
@@ -349,6 +386,7 @@ int32_t brasa_model_shape_from_file(const char *path, brasa_model_shape *shape, 
 void brasa_model_free(brasa_model *m) {
     if (!m) return;
     if (m->decode_graph) brasa_graph_free(m->decode_graph);
+    brasa_token_program_free(m->token_prog);
     for (brasa_buf *b : m->owned) brasa_buf_free(b);
     if (m->pinned_id) cudaFreeHost(m->pinned_id);
     delete m;

@@ -88,6 +88,9 @@ uint64_t brasa_ctx_launch_count(brasa_ctx *ctx);
  * vector in shared memory, fixed-point conversion done, registers loaded, first weight slot ready, all rows
  * done, exit. */
 int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]);
+/* The first n (<= 512) words of the same buffer; the whole-token decode kernel writes 8 time stamps per operation
+ * for 16 operations of block 0 from word 16 on (BRASA_TRACE_OP picks the first operation). */
+int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n);
 /* cudaStream_t of the context, for callers that order their own work (NCCL, torch) against it. */
 void *brasa_ctx_stream(brasa_ctx *ctx);
 
