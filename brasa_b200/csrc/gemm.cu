@@ -3,8 +3,14 @@
 // f16 as f16(f32(d) * (q - bias)) and products are accumulated in f32 (matmul_tiled.metal:35-53).
 // Precision F32 keeps both in f32.
 //
-// This file holds the warp-MMA version (mma.sync m16n8k16), valid for every shape.
+// This file holds the warp-MMA version (mma.sync m16n8k16), valid for every shape, and the exact f32 version; tiled q4_0
+// matrices whose rows are a multiple of 128 go to the tcgen05 kernel of gemm_tc.cu (BRASA_GEMM_TC=0 keeps them here).
+#include <stdlib.h>
+
 #include "brasa_internal.h"
+
+bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *y, uint32_t tokens);
 
 namespace {
 
@@ -179,6 +185,9 @@ int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_ar
     BRASA_REQUIRE(ctx, arg_fits(x, (uint64_t)tokens * w.cols * (half_in ? 2 : 4)) && arg_fits(y, (uint64_t)tokens * w.rows * 4), "gemm: x or y too small");
     BRASA_REQUIRE(ctx, x.offset % 16 == 0 && y.offset % 8 == 0, "gemm: misaligned x or y");
     if (tokens == 0) return BRASA_OK;
+    static const bool tc_on = [] { const char *e = getenv("BRASA_GEMM_TC"); return !(e && e[0] == '0'); }();
+    if (half_in && tc_on && tokens > 8 && brasa_gemm_tc_supported(w, tokens))
+        return brasa_gemm_tc_launch(cmd, w, (const __half *)arg_ptr(x), (float *)arg_ptr(y), tokens);
     WView v{arg_ptr(w.data), w.qtype, w.layout, w.rows, w.cols};
     dim3 grid((w.rows + TN - 1) / TN, (tokens + TM - 1) / TM);
     if (half_in) gemm_f16_kernel<<<grid, 128, 0, ctx->stream>>>(v, (const __half *)arg_ptr(x), (float *)arg_ptr(y), tokens);

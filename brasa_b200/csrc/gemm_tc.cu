@@ -1,0 +1,312 @@
+// Prefill GEMM on the 5th-generation tensor cores: Y[t, :] = W X[t, :] for many tokens, W q4_0 in the tiled layout,
+// X f16, f32 accumulation (crates/kernels/src/lib.rs:842-970 and matmul_tiled.metal:35-53: each dequantised weight
+// is rounded to f16 as f16(f32(d) * (q - 8)) before it meets the f16 activation).
+//
+// One CTA computes a [MT x 128 tokens] x [128 weight rows] block of Y with tcgen05.mma (M = 128 tokens, N = 128
+// rows, K = 16 per instruction), accumulating in tensor memory (MT x 128 columns of 128 lanes), K in stages of 64:
+//   * warp 0, one lane: TMA. The X tile of a stage (MT boxes of 128 tokens x 64 halves) arrives by
+//     cp.async.bulk.tensor with the 128-byte swizzle; tokens past the end read as zeros.
+//   * warps 4-7: weights. Each thread owns one weight row of the CTA: it reads the row's 32 code bytes and 2 scales
+//     of the stage, turns nibbles into f16 with exact arithmetic (0x6400 | q is the half 1024 + q; minus 1032;
+//     times d in f16 rounds the exact product once, as the reference's f32 product does) and writes the row in the
+//     same swizzled K-major form the TMA produces. The tensor core reads both operands from shared memory.
+//   * warp 1, one lane: tcgen05.mma for the stage, then tcgen05.commit to hand the stage back.
+//   * after the last stage warps 4-7 read the accumulators (tcgen05.ld, one token per lane) and store Y.
+// Every wait is bounded: a wait that runs out raises the context's status word and a CTA-wide flag, every role
+// leaves its loop, tensor memory is freed and the kernel returns.
+#include <cuda.h>
+
+#include "brasa_internal.h"
+#include "gemv_device.cuh"
+
+using namespace brasa_dev;
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr uint32_t A_TILE = BM * BK * 2, B_TILE = BN * BK * 2;  // 16 KB each
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ __half2 u2h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+// two nibbles (already in the low 4 bits of each half lane) -> f16(d * (q - 8)) for both
+__device__ __forceinline__ uint32_t deq2(uint32_t lanes, __half2 bias, __half2 d2) {
+    return h22u(__hmul2(__hsub2(u2h2((lanes & 0x000F000Fu) | 0x64006400u), bias), d2));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+struct GemmTcParams {
+    const uint8_t *w;
+    float *y;
+    uint32_t rows, cols, tokens, stages;
+    uint32_t *status;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the dynamic shared memory base is only 16-byte aligned by contract: round up to the swizzle atom
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t stage_bytes = MT * A_TILE + B_TILE;
+    __shared__ uint64_t full_x[8], full_w[8], empty[8], acc_full;
+    __shared__ uint32_t tmem_base_s, abort_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n0 = blockIdx.x * BN, tok0 = blockIdx.y * (MT * BM);
+    const uint32_t nk = p.cols / BK, NS = p.stages;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbar_init(&full_x[s], 1);
+            mbar_init(&full_w[s], 4);  // one arrival per weight warp
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&acc_full, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory for the accumulators: MT x 128 columns
+        uint32_t ncols = MT * BN;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    volatile uint32_t *abort_flag = &abort_s;
+
+    // bounded wait shared by every role; false when it gave up (or another role did)
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+        for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+            if (mbar_try(bar, parity)) return true;
+            if (*abort_flag) return false;
+        }
+        atomicExch(p.status, 4u);
+        *abort_flag = 1;
+        return false;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t issued = 0;
+            for (uint32_t k = 0; k < nk; ++k) {
+                const uint32_t s = k % NS;
+                if (k >= NS && !wait(&empty[s], ((k / NS) - 1) & 1)) break;
+                uint8_t *dst = smem + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full_x[s], MT * A_TILE);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     smem_u32(dst + mt * A_TILE)),
+                                 "l"(&tmap_x), "r"((int)(k * BK)), "r"((int)(tok0 + mt * BM)), "r"(smem_u32(&full_x[s]))
+                                 : "memory");
+                }
+                issued = k + 1;
+            }
+            if (*abort_flag) {  // leaving early: let the copies already in flight land before the CTA exits
+                for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; ++k)
+                    for (uint32_t it = 0; it < TC_WAIT_LIMIT && !mbar_try(&full_x[k % NS], (k / NS) & 1); ++it) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D f32, A and B f16, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (uint32_t k = 0; k < nk && ok; ++k) {
+                const uint32_t s = k % NS, ph = (k / NS) & 1;
+                ok = wait(&full_x[s], ph) && wait(&full_w[s], ph);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = smem_u32(smem + (size_t)s * stage_bytes), b0 = a0 + MT * A_TILE;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        const uint64_t da = smem_desc(a0 + mt * A_TILE + ks * 32), db = smem_desc(b0 + ks * 32);
+                        const uint32_t acc = (k > 0 || ks > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            ::"r"(tmem_base + mt * BN), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+                            : "memory");
+                    }
+                }
+                // the stage is free once these MMAs have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
+            }
+            if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&acc_full)) : "memory");
+        }
+    } else if (warp >= 4) {
+        // ---- weights: thread -> row n0 + dt of W; per stage two quantisation blocks (64 columns) ----
+        const uint32_t dt = tid - 128;
+        const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
+        const uint8_t *wrow = p.w + (size_t)(n0 + dt) * row_bytes;
+        const uint32_t r8 = dt & 7, row_off = (dt >> 3) * 1024 + r8 * 128;
+        uint4 c0 = *reinterpret_cast<const uint4 *>(wrow), c1 = *reinterpret_cast<const uint4 *>(wrow + 16);
+        uint32_t sc = *reinterpret_cast<const uint32_t *>(wrow + sc_off);
+        bool ok = true;
+        for (uint32_t k = 0; k < nk && ok; ++k) {
+            const uint32_t s = k % NS;
+            // next stage's codes and scales are in flight while this one is converted
+            uint4 n0c = c0, n1c = c1;
+            uint32_t nsc = sc;
+            if (k + 1 < nk) {
+                n0c = *reinterpret_cast<const uint4 *>(wrow + (size_t)(k + 1) * 32);
+                n1c = *reinterpret_cast<const uint4 *>(wrow + (size_t)(k + 1) * 32 + 16);
+                nsc = *reinterpret_cast<const uint32_t *>(wrow + sc_off + (size_t)(k + 1) * 4);
+            }
+            if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
+            if (!ok) break;
+            uint8_t *brow = smem + (size_t)s * stage_bytes + MT * A_TILE + row_off;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                const uint4 cw = blk == 0 ? c0 : c1;
+                const uint32_t dbits = blk == 0 ? (sc & 0xffffu) : (sc >> 16);
+                const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+                const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6408));  // 1032
+                const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
+                // elements 0..15 are the low nibbles of bytes 0..15, elements 16..31 the high nibbles
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t wv = words[i], wh = wv >> 4;
+                    const uint32_t p01 = __byte_perm(wv, 0, 0x4140), p23 = __byte_perm(wv, 0, 0x4342);  // bytes (0, 1) and (2, 3) into half lanes
+                    const uint32_t q01 = __byte_perm(wh, 0, 0x4140), q23 = __byte_perm(wh, 0, 0x4342);
+                    lo[2 * i] = deq2(p01, bias, d2);
+                    lo[2 * i + 1] = deq2(p23, bias, d2);
+                    hi[2 * i] = deq2(q01, bias, d2);
+                    hi[2 * i + 1] = deq2(q23, bias, d2);
+                }
+                // four 16-byte chunks of the row: columns 8c .. 8c + 7 of this block at chunk (4 blk + c) ^ (row & 7)
+                *reinterpret_cast<uint4 *>(brow + (((4 * blk + 0) ^ r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(brow + (((4 * blk + 1) ^ r8) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                *reinterpret_cast<uint4 *>(brow + (((4 * blk + 2) ^ r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(brow + (((4 * blk + 3) ^ r8) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes are read by the tensor core's proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_w[s]);
+            c0 = n0c;
+            c1 = n1c;
+            sc = nsc;
+        }
+        // ---- epilogue: lane = token inside a 128-token tile, columns = weight rows ----
+        ok = ok && wait(&acc_full, 0);
+        ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t q = warp & 3;  // the lane quarter of tensor memory this warp may read
+#pragma unroll 1
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t token = tok0 + mt * BM + q * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t v[16];
+                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BN + c;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (token < p.tokens) {
+                        float4 *dst = reinterpret_cast<float4 *>(p.y + (size_t)token * p.rows + n0 + c);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                                                 __uint_as_float(v[4 * i + 3]));
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t ncols = MT * BN;
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+
+}  // namespace
+
+// True when the tensor-core kernel takes this product (the caller falls back to the warp-MMA kernel otherwise).
+bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
+    return w.qtype == BRASA_Q4_0 && w.layout == BRASA_LAYOUT_TILED && w.rows % BN == 0 && w.cols % BK == 0 && w.cols >= BK && tokens > 0 &&
+           encode_tiled() != nullptr;
+}
+
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *y, uint32_t tokens) {
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(w, tokens), "gemm: shape not taken by the tensor-core kernel");
+    BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0, "gemm: misaligned x or y");
+    // X as a 2-D tensor [tokens][cols] of f16; a box is 64 columns x 128 tokens, 128-byte swizzle, zeros past the end
+    CUtensorMap tmap;
+    cuuint64_t dims[2] = {w.cols, tokens}, strides[1] = {(cuuint64_t)w.cols * 2};
+    cuuint32_t box[2] = {BK, BM}, estr[2] = {1, 1};
+    CUresult cr = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+
+    // tokens per CTA: as many 128-token tiles as keep the grid at about one CTA per SM or more (each CTA converts its
+    // 128 weight rows once, whatever its token count)
+    const uint32_t ntile = (tokens + BM - 1) / BM, ncta_n = w.rows / BN;
+    uint32_t mt = 1;
+    while (mt < 4 && mt * 2 <= ntile && (uint64_t)ncta_n * ((ntile + mt * 2 - 1) / (mt * 2)) >= (uint64_t)ctx->sm_count * 3 / 4) mt *= 2;
+    const uint32_t stage_bytes = mt * A_TILE + B_TILE;
+    uint32_t stages = (uint32_t)std::min<size_t>(8, (ctx->smem_optin - 4096) / stage_bytes);
+    stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, w.cols / BK));
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    GemmTcParams p{arg_ptr(w.data), y, w.rows, w.cols, tokens, stages, ctx->status};
+    dim3 grid(ncta_n, (ntile + mt - 1) / mt);
+#define LAUNCH_TC(MTV)                                                                                                           \
+    do {                                                                                                                         \
+        static bool done = false;                                                                                                \
+        if (!done) {                                                                                                             \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048));  /* the barriers are static */ \
+            done = true;                                                                                                         \
+        }                                                                                                                        \
+        gemm_tc_kernel<MTV><<<grid, 256, smem, ctx->stream>>>(tmap, p);                                                          \
+    } while (0)
+    if (mt == 1) LAUNCH_TC(1);
+    else if (mt == 2) LAUNCH_TC(2);
+    else LAUNCH_TC(4);
+#undef LAUNCH_TC
+    return brasa_post_launch(cmd, "gemm_tc");
+}

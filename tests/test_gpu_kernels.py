@@ -500,3 +500,21 @@ def test_argmax_edge_cases(ctx, K):
     g = ctx.buffer_from(a)
     run(ctx, lambda c: K.argmax(c, g, a.size, out))
     assert int(out.download(np.uint32)[0]) == 77
+
+
+@pytest.mark.parametrize("rows,cols", [(1024, 512), (128, 256), (256, 4096)])
+def test_gemm_tensor_core_token_counts(B, ctx, K, rows, cols):
+    """The tcgen05 prefill GEMM (tiled q4_0, rows a multiple of 128) over token counts that exercise 1, 2 and 4
+    token tiles per block, ragged last tiles and every pipeline depth; same bound as the reference's GEMM test
+    (1e-5 of sum |w x| against the f16-rounded product)."""
+    rng = O.Rng(77)
+    raw = rng.qmatrix(O.Q4_0, rows, cols)
+    mt, _ = tiled(B, ctx, K, "q4_0", raw, rows, cols)
+    for tokens in (16, 127, 128, 129, 300, 512, 700):
+        x = rng.vec(tokens * cols, 1.0)
+        xh = x.astype(np.float16)
+        want16, s16 = O.matmul(O.Q4_0, raw, rows, cols, x, f16_inputs=True)
+        gxh, gy = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4)
+        run(ctx, lambda c: K.gemm(c, mt, gxh, gy, tokens))
+        got = gy.download(np.float32).reshape(tokens, rows)
+        assert np.max(np.abs(got - want16) / s16) <= 1e-5, tokens
