@@ -292,6 +292,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     model = sess.model
     K = B.Kernels(ctx)
 
+    if args.only_prefill:
+        model.forward(ids, 0, want_logits=False)
+        profiler_range(True)
+        _, secs = model.forward(ids, 0)
+        ctx.sync()
+        profiler_range(False)
+        if rank == 0:
+            print(json.dumps({"metric": "prefill_tok_s", "value": PROMPT / secs, "unit": "tok/s", "ms": secs * 1e3,
+                              "config": {"workload": WORKLOAD, "tokens": PROMPT}, "note": "one prefill forward (profiling run)"}))
+        return
+
     # ---- device-resident decode (value) ----
     logits, _ = model.forward(ids, 0)
     first = int(np.argmax(logits[0]))
@@ -421,6 +432,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--decode-tokens", type=int, default=GENERATE - 1,
                     help="decode forwards per step (default: the workload's 255); smaller values are for profiler captures")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="run only one prefill forward of the workload's prompt (profiler captures)")
     ap.add_argument("--only-kernel", action="store_true",
                     help="run only the dominant kernel's own timing leg (profiler captures)")
     ap.add_argument("--only-decode", action="store_true",

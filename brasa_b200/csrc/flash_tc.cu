@@ -1,0 +1,325 @@
+// Causal GQA prefill attention on the 5th-generation tensor cores (crates/kernels/src/lib.rs:1185-1248,
+// flash_attention.metal:184-323), for the F16 prefill precision over an f16 KV cache: Q * scale is rounded to f16,
+// S, P and O are f32, the output is f16.
+//
+// One CTA = 128 queries of one query head. Per 128-key tile, S = Q K^T is 8 tcgen05.mma (M = 128 queries, N = 128
+// keys, K = 16 dims each) into tensor memory; the softmax threads (one per query row) read their row with
+// tcgen05.ld. Softmax is done in two sweeps over the keys instead of rescaling O: the first sweep only finds each
+// row's maximum m and sum l, the second recomputes S (tensor-core work is cheap next to everything else here),
+// forms P = exp(S - m) and accumulates O += P V in tensor memory. The reference keeps P in f32; a tensor core takes
+// f16 operands, so P goes in as two f16 terms (P = hi + lo, error 2^-22) and O += hi V + lo V.
+// K, V and Q tiles are written to shared memory in the 128-byte-swizzle layout tcgen05 reads: K and Q as K-major
+// operands (row = key / query, 128 dims in two 64-wide blocks), V with the same bytes as an MN-major B operand
+// (N = dim is contiguous), P as a K-major A operand (row = query, K = key).
+// Every wait is bounded; a wait that runs out raises the context's status word and the CTA leaves.
+#include "attn_device.cuh"
+#include "brasa_internal.h"
+#include "gemv_device.cuh"
+
+using namespace brasa_dev;
+
+namespace {
+
+constexpr uint32_t FA_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TILE_BYTES = 128 * 128 * 2;  // one 128 x 128 f16 tile: two [128][64] blocks of 16 KB
+
+__device__ __forceinline__ bool fa_mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// byte offset of the 16-byte chunk holding columns [8c, 8c + 8) of row r in a swizzled 128 x 128 f16 tile
+__device__ __forceinline__ uint32_t tile_chunk(uint32_t r, uint32_t c) {
+    return (c >> 6) * 16384 + (r >> 3) * 1024 + (r & 7) * 128 + ((((c >> 3) & 7) ^ (r & 7)) << 4);
+}
+
+// K-major operand (rows 128 bytes wide, 8-row groups 1024 bytes apart), 128-byte swizzle
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand: 64 contiguous N elements per row of 128 bytes, 8 K-rows per 1024-byte group (stride along K),
+// the next 64 N elements 16384 bytes further (leading offset)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, "
+        "%21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct FlashTcParams {
+    const float *q;        // [tokens][hq][128] after QK-norm and RoPE
+    const uint8_t *kc, *vc;  // f16 cache rows [position][hkv][128] from position 0
+    __half *o;             // [tokens][hq][128]
+    uint32_t tokens, hq, hkv, pos0;
+    float scale;
+    uint32_t *status;
+};
+
+__global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *qt = smem, *kt = smem + TILE_BYTES, *vt = smem + 2 * TILE_BYTES, *ph = smem + 3 * TILE_BYTES, *pl = smem + 4 * TILE_BYTES;
+    __shared__ uint64_t bar_s, bar_o;
+    __shared__ uint32_t tmem_base_s, abort_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // longest query tiles first (they see the most keys)
+    const uint32_t qtile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, kh = h / (p.hq / p.hkv);
+    const uint32_t q0 = qtile * 128, nq = min(128u, p.tokens - q0);
+    const uint32_t last_key = p.pos0 + q0 + nq - 1, lk = p.pos0 + p.tokens;  // inclusive; keys in the cache
+    const uint32_t nkt = last_key / 128 + 1;
+
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory: S in columns [0, 128), O in [128, 256)
+        uint32_t ncols = 256;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q tile: scale, round to f16, swizzled K-major; rows past the last query are zeros
+    for (uint32_t i = tid; i < 128 * 16; i += 256) {
+        const uint32_t r = i >> 4, c8 = (i & 15) * 8;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (r < nq) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)(q0 + r) * p.hq + h) * 128 + c8);
+            const float4 a = src[0], b = src[1];
+            __half2 h0 = __floats2half2_rn(a.x * p.scale, a.y * p.scale), h1 = __floats2half2_rn(a.z * p.scale, a.w * p.scale);
+            __half2 h2 = __floats2half2_rn(b.x * p.scale, b.y * p.scale), h3 = __floats2half2_rn(b.z * p.scale, b.w * p.scale);
+            out = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1), *reinterpret_cast<uint32_t *>(&h2),
+                             *reinterpret_cast<uint32_t *>(&h3));
+        }
+        *reinterpret_cast<uint4 *>(qt + tile_chunk(r, c8)) = out;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+    volatile uint32_t *abort_flag = &abort_s;
+
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+        for (uint32_t it = 0; it < FA_WAIT_LIMIT; ++it) {
+            if (fa_mbar_try(bar, parity)) return true;
+            if (*abort_flag) return false;
+        }
+        atomicExch(p.status, 5u);
+        *abort_flag = 1;
+        return false;
+    };
+    // rows [j * 128, j * 128 + 128) of one kv head's cache -> a swizzled tile; rows past the cache are zeros
+    auto load_tile = [&](const uint8_t *cache, uint8_t *tile, uint32_t j) {
+        for (uint32_t i = tid; i < 128 * 16; i += 256) {
+            const uint32_t r = i >> 4, c8 = (i & 15) * 8, key = j * 128 + r;
+            uint8_t *dst = tile + tile_chunk(r, c8);
+            if (key < lk) cp_async16(dst, cache + ((size_t)key * p.hkv + kh) * 256 + c8 * 2);
+            else *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    };
+    // instruction descriptors: D f32, A and B f16, M = N = 128; V is an MN-major B operand
+    const uint32_t idesc_s = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc_o = idesc_s | (1u << 16);
+    auto issue_s = [&]() {  // S = Q K^T
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+            umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kt) + off), idesc_s, ks > 0);
+        }
+        umma_commit(&bar_s);
+    };
+
+    const uint32_t row = (warp & 3) * 32 + lane;            // softmax threads are warps 0-3: one query row each
+    const uint32_t qpos = p.pos0 + q0 + row;
+    const uint32_t trow = ((warp & 3) * 32u) << 16;         // lane field of a tensor-memory address
+    float m = -INFINITY, l = 0.0f;
+    uint32_t ph_s = 0, ph_o = 0;
+    bool ok = true;
+
+    // ---- sweep 1: row maxima and sums ----
+    for (uint32_t j = 0; j < nkt && ok; ++j) {
+        load_tile(p.kc, kt, j);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s();
+        }
+        if (warp < 4) {
+            ok = wait(&bar_s, ph_s);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + trow + c, v);
+                    float cm = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t key = j * 128 + c + i;
+                        const float s = key <= qpos ? __uint_as_float(v[i]) : -INFINITY;
+                        v[i] = __float_as_uint(s);
+                        cm = fmaxf(cm, s);
+                    }
+                    const float mn = fmaxf(m, cm);
+                    if (mn != -INFINITY) {
+                        float add = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) add += expf(__uint_as_float(v[i]) - mn);
+                        l = l * (m == -INFINITY ? 0.0f : expf(m - mn)) + add;
+                        m = mn;
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+        ph_s ^= 1;
+        ok = __syncthreads_and(ok);  // S has been read: the K tile and S may be overwritten
+    }
+
+    // ---- sweep 2: P = exp(S - m), O += P V ----
+    for (uint32_t j = 0; j < nkt && ok; ++j) {
+        if (j > 0) {  // the previous tile's P V must have finished reading V and P
+            ok = wait(&bar_o, ph_o);
+            ph_o ^= 1;
+        }
+        load_tile(p.kc, kt, j);
+        load_tile(p.vc, vt, j);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s();
+        }
+        if (warp < 4) {
+            ok = wait(&bar_s, ph_s);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + trow + c, v);
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const uint32_t key = j * 128 + c + i;
+                        const float p0 = key <= qpos ? expf(__uint_as_float(v[i]) - m) : 0.0f;
+                        const float p1 = key + 1 <= qpos ? expf(__uint_as_float(v[i + 1]) - m) : 0.0f;
+                        const __half2 hh = __floats2half2_rn(p0, p1);
+                        const float2 hf = __half22float2(hh);
+                        const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+                        hi[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                        lo[i >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                        const uint32_t off = tile_chunk(row, c + 8 * g);
+                        *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+                        *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+        ph_s ^= 1;
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
+                const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
+                umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, 1u);
+            }
+            umma_commit(&bar_o);
+        }
+    }
+    // ---- output: O / l, rounded to f16 ----
+    if (ok && warp < 4) {
+        ok = wait(&bar_o, ph_o);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = 1.0f / l;
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + trow + c, v);
+                if (row < nq) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const __half2 hh = __floats2half2_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                    }
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.o + ((size_t)(q0 + row) * p.hq + h) * 128 + c);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) dst[g] = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t ncols = 256;
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(ncols) : "memory");
+    }
+}
+
+}  // namespace
+
+// F16 prefill precision over an f16 cache; q, k, v, o as for brasa_k_flash_attention_with (already validated there).
+int32_t brasa_flash_tc_launch(brasa_cmd *cmd, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh) {
+    brasa_ctx *ctx = cmd->ctx;
+    const size_t smem = 5 * TILE_BYTES + 1024;
+    static bool done = false;
+    if (!done) {
+        BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        done = true;
+    }
+    FlashTcParams p{q, kc, vc, o, sh.tokens, sh.hq, sh.hkv, sh.pos0, 1.0f / sqrtf(128.0f), ctx->status};
+    dim3 grid((sh.tokens + 127) / 128, sh.hq);
+    flash_tc_kernel<<<grid, 256, smem, ctx->stream>>>(p);
+    return brasa_post_launch(cmd, "flash_tc");
+}

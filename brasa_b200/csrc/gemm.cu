@@ -10,7 +10,7 @@
 #include "brasa_internal.h"
 
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
-int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *y, uint32_t tokens);
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens);
 
 namespace {
 
@@ -171,6 +171,11 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(WView w, const float *x, 
         }
 }
 
+bool tc_enabled() {
+    static const bool on = [] { const char *e = getenv("BRASA_GEMM_TC"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 }  // namespace
 
 extern "C" {
@@ -185,9 +190,10 @@ int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_ar
     BRASA_REQUIRE(ctx, arg_fits(x, (uint64_t)tokens * w.cols * (half_in ? 2 : 4)) && arg_fits(y, (uint64_t)tokens * w.rows * 4), "gemm: x or y too small");
     BRASA_REQUIRE(ctx, x.offset % 16 == 0 && y.offset % 8 == 0, "gemm: misaligned x or y");
     if (tokens == 0) return BRASA_OK;
-    static const bool tc_on = [] { const char *e = getenv("BRASA_GEMM_TC"); return !(e && e[0] == '0'); }();
-    if (half_in && tc_on && tokens > 8 && brasa_gemm_tc_supported(w, tokens))
-        return brasa_gemm_tc_launch(cmd, w, (const __half *)arg_ptr(x), (float *)arg_ptr(y), tokens);
+    if (half_in && tc_enabled() && tokens > 8 && brasa_gemm_tc_supported(w, tokens)) {
+        float *yp = (float *)arg_ptr(y);
+        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x), &yp, tokens);
+    }
     WView v{arg_ptr(w.data), w.qtype, w.layout, w.rows, w.cols};
     dim3 grid((w.rows + TN - 1) / TN, (tokens + TM - 1) / TM);
     if (half_in) gemm_f16_kernel<<<grid, 128, 0, ctx->stream>>>(v, (const __half *)arg_ptr(x), (float *)arg_ptr(y), tokens);
@@ -203,6 +209,16 @@ int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t cou
                            int32_t precision) {
     if (!cmd || !ws || !ys) return BRASA_EINVAL;
     BRASA_REQUIRE(cmd->ctx, count >= 1 && count <= 3, "gemm_multi: 1 to 3 matrices");
+    // one tensor-core launch for all of them when every matrix qualifies
+    bool all_tc = precision == BRASA_PREFILL_F16 && tc_enabled() && tokens > 8;
+    for (uint32_t i = 0; i < count && all_tc; ++i)
+        all_tc = brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols && qm_fits(ws[i]) &&
+                 arg_fits(x, (uint64_t)tokens * ws[i].cols * 2) && arg_fits(ys[i], (uint64_t)tokens * ws[i].rows * 4) && ys[i].offset % 16 == 0;
+    if (all_tc && x.offset % 16 == 0) {
+        float *yp[3] = {nullptr, nullptr, nullptr};
+        for (uint32_t i = 0; i < count; ++i) yp[i] = (float *)arg_ptr(ys[i]);
+        return brasa_gemm_tc_launch(cmd, count, ws, (const __half *)arg_ptr(x), yp, tokens);
+    }
     for (uint32_t i = 0; i < count; ++i) {
         BRASA_REQUIRE(cmd->ctx, ws[i].cols == ws[0].cols, "gemm_multi: matrices must share the input");
         BRASA_TRY(brasa_k_gemm_with(cmd, ws[i], x, ys[i], tokens, precision));

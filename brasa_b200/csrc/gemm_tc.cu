@@ -6,12 +6,13 @@
 // rows, K = 16 per instruction), accumulating in tensor memory (MT x 128 columns of 128 lanes), K in stages of 64:
 //   * warp 0, one lane: TMA. The X tile of a stage (MT boxes of 128 tokens x 64 halves) arrives by
 //     cp.async.bulk.tensor with the 128-byte swizzle; tokens past the end read as zeros.
-//   * warps 4-7: weights. Each thread owns one weight row of the CTA: it reads the row's 32 code bytes and 2 scales
-//     of the stage, turns nibbles into f16 with exact arithmetic (0x6400 | q is the half 1024 + q; minus 1032;
+//   * warps 4-11: weights. Each thread owns one quantisation block (32 columns) of one weight row per stage: it reads
+//     16 code bytes and the scale, turns nibbles into f16 with exact arithmetic (0x6400 | q is the half 1024 + q; minus 1032;
 //     times d in f16 rounds the exact product once, as the reference's f32 product does) and writes the row in the
 //     same swizzled K-major form the TMA produces. The tensor core reads both operands from shared memory.
 //   * warp 1, one lane: tcgen05.mma for the stage, then tcgen05.commit to hand the stage back.
-//   * after the last stage warps 4-7 read the accumulators (tcgen05.ld, one token per lane) and store Y.
+//   * after the last stage warps 4-11 read the accumulators (tcgen05.ld, one token per lane) and store Y.
+// Up to three matrices that share X (q, k, v) go into one launch: the grid's x index walks their 128-row tiles.
 // Every wait is bounded: a wait that runs out raises the context's status word and a CTA-wide flag, every role
 // leaves its loop, tensor memory is freed and the kernel returns.
 #include <cuda.h>
@@ -54,14 +55,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 }
 
 struct GemmTcParams {
-    const uint8_t *w;
-    float *y;
-    uint32_t rows, cols, tokens, stages;
+    const uint8_t *w[3];   // up to three matrices that share the input (q, k, v)
+    float *y[3];
+    uint32_t rows[3];
+    uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
+    uint32_t cols, tokens, stages;
     uint32_t *status;
 };
 
-template <int MT>
-__global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmTcParams p) {
+template <int MT, int G>
+__global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the dynamic shared memory base is only 16-byte aligned by contract: round up to the swizzle atom
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -70,13 +73,18 @@ __global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__
     __shared__ uint32_t tmem_base_s, abort_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t n0 = blockIdx.x * BN, tok0 = blockIdx.y * (MT * BM);
+    // which matrix and which 128 rows of it
+    const uint32_t mi = (blockIdx.x >= p.tile_end[0]) + (blockIdx.x >= p.tile_end[1]);
+    const uint32_t n0 = (blockIdx.x - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BN, tok0 = blockIdx.y * (MT * BM);
+    const uint8_t *wmat = mi == 0 ? p.w[0] : (mi == 1 ? p.w[1] : p.w[2]);
+    float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
+    const uint32_t yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
     const uint32_t nk = p.cols / BK, NS = p.stages;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < NS; ++s) {
             mbar_init(&full_x[s], 1);
-            mbar_init(&full_w[s], 4);  // one arrival per weight warp
+            mbar_init(&full_w[s], 8 / G);  // one arrival per warp of the group that converts the stage
             mbar_init(&empty[s], 1);
         }
         mbar_init(&acc_full, 1);
@@ -157,45 +165,67 @@ __global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__
             if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&acc_full)) : "memory");
         }
     } else if (warp >= 4) {
-        // ---- weights: thread -> row n0 + dt of W; per stage two quantisation blocks (64 columns) ----
-        const uint32_t dt = tid - 128;
+        // ---- weights. The eight warps form G groups that take the stages in turn (group g: stages g, g + G, ..), so
+        // G stages are being converted at once: the fence that makes a stage's writes visible to the tensor core costs
+        // far more than the conversion itself and must overlap with the next stages' work. A thread of a group owns G
+        // units of its stage, a unit being one quantisation block (32 columns) of one weight row. ----
+        constexpr uint32_t GT = 256 / G;  // threads of a group
+        const uint32_t dt = tid - 128, grp = dt / GT, gt = dt % GT;
         const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
-        const uint8_t *wrow = p.w + (size_t)(n0 + dt) * row_bytes;
-        const uint32_t r8 = dt & 7, row_off = (dt >> 3) * 1024 + r8 * 128;
-        uint4 c0 = *reinterpret_cast<const uint4 *>(wrow), c1 = *reinterpret_cast<const uint4 *>(wrow + 16);
-        uint32_t sc = *reinterpret_cast<const uint32_t *>(wrow + sc_off);
+        const uint8_t *wp[G];
+        const uint8_t *sp[G];
+        uint32_t soff[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const uint32_t u = gt + i * GT, wr = u & 127, blk = u >> 7;
+            wp[i] = wmat + (size_t)(n0 + wr) * row_bytes + blk * 16;
+            sp[i] = wmat + (size_t)(n0 + wr) * row_bytes + sc_off + blk * 2;
+            soff[i] = (wr >> 3) * 1024 + (wr & 7) * 128 + (blk << 16) + ((wr & 7) << 20);  // row offset | block | row & 7
+        }
+        uint4 cwq[G];
+        unsigned short scq[G];
+        {
+            const uint32_t kj = min(grp, nk - 1);
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kj * 32);
+                scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kj * 4);
+            }
+        }
         bool ok = true;
-        for (uint32_t k = 0; k < nk && ok; ++k) {
+        for (uint32_t k = grp; k < nk && ok; k += G) {
             const uint32_t s = k % NS;
-            // next stage's codes and scales are in flight while this one is converted
-            uint4 n0c = c0, n1c = c1;
-            uint32_t nsc = sc;
-            if (k + 1 < nk) {
-                n0c = *reinterpret_cast<const uint4 *>(wrow + (size_t)(k + 1) * 32);
-                n1c = *reinterpret_cast<const uint4 *>(wrow + (size_t)(k + 1) * 32 + 16);
-                nsc = *reinterpret_cast<const uint32_t *>(wrow + sc_off + (size_t)(k + 1) * 4);
+            uint4 cw[G];
+            unsigned short sc[G];
+            const uint32_t kn = min(k + G, nk - 1);  // this group's next stage: in flight during this one
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                cw[i] = cwq[i];
+                sc[i] = scq[i];
+                cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kn * 32);
+                scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kn * 4);
             }
             if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
             if (!ok) break;
-            uint8_t *brow = smem + (size_t)s * stage_bytes + MT * A_TILE + row_off;
+            uint8_t *btile = smem + (size_t)s * stage_bytes + MT * A_TILE;
 #pragma unroll
-            for (int blk = 0; blk < 2; ++blk) {
-                const uint4 cw = blk == 0 ? c0 : c1;
-                const uint32_t dbits = blk == 0 ? (sc & 0xffffu) : (sc >> 16);
-                const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+            for (int i = 0; i < G; ++i) {
+                const uint32_t r8 = soff[i] >> 20, blk = (soff[i] >> 16) & 1;
+                uint8_t *brow = btile + (soff[i] & 0xffffu);
+                const __half2 d2 = __half2half2(__ushort_as_half(sc[i]));
                 const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6408));  // 1032
-                const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
+                const uint32_t words[4] = {cw[i].x, cw[i].y, cw[i].z, cw[i].w};
                 // elements 0..15 are the low nibbles of bytes 0..15, elements 16..31 the high nibbles
                 uint32_t lo[8], hi[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t wv = words[i], wh = wv >> 4;
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t wv = words[j], wh = wv >> 4;
                     const uint32_t p01 = __byte_perm(wv, 0, 0x4140), p23 = __byte_perm(wv, 0, 0x4342);  // bytes (0, 1) and (2, 3) into half lanes
                     const uint32_t q01 = __byte_perm(wh, 0, 0x4140), q23 = __byte_perm(wh, 0, 0x4342);
-                    lo[2 * i] = deq2(p01, bias, d2);
-                    lo[2 * i + 1] = deq2(p23, bias, d2);
-                    hi[2 * i] = deq2(q01, bias, d2);
-                    hi[2 * i + 1] = deq2(q23, bias, d2);
+                    lo[2 * j] = deq2(p01, bias, d2);
+                    lo[2 * j + 1] = deq2(p23, bias, d2);
+                    hi[2 * j] = deq2(q01, bias, d2);
+                    hi[2 * j + 1] = deq2(q23, bias, d2);
                 }
                 // four 16-byte chunks of the row: columns 8c .. 8c + 7 of this block at chunk (4 blk + c) ^ (row & 7)
                 *reinterpret_cast<uint4 *>(brow + (((4 * blk + 0) ^ r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -206,21 +236,19 @@ __global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes are read by the tensor core's proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_w[s]);
-            c0 = n0c;
-            c1 = n1c;
-            sc = nsc;
         }
         // ---- epilogue: lane = token inside a 128-token tile, columns = weight rows ----
         ok = ok && wait(&acc_full, 0);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t q = warp & 3;  // the lane quarter of tensor memory this warp may read
+            const uint32_t q = warp & 3;           // the lane quarter of tensor memory this warp may read
+            const int c_begin = ((warp - 4) >> 2) * (BN / 2);  // two warps per quarter: half of the columns each
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t token = tok0 + mt * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
+                for (int c = c_begin; c < c_begin + BN / 2; c += 16) {
                     uint32_t v[16];
                     const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BN + c;
                     asm volatile(
@@ -231,7 +259,7 @@ __global__ void __launch_bounds__(256, 1) gemm_tc_kernel(const __grid_constant__
                         : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (token < p.tokens) {
-                        float4 *dst = reinterpret_cast<float4 *>(p.y + (size_t)token * p.rows + n0 + c);
+                        float4 *dst = reinterpret_cast<float4 *>(ymat + (size_t)token * yrows + n0 + c);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
                             dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
@@ -272,10 +300,25 @@ bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
            encode_tiled() != nullptr;
 }
 
-int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *y, uint32_t tokens) {
+// Y_i = W_i X for 1 to 3 matrices that share X (f16, [tokens][cols]); every W_i must pass brasa_gemm_tc_supported.
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens) {
     brasa_ctx *ctx = cmd->ctx;
-    BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(w, tokens), "gemm: shape not taken by the tensor-core kernel");
-    BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0, "gemm: misaligned x or y");
+    BRASA_REQUIRE(ctx, count >= 1 && count <= 3, "gemm: 1 to 3 matrices");
+    GemmTcParams p{};
+    uint32_t ncta_n = 0;
+    for (uint32_t i = 0; i < 3; ++i) {
+        if (i < count) {
+            BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols, "gemm: shape not taken by the tensor-core kernel");
+            BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(ys[i]) & 15) == 0, "gemm: misaligned y");
+            p.w[i] = arg_ptr(ws[i].data);
+            p.y[i] = ys[i];
+            p.rows[i] = ws[i].rows;
+            ncta_n += ws[i].rows / BN;
+        }
+        p.tile_end[i] = ncta_n;
+    }
+    const brasa_qmatrix &w = ws[0];
+    BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0, "gemm: misaligned x");
     // X as a 2-D tensor [tokens][cols] of f16; a box is 64 columns x 128 tokens, 128-byte swizzle, zeros past the end
     CUtensorMap tmap;
     cuuint64_t dims[2] = {w.cols, tokens}, strides[1] = {(cuuint64_t)w.cols * 2};
@@ -284,29 +327,41 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, const brasa_qmatrix &w, const __hal
                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
-    // tokens per CTA: as many 128-token tiles as keep the grid at about one CTA per SM or more (each CTA converts its
-    // 128 weight rows once, whatever its token count)
-    const uint32_t ntile = (tokens + BM - 1) / BM, ncta_n = w.rows / BN;
+    // tokens per CTA (1, 2 or 4 tiles of 128): the choice with the least estimated time, waves of CTAs x cycles per
+    // stage of one CTA (tensor core: about 300 cycles per token tile; conversion and hand-over: at least 450)
+    const uint32_t ntile = (tokens + BM - 1) / BM;
     uint32_t mt = 1;
-    while (mt < 4 && mt * 2 <= ntile && (uint64_t)ncta_n * ((ntile + mt * 2 - 1) / (mt * 2)) >= (uint64_t)ctx->sm_count * 3 / 4) mt *= 2;
+    uint64_t best = ~0ull;
+    for (uint32_t c = 1; c <= 4 && c <= std::max(1u, ntile); c *= 2) {
+        const uint64_t ctas = (uint64_t)ncta_n * ((ntile + c - 1) / c), waves = (ctas + ctx->sm_count - 1) / ctx->sm_count;
+        const uint64_t cost = waves * std::max<uint64_t>(300ull * c, 450);
+        if (cost <= best) {
+            best = cost;
+            mt = c;
+        }
+    }
     const uint32_t stage_bytes = mt * A_TILE + B_TILE;
     uint32_t stages = (uint32_t)std::min<size_t>(8, (ctx->smem_optin - 4096) / stage_bytes);
     stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, w.cols / BK));
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    GemmTcParams p{arg_ptr(w.data), y, w.rows, w.cols, tokens, stages, ctx->status};
+    p.cols = w.cols;
+    p.tokens = tokens;
+    p.stages = stages;
+    p.status = ctx->status;
     dim3 grid(ncta_n, (ntile + mt - 1) / mt);
-#define LAUNCH_TC(MTV)                                                                                                           \
+#define LAUNCH_TC(MTV, GV)                                                                                                        \
     do {                                                                                                                         \
         static bool done = false;                                                                                                \
         if (!done) {                                                                                                             \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048));  /* the barriers are static */ \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
             done = true;                                                                                                         \
         }                                                                                                                        \
-        gemm_tc_kernel<MTV><<<grid, 256, smem, ctx->stream>>>(tmap, p);                                                          \
+        gemm_tc_kernel<MTV, GV><<<grid, 384, smem, ctx->stream>>>(tmap, p);                                                          \
     } while (0)
-    if (mt == 1) LAUNCH_TC(1);
-    else if (mt == 2) LAUNCH_TC(2);
-    else LAUNCH_TC(4);
+    // conversion groups: as many stages in flight as the ring holds, at most four
+    if (mt == 1) LAUNCH_TC(1, 4);
+    else if (mt == 2) LAUNCH_TC(2, 4);
+    else LAUNCH_TC(4, 2);
 #undef LAUNCH_TC
     return brasa_post_launch(cmd, "gemm_tc");
 }

@@ -179,9 +179,15 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
         BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.attn_norm), A(m->norm_out), tokens, H, c.eps));
         xin = A(m->norm_out);
     }
-    BRASA_TRY(matmul(m, cmd, l.wq, xin, A(m->q), tokens, half_io));
-    BRASA_TRY(matmul(m, cmd, l.wk, xin, A(m->k_new), tokens, half_io));
-    BRASA_TRY(matmul(m, cmd, l.wv, xin, A(m->v_new), tokens, half_io));
+    if (tokens > GEMV_MAX_TOKENS) {  // one launch for q, k and v where the kernels allow it
+        brasa_qmatrix wqkv[3] = {l.wq.q, l.wk.q, l.wv.q};
+        brasa_arg yqkv[3] = {A(m->q), A(m->k_new), A(m->v_new)};
+        BRASA_TRY(brasa_k_gemm_multi(cmd, wqkv, 3, xin, yqkv, tokens, half_io ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32));
+    } else {
+        BRASA_TRY(matmul(m, cmd, l.wq, xin, A(m->q), tokens, half_io));
+        BRASA_TRY(matmul(m, cmd, l.wk, xin, A(m->k_new), tokens, half_io));
+        BRASA_TRY(matmul(m, cmd, l.wv, xin, A(m->v_new), tokens, half_io));
+    }
     brasa_attn_shape sh{tokens, c.heads, c.kv_heads, c.head_dim, pos0, m->limits.kv};
     KvView dst = kv_at(m, li, pos0), all = kv_at(m, li, 0);
     brasa_arg qkv[3] = {A(m->q), A(m->k_new), A(m->v_new)}, norms[2] = {A(l.q_norm), A(l.k_norm)}, dsts[2] = {dst.k, dst.v};

@@ -518,3 +518,22 @@ def test_gemm_tensor_core_token_counts(B, ctx, K, rows, cols):
         run(ctx, lambda c: K.gemm(c, mt, gxh, gy, tokens))
         got = gy.download(np.float32).reshape(tokens, rows)
         assert np.max(np.abs(got - want16) / s16) <= 1e-5, tokens
+
+
+@pytest.mark.parametrize("tokens,pos0", [(512, 0), (300, 77), (129, 255)])
+def test_flash_attention_tensor_core_many_query_tiles(B, ctx, K, tokens, pos0):
+    """The tcgen05 prefill attention (F16 precision over an f16 cache) with several 128-query tiles, ragged last
+    tiles and key ranges that start before the queries; bound of the reference's attention test."""
+    rng = O.Rng(23)
+    hq, hkv, dim = 8, 2, 128
+    lk = pos0 + tokens
+    cap = (lk + 63) // 64 * 64
+    q = rng.vec(tokens * hq * dim, 2.0)
+    gk, gv, k, v = make_cache(B, ctx, B.KvType.F16, rng.vec(cap * hkv * dim, 2.0), rng.vec(cap * hkv * dim, 3.0))
+    want16, vmax = O.attention(q, k, v, tokens, hq, hkv, dim, pos0, q16=True)
+    gq, goh = ctx.buffer_from(q), ctx.buffer(q.size * 2)
+    shape = B.AttnShape(tokens, hq, hkv, dim, pos0, B.KvType.F16)
+    run(ctx, lambda c: K.flash_attention(c, gq, gk, gv, goh, shape))
+    oh = goh.download(np.float16).astype(np.float32)
+    d = np.maximum(np.abs(oh - want16) - np.abs(want16) * 2.0 ** -11, 0.0)  # the output's own f16 rounding is discounted
+    assert float(np.max(d / np.maximum(vmax, 1e-30))) <= 1e-5
