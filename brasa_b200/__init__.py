@@ -500,6 +500,18 @@ class Kernels:
     def argmax(self, cmd, logits, n, out):
         self._k(self.L.brasa_k_argmax(cmd._h, _arg(logits), C.c_uint32(n), _arg(out)))
 
+    def sample_top_p(self, cmd, logits, n, temperature, top_k, top_p, rng_state, out):
+        """Sampler::sample on the device; rng_state is a 16-byte buffer made by pcg32_state(seed)."""
+        self._k(self.L.brasa_k_sample_top_p(cmd._h, _arg(logits), C.c_uint32(n), C.c_float(temperature), C.c_uint32(top_k), C.c_float(top_p),
+                                            _arg(rng_state), _arg(out)))
+
+
+def pcg32_state(seed: int) -> np.ndarray:
+    """Pcg32::new(seed) as the {state, increment} pair the device sampler keeps."""
+    out = (C.c_uint64 * 2)()
+    lib().brasa_pcg32_seed(C.c_uint64(seed), out)
+    return np.array([out[0], out[1]], dtype=np.uint64)
+
 
 # ---- model / session ---------------------------------------------------------------------------
 

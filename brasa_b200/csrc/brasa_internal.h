@@ -36,6 +36,8 @@ struct brasa_ctx {
     bool token_kernel = true;    // run a decode token as one persistent kernel (BRASA_TOKEN_KERNEL=0 turns it off)
     uint64_t launches = 0;       // kernels enqueued on this context (graph replays count their nodes)
     uint64_t capture_launches = 0;
+    float *sample_scratch = nullptr;  // weights of the device sampler (2 x vocabulary)
+    size_t sample_scratch_n = 0;
     void *argmax_scratch = nullptr;  // arrival counter + per-block partial maxima
     bool gemv_attr_done[10] = {};  // opt-in shared memory size set on this device, per kernel instance
 };

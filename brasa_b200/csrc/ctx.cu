@@ -71,6 +71,7 @@ void brasa_ctx_destroy(brasa_ctx *ctx) {
     cudaFree(ctx->gemv_partials);
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);
     cudaFree(ctx->status);
     cudaStreamDestroy(ctx->stream);
@@ -337,6 +338,7 @@ int32_t brasa_gemv_scratch(brasa_ctx *ctx, size_t partial_floats, size_t counter
         BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);
         ctx->gemv_counters = nullptr;
         ctx->gemv_counters_n = 0;

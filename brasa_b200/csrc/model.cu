@@ -661,14 +661,25 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
     const bool greedy = params.temperature <= 0.0f;
     // Greedy with nothing to mask keeps the logits on the device: the token is chosen there and only
     // its id crosses to the host.
-    const bool device_pick = greedy && !(s->ignore_stop && !s->stop_ids.empty());
+    const bool masked = s->ignore_stop && !s->stop_ids.empty();
+    const bool device_pick = greedy && !masked;
+    // Sampling with nothing to mask also stays on the device (brasa_k_sample_top_p, same PCG32 stream as the host
+    // sampler); the host sampler remains for the masked case.
+    const bool device_sample = !greedy && !masked && params.top_p > 0.0f;
     brasa::Sampler sampler(params.temperature, params.top_k, params.top_p, params.seed, m->cfg.vocab);
+    const brasa_arg rng_arg = A(m->dev_state, 128);
+    if (device_sample) {
+        uint64_t st[2];
+        brasa_pcg32_seed(params.seed, st);
+        BRASA_TRY(brasa_buf_upload(m->dev_state, 128, st, 16));
+    }
+    const bool host_logits = !device_pick && !device_sample;
 
     auto t0 = clk::now();
     for (uint32_t off = common; off < prompt_len; off += lim.max_tokens) {
         uint32_t n = std::min(lim.max_tokens, prompt_len - off);
         bool last = off + n == prompt_len;
-        BRASA_TRY(brasa_model_forward(m, prompt + off, n, (uint32_t)s->cached.size(), 1, (last && !device_pick) ? s->logits.data() : nullptr, nullptr));
+        BRASA_TRY(brasa_model_forward(m, prompt + off, n, (uint32_t)s->cached.size(), 1, (last && host_logits) ? s->logits.data() : nullptr, nullptr));
         s->cached.insert(s->cached.end(), prompt + off, prompt + off + n);
     }
     double prefill_ms = ms_since(t0);
@@ -695,6 +706,16 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
             next = *m->pinned_id;
         } else if (device_pick) {
             next = *m->pinned_id;  // read back by the previous step
+        } else if (device_sample) {
+            brasa_cmd *cmd;
+            BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+            int32_t rc = brasa_k_sample_top_p(cmd, A(m->logits), m->cfg.vocab, params.temperature, params.top_k, params.top_p, rng_arg, A(m->next_id));
+            if (rc == BRASA_OK)
+                rc = brasa_check_cuda(ctx, cudaMemcpyAsync(m->pinned_id, m->next_id->ptr, 4, cudaMemcpyDeviceToHost, ctx->stream), "token read");
+            int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+            BRASA_TRY(rc);
+            BRASA_TRY(rc2);
+            next = *m->pinned_id;
         } else {
             if (s->ignore_stop)
                 for (uint32_t id : s->stop_ids)
@@ -728,7 +749,7 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
             BRASA_CUDA(ctx, cudaMemcpyAsync(m->pinned_id, m->next_id->ptr, 4, cudaMemcpyDeviceToHost, ctx->stream));
             BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         } else {
-            BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, device_pick ? nullptr : s->logits.data(), nullptr));
+            BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, host_logits ? s->logits.data() : nullptr, nullptr));
         }
         s->cached.push_back(next);
     }

@@ -71,6 +71,139 @@ __global__ void advance_kernel(uint32_t *ids, const uint32_t *next, uint32_t *ou
     *pos += 1;
 }
 
+
+// ---- temperature / top-k / top-p sampling on the device (crates/runtime/src/sampler.rs:60-146) ----------------
+// The reference sorts the candidates (descending logit, f32 total order), turns them into weights
+// exp((l - max) / T), keeps the shortest prefix whose normalised mass reaches top_p and walks that prefix with one
+// PCG32 draw. Here nothing is sorted: a prefix of the sorted order is the set {key >= t} for a threshold t, its mass
+// is a block-wide sum, and the three prefixes the algorithm needs (the top_k-th candidate, the top_p cut, the drawn
+// token) are found by bisection over the 32-bit order key, then over the token id among candidates with equal logits
+// (equal logits keep ascending id, as the host sampler does). Sums are tree sums where the reference adds in sorted
+// order, so a draw that lands within rounding of a boundary may pick the neighbouring token.
+struct Prefix {
+    uint32_t t;   // candidates with key > t are in
+    uint32_t id;  // candidates with key == t are in when their id <= id
+};
+
+__device__ __forceinline__ uint32_t order_key(float f) {  // larger key = earlier in the descending total order
+    int32_t b = __float_as_int(f);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    return (uint32_t)b ^ 0x80000000u;
+}
+__device__ __forceinline__ bool in_prefix(uint32_t key, uint32_t id, Prefix p) { return key > p.t || (key == p.t && id <= p.id); }
+
+__device__ float block_sum(float v, float *sh) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();  // sh may still be read from the previous call
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = sh[threadIdx.x & 31];  // 1024 threads: 32 warp sums
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+// Sum of g over {i in `inside`: key_i > t or (key_i == t and id <= id_max)}; g = 1 counts.
+template <bool COUNT>
+__device__ float mass(const float *logits, const float *w, uint32_t n, Prefix inside, Prefix q, float *sh) {
+    float a = 0.0f;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t k = order_key(logits[i]);
+        if (in_prefix(k, i, inside) && in_prefix(k, i, q)) a += COUNT ? 1.0f : w[i];
+    }
+    return block_sum(a, sh);
+}
+
+// The shortest prefix of the sorted order (inside `inside`) whose mass reaches `bound`; `inside` itself when none does.
+template <bool COUNT>
+__device__ Prefix shortest_prefix(const float *logits, const float *w, uint32_t n, Prefix inside, float bound, float *sh) {
+    if (!(mass<COUNT>(logits, w, n, inside, Prefix{0u, 0xffffffffu}, sh) >= bound)) return inside;
+    // largest key t with mass{key >= t} >= bound
+    uint32_t lo = 0, hi = 0xffffffffu;
+    while (lo < hi) {
+        const uint32_t mid = lo + (hi - lo) / 2 + 1;
+        if (mass<COUNT>(logits, w, n, inside, Prefix{mid, 0xffffffffu}, sh) >= bound) lo = mid;
+        else hi = mid - 1;
+    }
+    const uint32_t t = lo;
+    // among the candidates with that key, the smallest id bound that still reaches it
+    uint32_t a = 0, b = n - 1;
+    while (a < b) {
+        const uint32_t mid = a + (b - a) / 2;
+        if (mass<COUNT>(logits, w, n, inside, Prefix{t, mid}, sh) >= bound) b = mid;
+        else a = mid + 1;
+    }
+    return Prefix{t, a};
+}
+
+__global__ void __launch_bounds__(1024) sample_kernel(const float *logits, uint32_t n, float temperature, uint32_t top_k, float top_p,
+                                                      unsigned long long *rng, float *w, uint32_t *out, uint32_t *ids0, uint32_t *out_ids,
+                                                      const uint32_t *out_count) {
+    __shared__ float sh[32];
+    __shared__ uint32_t shk[32];
+    const uint32_t tid = threadIdx.x;
+    // largest key: the maximum logit in the total order
+    uint32_t kmax = 0;
+    for (uint32_t i = tid; i < n; i += blockDim.x) kmax = max(kmax, order_key(logits[i]));
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    if ((tid & 31) == 0) shk[tid >> 5] = kmax;
+    __syncthreads();
+    kmax = shk[tid & 31];
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    int32_t mb = (int32_t)(kmax ^ 0x80000000u);
+    mb ^= (int32_t)(((uint32_t)(mb >> 31)) >> 1);
+    const float mx = __int_as_float(mb);
+
+    Prefix kept{0u, 0xffffffffu};  // everything
+    if (top_k > 0 && top_k < n) kept = shortest_prefix<true>(logits, nullptr, n, kept, (float)top_k, sh);
+    // weights of the kept candidates, their sum, and the normalised weights for the top-p cut
+    float a = 0.0f;
+    for (uint32_t i = tid; i < n; i += blockDim.x) {
+        const float v = in_prefix(order_key(logits[i]), i, kept) ? expf((logits[i] - mx) / temperature) : 0.0f;
+        w[i] = v;
+        a += v;
+    }
+    const float sum = block_sum(a, sh);
+    if (top_p < 1.0f) {
+        for (uint32_t i = tid; i < n; i += blockDim.x) w[n + i] = w[i] / sum;
+        __syncthreads();
+        kept = shortest_prefix<false>(logits, w + n, n, kept, top_p, sh);
+    }
+    const float total = mass<false>(logits, w, n, kept, Prefix{0u, 0xffffffffu}, sh);
+    // one PCG32 draw (every thread computes the same value; thread 0 stores the new state)
+    const unsigned long long old = rng[0], inc = rng[1];
+    uint32_t x = (uint32_t)(((old >> 18) ^ old) >> 27), rot = (uint32_t)(old >> 59);
+    const uint32_t u = (x >> rot) | (x << ((32 - rot) & 31));
+    const float r = (float)(u >> 8) / 16777216.0f * total;
+    // (a draw of exactly 0 picks the first candidate, as the reference's walk does)
+    Prefix pick = shortest_prefix<false>(logits, w, n, kept, fmaxf(r, 1.17549435e-38f), sh);  // first prefix whose weight reaches r; the kept set's end otherwise
+    // the chosen token is the last element of that prefix: the smallest key in it, largest id among equals
+    uint32_t best_k = 0xffffffffu, best_i = 0;
+    for (uint32_t i = tid; i < n; i += blockDim.x) {
+        const uint32_t k = order_key(logits[i]);
+        if (in_prefix(k, i, kept) && in_prefix(k, i, pick) && (k < best_k || (k == best_k && i > best_i))) {
+            best_k = k;
+            best_i = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const uint32_t ok = __shfl_xor_sync(0xffffffffu, best_k, o), oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ok < best_k || (ok == best_k && oi > best_i)) { best_k = ok; best_i = oi; }
+    }
+    __syncthreads();
+    if ((tid & 31) == 0) { shk[tid >> 5] = best_k; sh[tid >> 5] = __uint_as_float(best_i); }
+    __syncthreads();
+    if (tid == 0) {
+        for (int wi = 1; wi < 32; ++wi) {
+            const uint32_t ok = shk[wi], oi = __float_as_uint(sh[wi]);
+            if (ok < best_k || (ok == best_k && oi > best_i)) { best_k = ok; best_i = oi; }
+        }
+        rng[0] = old * 6364136223846793005ULL + inc;
+        *out = best_i;
+        if (ids0) *ids0 = best_i;
+        if (out_ids && out_count && *out_count > 0) out_ids[*out_count - 1] = best_i;
+    }
+}
+
 }  // namespace
 
 int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
@@ -100,6 +233,37 @@ int32_t brasa_k_argmax(brasa_cmd *cmd, brasa_arg logits, uint32_t n, brasa_arg o
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, arg_fits(logits, (uint64_t)n * 4) && arg_fits(out_u32, 4), "argmax: buffers too small");
     return brasa_argmax_launch(cmd, (const float *)arg_ptr(logits), n, (uint32_t *)arg_ptr(out_u32));
+}
+
+
+int32_t brasa_k_sample_top_p(brasa_cmd *cmd, brasa_arg logits, uint32_t n, float temperature, uint32_t top_k, float top_p, brasa_arg rng_state,
+                             brasa_arg out_u32) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, n > 0 && arg_fits(logits, (uint64_t)n * 4) && arg_fits(out_u32, 4) && arg_fits(rng_state, 16) && rng_state.offset % 8 == 0,
+                  "sample_top_p: buffers too small or misaligned");
+    if (temperature <= 0.0f) return brasa_argmax_launch(cmd, (const float *)arg_ptr(logits), n, (uint32_t *)arg_ptr(out_u32));
+    BRASA_REQUIRE(ctx, top_p > 0.0f, "sample_top_p: top_p must be positive");
+    if (ctx->sample_scratch_n < 2 * (size_t)n) {  // weights and normalised weights
+        if (ctx->sample_scratch) cudaFree(ctx->sample_scratch);
+        ctx->sample_scratch = nullptr;
+        ctx->sample_scratch_n = 0;
+        BRASA_CUDA(ctx, cudaMalloc(&ctx->sample_scratch, 2 * (size_t)n * 4));
+        ctx->sample_scratch_n = 2 * (size_t)n;
+    }
+    sample_kernel<<<1, 1024, 0, ctx->stream>>>((const float *)arg_ptr(logits), n, temperature, top_k, top_p, (unsigned long long *)arg_ptr(rng_state),
+                                               ctx->sample_scratch, (uint32_t *)arg_ptr(out_u32), nullptr, nullptr, nullptr);
+    return brasa_post_launch(cmd, "sample_top_p");
+}
+
+void brasa_pcg32_seed(uint64_t seed, uint64_t state_inc[2]) {
+    // Pcg32::new of the reference (sampler.rs:13-20): the state after seeding, and the increment
+    uint64_t state = 0, inc = (0xda3e39cb94b95bdbULL << 1) | 1;
+    state = state * 6364136223846793005ULL + inc;
+    state += seed;
+    state = state * 6364136223846793005ULL + inc;
+    state_inc[0] = state;
+    state_inc[1] = inc;
 }
 
 }  // extern "C"

@@ -201,6 +201,13 @@ int32_t brasa_k_flash_attention(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_
 
 /* first index of the maximum, NaN ignored, 0 when nothing exceeds -inf (:148-170); out: one u32 */
 int32_t brasa_k_argmax(brasa_cmd *cmd, brasa_arg logits, uint32_t n, brasa_arg out_u32);
+/* Sampler::sample on the device (crates/runtime/src/sampler.rs:60-146): temperature, top-k (0 = off) and top-p over
+ * n logits, one PCG32 draw from the 16-byte state {u64 state, u64 increment} in rng_state (advanced in place; fill it
+ * with brasa_pcg32_seed). temperature <= 0 is the greedy argmax. The chosen token id goes to out_u32. */
+int32_t brasa_k_sample_top_p(brasa_cmd *cmd, brasa_arg logits, uint32_t n, float temperature, uint32_t top_k, float top_p, brasa_arg rng_state,
+                             brasa_arg out_u32);
+/* Pcg32::new(seed) (sampler.rs:13-20) as the two words brasa_k_sample_top_p keeps on the device. */
+void brasa_pcg32_seed(uint64_t seed, uint64_t state_inc[2]);
 
 /* ---- memory planner (crates/memory/src/planner.rs) ------------------------------------------ */
 

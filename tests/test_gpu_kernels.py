@@ -537,3 +537,55 @@ def test_flash_attention_tensor_core_many_query_tiles(B, ctx, K, tokens, pos0):
     oh = goh.download(np.float16).astype(np.float32)
     d = np.maximum(np.abs(oh - want16) - np.abs(want16) * 2.0 ** -11, 0.0)  # the output's own f16 rounding is discounted
     assert float(np.max(d / np.maximum(vmax, 1e-30))) <= 1e-5
+
+
+# ---- sampling ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n", [50, 5000, 151_936])
+def test_device_sampler_follows_the_reference_sampler(B, ctx, K, n):
+    """brasa_k_sample_top_p against the oracle's restatement of Sampler::sample (sampler.rs:60-146) with the same
+    PCG32 stream. The device sums in a tree where the reference adds 150 000 f32 terms one after another, so both
+    carry rounding in the cumulative mass: every device pick must be a candidate the reference keeps and must sit
+    within 1e-3 of the total mass of the reference's pick in the sorted order; for vocabularies where f32 addition
+    order matters little (n <= 5000) at least 97 % of the draws must be the very same token."""
+    rng = np.random.default_rng(n)
+    out = ctx.buffer(4)
+    agree = total = 0
+    for temperature, top_k, top_p, seed in [(0.7, 0, 0.95, 11), (1.0, 40, 0.9, 5), (1.3, 0, 1.0, 7), (0.6, 20, 0.95, 3), (1.0, 3, 1.0, 1)]:
+        ref = O.Sampler(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed)
+        state = ctx.buffer_from(B.pcg32_state(seed))
+        for _ in range(12):
+            logits = (rng.standard_normal(n) * 3.0).astype(np.float32)
+            if n > 100:
+                logits[rng.integers(0, n, 5)] = logits.max()  # equal logits: ascending id order
+            want = ref.sample(logits)
+            g = ctx.buffer_from(logits)
+            run(ctx, lambda c: K.sample_top_p(c, g, n, temperature, top_k, top_p, state, out))
+            got = int(out.download(np.uint32, 1)[0])
+            total += 1
+            agree += got == want
+            order = np.lexsort((np.arange(n), -logits.astype(np.float64)))
+            rank = {int(t): i for i, t in enumerate(order[:ref.last_keep + 1])}
+            assert got in rank, (temperature, top_k, top_p, ref.last_keep)
+            w = np.exp((logits[order].astype(np.float64) - float(logits.max())) / temperature)
+            cum = np.cumsum(w[:ref.last_keep + 1])
+            assert abs(cum[rank[got]] - cum[rank[want]]) <= 1e-3 * cum[-1] + max(w[rank[got]], w[rank[want]]), (got, want)
+    if n <= 5000:
+        assert agree >= 0.97 * total, (agree, total)
+
+
+def test_device_sampler_frequency_and_greedy(B, ctx, K):
+    """The reference's frequency check (sampler.rs:252-267): logits (0, ln 3) at temperature 1 pick token 1 three
+    times out of four; temperature 0 is the greedy argmax."""
+    out = ctx.buffer(4)
+    g = ctx.buffer_from(np.array([0.0, np.log(3.0)], dtype=np.float32))
+    state = ctx.buffer_from(B.pcg32_state(3))
+    ones = 0
+    draws = 2000
+    for _ in range(draws):
+        run(ctx, lambda c: K.sample_top_p(c, g, 2, 1.0, 0, 1.0, state, out))
+        ones += int(out.download(np.uint32, 1)[0])
+    assert abs(ones / draws - 0.75) < 0.03
+    g2 = ctx.buffer_from(np.array([0.1, 3.0, -1.0, 2.9], dtype=np.float32))
+    run(ctx, lambda c: K.sample_top_p(c, g2, 4, 0.0, 0, 1.0, state, out))
+    assert int(out.download(np.uint32, 1)[0]) == 1
