@@ -266,12 +266,9 @@ def kernel_roofline(B, ctx, K, cfg, peak, peak_kind, profile=False):
 def run_ours(args, rank: int, world: int, local_rank: int):
     import brasa_b200 as B
     from brasa_b200 import synth
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from brasa_b200.replicas import Replicas
+    rep = Replicas("nccl" if world > 1 else None)  # replicas only: the ranks share a barrier and a few scalars
+    dist = rep.dist
     ctx = B.Context(local_rank)
     cfg = synth.QWEN3_4B
     if args.only_kernel:
@@ -324,13 +321,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     launches = ctx.launch_count() - launches0
     if dist:
         dist.barrier()
-    total_s = float(sum(dev_s))
-    if dist:
-        import torch
-        t = torch.tensor([total_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_s = float(t.item())
-    value = world * args.steps * steps_tokens / total_s
+    total_s = rep.max(float(sum(dev_s)))  # the job is as slow as its slowest replica
+    value = rep.sum(args.steps * steps_tokens) / total_s
     if args.only_decode:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -348,11 +340,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             prefill_vals.append(st.prefill_tok_s())
     e2e = statistics.median(e2e_vals)
     same_tokens = bool(out_ids is not None and list(gen[1:]) == list(out_ids))
-    if dist:
-        import torch
-        t = torch.tensor([e2e], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        e2e = float(t.item())
+    e2e = rep.sum(e2e)
     if rank != 0:
         return
 
