@@ -187,7 +187,7 @@ def run_reference(args, rank: int):
     path = model_path("qwen3-4b-random-blocks")
     if not path.exists():
         write_random_block_model(path, cfg)
-    cores = os.cpu_count() or 1
+    cores = use_all_host_cores()
     ids = prompt_ids(cfg["vocab_size"])
     total = args.warmup + args.steps
     times, _ = cpu_decode_sample(path, None, ids[:total], PROMPT, total)
@@ -202,6 +202,17 @@ def run_reference(args, rank: int):
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
+
+
+def use_all_host_cores() -> int:
+    """OpenMP threads for the CPU legs: every host core, also under torchrun (which exports OMP_NUM_THREADS=1)."""
+    import ctypes
+    cores = os.cpu_count() or 1
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
+    return cores
 
 
 # ---- the GPU arm ------------------------------------------------------------------------------------
@@ -370,6 +381,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     try:
         import oracle
         oracle.build()
+        use_all_host_cores()
         model.forward(ids, 0, want_logits=False)
         kvd = cfg["num_key_value_heads"] * cfg["head_dim"]
         kv_rows = []
@@ -434,6 +446,10 @@ def main():
         run_reference(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
+        if world > 1:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.destroy_process_group()
 
 
 if __name__ == "__main__":
