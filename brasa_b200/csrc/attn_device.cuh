@@ -25,6 +25,16 @@ __device__ __forceinline__ float tile_at(const uint8_t *row, int d) {
     return __half2float(reinterpret_cast<const __half *>(row + 128)[d >> 5]) * (float)reinterpret_cast<const int8_t *>(row)[d];
 }
 
+// elements d and d + 1 (d even)
+template <int KV>
+__device__ __forceinline__ float2 tile_at2(const uint8_t *row, int d) {
+    if (KV == BRASA_KV_F32) return *reinterpret_cast<const float2 *>(row + d * 4);
+    if (KV == BRASA_KV_F16) return __half22float2(*reinterpret_cast<const __half2 *>(row + d * 2));
+    const char2 q = *reinterpret_cast<const char2 *>(row + d);
+    const float sc = __half2float(reinterpret_cast<const __half *>(row + 128)[d >> 5]);
+    return make_float2(sc * (float)q.x, sc * (float)q.y);
+}
+
 // 8 consecutive elements starting at d (d % 8 == 0)
 template <int KV>
 __device__ __forceinline__ void tile_load8(const uint8_t *row, int d, float out[8]) {
@@ -108,6 +118,22 @@ __device__ __forceinline__ void norm_rope_vals(const float xv[4], const float *w
         float a = y[j], b = y[j + 2];
         y[j] = a * c - b * s;
         y[j + 2] = b * c + a * s;
+    }
+}
+
+
+// The same with the norm weight and the table entries already in registers (wv[j] = w[lane + 32 j], cs[j] / sn[j] =
+// cos / sin of pair lane + 32 j): what does not depend on the row can then be fetched before the row arrives.
+__device__ __forceinline__ void norm_rope_regs(const float xv[4], const float wv[4], const float cs[2], const float sn[2], float eps, float y[4]) {
+    float ss = 0.0f;
+    for (int j = 0; j < 4; ++j) ss += xv[j] * xv[j];
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float scale = 1.0f / sqrtf(ss / 128.0f + eps);
+    for (int j = 0; j < 4; ++j) y[j] = xv[j] * scale * wv[j];
+    for (int j = 0; j < 2; ++j) {
+        float a = y[j], b = y[j + 2];
+        y[j] = a * cs[j] - b * sn[j];
+        y[j + 2] = b * cs[j] + a * sn[j];
     }
 }
 

@@ -385,12 +385,15 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
     constexpr int RB = KvRow<KV>::BYTES, RS = KvRow<KV>::STRIDE;
     constexpr uint32_t C = KV == BRASA_KV_F32 ? 32 : 64;  // keys per work item
     constexpr int KPW = C / TK_WARPS, LPK = 32 / KPW, DPL = 128 / LPK;  // keys per warp, lanes per key, dims per lane
+    // q in shared memory: 16-float segments 20 floats apart, so the lanes of a key (one segment or half segment each)
+    // read conflict-free
+    constexpr int QS_SEG = 20, QS_HEAD = 8 * QS_SEG;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t Gq = heads / kv_heads, pos = c.pos;
     const uint32_t lk = pos + 1, nchunks = (lk + C - 1) / C;
     uint8_t *kt = c.xfb, *vt = c.xfb + C * RS;
-    float *qs = reinterpret_cast<float *>(vt + C * RS);  // [8][128]
-    float *ps = qs + 8 * 128;                            // [8][C]
+    float *qs = reinterpret_cast<float *>(vt + C * RS);  // [8][QS_HEAD]
+    float *ps = qs + 8 * QS_HEAD;                        // [8][C]
     float *ml = ps + 8 * C;                              // merge: m[max_chunks], l[max_chunks]
     float *red = c.red;
     const uint32_t nitems = kv_heads * nchunks;
@@ -415,15 +418,21 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             // warps 0 .. Gq-1: a query head; warp Gq: the new key row; warp Gq + 1: the new value row
             const uint32_t g = warp;
             const unsigned long long *src = g < Gq ? op.in + (size_t)(kh * Gq + g) * 128 : op.in + (size_t)(heads + (g - Gq) * kv_heads + kh) * 128;
-            float xv[4], y[4];
-            {
+            float xv[4], y[4], wv[4], cs[2], sn[2];
+            {   // what does not depend on this token's q, k, v first: norm weight, cos and sin of this position
+                const float *nw = g < Gq ? op.q_norm : op.k_norm;
+                for (int j = 0; j < 4; ++j) wv[j] = nw[lane + 32 * j];
+                for (int j = 0; j < 2; ++j) {
+                    cs[j] = cos_t[(size_t)pos * 64 + lane + 32 * j];
+                    sn[j] = sin_t[(size_t)pos * 64 + lane + 32 * j];
+                }
                 uint32_t raw[4];
                 ll_wait4(c, src + lane, src + lane + 32, src + lane + 64, src + lane + 96, epoch_in, raw);
                 for (int j = 0; j < 4; ++j) xv[j] = __uint_as_float(raw[j]);
             }
-            if (g <= Gq) norm_rope_vals(xv, g < Gq ? op.q_norm : op.k_norm, cos_t, sin_t, pos, op.eps, lane, y);
+            if (g <= Gq) norm_rope_regs(xv, wv, cs, sn, op.eps, y);
             if (g < Gq) {
-                for (int j = 0; j < 4; ++j) qs[g * 128 + lane + 32 * j] = y[j];
+                for (int j = 0; j < 4; ++j) qs[g * QS_HEAD + ((lane + 32 * j) >> 4) * QS_SEG + ((lane + 32 * j) & 15)] = y[j];
             } else {
                 const size_t grow = ((size_t)pos * kv_heads + kh) * RB;
                 if (g == Gq) put_row<KV>(op.kc + grow, kt + (nkeys - 1) * RS, y, lane);
@@ -446,7 +455,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                 float a = 0.0f;
 #pragma unroll
                 for (int d = 0; d < DPL; d += 4) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(qs + g * 128 + d0 + d);
+                    const float4 qa = *reinterpret_cast<const float4 *>(qs + g * QS_HEAD + (d0 >> 4) * QS_SEG + ((d0 + d) & 15));
                     a = fmaf(qa.x, kv[d], a); a = fmaf(qa.y, kv[d + 1], a); a = fmaf(qa.z, kv[d + 2], a); a = fmaf(qa.w, kv[d + 3], a);
                 }
                 for (int o = LPK / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
@@ -473,9 +482,17 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
 #pragma unroll 1
         for (uint32_t o = tid; o < Gq * 128; o += TK_THREADS) {  // P V: one output element per thread
             const uint32_t g = o >> 7, d = o & 127;
-            float acc = 0.0f;
-#pragma unroll 4
-            for (uint32_t j = 0; j < nkeys; ++j) acc = fmaf(ps[g * C + j], tile_at<KV>(vt + j * RS, d), acc);
+            // shared-memory instructions are the cost of this loop: four probabilities per load, two dependency chains
+            float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll 2
+            for (uint32_t j = 0; j < nkeys; j += 4) {
+                const float4 pj = *reinterpret_cast<const float4 *>(ps + g * C + j);
+                acc0 = fmaf(pj.x, tile_at<KV>(vt + j * RS, d), acc0);
+                if (j + 1 < nkeys) acc1 = fmaf(pj.y, tile_at<KV>(vt + (j + 1) * RS, d), acc1);
+                if (j + 2 < nkeys) acc0 = fmaf(pj.z, tile_at<KV>(vt + (j + 2) * RS, d), acc0);
+                if (j + 3 < nkeys) acc1 = fmaf(pj.w, tile_at<KV>(vt + (j + 3) * RS, d), acc1);
+            }
+            const float acc = acc0 + acc1;
             const uint32_t head = kh * Gq + g;
             if (nchunks == 1) {
                 ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(acc / red[8 + g]), epoch);
@@ -857,7 +874,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     p.block_ops = (const uint4 *)d_bops;
 
     // ---- shared memory ----
-    const size_t attn_bytes = (size_t)2 * C * attn_row_stride(m.kv) + (8 * 128 + 8 * C + 2 * max_chunks) * 4;
+    const size_t attn_bytes = (size_t)2 * C * attn_row_stride(m.kv) + (8 * 160 + 8 * C + 2 * max_chunks) * 4;
     p.xf_bytes = (uint32_t)((std::max<size_t>((size_t)max_cols * 4, attn_bytes) + 127) / 128 * 128);
     p.part_floats = (part_floats + 3) & ~3u;
     p.resid_floats = ((H + G - 1) / G + 4) & ~3u;
