@@ -54,7 +54,7 @@ struct TokOp {
     uint32_t type, qtype, cols, nmat;
     uint32_t rows[3], total_rows;
     uint32_t epilogue, scaled, log2S, nact;
-    uint32_t in_kind, in_op, save_resid, pad0;
+    uint32_t in_kind, in_op, save_resid, next_cols;  // next_cols: length of next_normw
     float eps;
     uint32_t pad1[3];
     const uint8_t *w[3];
@@ -63,6 +63,8 @@ struct TokOp {
     unsigned long long *out;
     const float *q_norm, *k_norm;
     uint8_t *kc, *vc;
+    const float *next_normw;  // norm weight of the operation after this one (null: none): staged in shared memory meanwhile
+    uint64_t pad2;
 };
 constexpr uint32_t OP_WORDS = sizeof(TokOp) / 4;
 constexpr uint32_t OPS_WORDS = OP_WORDS + 4;  // in shared memory the block's row counts follow the operation
@@ -74,7 +76,7 @@ struct TokParams {
     const SlotDesc *slots;
     const uint32_t *slot_begin;  // [grid + 1]
     const uint4 *block_ops;      // [nops][grid]: first output row, rows of segments 0 | 1 << 16, rows of segment 2, -
-    uint32_t nslot, xf_bytes, part_floats, resid_floats, sdesc_n;
+    uint32_t nslot, xf_bytes, part_floats, resid_floats, sdesc_n, nw_floats;
     uint32_t *state, *ids, *next_id, *out_ids;
     uint32_t out_cap;
     const uint8_t *embed;
@@ -159,7 +161,7 @@ __device__ __forceinline__ void embed_half_block(const uint8_t *table, uint32_t 
 // L1 cache is a few KB, so a stack frame (calls, spills) costs a trip to L2 per access.
 struct TokCtx {
     uint8_t *ring, *xfb;
-    float *part, *resid, *red;
+    float *part, *resid, *red, *nwbuf;
     uint4 *sdesc;
     uint64_t *full;
     uint32_t *done;
@@ -256,7 +258,7 @@ __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, co
                 if (e + 3 < c.hn) c.resid[e + 3] = v.w;
             }
             if (op.normw) {
-                const float4 nw = *reinterpret_cast<const float4 *>(op.normw + e0 + off[j]);
+                const float4 nw = *reinterpret_cast<const float4 *>(c.nwbuf + e0 + off[j]);
                 v.x *= nw.x; v.y *= nw.y; v.z *= nw.z; v.w *= nw.w;
             }
         }
@@ -559,7 +561,8 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
     c.xfb = c.ring + (size_t)p.nslot * SLOT_CAP;
     c.part = reinterpret_cast<float *>(c.xfb + p.xf_bytes);
     c.resid = c.part + p.part_floats;
-    c.sdesc = reinterpret_cast<uint4 *>(c.resid + p.resid_floats);  // descriptors of the slots this operation refills
+    c.nwbuf = c.resid + p.resid_floats;                              // norm weight of the current operation
+    c.sdesc = reinterpret_cast<uint4 *>(c.nwbuf + p.nw_floats);      // descriptors of the slots this operation refills
     c.full = reinterpret_cast<uint64_t *>(c.sdesc + p.sdesc_n);
     c.done = reinterpret_cast<uint32_t *>(c.full + p.nslot);
     c.red = reinterpret_cast<float *>(c.done + p.nslot);             // [48]
@@ -600,6 +603,14 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
     }
     fetch_op(0);
     __syncthreads();
+    {   // the first operation's norm weight (later ones are staged one operation ahead)
+        const TokOp &op0 = *reinterpret_cast<const TokOp *>(ops_s);
+        if (op0.normw)
+            for (uint32_t i = tid; i < op0.cols / 4; i += TK_THREADS) cp_async16(c.nwbuf + 4 * i, op0.normw + 4 * i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
     if (tid == 0) {
         uint32_t k = 0;
         for (; k < c.my_slots && k < p.nslot; ++k) issue_slot(c, c.myslots[k], k);
@@ -620,6 +631,10 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
         const uint32_t epoch_in = c.seq * EPOCH_SPAN + op.in_op + 1;
 
         TRACE(0);
+        if (op.next_normw) {  // the next operation's norm weight, copied while this one runs (the idle end of the block first)
+            for (uint32_t i = TK_THREADS - 1 - tid; i < op.next_cols / 4; i += TK_THREADS) cp_async16(c.nwbuf + 4 * i, op.next_normw + 4 * i);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         if (op.type == OP_GEMV) {
             const uint32_t lRPS = 4 - op.log2S, RPS = 1u << lRPS;
             const uint32_t total_slots = (((bo[1] & 0xffffu) + RPS - 1) >> lRPS) + (((bo[1] >> 16) + RPS - 1) >> lRPS) + ((bo[2] + RPS - 1) >> lRPS);
@@ -650,6 +665,7 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
             attention_op<KV>(c, op, oi, epoch, epoch_in, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
         }
         TRACE(6);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         TRACE(7);
     }
@@ -824,6 +840,15 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     BRASA_REQUIRE(ctx, m.head.rows == m.vocab && m.head.cols == H, "token program: unexpected lm_head shape");
     gemv_op(1, &m.head, EPI_LOGITS, true, m.final_norm, xa, x_op, nullptr, false);
     BRASA_REQUIRE(ctx, ops.size() + 2 < EPOCH_SPAN, "token program: too many operations");
+    uint32_t nw_floats = 0;
+    for (size_t i = 0; i < ops.size(); ++i) {
+        if (ops[i].normw) nw_floats = std::max(nw_floats, ops[i].cols);
+        if (i + 1 < ops.size() && ops[i + 1].normw) {
+            BRASA_REQUIRE(ctx, !ops[i].normw, "token program: two operations in a row with a norm weight");
+            ops[i].next_normw = ops[i + 1].normw;
+            ops[i].next_cols = ops[i + 1].cols;
+        }
+    }
 
     // ---- every block's slot list, in the order the kernel consumes it, and its rows of every operation ----
     std::vector<SlotDesc> slots;
@@ -879,7 +904,8 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     p.part_floats = (part_floats + 3) & ~3u;
     p.resid_floats = ((H + G - 1) / G + 4) & ~3u;
     p.sdesc_n = max_op_slots + L2_AHEAD;
-    const size_t fixed = p.xf_bytes + (size_t)(p.part_floats + p.resid_floats) * 4 + (size_t)p.sdesc_n * 16 + 48 * 4 + 2 * OPS_WORDS * 4 + 16;
+    p.nw_floats = (nw_floats + 3) & ~3u;
+    const size_t fixed = p.xf_bytes + (size_t)(p.part_floats + p.resid_floats + p.nw_floats) * 4 + (size_t)p.sdesc_n * 16 + 48 * 4 + 2 * OPS_WORDS * 4 + 16;
     BRASA_REQUIRE(ctx, fixed + 2 * (SLOT_CAP + 12) + 1024 <= ctx->smem_optin, "token program: the model's vectors do not fit shared memory");
     uint32_t nslot = (uint32_t)((ctx->smem_optin - 1024 - fixed) / (SLOT_CAP + 12));
     nslot &= ~1u;  // even: a ring slot always serves the same half of the warps
