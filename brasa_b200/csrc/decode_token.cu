@@ -305,12 +305,16 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
         const uint32_t qn = (n_slot + half_w - 1) >> lhw, in_slot = rwl * qn;
         const uint32_t nv = in_slot < n_slot ? min(qn, n_slot - in_slot) : 0u;
         const uint8_t *row0 = c.ring + (size_t)rs * SLOT_CAP + (size_t)in_slot * row_bytes;
+        uint32_t r = 0;
 #pragma unroll 1
-        for (uint32_t r = 0; r < nv; r += 2) {
-            const bool two = r + 1 < nv;
-            const uint8_t *row_a = row0 + (size_t)r * row_bytes, *row_b = two ? row_a + row_bytes : row_a;
-            float z = row_pair_dot<QT, NMAX>(row_a, row_b, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
-            if ((lane & 23) == 0 && (lane == 0 || two)) c.part[((sg_before + (ks << lRPS) + in_slot + r + (lane >> 3)) << lS) + slice] = z;
+        for (; r + 1 < nv; r += 2) {
+            const uint8_t *row_a = row0 + (size_t)r * row_bytes;
+            float z = row_pair_dot<QT, NMAX>(row_a, row_a + row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            if ((lane & 23) == 0) c.part[((sg_before + (ks << lRPS) + in_slot + r + (lane >> 3)) << lS) + slice] = z;
+        }
+        if (r < nv) {  // an odd row on its own: half the work of a pair (short last slots are shared out one row per warp)
+            float z = row_single_dot<QT, NMAX>(row0 + (size_t)r * row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            if (lane == 0) c.part[((sg_before + (ks << lRPS) + in_slot + r) << lS) + slice] = z;
         }
         __syncwarp();
         if (lane == 0 && kk + c.nslot < c.my_slots) {
@@ -396,7 +400,6 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
     uint8_t *kt = c.xfb, *vt = c.xfb + C * RS;
     float *qs = reinterpret_cast<float *>(vt + C * RS);  // [8][QS_HEAD]
     float *ps = qs + 8 * QS_HEAD;                        // [8][C]
-    float *ml = ps + 8 * C;                              // merge: m[max_chunks], l[max_chunks]
     float *red = c.red;
     const uint32_t nitems = kv_heads * nchunks;
 #pragma unroll 1
@@ -512,40 +515,58 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
 #pragma unroll 1
         for (uint32_t head = c.G - 1 - c.b; head < heads; head += c.G) {
             const unsigned long long *pp = partials + (size_t)head * max_chunks * 130;
-#pragma unroll 1
-            for (uint32_t ch = tid; ch < nchunks; ch += TK_THREADS) {
-                uint32_t raw[4];
-                ll_wait4(c, pp + (size_t)ch * 130, pp + (size_t)ch * 130 + 1, pp + (size_t)ch * 130, pp + (size_t)ch * 130 + 1, epoch, raw);
-                ml[ch] = __uint_as_float(raw[0]);
-                ml[max_chunks + ch] = __uint_as_float(raw[1]);
-            }
-            __syncthreads();
-            float M = -INFINITY;
-#pragma unroll 1
-            for (uint32_t ch = 0; ch < nchunks; ++ch) M = fmaxf(M, ml[ch]);
+            // thread (d, cg) merges the chunks cg, cg + 4, .. of output element d on its own (running maximum), four
+            // chunks per round trip with m, l and the accumulator in flight together; the four classes meet below
             const uint32_t d = tid & 127, cg = tid >> 7;
-            float L = 0.0f, a = 0.0f;
+            float M = -INFINITY, L = 0.0f, a = 0.0f;
 #pragma unroll 1
-            for (uint32_t ch = cg; ch < nchunks; ch += 16) {  // four of this thread's chunks per round trip
-                const uint32_t cc[4] = {ch, min(ch + 4, nchunks - 1), min(ch + 8, nchunks - 1), min(ch + 12, nchunks - 1)};
-                uint32_t raw[4];
-                ll_wait4(c, pp + (size_t)cc[0] * 130 + 2 + d, pp + (size_t)cc[1] * 130 + 2 + d, pp + (size_t)cc[2] * 130 + 2 + d,
-                         pp + (size_t)cc[3] * 130 + 2 + d, epoch, raw);
+            for (uint32_t ch = cg; ch < nchunks; ch += 16) {
+                uint32_t cc[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) cc[j] = min(ch + 4 * j, nchunks - 1);
+                unsigned long long w[12];
+                for (uint32_t it = 0;; ++it) {
+                    uint32_t bad = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const unsigned long long *q = pp + (size_t)cc[j] * 130;
+                        w[3 * j] = ll_load(q);
+                        w[3 * j + 1] = ll_load(q + 1);
+                        w[3 * j + 2] = ll_load(q + 2 + d);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 12; ++j) bad |= (uint32_t)(w[j] >> 32) ^ epoch;
+                    if (bad == 0 || *c.s_abort) break;
+                    if (it >= POLL_LIMIT) {
+                        give_up(c, 3);
+                        break;
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (ch + 4 * j < nchunks) {
-                        float w = expf(ml[cc[j]] - M);
-                        L = fmaf(ml[max_chunks + cc[j]], w, L);
-                        a = fmaf(__uint_as_float(raw[j]), w, a);
+                        const float mc = __uint_as_float((uint32_t)w[3 * j]), lc = __uint_as_float((uint32_t)w[3 * j + 1]);
+                        const float ac = __uint_as_float((uint32_t)w[3 * j + 2]);
+                        const float Mn = fmaxf(M, mc), so = expf(M - Mn), sn = expf(mc - Mn);  // M = -inf at first: so = 0
+                        L = L * so + lc * sn;
+                        a = a * so + ac * sn;
+                        M = Mn;
                     }
                 }
             }
+            // classes with no chunk keep M = -inf, L = a = 0
             qs[cg * 128 + d] = a;
-            if (d == 0) qs[512 + cg] = L;
+            if (d == 0) { qs[512 + cg] = L; qs[516 + cg] = M; }
             __syncthreads();
             if (tid < 128) {
-                float A = (qs[d] + qs[128 + d]) + (qs[256 + d] + qs[384 + d]);
-                float Lt = (qs[512] + qs[513]) + (qs[514] + qs[515]);
+                const float Mt = fmaxf(fmaxf(qs[516], qs[517]), fmaxf(qs[518], qs[519]));
+                float A = 0.0f, Lt = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float wj = qs[516 + j] == -INFINITY ? 0.0f : expf(qs[516 + j] - Mt);
+                    A = fmaf(qs[j * 128 + d], wj, A);
+                    Lt = fmaf(qs[512 + j], wj, Lt);
+                }
                 ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(A / Lt), epoch);
             }
             __syncthreads();

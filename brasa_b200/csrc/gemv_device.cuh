@@ -130,6 +130,27 @@ __device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_
     return z;
 }
 
+// One row only (the last row of an odd count): every lane ends up with the sum.
+template <int QT, int N>
+__device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb, uint32_t hi_off,
+                                                uint32_t sc_off, int lane, int nact = N) {
+    float acc_a = 0.0f;
+#pragma unroll
+    for (int it = 0; it < N; ++it) {
+        if (it < nact) {
+            const uint32_t hbi = min((slice * nact + it) * 32 + lane, nhb - 1);
+            uint2 ca = *reinterpret_cast<const uint2 *>(row_a + hbi * 8);
+            uint32_t ha = 0;
+            if (QT == BRASA_Q6_0) ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
+            float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
+            int sa = half_block_idot<QT>(ca, ha, xr[it]);
+            acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+    return acc_a;
+}
+
 // x to 22-bit fixed point: one half block (16 values, as the four quads that meet the low / high nibbles of code
 // word 0 and of code word 1) becomes a 64-byte record in xf: 12 byte-plane words, the sum of the integers, the step.
 __device__ __forceinline__ void x_half_block_to_fixed(uint4 *xf, uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) {
