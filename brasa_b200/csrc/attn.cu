@@ -10,7 +10,7 @@
 
 using namespace brasa_dev;
 
-int32_t brasa_flash_tc_launch(brasa_cmd *cmd, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh);
+int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh);
 
 namespace {
 
@@ -510,10 +510,10 @@ int32_t brasa_k_flash_attention_with(brasa_cmd *cmd, brasa_arg q, brasa_arg k, b
     uint64_t qn = (uint64_t)sh.tokens * sh.hq * 128;
     bool half_io = precision == BRASA_PREFILL_F16;
     BRASA_REQUIRE(ctx, arg_fits(q, qn * 4) && arg_fits(o, qn * (half_io ? 2 : 4)) && arg_fits(k, kvb) && arg_fits(v, kvb), "flash_attention: buffers too small");
-    // the F16 precision over an f16 cache runs on the tensor cores (BRASA_FLASH_TC=0 keeps the f32 kernel below)
+    // the F16 precision runs on the tensor cores (BRASA_FLASH_TC=0 keeps the f32 kernel below)
     static const bool tc_on = [] { const char *e = getenv("BRASA_FLASH_TC"); return !(e && e[0] == '0'); }();
-    if (half_io && sh.kv == BRASA_KV_F16 && tc_on && k.offset % 16 == 0 && v.offset % 16 == 0 && q.offset % 16 == 0 && o.offset % 16 == 0)
-        return brasa_flash_tc_launch(cmd, (const float *)arg_ptr(q), arg_ptr(k), arg_ptr(v), (__half *)arg_ptr(o), sh);
+    if (half_io && tc_on && k.offset % 16 == 0 && v.offset % 16 == 0 && q.offset % 16 == 0 && o.offset % 16 == 0)
+        return brasa_flash_tc_launch(cmd, sh.kv, (const float *)arg_ptr(q), arg_ptr(k), arg_ptr(v), (__half *)arg_ptr(o), sh);
     float scale = 1.0f / sqrtf((float)sh.dim);
     size_t smem = ((64 + 32 + 32) * TS + 64 * 33 + 3 * 64) * sizeof(float);
     dim3 grid((sh.tokens + 63) / 64, sh.hq);

@@ -1,10 +1,10 @@
 // Causal GQA prefill attention on the 5th-generation tensor cores (crates/kernels/src/lib.rs:1185-1248,
-// flash_attention.metal:184-323), for the F16 prefill precision over an f16 KV cache: Q * scale is rounded to f16,
+// flash_attention.metal:184-323), for the F16 prefill precision: Q * scale is rounded to f16,
 // S, P and O are f32, the output is f16.
 //
 // One CTA = 128 queries of one query head. Per 128-key tile, S = Q K^T is 8 tcgen05.mma (M = 128 queries, N = 128
 // keys, K = 16 dims each) into tensor memory; the softmax threads (one per query row) read their row with
-// tcgen05.ld. Softmax is done in two sweeps over the keys instead of rescaling O: the first sweep only finds each
+// tcgen05.ld (two threads per row, 64 columns each). Softmax is done in two sweeps over the keys instead of rescaling O: the first sweep only finds each
 // row's maximum m and sum l, the second recomputes S (tensor-core work is cheap next to everything else here),
 // forms P = exp(S - m) and accumulates O += P V in tensor memory. The reference keeps P in f32; a tensor core takes
 // f16 operands, so P goes in as two f16 terms (P = hi + lo, error 2^-22) and O += hi V + lo V.
@@ -75,17 +75,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
 
 struct FlashTcParams {
     const float *q;        // [tokens][hq][128] after QK-norm and RoPE
-    const uint8_t *kc, *vc;  // f16 cache rows [position][hkv][128] from position 0
+    const uint8_t *kc, *vc;  // cache rows [position][hkv][128] in the cache's type, from position 0
     __half *o;             // [tokens][hq][128]
     uint32_t tokens, hq, hkv, pos0;
     float scale;
     uint32_t *status;
 };
 
+template <int KV>
 __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
+    // an f16 cache enters the tensor core as it is; q8_0 and f32 rows are written as two f16 tiles (value = hi + lo,
+    // exact for q8_0, 2^-22 for f32) and every product with K or V becomes two
+    constexpr bool SPLIT = KV != BRASA_KV_F16;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *kt = smem + TILE_BYTES, *vt = smem + 2 * TILE_BYTES, *ph = smem + 3 * TILE_BYTES, *pl = smem + 4 * TILE_BYTES;
+    uint8_t *kl = smem + 5 * TILE_BYTES, *vl = smem + 6 * TILE_BYTES;  // low terms of K and V (SPLIT only)
     __shared__ uint64_t bar_s, bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
 
@@ -138,12 +143,30 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
         return false;
     };
     // rows [j * 128, j * 128 + 128) of one kv head's cache -> a swizzled tile; rows past the cache are zeros
-    auto load_tile = [&](const uint8_t *cache, uint8_t *tile, uint32_t j) {
+    auto load_tile = [&](const uint8_t *cache, uint8_t *tile, uint8_t *tile_lo, uint32_t j) {
         for (uint32_t i = tid; i < 128 * 16; i += 256) {
             const uint32_t r = i >> 4, c8 = (i & 15) * 8, key = j * 128 + r;
-            uint8_t *dst = tile + tile_chunk(r, c8);
-            if (key < lk) cp_async16(dst, cache + ((size_t)key * p.hkv + kh) * 256 + c8 * 2);
-            else *reinterpret_cast<uint4 *>(dst) = make_uint4(0, 0, 0, 0);
+            const uint32_t off = tile_chunk(r, c8);
+            if (!SPLIT) {
+                if (key < lk) cp_async16(tile + off, cache + ((size_t)key * p.hkv + kh) * 256 + c8 * 2);
+                else *reinterpret_cast<uint4 *>(tile + off) = make_uint4(0, 0, 0, 0);
+            } else {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+                if (key < lk) tile_load8<KV>(cache + ((size_t)key * p.hkv + kh) * KvRow<KV>::BYTES, (int)c8, v);
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const __half2 hh = __floats2half2_rn(v[e], v[e + 1]);
+                    const float2 hf = __half22float2(hh);
+                    const __half2 ll = __floats2half2_rn(v[e] - hf.x, v[e + 1] - hf.y);
+                    hi[e >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                    lo[e >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
+                }
+                *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4 *>(tile_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
         }
     };
     // instruction descriptors: D f32, A and B f16, M = N = 128; V is an MN-major B operand
@@ -154,20 +177,23 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
             umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kt) + off), idesc_s, ks > 0);
+            if (SPLIT) umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kl) + off), idesc_s, 1u);
         }
         umma_commit(&bar_s);
     };
 
-    const uint32_t row = (warp & 3) * 32 + lane;            // softmax threads are warps 0-3: one query row each
+    // softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63)
+    const uint32_t row = (warp & 3) * 32 + lane, chalf = (warp >> 2) * 64;
     const uint32_t qpos = p.pos0 + q0 + row;
     const uint32_t trow = ((warp & 3) * 32u) << 16;         // lane field of a tensor-memory address
+    constexpr float LOG2E = 1.4426950408889634f;
     float m = -INFINITY, l = 0.0f;
     uint32_t ph_s = 0, ph_o = 0;
     bool ok = true;
 
     // ---- sweep 1: row maxima and sums ----
     for (uint32_t j = 0; j < nkt && ok; ++j) {
-        load_tile(p.kc, kt, j);
+        load_tile(p.kc, kt, kl, j);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -176,37 +202,47 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s();
         }
-        if (warp < 4) {
-            ok = wait(&bar_s, ph_s);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        ok = wait(&bar_s, ph_s);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_s + trow + c, v);
-                    float cm = -INFINITY;
+            for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_s + trow + c, v);
+                float cm = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t key = j * 128 + c + i;
-                        const float s = key <= qpos ? __uint_as_float(v[i]) : -INFINITY;
-                        v[i] = __float_as_uint(s);
-                        cm = fmaxf(cm, s);
-                    }
-                    const float mn = fmaxf(m, cm);
-                    if (mn != -INFINITY) {
-                        float add = 0.0f;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) add += expf(__uint_as_float(v[i]) - mn);
-                        l = l * (m == -INFINITY ? 0.0f : expf(m - mn)) + add;
-                        m = mn;
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t key = j * 128 + c + i;
+                    const float sv = key <= qpos ? __uint_as_float(v[i]) : -INFINITY;
+                    v[i] = __float_as_uint(sv);
+                    cm = fmaxf(cm, sv);
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                const float mn = fmaxf(m, cm);
+                if (mn != -INFINITY) {
+                    float add = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) add += exp2f((__uint_as_float(v[i]) - mn) * LOG2E);
+                    l = l * (m == -INFINITY ? 0.0f : exp2f((m - mn) * LOG2E)) + add;
+                    m = mn;
+                }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
         ph_s ^= 1;
         ok = __syncthreads_and(ok);  // S has been read: the K tile and S may be overwritten
+    }
+    // the two halves of a row meet (the P tiles are free until the second sweep writes them)
+    {
+        float *stat = reinterpret_cast<float *>(ph);  // [2][128] maxima, then [2][128] sums
+        stat[(warp >> 2) * 128 + row] = m;
+        stat[256 + (warp >> 2) * 128 + row] = l;
+        __syncthreads();
+        const float m0 = stat[row], m1 = stat[128 + row], l0 = stat[256 + row], l1 = stat[384 + row];
+        const float M = fmaxf(m0, m1);
+        l = (m0 == -INFINITY ? 0.0f : l0 * exp2f((m0 - M) * LOG2E)) + (m1 == -INFINITY ? 0.0f : l1 * exp2f((m1 - M) * LOG2E));
+        m = M;
+        __syncthreads();
     }
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
@@ -215,8 +251,8 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
             ok = wait(&bar_o, ph_o);
             ph_o ^= 1;
         }
-        load_tile(p.kc, kt, j);
-        load_tile(p.vc, vt, j);
+        load_tile(p.kc, kt, kl, j);
+        load_tile(p.vc, vt, vl, j);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -226,37 +262,35 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s();
         }
-        if (warp < 4) {
-            ok = wait(&bar_s, ph_s);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        ok = wait(&bar_s, ph_s);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_s + trow + c, v);
-                    uint32_t hi[16], lo[16];
+            for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_s + trow + c, v);
+                uint32_t hi[16], lo[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const uint32_t key = j * 128 + c + i;
-                        const float p0 = key <= qpos ? expf(__uint_as_float(v[i]) - m) : 0.0f;
-                        const float p1 = key + 1 <= qpos ? expf(__uint_as_float(v[i + 1]) - m) : 0.0f;
-                        const __half2 hh = __floats2half2_rn(p0, p1);
-                        const float2 hf = __half22float2(hh);
-                        const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
-                        hi[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                        lo[i >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
-                    }
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
-                        const uint32_t off = tile_chunk(row, c + 8 * g);
-                        *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
-                        *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
-                    }
+                for (int i = 0; i < 32; i += 2) {
+                    const uint32_t key = j * 128 + c + i;
+                    const float p0 = key <= qpos ? exp2f((__uint_as_float(v[i]) - m) * LOG2E) : 0.0f;
+                    const float p1 = key + 1 <= qpos ? exp2f((__uint_as_float(v[i + 1]) - m) * LOG2E) : 0.0f;
+                    const __half2 hh = __floats2half2_rn(p0, p1);
+                    const float2 hf = __half22float2(hh);
+                    const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+                    hi[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                    lo[i >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                    const uint32_t off = tile_chunk(row, c + 8 * g);
+                    *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+                    *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+                }
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
         ph_s ^= 1;
         ok = __syncthreads_and(ok);
@@ -269,19 +303,20 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
                 const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
                 umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, 1u);
+                if (SPLIT) umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vl) + boff), idesc_o, 1u);  // lo x lo is below 2^-22
             }
             umma_commit(&bar_o);
         }
     }
     // ---- output: O / l, rounded to f16 ----
-    if (ok && warp < 4) {
+    if (ok) {
         ok = wait(&bar_o, ph_o);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l;
 #pragma unroll 1
-            for (int c = 0; c < 128; c += 32) {
+            for (uint32_t c = chalf; c < chalf + 64; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_o + trow + c, v);
                 if (row < nq) {
@@ -309,17 +344,24 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
 
 }  // namespace
 
-// F16 prefill precision over an f16 cache; q, k, v, o as for brasa_k_flash_attention_with (already validated there).
-int32_t brasa_flash_tc_launch(brasa_cmd *cmd, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh) {
+// F16 prefill precision over a cache of type kv; q, k, v, o as for brasa_k_flash_attention_with (already validated there).
+int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh) {
     brasa_ctx *ctx = cmd->ctx;
-    const size_t smem = 5 * TILE_BYTES + 1024;
-    static bool done = false;
-    if (!done) {
-        BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        done = true;
-    }
     FlashTcParams p{q, kc, vc, o, sh.tokens, sh.hq, sh.hkv, sh.pos0, 1.0f / sqrtf(128.0f), ctx->status};
     dim3 grid((sh.tokens + 127) / 128, sh.hq);
-    flash_tc_kernel<<<grid, 256, smem, ctx->stream>>>(p);
+#define LAUNCH_FTC(KVT, TILES)                                                                                              \
+    do {                                                                                                                   \
+        const size_t smem = (TILES) * TILE_BYTES + 1024;                                                                   \
+        static bool done = false;                                                                                          \
+        if (!done) {                                                                                                       \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            done = true;                                                                                                   \
+        }                                                                                                                  \
+        flash_tc_kernel<KVT><<<grid, 256, smem, ctx->stream>>>(p);                                                         \
+    } while (0)
+    if (kv == BRASA_KV_F16) LAUNCH_FTC(BRASA_KV_F16, 5);
+    else if (kv == BRASA_KV_F32) LAUNCH_FTC(BRASA_KV_F32, 7);
+    else LAUNCH_FTC(BRASA_KV_Q8_0, 7);
+#undef LAUNCH_FTC
     return brasa_post_launch(cmd, "flash_tc");
 }
