@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *kt = smem + TILE_BYTES, *vt = smem + 2 * TILE_BYTES, *ph = smem + 3 * TILE_BYTES, *pl = smem + 4 * TILE_BYTES;
-    uint8_t *kl = smem + 5 * TILE_BYTES, *vl = smem + 6 * TILE_BYTES;  // low terms of K and V (SPLIT only)
+    uint8_t *kl = smem + 5 * TILE_BYTES, *vl = smem + 6 * TILE_BYTES;  // SPLIT: low terms of K and V; else their second buffers
     __shared__ uint64_t bar_s, bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
 
@@ -172,11 +172,15 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     // instruction descriptors: D f32, A and B f16, M = N = 128; V is an MN-major B operand
     const uint32_t idesc_s = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     const uint32_t idesc_o = idesc_s | (1u << 16);
-    auto issue_s = [&]() {  // S = Q K^T
+    // An f16 cache leaves room for two K and two V buffers: the next tile's rows travel while this tile is worked on.
+    constexpr bool PIPE = !SPLIT;
+    auto KB = [&](uint32_t j) { return (PIPE && (j & 1)) ? kl : kt; };
+    auto VB = [&](uint32_t j) { return (PIPE && (j & 1)) ? vl : vt; };
+    auto issue_s = [&](const uint8_t *kb) {  // S = Q K^T
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kt) + off), idesc_s, ks > 0);
+            umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kb) + off), idesc_s, ks > 0);
             if (SPLIT) umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kl) + off), idesc_s, 1u);
         }
         umma_commit(&bar_s);
@@ -192,15 +196,25 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     bool ok = true;
 
     // ---- sweep 1: row maxima and sums ----
-    for (uint32_t j = 0; j < nkt && ok; ++j) {
-        load_tile(p.kc, kt, kl, j);
+    if (PIPE) {
+        load_tile(p.kc, KB(0), kl, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (uint32_t j = 0; j < nkt && ok; ++j) {
+        if (!PIPE) {
+            load_tile(p.kc, kt, kl, j);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s();
+            issue_s(KB(j));
+        }
+        if (PIPE && j + 1 < nkt) {  // the other K buffer was last read by S of tile j - 1, which this thread has seen finish
+            load_tile(p.kc, KB(j + 1), kl, j + 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
         ok = wait(&bar_s, ph_s);
         ok = __all_sync(0xffffffffu, ok);
@@ -246,23 +260,43 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     }
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
-    for (uint32_t j = 0; j < nkt && ok; ++j) {
-        if (j > 0) {  // the previous tile's P V must have finished reading V and P
-            ok = wait(&bar_o, ph_o);
-            ph_o ^= 1;
-        }
-        load_tile(p.kc, kt, kl, j);
-        load_tile(p.vc, vt, vl, j);
+    if (PIPE && ok) {
+        load_tile(p.kc, KB(0), kl, 0);
+        load_tile(p.vc, VB(0), vl, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (uint32_t j = 0; j < nkt && ok; ++j) {
+        if (!PIPE) {
+            if (j > 0) {  // the previous tile's P V must have finished reading V and P
+                ok = wait(&bar_o, ph_o);
+                ph_o ^= 1;
+            }
+            load_tile(p.kc, kt, kl, j);
+            load_tile(p.vc, vt, vl, j);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         ok = __syncthreads_and(ok);
         if (!ok) break;
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s();
+            issue_s(KB(j));
         }
-        ok = wait(&bar_s, ph_s);
+        if (PIPE && j + 1 < nkt) {
+            load_tile(p.kc, KB(j + 1), kl, j + 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        bool ok_o = true;
+        if (PIPE && j > 0) {  // P and the other V buffer are free once the previous tile's P V has finished
+            ok_o = wait(&bar_o, ph_o);
+            ph_o ^= 1;
+        }
+        if (PIPE && j + 1 < nkt) {
+            load_tile(p.vc, VB(j + 1), vl, j + 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        ok = wait(&bar_s, ph_s) && ok_o;
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -301,8 +335,8 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
             for (int ks = 0; ks < 8; ++ks) {
                 const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
                 const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
-                umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(vt) + boff), idesc_o, 1u);
+                umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
                 if (SPLIT) umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vl) + boff), idesc_o, 1u);  // lo x lo is below 2^-22
             }
             umma_commit(&bar_o);
@@ -359,7 +393,7 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
         }                                                                                                                  \
         flash_tc_kernel<KVT><<<grid, 256, smem, ctx->stream>>>(p);                                                         \
     } while (0)
-    if (kv == BRASA_KV_F16) LAUNCH_FTC(BRASA_KV_F16, 5);
+    if (kv == BRASA_KV_F16) LAUNCH_FTC(BRASA_KV_F16, 7);
     else if (kv == BRASA_KV_F32) LAUNCH_FTC(BRASA_KV_F32, 7);
     else LAUNCH_FTC(BRASA_KV_Q8_0, 7);
 #undef LAUNCH_FTC
