@@ -401,10 +401,20 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
     float *qs = reinterpret_cast<float *>(vt + C * RS);  // [8][QS_HEAD]
     float *ps = qs + 8 * QS_HEAD;                        // [8][C]
     float *red = c.red;
-    const uint32_t nitems = kv_heads * nchunks;
+    // A work item is (kv head, group of consecutive chunks). While the chunks are few there is one chunk per group;
+    // a long cache has more chunks than the grid has blocks per kv head, and a block then walks its group's chunks with
+    // a running maximum and sum, so that a head is merged from a dozen partial results instead of hundreds.
+    const uint32_t groups_max = max(1u, c.G / kv_heads);
+    const uint32_t cpg = (nchunks + groups_max - 1) / groups_max, ngroups = (nchunks + cpg - 1) / cpg;
+    const uint32_t nitems = kv_heads * ngroups;
 #pragma unroll 1
     for (uint32_t item = c.b; item < nitems; item += c.G) {
-        const uint32_t kh = item / nchunks, ch = item - kh * nchunks;
+        const uint32_t kh = item / ngroups, gi = item - kh * ngroups;
+        const uint32_t ch_lo = gi * cpg, ch_hi = min(nchunks, ch_lo + cpg);
+        float run[2] = {0.0f, 0.0f};  // this thread's output elements (two when the group has 8 query heads)
+        if (tid < 8) { red[16 + tid] = -INFINITY; red[24 + tid] = 0.0f; }  // running maximum and sum per head
+#pragma unroll 1
+        for (uint32_t ch = ch_lo; ch < ch_hi; ++ch) {
         const uint32_t key0 = ch * C, nkeys = min(C, lk - key0);
         const bool has_new = ch == nchunks - 1;
         const uint32_t nold = has_new ? nkeys - 1 : nkeys;
@@ -419,8 +429,8 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        if ((uint32_t)warp < Gq + 2 && ((uint32_t)warp < Gq || has_new)) {
-            // warps 0 .. Gq-1: a query head; warp Gq: the new key row; warp Gq + 1: the new value row
+        if ((uint32_t)warp < Gq + 2 && (((uint32_t)warp < Gq && ch == ch_lo) || ((uint32_t)warp >= Gq && has_new))) {
+            // warps 0 .. Gq-1: a query head (once per item); warp Gq: the new key row; warp Gq + 1: the new value row
             const uint32_t g = warp;
             const unsigned long long *src = g < Gq ? op.in + (size_t)(kh * Gq + g) * 128 : op.in + (size_t)(heads + (g - Gq) * kv_heads + kh) * 128;
             float xv[4], y[4], wv[4], cs[2], sn[2];
@@ -469,49 +479,66 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
         }
         __syncthreads();
         TRACE(3);
-        if ((uint32_t)warp < Gq) {  // softmax numerators of this chunk, head = warp
+        if ((uint32_t)warp < Gq) {  // softmax numerators of this chunk against the running maximum, head = warp
             const uint32_t g = warp;
             float v0 = ps[g * C + lane], v1 = C == 64 ? ps[g * C + lane + 32] : -INFINITY;
             float m = fmaxf(v0, v1);
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            v0 = expf(v0 - m);
-            v1 = C == 64 ? expf(v1 - m) : 0.0f;
+            const float m_old = red[16 + g], m_new = fmaxf(m_old, m);
+            v0 = expf(v0 - m_new);
+            v1 = C == 64 ? expf(v1 - m_new) : 0.0f;
             ps[g * C + lane] = v0;
             if (C == 64) ps[g * C + lane + 32] = v1;
             float l = v0 + v1;
             for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-            if (lane == 0) { red[g] = m; red[8 + g] = l; }
+            if (lane == 0) {
+                const float keep = m_old == -INFINITY ? 0.0f : expf(m_old - m_new);  // what the earlier chunks still weigh
+                red[32 + g] = keep;
+                red[24 + g] = red[24 + g] * keep + l;
+                red[16 + g] = m_new;
+            }
         }
         __syncthreads();
         TRACE(4);
-#pragma unroll 1
-        for (uint32_t o = tid; o < Gq * 128; o += TK_THREADS) {  // P V: one output element per thread
-            const uint32_t g = o >> 7, d = o & 127;
-            // shared-memory instructions are the cost of this loop: four probabilities per load, two dependency chains
-            float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+        for (int oi2 = 0; oi2 < 2; ++oi2) {  // P V: one output element per thread (two when Gq = 8)
+            const uint32_t o = tid + oi2 * TK_THREADS;
+            if (o < Gq * 128) {
+                const uint32_t g = o >> 7, d = o & 127;
+                // shared-memory instructions are the cost of this loop: four probabilities per load, two dependency chains
+                float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll 2
-            for (uint32_t j = 0; j < nkeys; j += 4) {
-                const float4 pj = *reinterpret_cast<const float4 *>(ps + g * C + j);
-                acc0 = fmaf(pj.x, tile_at<KV>(vt + j * RS, d), acc0);
-                if (j + 1 < nkeys) acc1 = fmaf(pj.y, tile_at<KV>(vt + (j + 1) * RS, d), acc1);
-                if (j + 2 < nkeys) acc0 = fmaf(pj.z, tile_at<KV>(vt + (j + 2) * RS, d), acc0);
-                if (j + 3 < nkeys) acc1 = fmaf(pj.w, tile_at<KV>(vt + (j + 3) * RS, d), acc1);
+                for (uint32_t j = 0; j < nkeys; j += 4) {
+                    const float4 pj = *reinterpret_cast<const float4 *>(ps + g * C + j);
+                    acc0 = fmaf(pj.x, tile_at<KV>(vt + j * RS, d), acc0);
+                    if (j + 1 < nkeys) acc1 = fmaf(pj.y, tile_at<KV>(vt + (j + 1) * RS, d), acc1);
+                    if (j + 2 < nkeys) acc0 = fmaf(pj.z, tile_at<KV>(vt + (j + 2) * RS, d), acc0);
+                    if (j + 3 < nkeys) acc1 = fmaf(pj.w, tile_at<KV>(vt + (j + 3) * RS, d), acc1);
+                }
+                run[oi2] = run[oi2] * red[32 + g] + (acc0 + acc1);
             }
-            const float acc = acc0 + acc1;
-            const uint32_t head = kh * Gq + g;
-            if (nchunks == 1) {
-                ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(acc / red[8 + g]), epoch);
-            } else {
-                unsigned long long *pp = partials + ((size_t)head * max_chunks + ch) * 130;
-                ll_store(pp + 2 + d, __float_as_uint(acc), epoch);
-                if (d == 0) { ll_store(pp, __float_as_uint(red[g]), epoch); ll_store(pp + 1, __float_as_uint(red[8 + g]), epoch); }
+        }
+        __syncthreads();
+        }  // chunks of the group
+#pragma unroll
+        for (int oi2 = 0; oi2 < 2; ++oi2) {
+            const uint32_t o = tid + oi2 * TK_THREADS;
+            if (o < Gq * 128) {
+                const uint32_t g = o >> 7, d = o & 127, head = kh * Gq + g;
+                if (ngroups == 1) {
+                    ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(run[oi2] / red[24 + g]), epoch);
+                } else {
+                    unsigned long long *pp = partials + ((size_t)head * max_chunks + gi) * 130;
+                    ll_store(pp + 2 + d, __float_as_uint(run[oi2]), epoch);
+                    if (d == 0) { ll_store(pp, __float_as_uint(red[16 + g]), epoch); ll_store(pp + 1, __float_as_uint(red[24 + g]), epoch); }
+                }
             }
         }
         __syncthreads();
     }
     TRACE(5);
-    if (nchunks > 1) {
-        // merge the chunks of a head; heads go to the blocks at the far end of the grid (the work items start at block 0)
+    if (ngroups > 1) {
+        // merge the groups of a head; heads go to the blocks at the far end of the grid (the work items start at block 0)
 #pragma unroll 1
         for (uint32_t head = c.G - 1 - c.b; head < heads; head += c.G) {
             const unsigned long long *pp = partials + (size_t)head * max_chunks * 130;
@@ -520,10 +547,10 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             const uint32_t d = tid & 127, cg = tid >> 7;
             float M = -INFINITY, L = 0.0f, a = 0.0f;
 #pragma unroll 1
-            for (uint32_t ch = cg; ch < nchunks; ch += 16) {
+            for (uint32_t ch = cg; ch < ngroups; ch += 16) {
                 uint32_t cc[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) cc[j] = min(ch + 4 * j, nchunks - 1);
+                for (int j = 0; j < 4; ++j) cc[j] = min(ch + 4 * j, ngroups - 1);
                 unsigned long long w[12];
                 for (uint32_t it = 0;; ++it) {
                     uint32_t bad = 0;
@@ -544,7 +571,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    if (ch + 4 * j < nchunks) {
+                    if (ch + 4 * j < ngroups) {
                         const float mc = __uint_as_float((uint32_t)w[3 * j]), lc = __uint_as_float((uint32_t)w[3 * j + 1]);
                         const float ac = __uint_as_float((uint32_t)w[3 * j + 2]);
                         const float Mn = fmaxf(M, mc), so = expf(M - Mn), sn = expf(mc - Mn);  // M = -inf at first: so = 0

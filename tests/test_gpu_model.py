@@ -346,3 +346,32 @@ def test_token_kernel_matches_kernel_per_operation_path(kv, monkeypatch, golden_
             assert top2[1] - top2[0] <= 2 * tol * scale, f"token {i}: {a} vs {b}"
             break
     assert len(ra) == len(rb) == 16
+
+
+@pytest.mark.gpu
+def test_token_kernel_long_cache_groups_chunks(monkeypatch, golden_dir):
+    """Past (SMs / kv heads) attention chunks a block of the whole-token kernel walks several chunks with a running
+    maximum and sum: 2 700 positions of an f32 cache (32-key chunks, 2 kv heads) are well beyond that point. Logits must
+    match the kernel-per-operation path within the f32-cache tolerance of crates/models/tests/forward.rs:40-55."""
+    import brasa_b200 as B
+    n_prompt, steps = 2700, 5
+    prompt = np.random.default_rng(8).integers(0, 512, n_prompt).astype(np.uint32)
+    runs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("BRASA_TOKEN_KERNEL", mode)
+        ctx = B.Context(0)
+        m = B.Qwen3.load(ctx, golden_dir / "tiny" / "model.brasa", B.Limits(ctx=2816, max_tokens=128, max_logit_rows=1, kv=B.KvType.F32))
+        m.set_prefill_precision(B.PrefillPrecision.F32)
+        lg = None
+        for off in range(0, n_prompt, 128):
+            lg, _ = m.forward(prompt[off:off + 128], off)
+        tok = int(np.argmax(lg[0]))
+        logits = []
+        for i in range(steps):
+            lg, _ = m.forward([tok], n_prompt + i)
+            logits.append(lg[0].copy())
+            tok = int(np.argmax(lg[0]))
+        runs[mode] = np.stack(logits)
+        m.free()
+    a, b = runs["0"], runs["1"]
+    assert np.abs(a - b).max() <= 1e-4 * np.abs(a).max()
