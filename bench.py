@@ -44,7 +44,7 @@ SEED = 20251
 GATE_UP_TRAFFIC_BYTES = 28_130_000
 # dram__bytes_read + dram__bytes_write of one decode_token_kernel launch at position 512, from the ncu capture summarised
 # in profiles/decode_token_kernel_qwen3_4b.md (algorithmic bytes at that position: 2 436 050 976)
-TOKEN_KERNEL_TRAFFIC_BYTES = 2_451_680_000
+TOKEN_KERNEL_TRAFFIC_BYTES = 2_453_830_000
 METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
 WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
 
