@@ -17,6 +17,8 @@
 // leaves its loop, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 
+#include <cmath>
+
 #include "brasa_internal.h"
 #include "gemv_device.cuh"
 
@@ -63,19 +65,20 @@ struct GemmTcParams {
     uint32_t *status;
 };
 
-template <int MT, int G>
+template <int MT, int G, int NB>
 __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the dynamic shared memory base is only 16-byte aligned by contract: round up to the swizzle atom
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const uint32_t stage_bytes = MT * A_TILE + B_TILE;
+    constexpr uint32_t BNT = BN * NB;  // weight rows of this CTA: one MMA covers them all (N = 128 or 256)
+    const uint32_t stage_bytes = MT * A_TILE + NB * B_TILE;
     __shared__ uint64_t full_x[8], full_w[8], empty[8], acc_full;
     __shared__ uint32_t tmem_base_s, abort_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // which matrix and which 128 rows of it
+    // which matrix and which BNT rows of it
     const uint32_t mi = (blockIdx.x >= p.tile_end[0]) + (blockIdx.x >= p.tile_end[1]);
-    const uint32_t n0 = (blockIdx.x - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BN, tok0 = blockIdx.y * (MT * BM);
+    const uint32_t n0 = (blockIdx.x - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BNT, tok0 = blockIdx.y * (MT * BM);
     const uint8_t *wmat = mi == 0 ? p.w[0] : (mi == 1 ? p.w[1] : p.w[2]);
     float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
     const uint32_t yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
@@ -91,8 +94,8 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory for the accumulators: MT x 128 columns
-        uint32_t ncols = MT * BN;
+    if (warp == 1) {  // tensor memory for the accumulators: MT x BNT columns
+        uint32_t ncols = MT * BNT;
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -137,8 +140,8 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // instruction descriptor: D f32, A and B f16, both K-major, N = 128, M = 128
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // instruction descriptor: D f32, A and B f16, both K-major, N = BNT, M = 128
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (uint32_t k = 0; k < nk && ok; ++k) {
                 const uint32_t s = k % NS, ph = (k / NS) & 1;
@@ -155,7 +158,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                            ::"r"(tmem_base + mt * BN), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+                            ::"r"(tmem_base + mt * BNT), "l"(da), "l"(db), "r"(idesc), "r"(acc)
                             : "memory");
                     }
                 }
@@ -172,22 +175,23 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         constexpr uint32_t GT = 256 / G;  // threads of a group
         const uint32_t dt = tid - 128, grp = dt / GT, gt = dt % GT;
         const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
-        const uint8_t *wp[G];
-        const uint8_t *sp[G];
-        uint32_t soff[G];
+        constexpr int UN = G * NB;  // units of a thread per stage
+        const uint8_t *wp[UN];
+        const uint8_t *sp[UN];
+        uint32_t soff[UN];
 #pragma unroll
-        for (int i = 0; i < G; ++i) {
-            const uint32_t u = gt + i * GT, wr = u & 127, blk = u >> 7;
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t u = gt + i * GT, wr = u & (BNT - 1), blk = u / BNT;
             wp[i] = wmat + (size_t)(n0 + wr) * row_bytes + blk * 16;
             sp[i] = wmat + (size_t)(n0 + wr) * row_bytes + sc_off + blk * 2;
             soff[i] = (wr >> 3) * 1024 + (wr & 7) * 128 + (blk << 16) + ((wr & 7) << 20);  // row offset | block | row & 7
         }
-        uint4 cwq[G];
-        unsigned short scq[G];
+        uint4 cwq[UN];
+        unsigned short scq[UN];
         {
             const uint32_t kj = min(grp, nk - 1);
 #pragma unroll
-            for (int i = 0; i < G; ++i) {
+            for (int i = 0; i < UN; ++i) {
                 cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kj * 32);
                 scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kj * 4);
             }
@@ -195,11 +199,11 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         bool ok = true;
         for (uint32_t k = grp; k < nk && ok; k += G) {
             const uint32_t s = k % NS;
-            uint4 cw[G];
-            unsigned short sc[G];
+            uint4 cw[UN];
+            unsigned short sc[UN];
             const uint32_t kn = min(k + G, nk - 1);  // this group's next stage: in flight during this one
 #pragma unroll
-            for (int i = 0; i < G; ++i) {
+            for (int i = 0; i < UN; ++i) {
                 cw[i] = cwq[i];
                 sc[i] = scq[i];
                 cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kn * 32);
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             if (!ok) break;
             uint8_t *btile = smem + (size_t)s * stage_bytes + MT * A_TILE;
 #pragma unroll
-            for (int i = 0; i < G; ++i) {
+            for (int i = 0; i < UN; ++i) {
                 const uint32_t r8 = soff[i] >> 20, blk = (soff[i] >> 16) & 1;
                 uint8_t *brow = btile + (soff[i] & 0xffffu);
                 const __half2 d2 = __half2half2(__ushort_as_half(sc[i]));
@@ -243,14 +247,14 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3;           // the lane quarter of tensor memory this warp may read
-            const int c_begin = ((warp - 4) >> 2) * (BN / 2);  // two warps per quarter: half of the columns each
+            const int c_begin = ((warp - 4) >> 2) * (BNT / 2);  // two warps per quarter: half of the columns each
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t token = tok0 + mt * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int c = c_begin; c < c_begin + BN / 2; c += 16) {
+                for (int c = c_begin; c < c_begin + (int)BNT / 2; c += 16) {
                     uint32_t v[16];
-                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BN + c;
+                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BNT + c;
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t ncols = MT * BN;
+        uint32_t ncols = MT * BNT;
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
     }
 }
@@ -305,15 +309,40 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, count >= 1 && count <= 3, "gemm: 1 to 3 matrices");
     GemmTcParams p{};
+    bool rows256 = true;
+    uint32_t tiles128 = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols, "gemm: shape not taken by the tensor-core kernel");
+        BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(ys[i]) & 15) == 0, "gemm: misaligned y");
+        rows256 = rows256 && ws[i].rows % 256 == 0;
+        tiles128 += ws[i].rows / BN;
+    }
+    // Shape of a CTA: MT token tiles of 128 x NB weight tiles of 128 rows (MT x NB x 128 accumulator columns <= 512).
+    // Every CTA reads its token tiles' X once per launch, so X crosses L2 -> SM (weight tiles / NB) times: the
+    // estimate is the larger of that traffic at about 4.5 TB/s and waves x stages x cycles per stage of one CTA.
+    const uint32_t ntile = (tokens + BM - 1) / BM, nkst = ws[0].cols / BK;
+    uint32_t mt = 1, nb = 1;
+    double best = 1e30;
+    for (uint32_t b = 1; b <= (rows256 ? 2u : 1u); ++b) {
+        for (uint32_t c = 1; c * b <= 4 && c <= std::max(1u, ntile); c *= 2) {
+            const double ctas = (double)(tiles128 / b) * ((ntile + c - 1) / c), waves = std::ceil(ctas / ctx->sm_count);
+            const double pipe = waves * nkst * (300.0 * c * b + 400.0);
+            const double xbytes = (double)(tiles128 / b) * ((ntile + c - 1) / c) * c * BM * ws[0].cols * 2.0;
+            const double cost = std::max(pipe, xbytes * 1.965e9 / 4.5e12);
+            if (cost < best * 0.999 || (cost < best * 1.001 && c * b > mt * nb)) {
+                best = cost;
+                mt = c;
+                nb = b;
+            }
+        }
+    }
     uint32_t ncta_n = 0;
     for (uint32_t i = 0; i < 3; ++i) {
         if (i < count) {
-            BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols, "gemm: shape not taken by the tensor-core kernel");
-            BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(ys[i]) & 15) == 0, "gemm: misaligned y");
             p.w[i] = arg_ptr(ws[i].data);
             p.y[i] = ys[i];
             p.rows[i] = ws[i].rows;
-            ncta_n += ws[i].rows / BN;
+            ncta_n += ws[i].rows / (BN * nb);
         }
         p.tile_end[i] = ncta_n;
     }
@@ -327,20 +356,7 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
-    // tokens per CTA (1, 2 or 4 tiles of 128): the choice with the least estimated time, waves of CTAs x cycles per
-    // stage of one CTA (tensor core: about 300 cycles per token tile; conversion and hand-over: at least 450)
-    const uint32_t ntile = (tokens + BM - 1) / BM;
-    uint32_t mt = 1;
-    uint64_t best = ~0ull;
-    for (uint32_t c = 1; c <= 4 && c <= std::max(1u, ntile); c *= 2) {
-        const uint64_t ctas = (uint64_t)ncta_n * ((ntile + c - 1) / c), waves = (ctas + ctx->sm_count - 1) / ctx->sm_count;
-        const uint64_t cost = waves * std::max<uint64_t>(300ull * c, 450);
-        if (cost <= best) {
-            best = cost;
-            mt = c;
-        }
-    }
-    const uint32_t stage_bytes = mt * A_TILE + B_TILE;
+    const uint32_t stage_bytes = mt * A_TILE + nb * B_TILE;
     uint32_t stages = (uint32_t)std::min<size_t>(8, (ctx->smem_optin - 4096) / stage_bytes);
     stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, w.cols / BK));
     const size_t smem = (size_t)stages * stage_bytes + 1024;
@@ -349,19 +365,21 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     p.stages = stages;
     p.status = ctx->status;
     dim3 grid(ncta_n, (ntile + mt - 1) / mt);
-#define LAUNCH_TC(MTV, GV)                                                                                                        \
+#define LAUNCH_TC(MTV, GV, NBV)                                                                                                        \
     do {                                                                                                                         \
         static bool done = false;                                                                                                \
         if (!done) {                                                                                                             \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV, NBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
             done = true;                                                                                                         \
         }                                                                                                                        \
-        gemm_tc_kernel<MTV, GV><<<grid, 384, smem, ctx->stream>>>(tmap, p);                                                          \
+        gemm_tc_kernel<MTV, GV, NBV><<<grid, 384, smem, ctx->stream>>>(tmap, p);                                                          \
     } while (0)
     // conversion groups: as many stages in flight as the ring holds, at most four
-    if (mt == 1) LAUNCH_TC(1, 4);
-    else if (mt == 2) LAUNCH_TC(2, 4);
-    else LAUNCH_TC(4, 2);
+    if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1);
+    else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1);
+    else if (nb == 1) LAUNCH_TC(4, 2, 1);
+    else if (mt == 1) LAUNCH_TC(1, 2, 2);
+    else LAUNCH_TC(2, 2, 2);
 #undef LAUNCH_TC
     return brasa_post_launch(cmd, "gemm_tc");
 }
