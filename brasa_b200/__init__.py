@@ -153,6 +153,10 @@ def lib() -> C.CDLL:
         L.brasa_model_free.restype = None
         L.brasa_session_free.restype = None
         L.brasa_graph_free.restype = None
+        L.brasa_batch_free.restype = None
+        L.brasa_batch_free.argtypes = [C.c_void_p]
+        L.brasa_batch_sequences.argtypes = [C.c_void_p]
+        L.brasa_batch_pages_in_use.argtypes = [C.c_void_p]
         for name in ("brasa_ctx_destroy", "brasa_model_free", "brasa_session_free", "brasa_buf_free", "brasa_buf_ptr", "brasa_buf_bytes",
                      "brasa_ctx_stream", "brasa_session_model", "brasa_graph_free"):
             getattr(L, name).argtypes = [C.c_void_p]
@@ -714,3 +718,56 @@ class Session:
                                                      out.ctypes.data_as(C.c_void_p), C.byref(st)))
         stats = GenStats(st.prompt_tokens, st.reused_tokens, st.prefill_ms, st.ttft_ms, st.generated, st.decode_ms, _STOP.get(st.stop, "?"))
         return out[:st.generated].copy(), stats
+
+
+class Batch:
+    """Many independent sequences of one model decoded together over a paged KV pool, with a prefix shared by all of
+    them computed once (the reference's single cached prefix, crates/runtime/src/session.rs:230-237, for many sequences)."""
+
+    PAGE = 16
+
+    def __init__(self, model: "Qwen3", max_seqs: int, num_pages: int, max_positions: int):
+        self.model, self.ctx = model, model.ctx
+        self._h = C.c_void_p()
+        self.ctx._check(lib().brasa_batch_create(model._h, C.c_uint32(max_seqs), C.c_uint32(num_pages), C.c_uint32(max_positions), C.byref(self._h)))
+
+    def free(self):
+        if self._h and self.ctx._h:
+            lib().brasa_batch_free(self._h)
+        self._h = C.c_void_p()
+
+    def set_prefix(self, ids):
+        a = np.ascontiguousarray(ids, dtype=np.uint32)
+        self.ctx._check(lib().brasa_batch_set_prefix(self._h, a.ctypes.data_as(C.c_void_p), C.c_uint32(a.size)))
+
+    def add_sequence(self, ids, params: SamplingParams | None = None) -> int:
+        params = params or SamplingParams.greedy()
+        a = np.ascontiguousarray(ids, dtype=np.uint32)
+        seq = C.c_uint32(0)
+        sp = _SamplingParams(params.temperature, params.top_k, params.top_p, params.seed)
+        self.ctx._check(lib().brasa_batch_add_sequence(self._h, a.ctypes.data_as(C.c_void_p), C.c_uint32(a.size), sp, C.byref(seq)))
+        return int(seq.value)
+
+    @property
+    def sequences(self) -> int:
+        return int(lib().brasa_batch_sequences(self._h))
+
+    @property
+    def pages_in_use(self) -> int:
+        return int(lib().brasa_batch_pages_in_use(self._h))
+
+    def decode(self, steps: int, params: SamplingParams | None = None):
+        """Returns (ids [sequences][steps + 1] with the token drawn at add time first, device seconds)."""
+        params = params or SamplingParams.greedy()
+        n = self.sequences
+        out = np.zeros((n, steps + 1), np.uint32)
+        secs = C.c_double(0.0)
+        sp = _SamplingParams(params.temperature, params.top_k, params.top_p, params.seed)
+        self.ctx._check(lib().brasa_batch_decode(self._h, C.c_uint32(steps), sp, out.ctypes.data_as(C.c_void_p), C.byref(secs)))
+        return out, float(secs.value)
+
+    def peek_logits(self) -> np.ndarray:
+        n = self.sequences
+        out = np.zeros((n, self.model.cfg["vocab"]), np.float32)
+        self.ctx._check(lib().brasa_batch_peek_logits(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out

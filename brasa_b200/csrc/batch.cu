@@ -1,0 +1,489 @@
+// Batched decode over a paged KV pool: many independent sequences of one model decoded together, one token each per
+// step (the serving case the reference handles one process at a time: crates/daemon/src/engine.rs:1-3 keeps a single
+// model thread, crates/runtime/src/session.rs:230-237 reuses one cached prefix).
+//
+// KV lives in pages of 16 positions, [layer][page][16][kv head][128] in the model's cache type; a sequence is a list
+// of pages. A prefix shared by every sequence is computed once and its pages are attached to each sequence, the
+// reference's prefix reuse generalised from one cached sequence to many. Prefill keeps using the model's contiguous
+// cache (the prefix stays resident there at positions [0, P), a sequence's own tokens are prefilled after it) and the
+// new rows are then copied into that sequence's pages, so the prefill kernels need no page tables. A decode step runs
+// the layer sequence of qwen3.rs:763-831 for `n` tokens at once: projections as GEMMs (f16 inputs above 8 sequences,
+// like a prefill chunk), QK-norm + RoPE + page store with one position per sequence, paged split-K attention, and the
+// batched sampler with one PCG32 stream per sequence.
+#include <memory>
+
+#include "attn_device.cuh"
+#include "model_internal.h"
+
+using namespace brasa_dev;
+
+int32_t brasa_sample_batched_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t count, float temperature, uint32_t top_k, float top_p,
+                                    unsigned long long *rng, float *scratch, uint32_t *out);
+
+namespace {
+
+constexpr uint32_t PAGE = 16;
+constexpr int D = 128, TS = D + 4;
+
+struct Paged {
+    const uint8_t *pool;     // this layer's pages
+    const int32_t *table;    // [seq][max_pages]
+    uint32_t max_pages, hkv;
+};
+
+template <int KV>
+__device__ __forceinline__ const uint8_t *paged_row(const Paged &p, uint32_t seq, uint32_t key, uint32_t kh) {
+    const int32_t page = p.table[(size_t)seq * p.max_pages + key / PAGE];
+    return p.pool + (((size_t)page * PAGE + key % PAGE) * p.hkv + kh) * KvRow<KV>::BYTES;
+}
+
+// rows [key0, key0 + nkeys) of one kv head of one sequence -> ts[key][d] as f32
+template <int KV>
+__device__ __forceinline__ void load_tile_paged(const Paged &p, uint32_t seq, float *ts, uint32_t key0, uint32_t nkeys, uint32_t kh) {
+    for (uint32_t i = threadIdx.x; i < nkeys * (D / 8); i += blockDim.x) {
+        const uint32_t key = i / (D / 8), v8 = i % (D / 8);
+        float v[8];
+        tile_load8<KV>(paged_row<KV>(p, seq, key0 + key, kh), (int)(v8 * 8), v);
+        float *o = ts + key * TS + v8 * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[j];
+    }
+}
+
+// One block per (128-key chunk, kv head, sequence); partial layout per (sequence, head, chunk): m, l, acc[128]
+// (the layout of crates/kernels/src/lib.rs:1335 with a sequence dimension in front).
+template <int KV>
+__global__ void __launch_bounds__(128) decode_partial_paged_kernel(const float *q, Paged kp, Paged vp, const uint32_t *lens, float *partials, uint32_t hq,
+                                                                   uint32_t max_chunks, float scale) {
+    extern __shared__ __align__(16) float sm[];
+    float *ts = sm, *qs = ts + 128 * TS, *ps = qs + 8 * D, *red = ps + 8 * 128;
+    const uint32_t chunk = blockIdx.x, kh = blockIdx.y, seq = blockIdx.z, hkv = kp.hkv, G = hq / hkv;
+    const uint32_t lk = lens[seq] + 1;  // the new token's row is already in its page
+    if (chunk * 128 >= lk) return;
+    const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    for (uint32_t i = t; i < G * D; i += 128) qs[i] = q[((size_t)seq * hq + kh * G) * D + i];
+    load_tile_paged<KV>(kp, seq, ts, key0, nkeys, kh);
+    __syncthreads();
+    for (uint32_t g = 0; g < G; ++g) {
+        float s = -INFINITY;
+        if ((uint32_t)t < nkeys) {
+            const float4 *kr = reinterpret_cast<const float4 *>(ts + t * TS), *qr = reinterpret_cast<const float4 *>(qs + g * D);
+            float a = 0.0f;
+#pragma unroll 8
+            for (int i = 0; i < D / 4; ++i) {
+                float4 kk = kr[i], qq = qr[i];
+                a = fmaf(qq.x, kk.x, a); a = fmaf(qq.y, kk.y, a); a = fmaf(qq.z, kk.z, a); a = fmaf(qq.w, kk.w, a);
+            }
+            s = a * scale;
+        }
+        ps[g * 128 + t] = s;
+    }
+    __syncthreads();
+    load_tile_paged<KV>(vp, seq, ts, key0, nkeys, kh);  // K is no longer needed
+    for (uint32_t g = 0; g < G; ++g) {
+        float s = ps[g * 128 + t], m = s;
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        float p = (uint32_t)t < nkeys ? expf(s - m) : 0.0f;
+        ps[g * 128 + t] = p;
+        float l = p;
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        __syncthreads();
+        if (lane == 0) red[4 + warp] = l;
+        __syncthreads();
+        if (t == 0) {
+            float *out = partials + (((size_t)seq * hq + kh * G + g) * max_chunks + chunk) * 130;
+            out[0] = m;
+            out[1] = (red[4] + red[5]) + (red[6] + red[7]);
+        }
+    }
+    __syncthreads();
+    for (uint32_t g = 0; g < G; ++g) {
+        float acc = 0.0f;
+        const float *pg = ps + g * 128;
+        for (uint32_t j = 0; j < nkeys; ++j) acc = fmaf(pg[j], ts[j * TS + t], acc);
+        partials[(((size_t)seq * hq + kh * G + g) * max_chunks + chunk) * 130 + 2 + t] = acc;
+    }
+}
+
+// grid (head, sequence); output f32 or f16 (the input type of the o_proj GEMM)
+template <bool HALF_OUT>
+__global__ void __launch_bounds__(128) decode_reduce_paged_kernel(const float *partials, const uint32_t *lens, void *o, uint32_t hq, uint32_t max_chunks) {
+    const uint32_t h = blockIdx.x, seq = blockIdx.y, t = threadIdx.x;
+    const uint32_t chunks = (lens[seq] + 1 + 127) / 128;
+    const float *p = partials + ((size_t)seq * hq + h) * max_chunks * 130;
+    float M = -INFINITY;
+    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, p[c * 130]);
+    float L = 0.0f, acc = 0.0f;
+    for (uint32_t c = 0; c < chunks; ++c) {
+        float w = expf(p[c * 130] - M);
+        L = fmaf(p[c * 130 + 1], w, L);
+        acc = fmaf(p[c * 130 + 2 + t], w, acc);
+    }
+    const size_t idx = ((size_t)seq * hq + h) * D + t;
+    if (HALF_OUT) reinterpret_cast<__half *>(o)[idx] = __float2half_rn(acc / L);
+    else reinterpret_cast<float *>(o)[idx] = acc / L;
+}
+
+// Per-head RMSNorm + RoPE of q and k (in place) and the page store of k and v, one token per sequence at that
+// sequence's own position (its current length). One warp per row.
+template <int KV>
+__global__ void __launch_bounds__(128) qk_norm_rope_store_paged_kernel(float *q, float *k, const float *v, const float *q_norm, const float *k_norm,
+                                                                       const float *cos_t, const float *sin_t, uint8_t *kpool, uint8_t *vpool,
+                                                                       const int32_t *table, uint32_t max_pages, const uint32_t *lens, uint32_t hq,
+                                                                       uint32_t hkv, float eps, uint32_t rows) {
+    __shared__ __align__(16) uint8_t scratch[4][528];
+    const uint32_t gr = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (gr >= rows) return;
+    const uint32_t per_tok = hq + 2 * hkv, t = gr / per_tok, r = gr % per_tok, pos = lens[t];
+    const size_t slot = (size_t)table[(size_t)t * max_pages + pos / PAGE] * PAGE + pos % PAGE;
+    if (r >= hq + hkv) {
+        const uint32_t kh = r - hq - hkv;
+        float y[4];
+        for (int j = 0; j < 4; ++j) y[j] = v[((size_t)t * hkv + kh) * 128 + lane + 32 * j];
+        put_row<KV>(vpool + (slot * hkv + kh) * KvRow<KV>::BYTES, scratch[warp], y, lane);
+        return;
+    }
+    const bool is_q = r < hq;
+    float *x = is_q ? q + ((size_t)t * hq + r) * 128 : k + ((size_t)t * hkv + (r - hq)) * 128;
+    float y[4];
+    norm_rope_row(x, is_q ? q_norm : k_norm, cos_t, sin_t, pos, eps, lane, y);
+    for (int j = 0; j < 4; ++j) x[lane + 32 * j] = y[j];
+    if (!is_q) put_row<KV>(kpool + (slot * hkv + (r - hq)) * KvRow<KV>::BYTES, scratch[warp], y, lane);
+}
+
+// Rows [p0, p0 + n) of every layer of the contiguous cache -> the pages of one sequence (16-byte units).
+__global__ void pages_from_cache_kernel(const uint8_t *cache, uint8_t *pool, const int32_t *table_row, uint32_t p0, uint32_t n, uint32_t row_bytes,
+                                        size_t cache_layer_bytes, size_t pool_layer_bytes) {
+    const uint32_t layer = blockIdx.y, units = row_bytes / 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n * units; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t pos = p0 + (uint32_t)(i / units), u = (uint32_t)(i % units);
+        const uint4 val = *reinterpret_cast<const uint4 *>(cache + layer * cache_layer_bytes + (size_t)pos * row_bytes + (size_t)u * 16);
+        const size_t slot = (size_t)table_row[pos / PAGE] * PAGE + pos % PAGE;
+        *reinterpret_cast<uint4 *>(pool + layer * pool_layer_bytes + slot * row_bytes + (size_t)u * 16) = val;
+    }
+}
+
+__global__ void gather_ids_kernel(uint32_t *dst, const uint32_t *src, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[i];
+}
+__global__ void bump_lens_kernel(uint32_t *lens, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) lens[i] += 1;
+}
+
+}  // namespace
+
+struct brasa_batch {
+    brasa_model *m = nullptr;
+    brasa_ctx *ctx = nullptr;
+    uint32_t max_seqs = 0, num_pages = 0, max_pages = 0;  // max_pages: per sequence
+    uint32_t nseq = 0, next_page = 0, prefix_len = 0;
+    size_t row_bytes = 0, pool_layer_bytes = 0, cache_layer_bytes = 0;
+    uint64_t max_chunks = 0;
+    brasa_buf *kpool = nullptr, *vpool = nullptr, *table = nullptr, *lens = nullptr, *ids = nullptr, *rng = nullptr, *logits = nullptr,
+              *partials = nullptr, *scratch = nullptr, *out = nullptr;
+    std::vector<int32_t> h_table;  // host mirror [max_seqs][max_pages]
+    std::vector<uint32_t> h_lens;
+    std::vector<brasa_buf *> owned;
+};
+
+namespace {
+
+int32_t balloc(brasa_batch *b, uint64_t bytes, brasa_buf **out) {
+    BRASA_TRY(brasa_buf_alloc(b->ctx, bytes, out));
+    b->owned.push_back(*out);
+    return BRASA_OK;
+}
+
+int32_t upload_table_row(brasa_batch *b, uint32_t seq) {
+    return brasa_buf_upload(b->table, (uint64_t)seq * b->max_pages * 4, b->h_table.data() + (size_t)seq * b->max_pages, (uint64_t)b->max_pages * 4);
+}
+
+// copies positions [p0, p0 + n) of the model's contiguous cache into the pages of sequence `seq`
+int32_t copy_rows_to_pages(brasa_batch *b, brasa_cmd *cmd, uint32_t seq, uint32_t p0, uint32_t n) {
+    if (n == 0) return BRASA_OK;
+    brasa_model *m = b->m;
+    dim3 grid(std::min<uint32_t>(1024, (uint32_t)(((size_t)n * (b->row_bytes / 16) + 255) / 256)), m->cfg.layers);
+    const int32_t *row = (const int32_t *)b->table->ptr + (size_t)seq * b->max_pages;
+    pages_from_cache_kernel<<<grid, 256, 0, b->ctx->stream>>>((const uint8_t *)m->kc->ptr, (uint8_t *)b->kpool->ptr, row, p0, n, (uint32_t)b->row_bytes,
+                                                              b->cache_layer_bytes, b->pool_layer_bytes);
+    BRASA_TRY(brasa_post_launch(cmd, "pages_from_cache"));
+    pages_from_cache_kernel<<<grid, 256, 0, b->ctx->stream>>>((const uint8_t *)m->vc->ptr, (uint8_t *)b->vpool->ptr, row, p0, n, (uint32_t)b->row_bytes,
+                                                              b->cache_layer_bytes, b->pool_layer_bytes);
+    return brasa_post_launch(cmd, "pages_from_cache");
+}
+
+// prefill of `n` tokens at positions [pos0, pos0 + n) through the model's contiguous cache, in chunks of max_tokens;
+// the logits of the last token stay in the model's logits buffer
+int32_t prefill_contiguous(brasa_batch *b, const uint32_t *ids, uint32_t n, uint32_t pos0) {
+    brasa_model *m = b->m;
+    for (uint32_t off = 0; off < n; off += m->limits.max_tokens) {
+        const uint32_t c = std::min(m->limits.max_tokens, n - off);
+        BRASA_TRY(brasa_model_forward(m, ids + off, c, pos0 + off, 1, nullptr, nullptr));
+    }
+    return BRASA_OK;
+}
+
+// One decode step for the first n sequences: ids[n] -> logits[n][vocab]. Uses the model's workspace (n <= max_tokens).
+int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
+    brasa_model *m = b->m;
+    brasa_ctx *ctx = b->ctx;
+    const brasa_config &c = m->cfg;
+    const uint32_t H = c.hidden;
+    const bool half_io = n > GEMV_MAX_TOKENS && m->prefill_precision == BRASA_PREFILL_F16;
+    const int32_t prec = half_io ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32;
+    auto mm = [&](const Matrix &w, brasa_arg x, brasa_arg y) -> int32_t {
+        if (n <= GEMV_MAX_TOKENS) return brasa_k_gemv(cmd, w.q, x, y, n);
+        return brasa_k_gemm_with(cmd, w.q, x, y, n, prec);
+    };
+    BRASA_TRY(brasa_k_embed(cmd, m->embed.q, A(b->ids), A(m->x), n));
+    const uint32_t rows = n * (c.heads + 2 * c.kv_heads);
+    const float scale = 1.0f / sqrtf(128.0f);
+    const size_t smem = (128 * TS + 8 * D + 8 * 128 + 16) * sizeof(float);
+    for (uint32_t li = 0; li < c.layers; ++li) {
+        Layer &l = m->layers[li];
+        brasa_arg xin;
+        if (half_io) {
+            BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.attn_norm), A(m->xh), n, H, c.eps));
+            xin = A(m->xh);
+        } else {
+            BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.attn_norm), A(m->norm_out), n, H, c.eps));
+            xin = A(m->norm_out);
+        }
+        if (n > GEMV_MAX_TOKENS) {
+            brasa_qmatrix wqkv[3] = {l.wq.q, l.wk.q, l.wv.q};
+            brasa_arg yqkv[3] = {A(m->q), A(m->k_new), A(m->v_new)};
+            BRASA_TRY(brasa_k_gemm_multi(cmd, wqkv, 3, xin, yqkv, n, prec));
+        } else {
+            BRASA_TRY(mm(l.wq, xin, A(m->q)));
+            BRASA_TRY(mm(l.wk, xin, A(m->k_new)));
+            BRASA_TRY(mm(l.wv, xin, A(m->v_new)));
+        }
+        uint8_t *kl = (uint8_t *)b->kpool->ptr + li * b->pool_layer_bytes, *vl = (uint8_t *)b->vpool->ptr + li * b->pool_layer_bytes;
+        const int32_t *table = (const int32_t *)b->table->ptr;
+        const uint32_t *lens = (const uint32_t *)b->lens->ptr;
+        Paged kp{kl, table, b->max_pages, c.kv_heads}, vp{vl, table, b->max_pages, c.kv_heads};
+        dim3 agrid((uint32_t)b->max_chunks, c.kv_heads, n), rgrid(c.heads, n);
+        void *attn_out = half_io ? m->xh->ptr : m->attn->ptr;
+#define LAUNCH_BATCH(KVT)                                                                                                                        \
+    do {                                                                                                                                         \
+        static bool done = false;                                                                                                                \
+        if (!done) {                                                                                                                             \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
+            done = true;                                                                                                                         \
+        }                                                                                                                                        \
+        qk_norm_rope_store_paged_kernel<KVT><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm),   \
+                                                                                     F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages,  \
+                                                                                     lens, c.heads, c.kv_heads, c.eps, rows);                     \
+        BRASA_TRY(brasa_post_launch(cmd, "qk_norm_rope_store_paged"));                                                                           \
+        decode_partial_paged_kernel<KVT><<<agrid, 128, smem, ctx->stream>>>(F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, \
+                                                                           scale);                                                               \
+        BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged"));                                                                               \
+    } while (0)
+        if (m->limits.kv == BRASA_KV_F32) LAUNCH_BATCH(BRASA_KV_F32);
+        else if (m->limits.kv == BRASA_KV_F16) LAUNCH_BATCH(BRASA_KV_F16);
+        else LAUNCH_BATCH(BRASA_KV_Q8_0);
+#undef LAUNCH_BATCH
+        if (half_io) decode_reduce_paged_kernel<true><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
+        else decode_reduce_paged_kernel<false><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
+        BRASA_TRY(brasa_post_launch(cmd, "decode_reduce_paged"));
+        BRASA_TRY(mm(l.wo, half_io ? A(m->xh) : A(m->attn), A(m->h)));
+        BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)n * H));
+        brasa_arg act;
+        if (half_io) {
+            BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
+            BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), A(m->xh), n));
+            act = A(m->xh);
+        } else {
+            BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.ffn_norm), A(m->norm_out), n, H, c.eps));
+            BRASA_TRY(mm(l.gate, A(m->norm_out), A(m->gate)));
+            BRASA_TRY(mm(l.up, A(m->norm_out), A(m->up)));
+            BRASA_TRY(brasa_k_swiglu(cmd, A(m->gate), A(m->up), A(m->gate), (uint64_t)n * c.ffn));
+            act = A(m->gate);
+        }
+        BRASA_TRY(mm(l.down, act, A(m->h)));
+        BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)n * H));
+    }
+    if (half_io) {
+        BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(m->final_norm), A(m->xh), n, H, c.eps));
+        return brasa_k_gemm_with(cmd, m->head.q, A(m->xh), A(b->logits), n, BRASA_PREFILL_F16);
+    }
+    BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(m->final_norm), A(m->norm_out), n, H, c.eps));
+    return brasa_k_gemv(cmd, m->head.q, A(m->norm_out), A(b->logits), n);
+}
+
+}  // namespace
+
+extern "C" {
+
+void brasa_batch_free(brasa_batch *b) {
+    if (!b) return;
+    for (brasa_buf *x : b->owned) brasa_buf_free(x);
+    delete b;
+}
+
+int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages, uint32_t max_positions, brasa_batch **out) {
+    if (!m || !out) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_REQUIRE(ctx, max_seqs >= 1 && max_seqs <= m->limits.max_tokens, "batch: 1 to max_tokens (%u) sequences", m->limits.max_tokens);
+    BRASA_REQUIRE(ctx, m->cfg.head_dim == 128 && m->cfg.heads % m->cfg.kv_heads == 0 && m->cfg.heads / m->cfg.kv_heads <= 8,
+                  "batch: head_dim 128 and a GQA group of at most 8");
+    BRASA_REQUIRE(ctx, max_positions >= PAGE && max_positions <= m->limits.ctx, "batch: max_positions within the model's context");
+    std::unique_ptr<brasa_batch, void (*)(brasa_batch *)> b(new brasa_batch, brasa_batch_free);
+    b->m = m;
+    b->ctx = ctx;
+    b->max_seqs = max_seqs;
+    b->num_pages = num_pages;
+    b->max_pages = (max_positions + PAGE - 1) / PAGE;
+    const uint64_t kvd = (uint64_t)m->cfg.kv_heads * 128;
+    b->row_bytes = brasa_kv_bytes(m->limits.kv, kvd);
+    b->pool_layer_bytes = (size_t)num_pages * PAGE * b->row_bytes;
+    b->cache_layer_bytes = (size_t)m->cap * b->row_bytes;
+    b->max_chunks = ((uint64_t)b->max_pages * PAGE + 127) / 128;
+    BRASA_TRY(balloc(b.get(), (uint64_t)m->cfg.layers * b->pool_layer_bytes, &b->kpool));
+    BRASA_TRY(balloc(b.get(), (uint64_t)m->cfg.layers * b->pool_layer_bytes, &b->vpool));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * b->max_pages * 4, &b->table));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 4, &b->lens));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 4, &b->ids));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 4, &b->out));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 16, &b->rng));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.vocab * 4, &b->logits));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.heads * b->max_chunks * 130 * 4, &b->partials));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 2 * m->cfg.vocab * 4, &b->scratch));
+    b->h_table.assign((size_t)max_seqs * b->max_pages, 0);
+    b->h_lens.assign(max_seqs, 0);
+    *out = b.release();
+    return BRASA_OK;
+}
+
+// The prefix every sequence starts with: computed once, kept in the model's contiguous cache at [0, n) and in shared pages.
+int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n) {
+    if (!b || (!ids && n)) return BRASA_EINVAL;
+    brasa_ctx *ctx = b->ctx;
+    BRASA_REQUIRE(ctx, b->nseq == 0 && b->next_page == 0, "batch: the prefix comes before the sequences");
+    BRASA_REQUIRE(ctx, n % PAGE == 0, "batch: the shared prefix must fill whole pages of %u positions", PAGE);
+    BRASA_REQUIRE(ctx, n / PAGE <= b->max_pages && n / PAGE <= b->num_pages, "batch: prefix longer than the page budget");
+    b->prefix_len = n;
+    if (n == 0) return BRASA_OK;
+    BRASA_TRY(prefill_contiguous(b, ids, n, 0));
+    // shared pages 0 .. n/16 - 1, listed in row 0 of the table for the copy
+    for (uint32_t i = 0; i < n / PAGE; ++i) b->h_table[i] = (int32_t)i;
+    b->next_page = n / PAGE;
+    BRASA_TRY(upload_table_row(b, 0));
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = copy_rows_to_pages(b, cmd, 0, 0, n);
+    int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+    BRASA_TRY(rc);
+    return rc2;
+}
+
+// A new sequence: the shared prefix followed by its own n tokens (n >= 1). Its first generated token is drawn from
+// the logits of its last prompt token with its own PCG32 stream (params.seed + sequence index).
+int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n, brasa_sampling_params params, uint32_t *seq_out) {
+    if (!b || !ids) return BRASA_EINVAL;
+    brasa_ctx *ctx = b->ctx;
+    brasa_model *m = b->m;
+    BRASA_REQUIRE(ctx, b->nseq < b->max_seqs, "batch: all %u sequence slots are in use", b->max_seqs);
+    BRASA_REQUIRE(ctx, n >= 1 && (uint64_t)b->prefix_len + n < (uint64_t)b->max_pages * PAGE, "batch: sequence longer than max_positions");
+    const uint32_t seq = b->nseq, total = b->prefix_len + n;
+    // pages: the shared ones, then own pages for every position this sequence may reach
+    const uint32_t shared = b->prefix_len / PAGE, own = b->max_pages - shared;
+    BRASA_REQUIRE(ctx, b->next_page + own <= b->num_pages, "batch: out of KV pages (%u of %u in use)", b->next_page, b->num_pages);
+    int32_t *row = b->h_table.data() + (size_t)seq * b->max_pages;
+    for (uint32_t i = 0; i < shared; ++i) row[i] = (int32_t)i;
+    for (uint32_t i = 0; i < own; ++i) row[shared + i] = (int32_t)(b->next_page + i);
+    b->next_page += own;
+    BRASA_TRY(upload_table_row(b, seq));
+    BRASA_TRY(prefill_contiguous(b, ids, n, b->prefix_len));
+    uint64_t st[2];
+    brasa_pcg32_seed(params.seed + seq, st);
+    BRASA_TRY(brasa_buf_upload(b->rng, (uint64_t)seq * 16, st, 16));
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = copy_rows_to_pages(b, cmd, seq, b->prefix_len, n);
+    if (rc == BRASA_OK)
+        rc = brasa_sample_batched_launch(cmd, F(m->logits), m->cfg.vocab, 1, params.temperature, params.top_k, params.top_p,
+                                         (unsigned long long *)b->rng->ptr + 2 * seq, F(b->scratch) + (size_t)seq * 2 * m->cfg.vocab,
+                                         (uint32_t *)b->ids->ptr + seq);
+    int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+    BRASA_TRY(rc);
+    BRASA_TRY(rc2);
+    b->h_lens[seq] = total;
+    BRASA_TRY(brasa_buf_upload(b->lens, (uint64_t)seq * 4, &total, 4));
+    b->nseq = seq + 1;
+    if (seq_out) *seq_out = seq;
+    return BRASA_OK;
+}
+
+// `steps` tokens for every sequence, on the device: step s feeds each sequence its previous token, samples the next.
+// out_ids[seq * (steps + 1) + s]: s = 0 is the token drawn at add time, then the steps' tokens.
+int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params params, uint32_t *out_ids, double *gpu_seconds) {
+    if (!b) return BRASA_EINVAL;
+    brasa_ctx *ctx = b->ctx;
+    brasa_model *m = b->m;
+    const uint32_t n = b->nseq;
+    BRASA_REQUIRE(ctx, n >= 1, "batch: no sequences");
+    for (uint32_t s = 0; s < n; ++s)
+        BRASA_REQUIRE(ctx, (uint64_t)b->h_lens[s] + steps <= (uint64_t)b->max_pages * PAGE, "batch: sequence %u would pass max_positions", s);
+    std::vector<uint32_t> tok(n);
+    if (out_ids) {
+        BRASA_TRY(brasa_buf_download(b->ids, 0, tok.data(), (uint64_t)n * 4));
+        for (uint32_t s = 0; s < n; ++s) out_ids[(size_t)s * (steps + 1)] = tok[s];
+    }
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+    int32_t rc = BRASA_OK;
+    std::vector<uint32_t> all((size_t)n * steps);
+    brasa_buf *hist = nullptr;
+    rc = brasa_buf_alloc(ctx, std::max<uint64_t>(4, (uint64_t)n * steps * 4), &hist);
+    for (uint32_t s = 0; s < steps && rc == BRASA_OK; ++s) {
+        rc = encode_step(b, cmd, n);
+        if (rc != BRASA_OK) break;
+        rc = brasa_sample_batched_launch(cmd, F(b->logits), m->cfg.vocab, n, params.temperature, params.top_k, params.top_p,
+                                         (unsigned long long *)b->rng->ptr, F(b->scratch), (uint32_t *)b->out->ptr);
+        if (rc != BRASA_OK) break;
+        gather_ids_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>((uint32_t *)b->ids->ptr, (const uint32_t *)b->out->ptr, n);
+        rc = brasa_post_launch(cmd, "next_ids");
+        if (rc != BRASA_OK) break;
+        gather_ids_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>((uint32_t *)hist->ptr + (size_t)s * n, (const uint32_t *)b->out->ptr, n);
+        rc = brasa_post_launch(cmd, "history");
+        if (rc != BRASA_OK) break;
+        bump_lens_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>((uint32_t *)b->lens->ptr, n);
+        rc = brasa_post_launch(cmd, "advance_lengths");
+    }
+    int32_t rc2 = brasa_cmd_wait(cmd, gpu_seconds);
+    if (rc == BRASA_OK) rc = rc2;
+    if (rc == BRASA_OK && out_ids && steps) {
+        rc = brasa_buf_download(hist, 0, all.data(), (uint64_t)n * steps * 4);
+        for (uint32_t s = 0; s < steps; ++s)
+            for (uint32_t q = 0; q < n; ++q) out_ids[(size_t)q * (steps + 1) + 1 + s] = all[(size_t)s * n + q];
+    }
+    if (hist) brasa_buf_free(hist);
+    if (rc == BRASA_OK)
+        for (uint32_t s = 0; s < n; ++s) b->h_lens[s] += steps;
+    return rc;
+}
+
+// Logits of every sequence's next token for its current input token, without sampling or advancing (tests).
+int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits) {
+    if (!b || !logits) return BRASA_EINVAL;
+    brasa_cmd *cmd;
+    BRASA_TRY(brasa_cmd_begin(b->ctx, &cmd));
+    int32_t rc = encode_step(b, cmd, b->nseq);
+    int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+    BRASA_TRY(rc);
+    BRASA_TRY(rc2);
+    return brasa_buf_download(b->logits, 0, logits, (uint64_t)b->nseq * b->m->cfg.vocab * 4);
+}
+
+uint32_t brasa_batch_sequences(brasa_batch *b) { return b ? b->nseq : 0; }
+uint32_t brasa_batch_pages_in_use(brasa_batch *b) { return b ? b->next_page : 0; }
+
+}  // extern "C"

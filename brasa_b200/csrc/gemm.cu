@@ -54,7 +54,8 @@ __device__ __forceinline__ void dequant_block(const WView &w, uint32_t r, uint32
                 int byte = codes[j & 15];
                 int lo = j < 16 ? (byte & 15) : (byte >> 4);
                 int ww = (j & 15) >> 2, k = 2 * (j & 3) + (j >> 4);
-                out[j] = d * (float)((lo | (((hw[ww >> 1] >> q6_hi_bitpos(ww & 1, k)) & 3) << 4)) - 32);
+                int h2 = (int)((hw[ww >> 1] >> q6_hi_bitpos(ww & 1, k)) & 3u);   // signed before the bias is removed
+                out[j] = d * (float)((lo | (h2 << 4)) - 32);
             }
             return;
         }

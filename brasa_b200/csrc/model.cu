@@ -15,6 +15,7 @@
 #include "brasa_internal.h"
 #include "decode_token.h"
 #include "host_util.h"
+#include "model_internal.h"
 
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
@@ -26,49 +27,6 @@ int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next
 int32_t brasa_attn_decode_fused_launch(brasa_cmd *cmd, int32_t kv, const float *q, const float *k_new, const float *v_new, const float *q_norm,
                                        const float *k_norm, const float *cos_t, const float *sin_t, uint8_t *kc, uint8_t *vc, float *partials,
                                        uint32_t *counters, float *o, const uint32_t *pos, uint32_t hq, uint32_t hkv, uint32_t ctx_len, float eps);
-
-namespace {
-
-constexpr uint32_t GEMV_MAX_TOKENS = 8;  // qwen3.rs:276
-
-struct Matrix {
-    brasa_buf *buf = nullptr;
-    brasa_qmatrix q{};
-};
-
-struct Layer {
-    brasa_buf *attn_norm, *q_norm, *k_norm, *ffn_norm;
-    Matrix wq, wk, wv, wo, gate, up, down;
-};
-
-inline brasa_arg A(brasa_buf *b, uint64_t off = 0) { return brasa_arg{b, off}; }
-inline float *F(brasa_buf *b, uint64_t off_floats = 0) { return (float *)b->ptr + off_floats; }
-
-}  // namespace
-
-struct brasa_model {
-    brasa_ctx *ctx = nullptr;
-    brasa_config cfg{};
-    brasa_limits limits{};
-    int32_t prefill_precision = BRASA_PREFILL_F16;
-    Matrix embed, head;  // head aliases embed when tied
-    brasa_buf *final_norm = nullptr;
-    std::vector<Layer> layers;
-    brasa_buf *rope_cos = nullptr, *rope_sin = nullptr;
-    brasa_buf *kc = nullptr, *vc = nullptr;  // [layers, cap, kv_heads, head_dim] in the cache type
-    uint32_t cap = 0;
-    // workspace
-    brasa_buf *x = nullptr, *h = nullptr, *q = nullptr, *k_new = nullptr, *v_new = nullptr, *attn = nullptr, *xh = nullptr,
-              *gate = nullptr, *up = nullptr, *ids = nullptr, *norm_out = nullptr, *ss = nullptr, *partials = nullptr, *logits = nullptr,
-              *next_id = nullptr, *out_ids = nullptr, *dev_state = nullptr;  // dev_state: u32 pos, out_count, attention counters
-    brasa_graph *decode_graph = nullptr;  // one decode step: embed .. lm_head, argmax, advance
-    brasa_token_program *token_prog = nullptr;  // the same step as one persistent kernel, when the shapes allow
-    bool token_prog_tried = false;
-    uint64_t partials_len = 0;
-    brasa_allocated alloc{};
-    std::vector<brasa_buf *> owned;
-    uint32_t *pinned_id = nullptr;  // pinned host word for the per-step token read
-};
 
 namespace {
 

@@ -141,6 +141,11 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float *logits, uint3
     __shared__ float sh[32];
     __shared__ uint32_t shk[32];
     const uint32_t tid = threadIdx.x;
+    // one block per sequence: its logits row, its weights, its PCG32 state, its output word
+    logits += (size_t)blockIdx.x * n;
+    w += (size_t)blockIdx.x * 2 * n;
+    rng += 2 * blockIdx.x;
+    out += blockIdx.x;
     // largest key: the maximum logit in the total order
     uint32_t kmax = 0;
     for (uint32_t i = tid; i < n; i += blockDim.x) kmax = max(kmax, order_key(logits[i]));
@@ -204,7 +209,35 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float *logits, uint3
     }
 }
 
+// greedy choice per row: first index of the maximum, NaN ignored, 0 when every logit is -inf
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *logits, uint32_t n, uint32_t *out) {
+    __shared__ Best sh[32];
+    const float *v = logits + (size_t)blockIdx.x * n;
+    Best b{-INFINITY, 0xffffffffu};
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float x = v[i];
+        if (x > b.v) b = Best{x, i};
+    }
+    b = block_best(b, sh);
+    if (threadIdx.x == 0) out[blockIdx.x] = (b.v == -INFINITY || b.i == 0xffffffffu) ? 0u : b.i;
+}
+
 }  // namespace
+
+// Sampler::sample for `count` rows of n logits at once: row r uses the PCG32 state at rng + 2 r and scratch of 2 n floats
+// at scratch + 2 n r; out[r] receives its token.
+int32_t brasa_sample_batched_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t count, float temperature, uint32_t top_k, float top_p,
+                                    unsigned long long *rng, float *scratch, uint32_t *out) {
+    brasa_ctx *ctx = cmd->ctx;
+    if (count == 0) return BRASA_OK;
+    if (temperature <= 0.0f) {
+        argmax_rows_kernel<<<count, 1024, 0, ctx->stream>>>(logits, n, out);
+        return brasa_post_launch(cmd, "argmax_rows");
+    }
+    BRASA_REQUIRE(ctx, top_p > 0.0f, "sample_top_p: top_p must be positive");
+    sample_kernel<<<count, 1024, 0, ctx->stream>>>(logits, n, temperature, top_k, top_p, rng, scratch, out, nullptr, nullptr, nullptr);
+    return brasa_post_launch(cmd, "sample_top_p");
+}
 
 int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
                              uint32_t *pos) {

@@ -298,6 +298,26 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
                                brasa_sampling_params params, brasa_token_cb on_token, void *user,
                                uint32_t *out_ids, brasa_gen_stats *stats);
 
+/* ---- batched decode over a paged KV pool (serving: many independent sequences of one model) -------------------
+ * No counterpart in the reference, which serves one sequence per process (crates/daemon/src/engine.rs:1-3) and
+ * reuses one cached prefix (crates/runtime/src/session.rs:230-237); this is that prefix reuse for many sequences.
+ * KV pages hold BRASA_KV_PAGE positions in the model's cache type. */
+#define BRASA_KV_PAGE 16
+typedef struct brasa_batch brasa_batch;
+/* up to max_seqs sequences (<= the model's max_tokens) of at most max_positions positions each, num_pages pages in all */
+int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages, uint32_t max_positions, brasa_batch **out);
+void brasa_batch_free(brasa_batch *b);
+/* the prefix every sequence shares (a multiple of BRASA_KV_PAGE tokens, possibly 0): prefilled once, its pages attached to every sequence */
+int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n);
+/* a sequence = the shared prefix + its own n >= 1 tokens; prefills them, draws its first token (PCG32 seed = params.seed + index) */
+int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n, brasa_sampling_params params, uint32_t *seq_out);
+/* `steps` tokens for every sequence; out_ids[seq * (steps + 1) + s], s = 0 being the token drawn when the sequence was added */
+int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params params, uint32_t *out_ids, double *gpu_seconds);
+/* logits [sequences][vocab] of the next token of every sequence, without sampling or advancing */
+int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits);
+uint32_t brasa_batch_sequences(brasa_batch *b);
+uint32_t brasa_batch_pages_in_use(brasa_batch *b);
+
 #ifdef __cplusplus
 }
 #endif

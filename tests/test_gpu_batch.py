@@ -1,0 +1,120 @@
+"""Batched decode over the paged KV pool against the single-sequence path: a sequence decoded inside a batch must give
+what it gives alone (crates/runtime/tests/session.rs:53-60: prefix reuse never changes the output)."""
+import numpy as np
+import pytest
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    import brasa_b200
+    return brasa_b200
+
+
+def alone(B, ctx, path, kvt, prompt, steps):
+    """Greedy decode of one sequence through the single-sequence model: (logits per step, tokens)."""
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=kvt))
+    try:
+        lg = None
+        for off in range(0, len(prompt), 64):
+            lg, _ = m.forward(prompt[off:off + 64], off)
+        tok = int(np.argmax(lg[0]))
+        toks, logits = [tok], []
+        for i in range(steps):
+            lg, _ = m.forward([tok], len(prompt) + i)
+            logits.append(lg[0].copy())
+            tok = int(np.argmax(lg[0]))
+            toks.append(tok)
+        return np.stack(logits), toks
+    finally:
+        m.free()
+
+
+@pytest.mark.parametrize("kv,nseq", [("f32", 3), ("f16", 3), ("q8_0", 2), ("f16", 12)])
+def test_batch_matches_sequences_decoded_alone(B, golden_dir, kv, nseq):
+    kvt = {"f32": B.KvType.F32, "f16": B.KvType.F16, "q8_0": B.KvType.Q8_0}[kv]
+    path = golden_dir / "tiny" / "model.brasa"
+    rng = np.random.default_rng(31)
+    prefix = rng.integers(0, 512, 32).astype(np.uint32)
+    suffixes = [rng.integers(0, 512, int(n)).astype(np.uint32) for n in rng.integers(1, 40, nseq)]
+    steps = 20
+    ctx = B.Context(0)
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=kvt))
+    bt = B.Batch(m, max_seqs=nseq, num_pages=2 + nseq * 8, max_positions=128)
+    try:
+        bt.set_prefix(prefix)
+        for sfx in suffixes:
+            bt.add_sequence(sfx)
+        assert bt.sequences == nseq and bt.pages_in_use == 2 + nseq * 6
+        first = bt.peek_logits()
+        ids, secs = bt.decode(steps)
+        assert secs > 0 and ids.shape == (nseq, steps + 1)
+    finally:
+        bt.free()
+        m.free()
+    # above 8 sequences the projections are f16-input GEMMs, like a prefill chunk: the looser bound of that precision
+    tol = {"f32": 1e-4, "f16": 1e-3, "q8_0": 2e-2}[kv] if nseq <= 8 else 5e-3
+    for s, sfx in enumerate(suffixes):
+        want_logits, want_toks = alone(B, ctx, path, kvt, np.concatenate([prefix, sfx]), steps)
+        scale = np.abs(want_logits[0]).max()
+        assert ids[s, 0] == want_toks[0]
+        assert np.abs(first[s] - want_logits[0]).max() <= tol * scale
+        # same tokens as long as the margin between the two best logits is clear of the tolerance
+        for i in range(steps):
+            if int(ids[s, i + 1]) != want_toks[i + 1]:
+                top2 = np.sort(want_logits[i])[-2:]
+                assert top2[1] - top2[0] <= 4 * tol * scale, (s, i)
+                break
+
+
+def test_batch_sampling_uses_one_stream_per_sequence(B, golden_dir):
+    """The first token of sequence i is drawn from its prompt's last logits with Pcg32(seed + i), exactly like the
+    oracle's sampler on the same logits."""
+    path = golden_dir / "tiny" / "model.brasa"
+    rng = np.random.default_rng(5)
+    prefix = rng.integers(0, 512, 16).astype(np.uint32)
+    suffixes = [rng.integers(0, 512, 9).astype(np.uint32) for _ in range(4)]
+    params = B.SamplingParams(temperature=0.7, top_k=0, top_p=0.95, seed=100)
+    ctx = B.Context(0)
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=128, max_tokens=32, max_logit_rows=1, kv=B.KvType.F32))
+    m.set_prefill_precision(B.PrefillPrecision.F32)
+    bt = B.Batch(m, max_seqs=4, num_pages=40, max_positions=64)
+    try:
+        bt.set_prefix(prefix)
+        for sfx in suffixes:
+            bt.add_sequence(sfx, params)
+        ids, _ = bt.decode(6, params)
+        again = None
+    finally:
+        bt.free()
+    try:
+        for i, sfx in enumerate(suffixes):
+            lg, _ = m.forward(np.concatenate([prefix, sfx]), 0)
+            assert O.Sampler(temperature=0.7, top_k=0, top_p=0.95, seed=100 + i).sample(lg[0]) == int(ids[i, 0])
+        assert len({tuple(r) for r in ids.tolist()}) > 1  # different prompts and streams give different continuations
+    finally:
+        m.free()
+
+
+def test_batch_rejects_what_does_not_fit(B, golden_dir):
+    path = golden_dir / "tiny" / "model.brasa"
+    ctx = B.Context(0)
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=128, max_tokens=32, max_logit_rows=1, kv=B.KvType.F16))
+    try:
+        with pytest.raises(B.BrasaError):
+            B.Batch(m, max_seqs=33, num_pages=8, max_positions=64)  # more sequences than the workspace holds
+        bt = B.Batch(m, max_seqs=2, num_pages=5, max_positions=64)
+        with pytest.raises(B.BrasaError):
+            bt.set_prefix(np.arange(10, dtype=np.uint32))  # not whole pages
+        bt.set_prefix(np.arange(16, dtype=np.uint32))
+        bt.add_sequence(np.arange(3, dtype=np.uint32))
+        with pytest.raises(B.BrasaError):
+            bt.add_sequence(np.arange(3, dtype=np.uint32))  # pages exhausted: 1 shared + 3 own, 5 in all
+        with pytest.raises(B.BrasaError):
+            bt.decode(64)  # would pass max_positions
+        bt.free()
+    finally:
+        m.free()

@@ -589,3 +589,22 @@ def test_device_sampler_frequency_and_greedy(B, ctx, K):
     g2 = ctx.buffer_from(np.array([0.1, 3.0, -1.0, 2.9], dtype=np.float32))
     run(ctx, lambda c: K.sample_top_p(c, g2, 4, 0.0, 0, 1.0, state, out))
     assert int(out.download(np.uint32, 1)[0]) == 1
+
+
+@pytest.mark.parametrize("name", ["q6_0", "q8_0"])
+@pytest.mark.parametrize("layout", ["file", "tiled"])
+def test_gemm_other_weight_types(B, ctx, K, name, layout):
+    """The warp-MMA prefill GEMM over q6_0 (both layouts: the lm_head of a batch) and q8_0 weights."""
+    if name == "q8_0" and layout == "tiled":
+        pytest.skip("q8_0 has no tiled layout")
+    rows, cols, tokens = 512, 256, 19
+    rng = O.Rng(41)
+    raw = rng.qmatrix(QT[name][0], rows, cols)
+    m = tiled(B, ctx, K, name, raw, rows, cols)[0] if layout == "tiled" else B.QMatrix(ctx.buffer_from(raw), B.WeightType(QT[name][1]), rows, cols)
+    x = rng.vec(tokens * cols, 1.0)
+    xh = x.astype(np.float16)
+    want16, s16 = O.matmul(QT[name][0], raw, rows, cols, x, f16_inputs=True)
+    gxh, gy = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4)
+    run(ctx, lambda c: K.gemm(c, m, gxh, gy, tokens))
+    got = gy.download(np.float32).reshape(tokens, rows)
+    assert np.max(np.abs(got - want16) / s16) <= 1e-5
