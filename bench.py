@@ -266,6 +266,109 @@ def prefill_16k(B, ctx, path, cfg, kv_name: str):
         m.free()
 
 
+def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048, suffix: int = 1024, steps: int = 512):
+    """Batched serving on one replica: `seqs` sequences that share a `prefix`-token prompt head (computed once, its KV pages
+    attached to every sequence) and each carry `suffix` tokens of their own, then `steps` sampled tokens per sequence
+    (temperature 0.7, top-p 0.95, one PCG32 stream per sequence) over f16 KV in 16-token pages. Returns a dict."""
+    V = cfg["vocab_size"]
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=prefix + suffix, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
+    page = B.Batch.PAGE
+    own_pages = (suffix + steps + 1 + page - 1) // page
+    batch = B.Batch(m, seqs, prefix // page + seqs * own_pages + 8, prefix + suffix + steps + page)
+    try:
+        params = B.SamplingParams(temperature=0.7, top_k=0, top_p=0.95, seed=SEED + 1000 * rank)
+        shared = np.random.default_rng(SEED + 4).integers(0, V, size=prefix).astype(np.uint32)
+        t0 = time.perf_counter()
+        batch.set_prefix(shared)
+        t_prefix = time.perf_counter() - t0
+        ttft = []
+        for i in range(seqs):
+            own = np.random.default_rng(SEED + 5 + i + 1000 * rank).integers(0, V, size=suffix).astype(np.uint32)
+            t1 = time.perf_counter()
+            batch.add_sequence(own, params)
+            ttft.append(time.perf_counter() - t1)
+        t_admit = time.perf_counter() - t0
+        batch.decode(4, params)  # warm-up steps (they advance the sequences by 4 positions)
+        ids, secs = batch.decode(steps, params)
+        kvb = synth_kv_bytes(cfg)
+        mean_pos = prefix + suffix + 4 + 1 + (steps - 1) / 2.0
+        step_bytes = weight_bytes(cfg) + seqs * kvb * mean_pos
+        return {"sequences": seqs, "shared_prefix_tokens": prefix, "own_prompt_tokens": suffix, "decode_steps": steps,
+                "sampling": "temperature 0.7, top-p 0.95, top-k 0, PCG32 per sequence", "kv": "f16, pages of 16 positions",
+                "decode_tok_s": seqs * steps / secs, "ms_per_step": secs / steps * 1e3,
+                "prefix_prefill_s": t_prefix, "admit_all_s": t_admit, "ttft_s_median": statistics.median(ttft), "ttft_s_max": max(ttft),
+                "prefix_tokens_not_recomputed": prefix * (seqs - 1), "pages_in_use": batch.pages_in_use,
+                "kv_resident_gib": batch.pages_in_use * page * kvb / 2**30,
+                "algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (secs / steps) / 1e9,
+                "distinct_tokens": int(np.unique(ids).size)}
+    finally:
+        batch.free()
+        m.free()
+
+
+def weight_bytes(cfg) -> int:
+    from brasa_b200 import synth
+    return synth.weight_bytes_per_token(cfg)
+
+
+def synth_kv_bytes(cfg) -> int:
+    from brasa_b200 import synth
+    return synth.kv_bytes_per_position(cfg, "f16")
+
+
+def tp_leg(B, ctx, rep, steps: int = 3, prompt: int = 1024, generate: int = 256):
+    """Qwen3-32B-architecture batch-1 decode, tensor-parallel over the ranks of this job: every rank holds its share of the
+    heads, FFN rows and lm_head rows (random init, q4_0; the q6_0 embedding table replicated), a 1024-token prompt is
+    prefilled in 512-token chunks, then `generate` greedy tokens run device-resident with the two sums over ranks of every
+    layer and the argmax exchange done by the ranks' own kernels through peer memory. Returns a dict (every rank calls)."""
+    from brasa_b200 import synth
+    from brasa_b200 import tp as TP
+    rank, world = rep.rank, rep.world
+    cfg = TP.shard_config(synth.QWEN3_32B, rank, world)
+    path = model_path(f"qwen3-32b-tp{world}-rank{rank}")
+    if not path.exists():
+        tmp = path.with_suffix(".tmp")
+        synth.write_synthetic_model(ctx, tmp, cfg, seed=SEED)
+        os.replace(tmp, path)
+    limits = B.Limits(ctx=2048, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16)
+    m = B.Qwen3.load(ctx, path, limits)
+    tp = TP.TensorParallel(ctx, rank, world, limits.max_tokens * cfg["hidden_size"])
+    m.set_tp(tp)
+    try:
+        ids = np.random.default_rng(SEED + 32).integers(0, cfg["vocab_size"], size=prompt).astype(np.uint32)
+        rep.barrier()
+        pre_s, lg = 0.0, None
+        for off in range(0, prompt, 512):
+            lg, s = m.forward(ids[off:off + 512], off, want_logits=off + 512 >= prompt)
+            pre_s += s
+        # the first generated token: the best logit over every rank's rows (ties to the lower index)
+        best = float(np.nanmax(lg[0]))
+        cand = int(np.flatnonzero(lg[0] == best)[0]) + m.cfg["head_row0"]
+        top = rep.max(best)
+        first = int(-rep.max(-(cand if best == top else 2**31)))
+        rep.barrier()
+        m.decode_greedy(first, prompt, 16)
+        secs, toks = [], None
+        for _ in range(steps):
+            rep.barrier()
+            toks, s = m.decode_greedy(first, prompt, generate)
+            secs.append(s)
+        total = rep.max(float(sum(secs)))
+        agree = rep.max(float(int(toks[-1]))) == -rep.max(-float(int(toks[-1])))
+        shard_bytes = synth.weight_bytes_per_token(cfg)
+        kvb = synth.kv_bytes_per_position(cfg, "f16")
+        per_token = shard_bytes + kvb * (prompt + 1 + (generate - 1) / 2.0)
+        t_tok = total / (steps * generate)
+        return {"model": "Qwen3-32B architecture, q4_0, random init", "tp": world, "prompt_tokens": prompt, "generated": generate,
+                "decode_tok_s": 1.0 / t_tok, "ms_per_token": t_tok * 1e3, "prefill_tok_s": prompt / rep.max(pre_s),
+                "bytes_per_token_per_gpu": per_token, "achieved_gbs_per_gpu": per_token / t_tok / 1e9,
+                "exchanges_per_token": 2 * cfg["num_hidden_layers"] + 1, "ranks_agree_on_tokens": bool(agree),
+                "batch": 1}
+    finally:
+        m.free()
+        tp.free()
+
+
 def kernel_roofline(B, ctx, K, cfg, peak, peak_kind, profile=False):
     """The dominant kernel alone: gate/up GEMV + SwiGLU over 36 distinct weight pairs (1 GB) in one CUDA graph."""
     roof = None
@@ -325,6 +428,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             print(json.dumps({"roofline": kernel_roofline(B, ctx, B.Kernels(ctx), cfg, peak, peak_kind, profile=True),
                               "note": "dominant kernel alone (profiling run)"}))
         return
+    if args.only_tp:
+        res = tp_leg(B, ctx, rep, steps=args.steps)
+        if rank == 0:
+            peak, peak_kind = measured_peaks()
+            res["frac_of_measured_hbm_per_gpu"] = res["achieved_gbs_per_gpu"] / peak
+            print(json.dumps({"metric": "qwen3_32b_tp_decode_tok_s", "value": res["decode_tok_s"], "unit": "tok/s", "n_gpus": world,
+                              "scaling": "strong", "tp": res, "note": "tensor-parallel 32B decode leg (run on its own)"}))
+        if dist:
+            dist.barrier()
+        rep.close()
+        return
     path = model_path("qwen3-4b")
     if rank == 0 and not path.exists():
         tmp = path.with_suffix(".tmp")
@@ -336,6 +450,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sess = B.Session(ctx, path, B.Limits(ctx=CTX, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
     model = sess.model
     K = B.Kernels(ctx)
+
+    if args.only_serving:
+        sess.free()
+        profiler_range(True)
+        res = serving_leg(B, ctx, path, cfg, rank, seqs=args.serving_seqs, steps=args.serving_steps)
+        profiler_range(False)
+        if rank == 0:
+            print(json.dumps({"metric": "serving_decode_tok_s", "value": res["decode_tok_s"], "unit": "tok/s", "serving": res,
+                              "note": "batched serving leg only (profiling run)"}))
+        return
 
     if args.only_prefill:
         model.forward(ids, 0, want_logits=False)
@@ -487,6 +611,10 @@ def main():
                     help="run only one prefill forward of the workload's prompt (profiler captures)")
     ap.add_argument("--only-kernel", action="store_true",
                     help="run only the dominant kernel's own timing leg (profiler captures)")
+    ap.add_argument("--only-tp", action="store_true", help="run only the tensor-parallel Qwen3-32B decode over the job's ranks")
+    ap.add_argument("--only-serving", action="store_true", help="run only the batched serving leg (profiling)")
+    ap.add_argument("--serving-seqs", type=int, default=64)
+    ap.add_argument("--serving-steps", type=int, default=512)
     ap.add_argument("--only-decode", action="store_true",
                     help="run only the device-resident decode loop (profiler captures): no end-to-end, kernel or CPU legs")
     args = ap.parse_args()

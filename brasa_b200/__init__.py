@@ -110,7 +110,7 @@ class _Limits(C.Structure):
 class _Config(C.Structure):
     _fields_ = [("hidden", C.c_uint32), ("layers", C.c_uint32), ("heads", C.c_uint32), ("kv_heads", C.c_uint32),
                 ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32), ("max_position", C.c_uint32),
-                ("eps", C.c_float), ("rope_theta", C.c_double), ("tied", C.c_int32)]
+                ("eps", C.c_float), ("rope_theta", C.c_double), ("tied", C.c_int32), ("head_rows", C.c_uint32), ("head_row0", C.c_uint32)]
 
 
 class _Allocated(C.Structure):
@@ -157,6 +157,12 @@ def lib() -> C.CDLL:
         L.brasa_batch_free.argtypes = [C.c_void_p]
         L.brasa_batch_sequences.argtypes = [C.c_void_p]
         L.brasa_batch_pages_in_use.argtypes = [C.c_void_p]
+        L.brasa_tp_free.restype = None
+        L.brasa_tp_free.argtypes = [C.c_void_p]
+        L.brasa_tp_rank.argtypes = [C.c_void_p]
+        L.brasa_tp_world.argtypes = [C.c_void_p]
+        L.brasa_tp_rank.restype = C.c_uint32
+        L.brasa_tp_world.restype = C.c_uint32
         for name in ("brasa_ctx_destroy", "brasa_model_free", "brasa_session_free", "brasa_buf_free", "brasa_buf_ptr", "brasa_buf_bytes",
                      "brasa_ctx_stream", "brasa_session_model", "brasa_graph_free"):
             getattr(L, name).argtypes = [C.c_void_p]
@@ -392,6 +398,21 @@ class Kernels:
 
     def _k(self, rc):
         self.ctx._check(rc)
+
+    # tensor-parallel exchange
+    def tp_allreduce_add(self, cmd, tp, partial, resid, out, n, phase=None):
+        if phase is None:
+            self._k(self.L.brasa_k_tp_allreduce_add(cmd._h, tp._h, _arg(partial), _arg(resid), _arg(out), C.c_uint64(n)))
+        else:  # "push" or "gather": the two halves as separate launches (ranks sharing one device)
+            self._k(self.L.brasa_k_tp_allreduce_add_phase(cmd._h, tp._h, _arg(partial), _arg(resid), _arg(out), C.c_uint64(n),
+                                                          C.c_int32(int(phase == "gather"))))
+
+    def tp_argmax(self, cmd, tp, logits, n, row0, out, phase=None):
+        if phase is None:
+            self._k(self.L.brasa_k_tp_argmax(cmd._h, tp._h, _arg(logits), C.c_uint32(n), C.c_uint32(row0), _arg(out)))
+        else:
+            self._k(self.L.brasa_k_tp_argmax_phase(cmd._h, tp._h, _arg(logits), C.c_uint32(n), C.c_uint32(row0), _arg(out),
+                                                   C.c_int32(int(phase == "gather"))))
 
     # layout / converter
     def repack(self, cmd, qtype, src, dst, rows, cols):
@@ -636,6 +657,11 @@ class Qwen3:
             lib().brasa_model_free(self._h)
         self._h = C.c_void_p()
 
+    def set_tp(self, tp) -> None:
+        """Attaches a tensor-parallel exchange (brasa_b200.tp.TensorParallel) to this shard, before its first step."""
+        self.ctx._check(lib().brasa_model_set_tp(self._h, tp._h))
+        self._tp = tp
+
     def allocated(self) -> dict:
         a = _Allocated()
         self.ctx._check(lib().brasa_model_allocated(self._h, C.byref(a)))
@@ -645,9 +671,10 @@ class Qwen3:
         self.ctx._check(lib().brasa_model_set_prefill_precision(self._h, C.c_int32(int(p))))
 
     def forward(self, ids, pos0: int, logit_rows: int = 1, want_logits: bool = True):
-        """Returns (logits [logit_rows, vocab] or None, device seconds)."""
+        """Returns (logits [logit_rows, vocab] or None, device seconds); a tensor-parallel shard returns its own
+        head_rows columns of the vocabulary, starting at head_row0."""
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
-        logits = np.empty((logit_rows, self.cfg["vocab"]), np.float32) if want_logits else None
+        logits = np.empty((logit_rows, self.cfg["head_rows"]), np.float32) if want_logits else None
         secs = C.c_double()
         self.ctx._check(lib().brasa_model_forward(self._h, ids.ctypes.data_as(C.c_void_p), C.c_uint32(ids.size), C.c_uint32(pos0),
                                                   C.c_uint32(logit_rows), logits.ctypes.data_as(C.c_void_p) if want_logits else None,

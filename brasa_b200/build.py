@@ -12,7 +12,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "_build"
 LIB = HERE / "libbrasa_cuda.so"
-SOURCES = ["ctx.cu", "quant.cu", "gemv.cu", "ops.cu", "attn.cu", "flash_tc.cu", "gemm.cu", "gemm_tc.cu", "sample.cu", "host_util.cu", "decode_token.cu", "model.cu", "batch.cu"]
+SOURCES = ["ctx.cu", "quant.cu", "gemv.cu", "ops.cu", "attn.cu", "flash_tc.cu", "gemm.cu", "gemm_tc.cu", "sample.cu", "host_util.cu", "decode_token.cu", "model.cu", "batch.cu", "tp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-diag-suppress", "550"]
 

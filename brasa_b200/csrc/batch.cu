@@ -335,6 +335,7 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     BRASA_REQUIRE(ctx, m->cfg.head_dim == 128 && m->cfg.heads % m->cfg.kv_heads == 0 && m->cfg.heads / m->cfg.kv_heads <= 8,
                   "batch: head_dim 128 and a GQA group of at most 8");
     BRASA_REQUIRE(ctx, max_positions >= PAGE && max_positions <= m->limits.ctx, "batch: max_positions within the model's context");
+    BRASA_REQUIRE(ctx, !m->tp && m->cfg.head_rows == m->cfg.vocab, "batch: tensor-parallel shards are decoded one sequence at a time");
     std::unique_ptr<brasa_batch, void (*)(brasa_batch *)> b(new brasa_batch, brasa_batch_free);
     b->m = m;
     b->ctx = ctx;

@@ -54,6 +54,10 @@ int32_t cfg_from_json(brasa_ctx *ctx, const brasa::Json &c, brasa_config *out, s
     const brasa::Json *e = c.get("rms_norm_eps"), *th = c.get("rope_theta");
     out->eps = e && e->kind == brasa::Json::Num ? (float)e->num : 1e-6f;
     out->rope_theta = th && th->kind == brasa::Json::Num ? th->num : 1e6;
+    // a tensor-parallel shard names the vocabulary row its lm_head starts at; the row count comes from the tensor
+    const brasa::Json *off = c.get("tp_vocab_offset");
+    out->head_rows = out->vocab;
+    out->head_row0 = off && off->kind == brasa::Json::Num ? (uint32_t)off->inum : 0;
     (void)ctx;
     return true;
 }
@@ -122,6 +126,12 @@ int32_t matmul(brasa_model *m, brasa_cmd *cmd, const Matrix &w, brasa_arg x, bra
 
 int32_t precision_for(brasa_model *m, uint32_t tokens) { return tokens <= GEMV_MAX_TOKENS ? BRASA_PREFILL_F32 : m->prefill_precision; }
 
+// x += h for n values: the plain add on one device, the sum over ranks of every rank's h for a tensor-parallel shard.
+int32_t residual_add(brasa_model *m, brasa_cmd *cmd, uint64_t n) {
+    if (m->tp) return brasa_k_tp_allreduce_add(cmd, m->tp, A(m->h), A(m->x), A(m->x), n);
+    return brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), n);
+}
+
 // Layer li for `tokens` > 1 tokens from pos0 (also used for a single token by run_layers when asked
 // for the unfused order). Input and output in ws.x.
 int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32_t tokens, uint32_t pos0) {
@@ -157,7 +167,7 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
         BRASA_TRY(brasa_k_flash_attention_with(cmd, A(m->q), all.k, all.v, attn, sh, half_io ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32));
     }
     BRASA_TRY(matmul(m, cmd, l.wo, attn, A(m->h), tokens, half_io));
-    BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)tokens * H));
+    BRASA_TRY(residual_add(m, cmd, (uint64_t)tokens * H));
     brasa_arg act;
     if (half_io) {
         BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), tokens, H, c.eps));
@@ -171,7 +181,7 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
         act = A(m->gate);
     }
     BRASA_TRY(matmul(m, cmd, l.down, act, A(m->h), tokens, half_io));
-    return brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)tokens * H);
+    return residual_add(m, cmd, (uint64_t)tokens * H);
 }
 
 bool decode_fused_ok(brasa_model *m) {
@@ -208,6 +218,11 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
             float *y[1] = {x};
             brasa_qmatrix nxt[2] = {l.gate.q, l.up.q};
             brasa_gemv_hint_next(m->ctx, 2, nxt, true);
+            if (m->tp) {  // this rank's part of Wo attn, then the sum over ranks lands in x
+                float *part[1] = {F(m->h)};
+                BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, part, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, SCALE, nullptr));
+                BRASA_TRY(residual_add(m, cmd, c.hidden));
+            } else
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
         {
@@ -225,6 +240,11 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
             } else if (with_head) {
                 brasa_gemv_hint_next(m->ctx, 1, &m->head.q, false);
             }
+            if (m->tp) {
+                float *part[1] = {F(m->h)};
+                BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, part, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, SCALE, nullptr));
+                BRASA_TRY(residual_add(m, cmd, c.hidden));
+            } else
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
     }
@@ -250,7 +270,8 @@ int32_t decode_step_kernels(brasa_model *m, brasa_cmd *cmd) {
     uint32_t *st = (uint32_t *)m->dev_state->ptr;
     BRASA_TRY(brasa_k_embed(cmd, m->embed.q, A(m->ids), A(m->x), 1));
     BRASA_TRY(encode_decode_token(m, cmd, 0, m->cfg.layers, true));
-    BRASA_TRY(brasa_argmax_launch(cmd, F(m->logits), m->cfg.vocab, (uint32_t *)m->next_id->ptr));
+    if (m->tp) BRASA_TRY(brasa_k_tp_argmax(cmd, m->tp, A(m->logits), m->cfg.head_rows, m->cfg.head_row0, A(m->next_id)));
+    else BRASA_TRY(brasa_argmax_launch(cmd, F(m->logits), m->cfg.head_rows, (uint32_t *)m->next_id->ptr));
     return brasa_advance_launch(cmd, (uint32_t *)m->ids->ptr, (const uint32_t *)m->next_id->ptr, (uint32_t *)m->out_ids->ptr, st + 1,
                                 m->limits.ctx, st);
 }
@@ -262,6 +283,10 @@ int32_t set_position(brasa_model *m, uint32_t pos0) {
 // Describes the model to the whole-token kernel and builds its program, once. Leaves token_prog null when the
 // shapes do not fit or BRASA_TOKEN_KERNEL=0 asks for the kernel-per-operation path.
 int32_t make_token_program(brasa_model *m) {
+    if (m->tp || m->cfg.head_rows != m->cfg.vocab) {  // a shard exchanges with its peers between kernels
+        m->token_prog_tried = true;
+        return BRASA_OK;
+    }
     m->token_prog_tried = true;
     if (!m->ctx->token_kernel) return BRASA_OK;
     const brasa_config &c = m->cfg;
@@ -402,7 +427,13 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         if (m->embed.q.qtype != BRASA_Q8_0 && m->embed.q.qtype != BRASA_Q6_0)
             return brasa_fail(ctx, BRASA_EIO, "the embedding table must be q8_0 or q6_0");
         if (c.tied) m->head = m->embed;
-        else BRASA_TRY(load_matrix(m, *f, "lm_head.weight", c.vocab, H, staging, &m->head));
+        else {
+            const brasa::TensorInfo *ht = f->tensor("lm_head.weight");
+            if (ht->shape.size() != 2 || ht->shape[0] == 0 || ht->shape[0] > c.vocab || m->cfg.head_row0 + ht->shape[0] > c.vocab)
+                return brasa_fail(ctx, BRASA_EIO, "lm_head.weight: unexpected shape");
+            m->cfg.head_rows = (uint32_t)ht->shape[0];
+            BRASA_TRY(load_matrix(m, *f, "lm_head.weight", m->cfg.head_rows, H, staging, &m->head));
+        }
         BRASA_TRY(load_f32(m, *f, "model.norm.weight", H, &m->final_norm));
         // staging is not part of the steady-state footprint
         m->owned.erase(std::remove(m->owned.begin(), m->owned.end(), staging), m->owned.end());
@@ -435,7 +466,7 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         BRASA_TRY(alloc_buf(m, (uint64_t)brasa_norm_partials(H) * 4, &m->ss, ws));
         m->partials_len = brasa_decode_partials_len(c.heads, limits.ctx);
         BRASA_TRY(alloc_buf(m, m->partials_len * 4, &m->partials, ws));
-        BRASA_TRY(alloc_buf(m, (uint64_t)limits.max_logit_rows * c.vocab * 4, &m->logits, ws));
+        BRASA_TRY(alloc_buf(m, (uint64_t)limits.max_logit_rows * m->cfg.head_rows * 4, &m->logits, ws));
         BRASA_TRY(alloc_buf(m, 64, &m->next_id, nullptr));
         BRASA_TRY(alloc_buf(m, (uint64_t)limits.ctx * 4, &m->out_ids, nullptr));
         BRASA_TRY(alloc_buf(m, 256, &m->dev_state, nullptr));
@@ -449,6 +480,16 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         return rc;
     }
     *out = m;
+    return BRASA_OK;
+}
+
+int32_t brasa_model_set_tp(brasa_model *m, brasa_tp *tp) {
+    if (!m || !tp) return BRASA_EINVAL;
+    brasa_ctx *ctx = m->ctx;
+    BRASA_REQUIRE(ctx, !m->decode_graph && !m->token_prog, "set_tp: attach the exchange before the first decode step");
+    BRASA_REQUIRE(ctx, m->cfg.hidden % 2 == 0, "set_tp: odd hidden size");
+    BRASA_REQUIRE(ctx, m->cfg.head_row0 == 0 || brasa_tp_world(tp) > 1, "set_tp: a shard with a vocabulary offset needs its peers");
+    m->tp = tp;
     return BRASA_OK;
 }
 
@@ -488,7 +529,7 @@ int32_t brasa_model_forward(brasa_model *m, const uint32_t *ids, uint32_t tokens
     int32_t rc2 = brasa_cmd_wait(cmd, gpu_seconds);
     BRASA_TRY(rc);
     BRASA_TRY(rc2);
-    if (logits) BRASA_TRY(brasa_buf_download(m->logits, 0, logits, (uint64_t)logit_rows * m->cfg.vocab * 4));
+    if (logits) BRASA_TRY(brasa_buf_download(m->logits, 0, logits, (uint64_t)logit_rows * m->cfg.head_rows * 4));
     return BRASA_OK;
 }
 
@@ -569,8 +610,13 @@ int32_t brasa_session_create(brasa_ctx *ctx, const char *path, brasa_limits limi
     brasa_session_shape ss{limits.ctx, limits.max_tokens, limits.max_logit_rows, limits.kv};
     // the plan is checked before anything is loaded: a rejection allocates nothing
     BRASA_TRY(brasa_plan_check(ctx, &shape, &ss, budget_bytes, nullptr, nullptr));
+    BRASA_REQUIRE(ctx, cfg.head_row0 == 0, "a tensor-parallel shard cannot run as a session");
     brasa_model *m = nullptr;
     BRASA_TRY(brasa_model_load(ctx, path, limits, &m));
+    if (m->cfg.head_rows != m->cfg.vocab) {
+        brasa_model_free(m);
+        return brasa_fail(ctx, BRASA_EINVAL, "a tensor-parallel shard cannot run as a session");
+    }
     brasa_session *s = new brasa_session();
     s->ctx = ctx;
     s->model = m;

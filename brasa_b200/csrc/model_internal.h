@@ -28,6 +28,7 @@ using namespace brasa_model_detail;
 
 struct brasa_model {
     brasa_ctx *ctx = nullptr;
+    brasa_tp *tp = nullptr;  // set for a tensor-parallel shard: residual adds are sums over ranks (not owned)
     brasa_config cfg{};
     brasa_limits limits{};
     int32_t prefill_precision = BRASA_PREFILL_F16;

@@ -41,7 +41,7 @@ def tensor_shapes(cfg: dict) -> dict[str, list[int]]:
                   p + "self_attn.v_proj.weight": [kvd, H], p + "self_attn.o_proj.weight": [H, qd],
                   p + "mlp.gate_proj.weight": [F, H], p + "mlp.up_proj.weight": [F, H], p + "mlp.down_proj.weight": [H, F]})
     if not cfg.get("tie_word_embeddings", True):
-        t["lm_head.weight"] = [V, H]
+        t["lm_head.weight"] = [cfg.get("tp_head_rows", V), H]  # a tensor-parallel shard holds its rows of the vocabulary
     return t
 
 
@@ -89,6 +89,9 @@ def write_synthetic_model(ctx: Context, path, cfg: dict, seed: int = 0, std: flo
     f32buf = ctx.buffer(biggest * 4)
     qbuf = ctx.buffer(max(t["nbytes"] for t in tensors))
     stream_off = 0
+    # a tensor-parallel shard (brasa_b200.tp.shard_config): the replicated embedding table comes from the shared seed,
+    # everything else from a seed of the rank's own
+    own_seed = seed + 1000003 * (cfg["tp_rank"] + 1) if "tp_rank" in cfg else seed
     with open(path, "wb") as f:
         f.truncate(total)
         for t in tensors:
@@ -97,11 +100,12 @@ def write_synthetic_model(ctx: Context, path, cfg: dict, seed: int = 0, std: flo
                 data = np.ones(n, dtype="<f4").tobytes()
             else:
                 cmd = ctx.command()
-                K.randn(cmd, f32buf, n, seed, stream_off, std)
+                shared = "tp_rank" in cfg and t["name"] == "model.embed_tokens.weight"
+                K.randn(cmd, f32buf, n, seed if shared else own_seed, 0 if shared else stream_off, std)
                 K.quantize(cmd, _QT[t["dtype"]], f32buf, qbuf, n)
                 cmd.wait()
                 data = qbuf.download(np.uint8, t["nbytes"]).tobytes()
-                stream_off += (n + 1) // 2
+                stream_off += 0 if shared else (n + 1) // 2
             t["sha256"] = hashlib.sha256(data).hexdigest()
             f.seek(t["offset"])
             f.write(data)

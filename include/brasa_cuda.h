@@ -244,6 +244,7 @@ typedef struct brasa_config { /* qwen3.rs:28-41 Config */
     float eps;
     double rope_theta;
     int32_t tied; /* 1: lm_head is the embedding table (the reference supports only this) */
+    uint32_t head_rows, head_row0; /* rows of the lm_head held here and the vocabulary row of the first (vocab, 0 unless sharded) */
 } brasa_config;
 
 typedef struct brasa_allocated { /* qwen3.rs:430 Allocated */
@@ -317,6 +318,37 @@ int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params
 int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits);
 uint32_t brasa_batch_sequences(brasa_batch *b);
 uint32_t brasa_batch_pages_in_use(brasa_batch *b);
+
+/* ---- tensor parallelism inside one node (large models split over GPUs) ---------------------------------------
+ * No counterpart in the reference (one device). A model shard is an ordinary `.brasa` file whose config carries this
+ * rank's share of the heads, KV heads and FFN rows (q/k/v and gate/up split by rows, o_proj and down_proj by columns,
+ * an untied lm_head by vocabulary rows, `tp_vocab_offset` = its first row); the two residual adds of every layer
+ * (qwen3.rs:763-831) become a sum over ranks, done by a one-shot push exchange through peer memory. One process per
+ * GPU: each rank creates its exchange buffer, the 64-byte handles travel over the job's own channel, every rank
+ * connects, and the ranks then make the same calls in the same order. */
+#define BRASA_TP_MAX_RANKS 8
+#define BRASA_TP_HANDLE_BYTES 64
+typedef struct brasa_tp brasa_tp;
+/* max_elems: the largest number of f32 values one exchange carries (max_tokens x hidden; even) */
+int32_t brasa_tp_create(brasa_ctx *ctx, uint32_t rank, uint32_t world, uint64_t max_elems, brasa_tp **out);
+void brasa_tp_free(brasa_tp *tp);
+uint32_t brasa_tp_rank(const brasa_tp *tp);
+uint32_t brasa_tp_world(const brasa_tp *tp);
+int32_t brasa_tp_handle(brasa_tp *tp, uint8_t *handle /* BRASA_TP_HANDLE_BYTES */);
+int32_t brasa_tp_connect(brasa_tp *tp, const uint8_t *handles /* world x BRASA_TP_HANDLE_BYTES, by rank */);
+int32_t brasa_tp_connect_same_process(brasa_tp *const *tps, uint32_t n); /* ranks of one process: plain pointers */
+/* out = resid + sum over ranks of partial (resid.buf NULL: out = the sum); n even; identical bits on every rank */
+int32_t brasa_k_tp_allreduce_add(brasa_cmd *cmd, brasa_tp *tp, brasa_arg partial, brasa_arg resid, brasa_arg out, uint64_t n);
+/* argmax over the concatenation of every rank's logits[n] (this rank's rows start at row0): out_u32 = global index */
+int32_t brasa_k_tp_argmax(brasa_cmd *cmd, brasa_tp *tp, brasa_arg logits, uint32_t n, uint32_t row0, brasa_arg out_u32);
+/* the send (gather = 0) and receive (gather = 1) halves as separate launches, for ranks that share one device:
+ * queue every rank's send before any rank's receive */
+int32_t brasa_k_tp_allreduce_add_phase(brasa_cmd *cmd, brasa_tp *tp, brasa_arg partial, brasa_arg resid, brasa_arg out, uint64_t n, int32_t gather);
+int32_t brasa_k_tp_argmax_phase(brasa_cmd *cmd, brasa_tp *tp, brasa_arg logits, uint32_t n, uint32_t row0, brasa_arg out_u32, int32_t gather);
+/* attaches the exchange to a model shard (before its first forward): residual adds become all-reduces, the greedy
+ * token of brasa_model_decode_greedy is chosen over all ranks' lm_head rows; brasa_model_forward returns this rank's
+ * rows of the logits (brasa_config.head_rows of them, starting at vocabulary row head_row0) */
+int32_t brasa_model_set_tp(brasa_model *m, brasa_tp *tp);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,177 @@
+"""Tensor-parallel exchange and sharded decode on the GPU.
+
+One device: the exchange kernels with two ranks that share the device (every rank's send queued before any rank's
+receive, so no kernel waits for a later launch), and a whole model with a one-rank exchange attached. Two devices
+(skipped otherwise): two processes, one shard each, against the unsplit model on one device.
+"""
+
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import oracle as O
+from oracle import brasa_format as BF
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    import brasa_b200
+    return brasa_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(B):
+    c = B.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def untied_model(tmp_path_factory):
+    d = tmp_path_factory.mktemp("tp_model")
+    cfg = BF.tiny_config(layers=3, hidden=512, heads=8, kv_heads=2, ffn=1280, vocab=1024)
+    cfg["tie_word_embeddings"] = False
+    BF.write_brasa(d / "model.brasa", cfg, BF.synth_weights(cfg, seed=29, std=0.04, norm_jitter=0.1))
+    return d / "model.brasa"
+
+
+@pytest.mark.parametrize("n", [5120, 64 * 512, 2])
+def test_allreduce_two_ranks_on_one_device(B, ctx, n):
+    from brasa_b200.tp import TensorParallel
+    K = B.Kernels(ctx)
+    tps = TensorParallel.same_process([ctx, ctx], max(n, 2))
+    try:
+        rng = np.random.default_rng(n)
+        x = rng.standard_normal(n).astype(np.float32)
+        gx = [ctx.buffer_from(x.copy()) for _ in range(2)]
+        gp = [ctx.buffer(n * 4) for _ in range(2)]
+        for it in range(5):  # several exchanges: both parities of the buffer and growing exchange numbers
+            parts = [rng.standard_normal(n).astype(np.float32) * (1 + r) for r in range(2)]
+            for r in range(2):
+                gp[r].upload(parts[r])
+            cmd = ctx.command()
+            for r in range(2):
+                K.tp_allreduce_add(cmd, tps[r], gp[r], gx[r], gx[r], n, phase="push")
+            for r in range(2):
+                K.tp_allreduce_add(cmd, tps[r], gp[r], gx[r], gx[r], n, phase="gather")
+            cmd.wait()
+            x = x + (parts[0] + parts[1])  # rank order, then the residual: the kernel's order exactly
+            for r in range(2):
+                assert np.array_equal(gx[r].download(np.float32)[:n], x), (it, r)
+        # without a residual the output is the plain sum
+        cmd = ctx.command()
+        out = [ctx.buffer(n * 4) for _ in range(2)]
+        for r in range(2):
+            K.tp_allreduce_add(cmd, tps[r], gp[r], None, out[r], n, phase="push")
+        for r in range(2):
+            K.tp_allreduce_add(cmd, tps[r], gp[r], None, out[r], n, phase="gather")
+        cmd.wait()
+        for r in range(2):
+            assert np.array_equal(out[r].download(np.float32)[:n], parts[0] + parts[1])
+    finally:
+        for t in tps:
+            t.free()
+
+
+def test_argmax_exchange_ties_and_nan(B, ctx):
+    from brasa_b200.tp import TensorParallel
+    K = B.Kernels(ctx)
+    world, n = 4, 1000
+    tps = TensorParallel.same_process([ctx] * world, 16)
+    try:
+        rng = np.random.default_rng(9)
+        cases = []
+        a = rng.standard_normal((world, n)).astype(np.float32)
+        cases.append(a.copy())
+        a[1, 17] = a[3, 5] = a.max() + 1.0  # equal maxima on two ranks: the lower global index wins
+        cases.append(a.copy())
+        a[0, :] = np.nan  # a rank with nothing but NaN never wins
+        cases.append(a.copy())
+        cases.append(np.full((world, n), -np.inf, np.float32))  # all -inf: index 0
+        for c in cases:
+            bufs = [ctx.buffer_from(c[r].copy()) for r in range(world)]
+            outs = [ctx.buffer(4) for _ in range(world)]
+            cmd = ctx.command()
+            for r in range(world):
+                K.tp_argmax(cmd, tps[r], bufs[r], n, r * n, outs[r], phase="push")
+            for r in range(world):
+                K.tp_argmax(cmd, tps[r], bufs[r], n, r * n, outs[r], phase="gather")
+            cmd.wait()
+            want = O.argmax(c.reshape(-1))
+            for r in range(world):
+                assert int(outs[r].download(np.uint32)[0]) == want
+    finally:
+        for t in tps:
+            t.free()
+
+
+@pytest.mark.parametrize("kv", ["F32", "F16"])
+def test_one_rank_exchange_changes_nothing(B, ctx, untied_model, kv):
+    from brasa_b200.tp import TensorParallel
+    limits = B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=getattr(B.KvType, kv))
+    ids = np.random.default_rng(5).integers(0, 1024, size=40).astype(np.uint32)
+    plain = B.Qwen3.load(ctx, untied_model, limits)
+    want, _ = plain.forward(ids, 0)
+    want1, _ = plain.forward(ids[:1], 40)
+    want_t, _ = plain.decode_greedy(int(ids[0]), 40, 12)
+    plain.free()
+    m = B.Qwen3.load(ctx, untied_model, limits)
+    tp = TensorParallel(ctx, 0, 1, 64 * 512)
+    m.set_tp(tp)
+    try:
+        got, _ = m.forward(ids, 0)
+        got1, _ = m.forward(ids[:1], 40)
+        toks, _ = m.decode_greedy(int(ids[0]), 40, 12)
+        toks2, _ = m.decode_greedy(int(ids[0]), 40, 12)
+        assert np.array_equal(got, want)
+        assert np.abs(got1 - want1).max() <= 1e-5 * np.abs(want1).max()  # x + (W a) in one kernel or in two
+        assert list(toks) == list(want_t) == list(toks2)
+    finally:
+        m.free()
+        tp.free()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("kv", ["F32", "F16"])
+def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model, tmp_path, kv):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from brasa_b200 import tp as TP
+    outs = [tmp_path / f"shard{r}.brasa" for r in range(2)]
+    TP.split_model(untied_model, outs)
+    n_prompt, steps = 40, 12
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
+           str(_free_port()), os.path.join(os.path.dirname(__file__), "tp_worker.py"), str(tmp_path / "shard{rank}.brasa"), str(tmp_path),
+           str(n_prompt), str(steps), kv]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    limits = B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=getattr(B.KvType, kv))
+    ids = np.random.default_rng(5).integers(0, 1024, size=n_prompt).astype(np.uint32)
+    m = B.Qwen3.load(ctx, untied_model, limits)
+    try:
+        want, _ = m.forward(ids, 0)
+        want1, _ = m.forward(ids[:1], n_prompt)
+        want_t, _ = m.decode_greedy(int(ids[0]), n_prompt, steps)
+    finally:
+        m.free()
+    ranks = [np.load(tmp_path / f"rank{r}.npz") for r in range(2)]
+    got = np.concatenate([r["logits"] for r in ranks], axis=1)
+    got1 = np.concatenate([r["one"] for r in ranks], axis=1)
+    assert [int(r["row0"]) for r in ranks] == [0, 512]
+    # the split changes only the order of the sums over o_proj's and down_proj's columns
+    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
+    assert np.abs(got1 - want1).max() <= 1e-4 * np.abs(want1).max()
+    for r in ranks:
+        assert list(r["toks"]) == list(want_t) and list(r["toks2"]) == list(want_t)

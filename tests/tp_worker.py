@@ -1,0 +1,48 @@
+"""One rank of the tensor-parallel parity test (launched by test_gpu_tp.py through torch.distributed.run).
+
+argv: shard path pattern with {rank}, output directory, prompt length, decode steps. Every rank loads its shard,
+connects the exchange over the process group (gloo on 127.0.0.1), runs a prefill and a device-resident greedy
+decode, and writes its rows of the logits and the tokens it chose.
+"""
+
+import os
+import pathlib
+import sys
+
+import numpy as np
+
+
+def main():
+    sys.path.insert(0, str(pathlib.Path(__file__).resolve().parents[1]))
+    import torch.distributed as dist
+
+    import brasa_b200 as B
+    from brasa_b200.tp import TensorParallel
+
+    pattern, out_dir, n_prompt, steps, kv_name = sys.argv[1], pathlib.Path(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dist.init_process_group("gloo")
+    ctx = B.Context(local)
+    limits = B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=getattr(B.KvType, kv_name))
+    m = B.Qwen3.load(ctx, pattern.format(rank=rank), limits)
+    tp = TensorParallel(ctx, rank, world, limits.max_tokens * m.cfg["hidden"])
+    m.set_tp(tp)
+    ids = np.random.default_rng(5).integers(0, m.cfg["vocab"], size=n_prompt).astype(np.uint32)
+    dist.barrier()
+    logits, _ = m.forward(ids, 0)                      # prefill: GEMM path, all-reduce of [tokens, hidden]
+    one, _ = m.forward(ids[:1], n_prompt)              # one token: the fused GEMV chain
+    first = int(ids[0])
+    dist.barrier()
+    toks, _ = m.decode_greedy(first, n_prompt, steps)  # device-resident loop with the argmax exchange
+    dist.barrier()
+    toks2, _ = m.decode_greedy(first, n_prompt, steps)  # CUDA graph replay of the same steps
+    np.savez(out_dir / f"rank{rank}.npz", logits=logits, one=one, toks=toks, toks2=toks2, row0=m.cfg["head_row0"])
+    dist.barrier()
+    m.free()
+    tp.free()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
