@@ -271,10 +271,11 @@ def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048
     attached to every sequence) and each carry `suffix` tokens of their own, then `steps` sampled tokens per sequence
     (temperature 0.7, top-p 0.95, one PCG32 stream per sequence) over f16 KV in 16-token pages. Returns a dict."""
     V = cfg["vocab_size"]
-    m = B.Qwen3.load(ctx, path, B.Limits(ctx=prefix + suffix, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
-    page = B.Batch.PAGE
-    own_pages = (suffix + steps + 1 + page - 1) // page
-    batch = B.Batch(m, seqs, prefix // page + seqs * own_pages + 8, prefix + suffix + steps + page)
+    page, warm = B.Batch.PAGE, 4
+    positions = (prefix + suffix + warm + steps + 1 + page - 1) // page * page  # the most one sequence ever holds
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=positions, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
+    own_pages = (positions - prefix) // page
+    batch = B.Batch(m, seqs, prefix // page + seqs * own_pages + 8, positions)
     try:
         params = B.SamplingParams(temperature=0.7, top_k=0, top_p=0.95, seed=SEED + 1000 * rank)
         shared = np.random.default_rng(SEED + 4).integers(0, V, size=prefix).astype(np.uint32)
@@ -288,10 +289,12 @@ def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048
             batch.add_sequence(own, params)
             ttft.append(time.perf_counter() - t1)
         t_admit = time.perf_counter() - t0
-        batch.decode(4, params)  # warm-up steps (they advance the sequences by 4 positions)
+        batch.decode(warm, params)  # warm-up steps (they advance the sequences by `warm` positions)
+        profiler_range(True)
         ids, secs = batch.decode(steps, params)
+        profiler_range(False)
         kvb = synth_kv_bytes(cfg)
-        mean_pos = prefix + suffix + 4 + 1 + (steps - 1) / 2.0
+        mean_pos = prefix + suffix + warm + 1 + (steps - 1) / 2.0
         step_bytes = weight_bytes(cfg) + seqs * kvb * mean_pos
         return {"sequences": seqs, "shared_prefix_tokens": prefix, "own_prompt_tokens": suffix, "decode_steps": steps,
                 "sampling": "temperature 0.7, top-p 0.95, top-k 0, PCG32 per sequence", "kv": "f16, pages of 16 positions",
@@ -453,9 +456,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     if args.only_serving:
         sess.free()
-        profiler_range(True)
         res = serving_leg(B, ctx, path, cfg, rank, seqs=args.serving_seqs, steps=args.serving_steps)
-        profiler_range(False)
         if rank == 0:
             print(json.dumps({"metric": "serving_decode_tok_s", "value": res["decode_tok_s"], "unit": "tok/s", "serving": res,
                               "note": "batched serving leg only (profiling run)"}))

@@ -161,6 +161,8 @@ def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model,
     ids = np.random.default_rng(5).integers(0, 1024, size=n_prompt).astype(np.uint32)
     m = B.Qwen3.load(ctx, untied_model, limits)
     try:
+        if kv == "F32":
+            m.set_prefill_precision(B.PrefillPrecision.F32)
         want, _ = m.forward(ids, 0)
         want1, _ = m.forward(ids[:1], n_prompt)
         want_t, _ = m.decode_greedy(int(ids[0]), n_prompt, steps)
@@ -170,8 +172,12 @@ def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model,
     got = np.concatenate([r["logits"] for r in ranks], axis=1)
     got1 = np.concatenate([r["one"] for r in ranks], axis=1)
     assert [int(r["row0"]) for r in ranks] == [0, 512]
-    # the split changes only the order of the sums over o_proj's and down_proj's columns
-    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
-    assert np.abs(got1 - want1).max() <= 1e-4 * np.abs(want1).max()
+    # The split changes only the order of the sums over o_proj's and down_proj's columns. With an f32 cache the test
+    # runs the f32 prefill, so everything is f32 and the model-level bound for f32 applies; with an f16 cache the
+    # prefill rounds its GEMM inputs to f16 (PrefillPrecision::F16), where a last-bit difference in x can flip a
+    # rounding: the bound is the reference's floor for that mode (crates/models/tests/forward.rs:40-55).
+    tol = 1e-4 if kv == "F32" else 2e-3
+    assert np.abs(got - want).max() <= tol * np.abs(want).max()
+    assert np.abs(got1 - want1).max() <= tol * np.abs(want1).max()
     for r in ranks:
         assert list(r["toks"]) == list(want_t) and list(r["toks2"]) == list(want_t)

@@ -27,6 +27,8 @@ def main():
     m = B.Qwen3.load(ctx, pattern.format(rank=rank), limits)
     tp = TensorParallel(ctx, rank, world, limits.max_tokens * m.cfg["hidden"])
     m.set_tp(tp)
+    if kv_name == "F32":
+        m.set_prefill_precision(B.PrefillPrecision.F32)
     ids = np.random.default_rng(5).integers(0, m.cfg["vocab"], size=n_prompt).astype(np.uint32)
     dist.barrier()
     logits, _ = m.forward(ids, 0)                      # prefill: GEMM path, all-reduce of [tokens, hidden]
