@@ -530,6 +530,11 @@ class Kernels:
         self._k(self.L.brasa_k_sample_top_p(cmd._h, _arg(logits), C.c_uint32(n), C.c_float(temperature), C.c_uint32(top_k), C.c_float(top_p),
                                             _arg(rng_state), _arg(out)))
 
+    def sample_rows(self, cmd, logits, n, count, temperature, top_k, top_p, rng_states, scratch, out):
+        """The same for `count` rows; rng_states holds one pcg32_state per row, scratch count * n * 8 bytes."""
+        self._k(self.L.brasa_k_sample_rows(cmd._h, _arg(logits), C.c_uint32(n), C.c_uint32(count), C.c_float(temperature), C.c_uint32(top_k),
+                                           C.c_float(top_p), _arg(rng_states), _arg(scratch), _arg(out)))
+
 
 def pcg32_state(seed: int) -> np.ndarray:
     """Pcg32::new(seed) as the {state, increment} pair the device sampler keeps."""

@@ -109,6 +109,177 @@ __global__ void __launch_bounds__(128) decode_partial_paged_kernel(const float *
     }
 }
 
+
+// ---- the same partial for an f16 pool on the tensor cores ----------------------------------------------------------
+// With many sequences the step reads gigabytes of KV and the scalar kernel above is bound by its FMA and shared-memory
+// traffic, not by HBM. Here a block (4 warps) takes the same (128-key chunk, kv head, sequence): K and V rows arrive
+// with cp.async as raw f16 (rows of 256 bytes, 16-byte pieces XOR-swizzled by the row), warp w owns keys [32 w, 32 w + 32):
+//   S = Q K^T with mma.sync m16n8k16 (rows = the GQA group's heads, padded to 16; Q enters as two f16 terms hi + lo, so the
+//   scores keep f32 accuracy: K is f16 in the cache, nothing else is rounded), block-wide row maximum and sum through
+//   shared memory, P = exp(S - m) again as hi + lo f16 terms, O = P V with V fragments from ldmatrix.trans, and the four
+//   warps' O added in shared memory. Output: the partial layout of the kernel above, so the reduction is shared.
+__device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, bool valid) {
+    const uint32_t bytes = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mma_f16(float c[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A (registers a1, a3) are zero: the group has at most 8 heads
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t r[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t r[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+// two floats -> packed f16 pair (hi) and the pair of what the rounding dropped (lo)
+__device__ __forceinline__ void split_h2(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 back = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - back.x, y - back.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+// byte offset of the 16-byte piece `c` of row `r` in a [128 rows][256 bytes] tile
+__device__ __forceinline__ uint32_t piece(uint32_t r, uint32_t c) { return r * 256u + ((c ^ (r & 7u)) << 4); }
+
+constexpr uint32_t MMA_TILE = 128 * 256;  // one K or V tile
+constexpr size_t MMA_SMEM = 2 * MMA_TILE + (2 * 4 * 8 + 16) * sizeof(float);  // three blocks per SM
+
+__global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const float *q, Paged kp, Paged vp, const uint32_t *lens, float *partials,
+                                                                       uint32_t hq, uint32_t max_chunks, float scale) {
+    extern __shared__ __align__(128) uint8_t smem_b[];
+    uint8_t *kt = smem_b, *vt = smem_b + MMA_TILE;
+    float *osum = reinterpret_cast<float *>(kt);  // [4 warps][8 heads][128], over the K tile once every warp is done with it
+    float *wmax = reinterpret_cast<float *>(smem_b + 2 * MMA_TILE), *wsum = wmax + 4 * 8;  // [4 warps][8 heads] each
+    const uint32_t chunk = blockIdx.x, kh = blockIdx.y, seq = blockIdx.z, hkv = kp.hkv, G = hq / hkv;
+    const uint32_t lk = lens[seq] + 1;
+    if (chunk * 128 >= lk) return;
+    const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
+    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
+    // ---- K then V: 128 rows x 16 pieces each; rows past the end are zero-filled ----
+    for (uint32_t i = t; i < 128 * 16; i += 128) {
+        const uint32_t r = i >> 4, c = i & 15;
+        const bool ok = r < nkeys;
+        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (uint32_t i = t; i < 128 * 16; i += 128) {
+        const uint32_t r = i >> 4, c = i & 15;
+        const bool ok = r < nkeys;
+        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    // ---- Q fragments of head g (rows >= G are zero): for k-step ks, a0 = dims 16 ks + 2 tq, +1; a2 = those + 8 ----
+    uint32_t qh0[8], qh2[8], ql0[8], ql2[8];
+    {
+        const float *qrow = q + ((size_t)seq * hq + kh * G + (g < G ? g : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            float2 a = make_float2(0.0f, 0.0f), b = a;
+            if (g < G) {
+                a = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq);
+                b = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq + 8);
+            }
+            split_h2(a.x, a.y, qh0[ks], ql0[ks]);
+            split_h2(b.x, b.y, qh2[ks], ql2[ks]);
+        }
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    // ---- S[head g][keys 32 warp + 8 j + 2 tq, +1], j = 0..3 ----
+    float sc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+    {
+        // ldmatrix.x4: lanes 0-7 address rows of tile 0, 8-15 tile 1, 16-23 tile 2, 24-31 tile 3;
+        // tiles = (dims 16 ks .. +7), (dims 16 ks + 8 ..), (dims 16 (ks + 1) ..), (dims 16 (ks + 1) + 8 ..) of 8 keys
+        const uint32_t lrow = lane & 7, ltile = lane >> 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t krow = 32 * warp + 8 * j + lrow;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks += 2) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kt + piece(krow, 2 * ks + ltile));
+                mma_f16(sc[j], qh0[ks], qh2[ks], b[0], b[1]);
+                mma_f16(sc[j], ql0[ks], ql2[ks], b[0], b[1]);
+                mma_f16(sc[j], qh0[ks + 1], qh2[ks + 1], b[2], b[3]);
+                mma_f16(sc[j], ql0[ks + 1], ql2[ks + 1], b[2], b[3]);
+            }
+        }
+    }
+    // ---- scale, mask, row maximum over the block ----
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t key = 32 * warp + 8 * j + 2 * tq + e;
+            const float v = key < nkeys ? sc[j][e] * scale : -INFINITY;
+            sc[j][e] = v;
+            mx = fmaxf(mx, v);
+        }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    if (tq == 0) wmax[warp * 8 + g] = mx;
+    __syncthreads();
+    const float m = fmaxf(fmaxf(wmax[g], wmax[8 + g]), fmaxf(wmax[16 + g], wmax[24 + g]));
+    float l = 0.0f;
+    uint32_t ph[4], pl[4];  // P of n-tile j as packed pairs: A fragment a0 (j even) or a2 (j odd) of k-step j / 2
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float p0 = sc[j][0] == -INFINITY ? 0.0f : expf(sc[j][0] - m), p1 = sc[j][1] == -INFINITY ? 0.0f : expf(sc[j][1] - m);
+        l += p0 + p1;
+        split_h2(p0, p1, ph[j], pl[j]);
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (tq == 0) wsum[warp * 8 + g] = l;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // ---- O[head g][dims 8 n + 2 tq, +1] += P[16 x 32 keys] V[32 keys x 128 dims] ----
+    float oc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) oc[n][0] = oc[n][1] = oc[n][2] = oc[n][3] = 0.0f;
+    {
+        // ldmatrix.x4.trans over V rows (keys): tiles = (keys 0-7, dims 8 n ..), (keys 8-15, dims 8 n ..),
+        // (keys 0-7, dims 8 (n + 1) ..), (keys 8-15, dims 8 (n + 1) ..) -> b0, b1 of n-tile n and of n-tile n + 1
+        const uint32_t lrow = lane & 7, ltile = lane >> 3;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            const uint32_t vrow = 32 * warp + 16 * kk + 8 * (ltile & 1) + lrow;
+#pragma unroll
+            for (int n = 0; n < 16; n += 2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vt + piece(vrow, n + (ltile >> 1)));
+                mma_f16(oc[n], ph[2 * kk], ph[2 * kk + 1], b[0], b[1]);
+                mma_f16(oc[n], pl[2 * kk], pl[2 * kk + 1], b[0], b[1]);
+                mma_f16(oc[n + 1], ph[2 * kk], ph[2 * kk + 1], b[2], b[3]);
+                mma_f16(oc[n + 1], pl[2 * kk], pl[2 * kk + 1], b[2], b[3]);
+            }
+        }
+    }
+    if (g < G) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) *reinterpret_cast<float2 *>(osum + (warp * 8 + g) * D + 8 * n + 2 * tq) = make_float2(oc[n][0], oc[n][1]);
+    }
+    __syncthreads();
+    for (uint32_t h = 0; h < G; ++h) {
+        float *out = partials + (((size_t)seq * hq + kh * G + h) * max_chunks + chunk) * 130;
+        out[2 + t] = (osum[(0 * 8 + h) * D + t] + osum[(1 * 8 + h) * D + t]) + (osum[(2 * 8 + h) * D + t] + osum[(3 * 8 + h) * D + t]);
+        if (t == 0) {
+            out[0] = fmaxf(fmaxf(wmax[h], wmax[8 + h]), fmaxf(wmax[16 + h], wmax[24 + h]));
+            out[1] = (wsum[h] + wsum[8 + h]) + (wsum[16 + h] + wsum[24 + h]);
+        }
+    }
+}
+
 // grid (head, sequence); output f32 or f16 (the input type of the o_proj GEMM)
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(128) decode_reduce_paged_kernel(const float *partials, const uint32_t *lens, void *o, uint32_t hq, uint32_t max_chunks) {
@@ -186,6 +357,7 @@ struct brasa_batch {
     uint32_t nseq = 0, next_page = 0, prefix_len = 0;
     size_t row_bytes = 0, pool_layer_bytes = 0, cache_layer_bytes = 0;
     uint64_t max_chunks = 0;
+    bool mma_attention = true;  // f16 pool: tensor-core partial kernel (BRASA_BATCH_MMA=0 keeps the scalar one)
     brasa_buf *kpool = nullptr, *vpool = nullptr, *table = nullptr, *lens = nullptr, *ids = nullptr, *rng = nullptr, *logits = nullptr,
               *partials = nullptr, *scratch = nullptr, *out = nullptr;
     std::vector<int32_t> h_table;  // host mirror [max_seqs][max_pages]
@@ -287,7 +459,20 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged"));                                                                               \
     } while (0)
         if (m->limits.kv == BRASA_KV_F32) LAUNCH_BATCH(BRASA_KV_F32);
-        else if (m->limits.kv == BRASA_KV_F16) LAUNCH_BATCH(BRASA_KV_F16);
+        else if (m->limits.kv == BRASA_KV_F16 && b->mma_attention) {
+            static bool attr_done = false;
+            if (!attr_done) {
+                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
+                attr_done = true;
+            }
+            qk_norm_rope_store_paged_kernel<BRASA_KV_F16><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(
+                F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages, lens, c.heads,
+                c.kv_heads, c.eps, rows);
+            BRASA_TRY(brasa_post_launch(cmd, "qk_norm_rope_store_paged"));
+            decode_partial_paged_mma_kernel<<<agrid, 128, MMA_SMEM, ctx->stream>>>(F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks,
+                                                                                scale);
+            BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma"));
+        } else if (m->limits.kv == BRASA_KV_F16) LAUNCH_BATCH(BRASA_KV_F16);
         else LAUNCH_BATCH(BRASA_KV_Q8_0);
 #undef LAUNCH_BATCH
         if (half_io) decode_reduce_paged_kernel<true><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
@@ -339,6 +524,10 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     std::unique_ptr<brasa_batch, void (*)(brasa_batch *)> b(new brasa_batch, brasa_batch_free);
     b->m = m;
     b->ctx = ctx;
+    {
+        const char *e = getenv("BRASA_BATCH_MMA");
+        b->mma_attention = !(e && e[0] == '0');
+    }
     b->max_seqs = max_seqs;
     b->num_pages = num_pages;
     b->max_pages = (max_positions + PAGE - 1) / PAGE;

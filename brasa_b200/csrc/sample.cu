@@ -209,6 +209,189 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float *logits, uint3
     }
 }
 
+
+// ---- the same sampler for many rows at once, every row spread over several blocks --------------------------------
+// One block per row walks the vocabulary some hundred times (a bisection step is a pass); with 64 rows that costs
+// milliseconds per decode step. Here a row is shared by up to 16 blocks and each search is a radix select: four
+// passes of 8 key bits, each building a 256-bin histogram of the candidates' mass under the prefix chosen so far;
+// the last block of a row to arrive picks the bin in which the running mass reaches the bound. Masses are 64-bit
+// fixed point (weight x 2^40, truncated), so sums do not depend on the order of the additions and a row's choice is
+// reproducible whatever the grid; candidates with equal logits have equal weights, so the cut inside a group of
+// equals is a count, resolved by rows_tie_kernel in ascending id order as the host sampler does.
+// A row's scratch: RowState, then 8 histograms (2 searches x 4 digits) of 256 x u64.
+constexpr int ROWS_THREADS = 256, ROWS_WARPS = ROWS_THREADS / 32, ROWS_MAX_BLOCKS = 16;
+constexpr float ROWS_FIX = 1099511627776.0f;  // 2^40
+
+struct RowState {
+    unsigned long long total, bound[2], above[2], m[2], wt[2];
+    uint32_t kmax, pref[2], t[2], id_cut, arrive[8];
+};
+constexpr size_t ROWS_STATE_BYTES = 256, ROWS_SCRATCH_BYTES = ROWS_STATE_BYTES + 8 * 256 * 8;
+static_assert(sizeof(RowState) <= ROWS_STATE_BYTES, "row state");
+
+__device__ __forceinline__ float key_value(uint32_t k) {  // inverse of order_key
+    int32_t b = (int32_t)(k ^ 0x80000000u);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    return __int_as_float(b);
+}
+__device__ __forceinline__ unsigned long long fixed_weight(float l, float mx, float temperature) {
+    return __float2ull_rz(expf((l - mx) / temperature) * ROWS_FIX);
+}
+
+__global__ void __launch_bounds__(ROWS_THREADS) rows_max_kernel(const float *logits, uint32_t n, uint8_t *scratch) {
+    RowState *st = reinterpret_cast<RowState *>(scratch + (size_t)blockIdx.y * ROWS_SCRATCH_BYTES);
+    const float *row = logits + (size_t)blockIdx.y * n;
+    uint32_t kmax = 0;
+    for (uint32_t i = blockIdx.x * ROWS_THREADS + threadIdx.x; i < n; i += gridDim.x * ROWS_THREADS) kmax = max(kmax, order_key(row[i]));
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(&st->kmax, kmax);
+}
+
+// phase 0: the top-p cut over the whole row; phase 1: the drawn token inside the cut. digit 3 (top byte) first.
+__global__ void __launch_bounds__(ROWS_THREADS) rows_hist_kernel(const float *logits, uint32_t n, uint8_t *scratch, float temperature, float top_p,
+                                                                 int phase, int digit) {
+    __shared__ unsigned long long wh[ROWS_WARPS][256];
+    __shared__ unsigned long long wtot[ROWS_WARPS];
+    __shared__ bool last;
+    RowState *st = reinterpret_cast<RowState *>(scratch + (size_t)blockIdx.y * ROWS_SCRATCH_BYTES);
+    unsigned long long *hist = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(st) + ROWS_STATE_BYTES) + (phase * 4 + 3 - digit) * 256;
+    const float *row = logits + (size_t)blockIdx.y * n;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (uint32_t i = tid; i < ROWS_WARPS * 256; i += ROWS_THREADS) (&wh[0][0])[i] = 0;
+    __syncthreads();
+    const float mx = key_value(st->kmax);
+    const uint32_t shift = 8u * digit, pref = st->pref[phase];
+    const Prefix cut = phase ? Prefix{st->t[0], st->id_cut} : Prefix{0u, 0xffffffffu};
+    for (uint32_t i = blockIdx.x * ROWS_THREADS + tid; i < n; i += gridDim.x * ROWS_THREADS) {
+        const float l = row[i];
+        const uint32_t k = order_key(l);
+        if (digit < 3 && (k >> (shift + 8)) != (pref >> (shift + 8))) continue;
+        if (phase && !in_prefix(k, i, cut)) continue;
+        const unsigned long long w = fixed_weight(l, mx, temperature);
+        if (w) atomicAdd(&wh[warp][(k >> shift) & 255u], w);
+    }
+    __syncthreads();
+    {
+        unsigned long long s = 0;
+        for (int w = 0; w < ROWS_WARPS; ++w) s += wh[w][tid];
+        if (s) atomicAdd(&hist[tid], s);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last = atomicAdd(&st->arrive[phase * 4 + 3 - digit], 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // ---- the row's histogram is complete: pick the bin where the mass, summed from the top, reaches the bound ----
+    const unsigned long long h = __ldcg(&hist[tid]);
+    unsigned long long v = h;  // inclusive suffix sum over bins >= tid
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_down_sync(0xffffffffu, v, o);
+        if (lane + o < 32) v += up;
+    }
+    if (lane == 0) wtot[warp] = v;
+    __syncthreads();
+    for (int w = warp + 1; w < ROWS_WARPS; ++w) v += wtot[w];
+    unsigned long long bound, above;
+    if (phase == 0 && digit == 3) {
+        unsigned long long total = 0;
+        for (int w = 0; w < ROWS_WARPS; ++w) total += wtot[w];
+        const double b = ceil((double)total * (double)top_p);
+        bound = b >= (double)total ? total : (unsigned long long)b;
+        if (bound < 1) bound = 1;
+        above = 0;
+        if (tid == 0) {
+            st->total = total;
+            st->bound[0] = bound;
+        }
+    } else {
+        bound = st->bound[phase];
+        above = st->above[phase];
+    }
+    const unsigned long long mine = above + v;                       // mass of the bins >= tid under this prefix
+    const unsigned long long next = __shfl_down_sync(0xffffffffu, mine, 1);
+    __syncthreads();
+    wtot[warp] = 0;  // reuse: first value of the following warp
+    __syncthreads();
+    if (lane == 0 && warp > 0) wtot[warp - 1] = mine;
+    __syncthreads();
+    const unsigned long long higher = tid == 255 ? above : (lane == 31 ? wtot[warp] : next);  // mass of the bins > tid
+    if (mine >= bound && higher < bound) {
+        const uint32_t chosen = pref | ((uint32_t)tid << shift);
+        st->pref[phase] = chosen;
+        st->above[phase] = higher;
+        if (digit == 0) {
+            const unsigned long long wt = fixed_weight(key_value(chosen), mx, temperature);
+            st->t[phase] = chosen;
+            st->wt[phase] = wt;
+            st->m[phase] = wt ? (bound - higher + wt - 1) / wt : 1;  // how many of the equal candidates the prefix takes
+        }
+    }
+}
+
+// The m-th candidate, in ascending id order, among those whose key equals the search's threshold: the last member of
+// the prefix. phase 0: it closes the top-p cut, then the row's PCG32 draw sets the bound of the second search;
+// phase 1: it is the sampled token.
+__global__ void __launch_bounds__(1024) rows_tie_kernel(const float *logits, uint32_t n, uint8_t *scratch, int phase, unsigned long long *rng,
+                                                        uint32_t *out) {
+    __shared__ uint32_t wsum[32];
+    RowState *st = reinterpret_cast<RowState *>(scratch + (size_t)blockIdx.x * ROWS_SCRATCH_BYTES);
+    const float *row = logits + (size_t)blockIdx.x * n;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t t = st->t[phase];
+    const unsigned long long m = st->m[phase];
+    const Prefix cut = phase ? Prefix{st->t[0], st->id_cut} : Prefix{0u, 0xffffffffu};
+    const uint32_t seg = (n + 1023) / 1024, lo = min(n, tid * seg), hi = min(n, lo + seg);
+    uint32_t cnt = 0;
+    for (uint32_t i = lo; i < hi; ++i) cnt += (order_key(row[i]) == t && in_prefix(t, i, cut)) ? 1u : 0u;
+    uint32_t incl = cnt;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t dn = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((int)lane >= o) incl += dn;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    uint32_t before = incl - cnt, all = 0;
+    for (uint32_t w = 0; w < 32; ++w) {
+        if (w < warp) before += wsum[w];
+        all += wsum[w];
+    }
+    if (all == 0) {  // nothing carries the threshold key (a row of NaN): token 0, and a second search that selects nothing
+        if (tid == 0) {
+            if (phase == 0) st->bound[1] = 1;
+            else out[blockIdx.x] = 0;
+        }
+        return;
+    }
+    const unsigned long long mm = m < 1 ? 1 : (m > all ? all : m);
+    if (!(before < mm && mm <= (unsigned long long)before + cnt)) return;
+    uint32_t left = (uint32_t)(mm - before), id = lo;
+    for (uint32_t i = lo; i < hi; ++i)
+        if (order_key(row[i]) == t && in_prefix(t, i, cut) && --left == 0) {
+            id = i;
+            break;
+        }
+    if (phase == 0) {
+        st->id_cut = id;
+        const unsigned long long kept = st->above[0] + mm * st->wt[0];
+        unsigned long long *state = rng + 2 * blockIdx.x;
+        const unsigned long long old = state[0], inc = state[1];
+        const uint32_t x = (uint32_t)(((old >> 18) ^ old) >> 27), rot = (uint32_t)(old >> 59);
+        const uint32_t u24 = ((x >> rot) | (x << ((32 - rot) & 31))) >> 8;
+        state[0] = old * 6364136223846793005ULL + inc;
+        // the walk stops at the first candidate whose running mass reaches u24 / 2^24 of the kept mass (at least 1 unit:
+        // a draw of 0 takes the first candidate)
+        const unsigned long long hi64 = __umul64hi(kept, (unsigned long long)u24), lo64 = kept * (unsigned long long)u24;
+        unsigned long long b = (hi64 << 40) | (lo64 >> 24);
+        if (lo64 & 0xffffffull) b += 1;
+        st->bound[1] = b < 1 ? 1 : b;
+        st->above[1] = 0;
+        st->pref[1] = 0;
+    } else {
+        out[blockIdx.x] = id;
+    }
+}
+
 // greedy choice per row: first index of the maximum, NaN ignored, 0 when every logit is -inf
 __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *logits, uint32_t n, uint32_t *out) {
     __shared__ Best sh[32];
@@ -235,6 +418,23 @@ int32_t brasa_sample_batched_launch(brasa_cmd *cmd, const float *logits, uint32_
         return brasa_post_launch(cmd, "argmax_rows");
     }
     BRASA_REQUIRE(ctx, top_p > 0.0f, "sample_top_p: top_p must be positive");
+    if (count > 1 && (top_k == 0 || top_k >= n) && (size_t)n * 8 >= ROWS_SCRATCH_BYTES) {
+        // many rows: every row over several blocks (a row's scratch of 2 n floats holds its state and histograms)
+        uint8_t *sc = reinterpret_cast<uint8_t *>(scratch);
+        BRASA_CUDA(ctx, cudaMemsetAsync(sc, 0, (size_t)count * ROWS_SCRATCH_BYTES, ctx->stream));
+        const dim3 grid(std::min<uint32_t>(ROWS_MAX_BLOCKS, (n + 4095) / 4096), count);
+        rows_max_kernel<<<grid, ROWS_THREADS, 0, ctx->stream>>>(logits, n, sc);
+        BRASA_TRY(brasa_post_launch(cmd, "sample_rows_max"));
+        for (int phase = 0; phase < 2; ++phase) {
+            for (int digit = 3; digit >= 0; --digit) {
+                rows_hist_kernel<<<grid, ROWS_THREADS, 0, ctx->stream>>>(logits, n, sc, temperature, top_p, phase, digit);
+                BRASA_TRY(brasa_post_launch(cmd, "sample_rows_hist"));
+            }
+            rows_tie_kernel<<<count, 1024, 0, ctx->stream>>>(logits, n, sc, phase, rng, out);
+            BRASA_TRY(brasa_post_launch(cmd, "sample_rows_tie"));
+        }
+        return BRASA_OK;
+    }
     sample_kernel<<<count, 1024, 0, ctx->stream>>>(logits, n, temperature, top_k, top_p, rng, scratch, out, nullptr, nullptr, nullptr);
     return brasa_post_launch(cmd, "sample_top_p");
 }
@@ -287,6 +487,18 @@ int32_t brasa_k_sample_top_p(brasa_cmd *cmd, brasa_arg logits, uint32_t n, float
     sample_kernel<<<1, 1024, 0, ctx->stream>>>((const float *)arg_ptr(logits), n, temperature, top_k, top_p, (unsigned long long *)arg_ptr(rng_state),
                                                ctx->sample_scratch, (uint32_t *)arg_ptr(out_u32), nullptr, nullptr, nullptr);
     return brasa_post_launch(cmd, "sample_top_p");
+}
+
+int32_t brasa_k_sample_rows(brasa_cmd *cmd, brasa_arg logits, uint32_t n, uint32_t count, float temperature, uint32_t top_k, float top_p,
+                            brasa_arg rng_states, brasa_arg scratch, brasa_arg out_u32) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, n > 0 && arg_fits(logits, (uint64_t)count * n * 4) && arg_fits(out_u32, (uint64_t)count * 4) &&
+                           arg_fits(rng_states, (uint64_t)count * 16) && arg_fits(scratch, (uint64_t)count * n * 8),
+                  "sample_rows: buffers too small");
+    BRASA_REQUIRE(ctx, rng_states.offset % 8 == 0 && scratch.offset % 8 == 0, "sample_rows: misaligned");
+    return brasa_sample_batched_launch(cmd, (const float *)arg_ptr(logits), n, count, temperature, top_k, top_p,
+                                       (unsigned long long *)arg_ptr(rng_states), (float *)arg_ptr(scratch), (uint32_t *)arg_ptr(out_u32));
 }
 
 void brasa_pcg32_seed(uint64_t seed, uint64_t state_inc[2]) {

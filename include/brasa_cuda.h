@@ -206,6 +206,11 @@ int32_t brasa_k_argmax(brasa_cmd *cmd, brasa_arg logits, uint32_t n, brasa_arg o
  * with brasa_pcg32_seed). temperature <= 0 is the greedy argmax. The chosen token id goes to out_u32. */
 int32_t brasa_k_sample_top_p(brasa_cmd *cmd, brasa_arg logits, uint32_t n, float temperature, uint32_t top_k, float top_p, brasa_arg rng_state,
                              brasa_arg out_u32);
+/* The same for `count` rows of n logits, row r with its own state at rng_states + 16 r and its token in out_u32[r];
+ * scratch: count x n x 8 bytes. With top-k off and two or more rows every row is spread over several blocks (radix
+ * select over 64-bit fixed-point masses: a row's token does not depend on how many rows share the launch). */
+int32_t brasa_k_sample_rows(brasa_cmd *cmd, brasa_arg logits, uint32_t n, uint32_t count, float temperature, uint32_t top_k, float top_p,
+                            brasa_arg rng_states, brasa_arg scratch, brasa_arg out_u32);
 /* Pcg32::new(seed) (sampler.rs:13-20) as the two words brasa_k_sample_top_p keeps on the device. */
 void brasa_pcg32_seed(uint64_t seed, uint64_t state_inc[2]);
 
