@@ -11,6 +11,8 @@
 
 #include "../../include/brasa_cuda.h"
 
+constexpr uint32_t GEMM_TC_COUNTERS = 8192;
+
 struct brasa_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -39,6 +41,9 @@ struct brasa_ctx {
     float *sample_scratch = nullptr;  // weights of the device sampler (2 x vocabulary)
     size_t sample_scratch_n = 0;
     void *argmax_scratch = nullptr;  // arrival counter + per-block partial maxima
+    float *gemm_part = nullptr;      // partial output tiles of the split-K tensor-core GEMM
+    size_t gemm_part_bytes = 0;
+    uint32_t *gemm_counters = nullptr;  // arrivals per output tile of that GEMM (GEMM_TC_COUNTERS words, zero between launches)
     bool gemv_attr_done[10] = {};  // opt-in shared memory size set on this device, per kernel instance
 };
 

@@ -71,6 +71,8 @@ void brasa_ctx_destroy(brasa_ctx *ctx) {
     cudaFree(ctx->gemv_partials);
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->gemm_part);
+    cudaFree(ctx->gemm_counters);
     cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);
     cudaFree(ctx->status);
@@ -117,6 +119,7 @@ int32_t brasa_ctx_sync(brasa_ctx *ctx) {
     BRASA_CUDA(ctx, cudaMemcpy(&st, ctx->status, 4, cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(ctx->status, 0, 4);
+        if (ctx->gemm_counters) cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4);  // a kernel that gave up may have left arrivals behind
         return brasa_fail(ctx, BRASA_ETIMEOUT, "a bounded device-side wait ran out (status %u)", st);
     }
     return BRASA_OK;
@@ -226,6 +229,7 @@ int32_t brasa_cmd_wait(brasa_cmd *cmd, double *gpu_seconds) {
         cudaMemcpy(&st, ctx->status, 4, cudaMemcpyDeviceToHost);
         if (st != 0) {
             cudaMemset(ctx->status, 0, 4);
+            if (ctx->gemm_counters) cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4);
             rc = brasa_fail(ctx, BRASA_ETIMEOUT, "a bounded device-side wait ran out (status %u)", st);
         }
     }
@@ -338,6 +342,8 @@ int32_t brasa_gemv_scratch(brasa_ctx *ctx, size_t partial_floats, size_t counter
         BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
+    cudaFree(ctx->gemm_part);
+    cudaFree(ctx->gemm_counters);
     cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);
         ctx->gemv_counters = nullptr;

@@ -73,6 +73,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// p0, p1 in [0, 1] -> packed f16 pair `hi` (each value cut to 11 significant bits in f32 first, so the f16 rounding is
+// exact down to the subnormals) and the packed pair `lo` of what the cut dropped: hi + lo = p to 2^-22.
+__device__ __forceinline__ void split_pair(float p0, float p1, uint32_t &hi, uint32_t &lo) {
+    const float h0 = __uint_as_float((__float_as_uint(p0) + 0x1000u) & 0xFFFFE000u), h1 = __uint_as_float((__float_as_uint(p1) + 0x1000u) & 0xFFFFE000u);
+    const __half2 hh = __floats2half2_rn(h0, h1), ll = __floats2half2_rn(p0 - h0, p1 - h1);
+    hi = *reinterpret_cast<const uint32_t *>(&hh);
+    lo = *reinterpret_cast<const uint32_t *>(&ll);
+}
+
 struct FlashTcParams {
     const float *q;        // [tokens][hq][128] after QK-norm and RoPE
     const uint8_t *kc, *vc;  // cache rows [position][hkv][128] in the cache's type, from position 0
@@ -91,7 +100,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *kt = smem + TILE_BYTES, *vt = smem + 2 * TILE_BYTES, *ph = smem + 3 * TILE_BYTES, *pl = smem + 4 * TILE_BYTES;
     uint8_t *kl = smem + 5 * TILE_BYTES, *vl = smem + 6 * TILE_BYTES;  // SPLIT: low terms of K and V; else their second buffers
-    __shared__ uint64_t bar_s, bar_o;
+    __shared__ uint64_t bar_s2[2], bar_o;  // S lives in two tensor-memory buffers when K is double-buffered (f16 caches)
     __shared__ uint32_t tmem_base_s, abort_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -102,13 +111,14 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     const uint32_t nkt = last_key / 128 + 1;
 
     if (tid == 0) {
-        mbar_init(&bar_s, 1);
+        mbar_init(&bar_s2[0], 1);
+        mbar_init(&bar_s2[1], 1);
         mbar_init(&bar_o, 1);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory: S in columns [0, 128), O in [128, 256)
-        uint32_t ncols = 256;
+    if (warp == 1) {  // tensor memory: S in columns [0, 128) and [128, 256), O in [256, 384)
+        uint32_t ncols = 512;
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -130,7 +140,8 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256;
+    uint64_t &bar_s = bar_s2[0];
     volatile uint32_t *abort_flag = &abort_s;
 
     auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
@@ -176,14 +187,14 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     constexpr bool PIPE = !SPLIT;
     auto KB = [&](uint32_t j) { return (PIPE && (j & 1)) ? kl : kt; };
     auto VB = [&](uint32_t j) { return (PIPE && (j & 1)) ? vl : vt; };
-    auto issue_s = [&](const uint8_t *kb) {  // S = Q K^T
+    auto issue_s = [&](const uint8_t *kb, uint32_t sbuf = 0) {  // S[sbuf] = Q K^T
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kb) + off), idesc_s, ks > 0);
-            if (SPLIT) umma(tmem_s, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kl) + off), idesc_s, 1u);
+            umma(tmem_s + 128 * sbuf, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kb) + off), idesc_s, ks > 0);
+            if (SPLIT) umma(tmem_s + 128 * sbuf, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kl) + off), idesc_s, 1u);
         }
-        umma_commit(&bar_s);
+        umma_commit(&bar_s2[sbuf]);
     };
 
     // softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63)
@@ -196,34 +207,45 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     bool ok = true;
 
     // ---- sweep 1: row maxima and sums ----
-    if (PIPE) {
+    uint32_t phs0 = 0, phs1 = 0;  // phases of the two S barriers
+    if constexpr (PIPE) {
+        // S of tile j + 1 is issued into the other tensor-memory buffer before tile j's scores are read, so the tensor
+        // core works while the rows are scanned; the K tile after that travels meanwhile.
         load_tile(p.kc, KB(0), kl, 0);
+        if (nkt > 1) load_tile(p.kc, KB(1), kl, 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    for (uint32_t j = 0; j < nkt && ok; ++j) {
-        if (!PIPE) {
-            load_tile(p.kc, kt, kl, j);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(KB(j));
+            issue_s(KB(0), 0);
         }
-        if (PIPE && j + 1 < nkt) {  // the other K buffer was last read by S of tile j - 1, which this thread has seen finish
-            load_tile(p.kc, KB(j + 1), kl, j + 1);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        ok = wait(&bar_s, ph_s);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (uint32_t j = 0; j < nkt; ++j) {
+            if (j > 0) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");  // K of tile j + 1
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            ok = __syncthreads_and(ok);  // tile j - 1's scores have been read by everyone: its S buffer may be overwritten
+            if (!ok) break;
+            if (tid == 0 && j + 1 < nkt) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(j + 1), (j + 1) & 1);
+            }
+            ok = wait(&bar_s2[j & 1], (j & 1) ? phs1 : phs0);
+            if (j & 1) phs1 ^= 1;
+            else phs0 ^= 1;
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && j + 2 < nkt) {  // S of tile j is complete: its K buffer is free
+                load_tile(p.kc, KB(j + 2), kl, j + 2);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (uint32_t c = chalf; c < chalf + 64; c += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_s + trow + c, v);
+                tmem_ld32(tmem_s + 128 * (j & 1) + trow + c, v);
                 float cm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -232,138 +254,266 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
                     v[i] = __float_as_uint(sv);
                     cm = fmaxf(cm, sv);
                 }
-                const float mn = fmaxf(m, cm);
-                if (mn != -INFINITY) {
-                    float add = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) add += exp2f((__uint_as_float(v[i]) - mn) * LOG2E);
-                    l = l * (m == -INFINITY ? 0.0f : exp2f((m - mn) * LOG2E)) + add;
-                    m = mn;
-                }
+                m = fmaxf(m, cm);
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
         }
-        ph_s ^= 1;
-        ok = __syncthreads_and(ok);  // S has been read: the K tile and S may be overwritten
+        ok = __syncthreads_and(ok);
+    } else {
+        if (PIPE) {
+            load_tile(p.kc, KB(0), kl, 0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        for (uint32_t j = 0; j < nkt && ok; ++j) {
+            if (!PIPE) {
+                load_tile(p.kc, kt, kl, j);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(j));
+            }
+            if (PIPE && j + 1 < nkt) {  // the other K buffer was last read by S of tile j - 1, which this thread has seen finish
+                load_tile(p.kc, KB(j + 1), kl, j + 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            ok = wait(&bar_s, ph_s);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    #pragma unroll 1
+                for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + trow + c, v);
+                    float cm = -INFINITY;
+    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t key = j * 128 + c + i;
+                        const float sv = key <= qpos ? __uint_as_float(v[i]) : -INFINITY;
+                        v[i] = __float_as_uint(sv);
+                        cm = fmaxf(cm, sv);
+                    }
+                    m = fmaxf(m, cm);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            ph_s ^= 1;
+            ok = __syncthreads_and(ok);  // S has been read: the K tile and S may be overwritten
+        }
     }
-    // the two halves of a row meet (the P tiles are free until the second sweep writes them)
+    // the two halves of a row agree on its maximum (the P tiles are free until the second sweep writes them); the sum
+    // of the row is gathered in the second sweep from the very probabilities that go into P V
     {
-        float *stat = reinterpret_cast<float *>(ph);  // [2][128] maxima, then [2][128] sums
+        float *stat = reinterpret_cast<float *>(ph);  // [2][128] maxima
         stat[(warp >> 2) * 128 + row] = m;
-        stat[256 + (warp >> 2) * 128 + row] = l;
         __syncthreads();
-        const float m0 = stat[row], m1 = stat[128 + row], l0 = stat[256 + row], l1 = stat[384 + row];
-        const float M = fmaxf(m0, m1);
-        l = (m0 == -INFINITY ? 0.0f : l0 * exp2f((m0 - M) * LOG2E)) + (m1 == -INFINITY ? 0.0f : l1 * exp2f((m1 - M) * LOG2E));
-        m = M;
+        m = fmaxf(stat[row], stat[128 + row]);
         __syncthreads();
     }
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
-    if (PIPE && ok) {
-        load_tile(p.kc, KB(0), kl, 0);
-        load_tile(p.vc, VB(0), vl, 0);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    for (uint32_t j = 0; j < nkt && ok; ++j) {
-        if (!PIPE) {
-            if (j > 0) {  // the previous tile's P V must have finished reading V and P
+    if constexpr (PIPE) {
+        // Tensor-core order: .. P V of tile j - 1, S of tile j + 1, P V of tile j ..: S of the next tile is computed while
+        // this tile's probabilities are formed (in registers; they are stored once P V of the previous tile has let go of the
+        // P tiles), and P V of this tile runs while the next tile's probabilities are formed.
+        if (ok) {
+            load_tile(p.kc, KB(0), kl, 0);
+            load_tile(p.vc, VB(0), vl, 0);
+            if (nkt > 1) load_tile(p.kc, KB(1), kl, 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        ok = __syncthreads_and(ok);
+        if (ok && tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(KB(0), 0);
+        }
+        for (uint32_t j = 0; j < nkt && ok; ++j) {
+            if (j > 0) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");  // K of tile j + 1 and V of tile j
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            if (tid == 0 && j + 1 < nkt) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(j + 1), (j + 1) & 1);
+            }
+            ok = wait(&bar_s2[j & 1], (j & 1) ? phs1 : phs0);
+            if (j & 1) phs1 ^= 1;
+            else phs0 ^= 1;
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && j + 2 < nkt) {
+                load_tile(p.kc, KB(j + 2), kl, j + 2);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            uint32_t hi[2][16], lo[2][16];
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const uint32_t c = chalf + 32 * cc;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + 128 * (j & 1) + trow + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const uint32_t key = j * 128 + c + i;
+                        const float p0 = key <= qpos ? exp2f((__uint_as_float(v[i]) - m) * LOG2E) : 0.0f;
+                        const float p1 = key + 1 <= qpos ? exp2f((__uint_as_float(v[i + 1]) - m) * LOG2E) : 0.0f;
+                        l += p0 + p1;
+                        split_pair(p0, p1, hi[cc][i >> 1], lo[cc][i >> 1]);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            if (ok && j > 0) {  // the P tiles and the other V buffer are free once P V of tile j - 1 has finished
                 ok = wait(&bar_o, ph_o);
                 ph_o ^= 1;
+                ok = __all_sync(0xffffffffu, ok);
             }
-            load_tile(p.kc, kt, kl, j);
-            load_tile(p.vc, vt, vl, j);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(KB(j));
-        }
-        if (PIPE && j + 1 < nkt) {
-            load_tile(p.kc, KB(j + 1), kl, j + 1);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        bool ok_o = true;
-        if (PIPE && j > 0) {  // P and the other V buffer are free once the previous tile's P V has finished
-            ok_o = wait(&bar_o, ph_o);
-            ph_o ^= 1;
-        }
-        if (PIPE && j + 1 < nkt) {
-            load_tile(p.vc, VB(j + 1), vl, j + 1);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        ok = wait(&bar_s, ph_s) && ok_o;
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (uint32_t c = chalf; c < chalf + 64; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_s + trow + c, v);
-                uint32_t hi[16], lo[16];
+            if (ok) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const uint32_t key = j * 128 + c + i;
-                    const float p0 = key <= qpos ? exp2f((__uint_as_float(v[i]) - m) * LOG2E) : 0.0f;
-                    const float p1 = key + 1 <= qpos ? exp2f((__uint_as_float(v[i + 1]) - m) * LOG2E) : 0.0f;
-                    const __half2 hh = __floats2half2_rn(p0, p1);
-                    const float2 hf = __half22float2(hh);
-                    const __half2 ll = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
-                    hi[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                    lo[i >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
-                }
+                for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
-                    const uint32_t off = tile_chunk(row, c + 8 * g);
-                    *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
-                    *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+                    for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                        const uint32_t off = tile_chunk(row, chalf + 32 * cc + 8 * g);
+                        *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[cc][4 * g], hi[cc][4 * g + 1], hi[cc][4 * g + 2], hi[cc][4 * g + 3]);
+                        *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[cc][4 * g], lo[cc][4 * g + 1], lo[cc][4 * g + 2], lo[cc][4 * g + 3]);
+                    }
                 }
+                if (j + 1 < nkt) {
+                    load_tile(p.vc, VB(j + 1), vl, j + 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
+                    const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
+                    umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
+                }
+                umma_commit(&bar_o);
+            }
+        }
+    } else {
+        if (PIPE && ok) {
+            load_tile(p.kc, KB(0), kl, 0);
+            load_tile(p.vc, VB(0), vl, 0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        for (uint32_t j = 0; j < nkt && ok; ++j) {
+            if (!PIPE) {
+                if (j > 0) {  // the previous tile's P V must have finished reading V and P
+                    ok = wait(&bar_o, ph_o);
+                    ph_o ^= 1;
+                }
+                load_tile(p.kc, kt, kl, j);
+                load_tile(p.vc, vt, vl, j);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        }
-        ph_s ^= 1;
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
-                const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
-                umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
-                if (SPLIT) umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vl) + boff), idesc_o, 1u);  // lo x lo is below 2^-22
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(j));
             }
-            umma_commit(&bar_o);
+            if (PIPE && j + 1 < nkt) {
+                load_tile(p.kc, KB(j + 1), kl, j + 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            bool ok_o = true;
+            if (PIPE && j > 0) {  // P and the other V buffer are free once the previous tile's P V has finished
+                ok_o = wait(&bar_o, ph_o);
+                ph_o ^= 1;
+            }
+            if (PIPE && j + 1 < nkt) {
+                load_tile(p.vc, VB(j + 1), vl, j + 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            ok = wait(&bar_s, ph_s) && ok_o;
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    #pragma unroll 1
+                for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_s + trow + c, v);
+                    uint32_t hi[16], lo[16];
+    #pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const uint32_t key = j * 128 + c + i;
+                        const float p0 = key <= qpos ? exp2f((__uint_as_float(v[i]) - m) * LOG2E) : 0.0f;
+                        const float p1 = key + 1 <= qpos ? exp2f((__uint_as_float(v[i + 1]) - m) * LOG2E) : 0.0f;
+                        l += p0 + p1;
+                        split_pair(p0, p1, hi[i >> 1], lo[i >> 1]);
+                    }
+    #pragma unroll
+                    for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                        const uint32_t off = tile_chunk(row, c + 8 * g);
+                        *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+                        *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            ph_s ^= 1;
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    #pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
+                    const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
+                    umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
+                    if (SPLIT) umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vl) + boff), idesc_o, 1u);  // lo x lo is below 2^-22
+                }
+                umma_commit(&bar_o);
+            }
         }
     }
     // ---- output: O / l, rounded to f16 ----
     if (ok) {
         ok = wait(&bar_o, ph_o);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = 1.0f / l;
+    }
+    ok = __syncthreads_and(ok);  // the last P V has finished: the P tiles are free
+    if (ok) {
+        float *stat = reinterpret_cast<float *>(ph);  // [2][128] row sums of the two column halves
+        stat[(warp >> 2) * 128 + row] = l;
+        __syncthreads();
+        l = stat[row] + stat[128 + row];
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = 1.0f / l;
 #pragma unroll 1
-            for (uint32_t c = chalf; c < chalf + 64; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + trow + c, v);
-                if (row < nq) {
-                    uint32_t packed[16];
+        for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + trow + c, v);
+            if (row < nq) {
+                uint32_t packed[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const __half2 hh = __floats2half2_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-                        packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                    }
-                    uint4 *dst = reinterpret_cast<uint4 *>(p.o + ((size_t)(q0 + row) * p.hq + h) * 128 + c);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) dst[g] = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+                for (int i = 0; i < 32; i += 2) {
+                    const __half2 hh = __floats2half2_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
                 }
+                uint4 *dst = reinterpret_cast<uint4 *>(p.o + ((size_t)(q0 + row) * p.hq + h) * 128 + c);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) dst[g] = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
             }
         }
     }
@@ -371,7 +521,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t ncols = 256;
+        uint32_t ncols = 512;
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(ncols) : "memory");
     }
 }

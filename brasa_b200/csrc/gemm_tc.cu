@@ -17,6 +17,10 @@
 // leaves its loop, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
 #include <cmath>
 
 #include "brasa_internal.h"
@@ -63,17 +67,33 @@ struct GemmTcParams {
     uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
     uint32_t cols, tokens, stages;
     uint32_t *status;
+    uint32_t ksplit;      // grid.z CTAs share one output tile, each over its own range of K stages
+    float *part;          // ksplit > 1: [z][tile][MT x 128 tokens][BNT rows] partial tiles
+    uint32_t *counters;   // ksplit > 1: arrivals per output tile (zero between launches)
 };
 
-template <int MT, int G, int NB>
-__global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmTcParams p) {
+// One tensor map per weight matrix: the tiled matrix as bytes [rows][row_bytes], box = 32 bytes x the CTA's rows. The
+// same box fetches a stage's codes (two blocks of 16 bytes per row) and, from the scale area behind the codes, the
+// 16 scales of 8 consecutive stages.
+struct WeightMaps {
+    CUtensorMap m[3];
+};
+constexpr uint32_t RAW_TILE = BN * 32;  // codes of one stage for 128 rows; as many bytes again for the scales
+
+// RAW: the stage's weight bytes come through TMA into shared memory and the conversion reads them there (few tokens:
+// weight traffic decides, and per-thread 16-byte loads from 128 different rows keep too few bytes in flight); otherwise
+// every conversion thread loads its codes straight from global memory one stage of its group ahead (many tokens: the
+// ring is only two stages deep and a weight tile that waits for a free slot before it even leaves L2 would stall it).
+template <int MT, int G, int NB, bool RAW>
+__global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ WeightMaps wmaps,
+                                                         GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // the dynamic shared memory base is only 16-byte aligned by contract: round up to the swizzle atom
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t BNT = BN * NB;  // weight rows of this CTA: one MMA covers them all (N = 128 or 256)
-    const uint32_t stage_bytes = MT * A_TILE + NB * B_TILE;
+    const uint32_t stage_bytes = MT * A_TILE + NB * B_TILE + (RAW ? NB * 2 * RAW_TILE : 0);  // X tiles, converted W, raw codes, raw scales
     __shared__ uint64_t full_x[8], full_w[8], empty[8], acc_full;
-    __shared__ uint32_t tmem_base_s, abort_s;
+    __shared__ uint32_t tmem_base_s, abort_s, last_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // which matrix and which BNT rows of it
@@ -82,7 +102,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
     const uint8_t *wmat = mi == 0 ? p.w[0] : (mi == 1 ? p.w[1] : p.w[2]);
     float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
     const uint32_t yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
-    const uint32_t nk = p.cols / BK, NS = p.stages;
+    const uint32_t NS = p.stages;
+    // this CTA's K stages: [kbeg, kbeg + nk) of the cols / BK stages of the product
+    const uint32_t nk_all = p.cols / BK, kbeg = (uint32_t)((uint64_t)blockIdx.z * nk_all / p.ksplit),
+                   nk = (uint32_t)((uint64_t)(blockIdx.z + 1) * nk_all / p.ksplit) - kbeg;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < NS; ++s) {
@@ -123,12 +146,25 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                 const uint32_t s = k % NS;
                 if (k >= NS && !wait(&empty[s], ((k / NS) - 1) & 1)) break;
                 uint8_t *dst = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_x[s], MT * A_TILE);
+                mbar_expect_tx(&full_x[s], MT * A_TILE + (RAW ? NB * 2 * RAW_TILE : 0));
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                                      smem_u32(dst + mt * A_TILE)),
-                                 "l"(&tmap_x), "r"((int)(k * BK)), "r"((int)(tok0 + mt * BM)), "r"(smem_u32(&full_x[s]))
+                                 "l"(&tmap_x), "r"((int)((kbeg + k) * BK)), "r"((int)(tok0 + mt * BM)), "r"(smem_u32(&full_x[s]))
+                                 : "memory");
+                }
+                if (RAW) {  // raw weights of the stage: codes at byte 32 k of every row, scales 16 at a time from the area behind the codes
+                    uint8_t *raw = dst + MT * A_TILE + NB * B_TILE;
+                    const CUtensorMap *wm = &wmaps.m[mi];
+                    const uint32_t kk = kbeg + k, sc_x = tiled_scale_off(BRASA_Q4_0, p.cols) + 32 * (kk >> 3);
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     smem_u32(raw)),
+                                 "l"(wm), "r"((int)(kk * 32)), "r"((int)n0), "r"(smem_u32(&full_x[s]))
+                                 : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     smem_u32(raw + NB * RAW_TILE)),
+                                 "l"(wm), "r"((int)sc_x), "r"((int)n0), "r"(smem_u32(&full_x[s]))
                                  : "memory");
                 }
                 issued = k + 1;
@@ -174,21 +210,22 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         // units of its stage, a unit being one quantisation block (32 columns) of one weight row. ----
         constexpr uint32_t GT = 256 / G;  // threads of a group
         const uint32_t dt = tid - 128, grp = dt / GT, gt = dt % GT;
-        const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
         constexpr int UN = G * NB;  // units of a thread per stage
+        const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
+        uint32_t soff[UN], roff[UN];
         const uint8_t *wp[UN];
         const uint8_t *sp[UN];
-        uint32_t soff[UN];
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = gt + i * GT, wr = u & (BNT - 1), blk = u / BNT;
-            wp[i] = wmat + (size_t)(n0 + wr) * row_bytes + blk * 16;
-            sp[i] = wmat + (size_t)(n0 + wr) * row_bytes + sc_off + blk * 2;
             soff[i] = (wr >> 3) * 1024 + (wr & 7) * 128 + (blk << 16) + ((wr & 7) << 20);  // row offset | block | row & 7
+            roff[i] = wr * 32 + blk * 16;                                                   // the unit's codes in the raw tile
+            wp[i] = wmat + (size_t)(n0 + wr) * row_bytes + blk * 16 + (size_t)kbeg * 32;
+            sp[i] = wmat + (size_t)(n0 + wr) * row_bytes + sc_off + blk * 2 + (size_t)kbeg * 4;
         }
         uint4 cwq[UN];
         unsigned short scq[UN];
-        {
+        if (!RAW) {
             const uint32_t kj = min(grp, nk - 1);
 #pragma unroll
             for (int i = 0; i < UN; ++i) {
@@ -201,16 +238,28 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             const uint32_t s = k % NS;
             uint4 cw[UN];
             unsigned short sc[UN];
-            const uint32_t kn = min(k + G, nk - 1);  // this group's next stage: in flight during this one
+            if (RAW) {
+                ok = wait(&full_x[s], (k / NS) & 1);  // the stage's raw weights have landed (its slot was free before they were sent)
+                if (!ok) break;
+                const uint8_t *raw = smem + (size_t)s * stage_bytes + MT * A_TILE + NB * B_TILE;
+                const uint8_t *rsc = raw + NB * RAW_TILE + ((kbeg + k) & 7) * 4;
 #pragma unroll
-            for (int i = 0; i < UN; ++i) {
-                cw[i] = cwq[i];
-                sc[i] = scq[i];
-                cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kn * 32);
-                scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kn * 4);
+                for (int i = 0; i < UN; ++i) {
+                    cw[i] = *reinterpret_cast<const uint4 *>(raw + roff[i]);
+                    sc[i] = *reinterpret_cast<const unsigned short *>(rsc + (roff[i] & ~31u) + ((roff[i] & 16u) >> 3));  // row * 32 + block * 2
+                }
+            } else {
+                const uint32_t kn = min(k + G, nk - 1);  // this group's next stage: in flight during this one
+#pragma unroll
+                for (int i = 0; i < UN; ++i) {
+                    cw[i] = cwq[i];
+                    sc[i] = scq[i];
+                    cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kn * 32);
+                    scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kn * 4);
+                }
+                if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
+                if (!ok) break;
             }
-            if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
-            if (!ok) break;
             uint8_t *btile = smem + (size_t)s * stage_bytes + MT * A_TILE;
 #pragma unroll
             for (int i = 0; i < UN; ++i) {
@@ -244,6 +293,9 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         // ---- epilogue: lane = token inside a 128-token tile, columns = weight rows ----
         ok = ok && wait(&acc_full, 0);
         ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+        // with split K the tile goes to this CTA's partial buffer and the last CTA of the tile to arrive adds them up
+        const uint32_t tile_elems = MT * BM * BNT, tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        float *ptile = p.ksplit > 1 ? p.part + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile_id) * tile_elems : nullptr;
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3;           // the lane quarter of tensor memory this warp may read
@@ -263,13 +315,52 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                         : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (token < p.tokens) {
-                        float4 *dst = reinterpret_cast<float4 *>(ymat + (size_t)token * yrows + n0 + c);
+                        float4 *dst = ptile ? reinterpret_cast<float4 *>(ptile + (size_t)(mt * BM + q * 32 + lane) * BNT + c)
+                                            : reinterpret_cast<float4 *>(ymat + (size_t)token * yrows + n0 + c);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
                             dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
                                                  __uint_as_float(v[4 * i + 3]));
                     }
                 }
+            }
+        }
+        if (p.ksplit > 1) {
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
+            if (tid == 128) last_s = (*abort_flag == 0 && atomicAdd(&p.counters[tile_id], 1u) == p.ksplit - 1) ? 1u : 0u;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (last_s) {
+                __threadfence();
+                const float *p0 = p.part + (size_t)tile_id * tile_elems;
+                const size_t zstride = (size_t)gridDim.x * gridDim.y * tile_elems;
+                // rows of the tile past the last token were never written: stop there
+                const uint32_t live = min((uint32_t)(MT * BM), p.tokens > tok0 ? p.tokens - tok0 : 0u) * (BNT / 4);
+#pragma unroll 1
+                for (uint32_t i0 = tid - 128; i0 < live; i0 += 4 * 256) {
+                    float4 a[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t i = i0 + u * 256;
+                        a[u] = i < live ? __ldcg(reinterpret_cast<const float4 *>(p0) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    for (uint32_t z = 1; z < p.ksplit; ++z) {  // always in the order of the K ranges, whoever arrives last
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const uint32_t i = i0 + u * 256;
+                            if (i < live) {
+                                const float4 b = __ldcg(reinterpret_cast<const float4 *>(p0 + z * zstride) + i);
+                                a[u].x += b.x; a[u].y += b.y; a[u].z += b.z; a[u].w += b.w;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t i = i0 + u * 256;
+                        if (i < live) *reinterpret_cast<float4 *>(ymat + (size_t)(tok0 + (i * 4) / BNT) * yrows + n0 + (i * 4) % BNT) = a[u];
+                    }
+                }
+                if (tid == 128) p.counters[tile_id] = 0;
             }
         }
     }
@@ -320,19 +411,28 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     // Shape of a CTA: MT token tiles of 128 x NB weight tiles of 128 rows (MT x NB x 128 accumulator columns <= 512).
     // Every CTA reads its token tiles' X once per launch, so X crosses L2 -> SM (weight tiles / NB) times: the
     // estimate is the larger of that traffic at about 4.5 TB/s and waves x stages x cycles per stage of one CTA.
+    // When the output tiles are too few for the SMs (few tokens: a decode step of a batch; narrow matrices), the K
+    // stages of a tile are shared by `ksplit` CTAs (grid z) that each write a partial tile; the last to arrive adds
+    // them in K order. A split keeps at least 8 stages.
     const uint32_t ntile = (tokens + BM - 1) / BM, nkst = ws[0].cols / BK;
-    uint32_t mt = 1, nb = 1;
+    static const bool split_on = [] { const char *e = getenv("BRASA_GEMM_SPLITK"); return !(e && e[0] == '0'); }();
+    uint32_t mt = 1, nb = 1, ksplit = 1;
     double best = 1e30;
     for (uint32_t b = 1; b <= (rows256 ? 2u : 1u); ++b) {
         for (uint32_t c = 1; c * b <= 4 && c <= std::max(1u, ntile); c *= 2) {
-            const double ctas = (double)(tiles128 / b) * ((ntile + c - 1) / c), waves = std::ceil(ctas / ctx->sm_count);
-            const double pipe = waves * nkst * (300.0 * c * b + 400.0);
-            const double xbytes = (double)(tiles128 / b) * ((ntile + c - 1) / c) * c * BM * ws[0].cols * 2.0;
+            const uint32_t ctas = (tiles128 / b) * ((ntile + c - 1) / c);
+            uint32_t ks = 1;
+            if (split_on && c == 1 && b == 1 && ctas * 2 <= (uint32_t)ctx->sm_count && ctas <= GEMM_TC_COUNTERS)
+                ks = std::max(1u, std::min((uint32_t)ctx->sm_count / ctas, nkst / 8));
+            const double waves = std::ceil((double)ctas * ks / ctx->sm_count);
+            const double pipe = waves * ((nkst + ks - 1) / ks) * (300.0 * c * b + 400.0) + (ks > 1 ? 4000.0 : 0.0);
+            const double xbytes = (double)ctas * c * BM * ws[0].cols * 2.0;
             const double cost = std::max(pipe, xbytes * 1.965e9 / 4.5e12);
             if (cost < best * 0.999 || (cost < best * 1.001 && c * b > mt * nb)) {
                 best = cost;
                 mt = c;
                 nb = b;
+                ksplit = ks;
             }
         }
     }
@@ -356,30 +456,65 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
-    const uint32_t stage_bytes = mt * A_TILE + nb * B_TILE;
+    // the weight matrices as byte tensors [rows][row_bytes]: box = 32 bytes x this CTA's rows, no swizzle
+    WeightMaps wmaps;
+    memset(&wmaps, 0, sizeof wmaps);
+    for (uint32_t i = 0; i < 3; ++i) {
+        const brasa_qmatrix &wi = ws[i < count ? i : 0];
+        const uint32_t rb = tiled_row_bytes(BRASA_Q4_0, wi.cols);
+        cuuint64_t wdims[2] = {rb, wi.rows}, wstrides[1] = {rb};
+        cuuint32_t wbox[2] = {32, BN * nb}, westr[2] = {1, 1};
+        BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(arg_ptr(wi.data)) & 15) == 0, "gemm: misaligned weights");
+        CUresult wr = encode_tiled()(&wmaps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, arg_ptr(wi.data), wdims, wstrides, wbox, westr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (wr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the weights (%d)", (int)wr);
+    }
+    const bool raw = mt == 1 && nb == 1;  // weight bytes through TMA when one token tile per CTA leaves the weights as the main traffic
+    const uint32_t stage_bytes = mt * A_TILE + nb * B_TILE + (raw ? nb * 2 * RAW_TILE : 0);
     uint32_t stages = (uint32_t)std::min<size_t>(8, (ctx->smem_optin - 4096) / stage_bytes);
-    stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, w.cols / BK));
+    stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, (w.cols / BK + ksplit - 1) / ksplit));
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     p.cols = w.cols;
     p.tokens = tokens;
     p.stages = stages;
     p.status = ctx->status;
-    dim3 grid(ncta_n, (ntile + mt - 1) / mt);
-#define LAUNCH_TC(MTV, GV, NBV)                                                                                                        \
+    p.ksplit = ksplit;
+    dim3 grid(ncta_n, (ntile + mt - 1) / mt, ksplit);
+    if (ksplit > 1) {
+        const size_t need = (size_t)ksplit * grid.x * grid.y * mt * BM * nb * BN * sizeof(float);
+        if (ctx->gemm_part_bytes < need) {
+            BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K workspace cannot grow while a graph is recorded");
+            BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (ctx->gemm_part) cudaFree(ctx->gemm_part);
+            ctx->gemm_part = nullptr;
+            ctx->gemm_part_bytes = 0;
+            BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_part, need));
+            ctx->gemm_part_bytes = need;
+        }
+        if (!ctx->gemm_counters) {
+            BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K counters cannot be created while a graph is recorded");
+            BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_counters, GEMM_TC_COUNTERS * 4));
+            BRASA_CUDA(ctx, cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4));
+        }
+        p.part = ctx->gemm_part;
+        p.counters = ctx->gemm_counters;
+    }
+#define LAUNCH_TC(MTV, GV, NBV, RAWV)                                                                                                        \
     do {                                                                                                                         \
         static bool done = false;                                                                                                \
         if (!done) {                                                                                                             \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV, NBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV, NBV, RAWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
             done = true;                                                                                                         \
         }                                                                                                                        \
-        gemm_tc_kernel<MTV, GV, NBV><<<grid, 384, smem, ctx->stream>>>(tmap, p);                                                          \
+        gemm_tc_kernel<MTV, GV, NBV, RAWV><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);                                                         \
     } while (0)
     // conversion groups: as many stages in flight as the ring holds, at most four
-    if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1);
-    else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1);
-    else if (nb == 1) LAUNCH_TC(4, 2, 1);
-    else if (mt == 1) LAUNCH_TC(1, 2, 2);
-    else LAUNCH_TC(2, 2, 2);
+    if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1, true);
+    else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1, false);
+    else if (nb == 1) LAUNCH_TC(4, 2, 1, false);
+    else if (mt == 1) LAUNCH_TC(1, 2, 2, false);
+    else LAUNCH_TC(2, 2, 2, false);
 #undef LAUNCH_TC
     return brasa_post_launch(cmd, "gemm_tc");
 }
