@@ -12,6 +12,9 @@
 // operands (row = key / query, 128 dims in two 64-wide blocks), V with the same bytes as an MN-major B operand
 // (N = dim is contiguous), P as a K-major A operand (row = query, K = key).
 // Every wait is bounded; a wait that runs out raises the context's status word and the CTA leaves.
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "attn_device.cuh"
 #include "brasa_internal.h"
 #include "gemv_device.cuh"
@@ -526,13 +529,365 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
     }
 }
 
+
+// ---- f16 caches: K and V tiles by TMA, two S buffers, two K and two V buffers -------------------------------------
+// The kernel above spends most of its instructions on moving tiles with per-thread copies and on a softmax written
+// for clarity. For an f16 cache the tiles are exactly what the tensor core reads, so one thread fetches them with
+// cp.async.bulk.tensor (the cache as a tensor [position][kv head][128], two boxes of 64 dims with the 128-byte swizzle;
+// positions past the end read as zeros) and nobody else touches them. The softmax threads only read S from tensor
+// memory and write P: tiles wholly below the diagonal skip the causal test, exp2 is one instruction on a fused
+// multiply-add, and the row sum is taken from the very probabilities that enter P V.
+// Order on the tensor core: .. P V (j - 1), S (j + 1), P V (j) ..: S of the next tile is computed while this tile's
+// probabilities are formed, P V of this tile while the next tile's are.
+struct FlashF16Maps {
+    CUtensorMap k, v;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool MASK>
+__device__ __forceinline__ void max_chunk(uint32_t taddr, uint32_t key0, uint32_t qpos, float &m) {
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float sv = __uint_as_float(v[i]);
+        if (MASK && key0 + i > qpos) sv = -INFINITY;
+        m = fmaxf(m, sv);
+    }
+}
+
+// 32 scores -> probabilities exp2(s * log2 e - m * log2 e) as packed hi and lo f16 pairs; their sum is added to l
+template <bool MASK>
+__device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32_t qpos, float mneg, float &l, uint32_t hi[16], uint32_t lo[16]) {
+    constexpr float LOG2E = 1.4426950408889634f;
+    uint32_t v[32];
+    tmem_ld32(taddr, v);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), LOG2E, mneg)), p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), LOG2E, mneg));
+        if (MASK) {
+            if (key0 + i > qpos) p0 = 0.0f;
+            if (key0 + i + 1 > qpos) p1 = 0.0f;
+        }
+        l += p0 + p1;
+        split_pair(p0, p1, hi[i >> 1], lo[i >> 1]);
+    }
+}
+
+__global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *qt = smem, *ph = smem + 5 * TILE_BYTES, *pl = smem + 6 * TILE_BYTES;
+    auto KB = [&](uint32_t j) { return smem + (1 + (j & 1)) * TILE_BYTES; };
+    auto VB = [&](uint32_t j) { return smem + (3 + (j & 1)) * TILE_BYTES; };
+    __shared__ uint64_t bar_s[2], bar_k[2], bar_v[2], bar_o;
+    __shared__ uint32_t tmem_base_s, abort_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t qtile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, kh = h / (p.hq / p.hkv);  // longest query tiles first
+    const uint32_t q0 = qtile * 128, nq = min(128u, p.tokens - q0);
+    const uint32_t last_key = p.pos0 + q0 + nq - 1;
+    const uint32_t nkt = last_key / 128 + 1;
+    const uint32_t nfree = (p.pos0 + q0 + 1) / 128;  // tiles [0, nfree) lie wholly at or below every row's own position
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_s[i], 1);
+            mbar_init(&bar_k[i], 1);
+            mbar_init(&bar_v[i], 1);
+        }
+        mbar_init(&bar_o, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory: S in columns [0, 128) and [128, 256), O in [256, 384)
+        uint32_t ncols = 512;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q tile: scale, round to f16, swizzled K-major; rows past the last query are zeros
+    for (uint32_t i = tid; i < 128 * 16; i += 256) {
+        const uint32_t r = i >> 4, c8 = (i & 15) * 8;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (r < nq) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.q + ((size_t)(q0 + r) * p.hq + h) * 128 + c8);
+            const float4 a = src[0], b = src[1];
+            __half2 h0 = __floats2half2_rn(a.x * p.scale, a.y * p.scale), h1 = __floats2half2_rn(a.z * p.scale, a.w * p.scale);
+            __half2 h2 = __floats2half2_rn(b.x * p.scale, b.y * p.scale), h3 = __floats2half2_rn(b.z * p.scale, b.w * p.scale);
+            out = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1), *reinterpret_cast<uint32_t *>(&h2),
+                             *reinterpret_cast<uint32_t *>(&h3));
+        }
+        *reinterpret_cast<uint4 *>(qt + tile_chunk(r, c8)) = out;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256;
+    volatile uint32_t *abort_flag = &abort_s;
+
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {
+        for (uint32_t it = 0; it < FA_WAIT_LIMIT; ++it) {
+            if (fa_mbar_try(bar, parity)) return true;
+            if (*abort_flag) return false;
+        }
+        atomicExch(p.status, 5u);
+        *abort_flag = 1;
+        return false;
+    };
+    // one thread: rows [128 j, 128 j + 128) of this kv head -> a tile (two boxes of 64 dims), completion on `bar`
+    auto fetch = [&](const CUtensorMap *map, uint8_t *dst, uint64_t *bar, uint32_t j) {
+        mbar_expect_tx(bar, TILE_BYTES);
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+            asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                             smem_u32(dst + half * 16384)),
+                         "l"(map), "r"(half * 64), "r"((int)kh), "r"((int)(j * 128)), "r"(smem_u32(bar))
+                         : "memory");
+    };
+    const uint32_t idesc_s = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc_o = idesc_s | (1u << 16);  // V is an MN-major B operand
+    auto issue_s = [&](const uint8_t *kb, uint32_t sbuf) {  // S[sbuf] = Q K^T
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+            umma(tmem_s + 128 * sbuf, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kb) + off), idesc_s, ks > 0);
+        }
+        umma_commit(&bar_s[sbuf]);
+    };
+
+    // softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63)
+    const uint32_t row = (warp & 3) * 32 + lane, chalf = (warp >> 2) * 64;
+    const uint32_t qpos = p.pos0 + q0 + row;
+    const uint32_t trow = ((warp & 3) * 32u) << 16;  // lane field of a tensor-memory address
+    float m = -INFINITY, l = 0.0f;
+    uint32_t phs0 = 0, phs1 = 0, ph_o = 0;           // phases every thread follows
+    uint32_t pk0 = 0, pk1 = 0, pv0 = 0, pv1 = 0;     // phases of the tile barriers (thread 0)
+    uint32_t inflight = 0;                           // thread 0: bit b = a K copy into buffer b, bit 2 + b = a V copy, not yet waited for
+    bool ok = true;
+    auto wait_k = [&](uint32_t j) -> bool {
+        const bool r = wait(&bar_k[j & 1], (j & 1) ? pk1 : pk0);
+        if (j & 1) pk1 ^= 1;
+        else pk0 ^= 1;
+        if (r) inflight &= ~(1u << (j & 1));
+        return r;
+    };
+    auto wait_v = [&](uint32_t j) -> bool {
+        const bool r = wait(&bar_v[j & 1], (j & 1) ? pv1 : pv0);
+        if (j & 1) pv1 ^= 1;
+        else pv0 ^= 1;
+        if (r) inflight &= ~(4u << (j & 1));
+        return r;
+    };
+    auto wait_s = [&](uint32_t j) -> bool {
+        bool r = wait(&bar_s[j & 1], (j & 1) ? phs1 : phs0);
+        if (j & 1) phs1 ^= 1;
+        else phs0 ^= 1;
+        return __all_sync(0xffffffffu, r);
+    };
+
+    // ---- sweep 1: row maxima ----
+    if (tid == 0) {
+        fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
+        if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
+        if (wait_k(0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(KB(0), 0);
+        }
+    }
+    for (uint32_t j = 0; j < nkt; ++j) {
+        ok = __syncthreads_and(ok);  // tile j - 1's scores have been read by everyone: its S buffer may be overwritten
+        if (!ok) break;
+        if (tid == 0 && j + 1 < nkt && wait_k(j + 1)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(KB(j + 1), (j + 1) & 1);
+        }
+        ok = wait_s(j);
+        if (!ok) continue;  // the barrier at the top ends the loop for everyone
+        if (tid == 0 && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);  // S of tile j is complete: its K buffer is free
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+        if (j < nfree) {
+            max_chunk<false>(ts, 0, 0, m);
+            max_chunk<false>(ts + 32, 0, 0, m);
+        } else {
+            max_chunk<true>(ts, j * 128 + chalf, qpos, m);
+            max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    ok = __syncthreads_and(ok);
+    // the two halves of a row agree on its maximum (the P tiles are not in use yet)
+    {
+        float *stat = reinterpret_cast<float *>(ph);
+        stat[(warp >> 2) * 128 + row] = m;
+        __syncthreads();
+        m = fmaxf(stat[row], stat[128 + row]);
+        __syncthreads();
+    }
+    const float mneg = -m * 1.4426950408889634f;
+
+    // ---- sweep 2: P = exp(S - m), O += P V ----
+    if (ok && tid == 0) {
+        fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
+        fetch(&maps.v, VB(0), &bar_v[0], 0), inflight |= 4u;
+        if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
+        if (wait_k(0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(KB(0), 0);
+        }
+    }
+    for (uint32_t j = 0; j < nkt; ++j) {
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0 && j + 1 < nkt && wait_k(j + 1)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(KB(j + 1), (j + 1) & 1);
+        }
+        ok = wait_s(j);
+        uint32_t hi[2][16], lo[2][16];
+        if (ok) {
+            if (tid == 0 && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+            if (j < nfree) {
+                prob_chunk<false>(ts, 0, 0, mneg, l, hi[0], lo[0]);
+                prob_chunk<false>(ts + 32, 0, 0, mneg, l, hi[1], lo[1]);
+            } else {
+                prob_chunk<true>(ts, j * 128 + chalf, qpos, mneg, l, hi[0], lo[0]);
+                prob_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, mneg, l, hi[1], lo[1]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (j > 0) {  // the P tiles and the other V buffer are free once P V of tile j - 1 has finished
+                ok = wait(&bar_o, ph_o);
+                ph_o ^= 1;
+                ok = __all_sync(0xffffffffu, ok);
+            }
+        }
+        if (ok) {
+            if (tid == 0 && j + 1 < nkt) fetch(&maps.v, VB(j + 1), &bar_v[(j + 1) & 1], j + 1), inflight |= 4u << ((j + 1) & 1);
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                    const uint32_t off = tile_chunk(row, chalf + 32 * cc + 8 * g);
+                    *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[cc][4 * g], hi[cc][4 * g + 1], hi[cc][4 * g + 2], hi[cc][4 * g + 3]);
+                    *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[cc][4 * g], lo[cc][4 * g + 1], lo[cc][4 * g + 2], lo[cc][4 * g + 3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
+        if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
+            if (wait_v(j)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t aoff = (ks >> 2) * 16384 + (ks & 3) * 32;  // K-major P: 16 keys = 32 bytes along the row
+                    const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
+                    umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
+                }
+                umma_commit(&bar_o);
+            }
+        }
+    }
+    // ---- output: O / l, rounded to f16 ----
+    if (ok) {
+        ok = wait(&bar_o, ph_o);
+        ok = __all_sync(0xffffffffu, ok);
+    }
+    ok = __syncthreads_and(ok);  // the last P V has finished: the P tiles are free
+    if (ok) {
+        float *stat = reinterpret_cast<float *>(ph);  // [2][128] row sums of the two column halves
+        stat[(warp >> 2) * 128 + row] = l;
+        __syncthreads();
+        l = stat[row] + stat[128 + row];
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = 1.0f / l;
+#pragma unroll 1
+        for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + trow + c, v);
+            if (row < nq) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const __half2 hh = __floats2half2_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                }
+                uint4 *dst = reinterpret_cast<uint4 *>(p.o + ((size_t)(q0 + row) * p.hq + h) * 128 + c);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) dst[g] = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+            }
+        }
+    } else if (tid == 0) {
+        // leaving early: let the tile copies already in flight land before the CTA's shared memory is handed on
+        for (int b = 0; b < 2; ++b) {
+            if (inflight & (1u << b))
+                for (uint32_t it = 0; it < FA_WAIT_LIMIT && !fa_mbar_try(&bar_k[b], b ? pk1 : pk0); ++it) {}
+            if (inflight & (4u << b))
+                for (uint32_t it = 0; it < FA_WAIT_LIMIT && !fa_mbar_try(&bar_v[b], b ? pv1 : pv0); ++it) {}
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t ncols = 512;
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(ncols) : "memory");
+    }
+}
+
 }  // namespace
 
 // F16 prefill precision over a cache of type kv; q, k, v, o as for brasa_k_flash_attention_with (already validated there).
+namespace {
+typedef CUresult (*FlashEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+FlashEncodeFn flash_encode() {
+    static FlashEncodeFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return (FlashEncodeFn)f;
+    }();
+    return fn;
+}
+}  // namespace
+
 int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const uint8_t *kc, const uint8_t *vc, __half *o, brasa_attn_shape sh) {
     brasa_ctx *ctx = cmd->ctx;
     FlashTcParams p{q, kc, vc, o, sh.tokens, sh.hq, sh.hkv, sh.pos0, 1.0f / sqrtf(128.0f), ctx->status};
     dim3 grid((sh.tokens + 127) / 128, sh.hq);
+    static const bool tma_on = [] { const char *e = getenv("BRASA_FLASH_TMA"); return !(e && e[0] == '0'); }();
+    if (kv == BRASA_KV_F16 && tma_on && flash_encode() && ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
+        // the caches as tensors [position][kv head][128] of f16, positions [0, pos0 + tokens); a box is 128 positions x 64 dims
+        FlashF16Maps maps;
+        const cuuint64_t dims[3] = {128, sh.hkv, (cuuint64_t)sh.pos0 + sh.tokens}, strides[2] = {256, (cuuint64_t)sh.hkv * 256};
+        const cuuint32_t box[3] = {64, 1, 128}, estr[3] = {1, 1, 1};
+        CUresult r1 = flash_encode()(&maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<uint8_t *>(kc), dims, strides, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CUresult r2 = flash_encode()(&maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<uint8_t *>(vc), dims, strides, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the KV cache (%d, %d)", (int)r1, (int)r2);
+        const size_t smem = 7 * TILE_BYTES + 1024;
+        static bool done = false;
+        if (!done) {
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done = true;
+        }
+        flash_tc_f16_kernel<<<grid, 256, smem, ctx->stream>>>(maps, p);
+        return brasa_post_launch(cmd, "flash_tc_f16");
+    }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
     do {                                                                                                                   \
         const size_t smem = (TILES) * TILE_BYTES + 1024;                                                                   \
