@@ -579,7 +579,7 @@ __device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32
     }
 }
 
-__global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
+__global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *ph = smem + 5 * TILE_BYTES, *pl = smem + 6 * TILE_BYTES;
@@ -611,7 +611,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // Q tile: scale, round to f16, swizzled K-major; rows past the last query are zeros
-    for (uint32_t i = tid; i < 128 * 16; i += 256) {
+    for (uint32_t i = tid; i < 128 * 16; i += 288) {
         const uint32_t r = i >> 4, c8 = (i & 15) * 8;
         uint4 out = make_uint4(0, 0, 0, 0);
         if (r < nq) {
@@ -661,8 +661,11 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
         umma_commit(&bar_s[sbuf]);
     };
 
-    // softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63)
-    const uint32_t row = (warp & 3) * 32 + lane, chalf = (warp >> 2) * 64;
+    // Warps 0-7 are the softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63).
+    // Warp 8, one lane, fetches tiles and issues the tensor-core work, so that no softmax warp carries that serial
+    // chain; the two sides meet at one block-wide barrier per tile.
+    const bool issuer = tid == 256, softmax = tid < 256;
+    const uint32_t row = (warp & 3) * 32 + lane, chalf = ((warp >> 2) & 1) * 64;
     const uint32_t qpos = p.pos0 + q0 + row;
     const uint32_t trow = ((warp & 3) * 32u) << 16;  // lane field of a tensor-memory address
     float m = -INFINITY, l = 0.0f;
@@ -692,7 +695,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
     };
 
     // ---- sweep 1: row maxima ----
-    if (tid == 0) {
+    if (issuer) {
         fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
         if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
         if (wait_k(0)) {
@@ -701,31 +704,34 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
         }
     }
     for (uint32_t j = 0; j < nkt; ++j) {
-        ok = __syncthreads_and(ok);  // tile j - 1's scores have been read by everyone: its S buffer may be overwritten
-        if (!ok) break;
-        if (tid == 0 && j + 1 < nkt && wait_k(j + 1)) {
+        // S of tile j + 1 goes into the buffer whose last readers (tile j - 1) passed the previous barrier
+        if (issuer && j + 1 < nkt && wait_k(j + 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(j + 1), (j + 1) & 1);
         }
         ok = wait_s(j);
-        if (!ok) continue;  // the barrier at the top ends the loop for everyone
-        if (tid == 0 && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);  // S of tile j is complete: its K buffer is free
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-        if (j < nfree) {
-            max_chunk<false>(ts, 0, 0, m);
-            max_chunk<false>(ts + 32, 0, 0, m);
-        } else {
-            max_chunk<true>(ts, j * 128 + chalf, qpos, m);
-            max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+        if (ok) {
+            if (issuer && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);  // S of tile j is complete: its K buffer is free
+            if (softmax) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+                if (j < nfree) {
+                    max_chunk<false>(ts, 0, 0, m);
+                    max_chunk<false>(ts + 32, 0, 0, m);
+                } else {
+                    max_chunk<true>(ts, j * 128 + chalf, qpos, m);
+                    max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        ok = __syncthreads_and(ok);
+        if (!ok) break;
     }
-    ok = __syncthreads_and(ok);
     // the two halves of a row agree on its maximum (the P tiles are not in use yet)
     {
         float *stat = reinterpret_cast<float *>(ph);
-        stat[(warp >> 2) * 128 + row] = m;
+        if (softmax) stat[(warp >> 2) * 128 + row] = m;
         __syncthreads();
         m = fmaxf(stat[row], stat[128 + row]);
         __syncthreads();
@@ -733,7 +739,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
     const float mneg = -m * 1.4426950408889634f;
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
-    if (ok && tid == 0) {
+    if (ok && issuer) {
         fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
         fetch(&maps.v, VB(0), &bar_v[0], 0), inflight |= 4u;
         if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
@@ -742,27 +748,27 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
             issue_s(KB(0), 0);
         }
     }
-    for (uint32_t j = 0; j < nkt; ++j) {
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
-        if (tid == 0 && j + 1 < nkt && wait_k(j + 1)) {
+    for (uint32_t j = 0; j < nkt && ok; ++j) {
+        if (issuer && j + 1 < nkt && wait_k(j + 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(j + 1), (j + 1) & 1);
         }
         ok = wait_s(j);
         uint32_t hi[2][16], lo[2][16];
         if (ok) {
-            if (tid == 0 && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-            if (j < nfree) {
-                prob_chunk<false>(ts, 0, 0, mneg, l, hi[0], lo[0]);
-                prob_chunk<false>(ts + 32, 0, 0, mneg, l, hi[1], lo[1]);
-            } else {
-                prob_chunk<true>(ts, j * 128 + chalf, qpos, mneg, l, hi[0], lo[0]);
-                prob_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, mneg, l, hi[1], lo[1]);
+            if (issuer && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);
+            if (softmax) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+                if (j < nfree) {
+                    prob_chunk<false>(ts, 0, 0, mneg, l, hi[0], lo[0]);
+                    prob_chunk<false>(ts + 32, 0, 0, mneg, l, hi[1], lo[1]);
+                } else {
+                    prob_chunk<true>(ts, j * 128 + chalf, qpos, mneg, l, hi[0], lo[0]);
+                    prob_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, mneg, l, hi[1], lo[1]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (j > 0) {  // the P tiles and the other V buffer are free once P V of tile j - 1 has finished
                 ok = wait(&bar_o, ph_o);
                 ph_o ^= 1;
@@ -770,21 +776,23 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
             }
         }
         if (ok) {
-            if (tid == 0 && j + 1 < nkt) fetch(&maps.v, VB(j + 1), &bar_v[(j + 1) & 1], j + 1), inflight |= 4u << ((j + 1) & 1);
+            if (issuer && j + 1 < nkt) fetch(&maps.v, VB(j + 1), &bar_v[(j + 1) & 1], j + 1), inflight |= 4u << ((j + 1) & 1);
+            if (softmax) {
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
+                for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
-                    const uint32_t off = tile_chunk(row, chalf + 32 * cc + 8 * g);
-                    *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[cc][4 * g], hi[cc][4 * g + 1], hi[cc][4 * g + 2], hi[cc][4 * g + 3]);
-                    *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[cc][4 * g], lo[cc][4 * g + 1], lo[cc][4 * g + 2], lo[cc][4 * g + 3]);
+                    for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
+                        const uint32_t off = tile_chunk(row, chalf + 32 * cc + 8 * g);
+                        *reinterpret_cast<uint4 *>(ph + off) = make_uint4(hi[cc][4 * g], hi[cc][4 * g + 1], hi[cc][4 * g + 2], hi[cc][4 * g + 3]);
+                        *reinterpret_cast<uint4 *>(pl + off) = make_uint4(lo[cc][4 * g], lo[cc][4 * g + 1], lo[cc][4 * g + 2], lo[cc][4 * g + 3]);
+                    }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
-        ok = __syncthreads_and(ok);
+        ok = __syncthreads_and(ok);  // P of tile j is complete; every read of S of tile j is done
         if (!ok) break;
-        if (tid == 0) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
+        if (issuer) {  // O += P_hi V + P_lo V over the tile's 128 keys, 16 per instruction
             if (wait_v(j)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -806,13 +814,13 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
     ok = __syncthreads_and(ok);  // the last P V has finished: the P tiles are free
     if (ok) {
         float *stat = reinterpret_cast<float *>(ph);  // [2][128] row sums of the two column halves
-        stat[(warp >> 2) * 128 + row] = l;
+        if (softmax) stat[(warp >> 2) * 128 + row] = l;
         __syncthreads();
         l = stat[row] + stat[128 + row];
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = 1.0f / l;
 #pragma unroll 1
-        for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+        for (uint32_t c = chalf; softmax && c < chalf + 64; c += 32) {
             uint32_t v[32];
             tmem_ld32(tmem_o + trow + c, v);
             if (row < nq) {
@@ -827,7 +835,7 @@ __global__ void __launch_bounds__(256, 1) flash_tc_f16_kernel(const __grid_const
                 for (int g = 0; g < 4; ++g) dst[g] = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
             }
         }
-    } else if (tid == 0) {
+    } else if (issuer) {
         // leaving early: let the tile copies already in flight land before the CTA's shared memory is handed on
         for (int b = 0; b < 2; ++b) {
             if (inflight & (1u << b))
@@ -885,7 +893,7 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
             BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             done = true;
         }
-        flash_tc_f16_kernel<<<grid, 256, smem, ctx->stream>>>(maps, p);
+        flash_tc_f16_kernel<<<grid, 288, smem, ctx->stream>>>(maps, p);
         return brasa_post_launch(cmd, "flash_tc_f16");
     }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
