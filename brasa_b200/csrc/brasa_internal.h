@@ -41,6 +41,8 @@ struct brasa_ctx {
     float *sample_scratch = nullptr;  // weights of the device sampler (2 x vocabulary)
     size_t sample_scratch_n = 0;
     void *argmax_scratch = nullptr;  // arrival counter + per-block partial maxima
+    uint8_t *kv_expand = nullptr;    // f16 hi/lo expansion of a q8_0 KV cache for the tensor-core prefill attention (K hi, K lo, V hi, V lo)
+    size_t kv_expand_bytes = 0;
     float *gemm_part = nullptr;      // partial output tiles of the split-K tensor-core GEMM
     size_t gemm_part_bytes = 0;
     uint32_t *gemm_counters = nullptr;  // arrivals per output tile of that GEMM (GEMM_TC_COUNTERS words, zero between launches)

@@ -72,6 +72,7 @@ void brasa_ctx_destroy(brasa_ctx *ctx) {
     cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gemm_part);
+    cudaFree(ctx->kv_expand);
     cudaFree(ctx->gemm_counters);
     cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);
@@ -343,6 +344,7 @@ int32_t brasa_gemv_scratch(brasa_ctx *ctx, size_t partial_floats, size_t counter
         cudaFree(ctx->gemv_counters);
     cudaFree(ctx->argmax_scratch);
     cudaFree(ctx->gemm_part);
+    cudaFree(ctx->kv_expand);
     cudaFree(ctx->gemm_counters);
     cudaFree(ctx->sample_scratch);
     cudaFree(ctx->gemv_trace);

@@ -14,6 +14,7 @@
 // Every wait is bounded; a wait that runs out raises the context's status word and the CTA leaves.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "attn_device.cuh"
 #include "brasa_internal.h"
@@ -540,8 +541,30 @@ __global__ void __launch_bounds__(256, 1) flash_tc_kernel(FlashTcParams p) {
 // Order on the tensor core: .. P V (j - 1), S (j + 1), P V (j) ..: S of the next tile is computed while this tile's
 // probabilities are formed, P V of this tile while the next tile's are.
 struct FlashF16Maps {
-    CUtensorMap k, v;
+    CUtensorMap k, v, klo, vlo;  // klo, vlo: the low f16 terms of a cache that was expanded from q8_0 (SPLITKV)
 };
+
+// A q8_0 cache for this kernel: every value d * q (f16 scale, 8-bit code) is written as two f16 terms hi + lo, which is
+// exact, into f16 arrays shaped like an f16 cache; the kernel then adds the products with the low terms.
+__global__ void __launch_bounds__(256) kv_q8_expand_kernel(const uint8_t *cache, __half *hi, __half *lo, uint64_t rows) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 values
+    if (i >= rows * 16) return;
+    const uint64_t r = i >> 4;
+    const int c8 = (int)(i & 15) * 8;
+    float v[8];
+    tile_load8<BRASA_KV_Q8_0>(cache + r * KvRow<BRASA_KV_Q8_0>::BYTES, c8, v);
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const __half2 hh = __floats2half2_rn(v[e], v[e + 1]);
+        const float2 hf = __half22float2(hh);
+        const __half2 ll = __floats2half2_rn(v[e] - hf.x, v[e + 1] - hf.y);
+        h[e >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+        l[e >> 1] = *reinterpret_cast<const uint32_t *>(&ll);
+    }
+    *reinterpret_cast<uint4 *>(hi + r * 128 + c8) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4 *>(lo + r * 128 + c8) = make_uint4(l[0], l[1], l[2], l[3]);
+}
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -579,12 +602,18 @@ __device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32
     }
 }
 
+// SPLITKV: K and V come as hi + lo tiles (one buffer each instead of two), S = Q K_hi + Q K_lo and
+// O += P_hi V_hi + P_lo V_hi + P_hi V_lo (lo x lo is below 2^-22).
+template <bool SPLITKV>
 __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *ph = smem + 5 * TILE_BYTES, *pl = smem + 6 * TILE_BYTES;
-    auto KB = [&](uint32_t j) { return smem + (1 + (j & 1)) * TILE_BYTES; };
-    auto VB = [&](uint32_t j) { return smem + (3 + (j & 1)) * TILE_BYTES; };
+    // tiles 1-4: K and V, two buffers each; with SPLITKV: K hi, K lo, V hi, V lo, one buffer each
+    auto KI = [&](uint32_t j) { return SPLITKV ? 0u : (j & 1); };  // which K (V) buffer and barrier tile j uses
+    auto KB = [&](uint32_t j) { return smem + (1 + KI(j)) * TILE_BYTES; };
+    auto VB = [&](uint32_t j) { return smem + (3 + KI(j)) * TILE_BYTES; };
+    uint8_t *klo = smem + 2 * TILE_BYTES, *vlo = smem + 4 * TILE_BYTES;
     __shared__ uint64_t bar_s[2], bar_k[2], bar_v[2], bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
 
@@ -640,15 +669,27 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         *abort_flag = 1;
         return false;
     };
+    uint32_t inflight = 0;  // issuing thread: bit b = a K copy into buffer b, bit 2 + b = a V copy, not yet waited for
     // one thread: rows [128 j, 128 j + 128) of this kv head -> a tile (two boxes of 64 dims), completion on `bar`
-    auto fetch = [&](const CUtensorMap *map, uint8_t *dst, uint64_t *bar, uint32_t j) {
-        mbar_expect_tx(bar, TILE_BYTES);
+    auto fetch1 = [&](const CUtensorMap *map, uint8_t *dst, uint64_t *bar, uint32_t j) {
 #pragma unroll
         for (int half = 0; half < 2; ++half)
             asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
                              smem_u32(dst + half * 16384)),
                          "l"(map), "r"(half * 64), "r"((int)kh), "r"((int)(j * 128)), "r"(smem_u32(bar))
                          : "memory");
+    };
+    auto fetch_k = [&](uint32_t j) {
+        mbar_expect_tx(&bar_k[KI(j)], (SPLITKV ? 2 : 1) * TILE_BYTES);
+        fetch1(&maps.k, KB(j), &bar_k[KI(j)], j);
+        if (SPLITKV) fetch1(&maps.klo, klo, &bar_k[KI(j)], j);
+        inflight |= 1u << KI(j);
+    };
+    auto fetch_v = [&](uint32_t j) {
+        mbar_expect_tx(&bar_v[KI(j)], (SPLITKV ? 2 : 1) * TILE_BYTES);
+        fetch1(&maps.v, VB(j), &bar_v[KI(j)], j);
+        if (SPLITKV) fetch1(&maps.vlo, vlo, &bar_v[KI(j)], j);
+        inflight |= 4u << KI(j);
     };
     const uint32_t idesc_s = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     const uint32_t idesc_o = idesc_s | (1u << 16);  // V is an MN-major B operand
@@ -657,6 +698,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
             umma(tmem_s + 128 * sbuf, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(kb) + off), idesc_s, ks > 0);
+            if (SPLITKV) umma(tmem_s + 128 * sbuf, desc_kmajor(smem_u32(qt) + off), desc_kmajor(smem_u32(klo) + off), idesc_s, 1u);
         }
         umma_commit(&bar_s[sbuf]);
     };
@@ -671,20 +713,21 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     float m = -INFINITY, l = 0.0f;
     uint32_t phs0 = 0, phs1 = 0, ph_o = 0;           // phases every thread follows
     uint32_t pk0 = 0, pk1 = 0, pv0 = 0, pv1 = 0;     // phases of the tile barriers (thread 0)
-    uint32_t inflight = 0;                           // thread 0: bit b = a K copy into buffer b, bit 2 + b = a V copy, not yet waited for
     bool ok = true;
     auto wait_k = [&](uint32_t j) -> bool {
-        const bool r = wait(&bar_k[j & 1], (j & 1) ? pk1 : pk0);
-        if (j & 1) pk1 ^= 1;
+        const uint32_t b = KI(j);
+        const bool r = wait(&bar_k[b], b ? pk1 : pk0);
+        if (b) pk1 ^= 1;
         else pk0 ^= 1;
-        if (r) inflight &= ~(1u << (j & 1));
+        if (r) inflight &= ~(1u << b);
         return r;
     };
     auto wait_v = [&](uint32_t j) -> bool {
-        const bool r = wait(&bar_v[j & 1], (j & 1) ? pv1 : pv0);
-        if (j & 1) pv1 ^= 1;
+        const uint32_t b = KI(j);
+        const bool r = wait(&bar_v[b], b ? pv1 : pv0);
+        if (b) pv1 ^= 1;
         else pv0 ^= 1;
-        if (r) inflight &= ~(4u << (j & 1));
+        if (r) inflight &= ~(4u << b);
         return r;
     };
     auto wait_s = [&](uint32_t j) -> bool {
@@ -696,8 +739,8 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
 
     // ---- sweep 1: row maxima ----
     if (issuer) {
-        fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
-        if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
+        fetch_k(0);
+        if (!SPLITKV && nkt > 1) fetch_k(1);
         if (wait_k(0)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(0), 0);
@@ -705,13 +748,22 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     }
     for (uint32_t j = 0; j < nkt; ++j) {
         // S of tile j + 1 goes into the buffer whose last readers (tile j - 1) passed the previous barrier
-        if (issuer && j + 1 < nkt && wait_k(j + 1)) {
+        if (!SPLITKV && issuer && j + 1 < nkt && wait_k(j + 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(j + 1), (j + 1) & 1);
         }
         ok = wait_s(j);
         if (ok) {
-            if (issuer && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);  // S of tile j is complete: its K buffer is free
+            if (issuer) {  // S of tile j is complete: its K buffer is free
+                if (!SPLITKV && j + 2 < nkt) fetch_k(j + 2);
+                if (SPLITKV && j + 1 < nkt) {  // one K buffer: the next tile travels and its S is issued while this tile's rows are scanned
+                    fetch_k(j + 1);
+                    if (wait_k(j + 1)) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_s(KB(j + 1), (j + 1) & 1);
+                    }
+                }
+            }
             if (softmax) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
@@ -740,23 +792,24 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
     if (ok && issuer) {
-        fetch(&maps.k, KB(0), &bar_k[0], 0), inflight |= 1u;
-        fetch(&maps.v, VB(0), &bar_v[0], 0), inflight |= 4u;
-        if (nkt > 1) fetch(&maps.k, KB(1), &bar_k[1], 1), inflight |= 2u;
+        fetch_k(0);
+        fetch_v(0);
+        if (!SPLITKV && nkt > 1) fetch_k(1);
         if (wait_k(0)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(0), 0);
         }
     }
     for (uint32_t j = 0; j < nkt && ok; ++j) {
-        if (issuer && j + 1 < nkt && wait_k(j + 1)) {
+        if (!SPLITKV && issuer && j + 1 < nkt && wait_k(j + 1)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(KB(j + 1), (j + 1) & 1);
         }
         ok = wait_s(j);
         uint32_t hi[2][16], lo[2][16];
         if (ok) {
-            if (issuer && j + 2 < nkt) fetch(&maps.k, KB(j + 2), &bar_k[j & 1], j + 2), inflight |= 1u << (j & 1);
+            if (issuer && !SPLITKV && j + 2 < nkt) fetch_k(j + 2);
+            if (issuer && SPLITKV && j + 1 < nkt) fetch_k(j + 1);
             if (softmax) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
@@ -776,7 +829,16 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
             }
         }
         if (ok) {
-            if (issuer && j + 1 < nkt) fetch(&maps.v, VB(j + 1), &bar_v[(j + 1) & 1], j + 1), inflight |= 4u << ((j + 1) & 1);
+            if (issuer) {
+                if (!SPLITKV && j + 1 < nkt) fetch_v(j + 1);
+                if (SPLITKV) {  // one V buffer, free now that P V of tile j - 1 is done; then S of the next tile
+                    if (j > 0) fetch_v(j);
+                    if (j + 1 < nkt && wait_k(j + 1)) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_s(KB(j + 1), (j + 1) & 1);
+                    }
+                }
+            }
             if (softmax) {
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
@@ -801,6 +863,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                     const uint32_t boff = ks * 2048;                          // MN-major V: 16 keys = two 8-key groups
                     umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                     umma(tmem_o, desc_kmajor(smem_u32(pl) + aoff), desc_mnmajor(smem_u32(VB(j)) + boff), idesc_o, 1u);
+                    if (SPLITKV) umma(tmem_o, desc_kmajor(smem_u32(ph) + aoff), desc_mnmajor(smem_u32(vlo) + boff), idesc_o, 1u);
                 }
                 umma_commit(&bar_o);
             }
@@ -875,25 +938,52 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
     FlashTcParams p{q, kc, vc, o, sh.tokens, sh.hq, sh.hkv, sh.pos0, 1.0f / sqrtf(128.0f), ctx->status};
     dim3 grid((sh.tokens + 127) / 128, sh.hq);
     static const bool tma_on = [] { const char *e = getenv("BRASA_FLASH_TMA"); return !(e && e[0] == '0'); }();
-    if (kv == BRASA_KV_F16 && tma_on && flash_encode() && ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
+    if ((kv == BRASA_KV_F16 || kv == BRASA_KV_Q8_0) && tma_on && flash_encode() &&
+        ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
+        const bool split = kv == BRASA_KV_Q8_0;
+        const uint64_t npos = (uint64_t)sh.pos0 + sh.tokens, rows = npos * sh.hkv;
+        const uint8_t *kh = kc, *vh = vc, *kl = nullptr, *vl = nullptr;
+        if (split) {  // q8_0: the rows seen by this call as f16 hi + lo arrays (exact), rebuilt on every call
+            const size_t one = rows * 256, need = 4 * one;
+            if (ctx->kv_expand_bytes < need) {
+                BRASA_REQUIRE(ctx, !ctx->capturing, "flash attention: the q8_0 expansion buffer cannot grow while a graph is recorded");
+                BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+                if (ctx->kv_expand) cudaFree(ctx->kv_expand);
+                ctx->kv_expand = nullptr;
+                ctx->kv_expand_bytes = 0;
+                const size_t grow = need + need / 4;  // a prompt fed in chunks asks for a little more every call
+                BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->kv_expand, grow));
+                ctx->kv_expand_bytes = grow;
+            }
+            uint8_t *base = ctx->kv_expand;
+            const uint32_t blocks = (uint32_t)((rows * 16 + 255) / 256);
+            kv_q8_expand_kernel<<<blocks, 256, 0, ctx->stream>>>(kc, (__half *)base, (__half *)(base + one), rows);
+            BRASA_TRY(brasa_post_launch(cmd, "kv_q8_expand"));
+            kv_q8_expand_kernel<<<blocks, 256, 0, ctx->stream>>>(vc, (__half *)(base + 2 * one), (__half *)(base + 3 * one), rows);
+            BRASA_TRY(brasa_post_launch(cmd, "kv_q8_expand"));
+            kh = base; kl = base + one; vh = base + 2 * one; vl = base + 3 * one;
+        }
         // the caches as tensors [position][kv head][128] of f16, positions [0, pos0 + tokens); a box is 128 positions x 64 dims
         FlashF16Maps maps;
-        const cuuint64_t dims[3] = {128, sh.hkv, (cuuint64_t)sh.pos0 + sh.tokens}, strides[2] = {256, (cuuint64_t)sh.hkv * 256};
+        memset(&maps, 0, sizeof maps);
+        const cuuint64_t dims[3] = {128, sh.hkv, npos}, strides[2] = {256, (cuuint64_t)sh.hkv * 256};
         const cuuint32_t box[3] = {64, 1, 128}, estr[3] = {1, 1, 1};
-        CUresult r1 = flash_encode()(&maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<uint8_t *>(kc), dims, strides, box, estr,
-                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        CUresult r2 = flash_encode()(&maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<uint8_t *>(vc), dims, strides, box, estr,
-                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the KV cache (%d, %d)", (int)r1, (int)r2);
+        auto enc = [&](CUtensorMap *m, const uint8_t *ptr) {
+            return flash_encode()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<uint8_t *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        };
+        CUresult r1 = enc(&maps.k, kh), r2 = enc(&maps.v, vh), r3 = split ? enc(&maps.klo, kl) : CUDA_SUCCESS, r4 = split ? enc(&maps.vlo, vl) : CUDA_SUCCESS;
+        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS || r3 != CUDA_SUCCESS || r4 != CUDA_SUCCESS)
+            return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the KV cache (%d, %d, %d, %d)", (int)r1, (int)r2, (int)r3, (int)r4);
         const size_t smem = 7 * TILE_BYTES + 1024;
         static bool done = false;
         if (!done) {
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             done = true;
         }
-        flash_tc_f16_kernel<<<grid, 288, smem, ctx->stream>>>(maps, p);
+        if (split) flash_tc_f16_kernel<true><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else flash_tc_f16_kernel<false><<<grid, 288, smem, ctx->stream>>>(maps, p);
         return brasa_post_launch(cmd, "flash_tc_f16");
     }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
