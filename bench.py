@@ -11,9 +11,14 @@ tokens with an f16 KV cache, ctx 2048. One step = the 255 decode forwards that f
 `value`   device-resident: the chosen token is fed back on the device, timed with CUDA events.
 `e2e`     through Session.generate with host buffers: prompt upload, prefill, and one token id read
           back per step, timed by the session itself (host clock around the decode loop).
-`roofline` the dominant kernel (the q4_0 GEMV at the gate/up shape) timed alone over the model's own 36
-          layers of weights (1 GB, larger than L2), against the measured HBM copy peak.
+`roofline` the dominant kernel, the one-launch-per-token decode kernel: algorithmic bytes of a token over its
+          event-timed duration, against the measured HBM copy peak (`gemv_roofline`: the q4_0 GEMV of the
+          kernel-per-operation path alone over 36 layers of gate/up weights, 1 GB).
+`prefill_16k` a 16 384-token prompt through chunked prefill, f16 and q8_0 caches, and decode over that cache.
+`serving` 64 sequences per replica (shared 2048-token prefix + 1024 own tokens each, paged f16 KV), 512 sampled
+          tokens per sequence (temperature 0.7, top-p 0.95, one PCG32 stream per sequence).
 `cpu_baseline` the oracle's C port of the reference CPU path, a few decode tokens on the host cores.
+`--only-tp` (on its own, under torch.distributed.run) the Qwen3-32B-architecture tensor-parallel decode.
 
 With --gpus N > 1 (launched by torch.distributed.run) every rank serves its own replica: the path has
 no exchange step at batch 1, so the ranks share nothing and the aggregate is the sum ("replicas only").
@@ -516,6 +521,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e2e = statistics.median(e2e_vals)
     same_tokens = bool(out_ids is not None and list(gen[1:]) == list(out_ids))
     e2e = rep.sum(e2e)
+
+    # ---- batched serving: every replica decodes its own 64 sequences (shared 2048-token prefix, paged f16 KV) ----
+    try:
+        serving = serving_leg(B, ctx, path, cfg, rank)
+        serving["aggregate_tok_s"] = rep.sum(serving["decode_tok_s"])
+        serving["replicas"] = world
+    except B.BrasaError as e:
+        serving = {"error": str(e)}
+        rep.sum(0.0)
     if rank != 0:
         return
 
@@ -595,6 +609,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "roofline": roof,
             "gemv_roofline": gemv_roof,
             "prefill_16k": long_prefill,
+            "serving": serving,
             "token_roofline": {"bytes_per_token": bytes_per_token, "achieved_gbs": per_gpu_tok_s * bytes_per_token / 1e9, "peak": peak,
                                "frac_of_measured": token_frac, "frac_of_8tbs": per_gpu_tok_s * bytes_per_token / 8e12,
                                "roofline_tok_s_at_8tbs": 8e12 / bytes_per_token},
