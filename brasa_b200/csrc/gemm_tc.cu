@@ -17,6 +17,7 @@
 // leaves its loop, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -434,6 +435,15 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
                 nb = b;
                 ksplit = ks;
             }
+        }
+    }
+    {   // BRASA_GEMM_SHAPE=mt,nb forces the CTA shape (A/B runs); ignored when the matrices do not allow it
+        static const char *force = getenv("BRASA_GEMM_SHAPE");
+        unsigned fm = 0, fn = 0;
+        if (force && sscanf(force, "%u,%u", &fm, &fn) == 2 && (fm == 1 || fm == 2 || fm == 4) && (fn == 1 || (fn == 2 && rows256)) && fm * fn <= 4) {
+            mt = fm;
+            nb = fn;
+            ksplit = 1;
         }
     }
     uint32_t ncta_n = 0;
