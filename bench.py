@@ -438,6 +438,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             print(json.dumps({"roofline": kernel_roofline(B, ctx, B.Kernels(ctx), cfg, peak, peak_kind, profile=True),
                               "note": "dominant kernel alone (profiling run)"}))
         return
+    if args.only_attention:
+        # the prefill attention kernel alone at long context: 512 queries of 32 heads at positions 15 872.. over a
+        # 16 384-position f16 cache of 8 KV heads (67 MB; inputs seeded normal), small enough for profiler captures
+        if rank == 0:
+            K = B.Kernels(ctx)
+            g = np.random.default_rng(SEED + 9)
+            hq, hkv, dim, tokens, pos0 = 32, 8, 128, 512, 15872
+            kc = ctx.buffer_from(g.standard_normal((pos0 + tokens) * hkv * dim).astype(np.float16))
+            vc = ctx.buffer_from(g.standard_normal((pos0 + tokens) * hkv * dim).astype(np.float16))
+            q = ctx.buffer_from(g.standard_normal(tokens * hq * dim).astype(np.float32))
+            o = ctx.buffer(tokens * hq * dim * 2)
+            shape = B.AttnShape(tokens, hq, hkv, dim, pos0, B.KvType.F16)
+            for _ in range(3):
+                cmd = ctx.command()
+                K.flash_attention(cmd, q, kc, vc, o, shape)
+                cmd.wait()
+            profiler_range(True)
+            cmd = ctx.command()
+            K.flash_attention(cmd, q, kc, vc, o, shape)
+            secs = cmd.wait()
+            profiler_range(False)
+            flops = 4.0 * hq * dim * sum(pos0 + t + 1 for t in range(tokens))
+            print(json.dumps({"metric": "prefill_attention_tflops", "value": flops / secs / 1e12, "unit": "TFLOP/s", "us": secs * 1e6,
+                              "config": {"queries": tokens, "first_position": pos0, "heads": hq, "kv_heads": hkv, "kv": "f16"},
+                              "note": "prefill attention kernel alone (profiling run)"}))
+        return
     if args.only_tp:
         res = tp_leg(B, ctx, rep, steps=args.steps)
         if rank == 0:
@@ -629,6 +655,7 @@ def main():
                     help="run only one prefill forward of the workload's prompt (profiler captures)")
     ap.add_argument("--only-kernel", action="store_true",
                     help="run only the dominant kernel's own timing leg (profiler captures)")
+    ap.add_argument("--only-attention", action="store_true", help="run only the prefill attention kernel at 16k context (profiling)")
     ap.add_argument("--only-tp", action="store_true", help="run only the tensor-parallel Qwen3-32B decode over the job's ranks")
     ap.add_argument("--only-serving", action="store_true", help="run only the batched serving leg (profiling)")
     ap.add_argument("--serving-seqs", type=int, default=64)
