@@ -122,12 +122,6 @@ __device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, boo
     const uint32_t bytes = valid ? 16u : 0u;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mma_f16(float c[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    // rows 8..15 of A (registers a1, a3) are zero: the group has at most 8 heads
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t r[4], const void *p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
@@ -148,16 +142,31 @@ __device__ __forceinline__ void split_h2(float x, float y, uint32_t &hi, uint32_
 __device__ __forceinline__ uint32_t piece(uint32_t r, uint32_t c) { return r * 256u + ((c ^ (r & 7u)) << 4); }
 
 constexpr uint32_t MMA_TILE = 128 * 256;  // one K or V tile
-constexpr size_t MMA_SMEM = 2 * MMA_TILE + (2 * 4 * 8 + 16) * sizeof(float);  // three blocks per SM
+constexpr size_t MMA_SMEM = 2 * MMA_TILE + (2 * 4 * 16 + 16) * sizeof(float);  // three blocks per SM
 
+__device__ __forceinline__ void mma_f16_full(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MULTI = false: the 16 MMA rows hold the G heads of ONE sequence's group (rows >= G are zero); grid z = sequence, chunk =
+// first_chunk + grid x. MULTI = true: chunks that lie wholly inside the prefix every sequence shares: the rows hold the
+// groups of 16 / G consecutive sequences (row = local sequence * G + head in group), so the shared K and V tiles are
+// fetched and multiplied once per 16 / G sequences; grid z = sequence group; the pages are those of the group's first
+// sequence (the prefix pages are the same for all).
+template <bool MULTI>
 __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const float *q, Paged kp, Paged vp, const uint32_t *lens, float *partials,
-                                                                       uint32_t hq, uint32_t max_chunks, float scale) {
+                                                                       uint32_t hq, uint32_t max_chunks, float scale, uint32_t first_chunk, uint32_t nseq) {
+    constexpr int RH = MULTI ? 2 : 1;  // row halves in use: rows g (and g + 8)
     extern __shared__ __align__(128) uint8_t smem_b[];
     uint8_t *kt = smem_b, *vt = smem_b + MMA_TILE;
-    float *osum = reinterpret_cast<float *>(kt);  // [4 warps][8 heads][128], over the K tile once every warp is done with it
-    float *wmax = reinterpret_cast<float *>(smem_b + 2 * MMA_TILE), *wsum = wmax + 4 * 8;  // [4 warps][8 heads] each
-    const uint32_t chunk = blockIdx.x, kh = blockIdx.y, seq = blockIdx.z, hkv = kp.hkv, G = hq / hkv;
-    const uint32_t lk = lens[seq] + 1;
+    float *osum = reinterpret_cast<float *>(kt);  // [4 warps][16 rows][128], over the K tile once every warp is done with it
+    float *wmax = reinterpret_cast<float *>(smem_b + 2 * MMA_TILE), *wsum = wmax + 4 * 16;  // [4 warps][16 rows] each
+    const uint32_t chunk = first_chunk + blockIdx.x, kh = blockIdx.y, hkv = kp.hkv, G = hq / hkv;
+    const uint32_t spb = MULTI ? 16 / G : 1, seq0 = blockIdx.z * spb;
+    const uint32_t nrows = min(spb, nseq - seq0) * G;  // rows of the MMA that carry a (sequence, head)
+    const uint32_t lk = MULTI ? (chunk + 1) * 128 : lens[seq0] + 1;
     if (chunk * 128 >= lk) return;
     const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
     const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
@@ -165,33 +174,36 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
     for (uint32_t i = t; i < 128 * 16; i += 128) {
         const uint32_t r = i >> 4, c = i & 15;
         const bool ok = r < nkeys;
-        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq0, key0 + (ok ? r : 0), kh) + 16 * c, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     for (uint32_t i = t; i < 128 * 16; i += 128) {
         const uint32_t r = i >> 4, c = i & 15;
         const bool ok = r < nkeys;
-        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq0, key0 + (ok ? r : 0), kh) + 16 * c, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    // ---- Q fragments of head g (rows >= G are zero): for k-step ks, a0 = dims 16 ks + 2 tq, +1; a2 = those + 8 ----
-    uint32_t qh0[8], qh2[8], ql0[8], ql2[8];
-    {
-        const float *qrow = q + ((size_t)seq * hq + kh * G + (g < G ? g : 0)) * D;
+    // ---- Q fragments of rows g and g + 8: for k-step ks, a0/a1 = dims 16 ks + 2 tq, +1; a2/a3 = those + 8 ----
+    uint32_t qh0[RH][8], qh2[RH][8], ql0[RH][8], ql2[RH][8];
+#pragma unroll
+    for (int rh = 0; rh < RH; ++rh) {
+        const uint32_t r = g + 8 * rh;
+        const bool live = r < nrows;
+        const float *qrow = q + ((size_t)(seq0 + (live ? r / G : 0)) * hq + kh * G + (live ? r % G : 0)) * D;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             float2 a = make_float2(0.0f, 0.0f), b = a;
-            if (g < G) {
+            if (live) {
                 a = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq);
                 b = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq + 8);
             }
-            split_h2(a.x, a.y, qh0[ks], ql0[ks]);
-            split_h2(b.x, b.y, qh2[ks], ql2[ks]);
+            split_h2(a.x, a.y, qh0[rh][ks], ql0[rh][ks]);
+            split_h2(b.x, b.y, qh2[rh][ks], ql2[rh][ks]);
         }
     }
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    // ---- S[head g][keys 32 warp + 8 j + 2 tq, +1], j = 0..3 ----
+    // ---- S[row g (c0, c1) and g + 8 (c2, c3)][keys 32 warp + 8 j + 2 tq, +1], j = 0..3 ----
     float sc[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
@@ -206,44 +218,56 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
             for (int ks = 0; ks < 8; ks += 2) {
                 uint32_t b[4];
                 ldmatrix_x4(b, kt + piece(krow, 2 * ks + ltile));
-                mma_f16(sc[j], qh0[ks], qh2[ks], b[0], b[1]);
-                mma_f16(sc[j], ql0[ks], ql2[ks], b[0], b[1]);
-                mma_f16(sc[j], qh0[ks + 1], qh2[ks + 1], b[2], b[3]);
-                mma_f16(sc[j], ql0[ks + 1], ql2[ks + 1], b[2], b[3]);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t h1 = MULTI ? qh0[RH - 1][ks + u] : 0u, h3 = MULTI ? qh2[RH - 1][ks + u] : 0u;
+                    const uint32_t l1 = MULTI ? ql0[RH - 1][ks + u] : 0u, l3 = MULTI ? ql2[RH - 1][ks + u] : 0u;
+                    mma_f16_full(sc[j], qh0[0][ks + u], h1, qh2[0][ks + u], h3, b[2 * u], b[2 * u + 1]);
+                    mma_f16_full(sc[j], ql0[0][ks + u], l1, ql2[0][ks + u], l3, b[2 * u], b[2 * u + 1]);
+                }
             }
         }
     }
-    // ---- scale, mask, row maximum over the block ----
-    float mx = -INFINITY;
+    // ---- scale, mask, row maxima over the block ----
+    float mx[RH], m[RH], l[RH];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int rh = 0; rh < RH; ++rh) {
+        mx[rh] = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const uint32_t key = 32 * warp + 8 * j + 2 * tq + e;
-            const float v = key < nkeys ? sc[j][e] * scale : -INFINITY;
-            sc[j][e] = v;
-            mx = fmaxf(mx, v);
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t key = 32 * warp + 8 * j + 2 * tq + e;
+                const float v = key < nkeys ? sc[j][2 * rh + e] * scale : -INFINITY;
+                sc[j][2 * rh + e] = v;
+                mx[rh] = fmaxf(mx[rh], v);
+            }
         }
+        mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 1));
+        mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 2));
+        if (tq == 0) wmax[warp * 16 + g + 8 * rh] = mx[rh];
     }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    if (tq == 0) wmax[warp * 8 + g] = mx;
     __syncthreads();
-    const float m = fmaxf(fmaxf(wmax[g], wmax[8 + g]), fmaxf(wmax[16 + g], wmax[24 + g]));
-    float l = 0.0f;
-    uint32_t ph[4], pl[4];  // P of n-tile j as packed pairs: A fragment a0 (j even) or a2 (j odd) of k-step j / 2
+    uint32_t ph[RH][4], pl[RH][4];  // P of n-tile j as packed pairs: A fragment a0/a1 (j even) or a2/a3 (j odd) of k-step j / 2
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float p0 = sc[j][0] == -INFINITY ? 0.0f : expf(sc[j][0] - m), p1 = sc[j][1] == -INFINITY ? 0.0f : expf(sc[j][1] - m);
-        l += p0 + p1;
-        split_h2(p0, p1, ph[j], pl[j]);
+    for (int rh = 0; rh < RH; ++rh) {
+        const uint32_t r = g + 8 * rh;
+        m[rh] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
+        l[rh] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float s0 = sc[j][2 * rh], s1 = sc[j][2 * rh + 1];
+            const float p0 = s0 == -INFINITY ? 0.0f : expf(s0 - m[rh]), p1 = s1 == -INFINITY ? 0.0f : expf(s1 - m[rh]);
+            l[rh] += p0 + p1;
+            split_h2(p0, p1, ph[rh][j], pl[rh][j]);
+        }
+        l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 1);
+        l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 2);
+        if (tq == 0) wsum[warp * 16 + r] = l[rh];
     }
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (tq == 0) wsum[warp * 8 + g] = l;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    // ---- O[head g][dims 8 n + 2 tq, +1] += P[16 x 32 keys] V[32 keys x 128 dims] ----
+    // ---- O[row][dims 8 n + 2 tq, +1] += P[16 x 32 keys] V[32 keys x 128 dims] ----
     float oc[16][4];
 #pragma unroll
     for (int n = 0; n < 16; ++n) oc[n][0] = oc[n][1] = oc[n][2] = oc[n][3] = 0.0f;
@@ -254,28 +278,36 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
             const uint32_t vrow = 32 * warp + 16 * kk + 8 * (ltile & 1) + lrow;
+            const uint32_t h1 = MULTI ? ph[RH - 1][2 * kk] : 0u, h3 = MULTI ? ph[RH - 1][2 * kk + 1] : 0u;
+            const uint32_t l1 = MULTI ? pl[RH - 1][2 * kk] : 0u, l3 = MULTI ? pl[RH - 1][2 * kk + 1] : 0u;
 #pragma unroll
             for (int n = 0; n < 16; n += 2) {
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, vt + piece(vrow, n + (ltile >> 1)));
-                mma_f16(oc[n], ph[2 * kk], ph[2 * kk + 1], b[0], b[1]);
-                mma_f16(oc[n], pl[2 * kk], pl[2 * kk + 1], b[0], b[1]);
-                mma_f16(oc[n + 1], ph[2 * kk], ph[2 * kk + 1], b[2], b[3]);
-                mma_f16(oc[n + 1], pl[2 * kk], pl[2 * kk + 1], b[2], b[3]);
+                mma_f16_full(oc[n], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[0], b[1]);
+                mma_f16_full(oc[n], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[0], b[1]);
+                mma_f16_full(oc[n + 1], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[2], b[3]);
+                mma_f16_full(oc[n + 1], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[2], b[3]);
             }
         }
     }
-    if (g < G) {
 #pragma unroll
-        for (int n = 0; n < 16; ++n) *reinterpret_cast<float2 *>(osum + (warp * 8 + g) * D + 8 * n + 2 * tq) = make_float2(oc[n][0], oc[n][1]);
+    for (int rh = 0; rh < RH; ++rh) {
+        const uint32_t r = g + 8 * rh;
+        if (r < nrows) {
+#pragma unroll
+            for (int n = 0; n < 16; ++n)
+                *reinterpret_cast<float2 *>(osum + (warp * 16 + r) * D + 8 * n + 2 * tq) = make_float2(oc[n][2 * rh], oc[n][2 * rh + 1]);
+        }
     }
     __syncthreads();
-    for (uint32_t h = 0; h < G; ++h) {
-        float *out = partials + (((size_t)seq * hq + kh * G + h) * max_chunks + chunk) * 130;
-        out[2 + t] = (osum[(0 * 8 + h) * D + t] + osum[(1 * 8 + h) * D + t]) + (osum[(2 * 8 + h) * D + t] + osum[(3 * 8 + h) * D + t]);
+    for (uint32_t r = 0; r < nrows; ++r) {
+        const uint32_t seq = seq0 + r / G, h = kh * G + r % G;
+        float *out = partials + (((size_t)seq * hq + h) * max_chunks + chunk) * 130;
+        out[2 + t] = (osum[(0 * 16 + r) * D + t] + osum[(1 * 16 + r) * D + t]) + (osum[(2 * 16 + r) * D + t] + osum[(3 * 16 + r) * D + t]);
         if (t == 0) {
-            out[0] = fmaxf(fmaxf(wmax[h], wmax[8 + h]), fmaxf(wmax[16 + h], wmax[24 + h]));
-            out[1] = (wsum[h] + wsum[8 + h]) + (wsum[16 + h] + wsum[24 + h]);
+            out[0] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
+            out[1] = (wsum[r] + wsum[16 + r]) + (wsum[32 + r] + wsum[48 + r]);
         }
     }
 }
@@ -462,16 +494,28 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         else if (m->limits.kv == BRASA_KV_F16 && b->mma_attention) {
             static bool attr_done = false;
             if (!attr_done) {
-                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
+                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
+                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
                 attr_done = true;
             }
             qk_norm_rope_store_paged_kernel<BRASA_KV_F16><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(
                 F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages, lens, c.heads,
                 c.kv_heads, c.eps, rows);
             BRASA_TRY(brasa_post_launch(cmd, "qk_norm_rope_store_paged"));
-            decode_partial_paged_mma_kernel<<<agrid, 128, MMA_SMEM, ctx->stream>>>(F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks,
-                                                                                scale);
-            BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma"));
+            // chunks wholly inside the shared prefix: one block serves 16 / G sequences; the rest per sequence
+            const uint32_t G = c.heads / c.kv_heads;
+            const uint32_t shared_chunks = (n > 1 && 16 % G == 0 && G < 16) ? b->prefix_len / 128 : 0;
+            if (shared_chunks) {
+                const uint32_t spb = 16 / G;
+                decode_partial_paged_mma_kernel<true><<<dim3(shared_chunks, c.kv_heads, (n + spb - 1) / spb), 128, MMA_SMEM, ctx->stream>>>(
+                    F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, 0, n);
+                BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma_shared"));
+            }
+            if ((uint32_t)b->max_chunks > shared_chunks) {
+                decode_partial_paged_mma_kernel<false><<<dim3((uint32_t)b->max_chunks - shared_chunks, c.kv_heads, n), 128, MMA_SMEM, ctx->stream>>>(
+                    F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, shared_chunks, n);
+                BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma"));
+            }
         } else if (m->limits.kv == BRASA_KV_F16) LAUNCH_BATCH(BRASA_KV_F16);
         else LAUNCH_BATCH(BRASA_KV_Q8_0);
 #undef LAUNCH_BATCH
