@@ -369,7 +369,27 @@ def tp_leg(B, ctx, rep, steps: int = 3, prompt: int = 1024, generate: int = 256)
         kvb = synth.kv_bytes_per_position(cfg, "f16")
         per_token = shard_bytes + kvb * (prompt + 1 + (generate - 1) / 2.0)
         t_tok = total / (steps * generate)
-        return {"model": "Qwen3-32B architecture, q4_0, random init", "tp": world, "prompt_tokens": prompt, "generated": generate,
+        # batch 16: sixteen sequences with their own 1024-token prompts decoded together over paged KV, greedy
+        nb, warm = 16, 4
+        page = B.Batch.PAGE
+        per_seq = (prompt + generate + page) // page
+        bt = B.Batch(m, nb, nb * per_seq + 8, per_seq * page)
+        try:
+            for i in range(nb):
+                own = np.random.default_rng(SEED + 64 + i).integers(0, cfg["vocab_size"], size=prompt).astype(np.uint32)
+                rep.barrier()
+                bt.add_sequence(own)
+            rep.barrier()
+            bt.decode(warm)
+            rep.barrier()
+            bids, bsecs = bt.decode(generate - warm - 1)
+            bsecs = rep.max(bsecs)
+            b_agree = rep.max(float(int(bids[:, -1].sum()))) == -rep.max(-float(int(bids[:, -1].sum())))
+            batch16 = {"sequences": nb, "decode_steps": generate - warm - 1, "decode_tok_s": nb * (generate - warm - 1) / bsecs,
+                       "ms_per_step": bsecs / (generate - warm - 1) * 1e3, "ranks_agree_on_tokens": bool(b_agree)}
+        finally:
+            bt.free()
+        return {"batch16": batch16, "model": "Qwen3-32B architecture, q4_0, random init", "tp": world, "prompt_tokens": prompt, "generated": generate,
                 "decode_tok_s": 1.0 / t_tok, "ms_per_token": t_tok * 1e3, "prefill_tok_s": prompt / rep.max(pre_s),
                 "bytes_per_token_per_gpu": per_token, "achieved_gbs_per_gpu": per_token / t_tok / 1e9,
                 "exchanges_per_token": 2 * cfg["num_hidden_layers"] + 1, "ranks_agree_on_tokens": bool(agree),

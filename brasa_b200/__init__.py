@@ -800,6 +800,6 @@ class Batch:
 
     def peek_logits(self) -> np.ndarray:
         n = self.sequences
-        out = np.zeros((n, self.model.cfg["vocab"]), np.float32)
+        out = np.zeros((n, self.model.cfg["head_rows"]), np.float32)
         self.ctx._check(lib().brasa_batch_peek_logits(self._h, out.ctypes.data_as(C.c_void_p)))
         return out

@@ -434,6 +434,27 @@ int32_t prefill_contiguous(brasa_batch *b, const uint32_t *ids, uint32_t n, uint
     return BRASA_OK;
 }
 
+// x += h: the plain add, or for a tensor-parallel shard the sum over ranks of every rank's h
+int32_t batch_residual_add(brasa_model *m, brasa_cmd *cmd, uint64_t n) {
+    if (m->tp) return brasa_k_tp_allreduce_add(cmd, m->tp, A(m->h), A(m->x), A(m->x), n);
+    return brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), n);
+}
+
+// Next token of `count` rows of logits (row stride = this rank's lm_head rows). A tensor-parallel shard holds only its
+// rows of the vocabulary: the choice is greedy, each row's best (value, index) pair exchanged between the ranks.
+int32_t choose_tokens(brasa_batch *b, brasa_cmd *cmd, brasa_buf *logits, uint32_t count, brasa_sampling_params params, unsigned long long *rng,
+                      float *scratch, brasa_buf *out, uint64_t out_index) {
+    brasa_model *m = b->m;
+    const uint32_t rows = m->cfg.head_rows;
+    if (!m->tp)
+        return brasa_sample_batched_launch(cmd, F(logits), rows, count, params.temperature, params.top_k, params.top_p, rng, scratch,
+                                           (uint32_t *)out->ptr + out_index);
+    BRASA_REQUIRE(b->ctx, params.temperature <= 0.0f, "batch: a tensor-parallel shard decodes greedily (temperature 0)");
+    for (uint32_t r = 0; r < count; ++r)
+        BRASA_TRY(brasa_k_tp_argmax(cmd, m->tp, A(logits, (uint64_t)r * rows * 4), rows, m->cfg.head_row0, A(out, (out_index + r) * 4)));
+    return BRASA_OK;
+}
+
 // One decode step for the first n sequences: ids[n] -> logits[n][vocab]. Uses the model's workspace (n <= max_tokens).
 int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
     brasa_model *m = b->m;
@@ -523,7 +544,7 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         else decode_reduce_paged_kernel<false><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
         BRASA_TRY(brasa_post_launch(cmd, "decode_reduce_paged"));
         BRASA_TRY(mm(l.wo, half_io ? A(m->xh) : A(m->attn), A(m->h)));
-        BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)n * H));
+        BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
         brasa_arg act;
         if (half_io) {
             BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
@@ -537,7 +558,7 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
             act = A(m->gate);
         }
         BRASA_TRY(mm(l.down, act, A(m->h)));
-        BRASA_TRY(brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), (uint64_t)n * H));
+        BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
     }
     if (half_io) {
         BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(m->final_norm), A(m->xh), n, H, c.eps));
@@ -564,7 +585,7 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     BRASA_REQUIRE(ctx, m->cfg.head_dim == 128 && m->cfg.heads % m->cfg.kv_heads == 0 && m->cfg.heads / m->cfg.kv_heads <= 8,
                   "batch: head_dim 128 and a GQA group of at most 8");
     BRASA_REQUIRE(ctx, max_positions >= PAGE && max_positions <= m->limits.ctx, "batch: max_positions within the model's context");
-    BRASA_REQUIRE(ctx, !m->tp && m->cfg.head_rows == m->cfg.vocab, "batch: tensor-parallel shards are decoded one sequence at a time");
+    BRASA_REQUIRE(ctx, m->tp || m->cfg.head_rows == m->cfg.vocab, "batch: a tensor-parallel shard needs its exchange attached first (brasa_model_set_tp)");
     std::unique_ptr<brasa_batch, void (*)(brasa_batch *)> b(new brasa_batch, brasa_batch_free);
     b->m = m;
     b->ctx = ctx;
@@ -587,7 +608,7 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 4, &b->ids));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 4, &b->out));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 16, &b->rng));
-    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.vocab * 4, &b->logits));
+    BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.head_rows * 4, &b->logits));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.heads * b->max_chunks * 130 * 4, &b->partials));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 2 * m->cfg.vocab * 4, &b->scratch));
     b->h_table.assign((size_t)max_seqs * b->max_pages, 0);
@@ -643,9 +664,8 @@ int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n
     BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
     int32_t rc = copy_rows_to_pages(b, cmd, seq, b->prefix_len, n);
     if (rc == BRASA_OK)
-        rc = brasa_sample_batched_launch(cmd, F(m->logits), m->cfg.vocab, 1, params.temperature, params.top_k, params.top_p,
-                                         (unsigned long long *)b->rng->ptr + 2 * seq, F(b->scratch) + (size_t)seq * 2 * m->cfg.vocab,
-                                         (uint32_t *)b->ids->ptr + seq);
+        rc = choose_tokens(b, cmd, m->logits, 1, params, (unsigned long long *)b->rng->ptr + 2 * seq, F(b->scratch) + (size_t)seq * 2 * m->cfg.vocab,
+                           b->ids, seq);
     int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
     BRASA_TRY(rc);
     BRASA_TRY(rc2);
@@ -680,8 +700,7 @@ int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params
     for (uint32_t s = 0; s < steps && rc == BRASA_OK; ++s) {
         rc = encode_step(b, cmd, n);
         if (rc != BRASA_OK) break;
-        rc = brasa_sample_batched_launch(cmd, F(b->logits), m->cfg.vocab, n, params.temperature, params.top_k, params.top_p,
-                                         (unsigned long long *)b->rng->ptr, F(b->scratch), (uint32_t *)b->out->ptr);
+        rc = choose_tokens(b, cmd, b->logits, n, params, (unsigned long long *)b->rng->ptr, F(b->scratch), b->out, 0);
         if (rc != BRASA_OK) break;
         gather_ids_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>((uint32_t *)b->ids->ptr, (const uint32_t *)b->out->ptr, n);
         rc = brasa_post_launch(cmd, "next_ids");
@@ -714,7 +733,7 @@ int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits) {
     int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
     BRASA_TRY(rc);
     BRASA_TRY(rc2);
-    return brasa_buf_download(b->logits, 0, logits, (uint64_t)b->nseq * b->m->cfg.vocab * 4);
+    return brasa_buf_download(b->logits, 0, logits, (uint64_t)b->nseq * b->m->cfg.head_rows * 4);
 }
 
 uint32_t brasa_batch_sequences(brasa_batch *b) { return b ? b->nseq : 0; }

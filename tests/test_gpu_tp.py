@@ -120,6 +120,19 @@ def test_one_rank_exchange_changes_nothing(B, ctx, untied_model, kv):
     want, _ = plain.forward(ids, 0)
     want1, _ = plain.forward(ids[:1], 40)
     want_t, _ = plain.decode_greedy(int(ids[0]), 40, 12)
+
+    def batch_of(model):
+        g = np.random.default_rng(6)
+        bt = B.Batch(model, max_seqs=10, num_pages=40, max_positions=64)
+        bt.set_prefix(g.integers(0, 1024, size=16).astype(np.uint32))
+        for k in (5, 11, 3, 7, 2, 9, 4, 6, 8, 10):  # ten sequences: the projections run as GEMMs
+            bt.add_sequence(g.integers(0, 1024, size=k).astype(np.uint32))
+        lg = bt.peek_logits()
+        out, _ = bt.decode(6)
+        bt.free()
+        return lg, out
+
+    want_bl, want_bids = batch_of(plain)
     plain.free()
     m = B.Qwen3.load(ctx, untied_model, limits)
     tp = TensorParallel(ctx, 0, 1, 64 * 512)
@@ -132,6 +145,8 @@ def test_one_rank_exchange_changes_nothing(B, ctx, untied_model, kv):
         assert np.array_equal(got, want)
         assert np.abs(got1 - want1).max() <= 1e-5 * np.abs(want1).max()  # x + (W a) in one kernel or in two
         assert list(toks) == list(want_t) == list(toks2)
+        got_bl, got_bids = batch_of(m)  # the batched path with the exchange in place of the residual adds
+        assert np.array_equal(got_bl, want_bl) and np.array_equal(got_bids, want_bids)
     finally:
         m.free()
         tp.free()
@@ -166,6 +181,16 @@ def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model,
         want, _ = m.forward(ids, 0)
         want1, _ = m.forward(ids[:1], n_prompt)
         want_t, _ = m.decode_greedy(int(ids[0]), n_prompt, steps)
+        g = np.random.default_rng(6)
+        prefix = g.integers(0, 1024, size=16).astype(np.uint32)
+        own = [g.integers(0, 1024, size=int(k)).astype(np.uint32) for k in (5, 11, 3)]
+        bt = B.Batch(m, max_seqs=3, num_pages=16, max_positions=64)
+        bt.set_prefix(prefix)
+        for o in own:
+            bt.add_sequence(o)
+        want_bl = bt.peek_logits()
+        want_bids, _ = bt.decode(8)
+        bt.free()
     finally:
         m.free()
     ranks = [np.load(tmp_path / f"rank{r}.npz") for r in range(2)]
@@ -181,3 +206,8 @@ def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model,
     assert np.abs(got1 - want1).max() <= tol * np.abs(want1).max()
     for r in ranks:
         assert list(r["toks"]) == list(want_t) and list(r["toks2"]) == list(want_t)
+    # the batched path over paged KV: every rank chose the same tokens, and they are the unsplit model's
+    got_bl = np.concatenate([r["batch_logits"] for r in ranks], axis=1)
+    assert np.abs(got_bl - want_bl).max() <= tol * np.abs(want_bl).max()
+    assert np.array_equal(ranks[0]["batch_ids"], ranks[1]["batch_ids"])
+    assert np.array_equal(ranks[0]["batch_ids"], want_bids)

@@ -38,7 +38,22 @@ def main():
     toks, _ = m.decode_greedy(first, n_prompt, steps)  # device-resident loop with the argmax exchange
     dist.barrier()
     toks2, _ = m.decode_greedy(first, n_prompt, steps)  # CUDA graph replay of the same steps
-    np.savez(out_dir / f"rank{rank}.npz", logits=logits, one=one, toks=toks, toks2=toks2, row0=m.cfg["head_row0"])
+    # several sequences decoded together over paged KV (greedy: each row's best pair is exchanged between the ranks)
+    g = np.random.default_rng(6)
+    prefix = g.integers(0, m.cfg["vocab"], size=16).astype(np.uint32)
+    own = [g.integers(0, m.cfg["vocab"], size=int(k)).astype(np.uint32) for k in (5, 11, 3)]
+    bt = B.Batch(m, max_seqs=3, num_pages=16, max_positions=64)
+    dist.barrier()
+    bt.set_prefix(prefix)
+    for o in own:
+        dist.barrier()
+        bt.add_sequence(o)
+    dist.barrier()
+    bl = bt.peek_logits()
+    dist.barrier()
+    bids, _ = bt.decode(8)
+    bt.free()
+    np.savez(out_dir / f"rank{rank}.npz", logits=logits, one=one, toks=toks, toks2=toks2, row0=m.cfg["head_row0"], batch_logits=bl, batch_ids=bids)
     dist.barrier()
     m.free()
     tp.free()
