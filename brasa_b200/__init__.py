@@ -480,6 +480,10 @@ class Kernels:
     def gemm(self, cmd, w: QMatrix, x, y, tokens):
         self._k(self.L.brasa_k_gemm(cmd._h, w._c(), _arg(x), _arg(y), C.c_uint32(tokens)))
 
+    def gemm_add(self, cmd, w: QMatrix, x, acc, scratch, tokens):
+        """acc += W x (f16 inputs): the residual add folded into the GEMM."""
+        self._k(self.L.brasa_k_gemm_add(cmd._h, w._c(), _arg(x), _arg(acc), _arg(scratch), C.c_uint32(tokens)))
+
     def gemm_with(self, cmd, w: QMatrix, x, y, tokens, precision):
         self._k(self.L.brasa_k_gemm_with(cmd._h, w._c(), _arg(x), _arg(y), C.c_uint32(tokens), C.c_int32(int(precision))))
 

@@ -543,8 +543,11 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         if (half_io) decode_reduce_paged_kernel<true><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
         else decode_reduce_paged_kernel<false><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
         BRASA_TRY(brasa_post_launch(cmd, "decode_reduce_paged"));
-        BRASA_TRY(mm(l.wo, half_io ? A(m->xh) : A(m->attn), A(m->h)));
-        BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
+        if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.wo.q, A(m->xh), A(m->x), A(m->h), n));
+        else {
+            BRASA_TRY(mm(l.wo, half_io ? A(m->xh) : A(m->attn), A(m->h)));
+            BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
+        }
         brasa_arg act;
         if (half_io) {
             BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
@@ -557,8 +560,11 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
             BRASA_TRY(brasa_k_swiglu(cmd, A(m->gate), A(m->up), A(m->gate), (uint64_t)n * c.ffn));
             act = A(m->gate);
         }
-        BRASA_TRY(mm(l.down, act, A(m->h)));
-        BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
+        if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.down.q, act, A(m->x), A(m->h), n));
+        else {
+            BRASA_TRY(mm(l.down, act, A(m->h)));
+            BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
+        }
     }
     if (half_io) {
         BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(m->final_norm), A(m->xh), n, H, c.eps));

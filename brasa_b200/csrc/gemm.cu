@@ -10,7 +10,8 @@
 #include "brasa_internal.h"
 
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
-int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens);
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
+                             const float *resid);
 
 namespace {
 
@@ -193,13 +194,30 @@ int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_ar
     if (tokens == 0) return BRASA_OK;
     if (half_in && tc_enabled() && tokens > 8 && brasa_gemm_tc_supported(w, tokens)) {
         float *yp = (float *)arg_ptr(y);
-        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x), &yp, tokens);
+        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x), &yp, tokens, nullptr);
     }
     WView v{arg_ptr(w.data), w.qtype, w.layout, w.rows, w.cols};
     dim3 grid((w.rows + TN - 1) / TN, (tokens + TM - 1) / TM);
     if (half_in) gemm_f16_kernel<<<grid, 128, 0, ctx->stream>>>(v, (const __half *)arg_ptr(x), (float *)arg_ptr(y), tokens);
     else gemm_f32_kernel<<<grid, 256, 0, ctx->stream>>>(v, (const float *)arg_ptr(x), (float *)arg_ptr(y), tokens);
     return brasa_post_launch(cmd, "gemm");
+}
+
+// acc += W X for f16 inputs (the residual add of a layer folded into the GEMM's epilogue when the tensor-core kernel
+// takes the product; otherwise the product goes to `scratch` and is added by the element-wise kernel).
+int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, uint32_t tokens) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    const uint64_t n = (uint64_t)tokens * w.rows;
+    BRASA_REQUIRE(ctx, arg_fits(acc, n * 4) && arg_fits(scratch, n * 4), "gemm_add: acc or scratch too small");
+    if (tokens == 0) return BRASA_OK;
+    if (tc_enabled() && tokens > 8 && w.qtype >= BRASA_Q4_0 && w.qtype <= BRASA_Q6_0 && qm_fits(w) && brasa_gemm_tc_supported(w, tokens) &&
+        arg_fits(x_f16, (uint64_t)tokens * w.cols * 2) && x_f16.offset % 16 == 0 && acc.offset % 16 == 0) {
+        float *yp = (float *)arg_ptr(acc);
+        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x_f16), &yp, tokens, yp);
+    }
+    BRASA_TRY(brasa_k_gemm_with(cmd, w, x_f16, scratch, tokens, BRASA_PREFILL_F16));
+    return brasa_k_add(cmd, acc, scratch, acc, n);
 }
 
 int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg y, uint32_t tokens) {
@@ -218,7 +236,7 @@ int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t cou
     if (all_tc && x.offset % 16 == 0) {
         float *yp[3] = {nullptr, nullptr, nullptr};
         for (uint32_t i = 0; i < count; ++i) yp[i] = (float *)arg_ptr(ys[i]);
-        return brasa_gemm_tc_launch(cmd, count, ws, (const __half *)arg_ptr(x), yp, tokens);
+        return brasa_gemm_tc_launch(cmd, count, ws, (const __half *)arg_ptr(x), yp, tokens, nullptr);
     }
     for (uint32_t i = 0; i < count; ++i) {
         BRASA_REQUIRE(cmd->ctx, ws[i].cols == ws[0].cols, "gemm_multi: matrices must share the input");

@@ -68,6 +68,7 @@ struct GemmTcParams {
     uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
     uint32_t cols, tokens, stages;
     uint32_t *status;
+    const float *resid;   // when set (one matrix only): Y = resid + W X, the residual add of the layer (resid may be Y itself)
     uint32_t ksplit;      // grid.z CTAs share one output tile, each over its own range of K stages
     float *part;          // ksplit > 1: [z][tile][MT x 128 tokens][BNT rows] partial tiles
     uint32_t *counters;   // ksplit > 1: arrivals per output tile (zero between launches)
@@ -318,10 +319,17 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                     if (token < p.tokens) {
                         float4 *dst = ptile ? reinterpret_cast<float4 *>(ptile + (size_t)(mt * BM + q * 32 + lane) * BNT + c)
                                             : reinterpret_cast<float4 *>(ymat + (size_t)token * yrows + n0 + c);
+                        const float4 *add = (!ptile && p.resid) ? reinterpret_cast<const float4 *>(p.resid + (size_t)token * yrows + n0 + c) : nullptr;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
-                                                 __uint_as_float(v[4 * i + 3]));
+                        for (int i = 0; i < 4; ++i) {
+                            float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                                                   __uint_as_float(v[4 * i + 3]));
+                            if (add) {
+                                const float4 r = add[i];
+                                o = make_float4(r.x + o.x, r.y + o.y, r.z + o.z, r.w + o.w);
+                            }
+                            dst[i] = o;
+                        }
                     }
                 }
             }
@@ -358,7 +366,14 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const uint32_t i = i0 + u * 256;
-                        if (i < live) *reinterpret_cast<float4 *>(ymat + (size_t)(tok0 + (i * 4) / BNT) * yrows + n0 + (i * 4) % BNT) = a[u];
+                        if (i < live) {
+                            const size_t at = (size_t)(tok0 + (i * 4) / BNT) * yrows + n0 + (i * 4) % BNT;
+                            if (p.resid) {
+                                const float4 r = *reinterpret_cast<const float4 *>(p.resid + at);
+                                a[u] = make_float4(r.x + a[u].x, r.y + a[u].y, r.z + a[u].z, r.w + a[u].w);
+                            }
+                            *reinterpret_cast<float4 *>(ymat + at) = a[u];
+                        }
                     }
                 }
                 if (tid == 128) p.counters[tile_id] = 0;
@@ -397,10 +412,14 @@ bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
 }
 
 // Y_i = W_i X for 1 to 3 matrices that share X (f16, [tokens][cols]); every W_i must pass brasa_gemm_tc_supported.
-int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens) {
+// resid (optional, one matrix): Y = resid + W X (same shape as Y; may be Y itself).
+int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
+                             const float *resid) {
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, count >= 1 && count <= 3, "gemm: 1 to 3 matrices");
+    BRASA_REQUIRE(ctx, !resid || (count == 1 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0), "gemm: a residual goes with one matrix and must be 16-byte aligned");
     GemmTcParams p{};
+    p.resid = resid;
     bool rows256 = true;
     uint32_t tiles128 = 0;
     for (uint32_t i = 0; i < count; ++i) {

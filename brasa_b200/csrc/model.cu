@@ -166,8 +166,11 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
     } else {
         BRASA_TRY(brasa_k_flash_attention_with(cmd, A(m->q), all.k, all.v, attn, sh, half_io ? BRASA_PREFILL_F16 : BRASA_PREFILL_F32));
     }
-    BRASA_TRY(matmul(m, cmd, l.wo, attn, A(m->h), tokens, half_io));
-    BRASA_TRY(residual_add(m, cmd, (uint64_t)tokens * H));
+    if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.wo.q, attn, A(m->x), A(m->h), tokens));  // x += Wo attn in the GEMM's epilogue
+    else {
+        BRASA_TRY(matmul(m, cmd, l.wo, attn, A(m->h), tokens, half_io));
+        BRASA_TRY(residual_add(m, cmd, (uint64_t)tokens * H));
+    }
     brasa_arg act;
     if (half_io) {
         BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), tokens, H, c.eps));
@@ -180,6 +183,7 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
         BRASA_TRY(brasa_k_swiglu(cmd, A(m->gate), A(m->up), A(m->gate), (uint64_t)tokens * c.ffn));
         act = A(m->gate);
     }
+    if (half_io && !m->tp) return brasa_k_gemm_add(cmd, l.down.q, act, A(m->x), A(m->h), tokens);
     BRASA_TRY(matmul(m, cmd, l.down, act, A(m->h), tokens, half_io));
     return residual_add(m, cmd, (uint64_t)tokens * H);
 }

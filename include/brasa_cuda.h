@@ -167,7 +167,10 @@ int32_t brasa_k_gemv(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, 
 int32_t brasa_k_gemv_simple(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens);     /* :813 */
 /* y[t, :] = W x[t, :]; precision F16: x is f16 and dequantised weights are rounded to f16 :856 */
 int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens, int32_t precision);
-int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg y, uint32_t tokens);        /* :842 */
+int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg y, uint32_t tokens);
+/* acc += W x for f16 inputs: the layer's residual add folded into the GEMM (scratch: tokens x rows f32, used when the
+ * product takes the generic kernel). New: the reference adds with a separate `add` dispatch (qwen3.rs:810-826). */
+int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, uint32_t tokens);        /* :842 */
 int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t count, brasa_arg x, const brasa_arg *ys, uint32_t tokens, int32_t precision); /* :872 */
 /* out_f16[t, :] = f16(silu(Wg x) * (Wu x)); gate/up scratch [tokens, rows] f32 may be used :455 */
 int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, brasa_arg x_f16, brasa_arg gate, brasa_arg up, brasa_arg out_f16, uint32_t tokens);

@@ -482,6 +482,22 @@ def test_gemm_swiglu_equals_unfused(B, ctx, K):
     assert np.all(np.abs(got - want) <= bound)
 
 
+@pytest.mark.parametrize("rows,cols,tokens", [(256, 4096, 16), (1024, 512, 300), (100, 96, 20)])
+def test_gemm_add_equals_gemm_then_add(B, ctx, K, rows, cols, tokens):
+    """acc += W x with the add in the GEMM's epilogue (split K, plain tensor-core and generic paths) gives the very
+    bits of the GEMM followed by the element-wise add."""
+    rng = O.Rng(83)
+    raw = rng.qmatrix(O.Q4_0, rows, cols)
+    m = tiled(B, ctx, K, "q4_0", raw, rows, cols)[0] if cols % 256 == 0 else B.QMatrix(ctx.buffer_from(raw), B.WeightType.Q4_0, rows, cols)
+    xh = rng.vec(tokens * cols, 1.0).astype(np.float16)
+    acc0 = rng.vec(tokens * rows, 2.0)
+    gx, gy, gs = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4), ctx.buffer(tokens * rows * 4)
+    ga, gb = ctx.buffer_from(acc0), ctx.buffer_from(acc0)
+    run(ctx, lambda c: (K.gemm(c, m, gx, gy, tokens), K.add(c, gb, gy, gb, tokens * rows)))
+    run(ctx, lambda c: K.gemm_add(c, m, gx, ga, gs, tokens))
+    assert np.array_equal(ga.download(np.float32), gb.download(np.float32))
+
+
 # ---- argmax --------------------------------------------------------------------------------------
 
 def test_argmax_edge_cases(ctx, K):
