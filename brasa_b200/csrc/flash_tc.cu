@@ -86,6 +86,17 @@ __device__ __forceinline__ void split_pair(float p0, float p1, uint32_t &hi, uin
     lo = *reinterpret_cast<const uint32_t *>(&ll);
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, "
+        "%21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+          "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+          "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 struct FlashTcParams {
     const float *q;        // [tokens][hq][128] after QK-norm and RoPE
     const uint8_t *kc, *vc;  // cache rows [position][hkv][128] in the cache's type, from position 0
@@ -604,7 +615,14 @@ __device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32
 
 // SPLITKV: K and V come as hi + lo tiles (one buffer each instead of two), S = Q K_hi + Q K_lo and
 // O += P_hi V_hi + P_lo V_hi + P_hi V_lo (lo x lo is below 2^-22).
-template <bool SPLITKV>
+// ONEPASS: one sweep over the keys. Each row keeps a reference value m_ref for its exponentials; a tile whose largest
+// score exceeds m_ref by more than ONEPASS_SLACK (or the first tile) moves the reference to that score, and the row of O
+// accumulated so far and the row sum are multiplied by exp(old - new) in tensor memory before the tile's P V is issued.
+// With the slack such moves are rare after the first tile, probabilities stay below e^slack = 256 (well inside f16), and
+// the sweep that only looked for the row maxima (a second Q K^T per tile) is gone.
+constexpr float ONEPASS_SLACK = 5.545177444f;  // 8 ln 2
+
+template <bool SPLITKV, bool ONEPASS>
 __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -616,6 +634,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     uint8_t *klo = smem + 2 * TILE_BYTES, *vlo = smem + 4 * TILE_BYTES;
     __shared__ uint64_t bar_s[2], bar_k[2], bar_v[2], bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
+    __shared__ float pair_max[2][128];  // ONEPASS: a tile's largest score of each column half, by row
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t qtile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, kh = h / (p.hq / p.hkv);  // longest query tiles first
@@ -737,58 +756,60 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         return __all_sync(0xffffffffu, r);
     };
 
-    // ---- sweep 1: row maxima ----
-    if (issuer) {
-        fetch_k(0);
-        if (!SPLITKV && nkt > 1) fetch_k(1);
-        if (wait_k(0)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(KB(0), 0);
+    if constexpr (!ONEPASS) {
+        // ---- sweep 1: row maxima ----
+        if (issuer) {
+            fetch_k(0);
+            if (!SPLITKV && nkt > 1) fetch_k(1);
+            if (wait_k(0)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(0), 0);
+            }
         }
-    }
-    for (uint32_t j = 0; j < nkt; ++j) {
-        // S of tile j + 1 goes into the buffer whose last readers (tile j - 1) passed the previous barrier
-        if (!SPLITKV && issuer && j + 1 < nkt && wait_k(j + 1)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(KB(j + 1), (j + 1) & 1);
-        }
-        ok = wait_s(j);
-        if (ok) {
-            if (issuer) {  // S of tile j is complete: its K buffer is free
-                if (!SPLITKV && j + 2 < nkt) fetch_k(j + 2);
-                if (SPLITKV && j + 1 < nkt) {  // one K buffer: the next tile travels and its S is issued while this tile's rows are scanned
-                    fetch_k(j + 1);
-                    if (wait_k(j + 1)) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_s(KB(j + 1), (j + 1) & 1);
+        for (uint32_t j = 0; j < nkt; ++j) {
+            // S of tile j + 1 goes into the buffer whose last readers (tile j - 1) passed the previous barrier
+            if (!SPLITKV && issuer && j + 1 < nkt && wait_k(j + 1)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(KB(j + 1), (j + 1) & 1);
+            }
+            ok = wait_s(j);
+            if (ok) {
+                if (issuer) {  // S of tile j is complete: its K buffer is free
+                    if (!SPLITKV && j + 2 < nkt) fetch_k(j + 2);
+                    if (SPLITKV && j + 1 < nkt) {  // one K buffer: the next tile travels and its S is issued while this tile's rows are scanned
+                        fetch_k(j + 1);
+                        if (wait_k(j + 1)) {
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            issue_s(KB(j + 1), (j + 1) & 1);
+                        }
                     }
                 }
-            }
-            if (softmax) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-                if (j < nfree) {
-                    max_chunk<false>(ts, 0, 0, m);
-                    max_chunk<false>(ts + 32, 0, 0, m);
-                } else {
-                    max_chunk<true>(ts, j * 128 + chalf, qpos, m);
-                    max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+                if (softmax) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+                    if (j < nfree) {
+                        max_chunk<false>(ts, 0, 0, m);
+                        max_chunk<false>(ts + 32, 0, 0, m);
+                    } else {
+                        max_chunk<true>(ts, j * 128 + chalf, qpos, m);
+                        max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
         }
-        ok = __syncthreads_and(ok);
-        if (!ok) break;
+        // the two halves of a row agree on its maximum (the P tiles are not in use yet)
+        {
+            float *stat = reinterpret_cast<float *>(ph);
+            if (softmax) stat[(warp >> 2) * 128 + row] = m;
+            __syncthreads();
+            m = fmaxf(stat[row], stat[128 + row]);
+            __syncthreads();
+        }
     }
-    // the two halves of a row agree on its maximum (the P tiles are not in use yet)
-    {
-        float *stat = reinterpret_cast<float *>(ph);
-        if (softmax) stat[(warp >> 2) * 128 + row] = m;
-        __syncthreads();
-        m = fmaxf(stat[row], stat[128 + row]);
-        __syncthreads();
-    }
-    const float mneg = -m * 1.4426950408889634f;
+    float mneg = -m * 1.4426950408889634f;  // ONEPASS: m is still -inf here and moves with the tiles
 
     // ---- sweep 2: P = exp(S - m), O += P V ----
     if (ok && issuer) {
@@ -810,9 +831,32 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         if (ok) {
             if (issuer && !SPLITKV && j + 2 < nkt) fetch_k(j + 2);
             if (issuer && SPLITKV && j + 1 < nkt) fetch_k(j + 1);
+            float rescale = 1.0f;
+            bool move = false;
             if (softmax) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
+                if (ONEPASS) {
+                    // this tile's largest score of the row: own 64 columns, then the other half's through shared memory
+                    float tmax = -INFINITY;
+                    if (j < nfree) {
+                        max_chunk<false>(ts, 0, 0, tmax);
+                        max_chunk<false>(ts + 32, 0, 0, tmax);
+                    } else {
+                        max_chunk<true>(ts, j * 128 + chalf, qpos, tmax);
+                        max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, tmax);
+                    }
+                    pair_max[(warp >> 2) & 1][row] = tmax;
+                    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");  // the two warps that share these rows
+                    tmax = fmaxf(tmax, pair_max[((warp >> 2) & 1) ^ 1][row]);
+                    if (tmax > m + ONEPASS_SLACK || (m == -INFINITY && tmax != -INFINITY)) {
+                        move = m != -INFINITY;
+                        rescale = move ? ex2_approx((m - tmax) * 1.4426950408889634f) : 1.0f;
+                        l *= rescale;
+                        m = tmax;
+                        mneg = -m * 1.4426950408889634f;
+                    }
+                }
                 if (j < nfree) {
                     prob_chunk<false>(ts, 0, 0, mneg, l, hi[0], lo[0]);
                     prob_chunk<false>(ts + 32, 0, 0, mneg, l, hi[1], lo[1]);
@@ -826,6 +870,20 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                 ok = wait(&bar_o, ph_o);
                 ph_o ^= 1;
                 ok = __all_sync(0xffffffffu, ok);
+            }
+            if (ONEPASS && softmax && ok && __any_sync(0xffffffffu, move)) {
+                // a row's reference moved: what O holds for it was accumulated against the old one (P V of tile j - 1 is
+                // complete, P V of tile j not yet issued); each half of the pair scales its own 64 dims
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_o + trow + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * rescale);
+                    tmem_st32(tmem_o + trow + c, v);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
         }
         if (ok) {
@@ -978,12 +1036,17 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
         const size_t smem = 7 * TILE_BYTES + 1024;
         static bool done = false;
         if (!done) {
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             done = true;
         }
-        if (split) flash_tc_f16_kernel<true><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else flash_tc_f16_kernel<false><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        static const bool onepass = [] { const char *e = getenv("BRASA_FLASH_ONEPASS"); return !(e && e[0] == '0'); }();
+        if (split && onepass) flash_tc_f16_kernel<true, true><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else if (split) flash_tc_f16_kernel<true, false><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else if (onepass) flash_tc_f16_kernel<false, true><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else flash_tc_f16_kernel<false, false><<<grid, 288, smem, ctx->stream>>>(maps, p);
         return brasa_post_launch(cmd, "flash_tc_f16");
     }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
