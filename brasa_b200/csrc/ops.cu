@@ -57,6 +57,42 @@ __global__ void rms_norm_kernel(const float *x, const float *w, void *out, uint3
     }
 }
 
+// The same with one warp per row and the row held in registers (n a multiple of 128, at most 128 * RMS_MAX_CHUNKS):
+// one pass over x with 16-byte loads, no shared memory, eight rows per block. Used for many rows (prefill, batch steps).
+constexpr int RMS_MAX_CHUNKS = 20;
+template <bool HALF_OUT>
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float *x, const float *w, void *out, uint32_t rows, uint32_t n, float eps) {
+    const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31, chunks = n / 128;
+    if (row >= rows) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * n);
+    float4 v[RMS_MAX_CHUNKS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < RMS_MAX_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            v[c] = xr[c * 32 + lane];
+            ss += (v[c].x * v[c].x + v[c].y * v[c].y) + (v[c].z * v[c].z + v[c].w * v[c].w);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    const float4 *wr = reinterpret_cast<const float4 *>(w);
+#pragma unroll
+    for (int c = 0; c < RMS_MAX_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            const float4 ww = wr[c * 32 + lane];
+            const float a = v[c].x * scale * ww.x, b = v[c].y * scale * ww.y, cc = v[c].z * scale * ww.z, d = v[c].w * scale * ww.w;
+            if (HALF_OUT) {
+                const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(cc, d);
+                reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(out) + (size_t)row * n)[c * 32 + lane] =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+            } else {
+                reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)row * n)[c * 32 + lane] = make_float4(a, b, cc, d);
+            }
+        }
+    }
+}
+
 __global__ void softmax_kernel(const float *x, float *out, uint32_t n) {
     __shared__ float red[32];
     const float *xr = x + (size_t)blockIdx.x * n;
@@ -266,6 +302,12 @@ static int32_t rms_norm_common(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_a
     uint64_t tot = (uint64_t)rows * n;
     BRASA_REQUIRE(ctx, n > 0 && arg_fits(x, tot * 4) && arg_fits(w, (uint64_t)n * 4) && arg_fits(out, tot * (half_out ? 2 : 4)), "rms_norm: buffers too small");
     if (rows == 0) return BRASA_OK;
+    if (rows >= 16 && n % 128 == 0 && n <= 128 * RMS_MAX_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
+        const unsigned blocks = (rows + 7) / 8;
+        if (half_out) rms_norm_rows_kernel<true><<<blocks, 256, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        else rms_norm_rows_kernel<false><<<blocks, 256, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        return brasa_post_launch(cmd, "rms_norm");
+    }
     unsigned threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 32);
     if (half_out) rms_norm_kernel<true><<<rows, threads, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
     else rms_norm_kernel<false><<<rows, threads, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
