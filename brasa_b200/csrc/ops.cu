@@ -58,11 +58,11 @@ __global__ void rms_norm_kernel(const float *x, const float *w, void *out, uint3
 }
 
 // The same with one warp per row and the row held in registers (n a multiple of 128, at most 128 * RMS_MAX_CHUNKS):
-// one pass over x with 16-byte loads, no shared memory, eight rows per block. Used for many rows (prefill, batch steps).
+// one pass over x with 16-byte loads, no shared memory, two rows per block. Used for many rows (prefill, batch steps).
 constexpr int RMS_MAX_CHUNKS = 20;
 template <bool HALF_OUT>
-__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float *x, const float *w, void *out, uint32_t rows, uint32_t n, float eps) {
-    const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31, chunks = n / 128;
+__global__ void __launch_bounds__(64) rms_norm_rows_kernel(const float *x, const float *w, void *out, uint32_t rows, uint32_t n, float eps) {
+    const uint32_t row = blockIdx.x * 2 + (threadIdx.x >> 5), lane = threadIdx.x & 31, chunks = n / 128;
     if (row >= rows) return;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * n);
     float4 v[RMS_MAX_CHUNKS];
@@ -303,9 +303,9 @@ static int32_t rms_norm_common(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_a
     BRASA_REQUIRE(ctx, n > 0 && arg_fits(x, tot * 4) && arg_fits(w, (uint64_t)n * 4) && arg_fits(out, tot * (half_out ? 2 : 4)), "rms_norm: buffers too small");
     if (rows == 0) return BRASA_OK;
     if (rows >= 16 && n % 128 == 0 && n <= 128 * RMS_MAX_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
-        const unsigned blocks = (rows + 7) / 8;
-        if (half_out) rms_norm_rows_kernel<true><<<blocks, 256, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
-        else rms_norm_rows_kernel<false><<<blocks, 256, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        const unsigned blocks = (rows + 1) / 2;
+        if (half_out) rms_norm_rows_kernel<true><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        else rms_norm_rows_kernel<false><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
         return brasa_post_launch(cmd, "rms_norm");
     }
     unsigned threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 32);
