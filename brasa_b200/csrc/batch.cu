@@ -551,8 +551,8 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         brasa_arg act;
         if (half_io) {
             BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
-            BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), A(m->xh), n));
-            act = A(m->xh);
+            act = brasa_gemm_swiglu_fuses(l.gate.q, l.up.q, n) ? A(m->up) : A(m->xh);
+            BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), act, n));
         } else {
             BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.ffn_norm), A(m->norm_out), n, H, c.eps));
             BRASA_TRY(mm(l.gate, A(m->norm_out), A(m->gate)));

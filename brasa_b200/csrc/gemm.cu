@@ -11,7 +11,7 @@
 
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
 int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
-                             const float *resid);
+                             const float *resid, __half *glu);
 
 namespace {
 
@@ -180,6 +180,14 @@ bool tc_enabled() {
 
 }  // namespace
 
+// True when brasa_k_gemm_swiglu runs as one tensor-core launch for these matrices and token count (given an output that
+// does not overlap the input). The model then hands it a separate output buffer.
+bool brasa_gemm_swiglu_fuses(const brasa_qmatrix &wg, const brasa_qmatrix &wu, uint32_t tokens) {
+    static const bool fuse = [] { const char *e = getenv("BRASA_GEMM_GLU"); return !(e && e[0] == '0'); }();
+    return fuse && tc_enabled() && tokens >= 128 && wg.rows == wu.rows && wg.cols == wu.cols && wg.qtype >= BRASA_Q4_0 && wg.qtype <= BRASA_Q6_0 &&
+           qm_fits(wg) && qm_fits(wu) && brasa_gemm_tc_supported(wg, tokens) && brasa_gemm_tc_supported(wu, tokens);
+}
+
 extern "C" {
 
 int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_arg y, uint32_t tokens, int32_t precision) {
@@ -194,7 +202,7 @@ int32_t brasa_k_gemm_with(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x, brasa_ar
     if (tokens == 0) return BRASA_OK;
     if (half_in && tc_enabled() && tokens > 8 && brasa_gemm_tc_supported(w, tokens)) {
         float *yp = (float *)arg_ptr(y);
-        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x), &yp, tokens, nullptr);
+        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x), &yp, tokens, nullptr, nullptr);
     }
     WView v{arg_ptr(w.data), w.qtype, w.layout, w.rows, w.cols};
     dim3 grid((w.rows + TN - 1) / TN, (tokens + TM - 1) / TM);
@@ -214,7 +222,7 @@ int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa
     if (tc_enabled() && tokens > 8 && w.qtype >= BRASA_Q4_0 && w.qtype <= BRASA_Q6_0 && qm_fits(w) && brasa_gemm_tc_supported(w, tokens) &&
         arg_fits(x_f16, (uint64_t)tokens * w.cols * 2) && x_f16.offset % 16 == 0 && acc.offset % 16 == 0) {
         float *yp = (float *)arg_ptr(acc);
-        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x_f16), &yp, tokens, yp);
+        return brasa_gemm_tc_launch(cmd, 1, &w, (const __half *)arg_ptr(x_f16), &yp, tokens, yp, nullptr);
     }
     BRASA_TRY(brasa_k_gemm_with(cmd, w, x_f16, scratch, tokens, BRASA_PREFILL_F16));
     return brasa_k_add(cmd, acc, scratch, acc, n);
@@ -236,7 +244,7 @@ int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t cou
     if (all_tc && x.offset % 16 == 0) {
         float *yp[3] = {nullptr, nullptr, nullptr};
         for (uint32_t i = 0; i < count; ++i) yp[i] = (float *)arg_ptr(ys[i]);
-        return brasa_gemm_tc_launch(cmd, count, ws, (const __half *)arg_ptr(x), yp, tokens, nullptr);
+        return brasa_gemm_tc_launch(cmd, count, ws, (const __half *)arg_ptr(x), yp, tokens, nullptr, nullptr);
     }
     for (uint32_t i = 0; i < count; ++i) {
         BRASA_REQUIRE(cmd->ctx, ws[i].cols == ws[0].cols, "gemm_multi: matrices must share the input");
@@ -249,6 +257,15 @@ int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, 
                             uint32_t tokens) {
     if (!cmd) return BRASA_EINVAL;
     BRASA_REQUIRE(cmd->ctx, wg.rows == wu.rows && wg.cols == wu.cols, "gemm_swiglu: gate and up shapes");
+    // many tokens: one tensor-core launch whose epilogue forms silu(gate) * up (gate and up are then not written). The
+    // output must not share memory with the input: other CTAs still read X while the first results are stored.
+    const bool apart = x_f16.buf != out_f16.buf || x_f16.offset + (uint64_t)tokens * wg.cols * 2 <= out_f16.offset ||
+                       out_f16.offset + (uint64_t)tokens * wg.rows * 2 <= x_f16.offset;
+    if (apart && brasa_gemm_swiglu_fuses(wg, wu, tokens) && arg_fits(x_f16, (uint64_t)tokens * wg.cols * 2) &&
+        arg_fits(out_f16, (uint64_t)tokens * wg.rows * 2) && x_f16.offset % 16 == 0 && out_f16.offset % 16 == 0) {
+        const brasa_qmatrix ws[2] = {wg, wu};
+        return brasa_gemm_tc_launch(cmd, 2, ws, (const __half *)arg_ptr(x_f16), nullptr, tokens, nullptr, (__half *)arg_ptr(out_f16));
+    }
     BRASA_TRY(brasa_k_gemm_with(cmd, wg, x_f16, gate, tokens, BRASA_PREFILL_F16));
     BRASA_TRY(brasa_k_gemm_with(cmd, wu, x_f16, up, tokens, BRASA_PREFILL_F16));
     return brasa_k_swiglu_f16(cmd, gate, up, out_f16, (uint64_t)tokens * wg.rows);

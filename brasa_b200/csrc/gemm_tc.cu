@@ -68,6 +68,7 @@ struct GemmTcParams {
     uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
     uint32_t cols, tokens, stages;
     uint32_t *status;
+    __half *glu;          // when set: w[0] = gate, w[1] = up, a CTA holds 128 rows of each and writes f16(silu(gate) * up) here
     const float *resid;   // when set (one matrix only): Y = resid + W X, the residual add of the layer (resid may be Y itself)
     uint32_t ksplit;      // grid.z CTAs share one output tile, each over its own range of K stages
     float *part;          // ksplit > 1: [z][tile][MT x 128 tokens][BNT rows] partial tiles
@@ -99,8 +100,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // which matrix and which BNT rows of it
-    const uint32_t mi = (blockIdx.x >= p.tile_end[0]) + (blockIdx.x >= p.tile_end[1]);
-    const uint32_t n0 = (blockIdx.x - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BNT, tok0 = blockIdx.y * (MT * BM);
+    const bool glu = NB == 2 && p.glu != nullptr;  // gate and up side by side: weight rows [0, 128) of the CTA are gate's, [128, 256) up's
+    const uint32_t mi = glu ? 0u : (blockIdx.x >= p.tile_end[0]) + (blockIdx.x >= p.tile_end[1]);
+    const uint32_t n0 = glu ? blockIdx.x * BN : (blockIdx.x - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BNT,
+                   tok0 = blockIdx.y * (MT * BM);
     const uint8_t *wmat = mi == 0 ? p.w[0] : (mi == 1 ? p.w[1] : p.w[2]);
     float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
     const uint32_t yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
@@ -222,8 +225,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             const uint32_t u = gt + i * GT, wr = u & (BNT - 1), blk = u / BNT;
             soff[i] = (wr >> 3) * 1024 + (wr & 7) * 128 + (blk << 16) + ((wr & 7) << 20);  // row offset | block | row & 7
             roff[i] = wr * 32 + blk * 16;                                                   // the unit's codes in the raw tile
-            wp[i] = wmat + (size_t)(n0 + wr) * row_bytes + blk * 16 + (size_t)kbeg * 32;
-            sp[i] = wmat + (size_t)(n0 + wr) * row_bytes + sc_off + blk * 2 + (size_t)kbeg * 4;
+            const uint8_t *wbase = (glu && wr >= BN) ? p.w[1] : wmat;
+            const uint32_t grow = glu ? n0 + (wr & (BN - 1)) : n0 + wr;
+            wp[i] = wbase + (size_t)grow * row_bytes + blk * 16 + (size_t)kbeg * 32;
+            sp[i] = wbase + (size_t)grow * row_bytes + sc_off + blk * 2 + (size_t)kbeg * 4;
         }
         uint4 cwq[UN];
         unsigned short scq[UN];
@@ -298,7 +303,47 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         // with split K the tile goes to this CTA's partial buffer and the last CTA of the tile to arrive adds them up
         const uint32_t tile_elems = MT * BM * BNT, tile_id = blockIdx.y * gridDim.x + blockIdx.x;
         float *ptile = p.ksplit > 1 ? p.part + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile_id) * tile_elems : nullptr;
-        if (ok) {
+        if (ok && glu) {
+            // silu(gate) * up, rounded to f16: columns [0, 128) of a token tile's accumulator are gate's, [128, 256) up's
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t q = warp & 3;
+            const int c_begin = ((warp - 4) >> 2) * (BN / 2);
+#pragma unroll 1
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t token = tok0 + mt * BM + q * 32 + lane;
+#pragma unroll 1
+                for (int c = c_begin; c < c_begin + BN / 2; c += 16) {
+                    uint32_t g[16], u[16];
+                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BNT + c;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]),
+                          "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
+                          "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+                        : "r"(taddr + BN)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (token < p.tokens) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float g0 = __uint_as_float(g[i]), g1 = __uint_as_float(g[i + 1]);
+                            const float v0 = (g0 / (1.0f + expf(-g0))) * __uint_as_float(u[i]), v1 = (g1 / (1.0f + expf(-g1))) * __uint_as_float(u[i + 1]);
+                            const __half2 hh = __floats2half2_rn(v0, v1);
+                            packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(p.glu + (size_t)token * yrows + n0 + c);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                }
+            }
+        } else if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3;           // the lane quarter of tensor memory this warp may read
             const int c_begin = ((warp - 4) >> 2) * (BNT / 2);  // two warps per quarter: half of the columns each
@@ -413,18 +458,23 @@ bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
 
 // Y_i = W_i X for 1 to 3 matrices that share X (f16, [tokens][cols]); every W_i must pass brasa_gemm_tc_supported.
 // resid (optional, one matrix): Y = resid + W X (same shape as Y; may be Y itself).
+// glu (optional, two matrices gate and up of equal shape, rows a multiple of 128): out = f16(silu(W_gate X) * (W_up X)), [tokens][rows];
+// ys is not written then.
 int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
-                             const float *resid) {
+                             const float *resid, __half *glu) {
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, count >= 1 && count <= 3, "gemm: 1 to 3 matrices");
+    BRASA_REQUIRE(ctx, !glu || (count == 2 && ws[0].rows == ws[1].rows && !resid && (reinterpret_cast<uintptr_t>(glu) & 15) == 0),
+                  "gemm: the fused SwiGLU takes gate and up of equal shape");
     BRASA_REQUIRE(ctx, !resid || (count == 1 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0), "gemm: a residual goes with one matrix and must be 16-byte aligned");
     GemmTcParams p{};
     p.resid = resid;
+    p.glu = glu;
     bool rows256 = true;
     uint32_t tiles128 = 0;
     for (uint32_t i = 0; i < count; ++i) {
         BRASA_REQUIRE(ctx, brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols, "gemm: shape not taken by the tensor-core kernel");
-        BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(ys[i]) & 15) == 0, "gemm: misaligned y");
+        BRASA_REQUIRE(ctx, glu || (reinterpret_cast<uintptr_t>(ys[i]) & 15) == 0, "gemm: misaligned y");
         rows256 = rows256 && ws[i].rows % 256 == 0;
         tiles128 += ws[i].rows / BN;
     }
@@ -465,16 +515,22 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
             ksplit = 1;
         }
     }
+    if (glu) {  // 128 rows of gate and the same 128 rows of up per CTA: the 256-row shape, one or two token tiles
+        nb = 2;
+        mt = ntile >= 2 ? 2 : 1;
+        ksplit = 1;
+    }
     uint32_t ncta_n = 0;
     for (uint32_t i = 0; i < 3; ++i) {
         if (i < count) {
             p.w[i] = arg_ptr(ws[i].data);
-            p.y[i] = ys[i];
+            p.y[i] = ys ? ys[i] : nullptr;
             p.rows[i] = ws[i].rows;
             ncta_n += ws[i].rows / (BN * nb);
         }
         p.tile_end[i] = ncta_n;
     }
+    if (glu) ncta_n = ws[0].rows / BN;
     const brasa_qmatrix &w = ws[0];
     BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0, "gemm: misaligned x");
     // X as a 2-D tensor [tokens][cols] of f16; a box is 64 columns x 128 tokens, 128-byte swizzle, zeros past the end
@@ -486,9 +542,10 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
     // the weight matrices as byte tensors [rows][row_bytes]: box = 32 bytes x this CTA's rows, no swizzle
+    const bool raw = mt == 1 && nb == 1;  // weight bytes through TMA when one token tile per CTA leaves the weights as the main traffic
     WeightMaps wmaps;
     memset(&wmaps, 0, sizeof wmaps);
-    for (uint32_t i = 0; i < 3; ++i) {
+    for (uint32_t i = 0; raw && i < 3; ++i) {
         const brasa_qmatrix &wi = ws[i < count ? i : 0];
         const uint32_t rb = tiled_row_bytes(BRASA_Q4_0, wi.cols);
         cuuint64_t wdims[2] = {rb, wi.rows}, wstrides[1] = {rb};
@@ -499,7 +556,6 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (wr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the weights (%d)", (int)wr);
     }
-    const bool raw = mt == 1 && nb == 1;  // weight bytes through TMA when one token tile per CTA leaves the weights as the main traffic
     const uint32_t stage_bytes = mt * A_TILE + nb * B_TILE + (raw ? nb * 2 * RAW_TILE : 0);
     uint32_t stages = (uint32_t)std::min<size_t>(8, (ctx->smem_optin - 4096) / stage_bytes);
     stages = std::min<uint32_t>(stages, std::max<uint32_t>(2, (w.cols / BK + ksplit - 1) / ksplit));

@@ -174,8 +174,9 @@ int32_t encode_layer_prefill(brasa_model *m, brasa_cmd *cmd, uint32_t li, uint32
     brasa_arg act;
     if (half_io) {
         BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), tokens, H, c.eps));
-        BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), A(m->xh), tokens));
-        act = A(m->xh);
+        // one fused launch writes the f16 activations while X is still being read: they go to the (then unused) up buffer
+        act = brasa_gemm_swiglu_fuses(l.gate.q, l.up.q, tokens) ? A(m->up) : A(m->xh);
+        BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), act, tokens));
     } else {
         BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.ffn_norm), A(m->norm_out), tokens, H, c.eps));
         BRASA_TRY(matmul(m, cmd, l.gate, A(m->norm_out), A(m->gate), tokens, false));

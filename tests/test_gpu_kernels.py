@@ -460,9 +460,12 @@ def test_gemm_f16_and_f32(B, ctx, K, rows, cols):
             break  # one token count is enough for the large shapes
 
 
-def test_gemm_swiglu_equals_unfused(B, ctx, K):
+@pytest.mark.parametrize("tokens", [70, 300])
+def test_gemm_swiglu_equals_unfused(B, ctx, K, tokens):
+    """From 128 tokens on gate and up run as one tensor-core launch whose epilogue forms silu(gate) * up; below, as two
+    GEMMs and the element-wise kernel. Both must give the bits of the unfused sequence."""
     rng = O.Rng(19)
-    rows, cols, tokens = 1024, 512, 70
+    rows, cols = 1024, 512
     graw, uraw = rng.qmatrix(O.Q4_0, rows, cols), rng.qmatrix(O.Q4_0, rows, cols)
     g, _ = tiled(B, ctx, K, "q4_0", graw, rows, cols)
     u, _ = tiled(B, ctx, K, "q4_0", uraw, rows, cols)
