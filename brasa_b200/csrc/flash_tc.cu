@@ -622,8 +622,9 @@ __device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32
 // the sweep that only looked for the row maxima (a second Q K^T per tile) is gone.
 constexpr float ONEPASS_SLACK = 5.545177444f;  // 8 ln 2
 
-template <bool SPLITKV, bool ONEPASS>
-__global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
+// SW softmax warps (8 or 16): 2 or 4 threads per query row, 64 or 32 score columns each; warp SW is the issuing warp.
+template <bool SPLITKV, bool ONEPASS, int SW>
+__global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *ph = smem + 5 * TILE_BYTES, *pl = smem + 6 * TILE_BYTES;
@@ -634,7 +635,9 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     uint8_t *klo = smem + 2 * TILE_BYTES, *vlo = smem + 4 * TILE_BYTES;
     __shared__ uint64_t bar_s[2], bar_k[2], bar_v[2], bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
-    __shared__ float pair_max[2][128];  // ONEPASS: a tile's largest score of each column half, by row
+    __shared__ __half pair_max[4][128];  // ONEPASS: a tile's largest score of each column group, by row (f16: a reference value
+                                         // need not be the exact maximum, only the same for every thread of the row)
+    constexpr int NG = SW / 4, CPT = 128 / NG, NCH = CPT / 32;  // column groups, columns per thread, 32-column chunks per thread
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t qtile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, kh = h / (p.hq / p.hkv);  // longest query tiles first
@@ -659,7 +662,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // Q tile: scale, round to f16, swizzled K-major; rows past the last query are zeros
-    for (uint32_t i = tid; i < 128 * 16; i += 288) {
+    for (uint32_t i = tid; i < 128 * 16; i += 32 * (SW + 1)) {
         const uint32_t r = i >> 4, c8 = (i & 15) * 8;
         uint4 out = make_uint4(0, 0, 0, 0);
         if (r < nq) {
@@ -725,8 +728,8 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     // Warps 0-7 are the softmax: two threads per query row (warp w: rows 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63).
     // Warp 8, one lane, fetches tiles and issues the tensor-core work, so that no softmax warp carries that serial
     // chain; the two sides meet at one block-wide barrier per tile.
-    const bool issuer = tid == 256, softmax = tid < 256;
-    const uint32_t row = (warp & 3) * 32 + lane, chalf = ((warp >> 2) & 1) * 64;
+    const bool issuer = tid == 32 * SW, softmax = tid < 32 * SW;
+    const uint32_t row = (warp & 3) * 32 + lane, cgrp = (warp >> 2) % NG, chalf = cgrp * CPT;
     const uint32_t qpos = p.pos0 + q0 + row;
     const uint32_t trow = ((warp & 3) * 32u) << 16;  // lane field of a tensor-memory address
     float m = -INFINITY, l = 0.0f;
@@ -787,12 +790,10 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                 if (softmax) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-                    if (j < nfree) {
-                        max_chunk<false>(ts, 0, 0, m);
-                        max_chunk<false>(ts + 32, 0, 0, m);
-                    } else {
-                        max_chunk<true>(ts, j * 128 + chalf, qpos, m);
-                        max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, m);
+#pragma unroll
+                    for (int cc = 0; cc < NCH; ++cc) {
+                        if (j < nfree) max_chunk<false>(ts + 32 * cc, 0, 0, m);
+                        else max_chunk<true>(ts + 32 * cc, j * 128 + chalf + 32 * cc, qpos, m);
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
@@ -803,9 +804,11 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
         // the two halves of a row agree on its maximum (the P tiles are not in use yet)
         {
             float *stat = reinterpret_cast<float *>(ph);
-            if (softmax) stat[(warp >> 2) * 128 + row] = m;
+            if (softmax) stat[cgrp * 128 + row] = m;
             __syncthreads();
-            m = fmaxf(stat[row], stat[128 + row]);
+            m = stat[row];
+#pragma unroll
+            for (int g = 1; g < NG; ++g) m = fmaxf(m, stat[g * 128 + row]);
             __syncthreads();
         }
     }
@@ -827,7 +830,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
             issue_s(KB(j + 1), (j + 1) & 1);
         }
         ok = wait_s(j);
-        uint32_t hi[2][16], lo[2][16];
+        uint32_t hi[NCH][16], lo[NCH][16];
         if (ok) {
             if (issuer && !SPLITKV && j + 2 < nkt) fetch_k(j + 2);
             if (issuer && SPLITKV && j + 1 < nkt) fetch_k(j + 1);
@@ -839,16 +842,16 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                 if (ONEPASS) {
                     // this tile's largest score of the row: own 64 columns, then the other half's through shared memory
                     float tmax = -INFINITY;
-                    if (j < nfree) {
-                        max_chunk<false>(ts, 0, 0, tmax);
-                        max_chunk<false>(ts + 32, 0, 0, tmax);
-                    } else {
-                        max_chunk<true>(ts, j * 128 + chalf, qpos, tmax);
-                        max_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, tmax);
+#pragma unroll
+                    for (int cc = 0; cc < NCH; ++cc) {
+                        if (j < nfree) max_chunk<false>(ts + 32 * cc, 0, 0, tmax);
+                        else max_chunk<true>(ts + 32 * cc, j * 128 + chalf + 32 * cc, qpos, tmax);
                     }
-                    pair_max[(warp >> 2) & 1][row] = tmax;
-                    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");  // the two warps that share these rows
-                    tmax = fmaxf(tmax, pair_max[((warp >> 2) & 1) ^ 1][row]);
+                    pair_max[cgrp][row] = __float2half_rn(tmax);
+                    asm volatile("bar.sync %0, %1;" ::"r"(1 + (warp & 3)), "r"(32 * NG) : "memory");  // the warps that share these rows
+                    tmax = -INFINITY;
+#pragma unroll
+                    for (int g = 0; g < NG; ++g) tmax = fmaxf(tmax, __half2float(pair_max[g][row]));
                     if (tmax > m + ONEPASS_SLACK || (m == -INFINITY && tmax != -INFINITY)) {
                         move = m != -INFINITY;
                         rescale = move ? ex2_approx((m - tmax) * 1.4426950408889634f) : 1.0f;
@@ -857,12 +860,10 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                         mneg = -m * 1.4426950408889634f;
                     }
                 }
-                if (j < nfree) {
-                    prob_chunk<false>(ts, 0, 0, mneg, l, hi[0], lo[0]);
-                    prob_chunk<false>(ts + 32, 0, 0, mneg, l, hi[1], lo[1]);
-                } else {
-                    prob_chunk<true>(ts, j * 128 + chalf, qpos, mneg, l, hi[0], lo[0]);
-                    prob_chunk<true>(ts + 32, j * 128 + chalf + 32, qpos, mneg, l, hi[1], lo[1]);
+#pragma unroll
+                for (int cc = 0; cc < NCH; ++cc) {
+                    if (j < nfree) prob_chunk<false>(ts + 32 * cc, 0, 0, mneg, l, hi[cc], lo[cc]);
+                    else prob_chunk<true>(ts + 32 * cc, j * 128 + chalf + 32 * cc, qpos, mneg, l, hi[cc], lo[cc]);
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
@@ -876,7 +877,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
                 // complete, P V of tile j not yet issued); each half of the pair scales its own 64 dims
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (uint32_t c = chalf; c < chalf + 64; c += 32) {
+                for (uint32_t c = chalf; c < chalf + CPT; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(tmem_o + trow + c, v);
 #pragma unroll
@@ -899,7 +900,7 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
             }
             if (softmax) {
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
+                for (int cc = 0; cc < NCH; ++cc) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {  // four 16-byte chunks of 8 keys
                         const uint32_t off = tile_chunk(row, chalf + 32 * cc + 8 * g);
@@ -935,13 +936,15 @@ __global__ void __launch_bounds__(288, 1) flash_tc_f16_kernel(const __grid_const
     ok = __syncthreads_and(ok);  // the last P V has finished: the P tiles are free
     if (ok) {
         float *stat = reinterpret_cast<float *>(ph);  // [2][128] row sums of the two column halves
-        if (softmax) stat[(warp >> 2) * 128 + row] = l;
+        if (softmax) stat[cgrp * 128 + row] = l;
         __syncthreads();
-        l = stat[row] + stat[128 + row];
+        l = stat[row];
+#pragma unroll
+        for (int g = 1; g < NG; ++g) l += stat[g * 128 + row];
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = 1.0f / l;
 #pragma unroll 1
-        for (uint32_t c = chalf; softmax && c < chalf + 64; c += 32) {
+        for (uint32_t c = chalf; softmax && c < chalf + CPT; c += 32) {
             uint32_t v[32];
             tmem_ld32(tmem_o + trow + c, v);
             if (row < nq) {
@@ -1036,17 +1039,23 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
         const size_t smem = 7 * TILE_BYTES + 1024;
         static bool done = false;
         if (!done) {
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             done = true;
         }
         static const bool onepass = [] { const char *e = getenv("BRASA_FLASH_ONEPASS"); return !(e && e[0] == '0'); }();
-        if (split && onepass) flash_tc_f16_kernel<true, true><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else if (split) flash_tc_f16_kernel<true, false><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else if (onepass) flash_tc_f16_kernel<false, true><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else flash_tc_f16_kernel<false, false><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        static const bool wide = [] { const char *e = getenv("BRASA_FLASH_WARPS"); return e && atoi(e) == 16; }();
+        if (onepass && wide) {
+            if (split) flash_tc_f16_kernel<true, true, 16><<<grid, 544, smem, ctx->stream>>>(maps, p);
+            else flash_tc_f16_kernel<false, true, 16><<<grid, 544, smem, ctx->stream>>>(maps, p);
+        } else if (split && onepass) flash_tc_f16_kernel<true, true, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else if (split) flash_tc_f16_kernel<true, false, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else if (onepass) flash_tc_f16_kernel<false, true, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
+        else flash_tc_f16_kernel<false, false, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
         return brasa_post_launch(cmd, "flash_tc_f16");
     }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
