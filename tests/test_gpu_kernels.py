@@ -539,19 +539,24 @@ def test_gemm_tensor_core_token_counts(B, ctx, K, rows, cols):
         assert np.max(np.abs(got - want16) / s16) <= 1e-5, tokens
 
 
-@pytest.mark.parametrize("tokens,pos0", [(512, 0), (300, 77), (129, 255)])
-def test_flash_attention_tensor_core_many_query_tiles(B, ctx, K, tokens, pos0):
-    """The tcgen05 prefill attention (F16 precision over an f16 cache) with several 128-query tiles, ragged last
-    tiles and key ranges that start before the queries; bound of the reference's attention test."""
+@pytest.mark.parametrize("kv", ["F16", "Q8_0"])
+@pytest.mark.parametrize("tokens,pos0", [(512, 0), (300, 77), (129, 255), (200, 1500)])
+def test_flash_attention_tensor_core_many_query_tiles(B, ctx, K, tokens, pos0, kv):
+    """The tcgen05 prefill attention (F16 precision over an f16 cache, and over a q8_0 cache expanded to hi + lo f16
+    tiles) with several 128-query tiles, ragged last tiles, key ranges that start before the queries and rows whose
+    reference value moves while O is being accumulated; bound of the reference's attention test."""
     rng = O.Rng(23)
     hq, hkv, dim = 8, 2, 128
     lk = pos0 + tokens
     cap = (lk + 63) // 64 * 64
     q = rng.vec(tokens * hq * dim, 2.0)
-    gk, gv, k, v = make_cache(B, ctx, B.KvType.F16, rng.vec(cap * hkv * dim, 2.0), rng.vec(cap * hkv * dim, 3.0))
+    kvt = getattr(B.KvType, kv)
+    kraw = rng.vec(cap * hkv * dim, 2.0)
+    kraw[(lk - 40) * hkv * dim:] *= 4.0  # late keys with much larger scores: the rows' references move after many tiles
+    gk, gv, k, v = make_cache(B, ctx, kvt, kraw, rng.vec(cap * hkv * dim, 3.0))
     want16, vmax = O.attention(q, k, v, tokens, hq, hkv, dim, pos0, q16=True)
     gq, goh = ctx.buffer_from(q), ctx.buffer(q.size * 2)
-    shape = B.AttnShape(tokens, hq, hkv, dim, pos0, B.KvType.F16)
+    shape = B.AttnShape(tokens, hq, hkv, dim, pos0, kvt)
     run(ctx, lambda c: K.flash_attention(c, gq, gk, gv, goh, shape))
     oh = goh.download(np.float16).astype(np.float32)
     d = np.maximum(np.abs(oh - want16) - np.abs(want16) * 2.0 ** -11, 0.0)  # the output's own f16 rounding is discounted
