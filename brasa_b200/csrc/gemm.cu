@@ -184,7 +184,7 @@ bool tc_enabled() {
 // does not overlap the input). The model then hands it a separate output buffer.
 bool brasa_gemm_swiglu_fuses(const brasa_qmatrix &wg, const brasa_qmatrix &wu, uint32_t tokens) {
     static const bool fuse = [] { const char *e = getenv("BRASA_GEMM_GLU"); return !(e && e[0] == '0'); }();
-    return fuse && tc_enabled() && tokens >= 128 && wg.rows == wu.rows && wg.cols == wu.cols && wg.qtype >= BRASA_Q4_0 && wg.qtype <= BRASA_Q6_0 &&
+    return fuse && tc_enabled() && tokens >= 128 && wg.rows == wu.rows && wg.cols == wu.cols && wg.qtype == BRASA_Q4_0 && wu.qtype == BRASA_Q4_0 &&
            qm_fits(wg) && qm_fits(wu) && brasa_gemm_tc_supported(wg, tokens) && brasa_gemm_tc_supported(wu, tokens);
 }
 
@@ -239,7 +239,7 @@ int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t cou
     // one tensor-core launch for all of them when every matrix qualifies
     bool all_tc = precision == BRASA_PREFILL_F16 && tc_enabled() && tokens > 8;
     for (uint32_t i = 0; i < count && all_tc; ++i)
-        all_tc = brasa_gemm_tc_supported(ws[i], tokens) && ws[i].cols == ws[0].cols && qm_fits(ws[i]) &&
+        all_tc = brasa_gemm_tc_supported(ws[i], tokens) && (count == 1 || ws[i].qtype == BRASA_Q4_0) && ws[i].cols == ws[0].cols && qm_fits(ws[i]) &&
                  arg_fits(x, (uint64_t)tokens * ws[i].cols * 2) && arg_fits(ys[i], (uint64_t)tokens * ws[i].rows * 4) && ys[i].offset % 16 == 0;
     if (all_tc && x.offset % 16 == 0) {
         float *yp[3] = {nullptr, nullptr, nullptr};

@@ -49,8 +49,8 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ __half2 u2h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 __device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 // two nibbles (already in the low 4 bits of each half lane) -> f16(d * (q - 8)) for both
-__device__ __forceinline__ uint32_t deq2(uint32_t lanes, __half2 bias, __half2 d2) {
-    return h22u(__hmul2(__hsub2(u2h2((lanes & 0x000F000Fu) | 0x64006400u), bias), d2));
+__device__ __forceinline__ uint32_t deq2(uint32_t lanes, __half2 bias, __half2 d2, uint32_t mask = 0x000F000Fu) {
+    return h22u(__hmul2(__hsub2(u2h2((lanes & mask) | 0x64006400u), bias), d2));
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -87,7 +87,9 @@ constexpr uint32_t RAW_TILE = BN * 32;  // codes of one stage for 128 rows; as m
 // weight traffic decides, and per-thread 16-byte loads from 128 different rows keep too few bytes in flight); otherwise
 // every conversion thread loads its codes straight from global memory one stage of its group ahead (many tokens: the
 // ring is only two stages deep and a weight tile that waits for a free slot before it even leaves L2 would stall it).
-template <int MT, int G, int NB, bool RAW>
+// QT: q4_0, or q6_0 (the tied lm_head of a batch step; direct loads only): the codes' two high bits come from the row's
+// high-bit words, laid out so that one shift per quad of codes puts them at bits 4-5 of the bytes (see brasa_internal.h).
+template <int MT, int G, int NB, bool RAW, int QT = BRASA_Q4_0>
 __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ WeightMaps wmaps,
                                                          GemmTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -216,10 +218,11 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         constexpr uint32_t GT = 256 / G;  // threads of a group
         const uint32_t dt = tid - 128, grp = dt / GT, gt = dt % GT;
         constexpr int UN = G * NB;  // units of a thread per stage
-        const uint32_t row_bytes = tiled_row_bytes(BRASA_Q4_0, p.cols), sc_off = tiled_scale_off(BRASA_Q4_0, p.cols);
+        const uint32_t row_bytes = tiled_row_bytes(QT, p.cols), sc_off = tiled_scale_off(QT, p.cols), hi_off = tiled_hi_off(p.cols);
         uint32_t soff[UN], roff[UN];
         const uint8_t *wp[UN];
         const uint8_t *sp[UN];
+        const uint8_t *hp[UN];  // q6_0: the unit's two high-bit words (8 bytes per block behind the row's codes)
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = gt + i * GT, wr = u & (BNT - 1), blk = u / BNT;
@@ -229,8 +232,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             const uint32_t grow = glu ? n0 + (wr & (BN - 1)) : n0 + wr;
             wp[i] = wbase + (size_t)grow * row_bytes + blk * 16 + (size_t)kbeg * 32;
             sp[i] = wbase + (size_t)grow * row_bytes + sc_off + blk * 2 + (size_t)kbeg * 4;
+            hp[i] = wbase + (size_t)grow * row_bytes + hi_off + blk * 8 + (size_t)kbeg * 16;
         }
         uint4 cwq[UN];
+        uint2 hwq[UN];
         unsigned short scq[UN];
         if (!RAW) {
             const uint32_t kj = min(grp, nk - 1);
@@ -238,12 +243,14 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             for (int i = 0; i < UN; ++i) {
                 cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kj * 32);
                 scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kj * 4);
+                if (QT == BRASA_Q6_0) hwq[i] = *reinterpret_cast<const uint2 *>(hp[i] + (size_t)kj * 16);
             }
         }
         bool ok = true;
         for (uint32_t k = grp; k < nk && ok; k += G) {
             const uint32_t s = k % NS;
             uint4 cw[UN];
+            uint2 hw[UN];
             unsigned short sc[UN];
             if (RAW) {
                 ok = wait(&full_x[s], (k / NS) & 1);  // the stage's raw weights have landed (its slot was free before they were sent)
@@ -263,6 +270,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                     sc[i] = scq[i];
                     cwq[i] = *reinterpret_cast<const uint4 *>(wp[i] + (size_t)kn * 32);
                     scq[i] = *reinterpret_cast<const unsigned short *>(sp[i] + (size_t)kn * 4);
+                    if (QT == BRASA_Q6_0) {
+                        hw[i] = hwq[i];
+                        hwq[i] = *reinterpret_cast<const uint2 *>(hp[i] + (size_t)kn * 16);
+                    }
                 }
                 if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
                 if (!ok) break;
@@ -273,19 +284,25 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                 const uint32_t r8 = soff[i] >> 20, blk = (soff[i] >> 16) & 1;
                 uint8_t *brow = btile + (soff[i] & 0xffffu);
                 const __half2 d2 = __half2half2(__ushort_as_half(sc[i]));
-                const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6408));  // 1032
+                const __half2 bias = __half2half2(__ushort_as_half((unsigned short)(QT == BRASA_Q6_0 ? 0x6420 : 0x6408)));  // 1024 + 32 or + 8
+                constexpr uint32_t cmask = QT == BRASA_Q6_0 ? 0x003F003Fu : 0x000F000Fu;
                 const uint32_t words[4] = {cw[i].x, cw[i].y, cw[i].z, cw[i].w};
                 // elements 0..15 are the low nibbles of bytes 0..15, elements 16..31 the high nibbles
                 uint32_t lo[8], hi[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t wv = words[j], wh = wv >> 4;
+                    uint32_t wv = words[j] & 0x0F0F0F0Fu, wh = (words[j] >> 4) & 0x0F0F0F0Fu;
+                    if (QT == BRASA_Q6_0) {  // bits 4-5 of every code: one shift of the pair's high-bit word per quad of codes
+                        const uint32_t h = j < 2 ? hw[i].x : hw[i].y;
+                        wv |= ((j & 1) ? (h << 2) : h) & 0x30303030u;
+                        wh |= ((j & 1) ? (h << 4) : (h >> 2)) & 0x30303030u;
+                    }
                     const uint32_t p01 = __byte_perm(wv, 0, 0x4140), p23 = __byte_perm(wv, 0, 0x4342);  // bytes (0, 1) and (2, 3) into half lanes
                     const uint32_t q01 = __byte_perm(wh, 0, 0x4140), q23 = __byte_perm(wh, 0, 0x4342);
-                    lo[2 * j] = deq2(p01, bias, d2);
-                    lo[2 * j + 1] = deq2(p23, bias, d2);
-                    hi[2 * j] = deq2(q01, bias, d2);
-                    hi[2 * j + 1] = deq2(q23, bias, d2);
+                    lo[2 * j] = deq2(p01, bias, d2, cmask);
+                    lo[2 * j + 1] = deq2(p23, bias, d2, cmask);
+                    hi[2 * j] = deq2(q01, bias, d2, cmask);
+                    hi[2 * j + 1] = deq2(q23, bias, d2, cmask);
                 }
                 // four 16-byte chunks of the row: columns 8c .. 8c + 7 of this block at chunk (4 blk + c) ^ (row & 7)
                 *reinterpret_cast<uint4 *>(brow + (((4 * blk + 0) ^ r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -452,7 +469,7 @@ EncodeTiledFn encode_tiled() {
 
 // True when the tensor-core kernel takes this product (the caller falls back to the warp-MMA kernel otherwise).
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
-    return w.qtype == BRASA_Q4_0 && w.layout == BRASA_LAYOUT_TILED && w.rows % BN == 0 && w.cols % BK == 0 && w.cols >= BK && tokens > 0 &&
+    return (w.qtype == BRASA_Q4_0 || w.qtype == BRASA_Q6_0) && w.layout == BRASA_LAYOUT_TILED && w.rows % BN == 0 && w.cols % BK == 0 && w.cols >= BK && tokens > 0 &&
            encode_tiled() != nullptr;
 }
 
@@ -506,10 +523,17 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
             }
         }
     }
+    const bool q6 = ws[0].qtype == BRASA_Q6_0;
+    for (uint32_t i = 0; i < count; ++i) BRASA_REQUIRE(ctx, (ws[i].qtype == BRASA_Q6_0) == q6, "gemm: q4_0 and q6_0 matrices cannot share a launch");
+    BRASA_REQUIRE(ctx, !q6 || (count == 1 && !glu), "gemm: a q6_0 matrix goes alone");
+    if (q6) {  // one token tile, 128 rows, direct loads: the shape the q6_0 conversion is built for
+        mt = 1;
+        nb = 1;
+    }
     {   // BRASA_GEMM_SHAPE=mt,nb forces the CTA shape (A/B runs); ignored when the matrices do not allow it
         static const char *force = getenv("BRASA_GEMM_SHAPE");
         unsigned fm = 0, fn = 0;
-        if (force && sscanf(force, "%u,%u", &fm, &fn) == 2 && (fm == 1 || fm == 2 || fm == 4) && (fn == 1 || (fn == 2 && rows256)) && fm * fn <= 4) {
+        if (!q6 && force && sscanf(force, "%u,%u", &fm, &fn) == 2 && (fm == 1 || fm == 2 || fm == 4) && (fn == 1 || (fn == 2 && rows256)) && fm * fn <= 4) {
             mt = fm;
             nb = fn;
             ksplit = 1;
@@ -542,7 +566,7 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
     // the weight matrices as byte tensors [rows][row_bytes]: box = 32 bytes x this CTA's rows, no swizzle
-    const bool raw = mt == 1 && nb == 1;  // weight bytes through TMA when one token tile per CTA leaves the weights as the main traffic
+    const bool raw = mt == 1 && nb == 1 && !q6;  // weight bytes through TMA when one token tile per CTA leaves the weights as the main traffic
     WeightMaps wmaps;
     memset(&wmaps, 0, sizeof wmaps);
     for (uint32_t i = 0; raw && i < 3; ++i) {
@@ -595,7 +619,14 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         gemm_tc_kernel<MTV, GV, NBV, RAWV><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);                                                         \
     } while (0)
     // conversion groups: as many stages in flight as the ring holds, at most four
-    if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1, true);
+    if (q6) {
+        static bool done6 = false;
+        if (!done6) {
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048));
+            done6 = true;
+        }
+        gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);
+    } else if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1, true);
     else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1, false);
     else if (nb == 1) LAUNCH_TC(4, 2, 1, false);
     else if (mt == 1) LAUNCH_TC(1, 2, 2, false);

@@ -501,6 +501,23 @@ def test_gemm_add_equals_gemm_then_add(B, ctx, K, rows, cols, tokens):
     assert np.array_equal(ga.download(np.float32), gb.download(np.float32))
 
 
+@pytest.mark.parametrize("tokens", [16, 200])
+def test_gemm_tiled_q6_tensor_core(B, ctx, K, tokens):
+    """A tiled q6_0 matrix whose rows are a multiple of 128 (the tied lm_head of a batch step) runs on the tcgen05 GEMM:
+    codes rebuilt from the nibbles and the high-bit words, same bound as every GEMM."""
+    rows, cols = 1280, 2560
+    rng = O.Rng(47)
+    raw = rng.qmatrix(O.Q6_0, rows, cols)
+    m = tiled(B, ctx, K, "q6_0", raw, rows, cols)[0]
+    x = rng.vec(tokens * cols, 1.0)
+    xh = x.astype(np.float16)
+    want16, s16 = O.matmul(O.Q6_0, raw, rows, cols, x, f16_inputs=True)
+    gxh, gy = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4)
+    run(ctx, lambda c: K.gemm(c, m, gxh, gy, tokens))
+    got = gy.download(np.float32).reshape(tokens, rows)
+    assert np.max(np.abs(got - want16) / s16) <= 1e-5
+
+
 # ---- argmax --------------------------------------------------------------------------------------
 
 def test_argmax_edge_cases(ctx, K):
