@@ -302,7 +302,7 @@ static int32_t rms_norm_common(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_a
     uint64_t tot = (uint64_t)rows * n;
     BRASA_REQUIRE(ctx, n > 0 && arg_fits(x, tot * 4) && arg_fits(w, (uint64_t)n * 4) && arg_fits(out, tot * (half_out ? 2 : 4)), "rms_norm: buffers too small");
     if (rows == 0) return BRASA_OK;
-    if (rows >= 16 && n % 128 == 0 && n <= 128 * RMS_MAX_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
+    if (rows >= 256 && n % 128 == 0 && n <= 128 * RMS_MAX_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
         const unsigned blocks = (rows + 1) / 2;
         if (half_out) rms_norm_rows_kernel<true><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
         else rms_norm_rows_kernel<false><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);

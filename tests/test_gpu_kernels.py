@@ -113,7 +113,7 @@ def test_add_and_swiglu(B, ctx, K):
         run(ctx, lambda c: K.add(c, ga, gb, go, n + 1))
 
 
-@pytest.mark.parametrize("rows,n", [(1, 2560), (37, 2560), (2048, 128), (3, 100)])
+@pytest.mark.parametrize("rows,n", [(1, 2560), (37, 2560), (301, 2560), (2048, 128), (3, 100)])
 def test_rms_norm(ctx, K, rows, n):
     rng = O.Rng(11)
     x, w = rng.vec(rows * n, 3.0), rng.vec(n, 2.0)
