@@ -253,7 +253,12 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
             uint2 hw[UN];
             unsigned short sc[UN];
             if (RAW) {
-                ok = wait(&full_x[s], (k / NS) & 1);  // the stage's raw weights have landed (its slot was free before they were sent)
+                // A parity wait cannot tell a phase from the one two before it. The copies of stage k - NS (same slot) may land
+                // after those of a later stage this group has already converted, and a wait for "stage k has landed" entered
+                // before that would then return at once. So first the slot's previous use must be over (its MMAs complete: that
+                // wait is never two phases behind because a group's previous stage is less than NS stages back), then the landing.
+                if (k >= NS) ok = wait(&empty[s], ((k / NS) - 1) & 1);
+                ok = ok && wait(&full_x[s], (k / NS) & 1);
                 if (!ok) break;
                 const uint8_t *raw = smem + (size_t)s * stage_bytes + MT * A_TILE + NB * B_TILE;
                 const uint8_t *rsc = raw + NB * RAW_TILE + ((kbeg + k) & 7) * 4;
