@@ -32,7 +32,9 @@ HERE = pathlib.Path(__file__).resolve().parent
 
 
 def main() -> None:
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of a checkout of the reference repository>")
+    ref = pathlib.Path(sys.argv[1])
     sys.path.insert(0, str(ref / "tools"))
     import brasa_file
     import convert_brasa
