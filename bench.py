@@ -280,7 +280,7 @@ def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048
     V = cfg["vocab_size"]
     page, warm = B.Batch.PAGE, 4
     positions = (prefix + suffix + warm + steps + 1 + page - 1) // page * page  # the most one sequence ever holds
-    m = B.Qwen3.load(ctx, path, B.Limits(ctx=positions, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=positions, max_tokens=suffix, max_logit_rows=1, kv=B.KvType.F16))  # a sequence's own prompt is one chunk
     own_pages = (positions - prefix) // page
     batch = B.Batch(m, seqs, prefix // page + seqs * own_pages + 8, positions)
     try:
