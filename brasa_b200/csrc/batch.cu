@@ -321,7 +321,8 @@ __global__ void __launch_bounds__(128) decode_reduce_paged_kernel(const float *p
     float M = -INFINITY;
     for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, p[c * 130]);
     float L = 0.0f, acc = 0.0f;
-    for (uint32_t c = 0; c < chunks; ++c) {
+#pragma unroll 4
+    for (uint32_t c = 0; c < chunks; ++c) {  // (unrolled: the chunks' loads are independent, only the sums are a chain)
         float w = expf(p[c * 130] - M);
         L = fmaf(p[c * 130 + 1], w, L);
         acc = fmaf(p[c * 130 + 2 + t], w, acc);

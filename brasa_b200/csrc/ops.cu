@@ -93,6 +93,45 @@ __global__ void __launch_bounds__(64) rms_norm_rows_kernel(const float *x, const
     }
 }
 
+// One block of 128 threads per row, the row in registers (n a multiple of 512, at most 512 * RMS_BLOCK_CHUNKS): one pass with
+// 16-byte loads and one block barrier. For few rows (a decode step of a batch), where the row count cannot hide latency.
+constexpr int RMS_BLOCK_CHUNKS = 10;
+template <bool HALF_OUT>
+__global__ void __launch_bounds__(128) rms_norm_block_kernel(const float *x, const float *w, void *out, uint32_t n, float eps) {
+    __shared__ float red[4];
+    const uint32_t t = threadIdx.x, chunks = n / 512;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)blockIdx.x * n);
+    float4 v[RMS_BLOCK_CHUNKS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < RMS_BLOCK_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            v[c] = xr[c * 128 + t];
+            ss += (v[c].x * v[c].x + v[c].y * v[c].y) + (v[c].z * v[c].z + v[c].w * v[c].w);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((t & 31) == 0) red[t >> 5] = ss;
+    __syncthreads();
+    ss = (red[0] + red[1]) + (red[2] + red[3]);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    const float4 *wr = reinterpret_cast<const float4 *>(w);
+#pragma unroll
+    for (int c = 0; c < RMS_BLOCK_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            const float4 ww = wr[c * 128 + t];
+            const float a = v[c].x * scale * ww.x, b = v[c].y * scale * ww.y, cc = v[c].z * scale * ww.z, d = v[c].w * scale * ww.w;
+            if (HALF_OUT) {
+                const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(cc, d);
+                reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(out) + (size_t)blockIdx.x * n)[c * 128 + t] =
+                    make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+            } else {
+                reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)blockIdx.x * n)[c * 128 + t] = make_float4(a, b, cc, d);
+            }
+        }
+    }
+}
+
 __global__ void softmax_kernel(const float *x, float *out, uint32_t n) {
     __shared__ float red[32];
     const float *xr = x + (size_t)blockIdx.x * n;
@@ -306,6 +345,11 @@ static int32_t rms_norm_common(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_a
         const unsigned blocks = (rows + 1) / 2;
         if (half_out) rms_norm_rows_kernel<true><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
         else rms_norm_rows_kernel<false><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        return brasa_post_launch(cmd, "rms_norm");
+    }
+    if (rows >= 2 && n % 512 == 0 && n <= 512 * RMS_BLOCK_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
+        if (half_out) rms_norm_block_kernel<true><<<rows, 128, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
+        else rms_norm_block_kernel<false><<<rows, 128, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
         return brasa_post_launch(cmd, "rms_norm");
     }
     unsigned threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 32);
