@@ -366,36 +366,51 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                 }
             }
         } else if (ok) {
+            // A lane of tensor memory is a token, so a thread holds one token's values and a warp's store would touch 32
+            // rows of Y at once (32 cache lines per instruction). Each warp therefore turns 32 tokens x 32 columns around in
+            // a private piece of shared memory (the stage ring is idle by now: every MMA has completed) and stores with eight
+            // lanes per token: four full 128-byte lines per instruction. The residual is read the same way.
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3;           // the lane quarter of tensor memory this warp may read
             const int c_begin = ((warp - 4) >> 2) * (BNT / 2);  // two warps per quarter: half of the columns each
+            float *tb = reinterpret_cast<float *>(smem) + (warp - 4) * (32 * 33);  // [32 tokens][32 columns + 1]
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t token = tok0 + mt * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int c = c_begin; c < c_begin + (int)BNT / 2; c += 16) {
-                    uint32_t v[16];
+                for (int c = c_begin; c < c_begin + (int)BNT / 2; c += 32) {
+                    uint32_t v[32];
                     const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BNT + c;
                     asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+                        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-                          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                         : "r"(taddr)
                         : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (token < p.tokens) {
-                        float4 *dst = ptile ? reinterpret_cast<float4 *>(ptile + (size_t)(mt * BM + q * 32 + lane) * BNT + c)
-                                            : reinterpret_cast<float4 *>(ymat + (size_t)token * yrows + n0 + c);
-                        const float4 *add = (!ptile && p.resid) ? reinterpret_cast<const float4 *>(p.resid + (size_t)token * yrows + n0 + c) : nullptr;
+                    __syncwarp();  // the previous round's reads of tb are done
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
-                                                   __uint_as_float(v[4 * i + 3]));
-                            if (add) {
-                                const float4 r = add[i];
-                                o = make_float4(r.x + o.x, r.y + o.y, r.z + o.z, r.w + o.w);
+                    for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = __uint_as_float(v[i]);
+                    __syncwarp();
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const uint32_t f = lane + 32 * r, trow = f >> 3, c4 = f & 7;  // token of the warp's 32, group of four columns
+                        const uint32_t tl = mt * BM + q * 32 + trow, token = tok0 + tl;
+                        if (token < p.tokens) {
+                            const float *src = tb + trow * 33 + 4 * c4;
+                            float4 o = make_float4(src[0], src[1], src[2], src[3]);
+                            if (ptile) {
+                                *reinterpret_cast<float4 *>(ptile + (size_t)tl * BNT + c + 4 * c4) = o;
+                            } else {
+                                const size_t at = (size_t)token * yrows + n0 + c + 4 * c4;
+                                if (p.resid) {
+                                    const float4 rr = *reinterpret_cast<const float4 *>(p.resid + at);
+                                    o = make_float4(rr.x + o.x, rr.y + o.y, rr.z + o.z, rr.w + o.w);
+                                }
+                                *reinterpret_cast<float4 *>(ymat + at) = o;
                             }
-                            dst[i] = o;
                         }
                     }
                 }
