@@ -326,42 +326,51 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
         const uint32_t tile_elems = MT * BM * BNT, tile_id = blockIdx.y * gridDim.x + blockIdx.x;
         float *ptile = p.ksplit > 1 ? p.part + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile_id) * tile_elems : nullptr;
         if (ok && glu) {
-            // silu(gate) * up, rounded to f16: columns [0, 128) of a token tile's accumulator are gate's, [128, 256) up's
+            // silu(gate) * up, rounded to f16: columns [0, 128) of a token tile's accumulator are gate's, [128, 256) up's.
+            // As below, 32 tokens x 32 results are turned around in shared memory: four lanes then store one token's 64 bytes.
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q = warp & 3;
             const int c_begin = ((warp - 4) >> 2) * (BN / 2);
+            uint32_t *tb = reinterpret_cast<uint32_t *>(smem) + (warp - 4) * (32 * 17);  // [32 tokens][16 words + 1]
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t token = tok0 + mt * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int c = c_begin; c < c_begin + BN / 2; c += 16) {
-                    uint32_t g[16], u[16];
-                    const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BNT + c;
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                        : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]),
-                          "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15])
-                        : "r"(taddr)
-                        : "memory");
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
-                          "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
-                        : "r"(taddr + BN)
-                        : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (token < p.tokens) {
-                        uint32_t packed[8];
+                for (int c = c_begin; c < c_begin + BN / 2; c += 32) {
+                    __syncwarp();  // the previous round's reads of tb are done
+#pragma unroll 1
+                    for (int sub = 0; sub < 2; ++sub) {
+                        uint32_t g[16], u[16];
+                        const uint32_t taddr = tmem_base + ((q * 32u) << 16) + mt * BNT + c + 16 * sub;
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                            : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]),
+                              "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15])
+                            : "r"(taddr)
+                            : "memory");
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                            : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
+                              "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+                            : "r"(taddr + BN)
+                            : "memory");
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int i = 0; i < 16; i += 2) {
                             const float g0 = __uint_as_float(g[i]), g1 = __uint_as_float(g[i + 1]);
                             const float v0 = (g0 / (1.0f + expf(-g0))) * __uint_as_float(u[i]), v1 = (g1 / (1.0f + expf(-g1))) * __uint_as_float(u[i + 1]);
                             const __half2 hh = __floats2half2_rn(v0, v1);
-                            packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                            tb[lane * 17 + 8 * sub + (i >> 1)] = *reinterpret_cast<const uint32_t *>(&hh);
                         }
-                        uint4 *dst = reinterpret_cast<uint4 *>(p.glu + (size_t)token * yrows + n0 + c);
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t f = lane + 32 * r, trow = f >> 2, q4 = f & 3;  // token of the warp's 32, group of eight results
+                        const uint32_t token = tok0 + mt * BM + q * 32 + trow;
+                        if (token < p.tokens) {
+                            const uint32_t *src = tb + trow * 17 + 4 * q4;
+                            *reinterpret_cast<uint4 *>(p.glu + (size_t)token * yrows + n0 + c + 8 * q4) = make_uint4(src[0], src[1], src[2], src[3]);
+                        }
                     }
                 }
             }
