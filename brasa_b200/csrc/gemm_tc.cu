@@ -538,10 +538,10 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         for (uint32_t c = 1; c * b <= 4 && c <= std::max(1u, ntile); c *= 2) {
             const uint32_t ctas = (tiles128 / b) * ((ntile + c - 1) / c);
             uint32_t ks = 1;
-            if (split_on && c == 1 && b == 1 && ctas * 2 <= (uint32_t)ctx->sm_count && ctas <= GEMM_TC_COUNTERS)
+            if (split_on && c * b <= 2 && ctas * 2 <= (uint32_t)ctx->sm_count && ctas <= GEMM_TC_COUNTERS)
                 ks = std::max(1u, std::min((uint32_t)ctx->sm_count / ctas, nkst / 8));
             const double waves = std::ceil((double)ctas * ks / ctx->sm_count);
-            const double pipe = waves * ((nkst + ks - 1) / ks) * (300.0 * c * b + 400.0) + (ks > 1 ? 4000.0 : 0.0);
+            const double pipe = waves * ((nkst + ks - 1) / ks) * (300.0 * c * b + 400.0) + (ks > 1 ? 4000.0 + 3000.0 * ks * c * b : 0.0);  // + the last CTA's sum over ks partial tiles
             const double xbytes = (double)ctas * c * BM * ws[0].cols * 2.0;
             const double cost = std::max(pipe, xbytes * 1.965e9 / 4.5e12);
             if (cost < best * 0.999 || (cost < best * 1.001 && c * b > mt * nb)) {

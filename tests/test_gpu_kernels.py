@@ -485,7 +485,7 @@ def test_gemm_swiglu_equals_unfused(B, ctx, K, tokens):
     assert np.all(np.abs(got - want) <= bound)
 
 
-@pytest.mark.parametrize("rows,cols,tokens", [(256, 4096, 16), (1024, 512, 300), (100, 96, 20)])
+@pytest.mark.parametrize("rows,cols,tokens", [(256, 4096, 16), (256, 4096, 300), (1024, 512, 300), (100, 96, 20)])
 def test_gemm_add_equals_gemm_then_add(B, ctx, K, rows, cols, tokens):
     """acc += W x with the add in the GEMM's epilogue (split K, plain tensor-core and generic paths) gives the very
     bits of the GEMM followed by the element-wise add."""
