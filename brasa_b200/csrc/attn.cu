@@ -370,29 +370,35 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedAttnParams 
     if (!last_block) return;
     __threadfence();
     if (t == 0) p.counters[kh] = 0;
-    // merge: weights of all (head, chunk) pairs first (one round trip), then the accumulators with all
-    // loads of a head in flight at once
-    for (uint32_t i = t; i < G * nchunks; i += 128) {
-        uint32_t g = i / nchunks, c = i % nchunks;
-        const float *pp = p.partials + ((size_t)(kh * G + g) * max_chunks + c) * 130;
-        ps[g * 128 + c] = __ldcg(pp);            // m
-        ps[g * 128 + 64 + c] = __ldcg(pp + 1);   // l
-    }
-    __syncthreads();
+    // merge: every thread reads the chunks' maxima and sums straight from the partials (broadcast loads that stay in
+    // L2), so nothing is staged per chunk and the context length is not bounded by shared memory. Two sweeps: the
+    // head's maximum first, then weights and accumulators in chunk order, eight chunks in flight at a time.
     for (uint32_t g = 0; g < G; ++g) {
-        const float *pp = p.partials + (size_t)(kh * G + g) * max_chunks * 130 + 2 + t;
+        const float *ph = p.partials + (size_t)(kh * G + g) * max_chunks * 130;
         float M = -INFINITY;
-        for (uint32_t c = 0; c < nchunks; ++c) M = fmaxf(M, ps[g * 128 + c]);
+        for (uint32_t c0 = 0; c0 < nchunks; c0 += 8) {
+            float mm[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mm[j] = c0 + j < nchunks ? __ldcg(ph + (size_t)(c0 + j) * 130) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) M = fmaxf(M, mm[j]);
+        }
         float L = 0.0f, a = 0.0f;
         for (uint32_t c0 = 0; c0 < nchunks; c0 += 8) {
-            float v[8];
+            float mm[8], ll[8], v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = c0 + j < nchunks ? __ldcg(pp + (size_t)(c0 + j) * 130) : 0.0f;
+            for (int j = 0; j < 8; ++j) {
+                const bool in = c0 + j < nchunks;
+                const float *pc = ph + (size_t)(c0 + j) * 130;
+                mm[j] = in ? __ldcg(pc) : -INFINITY;
+                ll[j] = in ? __ldcg(pc + 1) : 0.0f;
+                v[j] = in ? __ldcg(pc + 2 + t) : 0.0f;
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 if (c0 + j < nchunks) {
-                    float w = expf(ps[g * 128 + c0 + j] - M);
-                    L = fmaf(ps[g * 128 + 64 + c0 + j], w, L);
+                    float w = expf(mm[j] - M);
+                    L = fmaf(ll[j], w, L);
                     a = fmaf(v[j], w, a);
                 }
             }
@@ -408,6 +414,7 @@ int32_t check_decode(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, bras
     BRASA_REQUIRE(ctx, sh.dim == 128, "decode_attention needs head_dim 128");
     BRASA_REQUIRE(ctx, sh.hkv > 0 && sh.hq % sh.hkv == 0 && sh.hq / sh.hkv <= 8, "decode_attention: GQA group must divide and be <= 8");
     BRASA_REQUIRE(ctx, sh.kv >= BRASA_KV_F32 && sh.kv <= BRASA_KV_Q8_0, "unknown KV type %d", sh.kv);
+    BRASA_REQUIRE(ctx, sh.pos0 != 0xffffffffu, "decode_attention: position out of range");
     uint32_t lk = sh.pos0 + 1;
     BRASA_REQUIRE(ctx, partials_len >= brasa_decode_partials_len(sh.hq, lk) && arg_fits(partials, partials_len * 4), "decode scratch too small");
     uint64_t kvb = brasa_kv_bytes(sh.kv, (uint64_t)lk * sh.hkv * 128);
@@ -429,11 +436,7 @@ int32_t decode_common(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, bra
     float *pp = (float *)arg_ptr(partials);
 #define LAUNCH_DEC(KVT)                                                                                                   \
     do {                                                                                                                  \
-        static bool done = false;                                                                                         \
-        if (!done) {                                                                                                      \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-            done = true;                                                                                                  \
-        }                                                                                                                 \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_kernel<KVT>, smem)); \
         decode_partial_kernel<KVT><<<grid, 128, smem, ctx->stream>>>(qp, arg_ptr(k), arg_ptr(v), pp, sh.hq, sh.hkv, lk, scale); \
     } while (0)
     if (sh.kv == BRASA_KV_F32) LAUNCH_DEC(BRASA_KV_F32);
@@ -467,11 +470,7 @@ int32_t brasa_attn_decode_fused_launch(brasa_cmd *cmd, int32_t kv, const float *
 #define LAUNCH_FUSED(KVT)                                                                                                          \
     do {                                                                                                                           \
         size_t smem = 2 * 128 * KvRow<KVT>::STRIDE + (8 * 128 * 2 + 16) * sizeof(float);                                           \
-        static bool done = false;                                                                                                  \
-        if (!done) {                                                                                                               \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(attn_decode_fused_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-            done = true;                                                                                                           \
-        }                                                                                                                          \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)attn_decode_fused_kernel<KVT>, smem)); \
         cfg.dynamicSmemBytes = smem;                                                                                               \
         BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<KVT>, p));                                               \
     } while (0)
@@ -519,11 +518,7 @@ int32_t brasa_k_flash_attention_with(brasa_cmd *cmd, brasa_arg q, brasa_arg k, b
     dim3 grid((sh.tokens + 63) / 64, sh.hq);
 #define LAUNCH_FA(KVT, H)                                                                                                    \
     do {                                                                                                                     \
-        static bool done = false;                                                                                            \
-        if (!done) {                                                                                                         \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<KVT, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-            done = true;                                                                                                     \
-        }                                                                                                                    \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)prefill_attn_kernel<KVT, H>, smem)); \
         prefill_attn_kernel<KVT, H><<<grid, 256, smem, ctx->stream>>>((const float *)arg_ptr(q), arg_ptr(k), arg_ptr(v), arg_ptr(o), sh.tokens, \
                                                                       sh.hq, sh.hkv, sh.pos0, scale);                      \
     } while (0)
@@ -578,11 +573,7 @@ int32_t brasa_k_decode_attention_static(brasa_cmd *cmd, brasa_arg q, brasa_arg k
     const float *qp = (const float *)arg_ptr(q);
 #define LAUNCH_STATIC(KVT)                                                                                                 \
     do {                                                                                                                   \
-        static bool done = false;                                                                                          \
-        if (!done) {                                                                                                       \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-            done = true;                                                                                                   \
-        }                                                                                                                  \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_kernel<KVT>, smem)); \
         decode_partial_kernel<KVT><<<grid, 128, smem, ctx->stream>>>(qp, arg_ptr(k), arg_ptr(v), partials, shape.hq, shape.hkv, lk, scale); \
     } while (0)
     if (shape.kv == BRASA_KV_F32) LAUNCH_STATIC(BRASA_KV_F32);

@@ -390,7 +390,6 @@ struct brasa_batch {
     uint32_t nseq = 0, next_page = 0, prefix_len = 0;
     size_t row_bytes = 0, pool_layer_bytes = 0, cache_layer_bytes = 0;
     uint64_t max_chunks = 0;
-    bool mma_attention = true;  // f16 pool: tensor-core partial kernel (BRASA_BATCH_MMA=0 keeps the scalar one)
     brasa_buf *kpool = nullptr, *vpool = nullptr, *table = nullptr, *lens = nullptr, *ids = nullptr, *rng = nullptr, *logits = nullptr,
               *partials = nullptr, *scratch = nullptr, *out = nullptr;
     std::vector<int32_t> h_table;  // host mirror [max_seqs][max_pages]
@@ -499,11 +498,7 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         void *attn_out = half_io ? m->xh->ptr : m->attn->ptr;
 #define LAUNCH_BATCH(KVT)                                                                                                                        \
     do {                                                                                                                                         \
-        static bool done = false;                                                                                                                \
-        if (!done) {                                                                                                                             \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
-            done = true;                                                                                                                         \
-        }                                                                                                                                        \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_kernel<KVT>, smem)); \
         qk_norm_rope_store_paged_kernel<KVT><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm),   \
                                                                                      F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages,  \
                                                                                      lens, c.heads, c.kv_heads, c.eps, rows);                     \
@@ -513,13 +508,9 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged"));                                                                               \
     } while (0)
         if (m->limits.kv == BRASA_KV_F32) LAUNCH_BATCH(BRASA_KV_F32);
-        else if (m->limits.kv == BRASA_KV_F16 && b->mma_attention) {
-            static bool attr_done = false;
-            if (!attr_done) {
-                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
-                BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_partial_paged_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
-                attr_done = true;
-            }
+        else if (m->limits.kv == BRASA_KV_F16) {
+                BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<false>, MMA_SMEM));
+                BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<true>, MMA_SMEM));
             qk_norm_rope_store_paged_kernel<BRASA_KV_F16><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(
                 F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages, lens, c.heads,
                 c.kv_heads, c.eps, rows);
@@ -596,10 +587,6 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     std::unique_ptr<brasa_batch, void (*)(brasa_batch *)> b(new brasa_batch, brasa_batch_free);
     b->m = m;
     b->ctx = ctx;
-    {
-        const char *e = getenv("BRASA_BATCH_MMA");
-        b->mma_attention = !(e && e[0] == '0');
-    }
     b->max_seqs = max_seqs;
     b->num_pages = num_pages;
     b->max_pages = (max_positions + PAGE - 1) / PAGE;

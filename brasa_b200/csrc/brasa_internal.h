@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/brasa_cuda.h"
@@ -46,8 +47,21 @@ struct brasa_ctx {
     float *gemm_part = nullptr;      // partial output tiles of the split-K tensor-core GEMM
     size_t gemm_part_bytes = 0;
     uint32_t *gemm_counters = nullptr;  // arrivals per output tile of that GEMM (GEMM_TC_COUNTERS words, zero between launches)
-    bool gemv_attr_done[10] = {};  // opt-in shared memory size set on this device, per kernel instance
+    // opt-in dynamic shared memory already granted on this context's device: (kernel, bytes). The attribute belongs to
+    // a (kernel, device) pair, so it is remembered per context, never per process.
+    std::vector<std::pair<const void *, size_t>> smem_granted;
 };
+
+// Makes `bytes` of dynamic shared memory available to kernel `fn` on the context's device (once per context and
+// size; cheap afterwards).
+int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes);
+
+// Phase time stamps of the GEMV and whole-token kernels exist only in builds with -DBRASA_TRACE_BUILD (a
+// developer's build; the shipped library carries neither the stamps nor these entry points).
+#ifdef BRASA_TRACE_BUILD
+extern "C" int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]);
+extern "C" int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n);
+#endif
 
 struct brasa_buf {
     brasa_ctx *ctx;

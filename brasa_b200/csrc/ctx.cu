@@ -24,6 +24,19 @@ int32_t brasa_check_cuda(brasa_ctx *ctx, cudaError_t e, const char *what) {
     return brasa_fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
 }
 
+int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes) {
+    for (auto &g : ctx->smem_granted)
+        if (g.first == fn) {
+            if (g.second >= bytes) return BRASA_OK;
+            BRASA_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+            g.second = bytes;
+            return BRASA_OK;
+        }
+    BRASA_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    ctx->smem_granted.emplace_back(fn, bytes);
+    return BRASA_OK;
+}
+
 extern "C" {
 
 int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
@@ -50,8 +63,10 @@ int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
     cudaMemset(ctx->status, 0, 256);
     const char *env = getenv("BRASA_PDL");
     if (env && env[0] == '0') ctx->pdl = false;
+#ifdef BRASA_TRACE_BUILD
     env = getenv("BRASA_TRACE");
     if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 4096) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 4096);
+#endif
     env = getenv("BRASA_GRAPH");
     if (env && env[0] == '0') ctx->graphs = false;
     env = getenv("BRASA_TOKEN_KERNEL");
@@ -97,6 +112,7 @@ int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total
 
 uint64_t brasa_ctx_launch_count(brasa_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
+#ifdef BRASA_TRACE_BUILD
 int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]) {
     if (!ctx || !out) return BRASA_EINVAL;
     BRASA_REQUIRE(ctx, ctx->gemv_trace, "tracing is off: create the context with BRASA_TRACE=1");
@@ -112,6 +128,8 @@ int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n) {
     BRASA_CUDA(ctx, cudaMemcpy(out, ctx->gemv_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
     return BRASA_OK;
 }
+
+#endif
 
 int32_t brasa_ctx_sync(brasa_ctx *ctx) {
     if (!ctx) return BRASA_EINVAL;

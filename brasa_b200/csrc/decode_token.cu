@@ -155,7 +155,11 @@ __device__ __forceinline__ void embed_half_block(const uint8_t *table, uint32_t 
     }
 }
 
+#ifdef BRASA_TRACE_BUILD
 #define TRACE(i) do { if (c.trace && c.b == 0 && threadIdx.x == 0 && oi >= c.trace_op && oi < c.trace_op + 16) c.trace[16 + (oi - c.trace_op) * 8 + (i)] = (unsigned long long)clock64(); } while (0)
+#else
+#define TRACE(i) do { } while (0)
+#endif
 
 // What the phases of an operation share. The phase functions are inlined: with 227 KB of shared memory in use the
 // L1 cache is a few KB, so a stack frame (calls, spills) costs a trip to L2 per access.
@@ -984,7 +988,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         p.trace_op = env ? (uint32_t)atoi(env) : 5;
     }
 
-#define SET_ATTR(KVT) BRASA_CUDA(ctx, cudaFuncSetAttribute(decode_token_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prog->smem))
+#define SET_ATTR(KVT) BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_token_kernel<KVT>, prog->smem))
     if (m.kv == BRASA_KV_F32) SET_ATTR(BRASA_KV_F32);
     else if (m.kv == BRASA_KV_F16) SET_ATTR(BRASA_KV_F16);
     else SET_ATTR(BRASA_KV_Q8_0);

@@ -615,16 +615,18 @@ __device__ __forceinline__ void prob_chunk(uint32_t taddr, uint32_t key0, uint32
 
 // SPLITKV: K and V come as hi + lo tiles (one buffer each instead of two), S = Q K_hi + Q K_lo and
 // O += P_hi V_hi + P_lo V_hi + P_hi V_lo (lo x lo is below 2^-22).
-// ONEPASS: one sweep over the keys. Each row keeps a reference value m_ref for its exponentials; a tile whose largest
+// One sweep over the keys. Each row keeps a reference value m_ref for its exponentials; a tile whose largest
 // score exceeds m_ref by more than ONEPASS_SLACK (or the first tile) moves the reference to that score, and the row of O
 // accumulated so far and the row sum are multiplied by exp(old - new) in tensor memory before the tile's P V is issued.
 // With the slack such moves are rare after the first tile, probabilities stay below e^slack = 256 (well inside f16), and
-// the sweep that only looked for the row maxima (a second Q K^T per tile) is gone.
+// no separate sweep has to look for the row maxima first (that would be a second Q K^T per tile).
 constexpr float ONEPASS_SLACK = 5.545177444f;  // 8 ln 2
+constexpr int FLASH_SW = 8;
 
-// SW softmax warps (8 or 16): 2 or 4 threads per query row, 64 or 32 score columns each; warp SW is the issuing warp.
-template <bool SPLITKV, bool ONEPASS, int SW>
-__global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
+// SW = 8 softmax warps: 2 threads per query row, 64 score columns each; warp SW is the issuing warp.
+template <bool SPLITKV>
+__global__ void __launch_bounds__(32 * (FLASH_SW + 1), 1) flash_tc_f16_kernel(const __grid_constant__ FlashF16Maps maps, FlashTcParams p) {
+    constexpr int SW = FLASH_SW;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *qt = smem, *ph = smem + 5 * TILE_BYTES, *pl = smem + 6 * TILE_BYTES;
@@ -635,7 +637,7 @@ __global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __
     uint8_t *klo = smem + 2 * TILE_BYTES, *vlo = smem + 4 * TILE_BYTES;
     __shared__ uint64_t bar_s[2], bar_k[2], bar_v[2], bar_o;
     __shared__ uint32_t tmem_base_s, abort_s;
-    __shared__ __half pair_max[4][128];  // ONEPASS: a tile's largest score of each column group, by row (f16: a reference value
+    __shared__ __half pair_max[4][128];  // a tile's largest score of each column group, by row (f16: a reference value
                                          // need not be the exact maximum, only the same for every thread of the row)
     constexpr int NG = SW / 4, CPT = 128 / NG, NCH = CPT / 32;  // column groups, columns per thread, 32-column chunks per thread
 
@@ -759,62 +761,9 @@ __global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __
         return __all_sync(0xffffffffu, r);
     };
 
-    if constexpr (!ONEPASS) {
-        // ---- sweep 1: row maxima ----
-        if (issuer) {
-            fetch_k(0);
-            if (!SPLITKV && nkt > 1) fetch_k(1);
-            if (wait_k(0)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_s(KB(0), 0);
-            }
-        }
-        for (uint32_t j = 0; j < nkt; ++j) {
-            // S of tile j + 1 goes into the buffer whose last readers (tile j - 1) passed the previous barrier
-            if (!SPLITKV && issuer && j + 1 < nkt && wait_k(j + 1)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_s(KB(j + 1), (j + 1) & 1);
-            }
-            ok = wait_s(j);
-            if (ok) {
-                if (issuer) {  // S of tile j is complete: its K buffer is free
-                    if (!SPLITKV && j + 2 < nkt) fetch_k(j + 2);
-                    if (SPLITKV && j + 1 < nkt) {  // one K buffer: the next tile travels and its S is issued while this tile's rows are scanned
-                        fetch_k(j + 1);
-                        if (wait_k(j + 1)) {
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            issue_s(KB(j + 1), (j + 1) & 1);
-                        }
-                    }
-                }
-                if (softmax) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-#pragma unroll
-                    for (int cc = 0; cc < NCH; ++cc) {
-                        if (j < nfree) max_chunk<false>(ts + 32 * cc, 0, 0, m);
-                        else max_chunk<true>(ts + 32 * cc, j * 128 + chalf + 32 * cc, qpos, m);
-                    }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                }
-            }
-            ok = __syncthreads_and(ok);
-            if (!ok) break;
-        }
-        // the two halves of a row agree on its maximum (the P tiles are not in use yet)
-        {
-            float *stat = reinterpret_cast<float *>(ph);
-            if (softmax) stat[cgrp * 128 + row] = m;
-            __syncthreads();
-            m = stat[row];
-#pragma unroll
-            for (int g = 1; g < NG; ++g) m = fmaxf(m, stat[g * 128 + row]);
-            __syncthreads();
-        }
-    }
-    float mneg = -m * 1.4426950408889634f;  // ONEPASS: m is still -inf here and moves with the tiles
+    float mneg = -m * 1.4426950408889634f;  // m is still -inf here and moves with the tiles
 
-    // ---- sweep 2: P = exp(S - m), O += P V ----
+    // ---- the sweep over the key tiles: P = exp(S - m_ref), O += P V ----
     if (ok && issuer) {
         fetch_k(0);
         fetch_v(0);
@@ -839,7 +788,7 @@ __global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __
             if (softmax) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ts = tmem_s + 128 * (j & 1) + trow + chalf;
-                if (ONEPASS) {
+                {
                     // this tile's largest score of the row: own 64 columns, then the other half's through shared memory
                     float tmax = -INFINITY;
 #pragma unroll
@@ -872,7 +821,7 @@ __global__ void __launch_bounds__(32 * (SW + 1), 1) flash_tc_f16_kernel(const __
                 ph_o ^= 1;
                 ok = __all_sync(0xffffffffu, ok);
             }
-            if (ONEPASS && softmax && ok && __any_sync(0xffffffffu, move)) {
+            if (softmax && ok && __any_sync(0xffffffffu, move)) {
                 // a row's reference moved: what O holds for it was accumulated against the old one (P V of tile j - 1 is
                 // complete, P V of tile j not yet issued); each half of the pair scales its own 64 dims
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -998,8 +947,7 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
     brasa_ctx *ctx = cmd->ctx;
     FlashTcParams p{q, kc, vc, o, sh.tokens, sh.hq, sh.hkv, sh.pos0, 1.0f / sqrtf(128.0f), ctx->status};
     dim3 grid((sh.tokens + 127) / 128, sh.hq);
-    static const bool tma_on = [] { const char *e = getenv("BRASA_FLASH_TMA"); return !(e && e[0] == '0'); }();
-    if ((kv == BRASA_KV_F16 || kv == BRASA_KV_Q8_0) && tma_on && flash_encode() &&
+    if ((kv == BRASA_KV_F16 || kv == BRASA_KV_Q8_0) && flash_encode() &&
         ((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
         const bool split = kv == BRASA_KV_Q8_0;
         const uint64_t npos = (uint64_t)sh.pos0 + sh.tokens, rows = npos * sh.hkv;
@@ -1037,35 +985,19 @@ int32_t brasa_flash_tc_launch(brasa_cmd *cmd, int32_t kv, const float *q, const 
         if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS || r3 != CUDA_SUCCESS || r4 != CUDA_SUCCESS)
             return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the KV cache (%d, %d, %d, %d)", (int)r1, (int)r2, (int)r3, (int)r4);
         const size_t smem = 7 * TILE_BYTES + 1024;
-        static bool done = false;
-        if (!done) {
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<false, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_f16_kernel<true, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            done = true;
+        if (split) {
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)flash_tc_f16_kernel<true>, smem));
+            flash_tc_f16_kernel<true><<<grid, 32 * (FLASH_SW + 1), smem, ctx->stream>>>(maps, p);
+        } else {
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)flash_tc_f16_kernel<false>, smem));
+            flash_tc_f16_kernel<false><<<grid, 32 * (FLASH_SW + 1), smem, ctx->stream>>>(maps, p);
         }
-        static const bool onepass = [] { const char *e = getenv("BRASA_FLASH_ONEPASS"); return !(e && e[0] == '0'); }();
-        static const bool wide = [] { const char *e = getenv("BRASA_FLASH_WARPS"); return e && atoi(e) == 16; }();
-        if (onepass && wide) {
-            if (split) flash_tc_f16_kernel<true, true, 16><<<grid, 544, smem, ctx->stream>>>(maps, p);
-            else flash_tc_f16_kernel<false, true, 16><<<grid, 544, smem, ctx->stream>>>(maps, p);
-        } else if (split && onepass) flash_tc_f16_kernel<true, true, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else if (split) flash_tc_f16_kernel<true, false, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else if (onepass) flash_tc_f16_kernel<false, true, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
-        else flash_tc_f16_kernel<false, false, 8><<<grid, 288, smem, ctx->stream>>>(maps, p);
         return brasa_post_launch(cmd, "flash_tc_f16");
     }
 #define LAUNCH_FTC(KVT, TILES)                                                                                              \
     do {                                                                                                                   \
         const size_t smem = (TILES) * TILE_BYTES + 1024;                                                                   \
-        static bool done = false;                                                                                          \
-        if (!done) {                                                                                                       \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(flash_tc_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-            done = true;                                                                                                   \
-        }                                                                                                                  \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)flash_tc_kernel<KVT>, smem)); \
         flash_tc_kernel<KVT><<<grid, 256, smem, ctx->stream>>>(p);                                                         \
     } while (0)
     if (kv == BRASA_KV_F16) LAUNCH_FTC(BRASA_KV_F16, 7);

@@ -183,8 +183,7 @@ bool tc_enabled() {
 // True when brasa_k_gemm_swiglu runs as one tensor-core launch for these matrices and token count (given an output that
 // does not overlap the input). The model then hands it a separate output buffer.
 bool brasa_gemm_swiglu_fuses(const brasa_qmatrix &wg, const brasa_qmatrix &wu, uint32_t tokens) {
-    static const bool fuse = [] { const char *e = getenv("BRASA_GEMM_GLU"); return !(e && e[0] == '0'); }();
-    return fuse && tc_enabled() && tokens >= 128 && wg.rows == wu.rows && wg.cols == wu.cols && wg.qtype == BRASA_Q4_0 && wu.qtype == BRASA_Q4_0 &&
+    return tc_enabled() && tokens >= 128 && wg.rows == wu.rows && wg.cols == wu.cols && wg.qtype == BRASA_Q4_0 && wu.qtype == BRASA_Q4_0 &&
            qm_fits(wg) && qm_fits(wu) && brasa_gemm_tc_supported(wg, tokens) && brasa_gemm_tc_supported(wu, tokens);
 }
 

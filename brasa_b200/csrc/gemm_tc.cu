@@ -531,14 +531,13 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     // stages of a tile are shared by `ksplit` CTAs (grid z) that each write a partial tile; the last to arrive adds
     // them in K order. A split keeps at least 8 stages.
     const uint32_t ntile = (tokens + BM - 1) / BM, nkst = ws[0].cols / BK;
-    static const bool split_on = [] { const char *e = getenv("BRASA_GEMM_SPLITK"); return !(e && e[0] == '0'); }();
     uint32_t mt = 1, nb = 1, ksplit = 1;
     double best = 1e30;
     for (uint32_t b = 1; b <= (rows256 ? 2u : 1u); ++b) {
         for (uint32_t c = 1; c * b <= 4 && c <= std::max(1u, ntile); c *= 2) {
             const uint32_t ctas = (tiles128 / b) * ((ntile + c - 1) / c);
             uint32_t ks = 1;
-            if (split_on && c * b <= 2 && ctas * 2 <= (uint32_t)ctx->sm_count && ctas <= GEMM_TC_COUNTERS)
+            if (c * b <= 2 && ctas * 2 <= (uint32_t)ctx->sm_count && ctas <= GEMM_TC_COUNTERS)
                 ks = std::max(1u, std::min((uint32_t)ctx->sm_count / ctas, nkst / 8));
             const double waves = std::ceil((double)ctas * ks / ctx->sm_count);
             const double pipe = waves * ((nkst + ks - 1) / ks) * (300.0 * c * b + 400.0) + (ks > 1 ? 4000.0 + 3000.0 * ks * c * b : 0.0);  // + the last CTA's sum over ks partial tiles
@@ -558,15 +557,6 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     if (q6) {  // one token tile, 128 rows, direct loads: the shape the q6_0 conversion is built for
         mt = 1;
         nb = 1;
-    }
-    {   // BRASA_GEMM_SHAPE=mt,nb forces the CTA shape (A/B runs); ignored when the matrices do not allow it
-        static const char *force = getenv("BRASA_GEMM_SHAPE");
-        unsigned fm = 0, fn = 0;
-        if (!q6 && force && sscanf(force, "%u,%u", &fm, &fn) == 2 && (fm == 1 || fm == 2 || fm == 4) && (fn == 1 || (fn == 2 && rows256)) && fm * fn <= 4) {
-            mt = fm;
-            nb = fn;
-            ksplit = 1;
-        }
     }
     if (glu) {  // 128 rows of gate and the same 128 rows of up per CTA: the 256-row shape, one or two token tiles
         nb = 2;
@@ -640,20 +630,12 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
     }
 #define LAUNCH_TC(MTV, GV, NBV, RAWV)                                                                                                        \
     do {                                                                                                                         \
-        static bool done = false;                                                                                                \
-        if (!done) {                                                                                                             \
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<MTV, GV, NBV, RAWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048)); \
-            done = true;                                                                                                         \
-        }                                                                                                                        \
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_kernel<MTV, GV, NBV, RAWV>, ctx->smem_optin - 2048)); \
         gemm_tc_kernel<MTV, GV, NBV, RAWV><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);                                                         \
     } while (0)
     // conversion groups: as many stages in flight as the ring holds, at most four
     if (q6) {
-        static bool done6 = false;
-        if (!done6) {
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048));
-            done6 = true;
-        }
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0>, ctx->smem_optin - 2048));
         gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);
     } else if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1, true);
     else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1, false);

@@ -64,7 +64,11 @@ struct GemvParams {
     uint32_t pf_nmat, pf_total_rows, pf_row_bytes, pf_swiglu;
 };
 
+#ifdef BRASA_TRACE_BUILD
 #define TRACE(i) do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[i] = gtime(); } while (0)
+#else
+#define TRACE(i) do { } while (0)
+#endif
 // N = half blocks per lane and slice (the lane's x registers hold 14 N words).
 constexpr int R = 2;         // rows a warp works on at a time
 constexpr int MAX_CONV = 3;  // half blocks of x a thread converts with all its loads in flight
@@ -499,11 +503,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     }
     if (qtype == BRASA_Q4_0) { PICK(BRASA_Q4_0) } else { PICK(BRASA_Q6_0) }
 #undef PICK
-    bool &attr_done = ctx->gemv_attr_done[(qtype == BRASA_Q4_0 ? 0 : 5) + (N - 1)];
-    if (!attr_done) {
-        BRASA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin));
-        attr_done = true;
-    }
+    BRASA_TRY(brasa_smem_optin(ctx, (const void *)kern, ctx->smem_optin));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(warps * 32);

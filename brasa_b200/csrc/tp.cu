@@ -29,11 +29,11 @@ struct brasa_tp {
     bool ipc_opened[BRASA_TP_MAX_RANKS] = {};
     uint32_t *state = nullptr;                 // device: [0] exchanges done so far, [1] arrival counter, [2] local argmax index
     bool connected = false;
+    uint32_t poll_limit = 1u << 22;            // loads of one exchange word before a wait gives up (brasa_tp_set_poll_limit)
 };
 
 namespace {
 
-constexpr uint32_t TP_POLL_LIMIT = 1u << 22;
 enum { TP_PUSH = 1, TP_GATHER = 2 };
 
 struct TpParams {
@@ -41,6 +41,7 @@ struct TpParams {
     uint32_t rank, world;
     uint64_t max_elems;
     uint32_t *state, *status;
+    uint32_t poll_limit;
 };
 
 __device__ __forceinline__ void st_words(uint64_t *p, uint64_t a, uint64_t b) {
@@ -52,11 +53,11 @@ __device__ __forceinline__ void ld_words(const uint64_t *p, uint64_t &a, uint64_
 __device__ __forceinline__ uint64_t word(float v, uint32_t tag) { return (uint64_t)__float_as_uint(v) | ((uint64_t)tag << 32); }
 
 // Waits for the two words at p to carry `tag`. dead: a wait of this thread already ran out (do not wait again).
-__device__ __forceinline__ void wait_words(const uint64_t *p, uint32_t tag, uint64_t &a, uint64_t &b, bool &dead, uint32_t *status) {
+__device__ __forceinline__ void wait_words(const uint64_t *p, uint32_t tag, uint64_t &a, uint64_t &b, bool &dead, uint32_t *status, uint32_t limit) {
     for (uint32_t it = 0;; ++it) {
         ld_words(p, a, b);
         if (((uint32_t)(a >> 32) == tag && (uint32_t)(b >> 32) == tag) || dead) return;
-        if (it >= TP_POLL_LIMIT) {
+        if (it >= limit) {
             atomicExch(status, 6u);
             dead = true;
             return;
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_kernel(TpParams p, const
             float sx = 0.0f, sy = 0.0f;
             for (uint32_t r = 0; r < p.world; ++r) {
                 uint64_t a, b;
-                wait_words(mine + (uint64_t)r * p.max_elems + 2 * i, tag, a, b, dead, p.status);
+                wait_words(mine + (uint64_t)r * p.max_elems + 2 * i, tag, a, b, dead, p.status, p.poll_limit);
                 const float vx = __uint_as_float((uint32_t)a), vy = __uint_as_float((uint32_t)b);
                 sx = r == 0 ? vx : sx + vx;
                 sy = r == 0 ? vy : sy + vy;
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(32) tp_argmax_kernel(TpParams p, const float *
         if (lane < p.world) {
             uint64_t a, b;
             bool dead = false;
-            wait_words(p.peer[p.rank] + base + (uint64_t)lane * p.max_elems, tag, a, b, dead, p.status);
+            wait_words(p.peer[p.rank] + base + (uint64_t)lane * p.max_elems, tag, a, b, dead, p.status, p.poll_limit);
             const float got = __uint_as_float((uint32_t)a);
             if (!dead) {
                 id = (uint32_t)b;
@@ -141,7 +142,9 @@ __global__ void __launch_bounds__(32) tp_argmax_kernel(TpParams p, const float *
                 id = oi;
             }
         }
-        if (lane == 0) *out = id;
+        // nothing valid arrived (every wait ran out): token 0, as the argmax of sampler.rs:150-170 gives when no logit
+        // exceeds -inf
+        if (lane == 0) *out = id == 0xffffffffu ? 0u : id;
         finish_exchange(p, e);
     }
 }
@@ -154,6 +157,7 @@ TpParams params_of(brasa_tp *tp) {
     p.max_elems = tp->max_elems;
     p.state = tp->state;
     p.status = tp->ctx->status;
+    p.poll_limit = tp->poll_limit;
     return p;
 }
 
@@ -220,6 +224,13 @@ void brasa_tp_free(brasa_tp *tp) {
     cudaFree(tp->local);
     cudaFree(tp->state);
     delete tp;
+}
+
+int32_t brasa_tp_set_poll_limit(brasa_tp *tp, uint32_t polls) {
+    if (!tp) return BRASA_EINVAL;
+    BRASA_REQUIRE(tp->ctx, polls >= 1, "tp: the poll limit must be at least 1");
+    tp->poll_limit = polls;
+    return BRASA_OK;
 }
 
 uint32_t brasa_tp_rank(const brasa_tp *tp) { return tp ? tp->rank : 0; }

@@ -180,6 +180,10 @@ class TensorParallel:
         ctxs[0]._check(lib().brasa_tp_connect_same_process(arr, C.c_uint32(len(tps))))
         return tps
 
+    def set_poll_limit(self, polls: int):
+        """Re-reads of one exchange word before a receive gives up (the call then ends in BrasaError ETIMEOUT)."""
+        self.ctx._check(lib().brasa_tp_set_poll_limit(self._h, C.c_uint32(polls)))
+
     def free(self):
         if self._h and self.ctx._h:
             lib().brasa_tp_free(self._h)

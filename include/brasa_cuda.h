@@ -83,14 +83,6 @@ int32_t brasa_ctx_mem_info(brasa_ctx *ctx, uint64_t *free_bytes, uint64_t *total
 int32_t brasa_ctx_sync(brasa_ctx *ctx);
 /* Kernels enqueued on this context so far; a graph replay counts every kernel it holds. */
 uint64_t brasa_ctx_launch_count(brasa_ctx *ctx);
-/* Debugging aid: with BRASA_TRACE=1 in the environment when the context is created, block 0 of the latest
- * GEMV launch records the global timer (ns) at nine points: entry, before and after the dependency wait, input
- * vector in shared memory, fixed-point conversion done, registers loaded, first weight slot ready, all rows
- * done, exit. */
-int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]);
-/* The first n (<= 512) words of the same buffer; the whole-token decode kernel writes 8 time stamps per operation
- * for 16 operations of block 0 from word 16 on (BRASA_TRACE_OP picks the first operation). */
-int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n);
 /* cudaStream_t of the context, for callers that order their own work (NCCL, torch) against it. */
 void *brasa_ctx_stream(brasa_ctx *ctx);
 
@@ -345,6 +337,10 @@ uint32_t brasa_tp_world(const brasa_tp *tp);
 int32_t brasa_tp_handle(brasa_tp *tp, uint8_t *handle /* BRASA_TP_HANDLE_BYTES */);
 int32_t brasa_tp_connect(brasa_tp *tp, const uint8_t *handles /* world x BRASA_TP_HANDLE_BYTES, by rank */);
 int32_t brasa_tp_connect_same_process(brasa_tp *const *tps, uint32_t n); /* ranks of one process: plain pointers */
+/* How many times a receive re-reads one exchange word before it gives up (default 2^22, seconds of waiting). A rank
+ * whose peer stopped calling then finishes its kernel with what it has, the next brasa_cmd_wait / brasa_ctx_sync on its
+ * context returns BRASA_ETIMEOUT, and the context stays usable. */
+int32_t brasa_tp_set_poll_limit(brasa_tp *tp, uint32_t polls);
 /* out = resid + sum over ranks of partial (resid.buf NULL: out = the sum); n even; identical bits on every rank */
 int32_t brasa_k_tp_allreduce_add(brasa_cmd *cmd, brasa_tp *tp, brasa_arg partial, brasa_arg resid, brasa_arg out, uint64_t n);
 /* argmax over the concatenation of every rank's logits[n] (this rank's rows start at row0): out_u32 = global index */

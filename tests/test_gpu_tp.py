@@ -111,6 +111,44 @@ def test_argmax_exchange_ties_and_nan(B, ctx):
             t.free()
 
 
+def test_receive_without_a_send_gives_up_and_the_context_lives(B, ctx):
+    """A rank whose peer never sends: the receive runs out of polls by itself (nothing faults, nothing hangs), the
+    call reports ETIMEOUT, and the same context runs the next exchange correctly."""
+    from brasa_b200.tp import TensorParallel
+    K = B.Kernels(ctx)
+    n = 512
+    tps = TensorParallel.same_process([ctx, ctx], n)
+    try:
+        tps[0].set_poll_limit(2000)
+        part = ctx.buffer_from(np.ones(n, np.float32))
+        out = ctx.buffer(n * 4)
+        cmd = ctx.command()
+        K.tp_allreduce_add(cmd, tps[0], part, None, out, n, phase="push")
+        K.tp_allreduce_add(cmd, tps[0], part, None, out, n, phase="gather")  # rank 1 never pushed
+        with pytest.raises(B.BrasaError) as err:
+            cmd.wait()
+        assert err.value.code == B.ETIMEOUT
+        ctx.sync()  # the status word was cleared by the failed wait: the context is clean again
+        # rank 1 catches up with the abandoned exchange (its own receive finds both ranks' words), then a full one
+        cmd = ctx.command()
+        K.tp_allreduce_add(cmd, tps[1], part, None, out, n, phase="push")
+        K.tp_allreduce_add(cmd, tps[1], part, None, out, n, phase="gather")
+        cmd.wait()
+        assert np.array_equal(out.download(np.float32)[:n], np.full(n, 2.0, np.float32))
+        outs = [ctx.buffer(n * 4) for _ in range(2)]
+        cmd = ctx.command()
+        for r in range(2):
+            K.tp_allreduce_add(cmd, tps[r], part, None, outs[r], n, phase="push")
+        for r in range(2):
+            K.tp_allreduce_add(cmd, tps[r], part, None, outs[r], n, phase="gather")
+        cmd.wait()
+        for r in range(2):
+            assert np.array_equal(outs[r].download(np.float32)[:n], np.full(n, 2.0, np.float32))
+    finally:
+        for t in tps:
+            t.free()
+
+
 @pytest.mark.parametrize("kv", ["F32", "F16"])
 def test_one_rank_exchange_changes_nothing(B, ctx, untied_model, kv):
     from brasa_b200.tp import TensorParallel

@@ -68,3 +68,42 @@ def test_static_scratch_decode_attention_matches_the_allocating_one():
                 cmd.wait()
     finally:
         ctx.close()
+
+
+def test_static_scratch_at_the_top_of_its_range():
+    """64 query heads over 8 KV heads at position 8 191: the last chunk of the last head writes the last words of the
+    fixed array. Same bits as the allocating entry point; one key more is refused."""
+    import brasa_b200 as B
+    ctx = B.Context(0)
+    try:
+        K = B.Kernels(ctx)
+        rng = O.Rng(43)
+        hq, hkv, dim, pos0 = 64, 8, 128, 8191
+        lk = pos0 + 1
+        q = rng.vec(hq * dim, 2.0)
+        kd, vd = rng.vec(lk * hkv * dim, 2.0).astype(np.float16), rng.vec(lk * hkv * dim, 3.0).astype(np.float16)
+        gq, gk, gv = ctx.buffer_from(q), ctx.buffer_from(kd), ctx.buffer_from(vd)
+        want_buf, got_buf = ctx.buffer(hq * dim * 4), ctx.buffer(hq * dim * 4)
+        part = ctx.buffer(B.decode_partials_len(hq, lk) * 4)
+        shape = B.AttnShape(1, hq, hkv, dim, pos0, B.KvType.F16)
+        for _ in range(2):
+            cmd = ctx.command()
+            K.decode_attention(cmd, gq, gk, gv, part, want_buf, shape)
+            cmd.wait()
+            got_buf.fill(0xFF)
+            cmd = ctx.command()
+            K.decode_attention_static(cmd, gq, gk, gv, got_buf, shape)
+            cmd.wait()
+            assert np.array_equal(got_buf.download(np.float32), want_buf.download(np.float32))
+        ref, vmax = O.attention(q, kd.astype(np.float32), vd.astype(np.float32), 1, hq, hkv, dim, pos0)
+        assert np.max(np.abs(got_buf.download(np.float32) - ref) / np.maximum(vmax, 1e-30)) <= 1e-5
+        # the allocating entry point refuses a position whose key count does not fit 32 bits instead of launching nothing
+        with pytest.raises(B.BrasaError) as e:
+            cmd = ctx.command()
+            try:
+                K.decode_attention(cmd, gq, gk, gv, part, want_buf, B.AttnShape(1, hq, hkv, dim, 0xFFFFFFFF, B.KvType.F16))
+            finally:
+                cmd.wait()
+        assert e.value.code == B.EINVAL
+    finally:
+        ctx.close()
