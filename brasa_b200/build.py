@@ -15,6 +15,9 @@ LIB = HERE / "libbrasa_cuda.so"
 SOURCES = ["ctx.cu", "quant.cu", "gemv.cu", "ops.cu", "attn.cu", "flash_tc.cu", "gemm.cu", "gemm_tc.cu", "sample.cu", "host_util.cu", "decode_token.cu", "model.cu", "batch.cu", "tp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-diag-suppress", "550"]
+# extra compiler flags for a developer's build, e.g. BRASA_NVCC_FLAGS="-DBRASA_TRACE_BUILD" (phase time stamps in the
+# GEMV and whole-token kernels)
+NVCC_FLAGS += os.environ.get("BRASA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

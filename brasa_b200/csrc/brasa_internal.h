@@ -56,6 +56,18 @@ struct brasa_ctx {
 // size; cheap afterwards).
 int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes);
 
+// The part of a tensor-parallel exchange buffer that belongs to the whole-token decode kernel, as seen from this rank:
+// peer[r] points at rank r's area, laid out [2 parities][world][stride] words {f32, epoch} (partial sums of a residual
+// add, slot = sending rank) followed by [2][world][2] words (best logit, its index).
+struct brasa_tp;
+struct brasa_tp_token_area {
+    uint32_t world, rank;
+    uint64_t stride;
+    uint32_t poll_limit;
+    unsigned long long *peer[BRASA_TP_MAX_RANKS];
+};
+bool brasa_tp_token_area_get(brasa_tp *tp, brasa_tp_token_area *out);
+
 // Phase time stamps of the GEMV and whole-token kernels exist only in builds with -DBRASA_TRACE_BUILD (a
 // developer's build; the shipped library carries neither the stamps nor these entry points).
 #ifdef BRASA_TRACE_BUILD

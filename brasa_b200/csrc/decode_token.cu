@@ -56,7 +56,8 @@ struct TokOp {
     uint32_t epilogue, scaled, log2S, nact;
     uint32_t in_kind, in_op, save_resid, next_cols;  // next_cols: length of next_normw
     float eps;
-    uint32_t pad1[3];
+    uint32_t xchg;  // tensor parallel: 1 + index of this residual add among the token's exchanges (0: no exchange)
+    uint32_t pad1[2];
     const uint8_t *w[3];
     const float *normw;
     const unsigned long long *in;
@@ -89,6 +90,10 @@ struct TokParams {
     uint32_t *status;
     unsigned long long *trace;  // optional: block 0 stamps the phases of 16 operations from trace_op on (debugging aid)
     uint32_t trace_op;
+    // tensor parallel (tp_world > 1): every rank's exchange area as seen from here, see brasa_tp_token_area
+    uint32_t tp_world, tp_rank, tp_row0, tp_poll_limit;
+    unsigned long long tp_stride;
+    unsigned long long *tp_peer[BRASA_TP_MAX_RANKS];
 };
 
 struct Best {
@@ -108,6 +113,17 @@ __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *
 }
 __device__ __forceinline__ void ll_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+// Words that cross GPUs (a peer's store into this rank's exchange area over NVLink): system scope.
+__device__ __forceinline__ void xg_store(unsigned long long *p, uint32_t bits, uint32_t epoch) {
+    unsigned long long w = ((unsigned long long)epoch << 32) | bits;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long xg_load(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
 }
 
 // Rows of block b: logical rows [r0, r1) of `total` (matrices one after another; SwiGLU: the rows of gate, up follows
@@ -342,7 +358,7 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
 
 // ---- GEMV, phase 3: one thread per output row of this block; the result goes out as {value, epoch} words.
 __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, const uint32_t *bo, float scale, uint32_t epoch, float *logits,
-                                           unsigned long long *cand) {
+                                           unsigned long long *cand, const TokParams &p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t lS = op.log2S, S = 1u << lS;
     const bool swiglu = op.epilogue == EPI_SWIGLU;
@@ -362,6 +378,30 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
             for (uint32_t sl = 0; sl < S; ++sl) u += part[((nr + j) << lS) + sl];
             u *= scale;
             v = (v / (1.0f + expf(-v))) * u;
+        }
+        if (op.epilogue == EPI_RESID && op.xchg) {
+            // Tensor parallel: v is this rank's share of the sum over the split columns. It goes into slot [this rank] of
+            // every rank's exchange area (parity of the exchange: a slot is rewritten two exchanges later, when its
+            // reader has long passed); the owner of the row on every rank then adds the slots in rank order, so all
+            // ranks hold the same bits.
+            const size_t base = (size_t)((op.xchg - 1) & 1) * p.tp_world * p.tp_stride + r0 + j;
+            for (uint32_t q = 0; q < p.tp_world; ++q) xg_store(p.tp_peer[q] + base + (size_t)p.tp_rank * p.tp_stride, __float_as_uint(v), epoch);
+            float sum = 0.0f;
+            for (uint32_t q = 0; q < p.tp_world; ++q) {
+                const unsigned long long *src = p.tp_peer[p.tp_rank] + base + (size_t)q * p.tp_stride;
+                unsigned long long w = 0;
+                for (uint32_t it = 0;; ++it) {
+                    w = xg_load(src);
+                    if ((uint32_t)(w >> 32) == epoch || *c.s_abort) break;
+                    if (it >= p.tp_poll_limit) {
+                        give_up(c, 6);
+                        break;
+                    }
+                }
+                const float part = __uint_as_float((uint32_t)w);
+                sum = q == 0 ? part : sum + part;
+            }
+            v = sum;
         }
         if (op.epilogue == EPI_RESID) v += c.resid[j];
         if (op.epilogue == EPI_LOGITS) {
@@ -712,7 +752,7 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
             gslot += total_slots;
             __syncthreads();
             TRACE(5);
-            gemv_epilogue(c, op, bo, c.red[47], epoch, p.logits, p.cand);
+            gemv_epilogue(c, op, bo, c.red[47], epoch, p.logits, p.cand, p);
         } else {
             attention_op<KV>(c, op, oi, epoch, epoch_in, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
         }
@@ -741,6 +781,33 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
         if (tid == 0) {
 #pragma unroll 1
             for (int w = 1; w < TK_WARPS; ++w) bst = better(bst, Best{c.red[16 + w], __float_as_uint(c.red[32 + w])});
+            if (p.tp_world > 1) {
+                // this rank's best (logit, vocabulary row) to every rank, then the best of all: largest logit, lowest row
+                // among equals (NaN never wins: it never became a candidate)
+                const size_t abase = 2 * (size_t)p.tp_world * p.tp_stride + (size_t)(c.seq & 1) * p.tp_world * 2;
+                const uint32_t mine = bst.i == 0xffffffffu ? 0xffffffffu : bst.i + p.tp_row0;
+                for (uint32_t q = 0; q < p.tp_world; ++q) {
+                    xg_store(p.tp_peer[q] + abase + 2 * p.tp_rank, __float_as_uint(bst.v), epoch);
+                    xg_store(p.tp_peer[q] + abase + 2 * p.tp_rank + 1, mine, epoch);
+                }
+                Best all{-INFINITY, 0xffffffffu};
+                for (uint32_t q = 0; q < p.tp_world; ++q) {
+                    const unsigned long long *src = p.tp_peer[p.tp_rank] + abase + 2 * q;
+                    unsigned long long w0 = 0, w1 = 0;
+                    for (uint32_t it = 0;; ++it) {
+                        w0 = xg_load(src);
+                        w1 = xg_load(src + 1);
+                        if (((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch) || *c.s_abort) break;
+                        if (it >= p.tp_poll_limit) {
+                            give_up(c, 6);
+                            break;
+                        }
+                    }
+                    if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch)
+                        all = better(all, Best{__uint_as_float((uint32_t)w0), (uint32_t)w1});
+                }
+                bst = all;
+            }
             const uint32_t tok = (bst.v == -INFINITY || bst.i == 0xffffffffu) ? 0u : bst.i;
             *p.next_id = tok;
             p.ids[0] = tok;
@@ -866,6 +933,10 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         return (int)ops.size() - 1;
     };
     int x_op = -1;  // operation that produced the current residual stream (-1: the embedding row)
+    const bool tp_on = m.tp.world > 1;
+    BRASA_REQUIRE(ctx, !tp_on || (m.tp.world <= BRASA_TP_MAX_RANKS && m.tp.rank < m.tp.world && m.tp.stride >= H),
+                  "token program: the exchange area is smaller than the hidden size");
+    uint32_t nxchg = 0;
     for (const brasa_token_layer &l : m.layers) {
         brasa_qmatrix wqkv[3] = {l.wq, l.wk, l.wv};
         BRASA_REQUIRE(ctx, l.wq.rows == QD && l.wk.rows == KD && l.wv.rows == KD && l.wq.cols == H && l.wo.rows == H && l.wo.cols == QD &&
@@ -885,11 +956,13 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         ops.push_back(a);
         int attn_op = (int)ops.size() - 1;
         int o_op = gemv_op(1, &l.wo, EPI_RESID, false, nullptr, attn, attn_op, xb, false);
+        if (tp_on) ops[o_op].xchg = ++nxchg;
         brasa_qmatrix wgu[2] = {l.gate, l.up};
         int gu_op = gemv_op(2, wgu, EPI_SWIGLU, true, l.ffn_norm, xb, o_op, act, true);
         x_op = gemv_op(1, &l.down, EPI_RESID, false, nullptr, act, gu_op, xa, false);
+        if (tp_on) ops[x_op].xchg = ++nxchg;
     }
-    BRASA_REQUIRE(ctx, m.head.rows == m.vocab && m.head.cols == H, "token program: unexpected lm_head shape");
+    BRASA_REQUIRE(ctx, (tp_on ? m.head.rows + m.head_row0 <= m.vocab : m.head.rows == m.vocab) && m.head.cols == H, "token program: unexpected lm_head shape");
     gemv_op(1, &m.head, EPI_LOGITS, true, m.final_norm, xa, x_op, nullptr, false);
     BRASA_REQUIRE(ctx, ops.size() + 2 < EPOCH_SPAN, "token program: too many operations");
     uint32_t nw_floats = 0;
@@ -982,6 +1055,12 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     p.partials = partials;
     p.attn_scale = 1.0f / sqrtf(128.0f);
     p.status = ctx->status;
+    p.tp_world = tp_on ? m.tp.world : 1;
+    p.tp_rank = tp_on ? m.tp.rank : 0;
+    p.tp_row0 = m.head_row0;
+    p.tp_stride = m.tp.stride;
+    p.tp_poll_limit = m.tp.poll_limit ? m.tp.poll_limit : POLL_LIMIT;
+    for (uint32_t r = 0; r < BRASA_TP_MAX_RANKS; ++r) p.tp_peer[r] = tp_on && r < m.tp.world ? m.tp.peer[r] : nullptr;
     p.trace = ctx->gemv_trace;
     {
         const char *env = getenv("BRASA_TRACE_OP");

@@ -24,7 +24,12 @@ struct brasa_token_model {
     uint32_t *next_id;  // the chosen token
     uint32_t *out_ids;
     uint32_t out_cap;
-    float *logits;      // [vocab]
+    float *logits;      // [rows of the lm_head]
+    // Tensor parallelism: this rank's shard (q/k/v, gate/up and the lm_head split by rows, o_proj and down_proj by
+    // columns). world == 1: no exchange. Otherwise the two residual adds of a layer sum the ranks' partial vectors and
+    // the greedy choice runs over every rank's lm_head rows, both through the peers' exchange areas.
+    uint32_t head_row0 = 0;  // vocabulary row of this rank's first lm_head row
+    brasa_tp_token_area tp{};  // tp.world <= 1: single rank
 };
 
 struct brasa_token_program;

@@ -288,11 +288,13 @@ int32_t set_position(brasa_model *m, uint32_t pos0) {
 // Describes the model to the whole-token kernel and builds its program, once. Leaves token_prog null when the
 // shapes do not fit or BRASA_TOKEN_KERNEL=0 asks for the kernel-per-operation path.
 int32_t make_token_program(brasa_model *m) {
-    if (m->tp || m->cfg.head_rows != m->cfg.vocab) {  // a shard exchanges with its peers between kernels
-        m->token_prog_tried = true;
-        return BRASA_OK;
-    }
     m->token_prog_tried = true;
+    brasa_tp_token_area area{};
+    if (m->tp) {
+        if (!brasa_tp_token_area_get(m->tp, &area)) return BRASA_OK;  // not connected yet: the kernel-per-operation path
+    } else if (m->cfg.head_rows != m->cfg.vocab) {
+        return BRASA_OK;  // a shard without its exchange cannot choose a token
+    }
     if (!m->ctx->token_kernel) return BRASA_OK;
     const brasa_config &c = m->cfg;
     brasa_token_model d{};
@@ -317,6 +319,8 @@ int32_t make_token_program(brasa_model *m) {
     d.out_ids = (uint32_t *)m->out_ids->ptr;
     d.out_cap = m->limits.ctx;
     d.logits = F(m->logits);
+    d.head_row0 = m->cfg.head_row0;
+    d.tp = area;
     if (!brasa_token_program_supported(m->ctx, d)) return BRASA_OK;
     return brasa_token_program_create(m->ctx, d, &m->token_prog);
 }

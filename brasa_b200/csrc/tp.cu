@@ -30,6 +30,8 @@ struct brasa_tp {
     uint32_t *state = nullptr;                 // device: [0] exchanges done so far, [1] arrival counter, [2] local argmax index
     bool connected = false;
     uint32_t poll_limit = 1u << 22;            // loads of one exchange word before a wait gives up (brasa_tp_set_poll_limit)
+    uint64_t token_stride = 0;                 // words per rank slot of the whole-token kernel's own exchange area
+    bool shares_device = false;                // another rank of the group lives on this rank's device (tests)
 };
 
 namespace {
@@ -161,9 +163,26 @@ TpParams params_of(brasa_tp *tp) {
     return p;
 }
 
-uint64_t buffer_bytes(const brasa_tp *tp) { return 2ull * tp->world * tp->max_elems * 8; }
+// The exchange buffer: [2 parities][world][max_elems] words for the kernels of this file, followed by the area the
+// whole-token decode kernel uses on its own (its words carry that kernel's epochs, which must never meet the exchange
+// numbers used here): [2][world][token_stride] partial sums and [2][world][2] (best logit, index) pairs. One
+// allocation, so one IPC handle opens all of it.
+uint64_t main_words(const brasa_tp *tp) { return 2ull * tp->world * tp->max_elems; }
+uint64_t buffer_bytes(const brasa_tp *tp) { return (main_words(tp) + 2ull * tp->world * tp->token_stride + 4ull * tp->world) * 8; }
 
 }  // namespace
+
+bool brasa_tp_token_area_get(brasa_tp *tp, brasa_tp_token_area *out) {
+    // Ranks that share a device cannot run kernels that wait for one another (nothing makes two launches on one GPU
+    // run at the same time): such a group keeps the exchange kernels of this file, queued send-before-receive.
+    if (!tp || !out || !tp->connected || tp->shares_device) return false;
+    out->world = tp->world;
+    out->rank = tp->rank;
+    out->stride = tp->token_stride;
+    out->poll_limit = tp->poll_limit;
+    for (uint32_t r = 0; r < tp->world; ++r) out->peer[r] = reinterpret_cast<unsigned long long *>(tp->peer[r] + main_words(tp));
+    return true;
+}
 
 int32_t brasa_tp_allreduce_add_launch(brasa_cmd *cmd, brasa_tp *tp, const float *src, const float *resid, float *out, uint64_t n, int phases) {
     brasa_ctx *ctx = cmd->ctx;
@@ -196,6 +215,7 @@ int32_t brasa_tp_create(brasa_ctx *ctx, uint32_t rank, uint32_t world, uint64_t 
     tp->rank = rank;
     tp->world = world;
     tp->max_elems = max_elems;
+    tp->token_stride = std::min<uint64_t>(max_elems, 16384);
     int32_t rc = [&]() -> int32_t {
         BRASA_CUDA(ctx, cudaSetDevice(ctx->device));
         BRASA_CUDA(ctx, cudaMalloc((void **)&tp->local, buffer_bytes(tp)));
@@ -280,6 +300,8 @@ int32_t brasa_tp_connect_same_process(brasa_tp *const *tps, uint32_t n) {
                 cudaError_t e = cudaDeviceEnablePeerAccess(tps[r]->ctx->device, 0);
                 if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
                 else BRASA_CUDA(ctx, e);
+            } else {
+                tps[i]->shares_device = true;
             }
             tps[i]->peer[r] = tps[r]->local;
         }

@@ -75,7 +75,7 @@ def exercise(B, dev):
             lg, _ = m.forward(prompt, 0)
             first = int(np.argmax(lg[0]))
             dev_ids, _ = m.decode_greedy(first, 40, 6)  # the whole-token kernel on this device
-            bt = B.Batch(m, max_seqs=3, num_pages=16, max_positions=128)
+            bt = B.Batch(m, max_seqs=3, num_pages=24, max_positions=128)
             bt.set_prefix(prompt[:32])
             for _ in range(3):
                 bt.add_sequence(prompt[32:])
