@@ -222,23 +222,22 @@ def time_qwen3_ref(path, cfg: dict, ids: np.ndarray, warmup: int, steps: int):
     """The reference's own CPU forward (tools/qwen3_ref.py, staged under oracle/_ref/): prefill of the prompt, then
     single-token decode steps over its f16-rounded cache, dequantised layers kept in RAM so that a step is matmuls and
     not re-dequantisation. Returns (seconds per timed token, threads used, greedy token ids)."""
+    import concurrent.futures
     import tempfile
 
     import torch
+
+    import oracle
     sys.path.insert(0, str(ROOT / "oracle" / "_ref"))
+    import brasa_file
     import qwen3_ref
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    with tempfile.TemporaryDirectory() as td:
-        (pathlib.Path(td) / "config.json").write_text(json.dumps(cfg))
-        m = qwen3_ref.Qwen3Ref(td, brasa=path, kv_dtype=torch.float16)
-    # Dequantised tensors kept in RAM (the tool re-reads and dequantises every layer on every call otherwise). They are
-    # filled here by the oracle's C dequantiser, several tensors at a time: bit-identical to the tool's numpy dequantiser
-    # (the golden tests hold both to the same bytes) and minutes faster for 4e9 weights; the forward itself is the tool's.
-    import concurrent.futures
-
-    import oracle
-    bf = m.w.file
+    # Dequantised tensors are kept in RAM (the tool re-reads and dequantises every layer on every call otherwise), and
+    # they are filled by the oracle's C dequantiser, several tensors at a time: bit-identical to the tool's numpy
+    # dequantiser (the golden tests hold both to the same bytes) and minutes faster for 4e9 weights. The forward itself,
+    # prefill and decode steps, is the tool's own code.
+    bf = brasa_file.BrasaFile(path)
     cache: dict = {}
 
     def fill(name):
@@ -249,12 +248,13 @@ def time_qwen3_ref(path, cfg: dict, ids: np.ndarray, warmup: int, steps: int):
         else:
             arr = oracle.dequantize(oracle.QTYPE[t["dtype"]], data, int(np.prod(t["shape"]))).reshape(t["shape"])
         return name, torch.from_numpy(arr)
-    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, threads)) as ex:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(16, threads)) as ex:
         for name, ten in ex.map(fill, list(bf.tensors)):
             cache[name] = ten
-    m.w.get = lambda name: cache[name]
-    m.embed = cache["model.embed_tokens.weight"]
-    m.final_norm = cache["model.norm.weight"]
+    qwen3_ref.BrasaWeights.get = lambda self, name: cache[name]
+    with tempfile.TemporaryDirectory() as td:
+        (pathlib.Path(td) / "config.json").write_text(json.dumps(cfg))
+        m = qwen3_ref.Qwen3Ref(td, brasa=path, kv_dtype=torch.float16)
     with torch.no_grad():
         caches = [m.new_cache()]
         logits = m.forward_many([torch.from_numpy(ids.astype(np.int64))], caches)[0]

@@ -65,7 +65,7 @@ int32_t brasa_ctx_create(int32_t device, brasa_ctx **out) {
     if (env && env[0] == '0') ctx->pdl = false;
 #ifdef BRASA_TRACE_BUILD
     env = getenv("BRASA_TRACE");
-    if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 4096) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 4096);
+    if (env && env[0] == '1' && cudaMalloc(&ctx->gemv_trace, 65536) == cudaSuccess) cudaMemset(ctx->gemv_trace, 0, 65536);
 #endif
     env = getenv("BRASA_GRAPH");
     if (env && env[0] == '0') ctx->graphs = false;
@@ -123,7 +123,7 @@ int32_t brasa_debug_gemv_trace(brasa_ctx *ctx, uint64_t out[16]) {
 
 int32_t brasa_debug_trace_read(brasa_ctx *ctx, uint64_t *out, uint32_t n) {
     if (!ctx || !out) return BRASA_EINVAL;
-    BRASA_REQUIRE(ctx, ctx->gemv_trace && n <= 512, "tracing is off (create the context with BRASA_TRACE=1) or more than 512 words asked");
+    BRASA_REQUIRE(ctx, ctx->gemv_trace && n <= 8192, "tracing is off (create the context with BRASA_TRACE=1) or more than 8192 words asked");
     BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     BRASA_CUDA(ctx, cudaMemcpy(out, ctx->gemv_trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
     return BRASA_OK;

@@ -172,9 +172,11 @@ __device__ __forceinline__ void embed_half_block(const uint8_t *table, uint32_t 
 }
 
 #ifdef BRASA_TRACE_BUILD
-#define TRACE(i) do { if (c.trace && c.b == 0 && threadIdx.x == 0 && oi >= c.trace_op && oi < c.trace_op + 16) c.trace[16 + (oi - c.trace_op) * 8 + (i)] = (unsigned long long)clock64(); } while (0)
+#define TRACEB(i) do { if (c.trace && threadIdx.x == 0 && c.oi >= c.trace_op && c.oi < c.trace_op + 5) c.trace[512 + ((c.oi - c.trace_op) * 160 + c.b) * 4 + (i)] = gtime(); } while (0)
+#define TRACE(i) do { if (c.trace && c.b == 0 && threadIdx.x == 0 && c.oi >= c.trace_op && c.oi < c.trace_op + 16) c.trace[16 + (c.oi - c.trace_op) * 16 + (i)] = (unsigned long long)clock64(); } while (0)
 #else
 #define TRACE(i) do { } while (0)
+#define TRACEB(i) do { } while (0)
 #endif
 
 // What the phases of an operation share. The phase functions are inlined: with 227 KB of shared memory in use the
@@ -190,6 +192,7 @@ struct TokCtx {
     uint32_t *status;
     unsigned long long *trace;
     uint32_t trace_op, my_slots, nslot, G, b, pos, seq, token, h0, hn;
+    uint32_t oi;  // current operation (trace builds)
 };
 
 // This warp's place in the block's slot list: next list index, its ring slot, that use's phase parity.
@@ -226,11 +229,14 @@ __device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s)
 }
 __device__ __forceinline__ void l2_ask(uint4 d) {
     const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
+#ifndef BRASA_NO_L2ASK
     if (d.z) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(d.z) : "memory");
+#endif
 }
 
 // ---- GEMV, phase 1: wait for the input, fold the norm weight, convert to fixed point (thread t: half blocks t, t + 512, ..).
 // Returns the thread's share of sum x^2.
+template <int P>
 __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, const uint8_t *embed, uint32_t vocab, uint32_t epoch_in) {
     const int tid = threadIdx.x;
     const uint32_t cols = op.cols, nhb = cols / 16;
@@ -261,6 +267,7 @@ __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, co
                     break;
                 }
             }
+            TRACE(2);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 q[j] = make_float4(__uint_as_float((uint32_t)w[4 * j]), __uint_as_float((uint32_t)w[4 * j + 1]),
@@ -282,14 +289,14 @@ __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, co
                 v.x *= nw.x; v.y *= nw.y; v.z *= nw.z; v.w *= nw.w;
             }
         }
-        x_half_block_to_fixed(xf, hbi, q[0], q[1], q[2], q[3]);
+        x_half_block_to_fixed<P>(xf, hbi, q[0], q[1], q[2], q[3]);
     }
     return ssq;
 }
 
 // ---- GEMV, phase 2: the rows. A slot holds up to RPS rows of one segment; its eight warps (half_w rows x S slices)
 // share them; a lane keeps the same half blocks of x for every row.
-template <int QT>
+template <int QT, int P>
 __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, const uint32_t *bo, uint32_t gslot, const WarpRing wr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cols = op.cols, nhb = cols / 16, lS = op.log2S, S = 1u << lS, nact = op.nact;
@@ -299,20 +306,18 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
     const uint32_t sl0 = (rows0 + RPS - 1) >> lRPS, sl1 = sl0 + ((rows1 + RPS - 1) >> lRPS), total_slots = sl1 + ((rows2 + RPS - 1) >> lRPS);
     const uint4 *xf = reinterpret_cast<const uint4 *>(c.xfb);
     const uint32_t slice = warp & (S - 1), rwl = (warp >> lS) & (half_w - 1);
-    XFixed xr[NMAX];
+    XFixed<P> xr[NMAX];
 #pragma unroll
     for (int i = 0; i < NMAX; ++i) {
         const uint32_t want = (slice * nact + i) * 32 + lane;
-        const uint32_t hbi = min(want, nhb - 1), sw = (hbi >> 1) & 3;
-        uint4 c0 = xf[hbi * 4 + (0 ^ sw)], c1 = xf[hbi * 4 + (1 ^ sw)], c2 = xf[hbi * 4 + (2 ^ sw)], c3 = xf[hbi * 4 + (3 ^ sw)];
-        xr[i].d[0][0] = c0.x; xr[i].d[0][1] = c0.y; xr[i].d[0][2] = c0.z; xr[i].d[1][0] = c0.w;
-        xr[i].d[1][1] = c1.x; xr[i].d[1][2] = c1.y; xr[i].d[2][0] = c1.z; xr[i].d[2][1] = c1.w;
-        xr[i].d[2][2] = c2.x; xr[i].d[3][0] = c2.y; xr[i].d[3][1] = c2.z; xr[i].d[3][2] = c2.w;
-        xr[i].total = (int)c3.x;
-        xr[i].step = (want < nhb && (uint32_t)i < nact) ? __uint_as_float(c3.y) : 0.0f;
+        const uint32_t hbi = min(want, nhb - 1);
+        xr[i] = x_fixed_load<P>(xf, hbi);
+        if (want >= nhb || (uint32_t)i >= nact) xr[i].step = 0.0f;  // lanes past the end of the row, unused registers
     }
     const uint32_t hi_off = tiled_hi_off(cols), sc_off = tiled_scale_off(QT, cols);
     uint32_t kk = wr.kk, rs = wr.rs, rph = wr.rph;
+    bool first_slot = true;
+    TRACE(5);
 #pragma unroll 1
     for (uint32_t j = kk - gslot; j < total_slots; j += 2) {
         const uint32_t sgi = (j >= sl0) + (j >= sl1);
@@ -320,6 +325,10 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
         const uint32_t sg_rows = sgi == 0 ? rows0 : (sgi == 1 ? rows1 : rows2), sg_before = sgi == 0 ? 0u : (sgi == 1 ? rows0 : rows0 + rows1);
         if (!*c.s_abort && !mbar_wait(&c.full[rs], rph)) {
             if (lane == 0) give_up(c, 2);
+        }
+        if (first_slot) {
+            TRACE(6);
+            first_slot = false;
         }
         const uint32_t n_slot = min(RPS, sg_rows - (ks << lRPS));
         const uint32_t qn = (n_slot + half_w - 1) >> lhw, in_slot = rwl * qn;
@@ -366,6 +375,17 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
     const uint32_t nr = swiglu ? rows0 : rows0 + rows1 + rows2;  // segments follow one another in part[] and in the output
     const float *part = c.part;
     Best bst{-INFINITY, 0xffffffffu};
+#ifdef BRASA_TRACE_BUILD
+    {
+        TRACE(13);
+        volatile float dummy = *reinterpret_cast<volatile float *>(c.part);
+        if (dummy == 1.2345e-33f) c.part[0] = 0.0f;
+        TRACE(14);
+        volatile uint32_t d2 = *reinterpret_cast<volatile uint32_t *>(&c.red[40]);
+        if (d2 == 0x12345678u) c.part[0] = 0.0f;
+        TRACE(15);
+    }
+#endif
 #pragma unroll 1
     for (uint32_t j = tid; j < nr; j += TK_THREADS) {
         float v = 0.0f;
@@ -408,7 +428,9 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
             logits[r0 + j] = v;
             if (v > bst.v) bst = Best{v, r0 + j};
         } else {
+            TRACE(9);
             ll_store(op.out + r0 + j, __float_as_uint(v), epoch);
+            TRACE(10);
         }
     }
     if (op.epilogue == EPI_LOGITS) {  // this block's best logit for the greedy choice
@@ -647,6 +669,9 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
 
 template <int KV>
 __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
+    // byte planes of the fixed-point input of the GEMVs (gemv_device.cuh): an f32 cache keeps the f32 accuracy class of
+    // the kernel-per-operation path; f16 and q8_0 caches, whose own rounding is orders of magnitude larger, take two
+    constexpr int PLANES = KV == BRASA_KV_F32 ? 3 : 2;
     extern __shared__ __align__(128) uint8_t smem[];
     TokCtx c;
     c.ring = smem;
@@ -722,7 +747,9 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
         const uint32_t epoch = c.seq * EPOCH_SPAN + oi + 1;
         const uint32_t epoch_in = c.seq * EPOCH_SPAN + op.in_op + 1;
 
+        c.oi = oi;
         TRACE(0);
+        TRACEB(0);
         if (op.next_normw) {  // the next operation's norm weight, copied while this one runs (the idle end of the block first)
             for (uint32_t i = TK_THREADS - 1 - tid; i < op.next_cols / 4; i += TK_THREADS) cp_async16(c.nwbuf + 4 * i, op.next_normw + 4 * i);
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -735,31 +762,35 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
                 const uint32_t k = gslot + p.nslot + i;
                 c.sdesc[i] = k < c.my_slots ? c.myslots[k] : make_uint4(0, 0, 0, 0);
             }
-            float ssq = gemv_input(c, op, p.embed, p.vocab, epoch_in);
             TRACE(1);
+            float ssq = gemv_input<PLANES>(c, op, p.embed, p.vocab, epoch_in);
+            TRACE(3);
+            TRACEB(1);
             for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
             if (lane == 0) c.red[warp] = ssq;
             __syncthreads();
-            TRACE(2);
+            TRACE(4);
             if (warp == TK_WARPS - 1) {  // 1 / rms of the whole input from the warps' sums, parked for the epilogue
                 float tot = c.red[lane & (TK_WARPS - 1)];
                 for (int o = TK_WARPS / 2; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
                 if (lane == 0) c.red[47] = op.scaled ? 1.0f / sqrtf(tot / (float)op.cols + op.eps) : 1.0f;
             }
-            if (op.qtype == BRASA_Q4_0) wr = gemv_rows<BRASA_Q4_0>(c, op, bo, gslot, wr);
-            else wr = gemv_rows<BRASA_Q6_0>(c, op, bo, gslot, wr);
-            TRACE(4);
+            if (op.qtype == BRASA_Q4_0) wr = gemv_rows<BRASA_Q4_0, PLANES>(c, op, bo, gslot, wr);
+            else wr = gemv_rows<BRASA_Q6_0, PLANES>(c, op, bo, gslot, wr);
+            TRACE(7);
+            TRACEB(2);
             gslot += total_slots;
             __syncthreads();
-            TRACE(5);
+            TRACE(8);
             gemv_epilogue(c, op, bo, c.red[47], epoch, p.logits, p.cand, p);
         } else {
             attention_op<KV>(c, op, oi, epoch, epoch_in, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
         }
-        TRACE(6);
+        TRACE(11);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        TRACE(7);
+        TRACE(12);
+        TRACEB(3);
     }
 
     // ---- greedy choice and the step's bookkeeping: block 0 gathers every block's best logit ----
@@ -1025,7 +1056,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
 
     // ---- shared memory ----
     const size_t attn_bytes = (size_t)2 * C * attn_row_stride(m.kv) + (8 * 160 + 8 * C + 2 * max_chunks) * 4;
-    p.xf_bytes = (uint32_t)((std::max<size_t>((size_t)max_cols * 4, attn_bytes) + 127) / 128 * 128);
+    p.xf_bytes = (uint32_t)((std::max<size_t>((size_t)max_cols / 16 * 16 * (m.kv == BRASA_KV_F32 ? XRec<3>::CHUNKS : XRec<2>::CHUNKS), attn_bytes) + 127) / 128 * 128);
     p.part_floats = (part_floats + 3) & ~3u;
     p.resid_floats = ((H + G - 1) / G + 4) & ~3u;
     p.sdesc_n = max_op_slots + L2_AHEAD;

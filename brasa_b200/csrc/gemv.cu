@@ -71,6 +71,7 @@ struct GemvParams {
 #endif
 // N = half blocks per lane and slice (the lane's x registers hold 14 N words).
 constexpr int R = 2;         // rows a warp works on at a time
+constexpr int GEMV_PLANES = 3;  // byte planes of the fixed-point input: the f32 accuracy class (gemv_device.cuh)
 constexpr int MAX_CONV = 3;  // half blocks of x a thread converts with all its loads in flight
 
 template <int QT, int N>
@@ -82,7 +83,7 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
     // layout: ring [nslot][slot_bytes] | xf [nhb] records of 16 words | part [max_items] | full, empty [nslot] | red
     uint8_t *ring = smem;
     uint4 *xf = reinterpret_cast<uint4 *>(smem + (size_t)p.nslot * slot_bytes);
-    float *part = reinterpret_cast<float *>(xf + 4 * nhb);
+    float *part = reinterpret_cast<float *>(xf + XRec<GEMV_PLANES>::CHUNKS * nhb);
     uint64_t *full = reinterpret_cast<uint64_t *>(part + ((p.max_items + 1) & ~1u));
     uint64_t *empty = full + p.nslot;
     float *red = reinterpret_cast<float *>(empty + p.nslot);
@@ -181,7 +182,7 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
     // ---- x to 22-bit fixed point, once per block: thread t converts half blocks t, t + CT, ... into records ----
     // quad j of a half block: the values that meet the low / high nibbles of code word 0 (j = 0, 1) and 1 (j = 2, 3)
     float ssq = 0.0f;
-    auto convert = [&](uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) { x_half_block_to_fixed(xf, hbi, q0, q1, q2, q3); };
+    auto convert = [&](uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) { x_half_block_to_fixed<GEMV_PLANES>(xf, hbi, q0, q1, q2, q3); };
     {
         float4 xq[MAX_CONV][4];
 #pragma unroll
@@ -262,17 +263,13 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
     TRACE(4);
     // ---- the lane's share: the same half blocks of every row ----
     const uint32_t slice = warp % S, rw = warp / S;
-    XFixed xr[N];
+    XFixed<GEMV_PLANES> xr[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) {
         const uint32_t want = (slice * N + i) * 32 + lane;
-        const uint32_t hbi = min(want, nhb - 1), sw = (hbi >> 1) & 3;
-        uint4 c0 = xf[hbi * 4 + (0 ^ sw)], c1 = xf[hbi * 4 + (1 ^ sw)], c2 = xf[hbi * 4 + (2 ^ sw)], c3 = xf[hbi * 4 + (3 ^ sw)];
-        xr[i].d[0][0] = c0.x; xr[i].d[0][1] = c0.y; xr[i].d[0][2] = c0.z; xr[i].d[1][0] = c0.w;
-        xr[i].d[1][1] = c1.x; xr[i].d[1][2] = c1.y; xr[i].d[2][0] = c1.z; xr[i].d[2][1] = c1.w;
-        xr[i].d[2][2] = c2.x; xr[i].d[3][0] = c2.y; xr[i].d[3][1] = c2.z; xr[i].d[3][2] = c2.w;
-        xr[i].total = (int)c3.x;
-        xr[i].step = want < nhb ? __uint_as_float(c3.y) : 0.0f;  // lanes past the end of the row contribute nothing
+        const uint32_t hbi = min(want, nhb - 1);
+        xr[i] = x_fixed_load<GEMV_PLANES>(xf, hbi);
+        if (want >= nhb) xr[i].step = 0.0f;  // lanes past the end of the row contribute nothing
     }
     const uint32_t hi_off = tiled_hi_off(p.cols), sc_off = tiled_scale_off(QT, p.cols);
     TRACE(5);
@@ -478,7 +475,7 @@ int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_
     uint32_t rows_per_block = (total_rows + grid - 1) / grid;
     uint32_t segs = epilogue == EPI_SWIGLU ? 2 : nmat;
     p.max_items = (rows_per_block + 1) * S * (epilogue == EPI_SWIGLU ? 2 : 1) + S * nmat;
-    size_t fixed = (size_t)nhb * 64 + (size_t)((p.max_items + 1) & ~1u) * 4 + 160;
+    size_t fixed = (size_t)nhb * 16 * XRec<GEMV_PLANES>::CHUNKS + (size_t)((p.max_items + 1) & ~1u) * 4 + 160;
     uint32_t need_slots = (rows_per_block + 1 + p.rows_per_slot - 1) / p.rows_per_slot * (epilogue == EPI_SWIGLU ? 2 : 1) + segs;
     // When the block's whole share of rows fits next to a second block (100 KB each), stay under that: the
     // next kernel's block can then start on the same SM and prefetch its weights meanwhile. A larger share

@@ -58,18 +58,60 @@ __device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t b, uint32_t 
     return r;
 }
 
-// The lane's x values of one half block in fixed point: quad j (4 values) x byte plane d, the sum of
-// the 16 integers, and the power-of-two step.
+// The lane's x values of one half block in fixed point with P byte planes: quad j (4 values) x plane d (the top plane
+// signed, the others unsigned), the sum of the 16 integers, and the power-of-two step. The 16 values share the step
+// 2^(e - 20) (P = 3) or 2^(e - 14) (P = 2), e the exponent of the largest magnitude among them, and the integer dot
+// products are exact.
+//   P = 3: 22 bits below the group's largest value per element, the accuracy class of an f32 dot product (the
+//          stand-alone GEMV entry points, and every decode path of a model with an f32 cache);
+//   P = 2: 15 bits, an order of magnitude inside the 1e-5 * sum |w x| the reference allows its own f32 GEMV
+//          (crates/kernels/src/lib.rs:13) and one third fewer integer operations: the whole-token kernel of models
+//          whose cache is f16 or q8_0, where the reference's own logits bound is 1e-3 / 2e-2
+//          (crates/models/tests/forward.rs:40-55).
+template <int P>
 struct XFixed {
-    uint32_t d[4][3];
+    uint32_t d[4][P];
     int total;
     float step;
 };
+// 16-byte chunks of a record in shared memory: 4 P plane words, the total, the step
+template <int P>
+struct XRec {
+    static constexpr uint32_t CHUNKS = P == 3 ? 4 : 3;
+};
+
+// Record hbi from shared memory. P = 3: 64-byte records, chunk c of record h stored at chunk c ^ ((h >> 1) & 3)
+// (conflict-free for consecutive h). P = 2: 48-byte records; every quarter warp covers all 32 banks once, no swizzle.
+template <int P>
+__device__ __forceinline__ XFixed<P> x_fixed_load(const uint4 *xf, uint32_t hbi) {
+    XFixed<P> x;
+    if (P == 3) {
+        const uint32_t sw = (hbi >> 1) & 3;
+        const uint4 c0 = xf[hbi * 4 + (0 ^ sw)], c1 = xf[hbi * 4 + (1 ^ sw)], c2 = xf[hbi * 4 + (2 ^ sw)], c3 = xf[hbi * 4 + (3 ^ sw)];
+        const uint32_t w[12] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int d = 0; d < P; ++d) x.d[j][d] = w[P * j + d];
+        x.total = (int)c3.x;
+        x.step = __uint_as_float(c3.y);
+    } else {
+        const uint4 c0 = xf[hbi * 3], c1 = xf[hbi * 3 + 1], c2 = xf[hbi * 3 + 2];
+        const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int d = 0; d < P; ++d) x.d[j][d] = w[P * j + d];
+        x.total = (int)c2.x;
+        x.step = __uint_as_float(c2.y);
+    }
+    return x;
+}
 
 // sum over the 16 weights of a half block of (code - bias) * X, as an integer.
 // Quads: 0 = low nibbles of word x, 1 = high nibbles of word x, 2 and 3 likewise for word y.
-template <int QT>
-__device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const XFixed &x) {
+template <int QT, int P>
+__device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const XFixed<P> &x) {
     uint32_t a[4];
     a[0] = codes.x & 0x0F0F0F0Fu;
     a[1] = (codes.x >> 4) & 0x0F0F0F0Fu;
@@ -81,22 +123,27 @@ __device__ __forceinline__ int half_block_idot(uint2 codes, uint32_t hb, const X
         a[2] = lop_and_or(hb << 2, 0x30303030u, a[2]);
         a[3] = lop_and_or(hb << 4, 0x30303030u, a[3]);
     }
-    int s0 = 0, s1 = 0, s2 = 0;
+    constexpr int BIAS = QT == BRASA_Q4_0 ? 8 : 32;
+    int s[P];
+    s[0] = -BIAS * x.total;
+#pragma unroll
+    for (int d = 1; d < P; ++d) s[d] = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        s0 = dp4a_uu(a[j], x.d[j][0], s0);
-        s1 = dp4a_uu(a[j], x.d[j][1], s1);
-        s2 = dp4a_us(a[j], x.d[j][2], s2);
+#pragma unroll
+        for (int d = 0; d < P; ++d) s[d] = d == P - 1 ? dp4a_us(a[j], x.d[j][d], s[d]) : dp4a_uu(a[j], x.d[j][d], s[d]);
     }
-    constexpr int BIAS = QT == BRASA_Q4_0 ? 8 : 32;
-    return s0 + 256 * s1 + 65536 * s2 - BIAS * x.total;
+    int r = s[0];
+#pragma unroll
+    for (int d = 1; d < P; ++d) r += s[d] << (8 * d);
+    return r;
 }
 
 // Dot products of two rows of a slot with the lane's share of x (row_b == row_a when there is only one).
 // After folding across lanes, lane 0 holds the sum of row a and lane 8 the sum of row b. The body is kept
 // small on purpose: a fully unrolled four-row version ran out of instruction cache.
-template <int QT, int N>
-__device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_t *row_b, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb,
+template <int QT, int N, int P>
+__device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_t *row_b, const XFixed<P> (&xr)[N], uint32_t slice, uint32_t nhb,
                                               uint32_t hi_off, uint32_t sc_off, int lane, int nact = N) {
     float acc_a = 0.0f, acc_b = 0.0f;
     // straight-line code: lanes past the end of the row read the last half block and have step 0
@@ -113,8 +160,8 @@ __device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_
             }
             float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
             float db = __half2float(*reinterpret_cast<const __half *>(row_b + sc_off + (hbi >> 1) * 2));
-            int sa = half_block_idot<QT>(ca, ha, xr[it]);
-            int sb = half_block_idot<QT>(cb, hb, xr[it]);
+            int sa = half_block_idot<QT, P>(ca, ha, xr[it]);
+            int sb = half_block_idot<QT, P>(cb, hb, xr[it]);
             acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
             acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
         }
@@ -131,8 +178,8 @@ __device__ __forceinline__ float row_pair_dot(const uint8_t *row_a, const uint8_
 }
 
 // One row only (the last row of an odd count): every lane ends up with the sum.
-template <int QT, int N>
-__device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFixed (&xr)[N], uint32_t slice, uint32_t nhb, uint32_t hi_off,
+template <int QT, int N, int P>
+__device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFixed<P> (&xr)[N], uint32_t slice, uint32_t nhb, uint32_t hi_off,
                                                 uint32_t sc_off, int lane, int nact = N) {
     float acc_a = 0.0f;
 #pragma unroll
@@ -143,7 +190,7 @@ __device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFix
             uint32_t ha = 0;
             if (QT == BRASA_Q6_0) ha = *reinterpret_cast<const uint32_t *>(row_a + hi_off + hbi * 4);
             float da = __half2float(*reinterpret_cast<const __half *>(row_a + sc_off + (hbi >> 1) * 2));
-            int sa = half_block_idot<QT>(ca, ha, xr[it]);
+            int sa = half_block_idot<QT, P>(ca, ha, xr[it]);
             acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
         }
     }
@@ -151,21 +198,23 @@ __device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFix
     return acc_a;
 }
 
-// x to 22-bit fixed point: one half block (16 values, as the four quads that meet the low / high nibbles of code
-// word 0 and of code word 1) becomes a 64-byte record in xf: 12 byte-plane words, the sum of the integers, the step.
+// x to fixed point with P byte planes: one half block (16 values, as the four quads that meet the low / high nibbles
+// of code word 0 and of code word 1) becomes a record in xf: 4 P byte-plane words, the sum of the integers, the step.
+template <int P>
 __device__ __forceinline__ void x_half_block_to_fixed(uint4 *xf, uint32_t hbi, float4 q0, float4 q1, float4 q2, float4 q3) {
+    constexpr uint32_t BITS = P == 3 ? 22 : 16;  // |x| / step stays below 2^(BITS - 1): 21 (P = 3) or 15 (P = 2)
     float v[4][4] = {{q0.x, q0.y, q0.z, q0.w}, {q1.x, q1.y, q1.z, q1.w}, {q2.x, q2.y, q2.z, q2.w}, {q3.x, q3.y, q3.z, q3.w}};
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) amax = fmaxf(amax, fabsf(v[j][e]));
-    // step = 2^(exponent(amax) - 20): every |x| / step is below 2^21; zero (or denormal) groups get step 0
+    // step = 2^(exponent(amax) - (BITS - 2)); zero (or denormal) groups get step 0
     uint32_t ebits = __float_as_uint(amax) & 0x7F800000u;
-    bool live = ebits > (21u << 23) && ebits < 0x7F800000u;
+    bool live = ebits > ((BITS - 1) << 23) && ebits < 0x7F800000u;
     // infinities and NaNs are not representable: their group's step carries them into the result
-    float step = live ? __uint_as_float(ebits - (20u << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
-    float inv = live ? __uint_as_float((254u << 23) - (ebits - (20u << 23))) : 0.0f;  // 1 / step, exact
+    float step = live ? __uint_as_float(ebits - ((BITS - 2) << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
+    float inv = live ? __uint_as_float((254u << 23) - (ebits - ((BITS - 2) << 23))) : 0.0f;  // 1 / step, exact
     int total = 0;
     uint32_t rec[16];
 #pragma unroll
@@ -174,22 +223,29 @@ __device__ __forceinline__ void x_half_block_to_fixed(uint4 *xf, uint32_t hbi, f
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             X[e] = __float2int_rn(v[j][e] * inv);
+            if (P == 2) X[e] = min(X[e], 32767);  // a value that rounds up to 2^15 stays inside the signed top byte
             total += X[e];
         }
         // byte planes of the four integers: byte k of every X gathered into one word
         uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);
-        uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
-        rec[3 * j + 0] = __byte_perm(lo01, lo23, 0x5410);
-        rec[3 * j + 1] = __byte_perm(lo01, lo23, 0x7632);
-        rec[3 * j + 2] = __byte_perm(hi01, hi23, 0x5410);
+        rec[P * j + 0] = __byte_perm(lo01, lo23, 0x5410);
+        rec[P * j + 1] = __byte_perm(lo01, lo23, 0x7632);
+        if (P == 3) {
+            uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
+            rec[P * j + 2] = __byte_perm(hi01, hi23, 0x5410);
+        }
     }
-    rec[12] = (uint32_t)total;
-    rec[13] = __float_as_uint(step);
-    rec[14] = rec[15] = 0;
-    // 16-byte chunk c of record h is stored at chunk c ^ ((h >> 1) & 3): conflict-free for consecutive h
-    const uint32_t sw = (hbi >> 1) & 3;
+    rec[4 * P] = (uint32_t)total;
+    rec[4 * P + 1] = __float_as_uint(step);
+    rec[4 * P + 2] = rec[4 * P + 3] = 0;
+    if (P == 3) {
+        const uint32_t sw = (hbi >> 1) & 3;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) xf[hbi * 4 + (c ^ sw)] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
+        for (int c = 0; c < 4; ++c) xf[hbi * 4 + (c ^ sw)] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) xf[hbi * 3 + c] = make_uint4(rec[4 * c], rec[4 * c + 1], rec[4 * c + 2], rec[4 * c + 3]);
+    }
 }
 
 }  // namespace brasa_dev

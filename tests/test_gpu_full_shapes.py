@@ -207,7 +207,8 @@ def test_16k_prompt_in_bench_chunks_against_reference_goldens(B, ctx, golden_dir
 def test_decode_past_8192_positions_on_both_decode_paths(B, tmp_path, heads, kv_heads, token_kernel):
     """Prefill 8 300 tokens on the GPU, hand the GPU's own f16 cache to the oracle, then compare four decode steps:
     whatever the decode path (BRASA_TOKEN_KERNEL=1: one kernel per token; 0: one kernel per operation with the fused
-    attention that merges its 65 chunks of 128 keys), logits must match the oracle's decode over the same cache."""
+    attention that merges its 65 chunks of 128 keys), logits must match the oracle's decode over the same cache within
+    the reference's bound for an f16 cache."""
     cfg = BF.tiny_config(layers=2, hidden=256, heads=heads, kv_heads=kv_heads, ffn=512, vocab=512, max_pos=16384)
     path = tmp_path / "model.brasa"
     BF.write_brasa(path, cfg, BF.synth_weights(cfg, seed=heads, std=0.05, norm_jitter=0.1))
@@ -242,7 +243,7 @@ def test_decode_past_8192_positions_on_both_decode_paths(B, tmp_path, heads, kv_
             m.forward(prompt[off:off + 2048], off, want_logits=False)
         for i, t in enumerate(toks):
             got, _ = m.forward([t], n + i)
-            assert rel(got[0], want[i]) <= 2e-4, (i, rel(got[0], want[i]))
+            assert rel(got[0], want[i]) <= 1e-3, (i, rel(got[0], want[i]))  # forward.rs:40-55: the bound for an f16 cache
             if i + 1 < len(toks):
                 top2 = np.sort(want[i])[-2:]
                 assert toks[i + 1] == int(np.argmax(want[i])) or top2[1] - top2[0] <= 1e-3 * np.abs(want[i]).max(), i

@@ -338,13 +338,16 @@ def test_token_kernel_matches_kernel_per_operation_path(kv, monkeypatch, golden_
         runs[mode] = (np.stack(logits), toks, [int(t) for t in out])
     (la, ta, ra), (lb, tb, rb) = runs["0"], runs["1"]
     scale = np.abs(la).max()
-    assert np.abs(la - lb).max() <= tol * scale
-    # the paths agree on every token whose top-1 margin is clear of the tolerance
-    for i, (a, b) in enumerate(zip(ta, tb)):
-        if a != b:
-            top2 = np.sort(la[i])[-2:]
-            assert top2[1] - top2[0] <= 2 * tol * scale, f"token {i}: {a} vs {b}"
-            break
+    # The two paths round the GEMV input differently for f16 and q8_0 caches (22-bit against 16-bit fixed point), so a
+    # near tie may send the greedy sequences apart; from there on they decode different texts. Logits are compared as
+    # long as both paths fed the same tokens, and the parting must be a tie within the tolerance.
+    same = next((i for i, (a, b) in enumerate(zip(ta, tb)) if a != b), len(ta))
+    upto = min(same + 1, len(ta))
+    assert upto >= 20, f"the paths parted after {same} tokens"
+    assert np.abs(la[:upto] - lb[:upto]).max() <= tol * scale
+    if same < len(ta):
+        top2 = np.sort(la[same])[-2:]
+        assert top2[1] - top2[0] <= 2 * tol * scale, f"token {same}: {ta[same]} vs {tb[same]}"
     assert len(ra) == len(rb) == 16
 
 
