@@ -447,7 +447,7 @@ def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048
                 "sampling": "temperature 0.7, top-p 0.95, top-k 0, PCG32 per sequence", "kv": "f16, pages of 16 positions",
                 "decode_tok_s": seqs * steps / secs, "ms_per_step": secs / steps * 1e3,
                 "prefix_prefill_s": t_prefix, "admit_all_s": t_admit, "ttft_s_median": statistics.median(ttft), "ttft_s_max": max(ttft),
-                "prefix_tokens_not_recomputed": prefix * (seqs - 1), "pages_in_use": batch.pages_in_use,
+                "prefix_cache": batch.prefix_cache_stats(), "pages_in_use": batch.pages_in_use,
                 "kv_resident_gib": batch.pages_in_use * page * kvb / 2**30,
                 "algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (secs / steps) / 1e9,
                 "distinct_tokens": int(np.unique(ids).size)}

@@ -157,6 +157,7 @@ def lib() -> C.CDLL:
         L.brasa_batch_free.argtypes = [C.c_void_p]
         L.brasa_batch_sequences.argtypes = [C.c_void_p]
         L.brasa_batch_pages_in_use.argtypes = [C.c_void_p]
+        L.brasa_batch_prefix_cache_stats.argtypes = [C.c_void_p] * 5
         L.brasa_tp_free.restype = None
         L.brasa_tp_free.argtypes = [C.c_void_p]
         L.brasa_tp_rank.argtypes = [C.c_void_p]
@@ -791,6 +792,12 @@ class Batch:
     @property
     def pages_in_use(self) -> int:
         return int(lib().brasa_batch_pages_in_use(self._h))
+
+    def prefix_cache_stats(self) -> dict:
+        """Prompt tokens served from the prefix cache and computed so far, pages the cache knows, pages all sequences share."""
+        hit, done, pages, common = C.c_uint64(0), C.c_uint64(0), C.c_uint32(0), C.c_uint32(0)
+        self.ctx._check(lib().brasa_batch_prefix_cache_stats(self._h, C.byref(hit), C.byref(done), C.byref(pages), C.byref(common)))
+        return {"hit_tokens": int(hit.value), "prefilled_tokens": int(done.value), "cached_pages": int(pages.value), "common_pages": int(common.value)}
 
     def decode(self, steps: int, params: SamplingParams | None = None):
         """Returns (ids [sequences][steps + 1] with the token drawn at add time first, device seconds)."""

@@ -11,6 +11,7 @@
 // like a prefill chunk), QK-norm + RoPE + page store with one position per sequence, paged split-K attention, and the
 // batched sampler with one PCG32 stream per sequence.
 #include <memory>
+#include <unordered_map>
 
 #include "attn_device.cuh"
 #include "model_internal.h"
@@ -372,6 +373,19 @@ __global__ void pages_from_cache_kernel(const uint8_t *cache, uint8_t *pool, con
     }
 }
 
+// The inverse: pages of one sequence -> rows [p0, p0 + n) of every layer of the contiguous cache (a sequence admitted
+// behind pages another sequence computed needs their rows where the prefill kernels read them).
+__global__ void cache_from_pages_kernel(uint8_t *cache, const uint8_t *pool, const int32_t *table_row, uint32_t p0, uint32_t n, uint32_t row_bytes,
+                                        size_t cache_layer_bytes, size_t pool_layer_bytes) {
+    const uint32_t layer = blockIdx.y, units = row_bytes / 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n * units; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t pos = p0 + (uint32_t)(i / units), u = (uint32_t)(i % units);
+        const size_t slot = (size_t)table_row[pos / PAGE] * PAGE + pos % PAGE;
+        const uint4 val = *reinterpret_cast<const uint4 *>(pool + layer * pool_layer_bytes + slot * row_bytes + (size_t)u * 16);
+        *reinterpret_cast<uint4 *>(cache + layer * cache_layer_bytes + (size_t)pos * row_bytes + (size_t)u * 16) = val;
+    }
+}
+
 __global__ void gather_ids_kernel(uint32_t *dst, const uint32_t *src, uint32_t n) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = src[i];
@@ -395,9 +409,35 @@ struct brasa_batch {
     std::vector<int32_t> h_table;  // host mirror [max_seqs][max_pages]
     std::vector<uint32_t> h_lens;
     std::vector<brasa_buf *> owned;
+    // The prefix cache: every full page of prompt tokens ever computed, found again by what it holds. A page's key
+    // chains the key of the page before it with its own 16 token ids, so a key names the whole token sequence up to
+    // and including the page (a radix tree over pages, stored as a hash map of its nodes).
+    struct CachedPage {
+        int32_t page;
+        uint64_t parent;
+        uint32_t ids[PAGE];
+    };
+    std::unordered_map<uint64_t, CachedPage> cached;
+    std::vector<uint64_t> resident;     // key of the page whose rows the contiguous cache holds at page index i (0: none)
+    std::vector<uint32_t> prefix_ids;   // the declared prefix (brasa_batch_set_prefix)
+    uint32_t common_pages = 0;          // leading pages every sequence of the batch shares
+    uint64_t hit_tokens = 0, prefilled_tokens = 0;
 };
 
 namespace {
+
+constexpr uint64_t CHAIN_ROOT = 0x9E3779B97F4A7C15ull;
+
+// Key of a page given the key of the page before it (CHAIN_ROOT for the first) and its 16 token ids. Never 0.
+uint64_t chain_key(uint64_t parent, const uint32_t *ids) {
+    uint64_t h = parent;
+    for (uint32_t i = 0; i < PAGE; ++i) {
+        h ^= (uint64_t)ids[i] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+        h *= 0xBF58476D1CE4E5B9ull;
+        h ^= h >> 29;
+    }
+    return h ? h : 1;
+}
 
 int32_t balloc(brasa_batch *b, uint64_t bytes, brasa_buf **out) {
     BRASA_TRY(brasa_buf_alloc(b->ctx, bytes, out));
@@ -421,6 +461,20 @@ int32_t copy_rows_to_pages(brasa_batch *b, brasa_cmd *cmd, uint32_t seq, uint32_
     pages_from_cache_kernel<<<grid, 256, 0, b->ctx->stream>>>((const uint8_t *)m->vc->ptr, (uint8_t *)b->vpool->ptr, row, p0, n, (uint32_t)b->row_bytes,
                                                               b->cache_layer_bytes, b->pool_layer_bytes);
     return brasa_post_launch(cmd, "pages_from_cache");
+}
+
+// copies the pages of sequence `seq` that hold positions [p0, p0 + n) into the model's contiguous cache
+int32_t copy_pages_to_rows(brasa_batch *b, brasa_cmd *cmd, uint32_t seq, uint32_t p0, uint32_t n) {
+    if (n == 0) return BRASA_OK;
+    brasa_model *m = b->m;
+    dim3 grid(std::min<uint32_t>(1024, (uint32_t)(((size_t)n * (b->row_bytes / 16) + 255) / 256)), m->cfg.layers);
+    const int32_t *row = (const int32_t *)b->table->ptr + (size_t)seq * b->max_pages;
+    cache_from_pages_kernel<<<grid, 256, 0, b->ctx->stream>>>((uint8_t *)m->kc->ptr, (const uint8_t *)b->kpool->ptr, row, p0, n, (uint32_t)b->row_bytes,
+                                                              b->cache_layer_bytes, b->pool_layer_bytes);
+    BRASA_TRY(brasa_post_launch(cmd, "cache_from_pages"));
+    cache_from_pages_kernel<<<grid, 256, 0, b->ctx->stream>>>((uint8_t *)m->vc->ptr, (const uint8_t *)b->vpool->ptr, row, p0, n, (uint32_t)b->row_bytes,
+                                                              b->cache_layer_bytes, b->pool_layer_bytes);
+    return brasa_post_launch(cmd, "cache_from_pages");
 }
 
 // prefill of `n` tokens at positions [pos0, pos0 + n) through the model's contiguous cache, in chunks of max_tokens;
@@ -517,7 +571,7 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
             BRASA_TRY(brasa_post_launch(cmd, "qk_norm_rope_store_paged"));
             // chunks wholly inside the shared prefix: one block serves 16 / G sequences; the rest per sequence
             const uint32_t G = c.heads / c.kv_heads;
-            const uint32_t shared_chunks = (n > 1 && 16 % G == 0 && G < 16) ? b->prefix_len / 128 : 0;
+            const uint32_t shared_chunks = (n > 1 && 16 % G == 0 && G < 16) ? b->common_pages * PAGE / 128 : 0;
             if (shared_chunks) {
                 const uint32_t spb = 16 / G;
                 decode_partial_paged_mma_kernel<true><<<dim3(shared_chunks, c.kv_heads, (n + spb - 1) / spb), 128, MMA_SMEM, ctx->stream>>>(
@@ -607,11 +661,13 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 2 * m->cfg.vocab * 4, &b->scratch));
     b->h_table.assign((size_t)max_seqs * b->max_pages, 0);
     b->h_lens.assign(max_seqs, 0);
+    b->resident.assign(b->max_pages, 0);
     *out = b.release();
     return BRASA_OK;
 }
 
-// The prefix every sequence starts with: computed once, kept in the model's contiguous cache at [0, n) and in shared pages.
+// The prefix every sequence starts with: computed once, kept in the model's contiguous cache at [0, n) and in pages that
+// the prefix cache hands to every sequence that starts with these tokens.
 int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n) {
     if (!b || (!ids && n)) return BRASA_EINVAL;
     brasa_ctx *ctx = b->ctx;
@@ -619,10 +675,20 @@ int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n) 
     BRASA_REQUIRE(ctx, n % PAGE == 0, "batch: the shared prefix must fill whole pages of %u positions", PAGE);
     BRASA_REQUIRE(ctx, n / PAGE <= b->max_pages && n / PAGE <= b->num_pages, "batch: prefix longer than the page budget");
     b->prefix_len = n;
+    b->prefix_ids.assign(ids, ids + n);
     if (n == 0) return BRASA_OK;
     BRASA_TRY(prefill_contiguous(b, ids, n, 0));
-    // shared pages 0 .. n/16 - 1, listed in row 0 of the table for the copy
-    for (uint32_t i = 0; i < n / PAGE; ++i) b->h_table[i] = (int32_t)i;
+    b->prefilled_tokens += n;
+    // pages 0 .. n/16 - 1, listed in row 0 of the table for the copy, and entered into the prefix cache
+    uint64_t key = CHAIN_ROOT;
+    for (uint32_t i = 0; i < n / PAGE; ++i) {
+        b->h_table[i] = (int32_t)i;
+        brasa_batch::CachedPage cp{(int32_t)i, key, {}};
+        memcpy(cp.ids, ids + (size_t)i * PAGE, sizeof cp.ids);
+        key = chain_key(key, ids + (size_t)i * PAGE);
+        b->cached.emplace(key, cp);
+        b->resident[i] = key;
+    }
     b->next_page = n / PAGE;
     BRASA_TRY(upload_table_row(b, 0));
     brasa_cmd *cmd;
@@ -633,8 +699,11 @@ int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n) 
     return rc2;
 }
 
-// A new sequence: the shared prefix followed by its own n tokens (n >= 1). Its first generated token is drawn from
-// the logits of its last prompt token with its own PCG32 stream (params.seed + sequence index).
+// A new sequence: the declared prefix followed by its own n tokens (n >= 1). Every leading full page of that token
+// sequence that some earlier sequence (or the declared prefix) already computed is attached instead of recomputed
+// (crates/runtime/src/session.rs:230-237 for many sequences: the longest cached prefix is reused and at least the last
+// prompt token is always recomputed); the rest is prefilled and its full pages join the cache. Its first generated
+// token is drawn from the logits of its last prompt token with its own PCG32 stream (params.seed + sequence index).
 int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n, brasa_sampling_params params, uint32_t *seq_out) {
     if (!b || !ids) return BRASA_EINVAL;
     brasa_ctx *ctx = b->ctx;
@@ -642,21 +711,80 @@ int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n
     BRASA_REQUIRE(ctx, b->nseq < b->max_seqs, "batch: all %u sequence slots are in use", b->max_seqs);
     BRASA_REQUIRE(ctx, n >= 1 && (uint64_t)b->prefix_len + n < (uint64_t)b->max_pages * PAGE, "batch: sequence longer than max_positions");
     const uint32_t seq = b->nseq, total = b->prefix_len + n;
-    // pages: the shared ones, then own pages for every position this sequence may reach
-    const uint32_t shared = b->prefix_len / PAGE, own = b->max_pages - shared;
-    BRASA_REQUIRE(ctx, b->next_page + own <= b->num_pages, "batch: out of KV pages (%u of %u in use)", b->next_page, b->num_pages);
+    std::vector<uint32_t> full(b->prefix_ids);
+    full.insert(full.end(), ids, ids + n);
+    // walk the cache: page h of this sequence is a hit when its key is known and names these very tokens
     int32_t *row = b->h_table.data() + (size_t)seq * b->max_pages;
-    for (uint32_t i = 0; i < shared; ++i) row[i] = (int32_t)i;
-    for (uint32_t i = 0; i < own; ++i) row[shared + i] = (int32_t)(b->next_page + i);
+    std::vector<uint64_t> keys;
+    uint64_t key = CHAIN_ROOT;
+    uint32_t hit = 0;
+    const uint32_t max_hit = (total - 1) / PAGE;  // the last prompt token is computed here, whatever the cache holds
+    while (hit < max_hit) {
+        const uint64_t k = chain_key(key, full.data() + (size_t)hit * PAGE);
+        auto it = b->cached.find(k);
+        if (it == b->cached.end() || it->second.parent != key || memcmp(it->second.ids, full.data() + (size_t)hit * PAGE, sizeof it->second.ids) != 0) break;
+        row[hit] = it->second.page;
+        keys.push_back(k);
+        key = k;
+        ++hit;
+    }
+    const uint32_t matched = hit * PAGE, own = b->max_pages - hit;
+    BRASA_REQUIRE(ctx, b->next_page + own <= b->num_pages, "batch: out of KV pages (%u of %u in use)", b->next_page, b->num_pages);
+    for (uint32_t i = 0; i < own; ++i) row[hit + i] = (int32_t)(b->next_page + i);
     b->next_page += own;
     BRASA_TRY(upload_table_row(b, seq));
-    BRASA_TRY(prefill_contiguous(b, ids, n, b->prefix_len));
+    // the prefill kernels read earlier positions from the contiguous cache: bring in the hit pages it does not hold
+    {
+        brasa_cmd *cmd;
+        BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
+        int32_t rc = BRASA_OK;
+        for (uint32_t i = 0; i < hit && rc == BRASA_OK;) {
+            if (b->resident[i] == keys[i]) {
+                ++i;
+                continue;
+            }
+            uint32_t j = i;
+            while (j < hit && b->resident[j] != keys[j]) ++j;
+            rc = copy_pages_to_rows(b, cmd, seq, i * PAGE, (j - i) * PAGE);
+            for (uint32_t q = i; q < j; ++q) b->resident[q] = keys[q];
+            i = j;
+        }
+        int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
+        BRASA_TRY(rc);
+        BRASA_TRY(rc2);
+    }
+    BRASA_TRY(prefill_contiguous(b, full.data() + matched, total - matched, matched));
+    b->hit_tokens += matched;
+    b->prefilled_tokens += total - matched;
+    // the full pages computed just now join the cache; what lies behind them in the contiguous cache is not a page
+    const uint32_t full_pages = total / PAGE;
+    for (uint32_t i = hit; i < b->max_pages; ++i) {
+        if (i < full_pages) {
+            brasa_batch::CachedPage cp{row[i], key, {}};
+            memcpy(cp.ids, full.data() + (size_t)i * PAGE, sizeof cp.ids);
+            key = chain_key(key, full.data() + (size_t)i * PAGE);
+            b->cached.emplace(key, cp);  // an equal key already there (the page at max_hit of an identical prompt) keeps its page
+            b->resident[i] = key;
+        } else {
+            b->resident[i] = 0;
+        }
+    }
+    // leading pages shared by every sequence of the batch: their keys are read once per group of sequences by the
+    // attention kernel
+    if (seq == 0) {
+        b->common_pages = full_pages;
+    } else {
+        const int32_t *row0 = b->h_table.data();
+        uint32_t c = 0;
+        while (c < b->common_pages && c < hit && row[c] == row0[c]) ++c;
+        b->common_pages = c;
+    }
     uint64_t st[2];
     brasa_pcg32_seed(params.seed + seq, st);
     BRASA_TRY(brasa_buf_upload(b->rng, (uint64_t)seq * 16, st, 16));
     brasa_cmd *cmd;
     BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
-    int32_t rc = copy_rows_to_pages(b, cmd, seq, b->prefix_len, n);
+    int32_t rc = copy_rows_to_pages(b, cmd, seq, matched, total - matched);
     if (rc == BRASA_OK)
         rc = choose_tokens(b, cmd, m->logits, 1, params, (unsigned long long *)b->rng->ptr + 2 * seq, F(b->scratch) + (size_t)seq * 2 * m->cfg.vocab,
                            b->ids, seq);
@@ -732,5 +860,14 @@ int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits) {
 
 uint32_t brasa_batch_sequences(brasa_batch *b) { return b ? b->nseq : 0; }
 uint32_t brasa_batch_pages_in_use(brasa_batch *b) { return b ? b->next_page : 0; }
+
+int32_t brasa_batch_prefix_cache_stats(brasa_batch *b, uint64_t *hit_tokens, uint64_t *prefilled_tokens, uint32_t *cached_pages, uint32_t *common_pages) {
+    if (!b) return BRASA_EINVAL;
+    if (hit_tokens) *hit_tokens = b->hit_tokens;
+    if (prefilled_tokens) *prefilled_tokens = b->prefilled_tokens;
+    if (cached_pages) *cached_pages = (uint32_t)b->cached.size();
+    if (common_pages) *common_pages = b->common_pages;
+    return BRASA_OK;
+}
 
 }  // extern "C"

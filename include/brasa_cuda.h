@@ -308,10 +308,19 @@ typedef struct brasa_batch brasa_batch;
 /* up to max_seqs sequences (<= the model's max_tokens) of at most max_positions positions each, num_pages pages in all */
 int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages, uint32_t max_positions, brasa_batch **out);
 void brasa_batch_free(brasa_batch *b);
-/* the prefix every sequence shares (a multiple of BRASA_KV_PAGE tokens, possibly 0): prefilled once, its pages attached to every sequence */
+/* a prefix declared up front (a multiple of BRASA_KV_PAGE tokens, possibly 0): prefilled once; every sequence added later
+ * starts with it */
 int32_t brasa_batch_set_prefix(brasa_batch *b, const uint32_t *ids, uint32_t n);
-/* a sequence = the shared prefix + its own n >= 1 tokens; prefills them, draws its first token (PCG32 seed = params.seed + index) */
+/* a sequence = the declared prefix + its own n >= 1 tokens. Prefix cache (crates/runtime/src/session.rs:230-237 for many
+ * sequences): every full page of prompt tokens ever computed in this batch is kept under a key that chains the 16 token
+ * ids of the page with the key of the page before it; the leading pages of a new sequence that are found there are
+ * attached instead of recomputed (at least its last prompt token is always computed), whoever computed them, and the
+ * output never depends on what was reused. The rest is prefilled and its full pages join the cache. Draws the
+ * sequence's first token (PCG32 seed = params.seed + index). */
 int32_t brasa_batch_add_sequence(brasa_batch *b, const uint32_t *ids, uint32_t n, brasa_sampling_params params, uint32_t *seq_out);
+/* prompt tokens served from the prefix cache / computed so far, pages the cache knows, leading pages all sequences share */
+int32_t brasa_batch_prefix_cache_stats(brasa_batch *b, uint64_t *hit_tokens, uint64_t *prefilled_tokens, uint32_t *cached_pages,
+                                       uint32_t *common_pages);
 /* `steps` tokens for every sequence; out_ids[seq * (steps + 1) + s], s = 0 being the token drawn when the sequence was added */
 int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params params, uint32_t *out_ids, double *gpu_seconds);
 /* logits [sequences][vocab] of the next token of every sequence, without sampling or advancing */

@@ -153,3 +153,45 @@ def test_batch_rejects_what_does_not_fit(B, golden_dir):
         bt.free()
     finally:
         m.free()
+
+
+def test_prefix_cache_finds_pages_of_earlier_sequences(B, golden_dir):
+    """No prefix is declared. Sequences that happen to start alike share the pages an earlier one computed: a whole
+    branch (A, then A + B), a fork inside it (A + C), an unrelated prompt, and a prompt given twice (everything but the
+    page of its last token is served from the cache). The invariant of crates/runtime/tests/session.rs:53-60: tokens
+    and logits are what each sequence gives alone, where nothing is reused."""
+    path = golden_dir / "tiny" / "model.brasa"
+    rng = np.random.default_rng(77)
+    a, b2, c2, other = (rng.integers(0, 512, k).astype(np.uint32) for k in (150, 70, 45, 90))
+    prompts = [a, np.concatenate([a, b2]), np.concatenate([a, c2]), other, np.concatenate([a, b2]), np.concatenate([a[:100], c2])]
+    # pages of 16 tokens served from the cache: 0; 9 (144 of a); 9; 0; 13 (219 tokens: 13 full pages, the last recomputed); 6 (96 of a[:100])
+    want_hits = [0, 144, 144, 0, 208, 96]
+    steps = 10
+    ctx = B.Context(0)
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=512, max_tokens=64, max_logit_rows=1, kv=B.KvType.F16))
+    bt = B.Batch(m, max_seqs=len(prompts), num_pages=len(prompts) * 20, max_positions=320)
+    try:
+        seen = 0
+        for p, w in zip(prompts, want_hits):
+            bt.add_sequence(p)
+            st = bt.prefix_cache_stats()
+            assert st["hit_tokens"] - seen == w, (len(p), st)
+            seen = st["hit_tokens"]
+        assert st["prefilled_tokens"] == sum(len(p) for p in prompts) - sum(want_hits)
+        assert st["common_pages"] == 0  # the unrelated prompt shares nothing with the first
+        first = bt.peek_logits()
+        ids, _ = bt.decode(steps)
+    finally:
+        bt.free()
+        m.free()
+    assert np.array_equal(ids[1], ids[4])  # the same prompt twice: the same continuation, computed or reused
+    for s, p in enumerate(prompts):
+        want_logits, want_toks = alone(B, ctx, path, B.KvType.F16, p, steps, ctx_len=512)
+        scale = np.abs(want_logits[0]).max()
+        assert ids[s, 0] == want_toks[0], s
+        assert np.abs(first[s] - want_logits[0]).max() <= 1e-3 * scale, s
+        for i in range(steps):
+            if int(ids[s, i + 1]) != want_toks[i + 1]:
+                top2 = np.sort(want_logits[i])[-2:]
+                assert top2[1] - top2[0] <= 4e-3 * scale, (s, i)
+                break
