@@ -482,6 +482,7 @@ def tp_leg(B, ctx, rep, steps: int = 3, prompt: int = 1024, generate: int = 256)
         os.replace(tmp, path)
     limits = B.Limits(ctx=2048, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16)
     m = B.Qwen3.load(ctx, path, limits)
+    load = m.load_stats()
     tp = TP.TensorParallel(ctx, rank, world, limits.max_tokens * cfg["hidden_size"])
     m.set_tp(tp)
     try:
@@ -533,7 +534,7 @@ def tp_leg(B, ctx, rep, steps: int = 3, prompt: int = 1024, generate: int = 256)
                 "decode_tok_s": 1.0 / t_tok, "ms_per_token": t_tok * 1e3, "prefill_tok_s": prompt / rep.max(pre_s),
                 "bytes_per_token_per_gpu": per_token, "achieved_gbs_per_gpu": per_token / t_tok / 1e9,
                 "exchanges_per_token": 2 * cfg["num_hidden_layers"] + 1, "ranks_agree_on_tokens": bool(agree),
-                "batch": 1}
+                "batch": 1, "shard_load": load}
     finally:
         m.free()
         tp.free()
@@ -840,6 +841,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ids = prompt_ids(cfg["vocab_size"])
     sess = B.Session(ctx, path, B.Limits(ctx=CTX, max_tokens=512, max_logit_rows=1, kv=B.KvType.F16))
     model = sess.model
+    load_stats = model.load_stats()
     K = B.Kernels(ctx)
 
     if args.only_serving:
@@ -888,7 +890,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                               "ms_per_step": total_s / args.steps * 1e3, "config": {"workload": WORKLOAD, "tokens_per_step": steps_tokens},
-                              "gpu_launches": int(launches), "note": "decode loop only (profiling run)"}))
+                              "gpu_launches": int(launches), "model_load": load_stats, "note": "decode loop only (profiling run)"}))
         return
 
     # ---- end to end through Session.generate (host buffers) ----

@@ -103,6 +103,14 @@ class _MemoryPlan(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("weights", "kv", "workspace", "overhead", "total")]
 
 
+class _BatchShape(C.Structure):
+    _fields_ = [("max_seqs", C.c_uint32), ("num_pages", C.c_uint32), ("max_positions", C.c_uint32), ("head_rows", C.c_uint32), ("kv", C.c_int32)]
+
+
+class _BatchPlan(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("kv_pages", "tables", "logits", "attention_partials", "sampler", "total")]
+
+
 class _Limits(C.Structure):
     _fields_ = [("ctx", C.c_uint32), ("max_tokens", C.c_uint32), ("max_logit_rows", C.c_uint32), ("kv", C.c_int32)]
 
@@ -643,6 +651,29 @@ class planner:
         return rc == 0, {n: getattr(p, n) for n, _ in _MemoryPlan._fields_}, mx.value
 
 
+    @staticmethod
+    def plan_batch(shape: _ModelShape, max_seqs: int, num_pages: int, max_positions: int, kv: KvType, head_rows: int | None = None) -> dict:
+        """Bytes of a batch over a paged KV pool, buffer by buffer as brasa_batch_create allocates them."""
+        p = _BatchPlan()
+        s = _BatchShape(max_seqs, num_pages, max_positions, head_rows if head_rows is not None else shape.vocab, int(kv))
+        rc = lib().brasa_plan_batch(C.byref(shape), C.byref(s), C.byref(p))
+        if rc != 0:
+            raise BrasaError(rc, "plan_batch: bad arguments")
+        return {n: getattr(p, n) for n, _ in _BatchPlan._fields_}
+
+    @staticmethod
+    def max_batch(ctx: Context | None, shape: _ModelShape, kv: KvType, shared_prefix: int, positions_per_seq: int, budget: int = 0,
+                  cap: int = 1 << 20, head_rows: int | None = None) -> tuple[int, int, dict]:
+        """(largest number of sequences that fits, pages it needs, its plan); 0 sequences when not even one fits."""
+        p, n, pages = _BatchPlan(), C.c_uint32(), C.c_uint32()
+        rc = lib().brasa_plan_batch_max_seqs(ctx._h if ctx else None, C.byref(shape), C.c_int32(int(kv)),
+                                             C.c_uint32(head_rows if head_rows is not None else shape.vocab), C.c_uint32(shared_prefix),
+                                             C.c_uint32(positions_per_seq), C.c_uint32(cap), C.c_uint64(budget), C.byref(n), C.byref(pages), C.byref(p))
+        if rc not in (0, EBUDGET):
+            raise BrasaError(rc, "plan_batch_max_seqs: bad arguments")
+        return n.value, pages.value, {k: getattr(p, k) for k, _ in _BatchPlan._fields_}
+
+
 class Qwen3:
     """Model on the device with its KV cache and workspace (crates/models/src/qwen3.rs:301 Qwen3)."""
 
@@ -705,6 +736,12 @@ class Qwen3:
         self.ctx._check(lib().brasa_model_decode_greedy(self._h, C.c_uint32(first), C.c_uint32(pos0), C.c_uint32(steps),
                                                         out.ctypes.data_as(C.c_void_p), C.byref(secs)))
         return out, secs.value
+
+    def load_stats(self) -> dict:
+        """Seconds the weights took from the file to their device layout, the bytes moved, and the rate."""
+        s, n = C.c_double(0.0), C.c_uint64(0)
+        self.ctx._check(lib().brasa_model_load_stats(self._h, C.byref(s), C.byref(n)))
+        return {"seconds": s.value, "bytes": int(n.value), "gb_per_s": n.value / s.value / 1e9 if s.value > 0 else None}
 
     def read_kv(self, layer: int, which: str, pos_begin: int, pos_end: int) -> np.ndarray:
         kvd = self.cfg["kv_heads"] * self.cfg["head_dim"]
@@ -792,6 +829,11 @@ class Batch:
     @property
     def pages_in_use(self) -> int:
         return int(lib().brasa_batch_pages_in_use(self._h))
+
+    def allocated(self) -> int:
+        n = C.c_uint64(0)
+        self.ctx._check(lib().brasa_batch_allocated(self._h, C.byref(n)))
+        return int(n.value)
 
     def prefix_cache_stats(self) -> dict:
         """Prompt tokens served from the prefix cache and computed so far, pages the cache knows, pages all sequences share."""

@@ -624,6 +624,68 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
 
 extern "C" {
 
+// The buffers of brasa_batch_create, one term each, at the allocation granularity of the planner.
+int32_t brasa_plan_batch(const brasa_model_shape *m, const brasa_batch_shape *s, brasa_batch_plan *out) {
+    if (!m || !s || !out) return BRASA_EINVAL;
+    if (s->kv < BRASA_KV_F32 || s->kv > BRASA_KV_Q8_0 || s->max_seqs == 0 || s->max_positions < PAGE) return BRASA_EINVAL;
+    auto g = [](uint64_t n) { return brasa_plan_buffer_bytes(n); };
+    const uint64_t max_pages = ((uint64_t)s->max_positions + PAGE - 1) / PAGE, max_chunks = (max_pages * PAGE + 127) / 128;
+    const uint64_t row_bytes = brasa_kv_bytes(s->kv, (uint64_t)m->kv_heads * 128);
+    out->kv_pages = 2 * g((uint64_t)m->layers * s->num_pages * PAGE * row_bytes);
+    out->tables = g((uint64_t)s->max_seqs * max_pages * 4) + 3 * g((uint64_t)s->max_seqs * 4) + g((uint64_t)s->max_seqs * 16);
+    out->logits = g((uint64_t)s->max_seqs * s->head_rows * 4);
+    out->attention_partials = g((uint64_t)s->max_seqs * m->heads * max_chunks * 130 * 4);
+    out->sampler = g((uint64_t)s->max_seqs * 2 * m->vocab * 4);
+    out->total = out->kv_pages + out->tables + out->logits + out->attention_partials + out->sampler;
+    return BRASA_OK;
+}
+
+int32_t brasa_plan_batch_max_seqs(brasa_ctx *ctx, const brasa_model_shape *m, int32_t kv, uint32_t head_rows, uint32_t shared_prefix,
+                                  uint32_t positions_per_seq, uint32_t max_seqs_cap, uint64_t budget, uint32_t *max_seqs_out,
+                                  uint32_t *num_pages_out, brasa_batch_plan *plan_out) {
+    if (!m || !max_seqs_out) return BRASA_EINVAL;
+    BRASA_REQUIRE(ctx, shared_prefix % PAGE == 0 && positions_per_seq > shared_prefix && max_seqs_cap >= 1,
+                  "plan_batch: the shared prefix must fill whole pages and lie inside a sequence's positions");
+    if (budget == 0) {
+        if (!ctx) return BRASA_EINVAL;
+        uint64_t free_b = 0, total_b = 0;
+        BRASA_TRY(brasa_ctx_mem_info(ctx, &free_b, &total_b));
+        budget = free_b > (512ull << 20) ? free_b - (512ull << 20) : 0;
+    }
+    const uint32_t max_pages = (positions_per_seq + PAGE - 1) / PAGE, own = max_pages - shared_prefix / PAGE;
+    auto plan_of = [&](uint32_t n, brasa_batch_plan *p, uint32_t *pages) {
+        const uint64_t np = (uint64_t)shared_prefix / PAGE + (uint64_t)n * own;
+        *pages = (uint32_t)std::min<uint64_t>(np, UINT32_MAX);
+        const brasa_batch_shape s{n, *pages, positions_per_seq, head_rows, kv};
+        return brasa_plan_batch(m, &s, p);
+    };
+    uint32_t lo = 0, hi = max_seqs_cap;  // the plan grows with the number of sequences
+    while (lo < hi) {
+        const uint32_t mid = lo + (hi - lo + 1) / 2;
+        brasa_batch_plan p;
+        uint32_t pages;
+        BRASA_TRY(plan_of(mid, &p, &pages));
+        if (p.total <= budget) lo = mid;
+        else hi = mid - 1;
+    }
+    *max_seqs_out = lo;
+    if (lo == 0) return brasa_fail(ctx, BRASA_EBUDGET, "plan_batch: not even one sequence of %u positions fits %.2f GiB", positions_per_seq, budget / 1073741824.0);
+    brasa_batch_plan p;
+    uint32_t pages;
+    BRASA_TRY(plan_of(lo, &p, &pages));
+    if (plan_out) *plan_out = p;
+    if (num_pages_out) *num_pages_out = pages;
+    return BRASA_OK;
+}
+
+int32_t brasa_batch_allocated(brasa_batch *b, uint64_t *bytes) {
+    if (!b || !bytes) return BRASA_EINVAL;
+    uint64_t sum = 0;
+    for (brasa_buf *x : b->owned) sum += brasa_plan_buffer_bytes(x->bytes);
+    *bytes = sum;
+    return BRASA_OK;
+}
+
 void brasa_batch_free(brasa_batch *b) {
     if (!b) return;
     for (brasa_buf *x : b->owned) brasa_buf_free(x);
@@ -649,6 +711,16 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     b->pool_layer_bytes = (size_t)num_pages * PAGE * b->row_bytes;
     b->cache_layer_bytes = (size_t)m->cap * b->row_bytes;
     b->max_chunks = ((uint64_t)b->max_pages * PAGE + 127) / 128;
+    // the plan first: a batch that cannot fit is refused before anything is allocated
+    const brasa_model_shape shape{0, m->cfg.layers, m->cfg.hidden, m->cfg.heads, m->cfg.kv_heads, m->cfg.head_dim, m->cfg.ffn, m->cfg.vocab};
+    const brasa_batch_shape bshape{max_seqs, num_pages, max_positions, m->cfg.head_rows, m->limits.kv};
+    brasa_batch_plan plan;
+    BRASA_TRY(brasa_plan_batch(&shape, &bshape, &plan));
+    uint64_t free_b = 0, total_b = 0;
+    BRASA_TRY(brasa_ctx_mem_info(ctx, &free_b, &total_b));
+    if (plan.total + (512ull << 20) > free_b)
+        return brasa_fail(ctx, BRASA_EBUDGET, "batch: %u sequences over %u pages need %.2f GiB (KV pages %.2f) and the device has %.2f GiB free",
+                          max_seqs, num_pages, plan.total / 1073741824.0, plan.kv_pages / 1073741824.0, free_b / 1073741824.0);
     BRASA_TRY(balloc(b.get(), (uint64_t)m->cfg.layers * b->pool_layer_bytes, &b->kpool));
     BRASA_TRY(balloc(b.get(), (uint64_t)m->cfg.layers * b->pool_layer_bytes, &b->vpool));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * b->max_pages * 4, &b->table));

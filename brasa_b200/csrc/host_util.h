@@ -51,6 +51,7 @@ class BrasaFile {
     const std::vector<TensorInfo> &tensors() const { return tensors_; }
     const TensorInfo *tensor(const std::string &name) const;
     const uint8_t *data(const TensorInfo &t) const { return map_ + t.offset; }
+    int fd() const { return fd_; }  // for readers that fetch tensor bytes with pread instead of touching the mapping
     const Json &config() const { return *config_; }
     const std::string &family() const { return family_; }
 

@@ -9,8 +9,10 @@
 // GEMVs on f32 inputs. One token takes the fused decode path: RMSNorm folded into the GEMVs, the
 // residual adds folded into the next GEMV's input stage.
 #include <string.h>
+#include <unistd.h>
 
 #include <chrono>
+#include <thread>
 
 #include "brasa_internal.h"
 #include "decode_token.h"
@@ -62,6 +64,81 @@ int32_t cfg_from_json(brasa_ctx *ctx, const brasa::Json &c, brasa_config *out, s
     return true;
 }
 
+}  // namespace
+
+// File bytes -> device through two pinned buffers (crates/quant/src/brasa_file.rs:64-131 hands out slices of a mapped
+// file; a GPU cannot read those, and a copy straight from pageable memory is staged by the driver one small buffer at a
+// time, after a page fault per 4 KiB of the mapping). Here several host threads pread the file into a pinned chunk (no
+// page of the mapping is touched) while the previous chunk travels by DMA, and nothing waits for the device except the
+// reuse of a chunk: tensors follow one another on the stream.
+struct brasa_model_detail::Stager {
+    static constexpr size_t CHUNK = 32u << 20;
+    static constexpr int THREADS = 4;
+    brasa_ctx *ctx = nullptr;
+    uint8_t *pin[2] = {nullptr, nullptr};
+    cudaEvent_t idle[2] = {nullptr, nullptr};
+    int next = 0;
+    uint64_t bytes = 0;
+
+    int32_t init(brasa_ctx *c) {
+        ctx = c;
+        for (int i = 0; i < 2; ++i) {
+            BRASA_CUDA(ctx, cudaMallocHost((void **)&pin[i], CHUNK));
+            BRASA_CUDA(ctx, cudaEventCreateWithFlags(&idle[i], cudaEventDisableTiming));
+        }
+        return BRASA_OK;
+    }
+    ~Stager() {
+        for (int i = 0; i < 2; ++i) {
+            if (idle[i]) {
+                cudaEventSynchronize(idle[i]);
+                cudaEventDestroy(idle[i]);
+            }
+            if (pin[i]) cudaFreeHost(pin[i]);
+        }
+    }
+    // n bytes of the file at offset file_off (also mapped at src) -> dst (device), asynchronously on the context's stream
+    int32_t upload(void *dst, int fd, uint64_t file_off, const uint8_t *src, size_t n) {
+        bool failed = false;
+        auto fetch = [&failed, fd, file_off, src](uint8_t *to, size_t at, size_t len) {
+            size_t done = 0;
+            while (fd >= 0 && done < len) {
+                const ssize_t r = pread(fd, to + done, len - done, (off_t)(file_off + at + done));
+                if (r <= 0) break;
+                done += (size_t)r;
+            }
+            if (done < len) {
+                if (src) memcpy(to + done, src + at + done, len - done);
+                else failed = true;
+            }
+        };
+        for (size_t off = 0; off < n; off += CHUNK) {
+            const size_t len = std::min(CHUNK, n - off);
+            const int i = next;
+            next ^= 1;
+            BRASA_CUDA(ctx, cudaEventSynchronize(idle[i]));  // the copy that last used this chunk has left it
+            if (len >= (4u << 20)) {
+                std::thread workers[THREADS];
+                const size_t piece = (len / THREADS + 4095) & ~(size_t)4095;
+                for (int t = 0; t < THREADS; ++t) {
+                    const size_t b = std::min(len, piece * t), e = std::min(len, piece * (t + 1));
+                    workers[t] = std::thread([=, &fetch] { if (e > b) fetch(pin[i] + b, off + b, e - b); });
+                }
+                for (auto &w : workers) w.join();
+            } else {
+                fetch(pin[i], off, len);
+            }
+            if (failed) return brasa_fail(ctx, BRASA_EIO, "reading the model file failed");
+            BRASA_CUDA(ctx, cudaMemcpyAsync((uint8_t *)dst + off, pin[i], len, cudaMemcpyHostToDevice, ctx->stream));
+            BRASA_CUDA(ctx, cudaEventRecord(idle[i], ctx->stream));
+        }
+        bytes += n;
+        return BRASA_OK;
+    }
+};
+
+namespace {
+
 int32_t alloc_buf(brasa_model *m, uint64_t bytes, brasa_buf **out, uint64_t *account) {
     BRASA_TRY(brasa_buf_alloc(m->ctx, bytes, out));
     m->owned.push_back(*out);
@@ -75,11 +152,12 @@ int32_t load_f32(brasa_model *m, const brasa::BrasaFile &f, const std::string &n
     if (!t) return brasa_fail(ctx, BRASA_EIO, "missing tensor %s", name.c_str());
     if (t->dtype != "f32" || t->numel() != n) return brasa_fail(ctx, BRASA_EIO, "%s: expected %llu f32 values", name.c_str(), (unsigned long long)n);
     BRASA_TRY(alloc_buf(m, t->nbytes, out, &m->alloc.weights));
-    return brasa_buf_upload(*out, 0, f.data(*t), t->nbytes);
+    return m->stager->upload((*out)->ptr, f.fd(), t->offset, f.data(*t), t->nbytes);
 }
 
 // Uploads a quantised matrix and regroups it into the tiled layout when its shape allows.
-int32_t load_matrix(brasa_model *m, const brasa::BrasaFile &f, const std::string &name, uint32_t rows, uint32_t cols, brasa_buf *staging, Matrix *out) {
+int32_t load_matrix(brasa_model *m, brasa_cmd *load_cmd, const brasa::BrasaFile &f, const std::string &name, uint32_t rows, uint32_t cols, brasa_buf *staging,
+                    Matrix *out) {
     brasa_ctx *ctx = m->ctx;
     const brasa::TensorInfo *t = f.tensor(name);
     if (!t) return brasa_fail(ctx, BRASA_EIO, "missing tensor %s", name.c_str());
@@ -94,16 +172,13 @@ int32_t load_matrix(brasa_model *m, const brasa::BrasaFile &f, const std::string
     out->q.cols = cols;
     if (tiled_ok(qt, rows, cols)) {
         if (brasa_buf_bytes(staging) < t->nbytes) return brasa_fail(ctx, BRASA_EINVAL, "staging buffer too small for %s", name.c_str());
-        BRASA_TRY(brasa_buf_upload(staging, 0, f.data(*t), t->nbytes));
-        brasa_cmd *cmd;
-        BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
-        int32_t rc = brasa_k_repack(cmd, qt, A(staging), A(out->buf), rows, cols);
-        int32_t rc2 = brasa_cmd_wait(cmd, nullptr);
-        BRASA_TRY(rc);
-        BRASA_TRY(rc2);
+        // the file's bytes into the device staging buffer, regrouped from there; the next tensor's upload follows the
+        // regrouping on the same stream, so the host never waits here
+        BRASA_TRY(m->stager->upload(staging->ptr, f.fd(), t->offset, f.data(*t), t->nbytes));
+        BRASA_TRY(brasa_k_repack(load_cmd, qt, A(staging), A(out->buf), rows, cols));
         out->q.layout = BRASA_LAYOUT_TILED;
     } else {
-        BRASA_TRY(brasa_buf_upload(out->buf, 0, f.data(*t), t->nbytes));
+        BRASA_TRY(m->stager->upload(out->buf->ptr, f.fd(), t->offset, f.data(*t), t->nbytes));
         out->q.layout = BRASA_LAYOUT_FILE;
     }
     return BRASA_OK;
@@ -416,23 +491,37 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
         for (auto &t : f->tensors()) biggest = std::max<uint64_t>(biggest, t.nbytes);
         brasa_buf *staging = nullptr;
         BRASA_TRY(brasa_buf_alloc(ctx, biggest, &staging));
+        const auto t_load = std::chrono::steady_clock::now();
+        Stager stager;
+        BRASA_TRY(stager.init(ctx));
+        m->stager = &stager;
+        brasa_cmd *load_cmd = nullptr;
+        BRASA_TRY(brasa_cmd_begin(ctx, &load_cmd));
+        struct CmdGuard {  // the command is waited for and freed on every way out
+            brasa_cmd *&c;
+            brasa_model *m;
+            ~CmdGuard() {
+                if (c) brasa_cmd_wait(c, nullptr);
+                m->stager = nullptr;
+            }
+        } guard{load_cmd, m};
         m->layers.resize(c.layers);
         for (uint32_t i = 0; i < c.layers; ++i) {
             auto n = [&](const char *s) { return "model.layers." + std::to_string(i) + "." + s; };
             Layer &l = m->layers[i];
             BRASA_TRY(load_f32(m, *f, n("input_layernorm.weight"), H, &l.attn_norm));
-            BRASA_TRY(load_matrix(m, *f, n("self_attn.q_proj.weight"), qd, H, staging, &l.wq));
-            BRASA_TRY(load_matrix(m, *f, n("self_attn.k_proj.weight"), kvd, H, staging, &l.wk));
-            BRASA_TRY(load_matrix(m, *f, n("self_attn.v_proj.weight"), kvd, H, staging, &l.wv));
-            BRASA_TRY(load_matrix(m, *f, n("self_attn.o_proj.weight"), H, qd, staging, &l.wo));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("self_attn.q_proj.weight"), qd, H, staging, &l.wq));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("self_attn.k_proj.weight"), kvd, H, staging, &l.wk));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("self_attn.v_proj.weight"), kvd, H, staging, &l.wv));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("self_attn.o_proj.weight"), H, qd, staging, &l.wo));
             BRASA_TRY(load_f32(m, *f, n("self_attn.q_norm.weight"), c.head_dim, &l.q_norm));
             BRASA_TRY(load_f32(m, *f, n("self_attn.k_norm.weight"), c.head_dim, &l.k_norm));
             BRASA_TRY(load_f32(m, *f, n("post_attention_layernorm.weight"), H, &l.ffn_norm));
-            BRASA_TRY(load_matrix(m, *f, n("mlp.gate_proj.weight"), ffn, H, staging, &l.gate));
-            BRASA_TRY(load_matrix(m, *f, n("mlp.up_proj.weight"), ffn, H, staging, &l.up));
-            BRASA_TRY(load_matrix(m, *f, n("mlp.down_proj.weight"), H, ffn, staging, &l.down));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("mlp.gate_proj.weight"), ffn, H, staging, &l.gate));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("mlp.up_proj.weight"), ffn, H, staging, &l.up));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, n("mlp.down_proj.weight"), H, ffn, staging, &l.down));
         }
-        BRASA_TRY(load_matrix(m, *f, "model.embed_tokens.weight", c.vocab, H, staging, &m->embed));
+        BRASA_TRY(load_matrix(m, load_cmd, *f, "model.embed_tokens.weight", c.vocab, H, staging, &m->embed));
         if (m->embed.q.qtype != BRASA_Q8_0 && m->embed.q.qtype != BRASA_Q6_0)
             return brasa_fail(ctx, BRASA_EIO, "the embedding table must be q8_0 or q6_0");
         if (c.tied) m->head = m->embed;
@@ -441,9 +530,17 @@ int32_t brasa_model_load(brasa_ctx *ctx, const char *path, brasa_limits limits, 
             if (ht->shape.size() != 2 || ht->shape[0] == 0 || ht->shape[0] > c.vocab || m->cfg.head_row0 + ht->shape[0] > c.vocab)
                 return brasa_fail(ctx, BRASA_EIO, "lm_head.weight: unexpected shape");
             m->cfg.head_rows = (uint32_t)ht->shape[0];
-            BRASA_TRY(load_matrix(m, *f, "lm_head.weight", m->cfg.head_rows, H, staging, &m->head));
+            BRASA_TRY(load_matrix(m, load_cmd, *f, "lm_head.weight", m->cfg.head_rows, H, staging, &m->head));
         }
         BRASA_TRY(load_f32(m, *f, "model.norm.weight", H, &m->final_norm));
+        {
+            brasa_cmd *c2 = load_cmd;
+            load_cmd = nullptr;
+            BRASA_TRY(brasa_cmd_wait(c2, nullptr));  // every tensor is on the device and regrouped
+        }
+        m->load_bytes = stager.bytes;
+        m->load_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_load).count();
+        m->stager = nullptr;
         // staging is not part of the steady-state footprint
         m->owned.erase(std::remove(m->owned.begin(), m->owned.end(), staging), m->owned.end());
         BRASA_TRY(brasa_buf_free(staging));
@@ -515,6 +612,12 @@ int32_t brasa_model_limits(brasa_model *m, brasa_limits *out) {
 int32_t brasa_model_allocated(brasa_model *m, brasa_allocated *out) {
     if (!m || !out) return BRASA_EINVAL;
     *out = m->alloc;
+    return BRASA_OK;
+}
+int32_t brasa_model_load_stats(brasa_model *m, double *seconds, uint64_t *bytes) {
+    if (!m) return BRASA_EINVAL;
+    if (seconds) *seconds = m->load_seconds;
+    if (bytes) *bytes = m->load_bytes;
     return BRASA_OK;
 }
 int32_t brasa_model_set_prefill_precision(brasa_model *m, int32_t precision) {

@@ -24,6 +24,8 @@ struct Layer {
 inline brasa_arg A(brasa_buf *b, uint64_t off = 0) { return brasa_arg{b, off}; }
 inline float *F(brasa_buf *b, uint64_t off_floats = 0) { return (float *)b->ptr + off_floats; }
 
+struct Stager;
+
 }  // namespace brasa_model_detail
 
 using namespace brasa_model_detail;
@@ -51,5 +53,8 @@ struct brasa_model {
     brasa_allocated alloc{};
     std::vector<brasa_buf *> owned;
     uint32_t *pinned_id = nullptr;  // pinned host word for the per-step token read
+    struct Stager *stager = nullptr;  // pinned staging of the file's bytes while the model loads (null afterwards)
+    double load_seconds = 0.0;        // wall time of brasa_model_load, file bytes read included
+    uint64_t load_bytes = 0;          // tensor bytes that went to the device
 };
 

@@ -260,6 +260,9 @@ void brasa_model_free(brasa_model *m);
 int32_t brasa_model_config(brasa_model *m, brasa_config *out);
 int32_t brasa_model_limits(brasa_model *m, brasa_limits *out);
 int32_t brasa_model_allocated(brasa_model *m, brasa_allocated *out);
+/* How the weights came in: wall seconds from the first tensor to the last one regrouped on the device (the file is read
+ * through two pinned staging buffers while the previous chunk travels by DMA), and the tensor bytes moved. */
+int32_t brasa_model_load_stats(brasa_model *m, double *seconds, uint64_t *bytes);
 int32_t brasa_model_set_prefill_precision(brasa_model *m, int32_t precision); /* qwen3.rs:310 */
 /* Qwen3::forward :763. ids: host u32[tokens]; logits: host f32[logit_rows * vocab] (may be NULL to
  * leave them on the device); gpu_seconds: device time of the call (may be NULL). */
@@ -325,6 +328,26 @@ int32_t brasa_batch_prefix_cache_stats(brasa_batch *b, uint64_t *hit_tokens, uin
 int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params params, uint32_t *out_ids, double *gpu_seconds);
 /* logits [sequences][vocab] of the next token of every sequence, without sampling or advancing */
 int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits);
+/* Memory of a batch before it is created (crates/memory/src/planner.rs:57-95 for the paged pool): the same sums
+ * brasa_batch_create allocates, buffer by buffer. head_rows: the model's lm_head rows (its vocabulary unless it is a
+ * tensor-parallel shard). */
+typedef struct brasa_batch_shape {
+    uint32_t max_seqs, num_pages, max_positions, head_rows;
+    int32_t kv; /* brasa_kv_type */
+} brasa_batch_shape;
+typedef struct brasa_batch_plan {
+    uint64_t kv_pages, tables, logits, attention_partials, sampler, total;
+} brasa_batch_plan;
+int32_t brasa_plan_batch(const brasa_model_shape *m, const brasa_batch_shape *s, brasa_batch_plan *out);
+/* The largest batch that fits (planner.rs:237-281 max_context, for sequences instead of positions): every sequence may
+ * reach positions_per_seq positions, the first shared_prefix of them (a multiple of BRASA_KV_PAGE) held once for all.
+ * budget_bytes 0: the free memory of ctx's device minus a 512 MiB reserve. Returns BRASA_EBUDGET when not even one
+ * sequence fits. *plan_out (optional): the plan of that batch; *num_pages_out: the pages it needs. */
+int32_t brasa_plan_batch_max_seqs(brasa_ctx *ctx, const brasa_model_shape *m, int32_t kv, uint32_t head_rows, uint32_t shared_prefix,
+                                  uint32_t positions_per_seq, uint32_t max_seqs_cap, uint64_t budget_bytes, uint32_t *max_seqs_out,
+                                  uint32_t *num_pages_out, brasa_batch_plan *plan_out);
+/* bytes brasa_batch_create allocated for this batch: equals the total of brasa_plan_batch for its shape */
+int32_t brasa_batch_allocated(brasa_batch *b, uint64_t *bytes);
 uint32_t brasa_batch_sequences(brasa_batch *b);
 uint32_t brasa_batch_pages_in_use(brasa_batch *b);
 

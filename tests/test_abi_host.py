@@ -132,3 +132,31 @@ def test_no_cpu_fallback_without_a_device(B):
     with pytest.raises(B.BrasaError) as e:
         B.Context(0)
     assert e.value.code == B.ECUDA
+
+
+def test_batch_planner_arithmetic_and_largest_batch(B):
+    """The paged pool's plan (crates/memory/src/planner.rs:57-95 retargeted): every buffer of a batch at the allocation
+    granularity, and the largest batch that fits a budget (planner.rs:237-281 for sequences): one more sequence than
+    the answer does not fit, the answer does."""
+    shape = B._ModelShape(0, 36, 2560, 32, 8, 128, 9728, 151936)  # the Qwen3-4B architecture
+    bb = B.planner.buffer_bytes
+    p = B.planner.plan_batch(shape, 64, 2048 // 16 + 64 * 97, 3600, B.KvType.F16)
+    row = 8 * 128 * 2
+    assert p["kv_pages"] == 2 * bb(36 * (128 + 64 * 97) * 16 * row)
+    assert p["tables"] == bb(64 * 225 * 4) + 3 * bb(64 * 4) + bb(64 * 16)
+    assert p["logits"] == bb(64 * 151936 * 4) and p["sampler"] == bb(64 * 2 * 151936 * 4)
+    assert p["attention_partials"] == bb(64 * 32 * ((225 * 16 + 127) // 128) * 130 * 4)
+    assert p["total"] == sum(v for k, v in p.items() if k != "total")
+    q8 = B.planner.plan_batch(shape, 64, 2048 // 16 + 64 * 97, 3600, B.KvType.Q8_0)
+    assert q8["kv_pages"] == 2 * bb(36 * (128 + 64 * 97) * 16 * 8 * 136)
+    # 64 sequences of 3 600 positions behind a 2 048-token shared prefix: 13.9 GiB of pages; 31.5 GiB without sharing
+    assert abs(p["kv_pages"] / 2**30 - 13.92) < 0.05
+    budget = 40 << 30
+    n, pages, plan = B.planner.max_batch(None, shape, B.KvType.F16, 2048, 3600, budget=budget)
+    assert n > 64 and plan["total"] <= budget and pages == 128 + n * 97
+    more = B.planner.plan_batch(shape, n + 1, 128 + (n + 1) * 97, 3600, B.KvType.F16)
+    assert more["total"] > budget
+    n0, _, _ = B.planner.max_batch(None, shape, B.KvType.F16, 2048, 3600, budget=1 << 20)
+    assert n0 == 0
+    n_cap, _, _ = B.planner.max_batch(None, shape, B.KvType.F16, 2048, 3600, budget=budget, cap=10)
+    assert n_cap == 10

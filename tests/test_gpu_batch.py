@@ -195,3 +195,25 @@ def test_prefix_cache_finds_pages_of_earlier_sequences(B, golden_dir):
                 top2 = np.sort(want_logits[i])[-2:]
                 assert top2[1] - top2[0] <= 4e-3 * scale, (s, i)
                 break
+
+
+def test_batch_plan_equals_allocated_and_rejects_what_cannot_fit(B, golden_dir):
+    """crates/runtime/tests/planner.rs:59-62 for the paged pool: the plan made before brasa_batch_create equals what it
+    allocates; a pool larger than the device is refused with BRASA_EBUDGET before anything is allocated."""
+    path = golden_dir / "tiny" / "model.brasa"
+    ctx = B.Context(0)
+    m = B.Qwen3.load(ctx, path, B.Limits(ctx=512, max_tokens=64, max_logit_rows=1, kv=B.KvType.Q8_0))
+    try:
+        shape, _ = B.model_shape(path)
+        bt = B.Batch(m, max_seqs=7, num_pages=150, max_positions=400)
+        plan = B.planner.plan_batch(shape, 7, 150, 400, B.KvType.Q8_0)
+        assert bt.allocated() == plan["total"]
+        bt.free()
+        free0, _ = ctx.mem_info()
+        with pytest.raises(B.BrasaError) as e:
+            B.Batch(m, max_seqs=7, num_pages=2_000_000_000, max_positions=400)
+        assert e.value.code == B.EBUDGET
+        free1, _ = ctx.mem_info()
+        assert abs(free1 - free0) < (64 << 20)
+    finally:
+        m.free()
