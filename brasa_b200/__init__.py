@@ -416,6 +416,13 @@ class Kernels:
             self._k(self.L.brasa_k_tp_allreduce_add_phase(cmd._h, tp._h, _arg(partial), _arg(resid), _arg(out), C.c_uint64(n),
                                                           C.c_int32(int(phase == "gather"))))
 
+    def gemv_allreduce(self, cmd, tp, w: QMatrix, x, resid, out, phase=None):
+        """out = resid + sum over ranks of (w x); phase "push" / "gather" runs one half (ranks sharing a device)."""
+        if phase is None:
+            self._k(self.L.brasa_k_gemv_allreduce(cmd._h, tp._h, w._c(), _arg(x), _arg(resid), _arg(out)))
+        else:
+            self._k(self.L.brasa_k_gemv_allreduce_phase(cmd._h, tp._h, w._c(), _arg(x), _arg(resid), _arg(out), C.c_int32(1 if phase == "gather" else 0)))
+
     def tp_argmax(self, cmd, tp, logits, n, row0, out, phase=None):
         if phase is None:
             self._k(self.L.brasa_k_tp_argmax(cmd._h, tp._h, _arg(logits), C.c_uint32(n), C.c_uint32(row0), _arg(out)))

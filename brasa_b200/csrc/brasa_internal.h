@@ -68,6 +68,23 @@ struct brasa_tp_token_area {
 };
 bool brasa_tp_token_area_get(brasa_tp *tp, brasa_tp_token_area *out);
 
+// Where a kernel of this rank writes its share of an all-reduce: slot [rank] of every rank's exchange buffer
+// ([2 parities][world][max_elems] words {f32, exchange number}); state[0] counts the exchanges done so far.
+struct brasa_tp_push_target {
+    unsigned long long *peer[BRASA_TP_MAX_RANKS];
+    uint32_t world, rank;
+    uint64_t max_elems;
+    const uint32_t *state;
+};
+bool brasa_tp_push_target_get(brasa_tp *tp, brasa_tp_push_target *out);
+
+// The row-owning GEMV over tiled q4_0 / q6_0 matrices (gemv.cu). epilogue: 0 y = scale * W x, 1 SwiGLU (w[0] = gate,
+// w[1] = up, y[0]), 2 y = resid + W x, 3 W x pushed into the tensor-parallel exchange buffers named by `push`.
+int32_t brasa_tp_gemv_allreduce_launch(brasa_cmd *cmd, brasa_tp *tp, const brasa_qmatrix &w, const float *x, const float *resid, float *out, int phases);
+int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x, const float *h,
+                          const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps, int epilogue, const float *resid,
+                          const brasa_tp_push_target *push = nullptr);
+
 // Phase time stamps of the GEMV and whole-token kernels exist only in builds with -DBRASA_TRACE_BUILD (a
 // developer's build; the shipped library carries neither the stamps nor these entry points).
 #ifdef BRASA_TRACE_BUILD

@@ -32,7 +32,7 @@ namespace {
 
 constexpr int GEMV_WARPS = 16;              // consumer warps per block; column slices per row divide it
 
-enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2 };
+enum { EPI_SCALE = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_PUSH = 3 };
 
 struct GemvParams {
     const uint8_t *w[3];
@@ -52,6 +52,9 @@ struct GemvParams {
     const float *x, *h, *normw, *ss;
     float *x_out;          // when h is given: block 0 writes x + h here
     const float *resid;    // EPI_RESID: y = resid + W x
+    // EPI_PUSH (tensor parallel): W x is this rank's share of a sum over ranks; every output goes, tagged with the
+    // exchange number, into slot [this rank] of every rank's exchange buffer instead of a local vector
+    brasa_tp_push_target push;
     uint32_t nss;
     int scaled;            // multiply outputs by 1/sqrt(mean(x^2) + eps)
     float eps;
@@ -340,7 +343,15 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
                 uint32_t r = seg_first[i] + j;
                 v *= scale;
                 if (p.epilogue == EPI_RESID) v += (i == 0 && j == threadIdx.x) ? resid : p.resid[r];
-                p.y[i][r] = v;
+                if (p.epilogue == EPI_PUSH) {
+                    const uint32_t e = *reinterpret_cast<const volatile uint32_t *>(p.push.state);
+                    const unsigned long long word = (unsigned long long)__float_as_uint(v) | ((unsigned long long)(e + 1) << 32);
+                    const uint64_t at = (uint64_t)(e & 1) * p.push.world * p.push.max_elems + (uint64_t)p.push.rank * p.push.max_elems + r;
+                    for (uint32_t q = 0; q < p.push.world; ++q)
+                        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.push.peer[q] + at), "l"(word) : "memory");
+                } else {
+                    p.y[i][r] = v;
+                }
             }
         }
     }
@@ -423,9 +434,13 @@ void brasa_gemv_hint_next(brasa_ctx *ctx, uint32_t nmat, const brasa_qmatrix *w,
 // epilogue: 0 scale, 1 SwiGLU (w[0] = gate, w[1] = up, y[0]), 2 residual (y = resid + W x).
 int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
                           const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
-                          int epilogue, const float *resid) {
+                          int epilogue, const float *resid, const brasa_tp_push_target *push) {
     brasa_ctx *ctx = cmd->ctx;
     GemvParams p{};
+    if (epilogue == EPI_PUSH) {
+        BRASA_REQUIRE(ctx, push && nmat == 1 && push->world >= 1 && w[0].rows <= push->max_elems, "gemv push: one matrix whose rows fit the exchange buffer");
+        p.push = *push;
+    }
     p.nmat = nmat;
     p.cols = w[0].cols;
     uint32_t total_rows = 0;
@@ -544,7 +559,7 @@ int32_t gemv_any(brasa_cmd *cmd, const brasa_qmatrix &w, brasa_arg x, brasa_arg 
         for (uint32_t t = 0; t < tokens; ++t) {
             float *yt = (float *)arg_ptr(y) + (size_t)t * w.rows;
             BRASA_TRY(brasa_gemv_launch(cmd, w.qtype, 1, &w, &yt, (const float *)arg_ptr(x) + (size_t)t * w.cols, nullptr, nullptr, nullptr, ssp,
-                                        nss, scaled, eps, EPI_SCALE, nullptr));
+                                        nss, scaled, eps, EPI_SCALE, nullptr, nullptr));
         }
         return BRASA_OK;
     }
@@ -594,7 +609,7 @@ int32_t brasa_k_gemv_scaled3(brasa_cmd *cmd, const brasa_qmatrix w[3], brasa_arg
     BRASA_REQUIRE(ctx, arg_fits(xw, (uint64_t)w[0].cols * 4) && arg_fits(ss, (uint64_t)nss * 4), "gemv_scaled3: xw or ss too small");
     float *ys[3] = {(float *)arg_ptr(y[0]), (float *)arg_ptr(y[1]), (float *)arg_ptr(y[2])};
     return brasa_gemv_launch(cmd, BRASA_Q4_0, 3, w, ys, (const float *)arg_ptr(xw), nullptr, nullptr, nullptr, (const float *)arg_ptr(ss), nss, 1,
-                             eps, EPI_SCALE, nullptr);
+                             eps, EPI_SCALE, nullptr, nullptr);
 }
 
 int32_t brasa_k_gemv_scaled_swiglu(brasa_cmd *cmd, brasa_qmatrix gate, brasa_qmatrix up, brasa_arg xw, brasa_arg ss, float eps, brasa_arg y) {
@@ -609,7 +624,7 @@ int32_t brasa_k_gemv_scaled_swiglu(brasa_cmd *cmd, brasa_qmatrix gate, brasa_qma
         brasa_qmatrix w[2] = {gate, up};
         float *ys[2] = {(float *)arg_ptr(y), nullptr};
         return brasa_gemv_launch(cmd, BRASA_Q4_0, 2, w, ys, (const float *)arg_ptr(xw), nullptr, nullptr, nullptr, (const float *)arg_ptr(ss), nss,
-                                 1, eps, EPI_SWIGLU, nullptr);
+                                 1, eps, EPI_SWIGLU, nullptr, nullptr);
     }
     // file layout: gate into y, up into scratch, then SwiGLU in place
     BRASA_TRY(brasa_gemv_scratch(ctx, gate.rows, 1));

@@ -19,9 +19,6 @@
 #include "host_util.h"
 #include "model_internal.h"
 
-int32_t brasa_gemv_launch(brasa_cmd *cmd, int qtype, uint32_t nmat, const brasa_qmatrix *w, float *const *y, const float *x,
-                          const float *h, const float *normw, float *x_out, const float *ss, uint32_t nss, int scaled, float eps,
-                          int epilogue, const float *resid);
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
 void brasa_gemv_hint_next(brasa_ctx *ctx, uint32_t nmat, const brasa_qmatrix *w, bool swiglu);
 int32_t brasa_advance_launch(brasa_cmd *cmd, uint32_t *ids, const uint32_t *next, uint32_t *out_ids, uint32_t *out_count, uint32_t out_cap,
@@ -299,9 +296,7 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
             brasa_qmatrix nxt[2] = {l.gate.q, l.up.q};
             brasa_gemv_hint_next(m->ctx, 2, nxt, true);
             if (m->tp) {  // this rank's part of Wo attn, then the sum over ranks lands in x
-                float *part[1] = {F(m->h)};
-                BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, part, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, SCALE, nullptr));
-                BRASA_TRY(residual_add(m, cmd, c.hidden));
+                BRASA_TRY(brasa_tp_gemv_allreduce_launch(cmd, m->tp, l.wo.q, F(m->attn), x, x, 3));
             } else
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.wo.q, y, F(m->attn), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }
@@ -321,9 +316,7 @@ int32_t encode_decode_token(brasa_model *m, brasa_cmd *cmd, uint32_t layer_begin
                 brasa_gemv_hint_next(m->ctx, 1, &m->head.q, false);
             }
             if (m->tp) {
-                float *part[1] = {F(m->h)};
-                BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, part, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, SCALE, nullptr));
-                BRASA_TRY(residual_add(m, cmd, c.hidden));
+                BRASA_TRY(brasa_tp_gemv_allreduce_launch(cmd, m->tp, l.down.q, F(m->gate), x, x, 3));
             } else
             BRASA_TRY(brasa_gemv_launch(cmd, BRASA_Q4_0, 1, &l.down.q, y, F(m->gate), nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, RESID, x));
         }

@@ -19,6 +19,7 @@
 #include "brasa_internal.h"
 
 int32_t brasa_argmax_launch(brasa_cmd *cmd, const float *logits, uint32_t n, uint32_t *out);
+int32_t brasa_tp_allreduce_add_launch(brasa_cmd *cmd, brasa_tp *tp, const float *src, const float *resid, float *out, uint64_t n, int phases);
 
 struct brasa_tp {
     brasa_ctx *ctx = nullptr;
@@ -184,6 +185,33 @@ bool brasa_tp_token_area_get(brasa_tp *tp, brasa_tp_token_area *out) {
     return true;
 }
 
+bool brasa_tp_push_target_get(brasa_tp *tp, brasa_tp_push_target *out) {
+    if (!tp || !out || !tp->connected) return false;
+    for (uint32_t r = 0; r < BRASA_TP_MAX_RANKS; ++r) out->peer[r] = r < tp->world ? reinterpret_cast<unsigned long long *>(tp->peer[r]) : nullptr;
+    out->world = tp->world;
+    out->rank = tp->rank;
+    out->max_elems = tp->max_elems;
+    out->state = tp->state;
+    return true;
+}
+
+// y = W x of a column-split matrix (o_proj, down_proj) summed over the ranks, plus the residual: the GEMV's epilogue
+// writes its rows straight into every rank's exchange slot (no local vector, no separate send pass), and the receive
+// half of the exchange adds the slots in rank order. phases as in brasa_tp_allreduce_add_launch.
+int32_t brasa_tp_gemv_allreduce_launch(brasa_cmd *cmd, brasa_tp *tp, const brasa_qmatrix &w, const float *x, const float *resid, float *out, int phases) {
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, tp->connected, "tp: the ranks are not connected yet");
+    BRASA_REQUIRE(ctx, w.rows % 2 == 0 && w.rows <= tp->max_elems, "tp gemv: %u rows (even, at most %llu)", w.rows, (unsigned long long)tp->max_elems);
+    if (phases & TP_PUSH) {
+        brasa_tp_push_target target;
+        brasa_tp_push_target_get(tp, &target);
+        float *none[1] = {nullptr};
+        BRASA_TRY(brasa_gemv_launch(cmd, w.qtype, 1, &w, none, x, nullptr, nullptr, nullptr, nullptr, 0, 0, 0.0f, 3, nullptr, &target));
+    }
+    if (phases & TP_GATHER) BRASA_TRY(brasa_tp_allreduce_add_launch(cmd, tp, nullptr, resid, out, w.rows, TP_GATHER));
+    return BRASA_OK;
+}
+
 int32_t brasa_tp_allreduce_add_launch(brasa_cmd *cmd, brasa_tp *tp, const float *src, const float *resid, float *out, uint64_t n, int phases) {
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, tp->connected, "tp: the ranks are not connected yet");
@@ -326,6 +354,26 @@ int32_t brasa_k_tp_argmax(brasa_cmd *cmd, brasa_tp *tp, brasa_arg logits, uint32
     BRASA_REQUIRE(ctx, ctx == tp->ctx, "tp: command of another context");
     BRASA_REQUIRE(ctx, n > 0 && arg_fits(logits, (uint64_t)n * 4) && arg_fits(out_u32, 4), "tp argmax: buffers too small");
     return brasa_tp_argmax_launch(cmd, tp, (const float *)arg_ptr(logits), n, row0, (uint32_t *)arg_ptr(out_u32), TP_PUSH | TP_GATHER);
+}
+
+static int32_t gemv_allreduce_checked(brasa_cmd *cmd, brasa_tp *tp, brasa_qmatrix w, brasa_arg x, brasa_arg resid, brasa_arg out, int phases) {
+    if (!cmd || !tp) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_REQUIRE(ctx, ctx == tp->ctx, "tp: command of another context");
+    BRASA_REQUIRE(ctx, w.layout == BRASA_LAYOUT_TILED && (w.qtype == BRASA_Q4_0 || w.qtype == BRASA_Q6_0), "tp gemv: a tiled q4_0 or q6_0 matrix");
+    BRASA_REQUIRE(ctx, arg_fits(x, (uint64_t)w.cols * 4) && arg_fits(out, (uint64_t)w.rows * 4) && (!resid.buf || arg_fits(resid, (uint64_t)w.rows * 4)),
+                  "tp gemv: buffers too small");
+    BRASA_REQUIRE(ctx, x.offset % 16 == 0 && out.offset % 8 == 0 && resid.offset % 8 == 0, "tp gemv: misaligned");
+    return brasa_tp_gemv_allreduce_launch(cmd, tp, w, (const float *)arg_ptr(x), resid.buf ? (const float *)arg_ptr(resid) : nullptr, (float *)arg_ptr(out),
+                                          phases);
+}
+
+int32_t brasa_k_gemv_allreduce(brasa_cmd *cmd, brasa_tp *tp, brasa_qmatrix w, brasa_arg x, brasa_arg resid, brasa_arg out) {
+    return gemv_allreduce_checked(cmd, tp, w, x, resid, out, TP_PUSH | TP_GATHER);
+}
+
+int32_t brasa_k_gemv_allreduce_phase(brasa_cmd *cmd, brasa_tp *tp, brasa_qmatrix w, brasa_arg x, brasa_arg resid, brasa_arg out, int32_t gather) {
+    return gemv_allreduce_checked(cmd, tp, w, x, resid, out, gather ? TP_GATHER : TP_PUSH);
 }
 
 // The two halves of an exchange as separate launches, for ranks that share one device: a kernel that waits for a

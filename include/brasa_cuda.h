@@ -375,6 +375,13 @@ int32_t brasa_tp_connect_same_process(brasa_tp *const *tps, uint32_t n); /* rank
 int32_t brasa_tp_set_poll_limit(brasa_tp *tp, uint32_t polls);
 /* out = resid + sum over ranks of partial (resid.buf NULL: out = the sum); n even; identical bits on every rank */
 int32_t brasa_k_tp_allreduce_add(brasa_cmd *cmd, brasa_tp *tp, brasa_arg partial, brasa_arg resid, brasa_arg out, uint64_t n);
+/* out = resid + sum over ranks of (w x): the GEMV of a column-split o_proj / down_proj (crates/kernels/src/lib.rs:781-810
+ * gemv, matmul.metal:243) fused with the exchange: the GEMV's epilogue stores this rank's rows straight into every rank's
+ * exchange slot over peer memory (plain stores: no TMA, no multicast), the receive half adds the slots in rank order.
+ * w: tiled q4_0 / q6_0, rows even and <= max_elems; x f32[cols]; resid.buf NULL: out = the sum. */
+int32_t brasa_k_gemv_allreduce(brasa_cmd *cmd, brasa_tp *tp, brasa_qmatrix w, brasa_arg x, brasa_arg resid, brasa_arg out);
+/* its send (gather = 0: the GEMV) and receive (gather = 1) halves, for ranks that share one device */
+int32_t brasa_k_gemv_allreduce_phase(brasa_cmd *cmd, brasa_tp *tp, brasa_qmatrix w, brasa_arg x, brasa_arg resid, brasa_arg out, int32_t gather);
 /* argmax over the concatenation of every rank's logits[n] (this rank's rows start at row0): out_u32 = global index */
 int32_t brasa_k_tp_argmax(brasa_cmd *cmd, brasa_tp *tp, brasa_arg logits, uint32_t n, uint32_t row0, brasa_arg out_u32);
 /* the send (gather = 0) and receive (gather = 1) halves as separate launches, for ranks that share one device:
