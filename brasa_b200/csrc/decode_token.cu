@@ -7,8 +7,7 @@
 //   * Weights never wait. Every block owns the same share of rows of every matrix, known when the model is loaded,
 //     so its weight traffic is a fixed list of byte ranges (slots). They stream through a shared-memory ring with
 //     bulk async copies; the warp that is last to finish with a slot starts the copy that reuses it, across
-//     operation boundaries, and asks L2 for the slots a little further down the list. HBM keeps working while the
-//     blocks exchange activations.
+//     operation boundaries. HBM keeps working while the blocks exchange activations.
 //   * Activations cross blocks without barriers. Every activation vector lives in L2 as 8-byte words
 //     {float, epoch}; a consumer polls the words it needs until they carry the epoch of the producing operation of
 //     this launch. A single 8-byte store is indivisible, so no fence, flag or grid barrier is needed, and one round
@@ -37,7 +36,6 @@ constexpr uint32_t SLOT_CAP = 24 * 1024;   // bytes of one ring slot
 constexpr uint32_t POLL_LIMIT = 1u << 20;  // polls of an activation word before the wait gives up
 constexpr int R = 2;                       // rows a warp works on at a time
 constexpr int NMAX = 5;                    // half blocks of x a lane keeps per column slice
-constexpr uint32_t L2_AHEAD = 8;           // slots asked from L2 beyond the ring
 constexpr uint32_t EPOCH_SPAN = 1024;      // epochs of one launch; operations + 2 must stay below it
 
 enum { OP_GEMV = 0, OP_ATTN = 1 };
@@ -227,12 +225,6 @@ __device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s)
     mbar_expect_tx(&c.full[s], d.z);
     bulk_g2s(c.ring + (size_t)s * SLOT_CAP, src, d.z, &c.full[s]);
 }
-__device__ __forceinline__ void l2_ask(uint4 d) {
-    const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
-#ifndef BRASA_NO_L2ASK
-    if (d.z) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(d.z) : "memory");
-#endif
-}
 
 // ---- GEMV, phase 1: wait for the input, fold the norm weight, convert to fixed point (thread t: half blocks t, t + 512, ..).
 // Returns the thread's share of sum x^2.
@@ -352,7 +344,6 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
                 c.done[rs] = 0;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue_slot(c, c.sdesc[j], rs);
-                l2_ask(c.sdesc[j + L2_AHEAD]);
             }
         }
         kk += 2;
@@ -731,7 +722,6 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
     if (tid == 0) {
         uint32_t k = 0;
         for (; k < c.my_slots && k < p.nslot; ++k) issue_slot(c, c.myslots[k], k);
-        for (; k < c.my_slots && k < p.nslot + L2_AHEAD; ++k) l2_ask(c.myslots[k]);
     }
 
     // This warp's slots are the list entries kk = sub, sub + 2, ..: warps 0-7 take the even ones, warps 8-15 the odd
@@ -758,7 +748,7 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
             const uint32_t lRPS = 4 - op.log2S, RPS = 1u << lRPS;
             const uint32_t total_slots = (((bo[1] & 0xffffu) + RPS - 1) >> lRPS) + (((bo[1] >> 16) + RPS - 1) >> lRPS) + ((bo[2] + RPS - 1) >> lRPS);
             // the descriptors this operation's refills and L2 requests will need, fetched by the threads that poll least
-            for (uint32_t i = TK_THREADS - 1 - tid; i < total_slots + L2_AHEAD; i += TK_THREADS) {
+            for (uint32_t i = TK_THREADS - 1 - tid; i < total_slots; i += TK_THREADS) {
                 const uint32_t k = gslot + p.nslot + i;
                 c.sdesc[i] = k < c.my_slots ? c.myslots[k] : make_uint4(0, 0, 0, 0);
             }
@@ -1059,7 +1049,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     p.xf_bytes = (uint32_t)((std::max<size_t>((size_t)max_cols / 16 * 16 * (m.kv == BRASA_KV_F32 ? XRec<3>::CHUNKS : XRec<2>::CHUNKS), attn_bytes) + 127) / 128 * 128);
     p.part_floats = (part_floats + 3) & ~3u;
     p.resid_floats = ((H + G - 1) / G + 4) & ~3u;
-    p.sdesc_n = max_op_slots + L2_AHEAD;
+    p.sdesc_n = max_op_slots;
     p.nw_floats = (nw_floats + 3) & ~3u;
     const size_t fixed = p.xf_bytes + (size_t)(p.part_floats + p.resid_floats + p.nw_floats) * 4 + (size_t)p.sdesc_n * 16 + 48 * 4 + 2 * OPS_WORDS * 4 + 16;
     BRASA_REQUIRE(ctx, fixed + 2 * (SLOT_CAP + 12) + 1024 <= ctx->smem_optin, "token program: the model's vectors do not fit shared memory");

@@ -284,7 +284,7 @@ def test_prefill_gemm_real_shapes_every_block_shape(B, ctx, K, rows, cols):
     w = tiled_q4(B, ctx, K, raw, rows, cols)
     idx = sampled_rows(rows, 3 if rows > 4096 else 4)
     sub = take_rows(raw, rows, cols, idx)
-    for tokens in (3584, 1024, 512, 333, 64):
+    for tokens in (3584, 1024, 512, 333, 64, 37, 9):
         xh = rng.vec(tokens * cols, 1.0).astype(np.float16)
         gx, gy = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4)
         run(ctx, lambda c: K.gemm(c, w, gx, gy, tokens))
@@ -303,7 +303,7 @@ def test_prefill_gemm_real_shapes_every_block_shape(B, ctx, K, rows, cols):
         gy.free()
 
 
-@pytest.mark.parametrize("tokens", [3584, 512, 200])
+@pytest.mark.parametrize("tokens", [3584, 512, 200, 64, 23])
 def test_prefill_gemm_swiglu_real_shape(B, ctx, K, tokens):
     """gate and up of the 4B model (9 728 x 2 560 each) as the one-launch SwiGLU GEMM: sampled rows of every tile."""
     rows, cols = 9728, 2560
