@@ -52,9 +52,12 @@ SEED = 20251
 GATE_UP_TRAFFIC_BYTES = 28_130_000
 # dram__bytes_read + dram__bytes_write of one decode_token_kernel launch at position 512 under ncu (algorithmic bytes at
 # that position: 2 436 050 976)
-TOKEN_KERNEL_TRAFFIC_BYTES = 2_453_830_000
-# dram__bytes_read + dram__bytes_write of one serving decode step of 64 sequences (all its kernels) under ncu; None until captured
-SERVING_STEP_TRAFFIC_BYTES = None
+TOKEN_KERNEL_TRAFFIC_BYTES = 2_454_140_000
+# dram__bytes_read + dram__bytes_write of one serving decode step of 64 sequences (all its kernels, summed) under ncu,
+# captured at the first steps of the leg, where a step's algorithmic bytes are the second figure; the leg scales the
+# traffic to its own mean position by its algorithmic bytes (the KV share grows in proportion, the weights do not move)
+SERVING_STEP_TRAFFIC_BYTES = 14_554_000_000
+SERVING_STEP_TRAFFIC_AT_ALGORITHMIC_BYTES = 12_387_561_504
 METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
 WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
 
@@ -440,7 +443,8 @@ def serving_leg(B, ctx, path, cfg, rank: int, seqs: int = 64, prefix: int = 2048
         t_step = secs / steps
         roof = {"bound": "hbm", "kernel": "one decode step of 64 sequences (paged attention + 64-token GEMMs + sampler)",
                 "achieved": min_bytes / t_step / 1e9, "peak": hbm, "unit": "GB/s", "frac": min_bytes / t_step / 1e9 / hbm, "peak_source": hbm_kind,
-                "algorithmic_bytes_per_step": min_bytes, "traffic": SERVING_STEP_TRAFFIC_BYTES,
+                "algorithmic_bytes_per_step": min_bytes,
+                "traffic": SERVING_STEP_TRAFFIC_BYTES * min_bytes / SERVING_STEP_TRAFFIC_AT_ALGORITHMIC_BYTES,
                 "note": "numerator: weights once + the shared prefix's KV once + every sequence's own KV; `achieved_gbs` below counts the "
                         "prefix once per sequence, as the configuration's 33.77 GB per step does"}
         return {"sequences": seqs, "roofline": roof, "shared_prefix_tokens": prefix, "own_prompt_tokens": suffix, "decode_steps": steps,
@@ -1019,7 +1023,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * PROMPT + 4 * steps_tokens, "d2h_bytes_per_step": 4 * GENERATE,
                     "prefill_tok_s": statistics.median(prefill_vals), "same_tokens_as_device_resident": same_tokens},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "model_load": load_stats,
             "roofline": roof,
             "gemv_roofline": gemv_roof,
             "prefill_16k": long_prefill,
