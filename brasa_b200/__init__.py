@@ -90,6 +90,11 @@ class _AttnShape(C.Structure):
                 ("kv", C.c_int32)]
 
 
+class _PagedKv(C.Structure):
+    _fields_ = [("kpool", _Arg), ("vpool", _Arg), ("table", _Arg), ("lens", _Arg), ("seqs", C.c_uint32), ("max_pages", C.c_uint32),
+                ("num_pages", C.c_uint32), ("kv", C.c_int32)]
+
+
 class _ModelShape(C.Structure):
     _fields_ = [("weight_bytes", C.c_uint64), ("layers", C.c_uint32), ("hidden", C.c_uint32), ("heads", C.c_uint32),
                 ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32)]
@@ -519,6 +524,19 @@ class Kernels:
         cd = (_Arg * 2)(*[_arg(a) for a in dst])
         self._k(self.L.brasa_k_qk_norm_rope_store(cmd._h, C.c_int32(int(kv)), cq, cn, C.c_float(eps), _arg(table.cos), _arg(table.sin),
                                                   C.c_uint32(table.dim), C.c_uint32(table.max_pos), cd, shape._c()))
+
+    @staticmethod
+    def paged_kv(kpool, vpool, table, lens, seqs: int, max_pages: int, num_pages: int, kv) -> _PagedKv:
+        """One layer's KV pages, the sequences' page tables (i32 [seqs][max_pages]) and lengths (u32 [seqs]) on the device."""
+        return _PagedKv(_arg(kpool), _arg(vpool), _arg(table), _arg(lens), seqs, max_pages, num_pages, int(kv))
+
+    def qk_norm_rope_store_paged(self, cmd, q, k, v, q_norm, k_norm, eps, table: RopeTable, paged: _PagedKv, hq: int, hkv: int):
+        self._k(self.L.brasa_k_qk_norm_rope_store_paged(cmd._h, _arg(q), _arg(k), _arg(v), _arg(q_norm), _arg(k_norm), _arg(table.cos), _arg(table.sin),
+                                                        C.c_float(eps), paged, C.c_uint32(hq), C.c_uint32(hkv)))
+
+    def decode_attention_paged(self, cmd, q, paged: _PagedKv, partials, o, hq: int, hkv: int):
+        self._k(self.L.brasa_k_decode_attention_paged(cmd._h, _arg(q), paged, _arg(partials), C.c_uint64(partials.nbytes // 4), _arg(o),
+                                                      C.c_uint32(hq), C.c_uint32(hkv)))
 
     def store_kv(self, cmd, kv, src, dst, n):
         self._k(self.L.brasa_k_store_kv(cmd._h, C.c_int32(int(kv)), _arg(src), _arg(dst), C.c_uint64(n)))

@@ -624,6 +624,79 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
 
 extern "C" {
 
+static int32_t check_paged(brasa_ctx *ctx, const brasa_paged_kv &pg, uint32_t hq, uint32_t hkv) {
+    BRASA_REQUIRE(ctx, pg.kv >= BRASA_KV_F32 && pg.kv <= BRASA_KV_Q8_0, "paged kv: unknown KV type %d", pg.kv);
+    BRASA_REQUIRE(ctx, hkv > 0 && hq % hkv == 0 && hq / hkv <= 8, "paged kv: GQA group must divide and be <= 8");
+    BRASA_REQUIRE(ctx, pg.seqs >= 1 && pg.max_pages >= 1 && pg.num_pages >= 1, "paged kv: empty batch or pool");
+    const uint64_t pool_bytes = brasa_kv_bytes(pg.kv, (uint64_t)pg.num_pages * PAGE * hkv * 128);
+    BRASA_REQUIRE(ctx, arg_fits(pg.kpool, pool_bytes) && arg_fits(pg.vpool, pool_bytes), "paged kv: the pools are smaller than num_pages pages");
+    BRASA_REQUIRE(ctx, arg_fits(pg.table, (uint64_t)pg.seqs * pg.max_pages * 4) && arg_fits(pg.lens, (uint64_t)pg.seqs * 4), "paged kv: table or lens too small");
+    BRASA_REQUIRE(ctx, pg.kpool.offset % 16 == 0 && pg.vpool.offset % 16 == 0 && pg.table.offset % 4 == 0 && pg.lens.offset % 4 == 0, "paged kv: misaligned");
+    return BRASA_OK;
+}
+
+int32_t brasa_k_qk_norm_rope_store_paged(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg q_norm, brasa_arg k_norm, brasa_arg rope_cos,
+                                         brasa_arg rope_sin, float eps, brasa_paged_kv pg, uint32_t hq, uint32_t hkv) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_TRY(check_paged(ctx, pg, hq, hkv));
+    BRASA_REQUIRE(ctx, arg_fits(q, (uint64_t)pg.seqs * hq * 512) && arg_fits(k, (uint64_t)pg.seqs * hkv * 512) && arg_fits(v, (uint64_t)pg.seqs * hkv * 512),
+                  "qk_norm_rope_store_paged: q, k or v too small");
+    BRASA_REQUIRE(ctx, arg_fits(q_norm, 512) && arg_fits(k_norm, 512), "qk_norm_rope_store_paged: norm weights too small");
+    // the tables must cover every position a sequence of max_pages pages can reach
+    const uint64_t table_floats = (uint64_t)pg.max_pages * PAGE * 64;
+    BRASA_REQUIRE(ctx, arg_fits(rope_cos, table_floats * 4) && arg_fits(rope_sin, table_floats * 4), "qk_norm_rope_store_paged: RoPE tables shorter than max_pages pages");
+    const uint32_t rows = pg.seqs * (hq + 2 * hkv);
+    float *qp = (float *)arg_ptr(q), *kp = (float *)arg_ptr(k);
+    const float *vp = (const float *)arg_ptr(v), *qn = (const float *)arg_ptr(q_norm), *kn = (const float *)arg_ptr(k_norm),
+                *cs = (const float *)arg_ptr(rope_cos), *sn = (const float *)arg_ptr(rope_sin);
+    const int32_t *table = (const int32_t *)arg_ptr(pg.table);
+    const uint32_t *lens = (const uint32_t *)arg_ptr(pg.lens);
+#define STORE_PAGED(KVT)                                                                                                                      \
+    qk_norm_rope_store_paged_kernel<KVT><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(qp, kp, vp, qn, kn, cs, sn, arg_ptr(pg.kpool), arg_ptr(pg.vpool), table, \
+                                                                                 pg.max_pages, lens, hq, hkv, eps, rows)
+    if (pg.kv == BRASA_KV_F32) STORE_PAGED(BRASA_KV_F32);
+    else if (pg.kv == BRASA_KV_F16) STORE_PAGED(BRASA_KV_F16);
+    else STORE_PAGED(BRASA_KV_Q8_0);
+#undef STORE_PAGED
+    return brasa_post_launch(cmd, "qk_norm_rope_store_paged");
+}
+
+int32_t brasa_k_decode_attention_paged(brasa_cmd *cmd, brasa_arg q, brasa_paged_kv pg, brasa_arg partials, uint64_t partials_len, brasa_arg o, uint32_t hq,
+                                       uint32_t hkv) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    BRASA_TRY(check_paged(ctx, pg, hq, hkv));
+    const uint32_t max_chunks = (uint32_t)(((uint64_t)pg.max_pages * PAGE + 127) / 128);
+    const uint64_t need = (uint64_t)pg.seqs * hq * max_chunks * 130;
+    BRASA_REQUIRE(ctx, partials_len >= need && arg_fits(partials, partials_len * 4), "decode_attention_paged: scratch of %llu floats needed",
+                  (unsigned long long)need);
+    BRASA_REQUIRE(ctx, arg_fits(q, (uint64_t)pg.seqs * hq * 512) && arg_fits(o, (uint64_t)pg.seqs * hq * 512), "decode_attention_paged: q or o too small");
+    const float scale = 1.0f / sqrtf(128.0f);
+    const int32_t *table = (const int32_t *)arg_ptr(pg.table);
+    const uint32_t *lens = (const uint32_t *)arg_ptr(pg.lens);
+    Paged kp{arg_ptr(pg.kpool), table, pg.max_pages, hkv}, vp{arg_ptr(pg.vpool), table, pg.max_pages, hkv};
+    const float *qp = (const float *)arg_ptr(q);
+    float *pp = (float *)arg_ptr(partials);
+    dim3 agrid(max_chunks, hkv, pg.seqs), rgrid(hq, pg.seqs);
+    if (pg.kv == BRASA_KV_F16) {  // tensor-core partials (one block per chunk, kv head and sequence)
+        BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<false>, MMA_SMEM));
+        decode_partial_paged_mma_kernel<false><<<agrid, 128, MMA_SMEM, ctx->stream>>>(qp, kp, vp, lens, pp, hq, max_chunks, scale, 0, pg.seqs);
+    } else {
+        const size_t smem = (128 * TS + 8 * D + 8 * 128 + 16) * sizeof(float);
+        if (pg.kv == BRASA_KV_F32) {
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_kernel<BRASA_KV_F32>, smem));
+            decode_partial_paged_kernel<BRASA_KV_F32><<<agrid, 128, smem, ctx->stream>>>(qp, kp, vp, lens, pp, hq, max_chunks, scale);
+        } else {
+            BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_kernel<BRASA_KV_Q8_0>, smem));
+            decode_partial_paged_kernel<BRASA_KV_Q8_0><<<agrid, 128, smem, ctx->stream>>>(qp, kp, vp, lens, pp, hq, max_chunks, scale);
+        }
+    }
+    BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged"));
+    decode_reduce_paged_kernel<false><<<rgrid, 128, 0, ctx->stream>>>(pp, lens, arg_ptr(o), hq, max_chunks);
+    return brasa_post_launch(cmd, "decode_reduce_paged");
+}
+
 // The buffers of brasa_batch_create, one term each, at the allocation granularity of the planner.
 int32_t brasa_plan_batch(const brasa_model_shape *m, const brasa_batch_shape *s, brasa_batch_plan *out) {
     if (!m || !s || !out) return BRASA_EINVAL;

@@ -27,6 +27,7 @@ struct brasa_ctx {
     uint32_t *gemv_counters = nullptr;
     size_t gemv_counters_n = 0;
     uint32_t *status = nullptr;  // device status word: non-zero after a bounded wait gave up
+    uint32_t timeouts = 0;       // waits that gave up so far (kernels with state across launches compare it to what they last saw)
     bool pdl = true;             // programmatic dependent launch between decode kernels
     bool capturing = false;      // a stream capture is open (brasa_graph_capture_begin)
     unsigned long long *gemv_trace = nullptr;  // device buffer of phase timestamps when BRASA_TRACE=1
@@ -47,13 +48,10 @@ struct brasa_ctx {
     float *gemm_part = nullptr;      // partial output tiles of the split-K tensor-core GEMM
     size_t gemm_part_bytes = 0;
     uint32_t *gemm_counters = nullptr;  // arrivals per output tile of that GEMM (GEMM_TC_COUNTERS words, zero between launches)
-    // opt-in dynamic shared memory already granted on this context's device: (kernel, bytes). The attribute belongs to
-    // a (kernel, device) pair, so it is remembered per context, never per process.
-    std::vector<std::pair<const void *, size_t>> smem_granted;
 };
 
-// Makes `bytes` of dynamic shared memory available to kernel `fn` on the context's device (once per context and
-// size; cheap afterwards).
+// Makes at least `bytes` of dynamic shared memory available to kernel `fn` on the context's device (the grant is
+// per device and kernel, shared by every context of the process on that device, and never lowered; cheap afterwards).
 int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes);
 
 // The part of a tensor-parallel exchange buffer that belongs to the whole-token decode kernel, as seen from this rank:

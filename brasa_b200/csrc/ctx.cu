@@ -5,6 +5,8 @@
 #include <string.h>
 
 #include <algorithm>
+#include <map>
+#include <mutex>
 
 #include "brasa_internal.h"
 
@@ -24,16 +26,18 @@ int32_t brasa_check_cuda(brasa_ctx *ctx, cudaError_t e, const char *what) {
     return brasa_fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// The attribute belongs to a (device, kernel) pair of the process, and setting it replaces the earlier value. Two
+// contexts on one device share it, so what has been granted is remembered per process and only ever raised: a context
+// that asks for less than another one got never takes the larger grant away.
 int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes) {
-    for (auto &g : ctx->smem_granted)
-        if (g.first == fn) {
-            if (g.second >= bytes) return BRASA_OK;
-            BRASA_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-            g.second = bytes;
-            return BRASA_OK;
-        }
+    static std::mutex mu;
+    static std::map<std::pair<int, const void *>, size_t> granted;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = granted[std::make_pair(ctx->device, fn)];
+    if (have >= bytes) return BRASA_OK;
+    BRASA_CUDA(ctx, cudaSetDevice(ctx->device));
     BRASA_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
-    ctx->smem_granted.emplace_back(fn, bytes);
+    have = bytes;
     return BRASA_OK;
 }
 
@@ -138,6 +142,7 @@ int32_t brasa_ctx_sync(brasa_ctx *ctx) {
     BRASA_CUDA(ctx, cudaMemcpy(&st, ctx->status, 4, cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(ctx->status, 0, 4);
+        ++ctx->timeouts;
         if (ctx->gemm_counters) cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4);  // a kernel that gave up may have left arrivals behind
         return brasa_fail(ctx, BRASA_ETIMEOUT, "a bounded device-side wait ran out (status %u)", st);
     }
@@ -248,6 +253,7 @@ int32_t brasa_cmd_wait(brasa_cmd *cmd, double *gpu_seconds) {
         cudaMemcpy(&st, ctx->status, 4, cudaMemcpyDeviceToHost);
         if (st != 0) {
             cudaMemset(ctx->status, 0, 4);
+            ++ctx->timeouts;
             if (ctx->gemm_counters) cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4);
             rc = brasa_fail(ctx, BRASA_ETIMEOUT, "a bounded device-side wait ran out (status %u)", st);
         }

@@ -8,12 +8,15 @@
 //     so its weight traffic is a fixed list of byte ranges (slots). They stream through a shared-memory ring with
 //     bulk async copies; the warp that is last to finish with a slot starts the copy that reuses it, across
 //     operation boundaries. HBM keeps working while the blocks exchange activations.
-//   * Activations cross blocks without barriers. Every activation vector lives in L2 as 8-byte words
-//     {float, epoch}; a consumer polls the words it needs until they carry the epoch of the producing operation of
-//     this launch. A single 8-byte store is indivisible, so no fence, flag or grid barrier is needed, and one round
-//     trip to L2 both synchronises and delivers the data. Reuse of a buffer is safe by construction: a block can
-//     only write operation k + 2 after every block has finished reading the output of operation k (it needs all of
-//     k + 1, which needs every block to have produced its part, which needs all of k).
+//   * Activations cross blocks without barriers. Every operation has its own output vector in L2, twice (launches
+//     alternate between the two copies). A word holds either the float or the bit pattern VS_EMPTY, a NaN no
+//     arithmetic produces; a consumer polls the words it needs until none is empty. A 4-byte store is indivisible, so
+//     no fence, flag or grid barrier is needed, and one round trip to L2 both synchronises and delivers the data.
+//     The thread that writes a word of this launch's copy also empties the same word of the other copy, which the
+//     launch before wrote and read and the next launch will fill: the end of the kernel orders that store before
+//     every load of the next launch, so inside one launch a word changes exactly once, from empty to its value.
+//     (Attention partials, the argmax candidates and the words that cross GPUs are 8-byte {float, epoch} words,
+//     valid when they carry the epoch of the producing operation of this launch.)
 //   * Every poll and every mbarrier wait is bounded. A wait that runs out sets the context's status word and a
 //     block-wide flag after which the block stops waiting and runs to its end; the host reports BRASA_ETIMEOUT.
 // GEMV arithmetic, x conversion and epilogues are those of gemv.cu (same rounding); attention works on 64-key
@@ -37,6 +40,7 @@ constexpr uint32_t POLL_LIMIT = 1u << 20;  // polls of an activation word before
 constexpr int R = 2;                       // rows a warp works on at a time
 constexpr int NMAX = 5;                    // half blocks of x a lane keeps per column slice
 constexpr uint32_t EPOCH_SPAN = 1024;      // epochs of one launch; operations + 2 must stay below it
+constexpr uint32_t VS_EMPTY = 0xffffffffu;  // an activation word nobody has written in this launch
 
 enum { OP_GEMV = 0, OP_ATTN = 1 };
 enum { IN_LL = 0, IN_EMBED = 1 };
@@ -58,8 +62,8 @@ struct TokOp {
     uint32_t pad1[2];
     const uint8_t *w[3];
     const float *normw;
-    const unsigned long long *in;
-    unsigned long long *out;
+    const uint32_t *in;  // first copy; the second one lies TokParams::par_words further
+    uint32_t *out;
     const float *q_norm, *k_norm;
     uint8_t *kc, *vc;
     const float *next_normw;  // norm weight of the operation after this one (null: none): staged in shared memory meanwhile
@@ -76,6 +80,7 @@ struct TokParams {
     const uint32_t *slot_begin;  // [grid + 1]
     const uint4 *block_ops;      // [nops][grid]: first output row, rows of segments 0 | 1 << 16, rows of segment 2, -
     uint32_t nslot, xf_bytes, part_floats, resid_floats, sdesc_n, nw_floats;
+    uint32_t par_words;  // words of one copy of the activation vectors
     uint32_t *state, *ids, *next_id, *out_ids;
     uint32_t out_cap;
     const uint8_t *embed;
@@ -109,8 +114,22 @@ __device__ __forceinline__ unsigned long long ll_load(const unsigned long long *
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
     return w;
 }
-__device__ __forceinline__ void ll_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
-    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+
+// An activation word of this launch's copy, and the same word of the other copy emptied for the next launch.
+__device__ __forceinline__ void vs_store(uint32_t *cur, uint32_t *alt, uint32_t bits) {
+    if (bits == VS_EMPTY) bits = 0x7fffffffu;  // this one NaN pattern means "empty": another NaN takes its place
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(cur), "r"(bits) : "memory");
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(alt), "r"(VS_EMPTY) : "memory");
+}
+__device__ __forceinline__ uint32_t vs_load(const uint32_t *p) {
+    uint32_t w;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ uint4 vs_load4(const uint32_t *p) {  // four words, each indivisible on its own
+    uint4 w;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(p) : "memory");
+    return w;
 }
 
 // Words that cross GPUs (a peer's store into this rank's exchange area over NVLink): system scope.
@@ -190,6 +209,7 @@ struct TokCtx {
     uint32_t *status;
     unsigned long long *trace;
     uint32_t trace_op, my_slots, nslot, G, b, pos, seq, token, h0, hn;
+    uint32_t par_cur, par_alt;  // word offsets of this launch's copy of the activation vectors and of the other one
     uint32_t oi;  // current operation (trace builds)
 };
 
@@ -219,6 +239,19 @@ __device__ __forceinline__ void ll_wait4(const TokCtx &c, const unsigned long lo
     }
 }
 
+// Four activation words of a vector (attention's q, k, v rows).
+__device__ __forceinline__ void vs_wait4(const TokCtx &c, const uint32_t *p0, const uint32_t *p1, const uint32_t *p2, const uint32_t *p3, uint32_t out[4]) {
+    for (uint32_t it = 0;; ++it) {
+        out[0] = vs_load(p0); out[1] = vs_load(p1); out[2] = vs_load(p2); out[3] = vs_load(p3);
+        const bool ok = out[0] != VS_EMPTY && out[1] != VS_EMPTY && out[2] != VS_EMPTY && out[3] != VS_EMPTY;
+        if (ok || *c.s_abort) break;
+        if (it >= POLL_LIMIT) {
+            give_up(c, 3);
+            break;
+        }
+    }
+}
+
 // a slot descriptor {address lo, address hi, bytes, -} -> ring[s]
 __device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s) {
     const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
@@ -226,62 +259,99 @@ __device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s)
     bulk_g2s(c.ring + (size_t)s * SLOT_CAP, src, d.z, &c.full[s]);
 }
 
-// ---- GEMV, phase 1: wait for the input, fold the norm weight, convert to fixed point (thread t: half blocks t, t + 512, ..).
-// Returns the thread's share of sum x^2.
+// ---- GEMV, phase 1: wait for the input, fold the norm weight, convert to fixed point. A thread takes one quad of four
+// values at a time (quads t, t + 512, ..), so that the whole block polls at once; the four lanes of a half block share
+// its largest magnitude and its integer sum by shuffles and each writes its own words of the record (the record
+// x_half_block_to_fixed builds, same arithmetic). Returns the thread's share of sum x^2. (Asking for all of a thread's
+// quads at once measured 5 % slower over the token than one quad after the other: polls and weights share the L2.)
+
+// element index of quad qi: the quads of a half block start at +0, +16, +4, +20
+__device__ __forceinline__ uint32_t quad_elem(uint32_t qi) {
+    const uint32_t hbi = qi >> 2, j = qi & 3;
+    return (hbi >> 1) * 32 + 8 * (hbi & 1) + 16 * (j & 1) + 2 * (j & 2);
+}
+
 template <int P>
-__device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, const uint8_t *embed, uint32_t vocab, uint32_t epoch_in) {
+__device__ __forceinline__ void quad_to_fixed(const TokCtx &c, const TokOp &op, uint32_t *xw, uint32_t qi, float4 v, float &ssq) {
+    constexpr uint32_t BITS = P == 3 ? 22 : 16;
+    const uint32_t hbi = qi >> 2, j = qi & 3, e = quad_elem(qi);
+    ssq = fmaf(v.x, v.x, ssq); ssq = fmaf(v.y, v.y, ssq); ssq = fmaf(v.z, v.z, ssq); ssq = fmaf(v.w, v.w, ssq);
+    if (op.save_resid) {  // this vector is the residual a later epilogue adds: keep this block's rows
+        const uint32_t r = e - c.h0;  // wraps for rows before h0
+        if (r + 0 < c.hn) c.resid[r + 0] = v.x;
+        if (r + 1 < c.hn) c.resid[r + 1] = v.y;
+        if (r + 2 < c.hn) c.resid[r + 2] = v.z;
+        if (r + 3 < c.hn) c.resid[r + 3] = v.w;
+    }
+    if (op.normw) {
+        const float4 nw = *reinterpret_cast<const float4 *>(c.nwbuf + e);
+        v.x *= nw.x; v.y *= nw.y; v.z *= nw.z; v.w *= nw.w;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // step = 2^(exponent(amax) - (BITS - 2)); zero (or denormal) groups get step 0; infinities travel in the step
+    const uint32_t ebits = __float_as_uint(amax) & 0x7F800000u;
+    const bool live = ebits > ((BITS - 1) << 23) && ebits < 0x7F800000u;
+    const float step = live ? __uint_as_float(ebits - ((BITS - 2) << 23)) : (ebits == 0x7F800000u ? amax : 0.0f);
+    const float inv = live ? __uint_as_float((254u << 23) - (ebits - ((BITS - 2) << 23))) : 0.0f;  // 1 / step, exact
+    int X[4] = {__float2int_rn(v.x * inv), __float2int_rn(v.y * inv), __float2int_rn(v.z * inv), __float2int_rn(v.w * inv)};
+    if (P == 2) {  // a value that rounds up to 2^15 stays inside the signed top byte
+#pragma unroll
+        for (int k = 0; k < 4; ++k) X[k] = min(X[k], 32767);
+    }
+    int total = X[0] + X[1] + X[2] + X[3];
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    // byte planes of the four integers: byte k of every X gathered into one word
+    const uint32_t lo01 = __byte_perm(X[0], X[1], 0x5140), lo23 = __byte_perm(X[2], X[3], 0x5140);
+    const uint32_t w0 = __byte_perm(lo01, lo23, 0x5410), w1 = __byte_perm(lo01, lo23, 0x7632);
+    if (P == 3) {
+        const uint32_t hi01 = __byte_perm(X[0], X[1], 0x7362), hi23 = __byte_perm(X[2], X[3], 0x7362);
+        const uint32_t w2 = __byte_perm(hi01, hi23, 0x5410);
+        const uint32_t sw = (hbi >> 1) & 3;  // record words 3j .. 3j + 2; 16-byte chunk n of a record lies at n ^ sw
+        const uint32_t i0 = 3 * j, i1 = 3 * j + 1, i2 = 3 * j + 2;
+        xw[(hbi * 4 + ((i0 >> 2) ^ sw)) * 4 + (i0 & 3)] = w0;
+        xw[(hbi * 4 + ((i1 >> 2) ^ sw)) * 4 + (i1 & 3)] = w1;
+        xw[(hbi * 4 + ((i2 >> 2) ^ sw)) * 4 + (i2 & 3)] = w2;
+        if (j == 0) *reinterpret_cast<uint4 *>(xw + (hbi * 4 + (3 ^ sw)) * 4) = make_uint4((uint32_t)total, __float_as_uint(step), 0, 0);
+    } else {
+        *reinterpret_cast<uint2 *>(xw + hbi * 12 + 2 * j) = make_uint2(w0, w1);
+        if (j == 0) *reinterpret_cast<uint4 *>(xw + hbi * 12 + 8) = make_uint4((uint32_t)total, __float_as_uint(step), 0, 0);
+    }
+}
+
+template <int P>
+__device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, const uint8_t *embed, uint32_t vocab) {
     const int tid = threadIdx.x;
-    const uint32_t cols = op.cols, nhb = cols / 16;
-    uint4 *xf = reinterpret_cast<uint4 *>(c.xfb);
+    const uint32_t cols = op.cols, nq = cols / 4;  // a multiple of 64: a warp is inside or outside as a whole
+    uint32_t *xw = reinterpret_cast<uint32_t *>(c.xfb);
+    const uint32_t *in = op.in + c.par_cur;
     float ssq = 0.0f;
-    const uint32_t off[4] = {0, 16, 4, 20};
+    if (op.in_kind == IN_EMBED) {
 #pragma unroll 1
-    for (uint32_t hbi = tid; hbi < nhb; hbi += TK_THREADS) {
-        const uint32_t e0 = (hbi >> 1) * 32 + 8 * (hbi & 1);
-        float4 q[4];
-        if (op.in_kind == IN_EMBED) {
-            if (c.token < vocab) embed_half_block(embed, c.token, cols, hbi, q);
+        for (uint32_t qi = tid; qi < nq; qi += TK_THREADS) {
+            const uint32_t j = qi & 3;
+            float4 q[4];
+            if (c.token < vocab) embed_half_block(embed, c.token, cols, qi >> 2, q);
             else q[0] = q[1] = q[2] = q[3] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        } else {
-            const unsigned long long *src = op.in + e0;
-            unsigned long long w[16];
-            for (uint32_t it = 0;; ++it) {
-                ll_load2(src + 0, w[0], w[1]);   ll_load2(src + 2, w[2], w[3]);      // quad 0: e0 .. e0 + 3
-                ll_load2(src + 16, w[4], w[5]);  ll_load2(src + 18, w[6], w[7]);     // quad 1: e0 + 16 ..
-                ll_load2(src + 4, w[8], w[9]);   ll_load2(src + 6, w[10], w[11]);    // quad 2: e0 + 4 ..
-                ll_load2(src + 20, w[12], w[13]); ll_load2(src + 22, w[14], w[15]);  // quad 3: e0 + 20 ..
-                uint32_t bad = 0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) bad |= (uint32_t)(w[i] >> 32) ^ epoch_in;
-                if (bad == 0 || *c.s_abort) break;
-                if (it >= POLL_LIMIT) {
-                    give_up(c, 3);
-                    break;
-                }
-            }
-            TRACE(2);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                q[j] = make_float4(__uint_as_float((uint32_t)w[4 * j]), __uint_as_float((uint32_t)w[4 * j + 1]),
-                                   __uint_as_float((uint32_t)w[4 * j + 2]), __uint_as_float((uint32_t)w[4 * j + 3]));
+            quad_to_fixed<P>(c, op, xw, qi, j == 0 ? q[0] : (j == 1 ? q[1] : (j == 2 ? q[2] : q[3])), ssq);
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float4 &v = q[j];
-            ssq = fmaf(v.x, v.x, ssq); ssq = fmaf(v.y, v.y, ssq); ssq = fmaf(v.z, v.z, ssq); ssq = fmaf(v.w, v.w, ssq);
-            if (op.save_resid) {  // this vector is the residual a later epilogue adds: keep this block's rows
-                const uint32_t e = e0 + off[j] - c.h0;  // wraps for rows before h0
-                if (e + 0 < c.hn) c.resid[e + 0] = v.x;
-                if (e + 1 < c.hn) c.resid[e + 1] = v.y;
-                if (e + 2 < c.hn) c.resid[e + 2] = v.z;
-                if (e + 3 < c.hn) c.resid[e + 3] = v.w;
-            }
-            if (op.normw) {
-                const float4 nw = *reinterpret_cast<const float4 *>(c.nwbuf + e0 + off[j]);
-                v.x *= nw.x; v.y *= nw.y; v.z *= nw.z; v.w *= nw.w;
+        return ssq;
+    }
+#pragma unroll 1
+    for (uint32_t qi = tid; qi < nq; qi += TK_THREADS) {
+        uint4 w;
+        for (uint32_t it = 0;; ++it) {
+            w = vs_load4(in + quad_elem(qi));
+            if ((w.x != VS_EMPTY && w.y != VS_EMPTY && w.z != VS_EMPTY && w.w != VS_EMPTY) || *c.s_abort) break;
+            if (it >= POLL_LIMIT) {
+                give_up(c, 3);
+                break;
             }
         }
-        x_half_block_to_fixed<P>(xf, hbi, q[0], q[1], q[2], q[3]);
+        TRACE(2);
+        quad_to_fixed<P>(c, op, xw, qi, make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w)), ssq);
     }
     return ssq;
 }
@@ -356,7 +426,7 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
     return WarpRing{kk, rs, rph};
 }
 
-// ---- GEMV, phase 3: one thread per output row of this block; the result goes out as {value, epoch} words.
+// ---- GEMV, phase 3: one thread per output row of this block; the result goes out as activation words.
 __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, const uint32_t *bo, float scale, uint32_t epoch, float *logits,
                                            unsigned long long *cand, const TokParams &p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -420,7 +490,7 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
             if (v > bst.v) bst = Best{v, r0 + j};
         } else {
             TRACE(9);
-            ll_store(op.out + r0 + j, __float_as_uint(v), epoch);
+            vs_store(op.out + c.par_cur + r0 + j, op.out + c.par_alt + r0 + j, __float_as_uint(v));
             TRACE(10);
         }
     }
@@ -442,7 +512,7 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
 
 // ---- attention of this token over the cache, new row included ----
 template <int KV>
-__device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, uint32_t oi, uint32_t epoch, uint32_t epoch_in, uint32_t heads,
+__device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, uint32_t oi, uint32_t epoch, uint32_t heads,
                                           uint32_t kv_heads, uint32_t max_chunks, const float *cos_t, const float *sin_t,
                                           unsigned long long *partials, float attn_scale) {
     constexpr int RB = KvRow<KV>::BYTES, RS = KvRow<KV>::STRIDE;
@@ -489,7 +559,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
         if ((uint32_t)warp < Gq + 2 && (((uint32_t)warp < Gq && ch == ch_lo) || ((uint32_t)warp >= Gq && has_new))) {
             // warps 0 .. Gq-1: a query head (once per item); warp Gq: the new key row; warp Gq + 1: the new value row
             const uint32_t g = warp;
-            const unsigned long long *src = g < Gq ? op.in + (size_t)(kh * Gq + g) * 128 : op.in + (size_t)(heads + (g - Gq) * kv_heads + kh) * 128;
+            const uint32_t *src = op.in + c.par_cur + (g < Gq ? (size_t)(kh * Gq + g) * 128 : (size_t)(heads + (g - Gq) * kv_heads + kh) * 128);
             float xv[4], y[4], wv[4], cs[2], sn[2];
             {   // what does not depend on this token's q, k, v first: norm weight, cos and sin of this position
                 const float *nw = g < Gq ? op.q_norm : op.k_norm;
@@ -499,7 +569,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                     sn[j] = sin_t[(size_t)pos * 64 + lane + 32 * j];
                 }
                 uint32_t raw[4];
-                ll_wait4(c, src + lane, src + lane + 32, src + lane + 64, src + lane + 96, epoch_in, raw);
+                vs_wait4(c, src + lane, src + lane + 32, src + lane + 64, src + lane + 96, raw);
                 for (int j = 0; j < 4; ++j) xv[j] = __uint_as_float(raw[j]);
             }
             if (g <= Gq) norm_rope_regs(xv, wv, cs, sn, op.eps, y);
@@ -583,7 +653,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             if (o < Gq * 128) {
                 const uint32_t g = o >> 7, d = o & 127, head = kh * Gq + g;
                 if (ngroups == 1) {
-                    ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(run[oi2] / red[24 + g]), epoch);
+                    vs_store(op.out + c.par_cur + (size_t)head * 128 + d, op.out + c.par_alt + (size_t)head * 128 + d, __float_as_uint(run[oi2] / red[24 + g]));
                 } else {
                     unsigned long long *pp = partials + ((size_t)head * max_chunks + gi) * 130;
                     ll_store(pp + 2 + d, __float_as_uint(run[oi2]), epoch);
@@ -651,7 +721,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                     A = fmaf(qs[j * 128 + d], wj, A);
                     Lt = fmaf(qs[512 + j], wj, Lt);
                 }
-                ll_store(op.out + (size_t)head * 128 + d, __float_as_uint(A / Lt), epoch);
+                vs_store(op.out + c.par_cur + (size_t)head * 128 + d, op.out + c.par_alt + (size_t)head * 128 + d, __float_as_uint(A / Lt));
             }
             __syncthreads();
         }
@@ -686,6 +756,8 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
     c.b = b;
     c.pos = p.state[0];
     c.seq = p.state[2];
+    c.par_cur = (c.seq & 1) * p.par_words;
+    c.par_alt = p.par_words - c.par_cur;
     c.token = p.ids[0];
     c.nslot = p.nslot;
     const uint32_t slot_lo = p.slot_begin[b];
@@ -735,7 +807,6 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
         const uint32_t *bo = ops_s + (oi & 1) * OPS_WORDS + OP_WORDS;  // r0, rows of segments 0 and 1 (16 bits each), rows of segment 2
         if (oi + 1 < p.nops) fetch_op(oi + 1);
         const uint32_t epoch = c.seq * EPOCH_SPAN + oi + 1;
-        const uint32_t epoch_in = c.seq * EPOCH_SPAN + op.in_op + 1;
 
         c.oi = oi;
         TRACE(0);
@@ -753,7 +824,7 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
                 c.sdesc[i] = k < c.my_slots ? c.myslots[k] : make_uint4(0, 0, 0, 0);
             }
             TRACE(1);
-            float ssq = gemv_input<PLANES>(c, op, p.embed, p.vocab, epoch_in);
+            float ssq = gemv_input<PLANES>(c, op, p.embed, p.vocab);
             TRACE(3);
             TRACEB(1);
             for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
@@ -774,7 +845,7 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
             TRACE(8);
             gemv_epilogue(c, op, bo, c.red[47], epoch, p.logits, p.cand, p);
         } else {
-            attention_op<KV>(c, op, oi, epoch, epoch_in, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
+            attention_op<KV>(c, op, oi, epoch, p.heads, p.kv_heads, p.max_chunks, p.cos_t, p.sin_t, p.partials, p.attn_scale);
         }
         TRACE(11);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -869,6 +940,9 @@ struct brasa_token_program {
     int32_t kv = 0;
     uint32_t grid = 0;
     std::vector<void *> device;  // allocations owned by the program
+    void *vectors = nullptr;     // both copies of the activation vectors
+    size_t vector_bytes = 0;
+    uint32_t timeouts_seen = 0;  // the context's count of abandoned waits when the vectors were last known clean
 };
 
 bool brasa_token_program_supported(brasa_ctx *ctx, const brasa_token_model &m) {
@@ -909,23 +983,29 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         prog->device.push_back(*ptr);
         return brasa_check_cuda(ctx, cudaMemset(*ptr, 0, bytes), "cudaMemset");
     };
-    // activation vectors as {value, epoch} words
-    unsigned long long *xa, *xb, *qkv, *attn, *act, *partials, *cand;
-    const size_t ll_words = (size_t)2 * H + (QD + 2 * KD) + QD + F + (size_t)m.heads * max_chunks * 130 + 2 * G;
+    // attention partials and argmax candidates as {value, epoch} words
+    unsigned long long *partials, *cand;
+    const size_t ll_words = (size_t)m.heads * max_chunks * 130 + 2 * G;
     void *ll_base;
     BRASA_TRY(dev_alloc(ll_words * 8, &ll_base));
-    xa = (unsigned long long *)ll_base;
-    xb = xa + H;
-    qkv = xb + H;
-    attn = qkv + (QD + 2 * KD);
-    act = attn + QD;
-    partials = act + F;
+    partials = (unsigned long long *)ll_base;
     cand = partials + (size_t)m.heads * max_chunks * 130;
+    // every operation's output vector: two copies of par_words 4-byte words, all empty at first
+    const size_t per_layer = (size_t)(QD + 2 * KD) + QD + H + F + H;
+    const size_t par_words = (per_layer * m.layers.size() + 31) / 32 * 32;
+    BRASA_REQUIRE(ctx, par_words < (1u << 31), "token program: activation vectors too large");
+    void *vs_base;
+    BRASA_TRY(dev_alloc(par_words * 8, &vs_base));
+    BRASA_CUDA(ctx, cudaMemset(vs_base, 0xff, par_words * 8));
+    prog->vectors = vs_base;
+    prog->vector_bytes = par_words * 8;
+    prog->timeouts_seen = ctx->timeouts;
+    uint32_t *vs_next = (uint32_t *)vs_base;
+    auto vec_alloc = [&](size_t n) { uint32_t *r = vs_next; vs_next += n; return r; };
 
     // ---- the operations ----
     std::vector<TokOp> ops;
-    auto gemv_op = [&](uint32_t nmat, const brasa_qmatrix *w, uint32_t epilogue, bool scaled, const float *normw, const unsigned long long *in,
-                       int in_op, unsigned long long *outp, bool save_resid) {
+    auto gemv_op = [&](uint32_t nmat, const brasa_qmatrix *w, uint32_t epilogue, bool scaled, const float *normw, int in_op, bool save_resid) {
         TokOp o{};
         o.type = OP_GEMV;
         o.qtype = (uint32_t)w[0].qtype;
@@ -948,8 +1028,8 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         o.save_resid = save_resid ? 1 : 0;
         o.eps = m.eps;
         o.normw = normw;
-        o.in = in;
-        o.out = outp;
+        o.in = in_op < 0 ? nullptr : ops[in_op].out;
+        o.out = epilogue == EPI_LOGITS ? nullptr : vec_alloc(o.total_rows);
         ops.push_back(o);
         return (int)ops.size() - 1;
     };
@@ -963,28 +1043,29 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         BRASA_REQUIRE(ctx, l.wq.rows == QD && l.wk.rows == KD && l.wv.rows == KD && l.wq.cols == H && l.wo.rows == H && l.wo.cols == QD &&
                                l.gate.rows == F && l.up.rows == F && l.gate.cols == H && l.down.rows == H && l.down.cols == F,
                       "token program: unexpected matrix shape");
-        int qkv_op = gemv_op(3, wqkv, EPI_SCALE, true, l.attn_norm, xa, x_op, qkv, true);
+        int qkv_op = gemv_op(3, wqkv, EPI_SCALE, true, l.attn_norm, x_op, true);
         TokOp a{};
         a.type = OP_ATTN;
         a.in_op = (uint32_t)qkv_op;
         a.eps = m.eps;
-        a.in = qkv;
-        a.out = attn;
+        a.in = ops[qkv_op].out;
+        a.out = vec_alloc(QD);
         a.q_norm = l.q_norm;
         a.k_norm = l.k_norm;
         a.kc = l.kc;
         a.vc = l.vc;
         ops.push_back(a);
         int attn_op = (int)ops.size() - 1;
-        int o_op = gemv_op(1, &l.wo, EPI_RESID, false, nullptr, attn, attn_op, xb, false);
+        int o_op = gemv_op(1, &l.wo, EPI_RESID, false, nullptr, attn_op, false);
         if (tp_on) ops[o_op].xchg = ++nxchg;
         brasa_qmatrix wgu[2] = {l.gate, l.up};
-        int gu_op = gemv_op(2, wgu, EPI_SWIGLU, true, l.ffn_norm, xb, o_op, act, true);
-        x_op = gemv_op(1, &l.down, EPI_RESID, false, nullptr, act, gu_op, xa, false);
+        int gu_op = gemv_op(2, wgu, EPI_SWIGLU, true, l.ffn_norm, o_op, true);
+        x_op = gemv_op(1, &l.down, EPI_RESID, false, nullptr, gu_op, false);
         if (tp_on) ops[x_op].xchg = ++nxchg;
     }
     BRASA_REQUIRE(ctx, (tp_on ? m.head.rows + m.head_row0 <= m.vocab : m.head.rows == m.vocab) && m.head.cols == H, "token program: unexpected lm_head shape");
-    gemv_op(1, &m.head, EPI_LOGITS, true, m.final_norm, xa, x_op, nullptr, false);
+    gemv_op(1, &m.head, EPI_LOGITS, true, m.final_norm, x_op, false);
+    BRASA_REQUIRE(ctx, (size_t)(vs_next - (uint32_t *)vs_base) <= par_words, "token program: activation vectors overran their area");
     BRASA_REQUIRE(ctx, ops.size() + 2 < EPOCH_SPAN, "token program: too many operations");
     uint32_t nw_floats = 0;
     for (size_t i = 0; i < ops.size(); ++i) {
@@ -1073,6 +1154,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
     p.sin_t = m.sin_t;
     p.logits = m.logits;
     p.cand = cand;
+    p.par_words = (uint32_t)par_words;
     p.partials = partials;
     p.attn_scale = 1.0f / sqrtf(128.0f);
     p.status = ctx->status;
@@ -1104,6 +1186,11 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
 
 int32_t brasa_token_program_launch(brasa_cmd *cmd, brasa_token_program *prog) {
     brasa_ctx *ctx = cmd->ctx;
+    if (prog->timeouts_seen != ctx->timeouts) {
+        // a launch that gave up may have left words of either copy unwritten or not emptied: start from all empty
+        BRASA_CUDA(ctx, cudaMemsetAsync(prog->vectors, 0xff, prog->vector_bytes, ctx->stream));
+        prog->timeouts_seen = ctx->timeouts;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(prog->grid);
     cfg.blockDim = dim3(TK_THREADS);

@@ -328,6 +328,26 @@ int32_t brasa_batch_prefix_cache_stats(brasa_batch *b, uint64_t *hit_tokens, uin
 int32_t brasa_batch_decode(brasa_batch *b, uint32_t steps, brasa_sampling_params params, uint32_t *out_ids, double *gpu_seconds);
 /* logits [sequences][vocab] of the next token of every sequence, without sampling or advancing */
 int32_t brasa_batch_peek_logits(brasa_batch *b, float *logits);
+/* Kernel-level paged-KV operators, for a caller that keeps its own layer loop (crates/models/src/qwen3.rs on top of
+ * brasa_k_*) and its own page tables. One layer's pages: [page][BRASA_KV_PAGE positions][hkv][128] in the cache type;
+ * table: i32 [seqs][max_pages] page numbers (< num_pages) of every sequence in position order; lens: u32 [seqs], the
+ * positions a sequence already holds = the position of its new token. All of it lives in device buffers. */
+typedef struct brasa_paged_kv {
+    brasa_arg kpool, vpool, table, lens;
+    uint32_t seqs, max_pages, num_pages;
+    int32_t kv; /* brasa_kv_type */
+} brasa_paged_kv;
+/* crates/kernels/src/lib.rs:976-1025 qk_norm_rope_store for one new token per sequence: q f32[seqs][hq][128] and
+ * k f32[seqs][hkv][128] are normalised and rotated in place at position lens[seq], K and V (v f32[seqs][hkv][128]) are
+ * rounded to the cache type and stored into the sequence's page of that position */
+int32_t brasa_k_qk_norm_rope_store_paged(brasa_cmd *cmd, brasa_arg q, brasa_arg k, brasa_arg v, brasa_arg q_norm, brasa_arg k_norm,
+                                         brasa_arg rope_cos, brasa_arg rope_sin, float eps, brasa_paged_kv paged, uint32_t hq, uint32_t hkv);
+/* lib.rs:1110-1164 decode_attention_lanes over page tables: every sequence's new token attends to its lens[seq] + 1
+ * positions. partials: f32 scratch of at least brasa_decode_partials_len(hq, max_pages * BRASA_KV_PAGE) * seqs;
+ * o f32[seqs][hq][128] */
+int32_t brasa_k_decode_attention_paged(brasa_cmd *cmd, brasa_arg q, brasa_paged_kv paged, brasa_arg partials, uint64_t partials_len, brasa_arg o,
+                                       uint32_t hq, uint32_t hkv);
+
 /* Memory of a batch before it is created (crates/memory/src/planner.rs:57-95 for the paged pool): the same sums
  * brasa_batch_create allocates, buffer by buffer. head_rows: the model's lm_head rows (its vocabulary unless it is a
  * tensor-parallel shard). */

@@ -354,6 +354,61 @@ def test_qk_norm_rope_store(B, ctx, K, kv, tokens, pos0):
     assert not kc.download(np.uint8, off).any()
 
 
+@pytest.mark.parametrize("kv", ["F32", "F16", "Q8_0"])
+def test_paged_store_and_decode_attention(B, ctx, K, kv):
+    """The kernel-level paged operators: three sequences of different lengths whose 16-position pages lie scattered in
+    the pool. The new token's K and V land in the right page in the cache type (exact rounding of what the kernel
+    produced), q and k come back normalised and rotated at each sequence's own position, and attention over the page
+    tables equals the oracle's attention over each sequence's contiguous rows (1e-5 of max |v|, as the reference's test)."""
+    kvt = B.KvType[kv]
+    rng = O.Rng(61)
+    hq, hkv, dim = 8, 2, 128
+    lens = np.array([5, 200, 333], np.uint32)
+    seqs, max_pages, num_pages = 3, 24, 80
+    perm = np.random.default_rng(3).permutation(num_pages)[:seqs * max_pages].astype(np.int32).reshape(seqs, max_pages)
+    row = hkv * dim
+    kpool_f = np.zeros((num_pages * 16, row), np.float32)
+    vpool_f = np.zeros((num_pages * 16, row), np.float32)
+    old_k, old_v = [], []
+    for s in range(seqs):
+        k, v = rng.vec(int(lens[s]) * row, 2.0).reshape(-1, row), rng.vec(int(lens[s]) * row, 3.0).reshape(-1, row)
+        old_k.append(k)
+        old_v.append(v)
+        for pos in range(int(lens[s])):
+            slot = perm[s, pos // 16] * 16 + pos % 16
+            kpool_f[slot], vpool_f[slot] = k[pos], v[pos]
+    gk, gv, kr, vr = make_cache(B, ctx, kvt, kpool_f.reshape(-1), vpool_f.reshape(-1))  # pools in the cache type + the values they hold
+    q, kn_, vn_ = rng.vec(seqs * hq * dim, 2.0), rng.vec(seqs * hkv * dim, 2.0), rng.vec(seqs * hkv * dim, 3.0)
+    qn, knorm = rng.vec(dim, 1.5), rng.vec(dim, 1.5)
+    table = B.RopeTable(ctx, 1e6, dim, max_pages * 16)
+    cos, sin = O.rope_table(1e6, dim, max_pages * 16)
+    gq, gkn, gvn, gqn, gknorm = (ctx.buffer_from(a) for a in (q, kn_, vn_, qn, knorm))
+    gt, gl = ctx.buffer_from(perm.reshape(-1)), ctx.buffer_from(lens)
+    paged = K.paged_kv(gk, gv, gt, gl, seqs, max_pages, num_pages, kvt)
+    run(ctx, lambda c: K.qk_norm_rope_store_paged(c, gq, gkn, gvn, gqn, gknorm, 1e-6, table, paged, hq, hkv))
+    got_q, got_k = gq.download(np.float32).reshape(seqs, hq * dim), gkn.download(np.float32).reshape(seqs, hkv * dim)
+    part = ctx.buffer(seqs * hq * ((max_pages * 16 + 127) // 128) * 130 * 4)
+    go = ctx.buffer(seqs * hq * dim * 4)
+    run(ctx, lambda c: K.decode_attention_paged(c, gq, paged, part, go, hq, hkv))
+    out = go.download(np.float32).reshape(seqs, hq * dim)
+    kr, vr = kr.reshape(-1, row), vr.reshape(-1, row)
+    for s in range(seqs):
+        pos = int(lens[s])
+        want_q = O.rope_neox(O.rms_norm(q.reshape(seqs, -1)[s], qn, dim, 1e-6), hq, dim, pos, cos, sin)
+        want_k = O.rope_neox(O.rms_norm(kn_.reshape(seqs, -1)[s], knorm, dim, 1e-6), hkv, dim, pos, cos, sin)
+        assert np.max(np.abs(got_q[s] - want_q)) <= 2e-5 * np.max(np.abs(want_q))
+        assert np.max(np.abs(got_k[s] - want_k)) <= 2e-5 * np.max(np.abs(want_k))
+        newk, newv = O.round_kv(int(kvt), got_k[s]), O.round_kv(int(kvt), vn_.reshape(seqs, -1)[s])
+        slots = [perm[s, p // 16] * 16 + p % 16 for p in range(pos)]
+        kseq = np.concatenate([kr[slots].reshape(-1), newk])
+        vseq = np.concatenate([vr[slots].reshape(-1), newv])
+        want, vmax = O.attention(got_q[s], kseq, vseq, 1, hq, hkv, dim, pos)
+        assert np.max(np.abs(out[s] - want) / np.maximum(vmax, 1e-30)) <= 1e-5, s
+    with pytest.raises(B.BrasaError):  # a pool smaller than its page count says
+        bad = K.paged_kv(gk, gv, gt, gl, seqs, max_pages, num_pages * 2, kvt)
+        run(ctx, lambda c: K.decode_attention_paged(c, gq, bad, part, go, hq, hkv))
+
+
 # ---- attention -----------------------------------------------------------------------------------
 
 def make_cache(B, ctx, kvt, k, v):

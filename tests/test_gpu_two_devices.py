@@ -95,3 +95,36 @@ def test_the_same_kernels_on_two_devices_in_one_process():
     exercise(B, 0)
     exercise(B, 1)
     exercise(B, 0)
+
+
+def test_two_contexts_on_one_device_with_models_of_different_size():
+    """The opt-in shared-memory size of a kernel is one value per device: a second context whose model asks for less must
+    not take the first one's grant away. Two models of different widths decode alternately, each in its own context."""
+    import pathlib
+    import tempfile
+
+    import brasa_b200 as B
+    from oracle import brasa_format as BF
+    shapes = [dict(layers=2, hidden=1024, heads=8, kv_heads=4, ffn=4096, vocab=512), dict(layers=2, hidden=256, heads=4, kv_heads=2, ffn=512, vocab=512)]
+    with tempfile.TemporaryDirectory() as td:
+        ctxs, models, firsts, want = [], [], [], []
+        try:
+            for i, sh in enumerate(shapes):
+                path = pathlib.Path(td) / f"model{i}.brasa"
+                cfg = BF.tiny_config(**sh)
+                BF.write_brasa(path, cfg, BF.synth_weights(cfg, seed=5 + i, std=0.05, norm_jitter=0.1))
+                ctx = B.Context(0)
+                ctxs.append(ctx)
+                m = B.Qwen3.load(ctx, path, B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=B.KvType.F16))
+                models.append(m)
+                lg, _ = m.forward(np.arange(24, dtype=np.uint32), 0)
+                firsts.append(int(np.argmax(lg[0])))
+                want.append([int(t) for t in m.decode_greedy(firsts[i], 24, 5)[0]])
+            for _ in range(2):  # alternate: each launch follows one of the other context
+                for i, m in enumerate(models):
+                    assert [int(t) for t in m.decode_greedy(firsts[i], 24, 5)[0]] == want[i]
+        finally:
+            for m in models:
+                m.free()
+            for c in ctxs:
+                c.close()
