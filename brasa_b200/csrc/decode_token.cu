@@ -59,7 +59,8 @@ struct TokOp {
     uint32_t in_kind, in_op, save_resid, next_cols;  // next_cols: length of next_normw
     float eps;
     uint32_t xchg;  // tensor parallel: 1 + index of this residual add among the token's exchanges (0: no exchange)
-    uint32_t pad1[2];
+    uint32_t fast;  // every lane's half blocks before its last iteration lie inside the row (see gemv_rows)
+    uint32_t pad1[1];
     const uint8_t *w[3];
     const float *normw;
     const uint32_t *in;  // first copy; the second one lies TokParams::par_words further
@@ -358,8 +359,12 @@ __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, co
 
 // ---- GEMV, phase 2: the rows. A slot holds up to RPS rows of one segment; its eight warps (half_w rows x S slices)
 // share them; a lane keeps the same half blocks of x for every row.
-template <int QT, int P>
+// NACT > 0: the operation's half blocks per lane are known when the kernel is built and every lane's half blocks but those
+// of the last iteration lie inside the row (TokOp::fast): loads at addresses worked out once (row_pair_dot_at).
+// NACT = 0: any shape the kernel takes, addresses worked out per half block.
+template <int QT, int P, int NACT>
 __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, const uint32_t *bo, uint32_t gslot, const WarpRing wr) {
+    constexpr int NX = NACT > 0 ? NACT : NMAX;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cols = op.cols, nhb = cols / 16, lS = op.log2S, S = 1u << lS, nact = op.nact;
     const uint32_t lRPS = 4 - lS, RPS = 1u << lRPS, lhw = lRPS - 1, half_w = 1u << lhw;  // rows per slot = warps side by side
@@ -368,15 +373,19 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
     const uint32_t sl0 = (rows0 + RPS - 1) >> lRPS, sl1 = sl0 + ((rows1 + RPS - 1) >> lRPS), total_slots = sl1 + ((rows2 + RPS - 1) >> lRPS);
     const uint4 *xf = reinterpret_cast<const uint4 *>(c.xfb);
     const uint32_t slice = warp & (S - 1), rwl = (warp >> lS) & (half_w - 1);
-    XFixed<P> xr[NMAX];
+    XFixed<P> xr[NX];
 #pragma unroll
-    for (int i = 0; i < NMAX; ++i) {
+    for (int i = 0; i < NX; ++i) {
         const uint32_t want = (slice * nact + i) * 32 + lane;
         const uint32_t hbi = min(want, nhb - 1);
         xr[i] = x_fixed_load<P>(xf, hbi);
         if (want >= nhb || (uint32_t)i >= nact) xr[i].step = 0.0f;  // lanes past the end of the row, unused registers
+        if (NACT > 0) xr[i].total *= -(QT == BRASA_Q4_0 ? 8 : 32);  // the bias term of half_block_idot_pre
     }
     const uint32_t hi_off = tiled_hi_off(cols), sc_off = tiled_scale_off(QT, cols);
+    RowLaneOffsets lo{};
+    if (NACT > 0) lo = row_lane_offsets<QT, NX>(cols, slice, lane);
+    const uint32_t ring32 = smem_u32(c.ring);
     uint32_t kk = wr.kk, rs = wr.rs, rph = wr.rph;
     bool first_slot = true;
     TRACE(5);
@@ -385,9 +394,21 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
         const uint32_t sgi = (j >= sl0) + (j >= sl1);
         const uint32_t ks = j - (sgi == 0 ? 0u : (sgi == 1 ? sl0 : sl1));
         const uint32_t sg_rows = sgi == 0 ? rows0 : (sgi == 1 ? rows1 : rows2), sg_before = sgi == 0 ? 0u : (sgi == 1 ? rows0 : rows0 + rows1);
+#ifdef BRASA_TRACE_BUILD
+        const long long tw0 = clock64();
+#endif
         if (!*c.s_abort && !mbar_wait(&c.full[rs], rph)) {
             if (lane == 0) give_up(c, 2);
         }
+#ifdef BRASA_TRACE_BUILD
+        if (c.trace && c.b == 0 && (threadIdx.x == 0 || threadIdx.x == 256) && c.oi >= c.trace_op && c.oi < c.trace_op + 16) {
+            const uint32_t rnd = (j - (kk - gslot - (kk - gslot) % 2)) ;  // unused
+            (void)rnd;
+            const uint32_t round = (j >> 1) & 7;
+            c.trace[4096 + ((c.oi - c.trace_op) * 2 + (threadIdx.x >> 8)) * 16 + round * 2] = (unsigned long long)(clock64() - tw0);
+            c.trace[4096 + ((c.oi - c.trace_op) * 2 + (threadIdx.x >> 8)) * 16 + round * 2 + 1] = (unsigned long long)tw0;
+        }
+#endif
         if (first_slot) {
             TRACE(6);
             first_slot = false;
@@ -396,15 +417,23 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
         const uint32_t qn = (n_slot + half_w - 1) >> lhw, in_slot = rwl * qn;
         const uint32_t nv = in_slot < n_slot ? min(qn, n_slot - in_slot) : 0u;
         const uint8_t *row0 = c.ring + (size_t)rs * SLOT_CAP + (size_t)in_slot * row_bytes;
+        const uint32_t row0_32 = ring32 + rs * SLOT_CAP + in_slot * row_bytes;
         uint32_t r = 0;
 #pragma unroll 1
         for (; r + 1 < nv; r += 2) {
-            const uint8_t *row_a = row0 + (size_t)r * row_bytes;
-            float z = row_pair_dot<QT, NMAX>(row_a, row_a + row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            float z;
+            if (NACT > 0) {
+                z = row_pair_dot_at<QT, NX, P>(row0_32 + r * row_bytes, row0_32 + (r + 1) * row_bytes, lo, xr, lane);
+            } else {
+                const uint8_t *row_a = row0 + (size_t)r * row_bytes;
+                z = row_pair_dot<QT, NX>(row_a, row_a + row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            }
             if ((lane & 23) == 0) c.part[((sg_before + (ks << lRPS) + in_slot + r + (lane >> 3)) << lS) + slice] = z;
         }
         if (r < nv) {  // an odd row on its own: half the work of a pair (short last slots are shared out one row per warp)
-            float z = row_single_dot<QT, NMAX>(row0 + (size_t)r * row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
+            float z;
+            if (NACT > 0) z = row_single_dot_at<QT, NX, P>(row0_32 + r * row_bytes, lo, xr);
+            else z = row_single_dot<QT, NX>(row0 + (size_t)r * row_bytes, xr, slice, nhb, hi_off, sc_off, lane, (int)nact);
             if (lane == 0) c.part[((sg_before + (ks << lRPS) + in_slot + r) << lS) + slice] = z;
         }
         __syncwarp();
@@ -836,8 +865,14 @@ __global__ void __maxnreg__(128) decode_token_kernel(TokParams p) {
                 for (int o = TK_WARPS / 2; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
                 if (lane == 0) c.red[47] = op.scaled ? 1.0f / sqrtf(tot / (float)op.cols + op.eps) : 1.0f;
             }
-            if (op.qtype == BRASA_Q4_0) wr = gemv_rows<BRASA_Q4_0, PLANES>(c, op, bo, gslot, wr);
-            else wr = gemv_rows<BRASA_Q6_0, PLANES>(c, op, bo, gslot, wr);
+            if (op.qtype == BRASA_Q4_0) {
+                if (op.fast && op.nact == 5) wr = gemv_rows<BRASA_Q4_0, PLANES, 5>(c, op, bo, gslot, wr);
+                else if (op.fast && op.nact == 4) wr = gemv_rows<BRASA_Q4_0, PLANES, 4>(c, op, bo, gslot, wr);
+                else wr = gemv_rows<BRASA_Q4_0, PLANES, 0>(c, op, bo, gslot, wr);
+            } else {
+                if (op.fast && op.nact == 5) wr = gemv_rows<BRASA_Q6_0, PLANES, 5>(c, op, bo, gslot, wr);
+                else wr = gemv_rows<BRASA_Q6_0, PLANES, 0>(c, op, bo, gslot, wr);
+            }
             TRACE(7);
             TRACEB(2);
             gslot += total_slots;
@@ -1023,6 +1058,7 @@ int32_t brasa_token_program_create(brasa_ctx *ctx, const brasa_token_model &m, b
         uint32_t S = 1;
         gemv_shape(w[0].qtype, o.cols, &S, &o.nact);
         for (o.log2S = 0; (1u << o.log2S) < S; ++o.log2S) {}
+        o.fast = o.nact >= 2 ? ((S * o.nact - 2) * 32 + 31 < o.cols / 16) : 1;
         o.in_kind = in_op < 0 ? IN_EMBED : IN_LL;
         o.in_op = in_op < 0 ? 0 : (uint32_t)in_op;
         o.save_resid = save_resid ? 1 : 0;

@@ -198,6 +198,121 @@ __device__ __forceinline__ float row_single_dot(const uint8_t *row_a, const XFix
     return acc_a;
 }
 
+// ---- the same dot products with every address worked out beforehand ----
+// The rows of a ring slot lie in shared memory and a lane's half blocks are 32 apart, so for all iterations but the
+// last one the loads are [row + lane offset + constant]; the last iteration, whose lanes may lie past the end of the
+// row, uses offsets clamped once per operation. The bias term -BIAS * sum(X) is folded into the record when it is
+// loaded (XFixed::total then holds it) and starts the first accumulator.
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_f16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
+
+// Lane offsets inside a row: first half block (codes, scale, q6_0 high bits) and the clamped ones of the last iteration.
+struct RowLaneOffsets {
+    uint32_t c, s, h, lc, ls, lh;
+};
+template <int QT, int N>
+__device__ __forceinline__ RowLaneOffsets row_lane_offsets(uint32_t cols, uint32_t slice, int lane) {
+    const uint32_t nhb = cols / 16, first = slice * N * 32 + lane, last = min(first + (N - 1) * 32, nhb - 1);
+    RowLaneOffsets o;
+    o.c = first * 8;
+    o.s = tiled_scale_off(QT, cols) + (first >> 1) * 2;
+    o.h = tiled_hi_off(cols) + first * 4;
+    o.lc = last * 8;
+    o.ls = tiled_scale_off(QT, cols) + (last >> 1) * 2;
+    o.lh = tiled_hi_off(cols) + last * 4;
+    return o;
+}
+
+template <int QT, int P>
+__device__ __forceinline__ int half_block_idot_pre(uint2 codes, uint32_t hb, const XFixed<P> &x) {  // x.total = -BIAS * sum(X)
+    uint32_t a[4];
+    a[0] = codes.x & 0x0F0F0F0Fu;
+    a[1] = (codes.x >> 4) & 0x0F0F0F0Fu;
+    a[2] = codes.y & 0x0F0F0F0Fu;
+    a[3] = (codes.y >> 4) & 0x0F0F0F0Fu;
+    if (QT == BRASA_Q6_0) {
+        a[0] = lop_and_or(hb, 0x30303030u, a[0]);
+        a[1] = lop_and_or(hb >> 2, 0x30303030u, a[1]);
+        a[2] = lop_and_or(hb << 2, 0x30303030u, a[2]);
+        a[3] = lop_and_or(hb << 4, 0x30303030u, a[3]);
+    }
+    int s[P];
+    s[0] = x.total;
+#pragma unroll
+    for (int d = 1; d < P; ++d) s[d] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int d = 0; d < P; ++d) s[d] = d == P - 1 ? dp4a_us(a[j], x.d[j][d], s[d]) : dp4a_uu(a[j], x.d[j][d], s[d]);
+    }
+    int r = s[0];
+#pragma unroll
+    for (int d = 1; d < P; ++d) r += s[d] << (8 * d);
+    return r;
+}
+
+// Two rows at shared addresses ra, rb. After folding across lanes, lane 0 holds the sum of row a and lane 8 that of row b.
+template <int QT, int N, int P>
+__device__ __forceinline__ float row_pair_dot_at(uint32_t ra, uint32_t rb, const RowLaneOffsets &o, const XFixed<P> (&xr)[N], int lane) {
+    float acc_a = 0.0f, acc_b = 0.0f;
+#pragma unroll
+    for (int it = 0; it < N; ++it) {
+        const bool last = it == N - 1;
+        const uint32_t oc = last ? o.lc : o.c + it * 256, os = last ? o.ls : o.s + it * 32, oh = last ? o.lh : o.h + it * 128;
+        const uint2 ca = lds_u64(ra + oc), cb = lds_u64(rb + oc);
+        uint32_t ha = 0, hb = 0;
+        if (QT == BRASA_Q6_0) {
+            ha = lds_u32(ra + oh);
+            hb = lds_u32(rb + oh);
+        }
+        const float da = lds_f16(ra + os), db = lds_f16(rb + os);
+        const int sa = half_block_idot_pre<QT, P>(ca, ha, xr[it]);
+        const int sb = half_block_idot_pre<QT, P>(cb, hb, xr[it]);
+        acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+        acc_b = fmaf(db * xr[it].step, (float)sb, acc_b);
+    }
+    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 16);
+    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 16);
+    const bool hi3 = lane & 8;
+    float z = hi3 ? acc_b : acc_a, z_send = hi3 ? acc_a : acc_b;
+    z += __shfl_xor_sync(0xffffffffu, z_send, 8);
+    z += __shfl_xor_sync(0xffffffffu, z, 4);
+    z += __shfl_xor_sync(0xffffffffu, z, 2);
+    z += __shfl_xor_sync(0xffffffffu, z, 1);
+    return z;
+}
+
+template <int QT, int N, int P>
+__device__ __forceinline__ float row_single_dot_at(uint32_t ra, const RowLaneOffsets &o, const XFixed<P> (&xr)[N]) {
+    float acc_a = 0.0f;
+#pragma unroll
+    for (int it = 0; it < N; ++it) {
+        const bool last = it == N - 1;
+        const uint32_t oc = last ? o.lc : o.c + it * 256, os = last ? o.ls : o.s + it * 32, oh = last ? o.lh : o.h + it * 128;
+        const uint2 ca = lds_u64(ra + oc);
+        uint32_t ha = 0;
+        if (QT == BRASA_Q6_0) ha = lds_u32(ra + oh);
+        const float da = lds_f16(ra + os);
+        const int sa = half_block_idot_pre<QT, P>(ca, ha, xr[it]);
+        acc_a = fmaf(da * xr[it].step, (float)sa, acc_a);
+    }
+    for (int o2 = 16; o2 > 0; o2 >>= 1) acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o2);
+    return acc_a;
+}
+
 // x to fixed point with P byte planes: one half block (16 values, as the four quads that meet the low / high nibbles
 // of code word 0 and of code word 1) becomes a record in xf: 4 P byte-plane words, the sum of the integers, the step.
 template <int P>
