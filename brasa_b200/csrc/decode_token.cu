@@ -253,6 +253,25 @@ __device__ __forceinline__ void vs_wait4(const TokCtx &c, const uint32_t *p0, co
     }
 }
 
+// Bounded wait for a ring slot's bytes. The block's abort flag is looked at only while the wait has to spin, so a slot
+// that is already there costs one try. False when the limit ran out.
+__device__ __forceinline__ bool slot_wait(const TokCtx &c, uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 15) == 15 && *c.s_abort) return true;  // the block has given up: nobody waits any more
+    }
+    return false;
+}
+
 // a slot descriptor {address lo, address hi, bytes, -} -> ring[s]
 __device__ __forceinline__ void issue_slot(const TokCtx &c, uint4 d, uint32_t s) {
     const uint8_t *src = reinterpret_cast<const uint8_t *>(((unsigned long long)d.y << 32) | d.x);
@@ -397,9 +416,7 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
 #ifdef BRASA_TRACE_BUILD
         const long long tw0 = clock64();
 #endif
-        if (!*c.s_abort && !mbar_wait(&c.full[rs], rph)) {
-            if (lane == 0) give_up(c, 2);
-        }
+        if (!slot_wait(c, &c.full[rs], rph) && lane == 0) give_up(c, 2);
 #ifdef BRASA_TRACE_BUILD
         if (c.trace && c.b == 0 && (threadIdx.x == 0 || threadIdx.x == 256) && c.oi >= c.trace_op && c.oi < c.trace_op + 16) {
             const uint32_t rnd = (j - (kk - gslot - (kk - gslot) % 2)) ;  // unused
@@ -438,7 +455,7 @@ __device__ __forceinline__ WarpRing gemv_rows(const TokCtx &c, const TokOp &op, 
         }
         __syncwarp();
         if (lane == 0 && kk + c.nslot < c.my_slots) {
-            __threadfence_block();
+            // (the warp's reads of the slot are complete: their values went into the sums stored above)
             if (atomicAdd(&c.done[rs], 1u) == TK_WARPS / 2 - 1) {  // last of the eight: the slot is free, refill it
                 c.done[rs] = 0;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -567,7 +584,9 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
     for (uint32_t item = c.b; item < nitems; item += c.G) {
         const uint32_t kh = item / ngroups, gi = item - kh * ngroups;
         const uint32_t ch_lo = gi * cpg, ch_hi = min(nchunks, ch_lo + cpg);
-        float run[2] = {0.0f, 0.0f};  // this thread's output elements (two when the group has 8 query heads)
+        float run[8][2];  // this thread's share (its key class) of an output element pair of every head
+#pragma unroll
+        for (int g = 0; g < 8; ++g) run[g][0] = run[g][1] = 0.0f;
         if (tid < 8) { red[16 + tid] = -INFINITY; red[24 + tid] = 0.0f; }  // running maximum and sum per head
 #pragma unroll 1
         for (uint32_t ch = ch_lo; ch < ch_hi; ++ch) {
@@ -622,15 +641,26 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
 #pragma unroll
             for (int d = 0; d < DPL; d += 8) tile_load8<KV>(row, d0 + d, kv + d);
 #pragma unroll 1
-            for (uint32_t g = 0; g < Gq; ++g) {
-                float a = 0.0f;
+            for (uint32_t g0 = 0; g0 < Gq; g0 += 4) {  // four heads side by side: four independent chains (qs has eight head slots)
+                float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int d = 0; d < DPL; d += 4) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(qs + g * QS_HEAD + (d0 >> 4) * QS_SEG + ((d0 + d) & 15));
-                    a = fmaf(qa.x, kv[d], a); a = fmaf(qa.y, kv[d + 1], a); a = fmaf(qa.z, kv[d + 2], a); a = fmaf(qa.w, kv[d + 3], a);
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg) {
+                        const float4 qa = *reinterpret_cast<const float4 *>(qs + (g0 + gg) * QS_HEAD + (d0 >> 4) * QS_SEG + ((d0 + d) & 15));
+                        a[gg] = fmaf(qa.x, kv[d], a[gg]); a[gg] = fmaf(qa.y, kv[d + 1], a[gg]);
+                        a[gg] = fmaf(qa.z, kv[d + 2], a[gg]); a[gg] = fmaf(qa.w, kv[d + 3], a[gg]);
+                    }
                 }
-                for (int o = LPK / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                if (lane % LPK == 0) ps[g * C + key] = key < nkeys ? a * attn_scale : -INFINITY;
+                for (int o = LPK / 2; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg) a[gg] += __shfl_xor_sync(0xffffffffu, a[gg], o);
+                }
+                if (lane % LPK == 0) {
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg)
+                        if (g0 + gg < Gq) ps[(g0 + gg) * C + key] = key < nkeys ? a[gg] * attn_scale : -INFINITY;
+                }
             }
         }
         __syncthreads();
@@ -643,8 +673,9 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             const float m_old = red[16 + g], m_new = fmaxf(m_old, m);
             v0 = expf(v0 - m_new);
             v1 = C == 64 ? expf(v1 - m_new) : 0.0f;
-            ps[g * C + lane] = v0;
-            if (C == 64) ps[g * C + lane + 32] = v1;
+            float *pt = reinterpret_cast<float *>(kt);  // [key][8 heads]: the K tile is done with once the scores are out
+            pt[lane * 8 + g] = v0;
+            if (C == 64) pt[(lane + 32) * 8 + g] = v1;
             float l = v0 + v1;
             for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
             if (lane == 0) {
@@ -656,37 +687,65 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
         }
         __syncthreads();
         TRACE(4);
+        {   // P V. Warp w owns output elements 8w .. 8w + 7 of every head; its lanes are 4 element pairs x 8 key classes
+            // (keys ks, ks + 8, ..): a value pair is read once for all heads, the key's probabilities come as one
+            // broadcast vector, and no two lanes of a load share a bank. The key classes meet at the end of the item.
+            const float *pt = reinterpret_cast<const float *>(kt);
+            const int d = warp * 8 + 2 * (lane & 3);
+            float acc[8][2];
 #pragma unroll
-        for (int oi2 = 0; oi2 < 2; ++oi2) {  // P V: one output element per thread (two when Gq = 8)
-            const uint32_t o = tid + oi2 * TK_THREADS;
-            if (o < Gq * 128) {
-                const uint32_t g = o >> 7, d = o & 127;
-                // shared-memory instructions are the cost of this loop: four probabilities per load, two dependency chains
-                float acc0 = 0.0f, acc1 = 0.0f;
+            for (int g = 0; g < 8; ++g) acc[g][0] = acc[g][1] = 0.0f;
 #pragma unroll 2
-                for (uint32_t j = 0; j < nkeys; j += 4) {
-                    const float4 pj = *reinterpret_cast<const float4 *>(ps + g * C + j);
-                    acc0 = fmaf(pj.x, tile_at<KV>(vt + j * RS, d), acc0);
-                    if (j + 1 < nkeys) acc1 = fmaf(pj.y, tile_at<KV>(vt + (j + 1) * RS, d), acc1);
-                    if (j + 2 < nkeys) acc0 = fmaf(pj.z, tile_at<KV>(vt + (j + 2) * RS, d), acc0);
-                    if (j + 3 < nkeys) acc1 = fmaf(pj.w, tile_at<KV>(vt + (j + 3) * RS, d), acc1);
+            for (uint32_t j = lane >> 2; j < nkeys; j += 8) {
+                const float2 v = tile_at2<KV>(vt + j * RS, d);
+                const float4 p0 = *reinterpret_cast<const float4 *>(pt + j * 8);
+                acc[0][0] = fmaf(p0.x, v.x, acc[0][0]); acc[0][1] = fmaf(p0.x, v.y, acc[0][1]);
+                acc[1][0] = fmaf(p0.y, v.x, acc[1][0]); acc[1][1] = fmaf(p0.y, v.y, acc[1][1]);
+                acc[2][0] = fmaf(p0.z, v.x, acc[2][0]); acc[2][1] = fmaf(p0.z, v.y, acc[2][1]);
+                acc[3][0] = fmaf(p0.w, v.x, acc[3][0]); acc[3][1] = fmaf(p0.w, v.y, acc[3][1]);
+                if (Gq > 4) {
+                    const float4 p1 = *reinterpret_cast<const float4 *>(pt + j * 8 + 4);
+                    acc[4][0] = fmaf(p1.x, v.x, acc[4][0]); acc[4][1] = fmaf(p1.x, v.y, acc[4][1]);
+                    acc[5][0] = fmaf(p1.y, v.x, acc[5][0]); acc[5][1] = fmaf(p1.y, v.y, acc[5][1]);
+                    acc[6][0] = fmaf(p1.z, v.x, acc[6][0]); acc[6][1] = fmaf(p1.z, v.y, acc[6][1]);
+                    acc[7][0] = fmaf(p1.w, v.x, acc[7][0]); acc[7][1] = fmaf(p1.w, v.y, acc[7][1]);
                 }
-                run[oi2] = run[oi2] * red[32 + g] + (acc0 + acc1);
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if ((uint32_t)g < Gq) {  // heads past Gq multiplied whatever lay in their column: never used
+                    const float keep = red[32 + g];
+                    run[g][0] = run[g][0] * keep + acc[g][0];
+                    run[g][1] = run[g][1] * keep + acc[g][1];
+                }
             }
         }
         __syncthreads();
         }  // chunks of the group
+        {   // the key classes of an output element meet (lanes 4 apart), lanes 0-3 of the warp send the element pair out
+            const uint32_t d = warp * 8 + 2 * (lane & 3);
 #pragma unroll
-        for (int oi2 = 0; oi2 < 2; ++oi2) {
-            const uint32_t o = tid + oi2 * TK_THREADS;
-            if (o < Gq * 128) {
-                const uint32_t g = o >> 7, d = o & 127, head = kh * Gq + g;
-                if (ngroups == 1) {
-                    vs_store(op.out + c.par_cur + (size_t)head * 128 + d, op.out + c.par_alt + (size_t)head * 128 + d, __float_as_uint(run[oi2] / red[24 + g]));
-                } else {
-                    unsigned long long *pp = partials + ((size_t)head * max_chunks + gi) * 130;
-                    ll_store(pp + 2 + d, __float_as_uint(run[oi2]), epoch);
-                    if (d == 0) { ll_store(pp, __float_as_uint(red[16 + g]), epoch); ll_store(pp + 1, __float_as_uint(red[24 + g]), epoch); }
+            for (int g = 0; g < 8; ++g) {
+                if ((uint32_t)g < Gq) {
+                    float r0 = run[g][0], r1 = run[g][1];
+                    for (int o = 4; o < 32; o <<= 1) {
+                        r0 += __shfl_xor_sync(0xffffffffu, r0, o);
+                        r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                    }
+                    if (lane < 4) {
+                        const uint32_t head = kh * Gq + g;
+                        if (ngroups == 1) {
+                            const float l = red[24 + g];
+                            uint32_t *o0 = op.out + (size_t)head * 128 + d;
+                            vs_store(o0 + c.par_cur, o0 + c.par_alt, __float_as_uint(r0 / l));
+                            vs_store(o0 + c.par_cur + 1, o0 + c.par_alt + 1, __float_as_uint(r1 / l));
+                        } else {
+                            unsigned long long *pp = partials + ((size_t)head * max_chunks + gi) * 130;
+                            ll_store(pp + 2 + d, __float_as_uint(r0), epoch);
+                            ll_store(pp + 3 + d, __float_as_uint(r1), epoch);
+                            if (d == 0) { ll_store(pp, __float_as_uint(red[16 + g]), epoch); ll_store(pp + 1, __float_as_uint(red[24 + g]), epoch); }
+                        }
+                    }
                 }
             }
         }
