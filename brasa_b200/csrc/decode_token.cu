@@ -588,22 +588,29 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
 #pragma unroll
         for (int g = 0; g < 8; ++g) run[g][0] = run[g][1] = 0.0f;
         if (tid < 8) { red[16 + tid] = -INFINITY; red[24 + tid] = 0.0f; }  // running maximum and sum per head
+        // The cached rows of chunk ch2 into a tile, one copy group per tile. K of the next chunk is asked for as soon as the
+        // scores of this one are out, V as soon as P V is done, so a block that walks several chunks (a long cache) waits
+        // for neither; groups complete in the order K(ch), V(ch), K(ch + 1), .., and every wait below leaves one pending.
+        auto load_tile = [&](uint8_t *tile, const uint8_t *cache, uint32_t ch2) {
+            if (ch2 < ch_hi) {
+                constexpr int VEC = KV == BRASA_KV_Q8_0 ? 8 : 16, PER_ROW = RB / VEC;
+                const uint32_t k0 = ch2 * C, nk = min(C, lk - k0), n = ch2 == nchunks - 1 ? nk - 1 : nk;  // the new row is not in the cache yet
+#pragma unroll 1
+                for (uint32_t i = tid; i < n * PER_ROW; i += TK_THREADS) {
+                    const uint32_t r = i / PER_ROW, v = i % PER_ROW;
+                    const size_t goff = ((size_t)(k0 + r) * kv_heads + kh) * RB + (size_t)v * VEC;
+                    if (KV == BRASA_KV_Q8_0) cp_async8(tile + r * RS + v * VEC, cache + goff);
+                    else cp_async16(tile + r * RS + v * VEC, cache + goff);
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        load_tile(kt, op.kc, ch_lo);
+        load_tile(vt, op.vc, ch_lo);
 #pragma unroll 1
         for (uint32_t ch = ch_lo; ch < ch_hi; ++ch) {
         const uint32_t key0 = ch * C, nkeys = min(C, lk - key0);
         const bool has_new = ch == nchunks - 1;
-        const uint32_t nold = has_new ? nkeys - 1 : nkeys;
-        {
-            constexpr int VEC = KV == BRASA_KV_Q8_0 ? 8 : 16, PER_ROW = RB / VEC;
-#pragma unroll 1
-            for (uint32_t i = tid; i < nold * PER_ROW; i += TK_THREADS) {
-                uint32_t r = i / PER_ROW, v = i % PER_ROW;
-                size_t goff = ((size_t)(key0 + r) * kv_heads + kh) * RB + (size_t)v * VEC;
-                if (KV == BRASA_KV_Q8_0) { cp_async8(kt + r * RS + v * VEC, op.kc + goff); cp_async8(vt + r * RS + v * VEC, op.vc + goff); }
-                else { cp_async16(kt + r * RS + v * VEC, op.kc + goff); cp_async16(vt + r * RS + v * VEC, op.vc + goff); }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        }
         if ((uint32_t)warp < Gq + 2 && (((uint32_t)warp < Gq && ch == ch_lo) || ((uint32_t)warp >= Gq && has_new))) {
             // warps 0 .. Gq-1: a query head (once per item); warp Gq: the new key row; warp Gq + 1: the new value row
             const uint32_t g = warp;
@@ -630,7 +637,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             }
         }
         TRACE(1);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // K of this chunk
         __syncthreads();
         TRACE(2);
         {   // scores: KPW keys per warp, LPK lanes share a key
@@ -659,23 +666,23 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                 if (lane % LPK == 0) {
 #pragma unroll
                     for (int gg = 0; gg < 4; ++gg)
-                        if (g0 + gg < Gq) ps[(g0 + gg) * C + key] = key < nkeys ? a[gg] * attn_scale : -INFINITY;
+                        if (g0 + gg < Gq) ps[key * 8 + g0 + gg] = key < nkeys ? a[gg] * attn_scale : -INFINITY;
                 }
             }
         }
         __syncthreads();
+        load_tile(kt, op.kc, ch + 1);
         TRACE(3);
-        if ((uint32_t)warp < Gq) {  // softmax numerators of this chunk against the running maximum, head = warp
+        if ((uint32_t)warp < Gq) {  // softmax numerators of this chunk against the running maximum, head = warp; ps is [key][8 heads]
             const uint32_t g = warp;
-            float v0 = ps[g * C + lane], v1 = C == 64 ? ps[g * C + lane + 32] : -INFINITY;
+            float v0 = ps[lane * 8 + g], v1 = C == 64 ? ps[(lane + 32) * 8 + g] : -INFINITY;
             float m = fmaxf(v0, v1);
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             const float m_old = red[16 + g], m_new = fmaxf(m_old, m);
             v0 = expf(v0 - m_new);
             v1 = C == 64 ? expf(v1 - m_new) : 0.0f;
-            float *pt = reinterpret_cast<float *>(kt);  // [key][8 heads]: the K tile is done with once the scores are out
-            pt[lane * 8 + g] = v0;
-            if (C == 64) pt[(lane + 32) * 8 + g] = v1;
+            ps[lane * 8 + g] = v0;
+            if (C == 64) ps[(lane + 32) * 8 + g] = v1;
             float l = v0 + v1;
             for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
             if (lane == 0) {
@@ -685,12 +692,13 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
                 red[16 + g] = m_new;
             }
         }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // V of this chunk (K of the next one may still be on its way)
         __syncthreads();
         TRACE(4);
         {   // P V. Warp w owns output elements 8w .. 8w + 7 of every head; its lanes are 4 element pairs x 8 key classes
             // (keys ks, ks + 8, ..): a value pair is read once for all heads, the key's probabilities come as one
             // broadcast vector, and no two lanes of a load share a bank. The key classes meet at the end of the item.
-            const float *pt = reinterpret_cast<const float *>(kt);
+            const float *pt = ps;
             const int d = warp * 8 + 2 * (lane & 3);
             float acc[8][2];
 #pragma unroll
@@ -721,6 +729,7 @@ __device__ __forceinline__ void attention_op(const TokCtx &c, const TokOp &op, u
             }
         }
         __syncthreads();
+        load_tile(vt, op.vc, ch + 1);
         }  // chunks of the group
         {   // the key classes of an output element meet (lanes 4 apart), lanes 0-3 of the warp send the element pair out
             const uint32_t d = warp * 8 + 2 * (lane & 3);
