@@ -52,7 +52,7 @@ SEED = 20251
 GATE_UP_TRAFFIC_BYTES = 28_130_000
 # dram__bytes_read + dram__bytes_write of one decode_token_kernel launch at position 512 under ncu (algorithmic bytes at
 # that position: 2 436 050 976)
-TOKEN_KERNEL_TRAFFIC_BYTES = 2_454_140_000
+TOKEN_KERNEL_TRAFFIC_BYTES = 2_452_740_000
 # dram__bytes_read + dram__bytes_write of one serving decode step of 64 sequences (all its kernels, summed) under ncu,
 # captured at the first steps of the leg, where a step's algorithmic bytes are the second figure; the leg scales the
 # traffic to its own mean position by its algorithmic bytes (the KV share grows in proportion, the weights do not move)
