@@ -360,18 +360,24 @@ __device__ __forceinline__ float gemv_input(const TokCtx &c, const TokOp &op, co
         return ssq;
     }
 #pragma unroll 1
-    for (uint32_t qi = tid; qi < nq; qi += TK_THREADS) {
-        uint4 w;
+    for (uint32_t qi = tid; qi < nq; qi += 2 * TK_THREADS) {  // two quads of the thread in flight: half the round trips
+        const uint32_t qj = qi + TK_THREADS;
+        const bool two = qj < nq;
+        uint4 w0, w1 = make_uint4(0, 0, 0, 0);
         for (uint32_t it = 0;; ++it) {
-            w = vs_load4(in + quad_elem(qi));
-            if ((w.x != VS_EMPTY && w.y != VS_EMPTY && w.z != VS_EMPTY && w.w != VS_EMPTY) || *c.s_abort) break;
+            w0 = vs_load4(in + quad_elem(qi));
+            if (two) w1 = vs_load4(in + quad_elem(qj));
+            const bool ok = w0.x != VS_EMPTY && w0.y != VS_EMPTY && w0.z != VS_EMPTY && w0.w != VS_EMPTY &&
+                            w1.x != VS_EMPTY && w1.y != VS_EMPTY && w1.z != VS_EMPTY && w1.w != VS_EMPTY;
+            if (ok || *c.s_abort) break;
             if (it >= POLL_LIMIT) {
                 give_up(c, 3);
                 break;
             }
         }
         TRACE(2);
-        quad_to_fixed<P>(c, op, xw, qi, make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w)), ssq);
+        quad_to_fixed<P>(c, op, xw, qi, make_float4(__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z), __uint_as_float(w0.w)), ssq);
+        if (two) quad_to_fixed<P>(c, op, xw, qj, make_float4(__uint_as_float(w1.x), __uint_as_float(w1.y), __uint_as_float(w1.z), __uint_as_float(w1.w)), ssq);
     }
     return ssq;
 }

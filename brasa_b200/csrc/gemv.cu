@@ -275,6 +275,15 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
         if (want >= nhb) xr[i].step = 0.0f;  // lanes past the end of the row contribute nothing
     }
     const uint32_t hi_off = tiled_hi_off(p.cols), sc_off = tiled_scale_off(QT, p.cols);
+    // When every lane's half blocks before its last iteration lie inside the row (all the model shapes), the loads use
+    // addresses worked out once (row_pair_dot_at); the bias term then rides in the record's total.
+    const bool fast = N < 2 || (S * N - 2) * 32 + 31 < nhb;
+    const RowLaneOffsets lo = row_lane_offsets<QT, N>(p.cols, slice, lane);
+    if (fast) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) xr[i].total *= -(QT == BRASA_Q4_0 ? 8 : 32);
+    }
+    const uint32_t ring32 = smem_u32(ring);
     TRACE(5);
 
     // ---- consume: per iteration the block covers Wp * R rows of a segment; a warp takes R rows of one slot ----
@@ -305,7 +314,13 @@ __global__ void __maxnreg__(128) gemv_rows_kernel(GemvParams p) {
                 for (uint32_t r = 0; r < nv; r += 2) {
                     const bool two = r + 1 < nv;
                     const uint8_t *row_a = row0 + (size_t)r * row_bytes, *row_b = two ? row_a + row_bytes : row_a;
-                    float z = row_pair_dot<QT, N>(row_a, row_b, xr, slice, nhb, hi_off, sc_off, lane);
+                    float z;
+                    if (fast) {
+                        const uint32_t ra = ring32 + s * slot_bytes + (in_slot + r) * row_bytes;
+                        z = row_pair_dot_at<QT, N, GEMV_PLANES>(ra, two ? ra + row_bytes : ra, lo, xr, lane);
+                    } else {
+                        z = row_pair_dot<QT, N>(row_a, row_b, xr, slice, nhb, hi_off, sc_off, lane);
+                    }
                     // lane 0 holds row r, lane 8 row r + 1
                     if ((lane & 23) == 0 && (lane == 0 || two))
                         part[(seg_before[sgi] + ks * RPS + in_slot + r + (lane >> 3)) * S + slice] = z;

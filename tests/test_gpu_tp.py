@@ -165,12 +165,19 @@ def test_argmax_exchange_ties_and_nan(B, ctx):
             t.free()
 
 
-def test_receive_without_a_send_gives_up_and_the_context_lives(B, ctx):
+def test_receive_without_a_send_gives_up_and_the_context_lives(B, ctx, untied_model):
     """A rank whose peer never sends: the receive runs out of polls by itself (nothing faults, nothing hangs), the
-    call reports ETIMEOUT, and the same context runs the next exchange correctly."""
+    call reports ETIMEOUT, and the same context runs the next exchange correctly. A model decoding on the same context
+    with the whole-token kernel (whose activation words live across launches and are emptied after an abandoned wait)
+    gives the same tokens before and after."""
     from brasa_b200.tp import TensorParallel
     K = B.Kernels(ctx)
     n = 512
+    model = B.Qwen3.load(ctx, untied_model, B.Limits(ctx=256, max_tokens=64, max_logit_rows=1, kv=B.KvType.F16))
+    prompt = np.random.default_rng(9).integers(0, 1024, size=24).astype(np.uint32)
+    lg, _ = model.forward(prompt, 0)
+    first = int(np.argmax(lg[0]))
+    before = [int(t) for t in model.decode_greedy(first, 24, 7)[0]]  # an odd count: the next launch starts on the other copy
     tps = TensorParallel.same_process([ctx, ctx], n)
     try:
         tps[0].set_poll_limit(2000)
@@ -183,6 +190,8 @@ def test_receive_without_a_send_gives_up_and_the_context_lives(B, ctx):
             cmd.wait()
         assert err.value.code == B.ETIMEOUT
         ctx.sync()  # the status word was cleared by the failed wait: the context is clean again
+        assert [int(t) for t in model.decode_greedy(first, 24, 7)[0]] == before
+        assert [int(t) for t in model.decode_greedy(first, 24, 7)[0]] == before
         # rank 1 catches up with the abandoned exchange (its own receive finds both ranks' words), then a full one
         cmd = ctx.command()
         K.tp_allreduce_add(cmd, tps[1], part, None, out, n, phase="push")
@@ -201,6 +210,7 @@ def test_receive_without_a_send_gives_up_and_the_context_lives(B, ctx):
     finally:
         for t in tps:
             t.free()
+        model.free()
 
 
 @pytest.mark.parametrize("kv", ["F32", "F16"])
