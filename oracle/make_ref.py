@@ -1,6 +1,6 @@
 """Brings the reference's own CPU forward next to the oracle, for the benchmark's reference arm.
 
-    python oracle/make_ref.py [/path/to/reference]      (default: /root/reference)
+    python oracle/make_ref.py [/path/to/reference]      (default: the BRASA_REFERENCE environment variable, else REFERENCE_DEFAULT)
 
 The reference's CPU implementation of the token loop is three Python files (tools/qwen3_ref.py, tools/brasa_file.py,
 tools/convert_brasa.py: torch and numpy only). They are copied, unmodified, from the checkout into oracle/_ref/, which
@@ -11,15 +11,17 @@ port of this directory otherwise. Nothing else reads oracle/_ref/.
 
 from __future__ import annotations
 
+import os
 import pathlib
 import shutil
 import sys
 
 HERE = pathlib.Path(__file__).resolve().parent
 FILES = ("qwen3_ref.py", "brasa_file.py", "convert_brasa.py")
+REFERENCE_DEFAULT = pathlib.Path(os.environ.get("BRASA_REFERENCE", str(HERE.parents[1] / "reference")))
 
 
-def make(reference: str | pathlib.Path = "/root/reference") -> bool:
+def make(reference: str | pathlib.Path = REFERENCE_DEFAULT) -> bool:
     """Copies the tools when the checkout is there; returns whether oracle/_ref/ holds them afterwards."""
     src = pathlib.Path(reference) / "tools"
     dst = HERE / "_ref"
@@ -31,5 +33,5 @@ def make(reference: str | pathlib.Path = "/root/reference") -> bool:
 
 
 if __name__ == "__main__":
-    ok = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = make(sys.argv[1] if len(sys.argv) > 1 else REFERENCE_DEFAULT)
     print("oracle/_ref ready" if ok else "reference checkout not found: oracle/_ref not made")
