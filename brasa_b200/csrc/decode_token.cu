@@ -519,21 +519,30 @@ __device__ __forceinline__ void gemv_epilogue(const TokCtx &c, const TokOp &op, 
             // ranks hold the same bits.
             const size_t base = (size_t)((op.xchg - 1) & 1) * p.tp_world * p.tp_stride + r0 + j;
             for (uint32_t q = 0; q < p.tp_world; ++q) xg_store(p.tp_peer[q] + base + (size_t)p.tp_rank * p.tp_stride, __float_as_uint(v), epoch);
-            float sum = 0.0f;
-            for (uint32_t q = 0; q < p.tp_world; ++q) {
-                const unsigned long long *src = p.tp_peer[p.tp_rank] + base + (size_t)q * p.tp_stride;
-                unsigned long long w = 0;
-                for (uint32_t it = 0;; ++it) {
-                    w = xg_load(src);
-                    if ((uint32_t)(w >> 32) == epoch || *c.s_abort) break;
-                    if (it >= p.tp_poll_limit) {
-                        give_up(c, 6);
-                        break;
+            // all ranks' slots are asked for together and only the missing ones again: one round trip once they are there
+            const unsigned long long *mine = p.tp_peer[p.tp_rank] + base;
+            unsigned long long w[BRASA_TP_MAX_RANKS];
+#pragma unroll
+            for (int q = 0; q < BRASA_TP_MAX_RANKS; ++q) w[q] = 0;  // epoch 0 is never a launch's
+            for (uint32_t it = 0;; ++it) {
+                bool ok = true;
+#pragma unroll
+                for (int q = 0; q < BRASA_TP_MAX_RANKS; ++q) {
+                    if ((uint32_t)q < p.tp_world && (uint32_t)(w[q] >> 32) != epoch) {
+                        w[q] = xg_load(mine + (size_t)q * p.tp_stride);
+                        ok = ok && (uint32_t)(w[q] >> 32) == epoch;
                     }
                 }
-                const float part = __uint_as_float((uint32_t)w);
-                sum = q == 0 ? part : sum + part;
+                if (ok || *c.s_abort) break;
+                if (it >= p.tp_poll_limit) {
+                    give_up(c, 6);
+                    break;
+                }
             }
+            float sum = __uint_as_float((uint32_t)w[0]);
+#pragma unroll
+            for (int q = 1; q < BRASA_TP_MAX_RANKS; ++q)
+                if ((uint32_t)q < p.tp_world) sum += __uint_as_float((uint32_t)w[q]);
             v = sum;
         }
         if (op.epilogue == EPI_RESID) v += c.resid[j];
