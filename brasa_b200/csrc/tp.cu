@@ -96,13 +96,32 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_kernel(TpParams p, const
         bool dead = false;
         const uint64_t *mine = p.peer[p.rank] + base;
         for (uint64_t i = first; i < n2; i += stride) {
-            float sx = 0.0f, sy = 0.0f;
-            for (uint32_t r = 0; r < p.world; ++r) {
-                uint64_t a, b;
-                wait_words(mine + (uint64_t)r * p.max_elems + 2 * i, tag, a, b, dead, p.status, p.poll_limit);
-                const float vx = __uint_as_float((uint32_t)a), vy = __uint_as_float((uint32_t)b);
-                sx = r == 0 ? vx : sx + vx;
-                sy = r == 0 ? vy : sy + vy;
+            // every rank's pair is asked for together and only the missing ones again: one round trip once they are there
+            uint64_t wa[BRASA_TP_MAX_RANKS], wb[BRASA_TP_MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < BRASA_TP_MAX_RANKS; ++r) wa[r] = wb[r] = 0;  // tag 0 is never an exchange's
+            for (uint32_t it = 0; !dead; ++it) {
+                bool ok = true;
+#pragma unroll
+                for (int r = 0; r < BRASA_TP_MAX_RANKS; ++r) {
+                    if ((uint32_t)r < p.world && !((uint32_t)(wa[r] >> 32) == tag && (uint32_t)(wb[r] >> 32) == tag)) {
+                        ld_words(mine + (uint64_t)r * p.max_elems + 2 * i, wa[r], wb[r]);
+                        ok = ok && (uint32_t)(wa[r] >> 32) == tag && (uint32_t)(wb[r] >> 32) == tag;
+                    }
+                }
+                if (ok) break;
+                if (it >= p.poll_limit) {
+                    atomicExch(p.status, 6u);
+                    dead = true;
+                }
+            }
+            float sx = __uint_as_float((uint32_t)wa[0]), sy = __uint_as_float((uint32_t)wb[0]);
+#pragma unroll
+            for (int r = 1; r < BRASA_TP_MAX_RANKS; ++r) {
+                if ((uint32_t)r < p.world) {
+                    sx += __uint_as_float((uint32_t)wa[r]);
+                    sy += __uint_as_float((uint32_t)wb[r]);
+                }
             }
             float2 o = make_float2(sx, sy);
             if (resid) {
