@@ -143,6 +143,7 @@ __device__ __forceinline__ void split_h2(float x, float y, uint32_t &hi, uint32_
 __device__ __forceinline__ uint32_t piece(uint32_t r, uint32_t c) { return r * 256u + ((c ^ (r & 7u)) << 4); }
 
 constexpr uint32_t MMA_TILE = 128 * 256;  // one K or V tile
+constexpr int PAGED_MMA_TILES = 2;       // groups of 16 / G sequences a shared-prefix block serves with one pair of tiles
 constexpr size_t MMA_SMEM = 2 * MMA_TILE + (2 * 4 * 16 + 16) * sizeof(float);  // three blocks per SM
 
 __device__ __forceinline__ void mma_f16_full(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -160,14 +161,16 @@ template <bool MULTI>
 __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const float *q, Paged kp, Paged vp, const uint32_t *lens, float *partials,
                                                                        uint32_t hq, uint32_t max_chunks, float scale, uint32_t first_chunk, uint32_t nseq) {
     constexpr int RH = MULTI ? 2 : 1;  // row halves in use: rows g (and g + 8)
+    // MULTI: a block serves PAGED_MMA_TILES groups of 16 / G sequences with the same K and V tiles: all their scores first (K is
+    // then done with), then group by group softmax, P V and the four warps' sum in shared memory over the K tile.
+    constexpr int RT = MULTI ? PAGED_MMA_TILES : 1;
     extern __shared__ __align__(128) uint8_t smem_b[];
     uint8_t *kt = smem_b, *vt = smem_b + MMA_TILE;
     float *osum = reinterpret_cast<float *>(kt);  // [4 warps][16 rows][128], over the K tile once every warp is done with it
     float *wmax = reinterpret_cast<float *>(smem_b + 2 * MMA_TILE), *wsum = wmax + 4 * 16;  // [4 warps][16 rows] each
     const uint32_t chunk = first_chunk + blockIdx.x, kh = blockIdx.y, hkv = kp.hkv, G = hq / hkv;
-    const uint32_t spb = MULTI ? 16 / G : 1, seq0 = blockIdx.z * spb;
-    const uint32_t nrows = min(spb, nseq - seq0) * G;  // rows of the MMA that carry a (sequence, head)
-    const uint32_t lk = MULTI ? (chunk + 1) * 128 : lens[seq0] + 1;
+    const uint32_t spb = MULTI ? 16 / G : 1, seq00 = blockIdx.z * spb * RT;
+    const uint32_t lk = MULTI ? (chunk + 1) * 128 : lens[seq00] + 1;
     if (chunk * 128 >= lk) return;
     const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
     const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
@@ -175,40 +178,43 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
     for (uint32_t i = t; i < 128 * 16; i += 128) {
         const uint32_t r = i >> 4, c = i & 15;
         const bool ok = r < nkeys;
-        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq0, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq00, key0 + (ok ? r : 0), kh) + 16 * c, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     for (uint32_t i = t; i < 128 * 16; i += 128) {
         const uint32_t r = i >> 4, c = i & 15;
         const bool ok = r < nkeys;
-        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq0, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq00, key0 + (ok ? r : 0), kh) + 16 * c, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    // ---- Q fragments of rows g and g + 8: for k-step ks, a0/a1 = dims 16 ks + 2 tq, +1; a2/a3 = those + 8 ----
-    uint32_t qh0[RH][8], qh2[RH][8], ql0[RH][8], ql2[RH][8];
-#pragma unroll
-    for (int rh = 0; rh < RH; ++rh) {
-        const uint32_t r = g + 8 * rh;
-        const bool live = r < nrows;
-        const float *qrow = q + ((size_t)(seq0 + (live ? r / G : 0)) * hq + kh * G + (live ? r % G : 0)) * D;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            float2 a = make_float2(0.0f, 0.0f), b = a;
-            if (live) {
-                a = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq);
-                b = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq + 8);
-            }
-            split_h2(a.x, a.y, qh0[rh][ks], ql0[rh][ks]);
-            split_h2(b.x, b.y, qh2[rh][ks], ql2[rh][ks]);
-        }
-    }
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    // ---- S[row g (c0, c1) and g + 8 (c2, c3)][keys 32 warp + 8 j + 2 tq, +1], j = 0..3 ----
-    float sc[4][4];
+    // ---- S[row g (c0, c1) and g + 8 (c2, c3)][keys 32 warp + 8 j + 2 tq, +1], j = 0..3, for every group of sequences ----
+    float sc[RT][4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
-    {
+    for (int rt = 0; rt < RT; ++rt) {
+        const uint32_t seq0 = seq00 + rt * spb;
+        const uint32_t nrows = seq0 < nseq ? min(spb, nseq - seq0) * G : 0u;  // rows of the MMA that carry a (sequence, head)
+        // Q fragments of rows g and g + 8: for k-step ks, a0/a1 = dims 16 ks + 2 tq, +1; a2/a3 = those + 8
+        uint32_t qh0[RH][8], qh2[RH][8], ql0[RH][8], ql2[RH][8];
+#pragma unroll
+        for (int rh = 0; rh < RH; ++rh) {
+            const uint32_t r = g + 8 * rh;
+            const bool live = r < nrows;
+            const float *qrow = q + ((size_t)(seq0 + (live ? r / G : 0)) * hq + kh * G + (live ? r % G : 0)) * D;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                float2 a = make_float2(0.0f, 0.0f), b = a;
+                if (live) {
+                    a = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq);
+                    b = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * tq + 8);
+                }
+                split_h2(a.x, a.y, qh0[rh][ks], ql0[rh][ks]);
+                split_h2(b.x, b.y, qh2[rh][ks], ql2[rh][ks]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sc[rt][j][0] = sc[rt][j][1] = sc[rt][j][2] = sc[rt][j][3] = 0.0f;
         // ldmatrix.x4: lanes 0-7 address rows of tile 0, 8-15 tile 1, 16-23 tile 2, 24-31 tile 3;
         // tiles = (dims 16 ks .. +7), (dims 16 ks + 8 ..), (dims 16 (ks + 1) ..), (dims 16 (ks + 1) + 8 ..) of 8 keys
         const uint32_t lrow = lane & 7, ltile = lane >> 3;
@@ -223,93 +229,100 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
                 for (int u = 0; u < 2; ++u) {
                     const uint32_t h1 = MULTI ? qh0[RH - 1][ks + u] : 0u, h3 = MULTI ? qh2[RH - 1][ks + u] : 0u;
                     const uint32_t l1 = MULTI ? ql0[RH - 1][ks + u] : 0u, l3 = MULTI ? ql2[RH - 1][ks + u] : 0u;
-                    mma_f16_full(sc[j], qh0[0][ks + u], h1, qh2[0][ks + u], h3, b[2 * u], b[2 * u + 1]);
-                    mma_f16_full(sc[j], ql0[0][ks + u], l1, ql2[0][ks + u], l3, b[2 * u], b[2 * u + 1]);
+                    mma_f16_full(sc[rt][j], qh0[0][ks + u], h1, qh2[0][ks + u], h3, b[2 * u], b[2 * u + 1]);
+                    mma_f16_full(sc[rt][j], ql0[0][ks + u], l1, ql2[0][ks + u], l3, b[2 * u], b[2 * u + 1]);
                 }
             }
         }
     }
-    // ---- scale, mask, row maxima over the block ----
-    float mx[RH], m[RH], l[RH];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // V (waited for here once; the barriers below publish it)
 #pragma unroll
-    for (int rh = 0; rh < RH; ++rh) {
-        mx[rh] = -INFINITY;
+    for (int rt = 0; rt < RT; ++rt) {
+        const uint32_t seq0 = seq00 + rt * spb;
+        const uint32_t nrows = seq0 < nseq ? min(spb, nseq - seq0) * G : 0u;
+        if (nrows == 0) break;  // (the same for the whole block)
+        // ---- scale, mask, row maxima over the block ----
+        float mx[RH], m[RH], l[RH];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int rh = 0; rh < RH; ++rh) {
+            mx[rh] = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const uint32_t key = 32 * warp + 8 * j + 2 * tq + e;
-                const float v = key < nkeys ? sc[j][2 * rh + e] * scale : -INFINITY;
-                sc[j][2 * rh + e] = v;
-                mx[rh] = fmaxf(mx[rh], v);
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t key = 32 * warp + 8 * j + 2 * tq + e;
+                    const float v = key < nkeys ? sc[rt][j][2 * rh + e] * scale : -INFINITY;
+                    sc[rt][j][2 * rh + e] = v;
+                    mx[rh] = fmaxf(mx[rh], v);
+                }
+            }
+            mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 1));
+            mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 2));
+            if (tq == 0) wmax[warp * 16 + g + 8 * rh] = mx[rh];
+        }
+        __syncthreads();  // (also: every warp is done with the K tile, whose place osum takes)
+        uint32_t ph[RH][4], pl[RH][4];  // P of n-tile j as packed pairs: A fragment a0/a1 (j even) or a2/a3 (j odd) of k-step j / 2
+#pragma unroll
+        for (int rh = 0; rh < RH; ++rh) {
+            const uint32_t r = g + 8 * rh;
+            m[rh] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
+            l[rh] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float s0 = sc[rt][j][2 * rh], s1 = sc[rt][j][2 * rh + 1];
+                const float p0 = s0 == -INFINITY ? 0.0f : expf(s0 - m[rh]), p1 = s1 == -INFINITY ? 0.0f : expf(s1 - m[rh]);
+                l[rh] += p0 + p1;
+                split_h2(p0, p1, ph[rh][j], pl[rh][j]);
+            }
+            l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 1);
+            l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 2);
+            if (tq == 0) wsum[warp * 16 + r] = l[rh];
+        }
+        __syncthreads();
+        // ---- O[row][dims 8 n + 2 tq, +1] += P[16 x 32 keys] V[32 keys x 128 dims] ----
+        float oc[16][4];
+#pragma unroll
+        for (int n = 0; n < 16; ++n) oc[n][0] = oc[n][1] = oc[n][2] = oc[n][3] = 0.0f;
+        {
+            // ldmatrix.x4.trans over V rows (keys): tiles = (keys 0-7, dims 8 n ..), (keys 8-15, dims 8 n ..),
+            // (keys 0-7, dims 8 (n + 1) ..), (keys 8-15, dims 8 (n + 1) ..) -> b0, b1 of n-tile n and of n-tile n + 1
+            const uint32_t lrow = lane & 7, ltile = lane >> 3;
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                const uint32_t vrow = 32 * warp + 16 * kk + 8 * (ltile & 1) + lrow;
+                const uint32_t h1 = MULTI ? ph[RH - 1][2 * kk] : 0u, h3 = MULTI ? ph[RH - 1][2 * kk + 1] : 0u;
+                const uint32_t l1 = MULTI ? pl[RH - 1][2 * kk] : 0u, l3 = MULTI ? pl[RH - 1][2 * kk + 1] : 0u;
+#pragma unroll
+                for (int n = 0; n < 16; n += 2) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vt + piece(vrow, n + (ltile >> 1)));
+                    mma_f16_full(oc[n], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[0], b[1]);
+                    mma_f16_full(oc[n], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[0], b[1]);
+                    mma_f16_full(oc[n + 1], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[2], b[3]);
+                    mma_f16_full(oc[n + 1], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[2], b[3]);
+                }
             }
         }
-        mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 1));
-        mx[rh] = fmaxf(mx[rh], __shfl_xor_sync(0xffffffffu, mx[rh], 2));
-        if (tq == 0) wmax[warp * 16 + g + 8 * rh] = mx[rh];
-    }
-    __syncthreads();
-    uint32_t ph[RH][4], pl[RH][4];  // P of n-tile j as packed pairs: A fragment a0/a1 (j even) or a2/a3 (j odd) of k-step j / 2
 #pragma unroll
-    for (int rh = 0; rh < RH; ++rh) {
-        const uint32_t r = g + 8 * rh;
-        m[rh] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
-        l[rh] = 0.0f;
+        for (int rh = 0; rh < RH; ++rh) {
+            const uint32_t r = g + 8 * rh;
+            if (r < nrows) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float s0 = sc[j][2 * rh], s1 = sc[j][2 * rh + 1];
-            const float p0 = s0 == -INFINITY ? 0.0f : expf(s0 - m[rh]), p1 = s1 == -INFINITY ? 0.0f : expf(s1 - m[rh]);
-            l[rh] += p0 + p1;
-            split_h2(p0, p1, ph[rh][j], pl[rh][j]);
-        }
-        l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 1);
-        l[rh] += __shfl_xor_sync(0xffffffffu, l[rh], 2);
-        if (tq == 0) wsum[warp * 16 + r] = l[rh];
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    // ---- O[row][dims 8 n + 2 tq, +1] += P[16 x 32 keys] V[32 keys x 128 dims] ----
-    float oc[16][4];
-#pragma unroll
-    for (int n = 0; n < 16; ++n) oc[n][0] = oc[n][1] = oc[n][2] = oc[n][3] = 0.0f;
-    {
-        // ldmatrix.x4.trans over V rows (keys): tiles = (keys 0-7, dims 8 n ..), (keys 8-15, dims 8 n ..),
-        // (keys 0-7, dims 8 (n + 1) ..), (keys 8-15, dims 8 (n + 1) ..) -> b0, b1 of n-tile n and of n-tile n + 1
-        const uint32_t lrow = lane & 7, ltile = lane >> 3;
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-            const uint32_t vrow = 32 * warp + 16 * kk + 8 * (ltile & 1) + lrow;
-            const uint32_t h1 = MULTI ? ph[RH - 1][2 * kk] : 0u, h3 = MULTI ? ph[RH - 1][2 * kk + 1] : 0u;
-            const uint32_t l1 = MULTI ? pl[RH - 1][2 * kk] : 0u, l3 = MULTI ? pl[RH - 1][2 * kk + 1] : 0u;
-#pragma unroll
-            for (int n = 0; n < 16; n += 2) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, vt + piece(vrow, n + (ltile >> 1)));
-                mma_f16_full(oc[n], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[0], b[1]);
-                mma_f16_full(oc[n], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[0], b[1]);
-                mma_f16_full(oc[n + 1], ph[0][2 * kk], h1, ph[0][2 * kk + 1], h3, b[2], b[3]);
-                mma_f16_full(oc[n + 1], pl[0][2 * kk], l1, pl[0][2 * kk + 1], l3, b[2], b[3]);
+                for (int n = 0; n < 16; ++n)
+                    *reinterpret_cast<float2 *>(osum + (warp * 16 + r) * D + 8 * n + 2 * tq) = make_float2(oc[n][2 * rh], oc[n][2 * rh + 1]);
             }
         }
-    }
-#pragma unroll
-    for (int rh = 0; rh < RH; ++rh) {
-        const uint32_t r = g + 8 * rh;
-        if (r < nrows) {
-#pragma unroll
-            for (int n = 0; n < 16; ++n)
-                *reinterpret_cast<float2 *>(osum + (warp * 16 + r) * D + 8 * n + 2 * tq) = make_float2(oc[n][2 * rh], oc[n][2 * rh + 1]);
+        __syncthreads();
+        for (uint32_t r = 0; r < nrows; ++r) {
+            const uint32_t seq = seq0 + r / G, h = kh * G + r % G;
+            float *out = partials + (((size_t)seq * hq + h) * max_chunks + chunk) * 130;
+            out[2 + t] = (osum[(0 * 16 + r) * D + t] + osum[(1 * 16 + r) * D + t]) + (osum[(2 * 16 + r) * D + t] + osum[(3 * 16 + r) * D + t]);
+            if (t == 0) {
+                out[0] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
+                out[1] = (wsum[r] + wsum[16 + r]) + (wsum[32 + r] + wsum[48 + r]);
+            }
         }
-    }
-    __syncthreads();
-    for (uint32_t r = 0; r < nrows; ++r) {
-        const uint32_t seq = seq0 + r / G, h = kh * G + r % G;
-        float *out = partials + (((size_t)seq * hq + h) * max_chunks + chunk) * 130;
-        out[2 + t] = (osum[(0 * 16 + r) * D + t] + osum[(1 * 16 + r) * D + t]) + (osum[(2 * 16 + r) * D + t] + osum[(3 * 16 + r) * D + t]);
-        if (t == 0) {
-            out[0] = fmaxf(fmaxf(wmax[r], wmax[16 + r]), fmaxf(wmax[32 + r], wmax[48 + r]));
-            out[1] = (wsum[r] + wsum[16 + r]) + (wsum[32 + r] + wsum[48 + r]);
-        }
+        if (RT > 1) __syncthreads();  // the next group of sequences reuses wmax, wsum and osum
     }
 }
 
@@ -574,7 +587,7 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
             const uint32_t shared_chunks = (n > 1 && 16 % G == 0 && G < 16) ? b->common_pages * PAGE / 128 : 0;
             if (shared_chunks) {
                 const uint32_t spb = 16 / G;
-                decode_partial_paged_mma_kernel<true><<<dim3(shared_chunks, c.kv_heads, (n + spb - 1) / spb), 128, MMA_SMEM, ctx->stream>>>(
+                decode_partial_paged_mma_kernel<true><<<dim3(shared_chunks, c.kv_heads, (n + spb * PAGED_MMA_TILES - 1) / (spb * PAGED_MMA_TILES)), 128, MMA_SMEM, ctx->stream>>>(
                     F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, 0, n);
                 BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma_shared"));
             }
