@@ -419,6 +419,8 @@ struct brasa_batch {
     uint64_t max_chunks = 0;
     brasa_buf *kpool = nullptr, *vpool = nullptr, *table = nullptr, *lens = nullptr, *ids = nullptr, *rng = nullptr, *logits = nullptr,
               *partials = nullptr, *scratch = nullptr, *out = nullptr;
+    brasa_buf *tp_pad = nullptr, *tp_full = nullptr;  // tensor parallel: full-width logits of tp_rows sequences (this rank's share, all ranks')
+    uint32_t tp_rows = 0;
     std::vector<int32_t> h_table;  // host mirror [max_seqs][max_pages]
     std::vector<uint32_t> h_lens;
     std::vector<brasa_buf *> owned;
@@ -507,18 +509,47 @@ int32_t batch_residual_add(brasa_model *m, brasa_cmd *cmd, uint64_t n) {
     return brasa_k_add(cmd, A(m->x), A(m->h), A(m->x), n);
 }
 
+// full[r][v] = shard[r][v - row0] for this rank's rows of the vocabulary, 0 elsewhere
+__global__ void spread_shard_kernel(const float *shard, float *full, uint32_t n, uint32_t rows, uint32_t row0, uint32_t vocab) {
+    const uint64_t tot = (uint64_t)n * vocab;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < tot; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / vocab), v = (uint32_t)(i - (uint64_t)r * vocab);
+        full[i] = (v >= row0 && v < row0 + rows) ? shard[(size_t)r * rows + (v - row0)] : 0.0f;
+    }
+}
+
 // Next token of `count` rows of logits (row stride = this rank's lm_head rows). A tensor-parallel shard holds only its
-// rows of the vocabulary: the choice is greedy, each row's best (value, index) pair exchanged between the ranks.
+// rows of the vocabulary: a greedy choice exchanges each row's best (value, index) pair between the ranks, a sampled one the rows.
 int32_t choose_tokens(brasa_batch *b, brasa_cmd *cmd, brasa_buf *logits, uint32_t count, brasa_sampling_params params, unsigned long long *rng,
                       float *scratch, brasa_buf *out, uint64_t out_index) {
     brasa_model *m = b->m;
     const uint32_t rows = m->cfg.head_rows;
-    if (!m->tp)
+    if (!m->tp || (params.temperature > 0.0f && rows == m->cfg.vocab))  // (a one-rank group holds the whole vocabulary)
         return brasa_sample_batched_launch(cmd, F(logits), rows, count, params.temperature, params.top_k, params.top_p, rng, scratch,
                                            (uint32_t *)out->ptr + out_index);
-    BRASA_REQUIRE(b->ctx, params.temperature <= 0.0f, "batch: a tensor-parallel shard decodes greedily (temperature 0)");
-    for (uint32_t r = 0; r < count; ++r)
-        BRASA_TRY(brasa_k_tp_argmax(cmd, m->tp, A(logits, (uint64_t)r * rows * 4), rows, m->cfg.head_row0, A(out, (out_index + r) * 4)));
+    if (params.temperature <= 0.0f) {
+        for (uint32_t r = 0; r < count; ++r)
+            BRASA_TRY(brasa_k_tp_argmax(cmd, m->tp, A(logits, (uint64_t)r * rows * 4), rows, m->cfg.head_row0, A(out, (out_index + r) * 4)));
+        return BRASA_OK;
+    }
+    // Sampling needs every row's logits over the whole vocabulary on every rank. Each rank lays its rows of the vocabulary
+    // into a zeroed full-width copy and the copies are added across the ranks (x + 0 is exact, so the sum is the
+    // concatenation, bit for bit the same on every rank); then every rank runs the same sampler on the same numbers with
+    // the same PCG32 streams and draws the same tokens. As many sequences per exchange as it can carry.
+    const uint32_t vocab = m->cfg.vocab;
+    const uint64_t cap = brasa_tp_max_elems(m->tp);
+    BRASA_REQUIRE(b->ctx, b->tp_pad && b->tp_full && vocab % 2 == 0 && cap >= vocab, "batch: the tensor-parallel exchange is too small for one row of logits (%u values)", vocab);
+    const uint32_t per = (uint32_t)std::min<uint64_t>(b->tp_rows, cap / vocab);
+    for (uint32_t r0 = 0; r0 < count; r0 += per) {
+        const uint32_t n = std::min(per, count - r0);
+        const uint64_t tot = (uint64_t)n * vocab;
+        spread_shard_kernel<<<(unsigned)std::min<uint64_t>((tot + 255) / 256, 4096), 256, 0, b->ctx->stream>>>(
+            F(logits) + (size_t)r0 * rows, F(b->tp_pad), n, rows, m->cfg.head_row0, vocab);
+        BRASA_TRY(brasa_post_launch(cmd, "spread_shard"));
+        BRASA_TRY(brasa_k_tp_allreduce_add(cmd, m->tp, A(b->tp_pad), brasa_arg{nullptr, 0}, A(b->tp_full), tot));
+        BRASA_TRY(brasa_sample_batched_launch(cmd, F(b->tp_full), vocab, n, params.temperature, params.top_k, params.top_p, rng + 2 * (size_t)r0,
+                                              scratch + (size_t)r0 * 2 * vocab, (uint32_t *)out->ptr + out_index + r0));
+    }
     return BRASA_OK;
 }
 
@@ -722,6 +753,8 @@ int32_t brasa_plan_batch(const brasa_model_shape *m, const brasa_batch_shape *s,
     out->logits = g((uint64_t)s->max_seqs * s->head_rows * 4);
     out->attention_partials = g((uint64_t)s->max_seqs * m->heads * max_chunks * 130 * 4);
     out->sampler = g((uint64_t)s->max_seqs * 2 * m->vocab * 4);
+    // a tensor-parallel shard (fewer lm_head rows than the vocabulary) samples over logits gathered from all ranks
+    if (s->head_rows < m->vocab) out->sampler += 2 * g((uint64_t)s->max_seqs * m->vocab * 4);
     out->total = out->kv_pages + out->tables + out->logits + out->attention_partials + out->sampler;
     return BRASA_OK;
 }
@@ -817,6 +850,11 @@ int32_t brasa_batch_create(brasa_model *m, uint32_t max_seqs, uint32_t num_pages
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.head_rows * 4, &b->logits));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.heads * b->max_chunks * 130 * 4, &b->partials));
     BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * 2 * m->cfg.vocab * 4, &b->scratch));
+    if (m->cfg.head_rows < m->cfg.vocab) {
+        BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.vocab * 4, &b->tp_pad));
+        BRASA_TRY(balloc(b.get(), (uint64_t)max_seqs * m->cfg.vocab * 4, &b->tp_full));
+        b->tp_rows = max_seqs;
+    }
     b->h_table.assign((size_t)max_seqs * b->max_pages, 0);
     b->h_lens.assign(max_seqs, 0);
     b->resident.assign(b->max_pages, 0);

@@ -58,6 +58,8 @@ int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes);
 // peer[r] points at rank r's area, laid out [2 parities][world][stride] words {f32, epoch} (partial sums of a residual
 // add, slot = sending rank) followed by [2][world][2] words (best logit, its index).
 struct brasa_tp;
+// values one exchange of this group can carry
+uint64_t brasa_tp_max_elems(const brasa_tp *tp);
 struct brasa_tp_token_area {
     uint32_t world, rank;
     uint64_t stride;

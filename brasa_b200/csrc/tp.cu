@@ -231,6 +231,8 @@ int32_t brasa_tp_gemv_allreduce_launch(brasa_cmd *cmd, brasa_tp *tp, const brasa
     return BRASA_OK;
 }
 
+uint64_t brasa_tp_max_elems(const brasa_tp *tp) { return tp ? tp->max_elems : 0; }
+
 int32_t brasa_tp_allreduce_add_launch(brasa_cmd *cmd, brasa_tp *tp, const float *src, const float *resid, float *out, uint64_t n, int phases) {
     brasa_ctx *ctx = cmd->ctx;
     BRASA_REQUIRE(ctx, tp->connected, "tp: the ranks are not connected yet");

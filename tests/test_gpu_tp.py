@@ -313,3 +313,11 @@ def test_two_processes_two_devices_match_the_unsplit_model(B, ctx, untied_model,
     assert np.abs(got_bl - want_bl).max() <= tol * np.abs(want_bl).max()
     assert np.array_equal(ranks[0]["batch_ids"], ranks[1]["batch_ids"])
     assert np.array_equal(ranks[0]["batch_ids"], want_bids)
+    # sampled: the ranks drew the same tokens, and each sequence's first one is the oracle sampler's choice on the
+    # gathered logits of its prompt with that sequence's stream
+    assert np.array_equal(ranks[0]["sampled_ids"], ranks[1]["sampled_ids"])
+    if kv == "F32":  # (with f16 GEMM inputs a prompt prefilled whole and one prefilled behind the cached prefix differ in the last bits)
+        full = np.concatenate([r["prompt_last"] for r in ranks], axis=1)
+        for i in range(3):
+            assert O.Sampler(temperature=0.7, top_k=0, top_p=0.95, seed=100 + i).sample(full[i]) == int(ranks[0]["sampled_ids"][i, 0])
+    assert len({tuple(r) for r in ranks[0]["sampled_ids"].tolist()}) > 1

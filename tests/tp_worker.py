@@ -53,7 +53,23 @@ def main():
     dist.barrier()
     bids, _ = bt.decode(8)
     bt.free()
-    np.savez(out_dir / f"rank{rank}.npz", logits=logits, one=one, toks=toks, toks2=toks2, row0=m.cfg["head_row0"], batch_logits=bl, batch_ids=bids)
+    # the same sequences sampled: every rank gathers the rows' logits over the whole vocabulary and draws with the same streams
+    params = B.SamplingParams(temperature=0.7, top_k=0, top_p=0.95, seed=100)
+    bt = B.Batch(m, max_seqs=3, num_pages=16, max_positions=64)
+    dist.barrier()
+    bt.set_prefix(prefix)
+    for o in own:
+        dist.barrier()
+        bt.add_sequence(o, params)
+    dist.barrier()
+    sids, _ = bt.decode(8, params)
+    bt.free()
+    plast = []
+    for o in own:  # this rank's rows of the logits each first token was drawn from
+        dist.barrier()
+        plast.append(m.forward(np.concatenate([prefix, o]), 0)[0][0])
+    np.savez(out_dir / f"rank{rank}.npz", logits=logits, one=one, toks=toks, toks2=toks2, row0=m.cfg["head_row0"], batch_logits=bl, batch_ids=bids,
+             sampled_ids=sids, prompt_last=np.stack(plast))
     dist.barrier()
     m.free()
     tp.free()
