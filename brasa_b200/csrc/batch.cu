@@ -159,7 +159,13 @@ __device__ __forceinline__ void mma_f16_full(float c[4], uint32_t a0, uint32_t a
 // sequence (the prefix pages are the same for all).
 template <bool MULTI>
 __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const float *q, Paged kp, Paged vp, const uint32_t *lens, float *partials,
-                                                                       uint32_t hq, uint32_t max_chunks, float scale, uint32_t first_chunk, uint32_t nseq) {
+                                                                       uint32_t hq, uint32_t max_chunks, float scale, uint32_t first_chunk, uint32_t nseq,
+                                                                       uint32_t late_wait) {
+    // Launched as a programmatic dependent. late_wait: the kernel before this one is the shared-prefix form of the same step,
+    // which has itself waited for the step's K/V rows and whose output this one does not read: the two run side by side,
+    // and this one waits for the other only at its end, so that whoever waits for this kernel has waited for both.
+    if (!late_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int RH = MULTI ? 2 : 1;  // row halves in use: rows g (and g + 8)
     // MULTI: a block serves PAGED_MMA_TILES groups of 16 / G sequences with the same K and V tiles: all their scores first (K is
     // then done with), then group by group softmax, P V and the four warps' sum in shared memory over the K tile.
@@ -171,7 +177,10 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
     const uint32_t chunk = first_chunk + blockIdx.x, kh = blockIdx.y, hkv = kp.hkv, G = hq / hkv;
     const uint32_t spb = MULTI ? 16 / G : 1, seq00 = blockIdx.z * spb * RT;
     const uint32_t lk = MULTI ? (chunk + 1) * 128 : lens[seq00] + 1;
-    if (chunk * 128 >= lk) return;
+    if (chunk * 128 >= lk) {
+        if (late_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
     const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
     const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
     // ---- K then V: 128 rows x 16 pieces each; rows past the end are zero-filled ----
@@ -324,11 +333,14 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
         }
         if (RT > 1) __syncthreads();  // the next group of sequences reuses wmax, wsum and osum
     }
+    if (late_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // grid (head, sequence); output f32 or f16 (the input type of the o_proj GEMM)
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(128) decode_reduce_paged_kernel(const float *partials, const uint32_t *lens, void *o, uint32_t hq, uint32_t max_chunks) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (launched as a programmatic dependent: see brasa_launch_dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t h = blockIdx.x, seq = blockIdx.y, t = threadIdx.x;
     const uint32_t chunks = (lens[seq] + 1 + 127) / 128;
     const float *p = partials + ((size_t)seq * hq + h) * max_chunks * 130;
@@ -353,6 +365,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_paged_kernel(float *q,
                                                                        const float *cos_t, const float *sin_t, uint8_t *kpool, uint8_t *vpool,
                                                                        const int32_t *table, uint32_t max_pages, const uint32_t *lens, uint32_t hq,
                                                                        uint32_t hkv, float eps, uint32_t rows) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (launched as a programmatic dependent: see brasa_launch_dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __align__(16) uint8_t scratch[4][528];
     const uint32_t gr = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -609,29 +623,33 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         else if (m->limits.kv == BRASA_KV_F16) {
                 BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<false>, MMA_SMEM));
                 BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<true>, MMA_SMEM));
-            qk_norm_rope_store_paged_kernel<BRASA_KV_F16><<<(rows + 3) / 4, 128, 0, ctx->stream>>>(
-                F(m->q), F(m->k_new), F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages, lens, c.heads,
-                c.kv_heads, c.eps, rows);
+            // the step's kernels are programmatic dependents of one another: each sets itself up while the one before it ends
+            BRASA_CUDA(ctx, brasa_launch_dependent(ctx, qk_norm_rope_store_paged_kernel<BRASA_KV_F16>, dim3((rows + 3) / 4), dim3(128), 0, F(m->q), F(m->k_new),
+                                                   F(m->v_new), F(l.q_norm), F(l.k_norm), F(m->rope_cos), F(m->rope_sin), kl, vl, table, b->max_pages, lens,
+                                                   c.heads, c.kv_heads, c.eps, rows));
             BRASA_TRY(brasa_post_launch(cmd, "qk_norm_rope_store_paged"));
             // chunks wholly inside the shared prefix: one block serves 16 / G sequences; the rest per sequence
             const uint32_t G = c.heads / c.kv_heads;
             const uint32_t shared_chunks = (n > 1 && 16 % G == 0 && G < 16) ? b->common_pages * PAGE / 128 : 0;
             if (shared_chunks) {
                 const uint32_t spb = 16 / G;
-                decode_partial_paged_mma_kernel<true><<<dim3(shared_chunks, c.kv_heads, (n + spb * PAGED_MMA_TILES - 1) / (spb * PAGED_MMA_TILES)), 128, MMA_SMEM, ctx->stream>>>(
-                    F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, 0, n);
+                BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_partial_paged_mma_kernel<true>,
+                                                       dim3(shared_chunks, c.kv_heads, (n + spb * PAGED_MMA_TILES - 1) / (spb * PAGED_MMA_TILES)), dim3(128), MMA_SMEM,
+                                                       F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, 0u, n, 0u));
                 BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma_shared"));
             }
             if ((uint32_t)b->max_chunks > shared_chunks) {
-                decode_partial_paged_mma_kernel<false><<<dim3((uint32_t)b->max_chunks - shared_chunks, c.kv_heads, n), 128, MMA_SMEM, ctx->stream>>>(
-                    F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale, shared_chunks, n);
+                // (behind the shared-prefix form it runs beside it and waits for it at its end)
+                BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_partial_paged_mma_kernel<false>, dim3((uint32_t)b->max_chunks - shared_chunks, c.kv_heads, n),
+                                                       dim3(128), MMA_SMEM, F(m->q), kp, vp, lens, F(b->partials), c.heads, (uint32_t)b->max_chunks, scale,
+                                                       shared_chunks, n, shared_chunks ? 1u : 0u));
                 BRASA_TRY(brasa_post_launch(cmd, "decode_partial_paged_mma"));
             }
         } else if (m->limits.kv == BRASA_KV_F16) LAUNCH_BATCH(BRASA_KV_F16);
         else LAUNCH_BATCH(BRASA_KV_Q8_0);
 #undef LAUNCH_BATCH
-        if (half_io) decode_reduce_paged_kernel<true><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
-        else decode_reduce_paged_kernel<false><<<rgrid, 128, 0, ctx->stream>>>(F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks);
+        if (half_io) BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_reduce_paged_kernel<true>, rgrid, dim3(128), 0, F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks));
+        else BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_reduce_paged_kernel<false>, rgrid, dim3(128), 0, F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks));
         BRASA_TRY(brasa_post_launch(cmd, "decode_reduce_paged"));
         if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.wo.q, A(m->xh), A(m->x), A(m->h), n));
         else {
@@ -725,7 +743,7 @@ int32_t brasa_k_decode_attention_paged(brasa_cmd *cmd, brasa_arg q, brasa_paged_
     dim3 agrid(max_chunks, hkv, pg.seqs), rgrid(hq, pg.seqs);
     if (pg.kv == BRASA_KV_F16) {  // tensor-core partials (one block per chunk, kv head and sequence)
         BRASA_TRY(brasa_smem_optin(ctx, (const void *)decode_partial_paged_mma_kernel<false>, MMA_SMEM));
-        decode_partial_paged_mma_kernel<false><<<agrid, 128, MMA_SMEM, ctx->stream>>>(qp, kp, vp, lens, pp, hq, max_chunks, scale, 0, pg.seqs);
+        decode_partial_paged_mma_kernel<false><<<agrid, 128, MMA_SMEM, ctx->stream>>>(qp, kp, vp, lens, pp, hq, max_chunks, scale, 0, pg.seqs, 0);
     } else {
         const size_t smem = (128 * TS + 8 * D + 8 * 128 + 16) * sizeof(float);
         if (pg.kv == BRASA_KV_F32) {

@@ -50,6 +50,25 @@ struct brasa_ctx {
     uint32_t *gemm_counters = nullptr;  // arrivals per output tile of that GEMM (GEMM_TC_COUNTERS words, zero between launches)
 };
 
+// Launches `kernel` as a programmatic dependent of the kernel before it on the context's stream: it may start while that
+// kernel is still running and must execute griddepcontrol.wait before it touches anything that kernel produces (and the
+// kernels before that one are complete by then only if every kernel of the chain waits before it lets its own dependent
+// start). With BRASA_PDL=0 it is an ordinary launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t brasa_launch_dependent(brasa_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Makes at least `bytes` of dynamic shared memory available to kernel `fn` on the context's device (the grant is
 // per device and kernel, shared by every context of the process on that device, and never lowered; cheap afterwards).
 int32_t brasa_smem_optin(brasa_ctx *ctx, const void *fn, size_t bytes);

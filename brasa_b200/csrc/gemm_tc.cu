@@ -132,6 +132,29 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // Launched as a programmatic dependent: everything above ran while the kernel before this one was still finishing, and
+    // so do the copies of the first stages' weights (weights never change); that kernel's results (X, the residual, the
+    // split-K workspace) are read only after the wait.
+    auto issue_weights = [&](uint32_t k) {  // raw codes and scales of stage k (RAW only); the stage's byte count is announced here
+        const uint32_t s = k % NS;
+        uint8_t *raw = smem + (size_t)s * stage_bytes + MT * A_TILE + NB * B_TILE;
+        mbar_expect_tx(&full_x[s], MT * A_TILE + NB * 2 * RAW_TILE);
+        const CUtensorMap *wm = &wmaps.m[mi];
+        const uint32_t kk = kbeg + k, sc_x = tiled_scale_off(BRASA_Q4_0, p.cols) + 32 * (kk >> 3);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(raw)),
+                     "l"(wm), "r"((int)(kk * 32)), "r"((int)n0), "r"(smem_u32(&full_x[s]))
+                     : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         smem_u32(raw + NB * RAW_TILE)),
+                     "l"(wm), "r"((int)sc_x), "r"((int)n0), "r"(smem_u32(&full_x[s]))
+                     : "memory");
+    };
+    const uint32_t early = RAW ? min(NS, nk) : 0u;  // stages whose weights are asked for before the wait
+    if (RAW && tid == 0) {
+        for (uint32_t k = 0; k < early; ++k) issue_weights(k);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     volatile uint32_t *abort_flag = &abort_s;
 
@@ -153,25 +176,16 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                 const uint32_t s = k % NS;
                 if (k >= NS && !wait(&empty[s], ((k / NS) - 1) & 1)) break;
                 uint8_t *dst = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_x[s], MT * A_TILE + (RAW ? NB * 2 * RAW_TILE : 0));
+                if (RAW) {
+                    if (k >= early) issue_weights(k);  // (announces the stage's bytes; the first stages' went out before the wait)
+                } else {
+                    mbar_expect_tx(&full_x[s], MT * A_TILE);
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                                      smem_u32(dst + mt * A_TILE)),
                                  "l"(&tmap_x), "r"((int)((kbeg + k) * BK)), "r"((int)(tok0 + mt * BM)), "r"(smem_u32(&full_x[s]))
-                                 : "memory");
-                }
-                if (RAW) {  // raw weights of the stage: codes at byte 32 k of every row, scales 16 at a time from the area behind the codes
-                    uint8_t *raw = dst + MT * A_TILE + NB * B_TILE;
-                    const CUtensorMap *wm = &wmaps.m[mi];
-                    const uint32_t kk = kbeg + k, sc_x = tiled_scale_off(BRASA_Q4_0, p.cols) + 32 * (kk >> 3);
-                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                                     smem_u32(raw)),
-                                 "l"(wm), "r"((int)(kk * 32)), "r"((int)n0), "r"(smem_u32(&full_x[s]))
-                                 : "memory");
-                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                                     smem_u32(raw + NB * RAW_TILE)),
-                                 "l"(wm), "r"((int)sc_x), "r"((int)n0), "r"(smem_u32(&full_x[s]))
                                  : "memory");
                 }
                 issued = k + 1;
@@ -628,15 +642,26 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         p.part = ctx->gemm_part;
         p.counters = ctx->gemm_counters;
     }
+    // programmatic dependent launch: the kernel's set-up overlaps the end of the kernel before it (see griddepcontrol.wait)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
 #define LAUNCH_TC(MTV, GV, NBV, RAWV)                                                                                                        \
     do {                                                                                                                         \
             BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_kernel<MTV, GV, NBV, RAWV>, ctx->smem_optin - 2048)); \
-        gemm_tc_kernel<MTV, GV, NBV, RAWV><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);                                                         \
+        BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MTV, GV, NBV, RAWV>, tmap, wmaps, p));                                                  \
     } while (0)
     // conversion groups: as many stages in flight as the ring holds, at most four
     if (q6) {
             BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0>, ctx->smem_optin - 2048));
-        gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0><<<grid, 384, smem, ctx->stream>>>(tmap, wmaps, p);
+        BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<1, 4, 1, false, BRASA_Q6_0>, tmap, wmaps, p));
     } else if (nb == 1 && mt == 1) LAUNCH_TC(1, 4, 1, true);
     else if (nb == 1 && mt == 2) LAUNCH_TC(2, 4, 1, false);
     else if (nb == 1) LAUNCH_TC(4, 2, 1, false);

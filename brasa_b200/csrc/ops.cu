@@ -44,6 +44,8 @@ __device__ float block_reduce_max(float v, float *red) {
 // out = x * (1 / sqrt(mean(x^2) + eps)) * w, one block per row
 template <bool HALF_OUT>
 __global__ void rms_norm_kernel(const float *x, const float *w, void *out, uint32_t n, float eps) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (launched as a programmatic dependent: see brasa_launch_dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float red[32];
     const float *xr = x + (size_t)blockIdx.x * n;
     float ss = 0.0f;
@@ -62,6 +64,8 @@ __global__ void rms_norm_kernel(const float *x, const float *w, void *out, uint3
 constexpr int RMS_MAX_CHUNKS = 20;
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(64) rms_norm_rows_kernel(const float *x, const float *w, void *out, uint32_t rows, uint32_t n, float eps) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (launched as a programmatic dependent: see brasa_launch_dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t row = blockIdx.x * 2 + (threadIdx.x >> 5), lane = threadIdx.x & 31, chunks = n / 128;
     if (row >= rows) return;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * n);
@@ -98,6 +102,8 @@ __global__ void __launch_bounds__(64) rms_norm_rows_kernel(const float *x, const
 constexpr int RMS_BLOCK_CHUNKS = 10;
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(128) rms_norm_block_kernel(const float *x, const float *w, void *out, uint32_t n, float eps) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (launched as a programmatic dependent: see brasa_launch_dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float red[4];
     const uint32_t t = threadIdx.x, chunks = n / 512;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)blockIdx.x * n);
@@ -343,13 +349,13 @@ static int32_t rms_norm_common(brasa_cmd *cmd, brasa_arg x, brasa_arg w, brasa_a
     if (rows == 0) return BRASA_OK;
     if (rows >= 256 && n % 128 == 0 && n <= 128 * RMS_MAX_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
         const unsigned blocks = (rows + 1) / 2;
-        if (half_out) rms_norm_rows_kernel<true><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
-        else rms_norm_rows_kernel<false><<<blocks, 64, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps);
+        if (half_out) BRASA_CUDA(ctx, brasa_launch_dependent(ctx, rms_norm_rows_kernel<true>, dim3(blocks), dim3(64), 0, (const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps));
+        else BRASA_CUDA(ctx, brasa_launch_dependent(ctx, rms_norm_rows_kernel<false>, dim3(blocks), dim3(64), 0, (const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), rows, n, eps));
         return brasa_post_launch(cmd, "rms_norm");
     }
     if (rows >= 2 && n % 512 == 0 && n <= 512 * RMS_BLOCK_CHUNKS && x.offset % 16 == 0 && w.offset % 16 == 0 && out.offset % 16 == 0) {
-        if (half_out) rms_norm_block_kernel<true><<<rows, 128, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
-        else rms_norm_block_kernel<false><<<rows, 128, 0, ctx->stream>>>((const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps);
+        if (half_out) BRASA_CUDA(ctx, brasa_launch_dependent(ctx, rms_norm_block_kernel<true>, dim3(rows), dim3(128), 0, (const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps));
+        else BRASA_CUDA(ctx, brasa_launch_dependent(ctx, rms_norm_block_kernel<false>, dim3(rows), dim3(128), 0, (const float *)arg_ptr(x), (const float *)arg_ptr(w), arg_ptr(out), n, eps));
         return brasa_post_launch(cmd, "rms_norm");
     }
     unsigned threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 32);
