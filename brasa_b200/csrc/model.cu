@@ -801,6 +801,45 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
     // itself; per token the host launches one graph and reads one id (pinned memory), nothing else.
     const bool resident = device_pick && decode_fused_ok(m);
     bool primed = false;  // device position and input token are set up
+    // Resident decode keeps the device one step ahead of the host: the step that consumes token t + 1 (which the device
+    // feeds itself) is queued before the host waits for the id of token t + 1, so the GPU never idles while the host
+    // checks stop ids and calls back. A step queued ahead of a token that then ends the generation is harmless: the
+    // position is set again at the next call and the row it wrote lies behind the cached tokens.
+    // The id of a step is read back on a stream of its own (from the step's own place in the device's list of chosen
+    // tokens), so that the copy does not sit between two steps on the compute stream.
+    struct StepEvents {
+        cudaEvent_t ev[2] = {nullptr, nullptr}, done[2] = {nullptr, nullptr};
+        cudaStream_t copy = nullptr;
+        ~StepEvents() {
+            if (copy) {
+                cudaStreamSynchronize(copy);
+                cudaStreamDestroy(copy);
+            }
+            for (cudaEvent_t e : ev)
+                if (e) cudaEventDestroy(e);
+            for (cudaEvent_t e : done)
+                if (e) cudaEventDestroy(e);
+        }
+    } sev;
+    uint32_t steps_launched = 0;  // resident steps queued so far; step i consumes the i-th token of this call and yields the next
+    auto launch_step = [&]() -> int32_t {
+        brasa_cmd step{ctx, nullptr, nullptr, false};
+        BRASA_TRY(decode_step(m, &step, UINT32_MAX));
+        const uint32_t slot = steps_launched & 1;
+        BRASA_CUDA(ctx, cudaEventRecord(sev.done[slot], ctx->stream));
+        BRASA_CUDA(ctx, cudaStreamWaitEvent(sev.copy, sev.done[slot], 0));
+        BRASA_CUDA(ctx, cudaMemcpyAsync(m->pinned_id + slot, (const uint32_t *)m->out_ids->ptr + steps_launched, 4, cudaMemcpyDeviceToHost, sev.copy));
+        BRASA_CUDA(ctx, cudaEventRecord(sev.ev[slot], sev.copy));
+        ++steps_launched;
+        return BRASA_OK;
+    };
+    if (resident) {
+        for (int i = 0; i < 2; ++i) {
+            BRASA_CUDA(ctx, cudaEventCreateWithFlags(&sev.ev[i], cudaEventDisableTiming));
+            BRASA_CUDA(ctx, cudaEventCreateWithFlags(&sev.done[i], cudaEventDisableTiming));
+        }
+        BRASA_CUDA(ctx, cudaStreamCreateWithFlags(&sev.copy, cudaStreamNonBlocking));
+    }
     while (generated < max_new) {
         uint32_t next;
         if (device_pick && !(resident && primed)) {
@@ -814,7 +853,9 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
             BRASA_TRY(rc2);
             next = *m->pinned_id;
         } else if (device_pick) {
-            next = *m->pinned_id;  // read back by the previous step
+            const uint32_t slot = (generated - 1) & 1;  // the step that consumed the token before this one
+            BRASA_CUDA(ctx, cudaEventSynchronize(sev.ev[slot]));
+            next = m->pinned_id[slot];
         } else if (device_sample) {
             brasa_cmd *cmd;
             BRASA_TRY(brasa_cmd_begin(ctx, &cmd));
@@ -853,10 +894,9 @@ int32_t brasa_session_generate(brasa_session *s, const uint32_t *prompt, uint32_
                 BRASA_CUDA(ctx, cudaMemcpyAsync(m->dev_state->ptr, st, 8, cudaMemcpyHostToDevice, ctx->stream));
                 primed = true;
             }
-            brasa_cmd step{ctx, nullptr, nullptr, false};
-            BRASA_TRY(decode_step(m, &step, UINT32_MAX));
-            BRASA_CUDA(ctx, cudaMemcpyAsync(m->pinned_id, m->next_id->ptr, 4, cudaMemcpyDeviceToHost, ctx->stream));
-            BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            while (steps_launched < generated) BRASA_TRY(launch_step());  // this token's step (its cache row, the next id)
+            // one step ahead, if the next token can still be followed by another one
+            if (steps_launched == generated && generated < max_new && s->cached.size() + 2 <= lim.ctx) BRASA_TRY(launch_step());
         } else {
             BRASA_TRY(brasa_model_forward(m, &next, 1, (uint32_t)s->cached.size(), 1, host_logits ? s->logits.data() : nullptr, nullptr));
         }
