@@ -160,3 +160,7 @@ def test_batch_planner_arithmetic_and_largest_batch(B):
     assert n0 == 0
     n_cap, _, _ = B.planner.max_batch(None, shape, B.KvType.F16, 2048, 3600, budget=budget, cap=10)
     assert n_cap == 10
+    # a tensor-parallel shard (an eighth of the lm_head's rows): two more full-width logits buffers for the sampled choice
+    sh = B.planner.plan_batch(shape, 16, 2048 // 16 + 16 * 97, 3600, B.KvType.F16, head_rows=151936 // 8)
+    assert sh["logits"] == bb(16 * (151936 // 8) * 4)
+    assert sh["sampler"] == bb(16 * 2 * 151936 * 4) + 2 * bb(16 * 151936 * 4)
