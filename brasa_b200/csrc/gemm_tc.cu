@@ -191,7 +191,10 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
                 issued = k + 1;
             }
             if (*abort_flag) {  // leaving early: let the copies already in flight land before the CTA exits
-                for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; ++k)
+                // (the first stages' weights went out before the loop: a stage whose X never followed cannot complete its
+                // barrier, and the bounded spin below is then simply the time its weight copies are given to land)
+                const uint32_t last = max(issued, early);
+                for (uint32_t k = last > NS ? last - NS : 0; k < last; ++k)
                     for (uint32_t it = 0; it < TC_WAIT_LIMIT && !mbar_try(&full_x[k % NS], (k / NS) & 1); ++it) {}
             }
         }
