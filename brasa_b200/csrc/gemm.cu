@@ -265,8 +265,10 @@ int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, 
         const brasa_qmatrix ws[2] = {wg, wu};
         return brasa_gemm_tc_launch(cmd, 2, ws, (const __half *)arg_ptr(x_f16), nullptr, tokens, nullptr, (__half *)arg_ptr(out_f16));
     }
-    BRASA_TRY(brasa_k_gemm_with(cmd, wg, x_f16, gate, tokens, BRASA_PREFILL_F16));
-    BRASA_TRY(brasa_k_gemm_with(cmd, wu, x_f16, up, tokens, BRASA_PREFILL_F16));
+    // (few tokens: gate and up in one launch when the tensor-core kernel takes both, so that its runs cover all the SMs)
+    const brasa_qmatrix both[2] = {wg, wu};
+    const brasa_arg outs[2] = {gate, up};
+    BRASA_TRY(brasa_k_gemm_multi(cmd, both, 2, x_f16, outs, tokens, BRASA_PREFILL_F16));
     return brasa_k_swiglu_f16(cmd, gate, up, out_f16, (uint64_t)tokens * wg.rows);
 }
 

@@ -46,6 +46,28 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// the same test without the suspension try_wait may make: what a role does first when the phase is most likely over
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// true in one lane of the (converged) warp: the form under which the compiler keeps the issuing code on the uniform path
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ __half2 u2h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 __device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 // two nibbles (already in the low 4 bits of each half lane) -> f16(d * (q - 8)) for both
@@ -497,6 +519,434 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
     }
 }
 
+// ---- few tokens (a decode step of a batch, a short prompt): the weights are the M operand, the tokens N ----------------
+// With at most 64 tokens a step is nothing but the weight stream, and what decides its rate is how many weight bytes an
+// SM keeps in flight and how cheaply they reach the tensor core. So the kernel is persistent and:
+//   * raw weights travel in chunks of four K stages: one box of 128 rows x 128 code bytes (whole cache lines, 128-byte
+//     swizzle so that the conversion's 16-byte reads of eight rows fall on eight bank groups) and one of 128 rows x 16
+//     scale bytes, into a ring of `raw_slots` chunks (warp 0, one lane) that runs ahead of everything else;
+//   * tcgen05.mma takes the weights as A (M = 128 rows) out of TENSOR memory and X as B (N = 64 tokens) out of shared
+//     memory. A lane of tensor memory is a weight row, so a conversion thread (warps 4-11: warp & 3 picks the 32 rows,
+//     the other bit the quantisation block of the stage) turns the 32 codes of its row into 16 registers of f16 pairs
+//     and stores them with one tcgen05.st: no write of a 16 KB tile to shared memory, no proxy fence. Three chunks
+//     of A (four stages of 32 columns each) and the accumulator (64 columns) live in tensor memory;
+//   * everything behind the raw ring moves a chunk at a time (one wait per role and chunk, one commit): a role's loop is
+//     one lane's chain of dependent instructions, and a stage of 4.6 KB of weights must not cost it hundreds of cycles;
+//   * the ring in shared memory behind the raw one holds only X (64 tokens x 64 halves per stage by TMA: warp 2, one lane);
+//   * the accumulator's lanes are weight rows: the epilogue's stores are 128-byte lines of Y, no turn through shared memory.
+// Work is cut evenly: the launch's (row tile, K stage) pairs, in that order, are split into gridDim.x equal runs. A run
+// that covers a tile's whole K range stores Y; any other writes a partial tile, and the last block to arrive at a tile
+// adds its partial tiles in K order (the sum does not depend on who arrives last) and adds the residual.
+constexpr uint32_t SK_TT = 64, SK_X_TILE = SK_TT * BK * 2;  // 8 KB of X per stage
+constexpr uint32_t SK_NCS = 3, SK_X_CHUNK = 4 * SK_X_TILE;  // ring of three chunks (four stages each): 32 KB of X per slot
+constexpr uint32_t SK_ACOL = 128, SK_TMEM = 512;  // A in tensor memory: 128 columns per chunk slot from column 128; accumulator at column 0
+constexpr uint32_t SK_CODES = BN * 128, SK_RAW = SK_CODES + BN * 16;                     // 16 KB of codes + 2 KB of scales per four stages
+
+struct SkinnyMaps {
+    CUtensorMap codes[3], scales[3];
+};
+
+struct SkinnyParams {
+    float *y[3];
+    uint32_t rows[3];
+    uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
+    uint32_t cols, tokens, stages, raw_slots;
+    uint32_t units;      // row tiles x K stages of the launch
+    uint32_t max_parts;  // most blocks that share one tile
+    uint32_t *status;
+    const float *resid;
+    float *part;         // [tile][max_parts][64 tokens][128 rows]
+    uint32_t *counters;  // arrivals per tile (zero between launches)
+    unsigned long long *trace;  // a developer's build only: phase time stamps
+};
+
+#ifdef BRASA_TRACE_BUILD
+#define SKT(idx) do { if (p.trace && blockIdx.x == 0) p.trace[idx] = (unsigned long long)clock64(); } while (0)
+#define SKG(j) do { if (p.trace) p.trace[512 + blockIdx.x * 4 + (j)] = gtime(); } while (0)
+#else
+#define SKT(idx) do { } while (0)
+#define SKG(j) do { } while (0)
+#endif
+
+// The block whose run holds unit u when `units` units are cut into `blocks` runs [b units / blocks, (b + 1) units / blocks).
+BRASA_HD static inline uint32_t skinny_owner(uint32_t u, uint32_t units, uint32_t blocks) {
+    uint32_t c = (uint32_t)((uint64_t)u * blocks / units);
+    while ((uint32_t)((uint64_t)(c + 1) * units / blocks) <= u) ++c;
+    while ((uint32_t)((uint64_t)c * units / blocks) > u) --c;
+    return c;
+}
+
+__global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ SkinnyMaps maps,
+                                                                SkinnyParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_x[SK_NCS], full_a[SK_NCS], empty[SK_NCS], raw_full[8], raw_empty[8], acc_full, acc_empty;
+    __shared__ uint32_t tmem_base_s, abort_s, last_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t RC = p.raw_slots, nkst = p.cols / BK, cpt = (nkst + 3) / 4, P = gridDim.x;
+    const uint32_t u_beg = (uint32_t)((uint64_t)blockIdx.x * p.units / P), u_end = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.units / P);
+    const uint32_t nu = u_end - u_beg;  // this block's run of (tile, K stage) units
+    auto chunk_of = [&](uint32_t u) { return (u / nkst) * cpt + ((u % nkst) >> 2); };
+    const uint32_t g0 = nu ? chunk_of(u_beg) : 0u, nc = nu ? chunk_of(u_end - 1) - g0 + 1 : 0u;  // its chunks
+    const uint32_t k_beg = nu ? u_beg % nkst : 0u;
+    uint8_t *raw_base = smem + (size_t)SK_NCS * SK_X_CHUNK;
+    auto tile_matrix = [&](uint32_t t) { return (uint32_t)(t >= p.tile_end[0]) + (uint32_t)(t >= p.tile_end[1]); };
+    auto tile_row0 = [&](uint32_t t, uint32_t mi) { return (t - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BN; };
+    // Every role walks the run chunk by chunk with the same three numbers: k, the chunk's first stage in its tile; n, how
+    // many of the chunk's stages belong to the run (the run may begin or end inside a chunk; a tile's end ends one); left,
+    // the stages of the run not yet handed out. No division per chunk: a role's loop is mostly one lane's dependent chain.
+    auto chunk_len = [&](uint32_t k, uint32_t left) { return min(min(4u - (k & 3u), nkst - k), left); };
+
+    if (tid == 0) {
+        SKT(400);
+        SKG(0);
+        for (uint32_t s = 0; s < SK_NCS; ++s) {
+            mbar_init(&full_x[s], 1);
+            mbar_init(&full_a[s], 8);  // one arrival per conversion warp
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t s = 0; s < 8; ++s) {
+            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_empty[s], 8);  // one arrival per conversion warp
+        }
+        mbar_init(&acc_full, 1);
+        mbar_init(&acc_empty, 8);  // one arrival per epilogue warp
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        uint32_t ncols = SK_TMEM;
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    auto issue_chunk = [&](uint32_t ci) {  // codes and scales of the run's chunk ci
+        const uint32_t gch = g0 + ci, t = gch / cpt, kc = gch % cpt, mi = tile_matrix(t), n0 = tile_row0(t, mi), r = ci % RC;
+        uint8_t *dst = raw_base + (size_t)r * SK_RAW;
+        mbar_expect_tx(&raw_full[r], SK_RAW);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+                     "l"(&maps.codes[mi]), "r"((int)(kc * 128)), "r"((int)n0), "r"(smem_u32(&raw_full[r]))
+                     : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         smem_u32(dst + SK_CODES)),
+                     "l"(&maps.scales[mi]), "r"((int)(tiled_scale_off(BRASA_Q4_0, p.cols) + kc * 16)), "r"((int)n0), "r"(smem_u32(&raw_full[r]))
+                     : "memory");
+    };
+    // Launched as a programmatic dependent: the set-up above and the first chunks of weights (weights never change) overlap
+    // the end of the kernel before this one; what that kernel wrote (X, the residual, the workspace) is read after the wait.
+    const uint32_t early = min(RC, nc);
+    if (tid == 0) {
+        for (uint32_t ci = 0; ci < early; ++ci) issue_chunk(ci);
+    }
+    if (tid == 0) SKT(401);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        SKT(402);
+        SKG(1);
+    }
+    const uint32_t tmem_base = tmem_base_s;
+    volatile uint32_t *abort_flag = &abort_s;
+    auto wait = [&](uint64_t *bar, uint32_t parity) -> bool {  // bounded; false when it gave up (or another role did)
+        if (mbar_test(bar, parity)) return true;
+        for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+            if (mbar_try(bar, parity)) return true;
+            if (*abort_flag) return false;
+        }
+        atomicExch(p.status, 4u);
+        *abort_flag = 1;
+        return false;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {  // ---- raw weight chunks ----
+            uint32_t issued = early;
+            for (uint32_t ci = early; ci < nc; ++ci) {
+                if (!wait(&raw_empty[ci % RC], ((ci / RC) - 1) & 1)) break;  // (ci >= RC here: the first RC chunks went out above)
+                issue_chunk(ci);
+                issued = ci + 1;
+            }
+            if (*abort_flag) {  // leaving early: let the copies in flight land before the block exits
+                for (uint32_t ci = issued > RC ? issued - RC : 0; ci < issued; ++ci)
+                    for (uint32_t it = 0; it < TC_WAIT_LIMIT && !mbar_try(&raw_full[ci % RC], (ci / RC) & 1); ++it) {}
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {  // ---- X tiles: the chunk's stages, 64 tokens x 64 halves each, on one barrier ----
+            uint32_t issued = 0, k = k_beg, left = nu, cs = 0, ph = 0;
+            for (uint32_t c = 0; c < nc; ++c) {
+                const uint32_t n = chunk_len(k, left);
+                if (c >= SK_NCS && !wait(&empty[cs], ph ^ 1)) break;
+                if (c < 48) SKT(16 + c * 8 + 0);
+                mbar_expect_tx(&full_x[cs], n * SK_X_TILE);
+                for (uint32_t j = 0; j < n; ++j) {
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                     smem_u32(smem + (size_t)cs * SK_X_CHUNK + (size_t)((k + j) & 3) * SK_X_TILE)),
+                                 "l"(&tmap_x), "r"((int)((k + j) * BK)), "r"(0), "r"(smem_u32(&full_x[cs]))
+                                 : "memory");
+                }
+                issued = c + 1;
+                left -= n;
+                k = k + n == nkst ? 0 : k + n;
+                cs = cs + 1 == SK_NCS ? 0 : cs + 1;
+                ph ^= (cs == 0);
+            }
+            if (*abort_flag) {
+                for (uint32_t c = issued > SK_NCS ? issued - SK_NCS : 0; c < issued; ++c)
+                    for (uint32_t w = 0; w < TC_WAIT_LIMIT && !mbar_try(&full_x[c % SK_NCS], (c / SK_NCS) & 1); ++w) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor core. The whole warp walks the chunks and waits; one lane issues. A chunk costs the issuing lane two
+        // waits, up to sixteen products (operand addresses are constants of the unrolled slots) and one commit. ----
+        // instruction descriptor: D f32, A and B f16, both K-major, M = 128 weight rows, N = 64 tokens
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(SK_TT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+        const uint64_t db_slot0 = smem_desc(smem_u32(smem));
+        uint32_t seg = 0, k = k_beg, left = nu, ph = 0;  // seg: runs of one tile finished so far
+        bool first = true, ok = true;
+        for (uint32_t c0 = 0; c0 < nc && ok; c0 += SK_NCS, ph ^= 1) {
+#pragma unroll
+            for (uint32_t cs = 0; cs < SK_NCS; ++cs) {
+                if (c0 + cs >= nc) break;
+                const uint32_t n = chunk_len(k, left), kq0 = k & 3;
+                const bool last = k + n == nkst || n == left;
+                if (first && seg > 0) ok = wait(&acc_empty, (seg - 1) & 1);  // the epilogue has read the tile before this one
+                ok = ok && wait(&full_x[cs], ph) && wait(&full_a[cs], ph);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (elect_one()) {
+                    if (c0 + cs < 48) SKT(16 + (c0 + cs) * 8 + 2);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        if (j >= kq0 && j < kq0 + n) {
+                            const uint64_t db = db_slot0 + (uint64_t)((cs * SK_X_CHUNK + j * SK_X_TILE) >> 4);
+                            const uint32_t a0 = tmem_base + SK_ACOL + 128 * cs + 32 * j;
+#pragma unroll
+                            for (int ks = 0; ks < BK / 16; ++ks) {  // A: 16 halves of K = 8 columns of tensor memory; B: 32 bytes further along K
+                                const uint32_t acc = (!first || j > kq0 || ks > 0) ? 1u : 0u;
+                                asm volatile(
+                                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                    "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                                    ::"r"(tmem_base), "r"(a0 + ks * 8), "l"(db + (uint64_t)(ks * 2)), "r"(idesc), "r"(acc)
+                                    : "memory");
+                            }
+                        }
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[cs])) : "memory");
+                    if (last) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&acc_full)) : "memory");
+                    if (c0 + cs < 48) SKT(16 + (c0 + cs) * 8 + 3);
+                }
+                __syncwarp();
+                seg += last;
+                first = last;
+                left -= n;
+                k = k + n == nkst ? 0 : k + n;
+            }
+        }
+    } else if (warp >= 4) {
+        // ---- weights, then each finished tile's epilogue. Every chunk is converted by all eight warps: a thread owns one
+        // quantisation block (32 columns) of one weight row, the row its lane of tensor memory stands for, in each stage. ----
+        const uint32_t q = warp & 3, th = (warp - 4) >> 2;  // lane quarter of tensor memory (weight rows 32 q ..); block of the stage, half of the tokens
+        const uint32_t wr = 32 * q + lane, r8 = wr & 7;
+        const uint32_t coff = wr * 128, soff = SK_CODES + wr * 16 + th * 2;  // the row's codes and its scale in a raw chunk
+        const uint32_t a_lane = tmem_base + ((q * 32u) << 16) + SK_ACOL + 16 * th;
+        bool ok = true;
+        uint32_t seg = 0, left = nu, k = k_beg, c = 0, cs = 0, ph = 0, rslot = 0, rph = 0;  // (slots and phases are carried along)
+        uint32_t t = nu ? u_beg / nkst : 0u;
+        while (left > 0) {
+            const uint32_t k0 = k;  // this tile's run: stages [k0, k0 + seg_len)
+            const uint32_t seg_len = min(nkst - k0, left);
+            uint32_t seg_left = seg_len;
+            while (seg_left > 0 && ok) {
+                // the stages of one raw chunk together: their loads, conversions and stores overlap, one wait covers the stores
+                const uint32_t n = chunk_len(k, seg_left), kq0 = k & 3;
+                if (tid == 128 && c < 48) SKT(16 + c * 8 + 4);
+                // (a slot is refilled only after every warp has arrived for its previous use: no parity wait can be a whole phase behind)
+                ok = wait(&raw_full[rslot], rph);
+                if (c >= SK_NCS) ok = ok && wait(&empty[cs], ph ^ 1);
+                if (tid == 128 && c < 48) SKT(16 + c * 8 + 6);
+                ok = __all_sync(0xffffffffu, ok);  // the tensor-memory stores need the whole warp
+                if (!ok) break;
+                const uint8_t *raw = raw_base + (size_t)rslot * SK_RAW;
+                const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6408));  // 1024 + 8
+                uint4 cws[4];  // (all the loads first: a tensor-memory store orders what follows it behind it)
+                unsigned short scs[4];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    cws[j] = *reinterpret_cast<const uint4 *>(raw + coff + (((2 * j + th) ^ r8) << 4));
+                    scs[j] = *reinterpret_cast<const unsigned short *>(raw + soff + j * 4);
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    if (j >= kq0 && j < kq0 + n) {
+                        const uint4 cw = cws[j];
+                        const __half2 d2 = __half2half2(__ushort_as_half(scs[j]));
+                        const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
+                        uint32_t e[16];  // pairs of consecutive columns: elements 0..15 are the low nibbles of bytes 0..15, 16..31 the high nibbles
+#pragma unroll
+                        for (int w4 = 0; w4 < 4; ++w4) {
+                            const uint32_t wv = words[w4] & 0x0F0F0F0Fu, wh = (words[w4] >> 4) & 0x0F0F0F0Fu;
+                            // one byte permutation puts two codes under the 0x64 bytes of two halves: 1024 + q each
+                            e[2 * w4] = h22u(__hmul2(__hsub2(u2h2(__byte_perm(wv, 0x64646464u, 0x4140)), bias), d2));
+                            e[2 * w4 + 1] = h22u(__hmul2(__hsub2(u2h2(__byte_perm(wv, 0x64646464u, 0x4342)), bias), d2));
+                            e[8 + 2 * w4] = h22u(__hmul2(__hsub2(u2h2(__byte_perm(wh, 0x64646464u, 0x4140)), bias), d2));
+                            e[8 + 2 * w4 + 1] = h22u(__hmul2(__hsub2(u2h2(__byte_perm(wh, 0x64646464u, 0x4342)), bias), d2));
+                        }
+                        asm volatile(
+                            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(
+                                a_lane + 128 * cs + 32 * j),
+                            "r"(e[0]), "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]), "r"(e[8]), "r"(e[9]), "r"(e[10]),
+                            "r"(e[11]), "r"(e[12]), "r"(e[13]), "r"(e[14]), "r"(e[15])
+                            : "memory");
+                    }
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full_a[cs]);
+                    mbar_arrive(&raw_empty[rslot]);  // this warp has read what it needs of the chunk
+                }
+                if (tid == 128 && c < 48) SKT(16 + c * 8 + 7);
+                seg_left -= n;
+                k += n;
+                ++c;
+                cs = cs + 1 == SK_NCS ? 0 : cs + 1;
+                ph ^= (cs == 0);
+                rslot = rslot + 1 == RC ? 0 : rslot + 1;
+                rph ^= (rslot == 0);
+            }
+            // ---- this tile's run is converted: read its accumulator (lane = weight row, column = token) ----
+            const uint32_t mi = tile_matrix(t), n0 = tile_row0(t, mi), yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
+            float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
+            const bool whole = k0 == 0 && seg_len == nkst;  // otherwise other blocks hold the rest of this tile's K range
+            if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 0);
+            if (tid == 128 && seg == 0) SKG(2);
+            ok = ok && wait(&acc_full, seg & 1);
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory load needs the whole warp
+            if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 1);
+            uint32_t v[32];
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + 32 * th;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+                    "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                      "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                      "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                      "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty);  // the next tile's products may overwrite the accumulator
+                const uint32_t row = 32 * q + lane;
+                if (whole) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t token = 32 * th + i;
+                        if (token < p.tokens) {
+                            const size_t at = (size_t)token * yrows + n0 + row;
+                            float o = __uint_as_float(v[i]);
+                            if (p.resid) o = p.resid[at] + o;
+                            ymat[at] = o;
+                        }
+                    }
+                } else {
+                    const uint32_t z = blockIdx.x - skinny_owner(t * nkst, p.units, P);
+                    float *ptile = p.part + ((size_t)t * p.max_parts + z) * (SK_TT * BN);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t token = 32 * th + i;
+                        if (token < p.tokens) ptile[token * BN + row] = __uint_as_float(v[i]);
+                    }
+                }
+            }
+            if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 2);
+            if (!whole) {  // (every epilogue warp comes here, whether or not it gave up)
+                const uint32_t first_b = skinny_owner(t * nkst, p.units, P), parts = skinny_owner(t * nkst + nkst - 1, p.units, P) - first_b + 1;
+                __threadfence();
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (tid == 128) last_s = (*abort_flag == 0 && atomicAdd(&p.counters[t], 1u) == parts - 1) ? 1u : 0u;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 3);
+                if (last_s) {
+                    __threadfence();
+                    const float *p0 = p.part + (size_t)t * p.max_parts * (SK_TT * BN);
+                    const uint32_t live = min(SK_TT, p.tokens) * (BN / 4);  // float4s of the tile that hold tokens
+#pragma unroll 1
+                    for (uint32_t i0 = tid - 128; i0 < live; i0 += 4 * 256) {
+                        // four places of the tile per thread and four partial tiles at a time: sixteen loads in flight
+                        float4 a[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t i = i0 + e * 256;
+                            a[e] = i < live ? __ldcg(reinterpret_cast<const float4 *>(p0) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        for (uint32_t z0 = 1; z0 < parts; z0 += 4) {  // always in the order of the K ranges, whoever arrives last
+                            float4 b[4][4];
+#pragma unroll
+                            for (int dz = 0; dz < 4; ++dz) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const uint32_t i = i0 + e * 256;
+                                    b[dz][e] = (z0 + dz < parts && i < live) ? __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(z0 + dz) * (SK_TT * BN)) + i)
+                                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                                }
+                            }
+#pragma unroll
+                            for (int dz = 0; dz < 4; ++dz) {
+                                if (z0 + dz < parts) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        a[e].x += b[dz][e].x; a[e].y += b[dz][e].y; a[e].z += b[dz][e].z; a[e].w += b[dz][e].w;
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t i = i0 + e * 256;
+                            if (i < live) {
+                                const size_t at = (size_t)(i / (BN / 4)) * yrows + n0 + (i % (BN / 4)) * 4;
+                                if (p.resid) {
+                                    const float4 r = *reinterpret_cast<const float4 *>(p.resid + at);
+                                    a[e] = make_float4(r.x + a[e].x, r.y + a[e].y, r.z + a[e].z, r.w + a[e].w);
+                                }
+                                *reinterpret_cast<float4 *>(ymat + at) = a[e];
+                            }
+                        }
+                    }
+                    if (tid == 128) p.counters[t] = 0;
+                    if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 4);
+                }
+            }
+            left -= seg_len;
+            ++seg;
+            ++t;  // (a run goes on only into the next tile, from its first stage)
+            k = 0;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+        SKT(403);
+        SKG(3);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t ncols = SK_TMEM;
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
@@ -509,6 +959,96 @@ EncodeTiledFn encode_tiled() {
         return (EncodeTiledFn)f;
     }();
     return fn;
+}
+
+// The few-token form: see gemm_tc_skinny_kernel. Every matrix is q4_0, tiled, rows a multiple of 128, rows of whole 16 bytes.
+int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens, const float *resid) {
+    brasa_ctx *ctx = cmd->ctx;
+    SkinnyParams p{};
+    SkinnyMaps maps;
+    memset(&maps, 0, sizeof maps);
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < 3; ++i) {
+        if (i < count) {
+            p.y[i] = ys[i];
+            p.rows[i] = ws[i].rows;
+            tiles += ws[i].rows / BN;
+        }
+        p.tile_end[i] = tiles;
+    }
+    const uint32_t cols = ws[0].cols, nkst = cols / BK, units = tiles * nkst;
+    const uint32_t blocks = std::min<uint32_t>((uint32_t)ctx->sm_count, std::max(1u, units / 4));  // a run keeps at least four stages
+    uint32_t max_parts = 1;
+    for (uint32_t t = 0; t < tiles; ++t)
+        max_parts = std::max(max_parts, skinny_owner(t * nkst + nkst - 1, units, blocks) - skinny_owner(t * nkst, units, blocks) + 1);
+    BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0, "gemm: misaligned x");
+    CUtensorMap tmap;
+    {
+        cuuint64_t dims[2] = {cols, tokens}, strides[1] = {(cuuint64_t)cols * 2};
+        cuuint32_t box[2] = {BK, SK_TT}, estr[2] = {1, 1};
+        CUresult cr = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    }
+    const uint32_t rb = tiled_row_bytes(BRASA_Q4_0, cols);
+    for (uint32_t i = 0; i < 3; ++i) {
+        const brasa_qmatrix &wi = ws[i < count ? i : 0];
+        BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(arg_ptr(wi.data)) & 15) == 0, "gemm: misaligned weights");
+        cuuint64_t wdims[2] = {rb, wi.rows}, wstrides[1] = {rb};
+        cuuint32_t cbox[2] = {128, BN}, sbox[2] = {16, BN}, westr[2] = {1, 1};
+        CUresult wr = encode_tiled()(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, arg_ptr(wi.data), wdims, wstrides, cbox, westr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (wr == CUDA_SUCCESS)
+            wr = encode_tiled()(&maps.scales[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, arg_ptr(wi.data), wdims, wstrides, sbox, westr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (wr != CUDA_SUCCESS) return brasa_fail(ctx, BRASA_ECUDA, "cuTensorMapEncodeTiled failed for the weights (%d)", (int)wr);
+    }
+    p.cols = cols;
+    p.tokens = tokens;
+    p.stages = 4 * SK_NCS;
+    p.raw_slots = 7;
+    p.units = units;
+    p.max_parts = max_parts;
+    p.status = ctx->status;
+    p.resid = resid;
+#ifdef BRASA_TRACE_BUILD
+    p.trace = (unsigned long long *)ctx->gemv_trace;
+#endif
+    if (max_parts > 1) {
+        const size_t need = (size_t)tiles * max_parts * SK_TT * BN * sizeof(float);
+        if (ctx->gemm_part_bytes < need) {
+            BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K workspace cannot grow while a graph is recorded");
+            BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (ctx->gemm_part) cudaFree(ctx->gemm_part);
+            ctx->gemm_part = nullptr;
+            ctx->gemm_part_bytes = 0;
+            BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_part, need));
+            ctx->gemm_part_bytes = need;
+        }
+        if (!ctx->gemm_counters) {
+            BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K counters cannot be created while a graph is recorded");
+            BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_counters, GEMM_TC_COUNTERS * 4));
+            BRASA_CUDA(ctx, cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4));
+        }
+        p.part = ctx->gemm_part;
+        p.counters = ctx->gemm_counters;
+    }
+    const size_t smem = (size_t)SK_NCS * SK_X_CHUNK + (size_t)p.raw_slots * SK_RAW + 1024;
+    BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_skinny_kernel, ctx->smem_optin - 2048));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, tmap, maps, p));
+    return brasa_post_launch(cmd, "gemm_tc_skinny");
 }
 
 }  // namespace
@@ -541,6 +1081,10 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         rows256 = rows256 && ws[i].rows % 256 == 0;
         tiles128 += ws[i].rows / BN;
     }
+    // at most 64 tokens of q4_0 matrices: the persistent form whose accumulator rows are weight rows
+    bool few = !glu && tokens <= SK_TT && tiles128 <= GEMM_TC_COUNTERS && tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0;
+    for (uint32_t i = 0; i < count; ++i) few = few && ws[i].qtype == BRASA_Q4_0;
+    if (few) return launch_skinny(cmd, count, ws, x, ys, tokens, resid);
     // Shape of a CTA: MT token tiles of 128 x NB weight tiles of 128 rows (MT x NB x 128 accumulator columns <= 512).
     // Every CTA reads its token tiles' X once per launch, so X crosses L2 -> SM (weight tiles / NB) times: the
     // estimate is the larger of that traffic at about 4.5 TB/s and waves x stages x cycles per stage of one CTA.

@@ -556,6 +556,35 @@ def test_gemm_add_equals_gemm_then_add(B, ctx, K, rows, cols, tokens):
     assert np.array_equal(ga.download(np.float32), gb.download(np.float32))
 
 
+@pytest.mark.parametrize("rows,cols", [((1024, 256, 256), 2560), ((25600,), 256), ((2560,), 9728), ((6400, 6400), 512)])
+def test_gemm_few_tokens_persistent(B, ctx, K, rows, cols):
+    """Up to 64 tokens the tiled q4_0 GEMM is one persistent launch whose blocks take equal runs of (row tile, K stage)
+    pairs: runs that end inside a tile (partial tiles added up by the last block to arrive), runs that hold several whole
+    tiles, one to three matrices per launch, with and without the residual. Same bound as every GEMM; the residual form
+    gives the very bits of GEMM then add; a second launch gives the bits of the first (the sum's order is fixed)."""
+    rng = O.Rng(91)
+    raws = [rng.qmatrix(O.Q4_0, r, cols) for r in rows]
+    ms = [tiled(B, ctx, K, "q4_0", raw, r, cols)[0] for raw, r in zip(raws, rows)]
+    for tokens in (9, 40, 64):
+        x = rng.vec(tokens * cols, 1.0)
+        xh = x.astype(np.float16)
+        gxh = ctx.buffer_from(xh)
+        gys = [ctx.buffer(tokens * r * 4) for r in rows]
+        run(ctx, lambda c: K.gemm_multi(c, ms, gxh, gys, tokens, B.PrefillPrecision.F16))
+        first = [gy.download(np.float32) for gy in gys]
+        for raw, r, got in zip(raws, rows, first):
+            want16, s16 = O.matmul(O.Q4_0, raw, r, cols, x, f16_inputs=True)
+            assert np.max(np.abs(got.reshape(tokens, r) - want16) / s16) <= 1e-5, (tokens, r)
+        run(ctx, lambda c: K.gemm_multi(c, ms, gxh, gys, tokens, B.PrefillPrecision.F16))
+        for gy, got in zip(gys, first):
+            assert np.array_equal(gy.download(np.float32), got)
+        if len(rows) == 1:
+            acc0 = rng.vec(tokens * rows[0], 2.0)
+            ga, gs = ctx.buffer_from(acc0), ctx.buffer(tokens * rows[0] * 4)
+            run(ctx, lambda c: K.gemm_add(c, ms[0], gxh, ga, gs, tokens))
+            assert np.array_equal(ga.download(np.float32), acc0 + first[0])
+
+
 @pytest.mark.parametrize("tokens", [16, 200])
 def test_gemm_tiled_q6_tensor_core(B, ctx, K, tokens):
     """A tiled q6_0 matrix whose rows are a multiple of 128 (the tied lm_head of a batch step) runs on the tcgen05 GEMM:

@@ -312,15 +312,19 @@ def test_plan_equals_allocated_and_rejection_loads_nothing(B, ctx, mid_model):
 @pytest.mark.gpu
 @pytest.mark.parametrize("kv", ["f32", "f16", "q8_0"])
 def test_token_kernel_matches_kernel_per_operation_path(kv, monkeypatch, golden_dir):
-    """The whole-token decode kernel and the kernel-per-operation decode path give the same greedy tokens and
-    logits within the model tolerance of crates/models/tests/forward.rs:40-55, over positions that cross the
-    attention chunk boundaries (32 / 64 keys) and need the per-head merge."""
+    """The whole-token decode kernel and the kernel-per-operation decode path give the same logits within the model
+    tolerance of crates/models/tests/forward.rs:40-55, and the same greedy tokens up to ties within it, over positions
+    that cross the attention chunk boundaries (32 / 64 keys) and need the per-head merge."""
     import brasa_b200 as B
     kvt = {"f32": B.KvType.F32, "f16": B.KvType.F16, "q8_0": B.KvType.Q8_0}[kv]
     tol = {"f32": 1e-4, "f16": 1e-3, "q8_0": 2e-2}[kv]
     prompt = [int(t) for t in np.random.default_rng(5).integers(0, 512, 30)]
     steps = 110
     runs = {}
+    # The two paths round the GEMV input differently for f16 and q8_0 caches (22-bit against 16-bit fixed point), so a
+    # near tie may send their greedy choices apart. The second path is therefore fed the first one's tokens: every
+    # position stays comparable, and where the choices differ the two candidates must be a tie within the tolerance.
+    fed = None
     for mode in ("0", "1"):
         monkeypatch.setenv("BRASA_TOKEN_KERNEL", mode)
         ctx = B.Context(0)
@@ -331,23 +335,19 @@ def test_token_kernel_matches_kernel_per_operation_path(kv, monkeypatch, golden_
         for i in range(steps):
             lg, _ = m.forward([tok], len(prompt) + i)
             logits.append(lg[0].copy())
-            tok = int(np.argmax(lg[0]))
-            toks.append(tok)
+            toks.append(int(np.argmax(lg[0])))
+            tok = toks[-1] if fed is None else fed[i]
+        if fed is None:
+            fed = toks
         m.forward(prompt, 0, want_logits=False)
-        out, _ = m.decode_greedy(toks[0], len(prompt) + 1, 16)
+        out, _ = m.decode_greedy(fed[0], len(prompt) + 1, 16)
         runs[mode] = (np.stack(logits), toks, [int(t) for t in out])
     (la, ta, ra), (lb, tb, rb) = runs["0"], runs["1"]
     scale = np.abs(la).max()
-    # The two paths round the GEMV input differently for f16 and q8_0 caches (22-bit against 16-bit fixed point), so a
-    # near tie may send the greedy sequences apart; from there on they decode different texts. Logits are compared as
-    # long as both paths fed the same tokens, and the parting must be a tie within the tolerance.
-    same = next((i for i, (a, b) in enumerate(zip(ta, tb)) if a != b), len(ta))
-    upto = min(same + 1, len(ta))
-    assert upto >= 20, f"the paths parted after {same} tokens"
-    assert np.abs(la[:upto] - lb[:upto]).max() <= tol * scale
-    if same < len(ta):
-        top2 = np.sort(la[same])[-2:]
-        assert top2[1] - top2[0] <= 2 * tol * scale, f"token {same}: {ta[same]} vs {tb[same]}"
+    assert np.abs(la - lb).max() <= tol * scale
+    for i, (a, b) in enumerate(zip(ta, tb)):
+        if a != b:
+            assert abs(la[i][a] - la[i][b]) <= 2 * tol * scale, f"token {i}: {a} vs {b}"
     assert len(ra) == len(rb) == 16
 
 
