@@ -535,8 +535,9 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_kernel(const __grid_constant__
 //   * the ring in shared memory behind the raw one holds only X (64 tokens x 64 halves per stage by TMA: warp 2, one lane);
 //   * the accumulator's lanes are weight rows: the epilogue's stores are 128-byte lines of Y, no turn through shared memory.
 // Work is cut evenly: the launch's (row tile, K stage) pairs, in that order, are split into gridDim.x equal runs. A run
-// that covers a tile's whole K range stores Y; any other writes a partial tile, and the last block to arrive at a tile
-// adds its partial tiles in K order (the sum does not depend on who arrives last) and adds the residual.
+// that covers a tile's whole K range stores Y; any other writes a partial tile, and a second small kernel, launched as
+// this one's dependent, adds each shared tile's partial tiles in K order and the residual (every SM takes part; one block
+// doing it as the last to arrive took longer than the products themselves).
 constexpr uint32_t SK_TT = 64, SK_X_TILE = SK_TT * BK * 2;  // 8 KB of X per stage
 constexpr uint32_t SK_NCS = 3, SK_X_CHUNK = 4 * SK_X_TILE;  // ring of three chunks (four stages each): 32 KB of X per slot
 constexpr uint32_t SK_ACOL = 128, SK_TMEM = 512;  // A in tensor memory: 128 columns per chunk slot from column 128; accumulator at column 0
@@ -555,8 +556,7 @@ struct SkinnyParams {
     uint32_t max_parts;  // most blocks that share one tile
     uint32_t *status;
     const float *resid;
-    float *part;         // [tile][max_parts][64 tokens][128 rows]
-    uint32_t *counters;  // arrivals per tile (zero between launches)
+    float *part;         // [tile][max_parts][64 tokens][128 rows]: what the blocks that share a tile leave for the kernel below
     unsigned long long *trace;  // a developer's build only: phase time stamps
 };
 
@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_x[SK_NCS], full_a[SK_NCS], empty[SK_NCS], raw_full[8], raw_empty[8], acc_full, acc_empty;
-    __shared__ uint32_t tmem_base_s, abort_s, last_s;
+    __shared__ uint32_t tmem_base_s, abort_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t RC = p.raw_slots, nkst = p.cols / BK, cpt = (nkst + 3) / 4, P = gridDim.x;
@@ -870,64 +870,6 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
                 }
             }
             if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 2);
-            if (!whole) {  // (every epilogue warp comes here, whether or not it gave up)
-                const uint32_t first_b = skinny_owner(t * nkst, p.units, P), parts = skinny_owner(t * nkst + nkst - 1, p.units, P) - first_b + 1;
-                __threadfence();
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (tid == 128) last_s = (*abort_flag == 0 && atomicAdd(&p.counters[t], 1u) == parts - 1) ? 1u : 0u;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 3);
-                if (last_s) {
-                    __threadfence();
-                    const float *p0 = p.part + (size_t)t * p.max_parts * (SK_TT * BN);
-                    const uint32_t live = min(SK_TT, p.tokens) * (BN / 4);  // float4s of the tile that hold tokens
-#pragma unroll 1
-                    for (uint32_t i0 = tid - 128; i0 < live; i0 += 4 * 256) {
-                        // four places of the tile per thread and four partial tiles at a time: sixteen loads in flight
-                        float4 a[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t i = i0 + e * 256;
-                            a[e] = i < live ? __ldcg(reinterpret_cast<const float4 *>(p0) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                        for (uint32_t z0 = 1; z0 < parts; z0 += 4) {  // always in the order of the K ranges, whoever arrives last
-                            float4 b[4][4];
-#pragma unroll
-                            for (int dz = 0; dz < 4; ++dz) {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const uint32_t i = i0 + e * 256;
-                                    b[dz][e] = (z0 + dz < parts && i < live) ? __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(z0 + dz) * (SK_TT * BN)) + i)
-                                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-                                }
-                            }
-#pragma unroll
-                            for (int dz = 0; dz < 4; ++dz) {
-                                if (z0 + dz < parts) {
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        a[e].x += b[dz][e].x; a[e].y += b[dz][e].y; a[e].z += b[dz][e].z; a[e].w += b[dz][e].w;
-                                    }
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t i = i0 + e * 256;
-                            if (i < live) {
-                                const size_t at = (size_t)(i / (BN / 4)) * yrows + n0 + (i % (BN / 4)) * 4;
-                                if (p.resid) {
-                                    const float4 r = *reinterpret_cast<const float4 *>(p.resid + at);
-                                    a[e] = make_float4(r.x + a[e].x, r.y + a[e].y, r.z + a[e].z, r.w + a[e].w);
-                                }
-                                *reinterpret_cast<float4 *>(ymat + at) = a[e];
-                            }
-                        }
-                    }
-                    if (tid == 128) p.counters[t] = 0;
-                    if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 4);
-                }
-            }
             left -= seg_len;
             ++seg;
             ++t;  // (a run goes on only into the next tile, from its first stage)
@@ -944,6 +886,43 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         uint32_t ncols = SK_TMEM;
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+    }
+}
+
+// Y = resid + the partial tiles in K order, for every tile that more than one block of the kernel above worked on.
+// Launched as its dependent: its blocks sit beside the GEMM's and start the moment the last partial tile is out, and
+// every SM takes part (one float4 of Y per thread, all of its partial tiles' loads in flight at once).
+__global__ void __launch_bounds__(256) gemm_tc_skinny_sum_kernel(SkinnyParams p, uint32_t blocks) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t t = blockIdx.x, nkst = p.cols / BK;
+    const uint32_t first_b = skinny_owner(t * nkst, p.units, blocks), parts = skinny_owner(t * nkst + nkst - 1, p.units, blocks) - first_b + 1;
+    if (parts == 1) return;  // one block held the tile's whole K range and stored Y itself
+    const uint32_t mi = (uint32_t)(t >= p.tile_end[0]) + (uint32_t)(t >= p.tile_end[1]);
+    const uint32_t n0 = (t - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BN, yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
+    float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
+    const float *p0 = p.part + (size_t)t * p.max_parts * (SK_TT * BN);
+    const uint32_t live = min(SK_TT, p.tokens) * (BN / 4);  // float4s of the tile that hold tokens
+    for (uint32_t i = blockIdx.y * 256 + threadIdx.x; i < live; i += gridDim.y * 256) {
+        float4 a = __ldcg(reinterpret_cast<const float4 *>(p0) + i);
+        for (uint32_t z0 = 1; z0 < parts; z0 += 8) {  // always in the order of the K ranges
+            float4 b[8];
+#pragma unroll
+            for (int dz = 0; dz < 8; ++dz)
+                b[dz] = z0 + dz < parts ? __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(z0 + dz) * (SK_TT * BN)) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int dz = 0; dz < 8; ++dz) {
+                if (z0 + dz < parts) {
+                    a.x += b[dz].x; a.y += b[dz].y; a.z += b[dz].z; a.w += b[dz].w;
+                }
+            }
+        }
+        const size_t at = (size_t)(i / (BN / 4)) * yrows + n0 + (i % (BN / 4)) * 4;
+        if (p.resid) {
+            const float4 r = *reinterpret_cast<const float4 *>(p.resid + at);
+            a = make_float4(r.x + a.x, r.y + a.y, r.z + a.z, r.w + a.w);
+        }
+        *reinterpret_cast<float4 *>(ymat + at) = a;
     }
 }
 
@@ -1027,13 +1006,7 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
             BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_part, need));
             ctx->gemm_part_bytes = need;
         }
-        if (!ctx->gemm_counters) {
-            BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K counters cannot be created while a graph is recorded");
-            BRASA_CUDA(ctx, cudaMalloc((void **)&ctx->gemm_counters, GEMM_TC_COUNTERS * 4));
-            BRASA_CUDA(ctx, cudaMemset(ctx->gemm_counters, 0, GEMM_TC_COUNTERS * 4));
-        }
         p.part = ctx->gemm_part;
-        p.counters = ctx->gemm_counters;
     }
     const size_t smem = (size_t)SK_NCS * SK_X_CHUNK + (size_t)p.raw_slots * SK_RAW + 1024;
     BRASA_TRY(brasa_smem_optin(ctx, (const void *)gemm_tc_skinny_kernel, ctx->smem_optin - 2048));
@@ -1048,7 +1021,10 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, tmap, maps, p));
-    return brasa_post_launch(cmd, "gemm_tc_skinny");
+    BRASA_TRY(brasa_post_launch(cmd, "gemm_tc_skinny"));
+    if (max_parts == 1) return BRASA_OK;
+    BRASA_CUDA(ctx, brasa_launch_dependent(ctx, gemm_tc_skinny_sum_kernel, dim3(tiles, 8), dim3(256), 0, p, blocks));
+    return brasa_post_launch(cmd, "gemm_tc_skinny_sum");
 }
 
 }  // namespace
@@ -1082,7 +1058,7 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         tiles128 += ws[i].rows / BN;
     }
     // at most 64 tokens of q4_0 matrices: the persistent form whose accumulator rows are weight rows
-    bool few = !glu && tokens <= SK_TT && tiles128 <= GEMM_TC_COUNTERS && tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0;
+    bool few = !glu && tokens <= SK_TT && tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0;
     for (uint32_t i = 0; i < count; ++i) few = few && ws[i].qtype == BRASA_Q4_0;
     if (few) return launch_skinny(cmd, count, ws, x, ys, tokens, resid);
     // Shape of a CTA: MT token tiles of 128 x NB weight tiles of 128 rows (MT x NB x 128 accumulator columns <= 512).
