@@ -10,6 +10,7 @@
 #include "brasa_internal.h"
 
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
+bool brasa_gemm_tc_few_tokens(brasa_ctx *ctx, const brasa_qmatrix *ws, uint32_t count, uint32_t tokens);
 int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
                              const float *resid, __half *glu);
 
@@ -267,6 +268,10 @@ int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, 
     }
     // (few tokens: gate and up in one launch when the tensor-core kernel takes both, so that its runs cover all the SMs)
     const brasa_qmatrix both[2] = {wg, wu};
+    if (tc_enabled() && tokens > 8 && qm_fits(wg) && qm_fits(wu) && brasa_gemm_tc_few_tokens(cmd->ctx, both, 2, tokens) &&
+        arg_fits(x_f16, (uint64_t)tokens * wg.cols * 2) && arg_fits(out_f16, (uint64_t)tokens * wg.rows * 2) && x_f16.offset % 16 == 0 &&
+        out_f16.offset % 16 == 0)  // its SwiGLU is formed by the kernel that adds up the blocks' partial tiles (the output may be X itself)
+        return brasa_gemm_tc_launch(cmd, 2, both, (const __half *)arg_ptr(x_f16), nullptr, tokens, nullptr, (__half *)arg_ptr(out_f16));
     const brasa_arg outs[2] = {gate, up};
     BRASA_TRY(brasa_k_gemm_multi(cmd, both, 2, x_f16, outs, tokens, BRASA_PREFILL_F16));
     return brasa_k_swiglu_f16(cmd, gate, up, out_f16, (uint64_t)tokens * wg.rows);

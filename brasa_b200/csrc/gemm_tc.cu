@@ -557,6 +557,7 @@ struct SkinnyParams {
     uint32_t *status;
     const float *resid;
     float *part;         // [tile][max_parts][64 tokens][128 rows]: what the blocks that share a tile leave for the kernel below
+    __half *glu;         // when set (two matrices, gate then up): every tile goes to `part` and the kernel below writes f16(silu(gate) * up) here
     unsigned long long *trace;  // a developer's build only: phase time stamps
 };
 
@@ -569,10 +570,11 @@ struct SkinnyParams {
 #endif
 
 // The block whose run holds unit u when `units` units are cut into `blocks` runs [b units / blocks, (b + 1) units / blocks).
+// (units x blocks stays below 2^32: the launcher sees to it, and the kernels divide 32-bit numbers)
 BRASA_HD static inline uint32_t skinny_owner(uint32_t u, uint32_t units, uint32_t blocks) {
-    uint32_t c = (uint32_t)((uint64_t)u * blocks / units);
-    while ((uint32_t)((uint64_t)(c + 1) * units / blocks) <= u) ++c;
-    while ((uint32_t)((uint64_t)c * units / blocks) > u) --c;
+    uint32_t c = u * blocks / units;
+    while ((c + 1) * units / blocks <= u) ++c;
+    while (c * units / blocks > u) --c;
     return c;
 }
 
@@ -585,7 +587,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t RC = p.raw_slots, nkst = p.cols / BK, cpt = (nkst + 3) / 4, P = gridDim.x;
-    const uint32_t u_beg = (uint32_t)((uint64_t)blockIdx.x * p.units / P), u_end = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.units / P);
+    const uint32_t u_beg = blockIdx.x * p.units / P, u_end = (blockIdx.x + 1) * p.units / P;  // (units x blocks < 2^32)
     const uint32_t nu = u_end - u_beg;  // this block's run of (tile, K stage) units
     auto chunk_of = [&](uint32_t u) { return (u / nkst) * cpt + ((u % nkst) >> 2); };
     const uint32_t g0 = nu ? chunk_of(u_beg) : 0u, nc = nu ? chunk_of(u_end - 1) - g0 + 1 : 0u;  // its chunks
@@ -824,7 +826,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
             // ---- this tile's run is converted: read its accumulator (lane = weight row, column = token) ----
             const uint32_t mi = tile_matrix(t), n0 = tile_row0(t, mi), yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
             float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
-            const bool whole = k0 == 0 && seg_len == nkst;  // otherwise other blocks hold the rest of this tile's K range
+            const bool whole = k0 == 0 && seg_len == nkst && !p.glu;  // otherwise other blocks hold the rest of this tile's K range (or gate meets up below)
             if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 0);
             if (tid == 128 && seg == 0) SKG(2);
             ok = ok && wait(&acc_full, seg & 1);
@@ -860,7 +862,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
                         }
                     }
                 } else {
-                    const uint32_t z = blockIdx.x - skinny_owner(t * nkst, p.units, P);
+                    const uint32_t z = k0 == 0 ? 0u : blockIdx.x - skinny_owner(t * nkst, p.units, P);  // (a tile begun here is this block's from its first stage)
                     float *ptile = p.part + ((size_t)t * p.max_parts + z) * (SK_TT * BN);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
@@ -892,31 +894,48 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
 // Y = resid + the partial tiles in K order, for every tile that more than one block of the kernel above worked on.
 // Launched as its dependent: its blocks sit beside the GEMM's and start the moment the last partial tile is out, and
 // every SM takes part (one float4 of Y per thread, all of its partial tiles' loads in flight at once).
+__device__ __forceinline__ float4 skinny_tile_sum(const SkinnyParams &p, uint32_t t, uint32_t parts, uint32_t i) {
+    const float *p0 = p.part + (size_t)t * p.max_parts * (SK_TT * BN);
+    float4 a = __ldcg(reinterpret_cast<const float4 *>(p0) + i);
+    for (uint32_t z0 = 1; z0 < parts; z0 += 8) {  // always in the order of the K ranges
+        float4 b[8];
+#pragma unroll
+        for (int dz = 0; dz < 8; ++dz)
+            b[dz] = z0 + dz < parts ? __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(z0 + dz) * (SK_TT * BN)) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int dz = 0; dz < 8; ++dz) {
+            if (z0 + dz < parts) {
+                a.x += b[dz].x; a.y += b[dz].y; a.z += b[dz].z; a.w += b[dz].w;
+            }
+        }
+    }
+    return a;
+}
+
 __global__ void __launch_bounds__(256) gemm_tc_skinny_sum_kernel(SkinnyParams p, uint32_t blocks) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t t = blockIdx.x, nkst = p.cols / BK;
-    const uint32_t first_b = skinny_owner(t * nkst, p.units, blocks), parts = skinny_owner(t * nkst + nkst - 1, p.units, blocks) - first_b + 1;
+    const uint32_t parts = skinny_owner(t * nkst + nkst - 1, p.units, blocks) - skinny_owner(t * nkst, p.units, blocks) + 1;
+    const uint32_t live = min(SK_TT, p.tokens) * (BN / 4);  // float4s of the tile that hold tokens
+    if (p.glu) {  // tile t of gate and tile t of up: out = f16(silu(gate) * up), four rows of a token per thread
+        const uint32_t tu = t + p.tile_end[0];
+        const uint32_t parts_u = skinny_owner(tu * nkst + nkst - 1, p.units, blocks) - skinny_owner(tu * nkst, p.units, blocks) + 1;
+        for (uint32_t i = blockIdx.y * 256 + threadIdx.x; i < live; i += gridDim.y * 256) {
+            const float4 g = skinny_tile_sum(p, t, parts, i), u = skinny_tile_sum(p, tu, parts_u, i);
+            const __half2 lo = __floats2half2_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+            const __half2 hi = __floats2half2_rn((g.z / (1.0f + expf(-g.z))) * u.z, (g.w / (1.0f + expf(-g.w))) * u.w);
+            const size_t at = (size_t)(i / (BN / 4)) * p.rows[0] + t * BN + (i % (BN / 4)) * 4;
+            *reinterpret_cast<uint2 *>(p.glu + at) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+        }
+        return;
+    }
     if (parts == 1) return;  // one block held the tile's whole K range and stored Y itself
     const uint32_t mi = (uint32_t)(t >= p.tile_end[0]) + (uint32_t)(t >= p.tile_end[1]);
     const uint32_t n0 = (t - (mi == 0 ? 0u : (mi == 1 ? p.tile_end[0] : p.tile_end[1]))) * BN, yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
     float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
-    const float *p0 = p.part + (size_t)t * p.max_parts * (SK_TT * BN);
-    const uint32_t live = min(SK_TT, p.tokens) * (BN / 4);  // float4s of the tile that hold tokens
     for (uint32_t i = blockIdx.y * 256 + threadIdx.x; i < live; i += gridDim.y * 256) {
-        float4 a = __ldcg(reinterpret_cast<const float4 *>(p0) + i);
-        for (uint32_t z0 = 1; z0 < parts; z0 += 8) {  // always in the order of the K ranges
-            float4 b[8];
-#pragma unroll
-            for (int dz = 0; dz < 8; ++dz)
-                b[dz] = z0 + dz < parts ? __ldcg(reinterpret_cast<const float4 *>(p0 + (size_t)(z0 + dz) * (SK_TT * BN)) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int dz = 0; dz < 8; ++dz) {
-                if (z0 + dz < parts) {
-                    a.x += b[dz].x; a.y += b[dz].y; a.z += b[dz].z; a.w += b[dz].w;
-                }
-            }
-        }
+        float4 a = skinny_tile_sum(p, t, parts, i);
         const size_t at = (size_t)(i / (BN / 4)) * yrows + n0 + (i % (BN / 4)) * 4;
         if (p.resid) {
             const float4 r = *reinterpret_cast<const float4 *>(p.resid + at);
@@ -941,7 +960,8 @@ EncodeTiledFn encode_tiled() {
 }
 
 // The few-token form: see gemm_tc_skinny_kernel. Every matrix is q4_0, tiled, rows a multiple of 128, rows of whole 16 bytes.
-int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens, const float *resid) {
+int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens, const float *resid,
+                      __half *glu) {
     brasa_ctx *ctx = cmd->ctx;
     SkinnyParams p{};
     SkinnyMaps maps;
@@ -949,7 +969,7 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     uint32_t tiles = 0;
     for (uint32_t i = 0; i < 3; ++i) {
         if (i < count) {
-            p.y[i] = ys[i];
+            p.y[i] = ys ? ys[i] : nullptr;
             p.rows[i] = ws[i].rows;
             tiles += ws[i].rows / BN;
         }
@@ -992,10 +1012,11 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     p.max_parts = max_parts;
     p.status = ctx->status;
     p.resid = resid;
+    p.glu = glu;
 #ifdef BRASA_TRACE_BUILD
     p.trace = (unsigned long long *)ctx->gemv_trace;
 #endif
-    if (max_parts > 1) {
+    if (max_parts > 1 || glu) {
         const size_t need = (size_t)tiles * max_parts * SK_TT * BN * sizeof(float);
         if (ctx->gemm_part_bytes < need) {
             BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K workspace cannot grow while a graph is recorded");
@@ -1022,8 +1043,8 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     cfg.numAttrs = 1;
     BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, tmap, maps, p));
     BRASA_TRY(brasa_post_launch(cmd, "gemm_tc_skinny"));
-    if (max_parts == 1) return BRASA_OK;
-    BRASA_CUDA(ctx, brasa_launch_dependent(ctx, gemm_tc_skinny_sum_kernel, dim3(tiles, 8), dim3(256), 0, p, blocks));
+    if (max_parts == 1 && !glu) return BRASA_OK;
+    BRASA_CUDA(ctx, brasa_launch_dependent(ctx, gemm_tc_skinny_sum_kernel, dim3(glu ? tiles / 2 : tiles, 8), dim3(256), 0, p, blocks));
     return brasa_post_launch(cmd, "gemm_tc_skinny_sum");
 }
 
@@ -1033,6 +1054,18 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {
     return (w.qtype == BRASA_Q4_0 || w.qtype == BRASA_Q6_0) && w.layout == BRASA_LAYOUT_TILED && w.rows % BN == 0 && w.cols % BK == 0 && w.cols >= BK && tokens > 0 &&
            encode_tiled() != nullptr;
+}
+
+// True when brasa_gemm_tc_launch takes these matrices with the few-token kernel (whose fused SwiGLU may write over X: its
+// output is stored by a kernel that starts after every product has been formed).
+bool brasa_gemm_tc_few_tokens(brasa_ctx *ctx, const brasa_qmatrix *ws, uint32_t count, uint32_t tokens) {
+    if (tokens == 0 || tokens > SK_TT || count < 1 || count > 3) return false;
+    uint64_t tiles = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (!brasa_gemm_tc_supported(ws[i], tokens) || ws[i].qtype != BRASA_Q4_0 || ws[i].cols != ws[0].cols) return false;
+        tiles += ws[i].rows / BN;
+    }
+    return tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0 && tiles * (ws[0].cols / BK) * (uint64_t)(ctx->sm_count + 1) < (1ull << 32);
 }
 
 // Y_i = W_i X for 1 to 3 matrices that share X (f16, [tokens][cols]); every W_i must pass brasa_gemm_tc_supported.
@@ -1058,9 +1091,10 @@ int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix
         tiles128 += ws[i].rows / BN;
     }
     // at most 64 tokens of q4_0 matrices: the persistent form whose accumulator rows are weight rows
-    bool few = !glu && tokens <= SK_TT && tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0;
+    bool few = tokens <= SK_TT && tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0 &&
+               (uint64_t)tiles128 * (ws[0].cols / BK) * (uint64_t)(ctx->sm_count + 1) < (1ull << 32);
     for (uint32_t i = 0; i < count; ++i) few = few && ws[i].qtype == BRASA_Q4_0;
-    if (few) return launch_skinny(cmd, count, ws, x, ys, tokens, resid);
+    if (few) return launch_skinny(cmd, count, ws, x, ys, tokens, resid, glu);
     // Shape of a CTA: MT token tiles of 128 x NB weight tiles of 128 rows (MT x NB x 128 accumulator columns <= 512).
     // Every CTA reads its token tiles' X once per launch, so X crosses L2 -> SM (weight tiles / NB) times: the
     // estimate is the larger of that traffic at about 4.5 TB/s and waves x stages x cycles per stage of one CTA.

@@ -515,10 +515,11 @@ def test_gemm_f16_and_f32(B, ctx, K, rows, cols):
             break  # one token count is enough for the large shapes
 
 
-@pytest.mark.parametrize("tokens", [70, 300])
+@pytest.mark.parametrize("tokens", [40, 70, 300])
 def test_gemm_swiglu_equals_unfused(B, ctx, K, tokens):
-    """From 128 tokens on gate and up run as one tensor-core launch whose epilogue forms silu(gate) * up; below, as two
-    GEMMs and the element-wise kernel. Both must give the bits of the unfused sequence."""
+    """From 128 tokens on gate and up run as one tensor-core launch whose epilogue forms silu(gate) * up; up to 64 tokens
+    as one few-token launch whose partial-tile sum forms it; in between, as two GEMMs and the element-wise kernel. All
+    must give the bits of the unfused sequence."""
     rng = O.Rng(19)
     rows, cols = 1024, 512
     graw, uraw = rng.qmatrix(O.Q4_0, rows, cols), rng.qmatrix(O.Q4_0, rows, cols)
