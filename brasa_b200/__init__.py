@@ -505,6 +505,11 @@ class Kernels:
         """acc += W x (f16 inputs): the residual add folded into the GEMM."""
         self._k(self.L.brasa_k_gemm_add(cmd._h, w._c(), _arg(x), _arg(acc), _arg(scratch), C.c_uint32(tokens)))
 
+    def gemm_add_rms_norm_f16(self, cmd, w: QMatrix, x, acc, scratch, norm_w, out, tokens, eps):
+        """acc += W x, then out = f16(rms_norm(acc) * norm_w)."""
+        self._k(self.L.brasa_k_gemm_add_rms_norm_f16(cmd._h, w._c(), _arg(x), _arg(acc), _arg(scratch), _arg(norm_w), _arg(out), C.c_uint32(tokens),
+                                                     C.c_float(eps)))
+
     def gemm_with(self, cmd, w: QMatrix, x, y, tokens, precision):
         self._k(self.L.brasa_k_gemm_with(cmd._h, w._c(), _arg(x), _arg(y), C.c_uint32(tokens), C.c_int32(int(precision))))
 

@@ -587,7 +587,8 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         Layer &l = m->layers[li];
         brasa_arg xin;
         if (half_io) {
-            BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.attn_norm), A(m->xh), n, H, c.eps));
+            // (after the first layer the norm was formed behind the down projection of the layer before: see below)
+            if (li == 0 || m->tp) BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.attn_norm), A(m->xh), n, H, c.eps));
             xin = A(m->xh);
         } else {
             BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(l.attn_norm), A(m->norm_out), n, H, c.eps));
@@ -651,14 +652,16 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
         if (half_io) BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_reduce_paged_kernel<true>, rgrid, dim3(128), 0, F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks));
         else BRASA_CUDA(ctx, brasa_launch_dependent(ctx, decode_reduce_paged_kernel<false>, rgrid, dim3(128), 0, F(b->partials), lens, attn_out, c.heads, (uint32_t)b->max_chunks));
         BRASA_TRY(brasa_post_launch(cmd, "decode_reduce_paged"));
-        if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.wo.q, A(m->xh), A(m->x), A(m->h), n));
+        // x += Wo attn and the norm of the feed-forward block: one call (one GEMM and one kernel behind it when the few-token
+        // kernel takes the product)
+        if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add_rms_norm_f16(cmd, l.wo.q, A(m->xh), A(m->x), A(m->h), A(l.ffn_norm), A(m->xh), n, c.eps));
         else {
             BRASA_TRY(mm(l.wo, half_io ? A(m->xh) : A(m->attn), A(m->h)));
             BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
         }
         brasa_arg act;
         if (half_io) {
-            BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
+            if (m->tp) BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(l.ffn_norm), A(m->xh), n, H, c.eps));
             act = brasa_gemm_swiglu_fuses(l.gate.q, l.up.q, n) ? A(m->up) : A(m->xh);
             BRASA_TRY(brasa_k_gemm_swiglu(cmd, l.gate.q, l.up.q, A(m->xh), A(m->gate), A(m->up), act, n));
         } else {
@@ -668,14 +671,17 @@ int32_t encode_step(brasa_batch *b, brasa_cmd *cmd, uint32_t n) {
             BRASA_TRY(brasa_k_swiglu(cmd, A(m->gate), A(m->up), A(m->gate), (uint64_t)n * c.ffn));
             act = A(m->gate);
         }
-        if (half_io && !m->tp) BRASA_TRY(brasa_k_gemm_add(cmd, l.down.q, act, A(m->x), A(m->h), n));
+        // x += Wdown act and the norm that opens the next layer (the final norm after the last one)
+        if (half_io && !m->tp)
+            BRASA_TRY(brasa_k_gemm_add_rms_norm_f16(cmd, l.down.q, act, A(m->x), A(m->h), li + 1 < c.layers ? A(m->layers[li + 1].attn_norm) : A(m->final_norm),
+                                                  A(m->xh), n, c.eps));
         else {
             BRASA_TRY(mm(l.down, act, A(m->h)));
             BRASA_TRY(batch_residual_add(m, cmd, (uint64_t)n * H));
         }
     }
     if (half_io) {
-        BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(m->final_norm), A(m->xh), n, H, c.eps));
+        if (m->tp) BRASA_TRY(brasa_k_rms_norm_f16(cmd, A(m->x), A(m->final_norm), A(m->xh), n, H, c.eps));
         return brasa_k_gemm_with(cmd, m->head.q, A(m->xh), A(b->logits), n, BRASA_PREFILL_F16);
     }
     BRASA_TRY(brasa_k_rms_norm(cmd, A(m->x), A(m->final_norm), A(m->norm_out), n, H, c.eps));

@@ -11,6 +11,8 @@
 
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens);
 bool brasa_gemm_tc_few_tokens(brasa_ctx *ctx, const brasa_qmatrix *ws, uint32_t count, uint32_t tokens);
+int32_t brasa_gemm_tc_add_norm(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *acc, const float *norm_w, __half *out, uint32_t tokens,
+                               float eps);
 int32_t brasa_gemm_tc_launch(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens,
                              const float *resid, __half *glu);
 
@@ -226,6 +228,22 @@ int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa
     }
     BRASA_TRY(brasa_k_gemm_with(cmd, w, x_f16, scratch, tokens, BRASA_PREFILL_F16));
     return brasa_k_add(cmd, acc, scratch, acc, n);
+}
+
+// acc += W x, then out = f16(rms_norm(acc) * norm_w): the residual add of a layer and the norm that opens the next block.
+// One GEMM and one kernel behind it when the few-token tensor-core kernel takes the product; otherwise the two calls.
+int32_t brasa_k_gemm_add_rms_norm_f16(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, brasa_arg norm_w, brasa_arg out_f16,
+                                    uint32_t tokens, float eps) {
+    if (!cmd) return BRASA_EINVAL;
+    brasa_ctx *ctx = cmd->ctx;
+    const uint64_t n = (uint64_t)tokens * w.rows;
+    if (tc_enabled() && tokens >= 2 && tokens > 8 && qm_fits(w) && brasa_gemm_tc_few_tokens(ctx, &w, 1, tokens) && w.rows % 512 == 0 && w.rows <= 5120 &&
+        arg_fits(x_f16, (uint64_t)tokens * w.cols * 2) && arg_fits(acc, n * 4) && arg_fits(out_f16, n * 2) && arg_fits(norm_w, (uint64_t)w.rows * 4) &&
+        x_f16.offset % 16 == 0 && acc.offset % 16 == 0 && out_f16.offset % 16 == 0 && norm_w.offset % 16 == 0)
+        return brasa_gemm_tc_add_norm(cmd, w, (const __half *)arg_ptr(x_f16), (float *)arg_ptr(acc), (const float *)arg_ptr(norm_w),
+                                      (__half *)arg_ptr(out_f16), tokens, eps);
+    BRASA_TRY(brasa_k_gemm_add(cmd, w, x_f16, acc, scratch, tokens));
+    return brasa_k_rms_norm_f16(cmd, acc, norm_w, out_f16, tokens, w.rows, eps);
 }
 
 int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg y, uint32_t tokens) {

@@ -558,6 +558,7 @@ struct SkinnyParams {
     const float *resid;
     float *part;         // [tile][max_parts][64 tokens][128 rows]: what the blocks that share a tile leave for the kernel below
     __half *glu;         // when set (two matrices, gate then up): every tile goes to `part` and the kernel below writes f16(silu(gate) * up) here
+    uint32_t defer;      // every tile goes to `part`: the kernel that follows forms Y (and more) from the partial tiles
     unsigned long long *trace;  // a developer's build only: phase time stamps
 };
 
@@ -826,7 +827,7 @@ __global__ void __launch_bounds__(384, 1) gemm_tc_skinny_kernel(const __grid_con
             // ---- this tile's run is converted: read its accumulator (lane = weight row, column = token) ----
             const uint32_t mi = tile_matrix(t), n0 = tile_row0(t, mi), yrows = mi == 0 ? p.rows[0] : (mi == 1 ? p.rows[1] : p.rows[2]);
             float *ymat = mi == 0 ? p.y[0] : (mi == 1 ? p.y[1] : p.y[2]);
-            const bool whole = k0 == 0 && seg_len == nkst && !p.glu;  // otherwise other blocks hold the rest of this tile's K range (or gate meets up below)
+            const bool whole = k0 == 0 && seg_len == nkst && !p.defer;  // otherwise other blocks hold the rest of this tile's K range (or gate meets up below)
             if (tid == 128 && seg < 4) SKT(410 + seg * 8 + 0);
             if (tid == 128 && seg == 0) SKG(2);
             ok = ok && wait(&acc_full, seg & 1);
@@ -945,6 +946,57 @@ __global__ void __launch_bounds__(256) gemm_tc_skinny_sum_kernel(SkinnyParams p,
     }
 }
 
+// The residual add and the RMS norm that follows it in one pass over the partial tiles: block = token; acc = acc + W X
+// (stored), out = f16(norm(acc) * w). The sums are formed by 512 threads (many loads in flight) and left in shared
+// memory; the norm then runs with the thread layout, the order of additions and the rounding of rms_norm_block_kernel,
+// so that the result has the bits of the two kernels run one after the other.
+constexpr int SK_NORM_CHUNKS = 10;  // rows of up to 512 x 10 values
+__global__ void __launch_bounds__(512) gemm_tc_skinny_sum_norm_kernel(SkinnyParams p, uint32_t blocks, const float *w, __half *out, float eps) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float4 row[128 * SK_NORM_CHUNKS];
+    __shared__ uint32_t parts_s[4 * SK_NORM_CHUNKS];
+    __shared__ float red[4];
+    const uint32_t token = blockIdx.x, t = threadIdx.x, n = p.rows[0], nkst = p.cols / BK, tiles = n / BN;
+    if (t < tiles) parts_s[t] = skinny_owner(t * nkst + nkst - 1, p.units, blocks) - skinny_owner(t * nkst, p.units, blocks) + 1;
+    __syncthreads();
+    float *acc = p.y[0] + (size_t)token * n;
+    for (uint32_t f = t; f < n / 4; f += 512) {  // float4 f of the row: tile f / 32, place token x 32 + f % 32 in it
+        float4 a = skinny_tile_sum(p, f / (BN / 4), parts_s[f / (BN / 4)], token * (BN / 4) + f % (BN / 4));
+        const float4 r = reinterpret_cast<const float4 *>(acc)[f];
+        a = make_float4(r.x + a.x, r.y + a.y, r.z + a.z, r.w + a.w);
+        reinterpret_cast<float4 *>(acc)[f] = a;
+        row[f] = a;
+    }
+    __syncthreads();
+    if (t >= 128) return;
+    const uint32_t chunks = n / 512;
+    float4 v[SK_NORM_CHUNKS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < SK_NORM_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            v[c] = row[c * 128 + t];
+            ss += (v[c].x * v[c].x + v[c].y * v[c].y) + (v[c].z * v[c].z + v[c].w * v[c].w);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((t & 31) == 0) red[t >> 5] = ss;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    ss = (red[0] + red[1]) + (red[2] + red[3]);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    const float4 *wr = reinterpret_cast<const float4 *>(w);
+#pragma unroll
+    for (int c = 0; c < SK_NORM_CHUNKS; ++c) {
+        if (c < (int)chunks) {
+            const float4 ww = wr[c * 128 + t];
+            const float a = v[c].x * scale * ww.x, b = v[c].y * scale * ww.y, cc = v[c].z * scale * ww.z, d = v[c].w * scale * ww.w;
+            const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(cc, d);
+            reinterpret_cast<uint2 *>(out + (size_t)token * n)[c * 128 + t] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
@@ -961,7 +1013,7 @@ EncodeTiledFn encode_tiled() {
 
 // The few-token form: see gemm_tc_skinny_kernel. Every matrix is q4_0, tiled, rows a multiple of 128, rows of whole 16 bytes.
 int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens, const float *resid,
-                      __half *glu) {
+                      __half *glu, const float *norm_w = nullptr, __half *norm_out = nullptr, float eps = 0.0f) {
     brasa_ctx *ctx = cmd->ctx;
     SkinnyParams p{};
     SkinnyMaps maps;
@@ -1013,10 +1065,11 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     p.status = ctx->status;
     p.resid = resid;
     p.glu = glu;
+    p.defer = (glu || norm_out) ? 1u : 0u;
 #ifdef BRASA_TRACE_BUILD
     p.trace = (unsigned long long *)ctx->gemv_trace;
 #endif
-    if (max_parts > 1 || glu) {
+    if (max_parts > 1 || p.defer) {
         const size_t need = (size_t)tiles * max_parts * SK_TT * BN * sizeof(float);
         if (ctx->gemm_part_bytes < need) {
             BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K workspace cannot grow while a graph is recorded");
@@ -1043,6 +1096,10 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     cfg.numAttrs = 1;
     BRASA_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_skinny_kernel, tmap, maps, p));
     BRASA_TRY(brasa_post_launch(cmd, "gemm_tc_skinny"));
+    if (norm_out) {  // one matrix, Y = the residual stream itself: sum, residual add and the norm behind it
+        BRASA_CUDA(ctx, brasa_launch_dependent(ctx, gemm_tc_skinny_sum_norm_kernel, dim3(tokens), dim3(512), 0, p, blocks, norm_w, norm_out, eps));
+        return brasa_post_launch(cmd, "gemm_tc_skinny_sum_norm");
+    }
     if (max_parts == 1 && !glu) return BRASA_OK;
     BRASA_CUDA(ctx, brasa_launch_dependent(ctx, gemm_tc_skinny_sum_kernel, dim3(glu ? tiles / 2 : tiles, 8), dim3(256), 0, p, blocks));
     return brasa_post_launch(cmd, "gemm_tc_skinny_sum");
@@ -1066,6 +1123,14 @@ bool brasa_gemm_tc_few_tokens(brasa_ctx *ctx, const brasa_qmatrix *ws, uint32_t 
         tiles += ws[i].rows / BN;
     }
     return tiled_row_bytes(BRASA_Q4_0, ws[0].cols) % 16 == 0 && tiles * (ws[0].cols / BK) * (uint64_t)(ctx->sm_count + 1) < (1ull << 32);
+}
+
+// acc = acc + W X and out = f16(rms_norm(acc) * norm_w) for at most 64 tokens (brasa_gemm_tc_few_tokens holds for w, its rows
+// are a multiple of 512 up to 5120, pointers 16-byte aligned): the few-token kernel, then one kernel for sum, add and norm.
+int32_t brasa_gemm_tc_add_norm(brasa_cmd *cmd, const brasa_qmatrix &w, const __half *x, float *acc, const float *norm_w, __half *out, uint32_t tokens,
+                               float eps) {
+    float *ys[1] = {acc};
+    return launch_skinny(cmd, 1, &w, x, ys, tokens, acc, nullptr, norm_w, out, eps);
 }
 
 // Y_i = W_i X for 1 to 3 matrices that share X (f16, [tokens][cols]); every W_i must pass brasa_gemm_tc_supported.

@@ -163,6 +163,10 @@ int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg
 /* acc += W x for f16 inputs: the layer's residual add folded into the GEMM (scratch: tokens x rows f32, used when the
  * product takes the generic kernel). New: the reference adds with a separate `add` dispatch (qwen3.rs:810-826). */
 int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, uint32_t tokens);        /* :842 */
+/* acc += W x, then out_f16 = f16(rms_norm(acc) * norm_w): a layer's residual add and the norm that opens the next block
+ * (qwen3.rs:810-826 then :700-712 as one call). One GEMM and one kernel behind it for up to 64 tokens; otherwise the two calls. */
+int32_t brasa_k_gemm_add_rms_norm_f16(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, brasa_arg norm_w,
+                                      brasa_arg out_f16, uint32_t tokens, float eps);
 int32_t brasa_k_gemm_multi(brasa_cmd *cmd, const brasa_qmatrix *ws, uint32_t count, brasa_arg x, const brasa_arg *ys, uint32_t tokens, int32_t precision); /* :872 */
 /* out_f16[t, :] = f16(silu(Wg x) * (Wu x)); gate/up scratch [tokens, rows] f32 may be used :455 */
 int32_t brasa_k_gemm_swiglu(brasa_cmd *cmd, brasa_qmatrix wg, brasa_qmatrix wu, brasa_arg x_f16, brasa_arg gate, brasa_arg up, brasa_arg out_f16, uint32_t tokens);

@@ -586,6 +586,32 @@ def test_gemm_few_tokens_persistent(B, ctx, K, rows, cols):
             assert np.array_equal(ga.download(np.float32), acc0 + first[0])
 
 
+@pytest.mark.parametrize("rows,cols,tokens", [(2560, 4096, 40), (2560, 9728, 64), (5120, 512, 9), (1024, 512, 33), (2560, 4096, 100)])
+def test_gemm_add_rms_norm_equals_the_two_calls(B, ctx, K, rows, cols, tokens):
+    """acc += W x followed by the RMS norm of acc, as one call: behind the few-token GEMM one kernel adds the blocks' partial
+    tiles and the residual and forms the norm; shapes it does not take fall back to the two calls. Same bits either way."""
+    rng = O.Rng(59)
+    raw = rng.qmatrix(O.Q4_0, rows, cols)
+    m = tiled(B, ctx, K, "q4_0", raw, rows, cols)[0]
+    xh = rng.vec(tokens * cols, 1.0).astype(np.float16)
+    acc0, wn = rng.vec(tokens * rows, 2.0), rng.vec(rows, 1.0)
+    gx, gs, gw = ctx.buffer_from(xh), ctx.buffer(tokens * rows * 4), ctx.buffer_from(wn)
+    ga, gb = ctx.buffer_from(acc0), ctx.buffer_from(acc0)
+    oa, ob = ctx.buffer(tokens * rows * 2), ctx.buffer(tokens * rows * 2)
+    run(ctx, lambda c: (K.gemm_add(c, m, gx, ga, gs, tokens), K.rms_norm_f16(c, ga, gw, oa, tokens, rows, 1e-6)))
+    run(ctx, lambda c: K.gemm_add_rms_norm_f16(c, m, gx, gb, gs, gw, ob, tokens, 1e-6))
+    assert np.array_equal(ga.download(np.float32), gb.download(np.float32))
+    assert np.array_equal(oa.download(np.uint16, tokens * rows), ob.download(np.uint16, tokens * rows))
+    # and in place: the norm written over the GEMM's input, as the layer loop does
+    if cols == rows:
+        return
+    gb2 = ctx.buffer_from(acc0)
+    gx2 = ctx.buffer(max(tokens * cols, tokens * rows) * 2)
+    gx2.upload(xh)
+    run(ctx, lambda c: K.gemm_add_rms_norm_f16(c, m, gx2, gb2, gs, gw, gx2, tokens, 1e-6))
+    assert np.array_equal(gx2.download(np.uint16, tokens * rows), oa.download(np.uint16, tokens * rows))
+
+
 @pytest.mark.parametrize("tokens", [16, 200])
 def test_gemm_tiled_q6_tensor_core(B, ctx, K, tokens):
     """A tiled q6_0 matrix whose rows are a multiple of 128 (the tied lm_head of a batch step) runs on the tcgen05 GEMM:
