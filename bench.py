@@ -55,8 +55,10 @@ GATE_UP_TRAFFIC_BYTES = 28_130_000
 TOKEN_KERNEL_TRAFFIC_BYTES = 2_452_740_000
 # dram__bytes_read + dram__bytes_write of one serving decode step of 64 sequences (all its kernels, summed) under ncu,
 # captured at the first steps of the leg, where a step's algorithmic bytes are the second figure; the leg scales the
-# traffic to its own mean position by its algorithmic bytes (the KV share grows in proportion, the weights do not move)
-SERVING_STEP_TRAFFIC_BYTES = 14_554_000_000
+# traffic to its own mean position by its algorithmic bytes (the KV share grows in proportion, the weights do not move).
+# ncu empties the caches before every kernel, so the GEMMs' partial tiles (about 1.0 GB of this) come back from DRAM
+# there and out of L2 in the timed run: an upper bound.
+SERVING_STEP_TRAFFIC_BYTES = 15_283_000_000
 SERVING_STEP_TRAFFIC_AT_ALGORITHMIC_BYTES = 12_387_561_504
 METRIC = "qwen3_4b_q4_bs1_decode_tok_s"
 WORKLOAD = "qwen3-4b-arch q4_0/q6_0 .brasa, bs1, 512-token seeded prompt + 256 greedy tokens, KV f16, ctx 2048"
