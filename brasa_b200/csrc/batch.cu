@@ -183,17 +183,30 @@ __global__ void __launch_bounds__(128) decode_partial_paged_mma_kernel(const flo
     }
     const uint32_t key0 = chunk * 128, nkeys = min(128u, lk - key0);
     const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
-    // ---- K then V: 128 rows x 16 pieces each; rows past the end are zero-filled ----
-    for (uint32_t i = t; i < 128 * 16; i += 128) {
-        const uint32_t r = i >> 4, c = i & 15;
+    // ---- K then V: 128 rows x 16 pieces each; rows past the end are zero-filled. The chunk's eight page numbers are read
+    // first, all at once: a look-up in front of every copy (which the copies' ordering keeps in program order) held a block
+    // for thirty-two L2 round trips before its first product ----
+    int32_t pg[8];
+    {
+        const int32_t *trow = kp.table + (size_t)seq00 * kp.max_pages + key0 / PAGE;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pg[j] = (uint32_t)(j * PAGE) < nkeys ? trow[j] : trow[0];
+    }
+    const uint32_t r_lo = t >> 4, pc = t & 15;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const uint32_t r = 8 * k + r_lo;
         const bool ok = r < nkeys;
-        cp_async16_zfill(kt + piece(r, c), paged_row<BRASA_KV_F16>(kp, seq00, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        const size_t row = ((size_t)(ok ? pg[k >> 1] : pg[0]) * PAGE + (ok ? (r & (PAGE - 1)) : 0u)) * hkv + kh;
+        cp_async16_zfill(kt + piece(r, pc), kp.pool + row * KvRow<BRASA_KV_F16>::BYTES + 16 * pc, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    for (uint32_t i = t; i < 128 * 16; i += 128) {
-        const uint32_t r = i >> 4, c = i & 15;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const uint32_t r = 8 * k + r_lo;
         const bool ok = r < nkeys;
-        cp_async16_zfill(vt + piece(r, c), paged_row<BRASA_KV_F16>(vp, seq00, key0 + (ok ? r : 0), kh) + 16 * c, ok);
+        const size_t row = ((size_t)(ok ? pg[k >> 1] : pg[0]) * PAGE + (ok ? (r & (PAGE - 1)) : 0u)) * hkv + kh;
+        cp_async16_zfill(vt + piece(r, pc), vp.pool + row * KvRow<BRASA_KV_F16>::BYTES + 16 * pc, ok);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");

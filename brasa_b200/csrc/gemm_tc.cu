@@ -551,7 +551,7 @@ struct SkinnyParams {
     float *y[3];
     uint32_t rows[3];
     uint32_t tile_end[3];  // 128-row tiles of matrices 0..i, cumulative
-    uint32_t cols, tokens, stages, raw_slots;
+    uint32_t cols, tokens, raw_slots;
     uint32_t units;      // row tiles x K stages of the launch
     uint32_t max_parts;  // most blocks that share one tile
     uint32_t *status;
@@ -1058,7 +1058,6 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     }
     p.cols = cols;
     p.tokens = tokens;
-    p.stages = 4 * SK_NCS;
     p.raw_slots = 7;
     p.units = units;
     p.max_parts = max_parts;
