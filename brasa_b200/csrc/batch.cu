@@ -357,10 +357,11 @@ __global__ void __launch_bounds__(128) decode_reduce_paged_kernel(const float *p
     const uint32_t h = blockIdx.x, seq = blockIdx.y, t = threadIdx.x;
     const uint32_t chunks = (lens[seq] + 1 + 127) / 128;
     const float *p = partials + ((size_t)seq * hq + h) * max_chunks * 130;
-    float M = -INFINITY;
-    for (uint32_t c = 0; c < chunks; ++c) M = fmaxf(M, p[c * 130]);
+    float M = -INFINITY;  // (a lane per chunk: one round trip for all the maxima, whatever the number of chunks)
+    for (uint32_t c = t & 31; c < chunks; c += 32) M = fmaxf(M, p[c * 130]);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     float L = 0.0f, acc = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
     for (uint32_t c = 0; c < chunks; ++c) {  // (unrolled: the chunks' loads are independent, only the sums are a chain)
         float w = expf(p[c * 130] - M);
         L = fmaf(p[c * 130 + 1], w, L);
