@@ -348,8 +348,8 @@ def prefill_16k(B, ctx, path, cfg, kv_name: str, cpu_steps: int = 0):
     ids = np.random.default_rng(SEED + 16).integers(0, cfg["vocab_size"], size=n_prompt).astype(np.uint32)
     m = B.Qwen3.load(ctx, path, B.Limits(ctx=n_prompt + 256, max_tokens=chunk, max_logit_rows=1, kv=kvt))
     try:
-        # the prompt goes through twice: the first pass also pays what a process pays once (kernels loaded on first use,
-        # workspaces grown); the second, over the same positions, is the one reported
+        # the prompt goes through twice over the same positions and the faster pass is reported: one pass alone carries what
+        # a process pays once (kernels loaded on first use, workspaces grown) or a moment of another clock
         passes = []
         lg = None
         for _ in range(2):
@@ -358,6 +358,7 @@ def prefill_16k(B, ctx, path, cfg, kv_name: str, cpu_steps: int = 0):
                 lg, s = m.forward(ids[off:off + chunk], off, want_logits=off + chunk >= n_prompt)
                 secs += s
             passes.append(secs)
+        secs = min(passes)
         first = int(np.argmax(lg[0]))
         m.decode_greedy(first, n_prompt, 4)
         toks, dsecs = m.decode_greedy(first, n_prompt, ntok)
@@ -370,7 +371,7 @@ def prefill_16k(B, ctx, path, cfg, kv_name: str, cpu_steps: int = 0):
         per_token = synth.weight_bytes_per_token(cfg) + synth.kv_bytes_per_position(cfg, kv_name) * (n_prompt + 1 + (ntok - 1) / 2.0)
         hbm, _ = measured_peaks()
         out = {"prompt_tokens": n_prompt, "chunk": chunk, "kv": kv_name, "prefill_tok_s": n_prompt / secs, "prefill_s": secs,
-               "prefill_s_first_pass": passes[0], "tflops": flops / secs / 1e12, "decode_steps": ntok, "decode_tok_s_at_16k": ntok / dsecs,
+               "prefill_s_passes": passes, "tflops": flops / secs / 1e12, "decode_steps": ntok, "decode_tok_s_at_16k": ntok / dsecs,
                "decode_bytes_per_token": per_token, "decode_frac_of_measured_hbm": per_token * ntok / dsecs / 1e9 / hbm}
         if cpu_steps > 0:
             try:
