@@ -1012,6 +1012,7 @@ EncodeTiledFn encode_tiled() {
 }
 
 // The few-token form: see gemm_tc_skinny_kernel. Every matrix is q4_0, tiled, rows a multiple of 128, rows of whole 16 bytes.
+// (brasa_gemm_few_tokens_plan, below the namespace, is the one place that decides the cut.)
 int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, const __half *x, float *const *ys, uint32_t tokens, const float *resid,
                       __half *glu, const float *norm_w = nullptr, __half *norm_out = nullptr, float eps = 0.0f) {
     brasa_ctx *ctx = cmd->ctx;
@@ -1028,10 +1029,9 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
         p.tile_end[i] = tiles;
     }
     const uint32_t cols = ws[0].cols, nkst = cols / BK, units = tiles * nkst;
-    const uint32_t blocks = std::min<uint32_t>((uint32_t)ctx->sm_count, std::max(1u, units / 4));  // a run keeps at least four stages
-    uint32_t max_parts = 1;
-    for (uint32_t t = 0; t < tiles; ++t)
-        max_parts = std::max(max_parts, skinny_owner(t * nkst + nkst - 1, units, blocks) - skinny_owner(t * nkst, units, blocks) + 1);
+    uint32_t blocks = 0, max_parts = 0;
+    uint64_t scratch = 0;
+    BRASA_REQUIRE(ctx, brasa_gemm_few_tokens_plan((uint32_t)ctx->sm_count, tiles, nkst, &blocks, &max_parts, &scratch) == BRASA_OK, "gemm: shape outside the few-token kernel");
     BRASA_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x) & 15) == 0, "gemm: misaligned x");
     CUtensorMap tmap;
     {
@@ -1069,7 +1069,7 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
     p.trace = (unsigned long long *)ctx->gemv_trace;
 #endif
     if (max_parts > 1 || p.defer) {
-        const size_t need = (size_t)tiles * max_parts * SK_TT * BN * sizeof(float);
+        const size_t need = (size_t)scratch;
         if (ctx->gemm_part_bytes < need) {
             BRASA_REQUIRE(ctx, !ctx->capturing, "gemm: the split-K workspace cannot grow while a graph is recorded");
             BRASA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -1105,6 +1105,27 @@ int32_t launch_skinny(brasa_cmd *cmd, uint32_t count, const brasa_qmatrix *ws, c
 }
 
 }  // namespace
+
+// How a product of up to 64 tokens is cut over the SMs (include/brasa_cuda.h): the (tile, stage) units in order, `blocks`
+// equal runs, run b = units [b units / blocks, (b + 1) units / blocks).
+extern "C" int32_t brasa_gemm_few_tokens_plan(uint32_t sm_count, uint32_t tiles, uint32_t stages, uint32_t *blocks, uint32_t *max_parts,
+                                              uint64_t *scratch_bytes) {
+    if (!blocks || !max_parts || !scratch_bytes || sm_count == 0 || tiles == 0 || stages == 0) return BRASA_EINVAL;
+    if ((uint64_t)tiles * stages * ((uint64_t)sm_count + 1) >= (1ull << 32)) return BRASA_EINVAL;  // the kernels divide 32-bit numbers
+    const uint32_t units = tiles * stages;
+    const uint32_t nb = std::min<uint32_t>(sm_count, std::max(1u, units / 4));  // a run keeps at least four stages
+    uint32_t mp = 1;
+    for (uint32_t t = 0; t < tiles; ++t) mp = std::max(mp, skinny_owner(t * stages + stages - 1, units, nb) - skinny_owner(t * stages, units, nb) + 1);
+    *blocks = nb;
+    *max_parts = mp;
+    *scratch_bytes = (uint64_t)tiles * mp * SK_TT * BN * sizeof(float);
+    return BRASA_OK;
+}
+
+extern "C" uint32_t brasa_gemm_few_tokens_owner(uint32_t units, uint32_t blocks, uint32_t unit) {
+    if (units == 0 || blocks == 0 || blocks > units || unit >= units || (uint64_t)units * ((uint64_t)blocks + 1) >= (1ull << 32)) return UINT32_MAX;
+    return skinny_owner(unit, units, blocks);
+}
 
 // True when the tensor-core kernel takes this product (the caller falls back to the warp-MMA kernel otherwise).
 bool brasa_gemm_tc_supported(const brasa_qmatrix &w, uint32_t tokens) {

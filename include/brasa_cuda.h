@@ -163,6 +163,15 @@ int32_t brasa_k_gemm(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg
 /* acc += W x for f16 inputs: the layer's residual add folded into the GEMM (scratch: tokens x rows f32, used when the
  * product takes the generic kernel). New: the reference adds with a separate `add` dispatch (qwen3.rs:810-826). */
 int32_t brasa_k_gemm_add(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, uint32_t tokens);        /* :842 */
+/* How a product of 9 to 64 tokens with tiled q4_0 matrices is cut over the SMs (no counterpart in the reference: its Metal
+ * GEMM takes one threadgroup per output tile, matmul_tiled.metal:35-53). The (128-row tile, 64-column stage) pairs of the
+ * launch's matrices, in that order, are `tiles x stages` units; block b of `blocks` takes units [b units / blocks,
+ * (b + 1) units / blocks). A tile shared by several blocks is summed from their partial tiles in K order by a second kernel;
+ * `max_parts` is the most blocks that share a tile and `scratch_bytes` what the library keeps for the partial tiles (inside
+ * the planners' overhead allowance). BRASA_EINVAL for an empty shape or one whose unit count does not fit 32-bit arithmetic. */
+int32_t brasa_gemm_few_tokens_plan(uint32_t sm_count, uint32_t tiles, uint32_t stages, uint32_t *blocks, uint32_t *max_parts, uint64_t *scratch_bytes);
+/* the block whose run holds `unit` (UINT32_MAX for arguments outside a plan) */
+uint32_t brasa_gemm_few_tokens_owner(uint32_t units, uint32_t blocks, uint32_t unit);
 /* acc += W x, then out_f16 = f16(rms_norm(acc) * norm_w): a layer's residual add and the norm that opens the next block
  * (qwen3.rs:810-826 then :700-712 as one call). One GEMM and one kernel behind it for up to 64 tokens; otherwise the two calls. */
 int32_t brasa_k_gemm_add_rms_norm_f16(brasa_cmd *cmd, brasa_qmatrix w, brasa_arg x_f16, brasa_arg acc, brasa_arg scratch, brasa_arg norm_w,

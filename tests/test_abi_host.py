@@ -164,3 +164,37 @@ def test_batch_planner_arithmetic_and_largest_batch(B):
     sh = B.planner.plan_batch(shape, 16, 2048 // 16 + 16 * 97, 3600, B.KvType.F16, head_rows=151936 // 8)
     assert sh["logits"] == bb(16 * (151936 // 8) * 4)
     assert sh["sampler"] == bb(16 * 2 * 151936 * 4) + 2 * bb(16 * 151936 * 4)
+
+
+def test_few_token_gemm_partition(B):
+    """The cut of a few-token GEMM over the SMs (`brasa_gemm_few_tokens_plan`): the runs tile the units exactly, every
+    unit's owner is the block whose run holds it, the blocks that share a tile are consecutive and never more than
+    `max_parts`, and the scratch holds one 64 x 128 f32 tile per (tile, part). Shapes: the Qwen3-4B layer at 148 SMs
+    (qkv, o, gate + up, down), a shard's, tiny ones, and one too large for 32-bit unit arithmetic."""
+    L = B.lib()
+    L.brasa_gemm_few_tokens_plan.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]
+    L.brasa_gemm_few_tokens_plan.restype = C.c_int32
+    L.brasa_gemm_few_tokens_owner.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32]
+    L.brasa_gemm_few_tokens_owner.restype = C.c_uint32
+    for sms, tiles, stages in [(148, 48, 40), (148, 20, 64), (148, 152, 40), (148, 20, 152), (148, 1, 4), (148, 3, 4), (148, 1, 1), (132, 25, 38),
+                               (148, 200, 4), (7, 5, 9)]:
+        blocks, parts, scratch = C.c_uint32(), C.c_uint32(), C.c_uint64()
+        assert L.brasa_gemm_few_tokens_plan(sms, tiles, stages, C.byref(blocks), C.byref(parts), C.byref(scratch)) == 0
+        nb, units = blocks.value, tiles * stages
+        assert 1 <= nb <= min(sms, units) and (nb == sms or nb == max(1, units // 4))
+        beg = [b * units // nb for b in range(nb + 1)]
+        assert beg[0] == 0 and beg[-1] == units and all(beg[b] < beg[b + 1] for b in range(nb))  # no empty run
+        owner = [L.brasa_gemm_few_tokens_owner(units, nb, u) for u in range(units)]
+        for u, b in enumerate(owner):
+            assert beg[b] <= u < beg[b + 1], (u, b)
+        worst = 0
+        for t in range(tiles):
+            own = owner[t * stages:(t + 1) * stages]
+            assert own == sorted(own) and set(own) == set(range(own[0], own[-1] + 1))  # consecutive blocks, in K order
+            worst = max(worst, own[-1] - own[0] + 1)
+        assert parts.value == worst
+        assert scratch.value == tiles * worst * 64 * 128 * 4
+    blocks, parts, scratch = C.c_uint32(), C.c_uint32(), C.c_uint64()
+    assert L.brasa_gemm_few_tokens_plan(148, 1 << 20, 1 << 6, C.byref(blocks), C.byref(parts), C.byref(scratch)) != 0
+    assert L.brasa_gemm_few_tokens_plan(148, 0, 4, C.byref(blocks), C.byref(parts), C.byref(scratch)) != 0
+    assert L.brasa_gemm_few_tokens_owner(100, 10, 100) == 0xFFFFFFFF
