@@ -6,6 +6,7 @@
 #include "decode_token.h"
 
 bool brasa_gemm_swiglu_fuses(const brasa_qmatrix &wg, const brasa_qmatrix &wu, uint32_t tokens);
+
 namespace brasa_model_detail {
 
 constexpr uint32_t GEMV_MAX_TOKENS = 8;  // qwen3.rs:276
